@@ -1,0 +1,112 @@
+/*
+ * C ABI of the B200 (sm_100a) implementation of NestQuant's W4A4KV4 hot path.
+ *
+ * Conventions (all entry points):
+ *   - plain pointers and sizes, no framework types; every pointer is a DEVICE
+ *     pointer unless its name ends in _host;
+ *   - the caller owns every buffer, passes the CUDA stream explicitly and
+ *     supplies workspaces; nothing here allocates device memory, synchronises
+ *     the host, or keeps global state, so every call can be captured in a
+ *     CUDA graph;
+ *   - return value 0 = success, negative = argument error (NQ_ERR_*), positive
+ *     = cudaError_t of the failed launch; nq_last_error() describes the last
+ *     failure of the calling thread;
+ *   - q = 14, 4-bit residues, four betas (2-bit ids): the NQRT4 / NQA4 / NQKV4
+ *     formats of the reference (core/packing.py:137-208: value i of width w in
+ *     byte floor(i*w/8), bit offset (i*w) mod 8, LSB first).
+ *
+ * Each declaration cites the reference interface it replaces
+ * (file:line inside the reference project).
+ */
+#ifndef NQ_B200_H
+#define NQ_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* nq_stream_t; /* cudaStream_t */
+
+enum { NQ_F32 = 0, NQ_BF16 = 1, NQ_F16 = 2 };
+
+enum {
+    NQ_OK = 0,
+    NQ_ERR_ARG = -1,       /* null pointer, bad size, unsupported shape */
+    NQ_ERR_ALIGN = -2,     /* pointer or stride not 16-byte aligned */
+    NQ_ERR_WORKSPACE = -3, /* workspace missing or too small */
+    NQ_ERR_DEVICE = -4     /* not an sm_100 device / driver entry point missing */
+};
+
+int nq_abi_version(void);
+const char* nq_last_error(void);
+
+/* -------------------------------------------------------------------------
+ * On-the-fly E8 encoder (activations, and K/V rows with k = head_dim).
+ * Replaces quantize_activation_cuda (runtime/triton_w4a4_linear.py:581-617) =
+ * torch vector_norm + _nqkv_encode_kernel (runtime/nqkv_page.py:97-185,332-372)
+ * + two _pack_unsigned_cuda chains (runtime/nqkv_page.py:446-456), in ONE launch.
+ * Bit-exact with quantize_rows + pack_nestquant_indices on the CPU
+ * (core/quantizer.py:214-301, core/packing.py:137-171).
+ *
+ *   x            [rows, k] of x_dtype, row r at x + r*row_stride elements
+ *   beta_table   4 floats
+ *   out_codes    rows*k/2 bytes, out_beta_ids rows*k/32 bytes, out_norms rows floats
+ *   out_decoded  optional (may be NULL): bf16 [rows, k] reconstruction
+ *                bf16(((t - 14 Q(t/14)) * beta) * (norm / sqrt(k)))
+ * Requirements: k % 32 == 0, 32 <= k <= 32768, 16-byte aligned x and stride. */
+int nq_a4_encode(const void* x, int x_dtype, int64_t rows, int64_t k, int64_t row_stride,
+                 const float* beta_table, uint8_t* out_codes, uint8_t* out_beta_ids,
+                 float* out_norms, void* out_decoded, nq_stream_t stream);
+
+/* Diagnostic / operand decode of a packed undithered stream.
+ * Replaces decode_packed_a4_m16 (runtime/cuda_w4a4_mma.py:688-696, kernel
+ * nqrt4_w4a4_mma.cu:83-93) and dequantize_nqkv_page_triton
+ * (runtime/nqkv_page.py:494-537).  Output is bit-identical to
+ * QuantizedRows.dequantize (core/quantizer.py:39-51), then cast to out_dtype
+ * (NQ_F32 or NQ_BF16). */
+int nq_a4_decode(const uint8_t* codes, const uint8_t* beta_ids, const float* norms,
+                 const float* beta_table, int64_t rows, int64_t k, void* out, int out_dtype,
+                 nq_stream_t stream);
+
+/* -------------------------------------------------------------------------
+ * Packed W4A4 projection  Y[m,n] = sum_k bf16(A^[m,k]) * bf16(W^[n,k]).
+ * One entry for every M regime; replaces the pybind family run_m1 / run_small_m /
+ * run_m16 / run_large_m_staged (runtime/nqrt4_w4a4_mma_binding.cpp:51-69) and the
+ * Python chunk+pad wrapper (runtime/cuda_w4a4_mma.py:393-484).
+ *
+ *   act_*      packed activation streams of m rows (from nq_a4_encode)
+ *   act_decoded optional bf16 [m,k] produced by nq_a4_encode; NULL = decode here
+ *   w_*        NQRT4 streams of n rows: codes n*k/2 bytes, beta ids n*k/32, norms n, betas 4
+ *   w_block_offset  global index of the weight's first E8 block in its record
+ *              (the dither counter of block b of row r is w_block_offset + r*k/8 + b);
+ *              the reference always passes 0 (runtime/cuda_w4a4_mma.py:243)
+ *   seed       stateless dither seed of the record, in [0, 2^31)
+ *   out        [m, n] of out_dtype (NQ_F32 = accumulator before rounding, NQ_BF16)
+ *   workspace  at least nq_w4a4_workspace_bytes(m,n,k) bytes; its first
+ *              NQ_WS_COUNTER_BYTES bytes must be zero before the FIRST use and are
+ *              left zero by every call.
+ * Requirements: k % 32 == 0, n % 8 == 0. */
+#define NQ_WS_COUNTER_BYTES 65536
+size_t nq_w4a4_workspace_bytes(int64_t m, int64_t n, int64_t k);
+int nq_w4a4_gemm(const uint8_t* act_codes, const uint8_t* act_beta_ids, const float* act_norms,
+                 const float* act_betas, const void* act_decoded,
+                 const uint8_t* w_codes, const uint8_t* w_beta_ids, const float* w_norms,
+                 const float* w_betas, int64_t m, int64_t n, int64_t k,
+                 int64_t w_block_offset, int64_t seed, void* out, int out_dtype,
+                 void* workspace, size_t workspace_bytes, nq_stream_t stream);
+
+/* Decode a packed NQRT4 weight to bf16 [n,k] (dither regenerated on the fly);
+ * bit-identical to bf16(QuantizedRows.dequantize) of the record
+ * (core/quantizer.py:39-51, dither core/codec.py:176-224).  Used by the
+ * large-M path and by parity tests. */
+int nq_w4_decode(const uint8_t* w_codes, const uint8_t* w_beta_ids, const float* w_norms,
+                 const float* w_betas, int64_t n, int64_t k, int64_t w_block_offset,
+                 int64_t seed, void* out_bf16, nq_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NQ_B200_H */

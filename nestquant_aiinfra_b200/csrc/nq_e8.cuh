@@ -1,0 +1,284 @@
+// Nested-E8 codec arithmetic shared by every kernel of the W4A4KV4 path.
+//
+// The functions are written once for host and device: device builds use the
+// IEEE round-to-nearest intrinsics (which the compiler never contracts into
+// FMAs), host builds (g++ -ffp-contract=off) use plain operators.  The host
+// build exists so the CPU test-suite can run exactly this source against the
+// CPU checker before any GPU time is spent.
+//
+// "exact" functions reproduce the float32 operation ORDER of the reference's
+// CPU path (nestquant/core/lattice.py:18-81, codec.py:53-142,
+// quantizer.py:257-301): sequential 8-term error sums, strict "<" between the
+// two E8 cosets, first-max / first-min tie rules.  They are used wherever the
+// result must be bit-identical (the encoder, and every decode of an
+// undithered stream, where exact Voronoi-boundary ties do occur).
+#pragma once
+
+#include <stdint.h>
+#include <string.h>
+#include <math.h>
+
+#if defined(__CUDACC__)
+#define NQ_HD __host__ __device__ __forceinline__
+#else
+#define NQ_HD inline
+#endif
+
+#define NQ_Q 14
+#define NQ_MAGIC 12582912.0f /* 1.5 * 2^23: adding it rounds to nearest-even integer */
+
+NQ_HD float nq_add(float a, float b) {
+#if defined(__CUDA_ARCH__)
+    return __fadd_rn(a, b);
+#else
+    return a + b;
+#endif
+}
+NQ_HD float nq_sub(float a, float b) {
+#if defined(__CUDA_ARCH__)
+    return __fsub_rn(a, b);
+#else
+    return a - b;
+#endif
+}
+NQ_HD float nq_mul(float a, float b) {
+#if defined(__CUDA_ARCH__)
+    return __fmul_rn(a, b);
+#else
+    return a * b;
+#endif
+}
+NQ_HD float nq_div(float a, float b) {
+#if defined(__CUDA_ARCH__)
+    return __fdiv_rn(a, b);
+#else
+    return a / b;
+#endif
+}
+NQ_HD float nq_rcp(float a) {
+#if defined(__CUDA_ARCH__)
+    return __frcp_rn(a);
+#else
+    return 1.0f / a;
+#endif
+}
+NQ_HD float nq_sqrt(float a) {
+#if defined(__CUDA_ARCH__)
+    return __fsqrt_rn(a);
+#else
+    return sqrtf(a);
+#endif
+}
+NQ_HD int nq_float_bits(float v) {
+#if defined(__CUDA_ARCH__)
+    return __float_as_int(v);
+#else
+    int b;
+    memcpy(&b, &v, 4);
+    return b;
+#endif
+}
+NQ_HD float nq_bits_float(uint32_t b) {
+#if defined(__CUDA_ARCH__)
+    return __uint_as_float(b);
+#else
+    float v;
+    memcpy(&v, &b, 4);
+    return v;
+#endif
+}
+
+// float32 -> bfloat16 (round to nearest even) -> float32, finite inputs only.
+NQ_HD float nq_bf16_round(float v) {
+    uint32_t u = (uint32_t)nq_float_bits(v);
+    u += 0x7fffu + ((u >> 16) & 1u);
+    return nq_bits_float(u & 0xffff0000u);
+}
+NQ_HD uint32_t nq_bf16_bits(float v) {
+    uint32_t u = (uint32_t)nq_float_bits(v);
+    u += 0x7fffu + ((u >> 16) & 1u);
+    return u >> 16;
+}
+
+// ---------------------------------------------------------------- E8 ------
+
+// Nearest point of D8 = {z in Z^8, sum even}; exact reference order.
+// Rounding uses the magic-constant trick (valid for |y| < 2^22, far above
+// any normalised value here); the low mantissa bit of the shifted value is
+// the parity of the rounded integer, so no float->int conversion is needed.
+NQ_HD void nq_d8_nearest_exact(const float y[8], float r[8]) {
+    float e[8];
+    int parity = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const float t = nq_add(y[j], NQ_MAGIC);
+        r[j] = nq_sub(t, NQ_MAGIC);
+        parity ^= nq_float_bits(t);
+        e[j] = nq_sub(y[j], r[j]);
+    }
+    float best = fabsf(e[0]);
+    int jm = 0;
+#pragma unroll
+    for (int j = 1; j < 8; ++j) {
+        const float a = fabsf(e[j]);
+        if (a > best) { best = a; jm = j; }
+    }
+    if (parity & 1) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            if (j == jm) r[j] = nq_add(r[j], e[j] >= 0.0f ? 1.0f : -1.0f);
+    }
+}
+
+NQ_HD float nq_sqdist8_seq(const float a[8], const float b[8]) {
+    float acc = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const float d = nq_sub(a[j], b[j]);
+        acc = nq_add(acc, nq_mul(d, d));
+    }
+    return acc;
+}
+
+// Nearest E8 point, half-integer coset wins ties (strict "<" for the integer
+// coset) -- the "e8_upstream_half_coset_tie_v1" semantic.
+NQ_HD void nq_e8_nearest_exact(const float x[8], float out[8]) {
+    float p0[8], p1[8], y[8];
+    nq_d8_nearest_exact(x, p0);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) y[j] = nq_sub(x[j], 0.5f);
+    nq_d8_nearest_exact(y, p1);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) p1[j] = nq_add(p1[j], 0.5f);
+    const float e0 = nq_sqdist8_seq(x, p0);
+    const float e1 = nq_sqdist8_seq(x, p1);
+    const bool integer_coset = e0 < e1;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) out[j] = integer_coset ? p0[j] : p1[j];
+}
+
+// Exact int -> float for |v| < 2^22 without the (slow) conversion unit: the
+// integer is added into the mantissa of the magic constant.
+NQ_HD float nq_small_int_to_float(int v) {
+    return nq_sub(nq_bits_float(0x4B400000u + (uint32_t)v), NQ_MAGIC);
+}
+
+// coset representative G*c of integer coordinates c (codec.py:30-43).
+NQ_HD void nq_generator_apply(const int c[8], float t[8]) {
+    const float h = 0.5f * nq_small_int_to_float(c[7]);
+    t[0] = nq_small_int_to_float(2 * c[0] - c[1]) + h;
+#pragma unroll
+    for (int j = 1; j < 6; ++j) t[j] = nq_small_int_to_float(c[j] - c[j + 1]) + h;
+    t[6] = nq_small_int_to_float(c[6]) + h;
+    t[7] = h;
+}
+
+// Same from a packed codeword (coordinate j in bits [4j, 4j+3]).
+NQ_HD void nq_codeword_coset(uint32_t word, float t[8]) {
+    int c[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) c[j] = (int)((word >> (4 * j)) & 15u);
+    nq_generator_apply(c, t);
+}
+
+// Integer coordinates of a lattice point, reduced modulo q, as a codeword.
+// All intermediate values are exact small integers in float32.
+NQ_HD uint32_t nq_lattice_to_codeword(const float l[8]) {
+    float c[8];
+    c[7] = 2.0f * l[7];
+    c[6] = l[6] - l[7];
+    c[5] = l[5] + c[6] - l[7];
+    c[4] = l[4] + c[5] - l[7];
+    c[3] = l[3] + c[4] - l[7];
+    c[2] = l[2] + c[3] - l[7];
+    c[1] = l[1] + c[2] - l[7];
+    c[0] = 0.5f * (l[0] + c[1] - l[7]);
+    uint32_t word = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        // c is an exact integer with |c| < 2^22: it can be read back from the
+        // mantissa of (c + magic) without a float->int conversion.
+        const int v = (nq_float_bits(nq_add(c[j], NQ_MAGIC)) & 0x7fffff) - 0x400000;
+        int m = v % NQ_Q;
+        m += (m < 0) ? NQ_Q : 0;
+        word |= (uint32_t)m << (4 * j);
+    }
+    return word;
+}
+
+// Minimum-energy representative of the coset of `word`:  t - q*Q(t/q), with
+// the optional dither subtracted first (weights).  Exact reference order.
+NQ_HD void nq_decode_codeword_exact(uint32_t word, const float* dither, float r[8]) {
+    float t[8], s[8], n[8];
+    nq_codeword_coset(word, t);
+    if (dither) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) t[j] = nq_sub(t[j], dither[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s[j] = nq_div(t[j], 14.0f);
+    nq_e8_nearest_exact(s, n);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) r[j] = nq_sub(t[j], nq_mul(14.0f, n[j]));
+}
+
+// ------------------------------------------------------------ dither ------
+
+// "lcg31_mix_v1" (codec.py:204-221): every stage reduced modulo 2^31.
+NQ_HD uint32_t nq_lcg31_mix(uint32_t counter_plus_seed) {
+    uint32_t v = counter_plus_seed & 0x7fffffffu;
+    v ^= v >> 16;
+    v = (v * 1103515245u + 12345u) & 0x7fffffffu;
+    v ^= v >> 13;
+    v = (v * 134775813u + 1u) & 0x7fffffffu;
+    v ^= v >> 16;
+    return v;
+}
+
+// Subtractive dither of one global block: u - Q(u), u uniform in [0,2)^8.
+// `base` = (8*global_block + seed) mod 2^32 (only its low 31 bits matter).
+NQ_HD void nq_dither_block(uint32_t base, float d[8]) {
+    float u[8], n[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) u[j] = (float)nq_lcg31_mix(base + (uint32_t)j) * (2.0f / 2147483648.0f);
+    nq_e8_nearest_exact(u, n);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) d[j] = nq_sub(u[j], n[j]);
+}
+
+// ----------------------------------------------------------- encoder ------
+
+// Multi-beta search for one normalised block x (quantizer.py:275-283): for
+// each beta in table order quantise x/beta (+dither), reconstruct, and keep
+// the FIRST beta with the smallest sequentially-summed squared error.
+// Returns the codeword; writes the beta index and the chosen reconstruction
+// (normalised domain, already multiplied by beta).
+NQ_HD uint32_t nq_encode_block(const float x[8], const float* beta, const float* dither,
+                               int& beta_id, float recon[8]) {
+    float best_err = 0.0f;
+    uint32_t best_word = 0;
+    beta_id = -1;
+#pragma unroll 1
+    for (int b = 0; b < 4; ++b) {
+        float y[8], lam[8], r[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            y[j] = nq_div(x[j], beta[b]);
+            if (dither) y[j] = nq_add(y[j], dither[j]);
+        }
+        nq_e8_nearest_exact(y, lam);
+        const uint32_t word = nq_lattice_to_codeword(lam);
+        nq_decode_codeword_exact(word, dither, r);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) r[j] = nq_mul(r[j], beta[b]);
+        const float err = nq_sqdist8_seq(r, x);
+        if (beta_id < 0 || err < best_err) {
+            best_err = err;
+            best_word = word;
+            beta_id = b;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) recon[j] = r[j];
+        }
+    }
+    return best_word;
+}

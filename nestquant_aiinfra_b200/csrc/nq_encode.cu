@@ -1,0 +1,255 @@
+// E8 row encoder (activations and K/V rows) and the decode of undithered and
+// dithered packed streams.  HBM-bound by bytes, instruction-bound in practice:
+// one thread owns one E8 block (8 values in registers, no shuffles in the
+// search), 128-bit loads, one 32-bit codeword store per block.
+#include <stdarg.h>
+#include <math.h>
+
+#include "nq_common.cuh"
+
+// ---- error message storage (one per host thread) ---------------------------
+static thread_local char g_nq_error[512] = "";
+
+void nq_set_error(const char* fmt, ...) {
+    va_list args;
+    va_start(args, fmt);
+    vsnprintf(g_nq_error, sizeof(g_nq_error), fmt, args);
+    va_end(args);
+}
+
+extern "C" const char* nq_last_error(void) { return g_nq_error; }
+extern "C" int nq_abi_version(void) { return 1; }
+
+// ---------------------------------------------------------------------------
+// Encoder.  One CTA of 256 threads owns `rows_per_cta` consecutive rows
+// (256 / (k/8) rows for short rows, one row otherwise).
+//   phase 1  every thread squares its blocks into shared memory
+//   phase 2  8 threads per row run the reference's 8-lane strided accumulation
+//            (the order PyTorch's CPU vector_norm uses; it decides the last
+//            bit of the norm and therefore the emitted codes)
+//   phase 3  every thread runs the 4-beta search on its blocks and stores the
+//            codeword; beta ids of 4 neighbouring blocks are merged by shuffle.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+nq_encode_rows_kernel(const T* __restrict__ x, int64_t rows, int k, int64_t row_stride,
+                      const float* __restrict__ beta_table, float sqrt_k,
+                      uint32_t* __restrict__ codes, uint8_t* __restrict__ beta_ids,
+                      float* __restrict__ norms, __nv_bfloat16* __restrict__ decoded,
+                      int rows_per_cta) {
+    extern __shared__ float smem[];
+    const int bpr = k >> 3;
+    const int pitch = k + 8;  // de-conflicts the strided chain reads of neighbouring rows
+    float* sq = smem;
+    float* partial = smem + (size_t)rows_per_cta * pitch;
+    float* scale = partial + rows_per_cta * 8;
+    float* dscale = scale + rows_per_cta;
+
+    const int tid = threadIdx.x;
+    const int64_t row0 = (int64_t)blockIdx.x * rows_per_cta;
+    const int nrows = (int)min((int64_t)rows_per_cta, rows - row0);
+    const int nblocks = nrows * bpr;
+
+    for (int b = tid; b < nblocks; b += 256) {
+        const int r = b / bpr, bb = b - r * bpr;
+        float v[8];
+        nq_load8<T>(x + (row0 + r) * row_stride + (int64_t)bb * 8, v);
+        float4 lo = make_float4(nq_mul(v[0], v[0]), nq_mul(v[1], v[1]), nq_mul(v[2], v[2]), nq_mul(v[3], v[3]));
+        float4 hi = make_float4(nq_mul(v[4], v[4]), nq_mul(v[5], v[5]), nq_mul(v[6], v[6]), nq_mul(v[7], v[7]));
+        float4* dst = reinterpret_cast<float4*>(sq + (size_t)r * pitch + bb * 8);
+        dst[0] = lo;
+        dst[1] = hi;
+    }
+    __syncthreads();
+
+    if (tid < nrows * 8) {
+        const int r = tid >> 3, l = tid & 7;
+        const float* p = sq + (size_t)r * pitch + l;
+        float acc = 0.0f;
+#pragma unroll 8
+        for (int i = 0; i < bpr; ++i) acc = nq_add(acc, p[8 * i]);
+        partial[tid] = acc;
+    }
+    __syncthreads();
+
+    if (tid < nrows) {
+        float total = partial[tid * 8];
+#pragma unroll
+        for (int l = 1; l < 8; ++l) total = nq_add(total, partial[tid * 8 + l]);
+        const float norm = nq_sqrt(total);
+        norms[row0 + tid] = norm;
+        // sqrt(K)/norm is evaluated as reciprocal(norm) * sqrt(K) by the reference.
+        scale[tid] = norm > 0.0f ? nq_mul(nq_rcp(norm), sqrt_k) : 0.0f;
+        dscale[tid] = nq_div(norm, sqrt_k);
+    }
+    __syncthreads();
+
+    const int padded = (nblocks + 31) & ~31;
+    for (int b = tid; b < padded; b += 256) {
+        const bool valid = b < nblocks;
+        int bid = 0;
+        if (valid) {
+            const int r = b / bpr, bb = b - r * bpr;
+            float v[8], recon[8];
+            nq_load8<T>(x + (row0 + r) * row_stride + (int64_t)bb * 8, v);
+            const float s = scale[r];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = nq_mul(v[j], s);
+            const uint32_t word = nq_encode_block(v, beta_table, nullptr, bid, recon);
+            const int64_t g = row0 * bpr + b;
+            codes[g] = word;
+            if (decoded != nullptr) {
+                const float ds = dscale[r];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) recon[j] = nq_mul(recon[j], ds);
+                *reinterpret_cast<uint4*>(decoded + g * 8) = nq_pack_bf16x8(recon);
+            }
+        }
+        // four neighbouring blocks share one beta byte (block i -> bits 2i..2i+1)
+        unsigned merged = (unsigned)bid;
+        merged |= __shfl_down_sync(0xffffffffu, (unsigned)bid, 1) << 2;
+        merged |= __shfl_down_sync(0xffffffffu, (unsigned)bid, 2) << 4;
+        merged |= __shfl_down_sync(0xffffffffu, (unsigned)bid, 3) << 6;
+        if (valid && (tid & 3) == 0) beta_ids[(row0 * bpr + b) >> 2] = (uint8_t)merged;
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Decode of an undithered packed stream (activations / KV pages): one thread
+// per block, exact reference arithmetic.
+// ---------------------------------------------------------------------------
+template <bool OUT_BF16>
+__global__ void __launch_bounds__(256)
+nq_a4_decode_kernel(const uint32_t* __restrict__ codes, const uint8_t* __restrict__ beta_ids,
+                    const float* __restrict__ norms, const float* __restrict__ beta_table,
+                    int64_t blocks, int bpr, float sqrt_k, void* __restrict__ out) {
+    const int64_t g = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    if (g >= blocks) return;
+    const int64_t row = g / bpr;
+    float r[8];
+    nq_decode_codeword_exact(__ldg(codes + g), nullptr, r);
+    const float beta = __ldg(beta_table + nq_beta_id(beta_ids, g));
+    const float ds = nq_div(__ldg(norms + row), sqrt_k);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) r[j] = nq_mul(nq_mul(r[j], beta), ds);
+    if (OUT_BF16) {
+        reinterpret_cast<uint4*>(out)[g] = nq_pack_bf16x8(r);
+    } else {
+        float4* o = reinterpret_cast<float4*>(out) + 2 * g;
+        o[0] = make_float4(r[0], r[1], r[2], r[3]);
+        o[1] = make_float4(r[4], r[5], r[6], r[7]);
+    }
+}
+
+// Decode of a dithered weight stream to bf16 [n,k]; the dither of block g is a
+// pure function of (w_block_offset + g, seed).
+__global__ void __launch_bounds__(256)
+nq_w4_decode_kernel(const uint32_t* __restrict__ codes, const uint8_t* __restrict__ beta_ids,
+                    const float* __restrict__ norms, const float* __restrict__ beta_table,
+                    int64_t blocks, int bpr, float sqrt_k, uint32_t counter_base,
+                    uint4* __restrict__ out) {
+    const int64_t g = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    if (g >= blocks) return;
+    const int64_t row = g / bpr;
+    float d[8], r[8];
+    nq_dither_block(counter_base + (uint32_t)g * 8u, d);
+    nq_decode_codeword_exact(__ldg(codes + g), d, r);
+    const float beta = __ldg(beta_table + nq_beta_id(beta_ids, g));
+    const float ds = nq_div(__ldg(norms + row), sqrt_k);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) r[j] = nq_mul(nq_mul(r[j], beta), ds);
+    out[g] = nq_pack_bf16x8(r);
+}
+
+// ---- C ABI ------------------------------------------------------------------
+
+static int encode_rows_per_cta(int64_t k) {
+    const int bpr = (int)(k / 8);
+    return bpr >= 256 ? 1 : 256 / bpr;
+}
+
+template <typename T>
+static int launch_encode(const void* x, int64_t rows, int64_t k, int64_t row_stride,
+                         const float* beta_table, uint8_t* out_codes, uint8_t* out_beta_ids,
+                         float* out_norms, void* out_decoded, cudaStream_t stream) {
+    const int rpc = encode_rows_per_cta(k);
+    const size_t smem = ((size_t)rpc * (k + 8) + (size_t)rpc * 10) * sizeof(float);
+    auto kernel = nq_encode_rows_kernel<T>;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) {
+            nq_set_error("nq_a4_encode: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+            return (int)e;
+        }
+    }
+    const int64_t grid = (rows + rpc - 1) / rpc;
+    kernel<<<(unsigned)grid, 256, smem, stream>>>(
+        reinterpret_cast<const T*>(x), rows, (int)k, row_stride, beta_table,
+        (float)sqrt((double)k), reinterpret_cast<uint32_t*>(out_codes), out_beta_ids, out_norms,
+        reinterpret_cast<__nv_bfloat16*>(out_decoded), rpc);
+    NQ_CHECK_LAUNCH("nq_a4_encode");
+    return NQ_OK;
+}
+
+extern "C" int nq_a4_encode(const void* x, int x_dtype, int64_t rows, int64_t k, int64_t row_stride,
+                            const float* beta_table, uint8_t* out_codes, uint8_t* out_beta_ids,
+                            float* out_norms, void* out_decoded, nq_stream_t stream) {
+    NQ_REQUIRE(x && beta_table && out_codes && out_beta_ids && out_norms, NQ_ERR_ARG,
+               "nq_a4_encode: null pointer");
+    NQ_REQUIRE(rows >= 1 && rows <= (int64_t)1 << 31, NQ_ERR_ARG, "nq_a4_encode: rows=%lld out of range", (long long)rows);
+    NQ_REQUIRE(k >= 32 && k <= 32768 && k % 32 == 0, NQ_ERR_ARG,
+               "nq_a4_encode: k=%lld must be a multiple of 32 in [32, 32768]", (long long)k);
+    NQ_REQUIRE(row_stride >= k, NQ_ERR_ARG, "nq_a4_encode: row_stride < k");
+    const int64_t esize = x_dtype == NQ_F32 ? 4 : 2;
+    NQ_REQUIRE(nq_aligned16(x) && (row_stride * esize) % 16 == 0, NQ_ERR_ALIGN,
+               "nq_a4_encode: x and its row stride must be 16-byte aligned");
+    NQ_REQUIRE(nq_aligned16(out_codes) && (!out_decoded || nq_aligned16(out_decoded)), NQ_ERR_ALIGN,
+               "nq_a4_encode: outputs must be 16-byte aligned");
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    switch (x_dtype) {
+        case NQ_F32: return launch_encode<float>(x, rows, k, row_stride, beta_table, out_codes, out_beta_ids, out_norms, out_decoded, s);
+        case NQ_BF16: return launch_encode<__nv_bfloat16>(x, rows, k, row_stride, beta_table, out_codes, out_beta_ids, out_norms, out_decoded, s);
+        case NQ_F16: return launch_encode<__half>(x, rows, k, row_stride, beta_table, out_codes, out_beta_ids, out_norms, out_decoded, s);
+        default: nq_set_error("nq_a4_encode: unknown dtype %d", x_dtype); return NQ_ERR_ARG;
+    }
+}
+
+extern "C" int nq_a4_decode(const uint8_t* codes, const uint8_t* beta_ids, const float* norms,
+                            const float* beta_table, int64_t rows, int64_t k, void* out, int out_dtype,
+                            nq_stream_t stream) {
+    NQ_REQUIRE(codes && beta_ids && norms && beta_table && out, NQ_ERR_ARG, "nq_a4_decode: null pointer");
+    NQ_REQUIRE(rows >= 1 && k >= 8 && k % 8 == 0, NQ_ERR_ARG, "nq_a4_decode: bad shape");
+    NQ_REQUIRE(out_dtype == NQ_F32 || out_dtype == NQ_BF16, NQ_ERR_ARG, "nq_a4_decode: out_dtype must be f32 or bf16");
+    NQ_REQUIRE(nq_aligned16(out) && (reinterpret_cast<uintptr_t>(codes) & 3u) == 0, NQ_ERR_ALIGN,
+               "nq_a4_decode: out must be 16-byte and codes 4-byte aligned");
+    const int64_t blocks = rows * (k / 8);
+    const unsigned grid = (unsigned)((blocks + 255) / 256);
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    const float sqrt_k = (float)sqrt((double)k);
+    if (out_dtype == NQ_BF16)
+        nq_a4_decode_kernel<true><<<grid, 256, 0, s>>>(reinterpret_cast<const uint32_t*>(codes), beta_ids, norms, beta_table, blocks, (int)(k / 8), sqrt_k, out);
+    else
+        nq_a4_decode_kernel<false><<<grid, 256, 0, s>>>(reinterpret_cast<const uint32_t*>(codes), beta_ids, norms, beta_table, blocks, (int)(k / 8), sqrt_k, out);
+    NQ_CHECK_LAUNCH("nq_a4_decode");
+    return NQ_OK;
+}
+
+extern "C" int nq_w4_decode(const uint8_t* w_codes, const uint8_t* w_beta_ids, const float* w_norms,
+                            const float* w_betas, int64_t n, int64_t k, int64_t w_block_offset,
+                            int64_t seed, void* out_bf16, nq_stream_t stream) {
+    NQ_REQUIRE(w_codes && w_beta_ids && w_norms && w_betas && out_bf16, NQ_ERR_ARG, "nq_w4_decode: null pointer");
+    NQ_REQUIRE(n >= 1 && k >= 8 && k % 8 == 0, NQ_ERR_ARG, "nq_w4_decode: bad shape");
+    NQ_REQUIRE(seed >= 0 && seed < ((int64_t)1 << 31) && w_block_offset >= 0, NQ_ERR_ARG, "nq_w4_decode: bad seed/offset");
+    NQ_REQUIRE(w_block_offset + n * (k / 8) <= ((int64_t)1 << 28), NQ_ERR_ARG,
+               "nq_w4_decode: block range exceeds the dither counter space");
+    NQ_REQUIRE(nq_aligned16(out_bf16) && (reinterpret_cast<uintptr_t>(w_codes) & 3u) == 0, NQ_ERR_ALIGN,
+               "nq_w4_decode: alignment");
+    const int64_t blocks = n * (k / 8);
+    const unsigned grid = (unsigned)((blocks + 255) / 256);
+    const uint32_t base = (uint32_t)((uint64_t)w_block_offset * 8u + (uint64_t)seed);
+    nq_w4_decode_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const uint32_t*>(w_codes), w_beta_ids, w_norms, w_betas, blocks, (int)(k / 8),
+        (float)sqrt((double)k), base, reinterpret_cast<uint4*>(out_bf16));
+    NQ_CHECK_LAUNCH("nq_w4_decode");
+    return NQ_OK;
+}

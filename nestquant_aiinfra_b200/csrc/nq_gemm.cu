@@ -1,0 +1,102 @@
+// nq_w4a4_gemm: regime selection and workspace carving for the packed W4A4
+// projection.  M <= 16 runs the split-K CUDA-core kernel (nq_gemv.cu); larger
+// M decodes both operands to BF16 once and runs the tcgen05 GEMM
+// (nq_gemm_tc.cu).  Native tails: any M >= 1 is one call, no padding rows.
+#include "nq_common.cuh"
+
+size_t nq_small_m_partial_bytes(int64_t m, int64_t n, int64_t k);
+int nq_launch_small_m(const void* a_dec, const uint8_t* w_codes, const uint8_t* w_beta_ids,
+                      const float* w_norms, const float* w_betas, int64_t m, int64_t n, int64_t k,
+                      int64_t w_block_offset, int64_t seed, void* out, int out_dtype,
+                      float* partial, unsigned* counters, cudaStream_t stream);
+// tcgen05 path (nq_gemm_tc.cu)
+bool nq_tc_supported(int64_t m, int64_t n, int64_t k);
+size_t nq_tc_workspace_bytes(int64_t m, int64_t n, int64_t k);
+int nq_launch_tc_gemm(const void* a_dec, const void* w_dec, int64_t m, int64_t n, int64_t k,
+                      void* out, int out_dtype, void* workspace, cudaStream_t stream);
+
+namespace {
+
+constexpr int64_t kSmallMMax = 16;
+
+inline size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
+
+struct Carve {
+    size_t a_dec, w_dec, partial, tc, total;
+};
+
+Carve carve(int64_t m, int64_t n, int64_t k) {
+    Carve c;
+    size_t off = NQ_WS_COUNTER_BYTES;
+    c.a_dec = off;
+    off += align256((size_t)m * k * 2);
+    const bool tc = m > kSmallMMax && nq_tc_supported(m, n, k);
+    c.w_dec = off;
+    if (tc) off += align256((size_t)n * k * 2);
+    c.partial = off;
+    off += align256(nq_small_m_partial_bytes(m < kSmallMMax ? m : kSmallMMax, n, k));
+    c.tc = off;
+    if (tc) off += align256(nq_tc_workspace_bytes(m, n, k));
+    c.total = off;
+    return c;
+}
+
+}  // namespace
+
+extern "C" size_t nq_w4a4_workspace_bytes(int64_t m, int64_t n, int64_t k) {
+    if (m < 1 || n < 1 || k < 8) return 0;
+    return carve(m, n, k).total;
+}
+
+extern "C" int nq_w4a4_gemm(const uint8_t* act_codes, const uint8_t* act_beta_ids, const float* act_norms,
+                            const float* act_betas, const void* act_decoded,
+                            const uint8_t* w_codes, const uint8_t* w_beta_ids, const float* w_norms,
+                            const float* w_betas, int64_t m, int64_t n, int64_t k,
+                            int64_t w_block_offset, int64_t seed, void* out, int out_dtype,
+                            void* workspace, size_t workspace_bytes, nq_stream_t stream) {
+    NQ_REQUIRE(w_codes && w_beta_ids && w_norms && w_betas && out, NQ_ERR_ARG, "nq_w4a4_gemm: null pointer");
+    NQ_REQUIRE(act_decoded || (act_codes && act_beta_ids && act_norms && act_betas), NQ_ERR_ARG,
+               "nq_w4a4_gemm: activation streams missing");
+    NQ_REQUIRE(m >= 1 && n >= 8 && n % 8 == 0 && n <= 131072, NQ_ERR_ARG,
+               "nq_w4a4_gemm: m=%lld n=%lld unsupported (n must be a multiple of 8, <= 131072)",
+               (long long)m, (long long)n);
+    NQ_REQUIRE(k >= 32 && k % 32 == 0, NQ_ERR_ARG, "nq_w4a4_gemm: k=%lld must be a multiple of 32", (long long)k);
+    NQ_REQUIRE(out_dtype == NQ_F32 || out_dtype == NQ_BF16, NQ_ERR_ARG, "nq_w4a4_gemm: out_dtype must be f32 or bf16");
+    NQ_REQUIRE(seed >= 0 && seed < ((int64_t)1 << 31) && w_block_offset >= 0 &&
+                   w_block_offset + n * (k / 8) <= ((int64_t)1 << 28),
+               NQ_ERR_ARG, "nq_w4a4_gemm: dither seed / block range outside the 31-bit counter space");
+    const Carve c = carve(m, n, k);
+    NQ_REQUIRE(workspace && workspace_bytes >= c.total, NQ_ERR_WORKSPACE,
+               "nq_w4a4_gemm: workspace of %zu bytes needed, %zu given", c.total, workspace_bytes);
+    NQ_REQUIRE(nq_aligned16(workspace) && nq_aligned16(out) && nq_aligned16(w_codes) &&
+                   (!act_decoded || nq_aligned16(act_decoded)),
+               NQ_ERR_ALIGN, "nq_w4a4_gemm: workspace, out, w_codes and act_decoded must be 16-byte aligned");
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    char* ws = reinterpret_cast<char*>(workspace);
+    unsigned* counters = reinterpret_cast<unsigned*>(ws);
+
+    const void* a_dec = act_decoded;
+    if (!a_dec) {
+        int rc = nq_a4_decode(act_codes, act_beta_ids, act_norms, act_betas, m, k, ws + c.a_dec, NQ_BF16, stream);
+        if (rc) return rc;
+        a_dec = ws + c.a_dec;
+    }
+
+    if (m > kSmallMMax && nq_tc_supported(m, n, k)) {
+        int rc = nq_w4_decode(w_codes, w_beta_ids, w_norms, w_betas, n, k, w_block_offset, seed, ws + c.w_dec, stream);
+        if (rc) return rc;
+        return nq_launch_tc_gemm(a_dec, ws + c.w_dec, m, n, k, out, out_dtype, ws + c.tc, s);
+    }
+
+    // CUDA-core path; rows beyond 16 are processed 16 at a time
+    const size_t out_elem = out_dtype == NQ_BF16 ? 2 : 4;
+    for (int64_t m0 = 0; m0 < m; m0 += kSmallMMax) {
+        const int64_t mc = (m - m0) < kSmallMMax ? (m - m0) : kSmallMMax;
+        int rc = nq_launch_small_m(reinterpret_cast<const char*>(a_dec) + (size_t)m0 * k * 2, w_codes, w_beta_ids,
+                                   w_norms, w_betas, mc, n, k, w_block_offset, seed,
+                                   reinterpret_cast<char*>(out) + (size_t)m0 * n * out_elem, out_dtype,
+                                   reinterpret_cast<float*>(ws + c.partial), counters, s);
+        if (rc) return rc;
+    }
+    return NQ_OK;
+}

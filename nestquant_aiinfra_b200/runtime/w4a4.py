@@ -1,0 +1,362 @@
+"""Packed W4A4 projection: host mirror of the reference's operator interface.
+
+Same names, argument meaning and error behaviour as
+``nestquant.runtime.triton_w4a4_linear`` (``PreparedNQA4Activation``,
+``quantize_activation_cuda``; triton_w4a4_linear.py:489-617),
+``nestquant.runtime.triton_fused_linear`` (``PreparedNQRTLinear``,
+``prepare_fused_linear``; triton_fused_linear.py:136-165) and
+``nestquant.runtime.cuda_w4a4_mma`` (``can_use_*`` / ``linear_packed_w4a4_*``;
+cuda_w4a4_mma.py:44-704).  Every function launches hand-written sm_100a kernels
+through the C ABI on the current torch stream; there is no Triton, no backend
+dispatch and no CPU fallback.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import math
+from dataclasses import dataclass
+from typing import Any, Sequence
+
+import numpy as np
+import torch
+
+from .. import _lib
+from ..formats import (STATELESS_DITHER_ALGORITHM, UPSTREAM_CODEC_SEMANTICS)
+
+_DTYPE_TAG = {torch.float32: _lib.NQ_F32, torch.bfloat16: _lib.NQ_BF16, torch.float16: _lib.NQ_F16}
+
+
+def _ptr(tensor: torch.Tensor | None) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if tensor is None else tensor.data_ptr())
+
+
+def _stream(device: torch.device) -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+_I64 = ctypes.c_int64
+
+# ---------------------------------------------------------------------------
+# workspaces: one zero-initialised buffer per (device, stream), grown on demand.
+# The first WS_COUNTER_BYTES hold the split-K arrival counters; kernels leave
+# them zero, so the buffer can be reused by every later call.
+# ---------------------------------------------------------------------------
+_WORKSPACES: dict[tuple[int, int], torch.Tensor] = {}
+
+
+def workspace_for(device: torch.device, nbytes: int) -> torch.Tensor:
+    capturing = torch.cuda.is_current_stream_capturing()
+    key = (device.index if device.index is not None else torch.cuda.current_device(),
+           torch.cuda.current_stream(device).cuda_stream)
+    buffer = _WORKSPACES.get(key)
+    if buffer is None or buffer.numel() < nbytes or capturing:
+        # Under graph capture the allocation comes from the graph's private pool
+        # and must not be shared with eager code.
+        size = max(nbytes, 1 << 20)
+        buffer = torch.zeros(size, dtype=torch.uint8, device=device)
+        if not capturing:
+            _WORKSPACES[key] = buffer
+    return buffer
+
+
+# ---------------------------------------------------------------------------
+# prepared (device-resident) operands
+# ---------------------------------------------------------------------------
+@dataclass(frozen=True)
+class PreparedNQA4Activation:
+    """GPU-resident packed activation rows (triton_w4a4_linear.py:489-519).
+
+    ``decoded`` is an optional extra of this implementation: the BF16
+    reconstruction the encoder produced in the same launch.  The projection
+    kernels use it when present and decode the packed streams otherwise.
+    """
+
+    code_payload: torch.Tensor
+    beta_payload: torch.Tensor
+    row_norms: torch.Tensor
+    beta_table: torch.Tensor
+    original_shape: tuple[int, ...]
+    q: int
+    code_width: int
+    beta_width: int
+    output_dtype: torch.dtype
+    decoded: torch.Tensor | None = None
+
+    @property
+    def token_count(self) -> int:
+        return math.prod(self.original_shape[:-1])
+
+    @property
+    def feature_count(self) -> int:
+        return self.original_shape[-1]
+
+    @property
+    def resident_bytes(self) -> int:
+        return sum(t.numel() * t.element_size()
+                   for t in (self.code_payload, self.beta_payload, self.row_norms, self.beta_table))
+
+
+@dataclass(frozen=True)
+class PreparedNQRTLinear:
+    """GPU-resident packed NQRT4 weight streams (triton_fused_linear.py:136-144)."""
+
+    record: Any
+    code_payload: torch.Tensor
+    beta_payload: torch.Tensor
+    row_norms: torch.Tensor
+    beta_table: torch.Tensor
+
+
+def _payload_tensor(payload, device: torch.device) -> torch.Tensor:
+    if isinstance(payload, torch.Tensor):
+        return payload.to(device=device, dtype=torch.uint8).contiguous()
+    array = np.frombuffer(payload, dtype=np.uint8) if isinstance(payload, (bytes, bytearray, memoryview)) \
+        else np.ascontiguousarray(payload, dtype=np.uint8)
+    return torch.from_numpy(array.copy()).to(device)
+
+
+def prepare_fused_linear(record, *, device: torch.device | str = "cuda") -> PreparedNQRTLinear:
+    """Copy only the packed streams and compact metadata to the GPU.
+
+    ``record`` is a ``PackedNestQuantTensor`` of this package or of the
+    reference (same attribute names).
+    """
+    for name in ("indices", "row_norms", "betas", "feature_count"):
+        if not hasattr(record, name):
+            raise TypeError("record must be a PackedNestQuantTensor")
+    target = torch.device(device)
+    if target.type != "cuda" or not torch.cuda.is_available():
+        raise ValueError("packed Linear preparation requires CUDA")
+    if record.dither_seed is None or record.dither_algorithm != STATELESS_DITHER_ALGORITHM:
+        raise ValueError("packed Linear requires NQRT v4 stateless dither")
+    if record.codec_semantics != UPSTREAM_CODEC_SEMANTICS:
+        raise ValueError("packed Linear requires upstream E8 semantics")
+    return PreparedNQRTLinear(
+        record=record,
+        code_payload=_payload_tensor(record.indices.code_payload, target),
+        beta_payload=_payload_tensor(record.indices.beta_payload, target),
+        row_norms=record.row_norms.to(device=target, dtype=torch.float32).contiguous(),
+        beta_table=torch.tensor(tuple(record.betas), device=target, dtype=torch.float32),
+    )
+
+
+def quantize_activation_cuda(
+    inputs: torch.Tensor, *, q: int, betas: Sequence[float],
+    beta_table: torch.Tensor | None = None, keep_decoded: bool = True,
+) -> PreparedNQA4Activation:
+    """Encode floating activations into packed NQA4 payloads in one launch.
+
+    Bit-exact with ``pack_nestquant_indices(quantize_rows(inputs.float(), q, betas))``
+    of the reference CPU path.
+    """
+    if not isinstance(inputs, torch.Tensor) or not inputs.is_floating_point():
+        raise TypeError("inputs must be a floating-point tensor")
+    if inputs.device.type != "cuda" or inputs.ndim < 1 or inputs.numel() == 0:
+        raise ValueError("inputs must be a nonempty CUDA tensor")
+    if inputs.shape[-1] % 8:
+        raise ValueError("activation feature dimension must be divisible by 8")
+    beta_values = tuple(float(value) for value in betas)
+    if not beta_values or any(not math.isfinite(value) or value <= 0 for value in beta_values):
+        raise ValueError("betas must be positive finite values")
+    code_width = max(1, math.ceil(math.log2(q)))
+    beta_width = max(1, math.ceil(math.log2(len(beta_values))))
+    if code_width not in {1, 2, 4, 8} or beta_width not in {1, 2, 4, 8}:
+        raise ValueError("packed activation fields require 1, 2, 4, or 8 bits")
+    if q != 14 or len(beta_values) != 4:
+        raise ValueError("the sm_100a encoder implements q=14 with four betas")
+    if inputs.dtype not in _DTYPE_TAG:
+        raise ValueError("inputs must use float16, bfloat16, or float32")
+    k = inputs.shape[-1]
+    rows = inputs.reshape(-1, k)
+    if rows.stride(-1) != 1 or (rows.stride(0) * rows.element_size()) % 16 or rows.data_ptr() % 16:
+        rows = rows.contiguous()
+    device = inputs.device
+    if beta_table is None:
+        beta_table = torch.tensor(beta_values, device=device, dtype=torch.float32)
+    elif (beta_table.device != device or beta_table.dtype != torch.float32 or beta_table.ndim != 1
+          or beta_table.numel() != len(beta_values) or not beta_table.is_contiguous()):
+        raise ValueError("beta_table must be contiguous float32 on the input device")
+    m = rows.shape[0]
+    codes = torch.empty(m * k // 2, dtype=torch.uint8, device=device)
+    beta_ids = torch.empty(m * k // 32, dtype=torch.uint8, device=device)
+    norms = torch.empty(m, dtype=torch.float32, device=device)
+    decoded = torch.empty((m, k), dtype=torch.bfloat16, device=device) if keep_decoded else None
+    status = _lib.lib().nq_a4_encode(
+        _ptr(rows), _DTYPE_TAG[inputs.dtype], _I64(m), _I64(k), _I64(rows.stride(0)), _ptr(beta_table),
+        _ptr(codes), _ptr(beta_ids), _ptr(norms), _ptr(decoded), _stream(device))
+    _lib.check(status, "quantize_activation_cuda")
+    return PreparedNQA4Activation(
+        code_payload=codes, beta_payload=beta_ids, row_norms=norms, beta_table=beta_table,
+        original_shape=tuple(inputs.shape), q=q, code_width=code_width, beta_width=beta_width,
+        output_dtype=inputs.dtype, decoded=decoded)
+
+
+# ---------------------------------------------------------------------------
+# predicates (host only; return False instead of raising, as the reference does)
+# ---------------------------------------------------------------------------
+def _tensors(activation: PreparedNQA4Activation, weight: PreparedNQRTLinear):
+    return (activation.code_payload, activation.beta_payload, activation.row_norms, activation.beta_table,
+            weight.code_payload, weight.beta_payload, weight.row_norms, weight.beta_table)
+
+
+def can_use_w4a4(activation: PreparedNQA4Activation, weight: PreparedNQRTLinear) -> bool:
+    """Formats and device invariants shared by every M regime."""
+    record = weight.record
+    tensors = _tensors(activation, weight)
+    return bool(
+        activation.token_count >= 1
+        and activation.feature_count == record.feature_count
+        and activation.q == 14 and activation.code_width == 4 and activation.beta_width == 2
+        and activation.beta_table.numel() == 4
+        and record.feature_count % 32 == 0
+        and record.indices.shape[0] % 8 == 0
+        and record.indices.q == 14 and record.indices.code_bit_width == 4
+        and record.indices.beta_count == 4 and record.indices.beta_index_bit_width == 2
+        and record.dither_seed is not None
+        and record.dither_algorithm == STATELESS_DITHER_ALGORITHM
+        and record.codec_semantics == UPSTREAM_CODEC_SEMANTICS
+        and all(t.is_contiguous() for t in tensors)
+        and all(t.device == activation.code_payload.device for t in tensors)
+        and activation.code_payload.device.type == "cuda"
+    )
+
+
+def can_use_w4a4_gemv_m1(activation, weight) -> bool:
+    return activation.token_count == 1 and can_use_w4a4(activation, weight)
+
+
+def can_use_w4a4_mma_small_m(activation, weight) -> bool:
+    return activation.token_count in (2, 4, 8) and can_use_w4a4(activation, weight)
+
+
+def can_use_w4a4_mma_m16(activation, weight) -> bool:
+    return activation.token_count == 16 and can_use_w4a4(activation, weight)
+
+
+def can_use_w4a4_mma_large_m_staged(activation, weight) -> bool:
+    return activation.token_count in (32, 64, 128) and can_use_w4a4(activation, weight)
+
+
+def can_use_w4a4_mma_chunked_staged(activation, weight) -> bool:
+    return can_use_w4a4(activation, weight)
+
+
+# ---------------------------------------------------------------------------
+# the projection
+# ---------------------------------------------------------------------------
+def _run(activation: PreparedNQA4Activation, weight: PreparedNQRTLinear, out_dtype: torch.dtype,
+         *, use_decoded: bool = True) -> torch.Tensor:
+    record = weight.record
+    m, k, n = activation.token_count, activation.feature_count, int(record.indices.shape[0])
+    device = activation.code_payload.device
+    library = _lib.lib()
+    nbytes = library.nq_w4a4_workspace_bytes(_I64(m), _I64(n), _I64(k))
+    workspace = workspace_for(device, nbytes)
+    out = torch.empty((m, n), dtype=out_dtype, device=device)
+    decoded = activation.decoded if use_decoded else None
+    status = library.nq_w4a4_gemm(
+        _ptr(activation.code_payload), _ptr(activation.beta_payload), _ptr(activation.row_norms),
+        _ptr(activation.beta_table), _ptr(decoded),
+        _ptr(weight.code_payload), _ptr(weight.beta_payload), _ptr(weight.row_norms), _ptr(weight.beta_table),
+        _I64(m), _I64(n), _I64(k), _I64(0), _I64(int(record.dither_seed)),
+        _ptr(out), _DTYPE_TAG[out_dtype], _ptr(workspace), ctypes.c_size_t(workspace.numel()), _stream(device))
+    _lib.check(status, "linear_packed_w4a4")
+    return out
+
+
+def _check_types(activation, weight) -> None:
+    if not isinstance(activation, PreparedNQA4Activation):
+        raise TypeError("activation must be PreparedNQA4Activation")
+    if not isinstance(weight, PreparedNQRTLinear):
+        raise TypeError("weight must be PreparedNQRTLinear")
+
+
+def _output_dtype(activation: PreparedNQA4Activation) -> torch.dtype:
+    return torch.bfloat16 if activation.output_dtype == torch.bfloat16 else torch.float32
+
+
+def linear_packed_w4a4(activation: PreparedNQA4Activation, weight: PreparedNQRTLinear) -> torch.Tensor:
+    """Packed W4A4 projection for any token count (one entry, native tails)."""
+    _check_types(activation, weight)
+    if not can_use_w4a4(activation, weight):
+        raise ValueError("activation or packed weight is unsupported by the W4A4 kernels")
+    out = _run(activation, weight, _output_dtype(activation))
+    n = int(weight.record.indices.shape[0])
+    return out.to(activation.output_dtype).reshape(*activation.original_shape[:-1], n)
+
+
+def linear_packed_w4a4_fp32(activation: PreparedNQA4Activation, weight: PreparedNQRTLinear) -> torch.Tensor:
+    """The FP32 accumulator before output rounding (reference: ``*_fp32_probe``)."""
+    _check_types(activation, weight)
+    if not can_use_w4a4(activation, weight):
+        raise ValueError("activation or packed weight is unsupported by the W4A4 kernels")
+    n = int(weight.record.indices.shape[0])
+    return _run(activation, weight, torch.float32).reshape(*activation.original_shape[:-1], n)
+
+
+def _regime(name: str, predicate):
+    def run(activation: PreparedNQA4Activation, weight: PreparedNQRTLinear) -> torch.Tensor:
+        _check_types(activation, weight)
+        if not predicate(activation, weight):
+            raise ValueError(f"activation or packed weight is unsupported by {name}")
+        return linear_packed_w4a4(activation, weight)
+
+    run.__name__ = name
+    run.__doc__ = f"Reference entry ``{name}`` (runtime/cuda_w4a4_mma.py); same kernels for every M."
+    return run
+
+
+linear_packed_w4a4_gemv_m1 = _regime("linear_packed_w4a4_gemv_m1", can_use_w4a4_gemv_m1)
+linear_packed_w4a4_mma_small_m = _regime("linear_packed_w4a4_mma_small_m", can_use_w4a4_mma_small_m)
+linear_packed_w4a4_mma_m16 = _regime("linear_packed_w4a4_mma_m16", can_use_w4a4_mma_m16)
+linear_packed_w4a4_mma_large_m_staged = _regime("linear_packed_w4a4_mma_large_m_staged",
+                                                can_use_w4a4_mma_large_m_staged)
+linear_packed_w4a4_mma_chunked_staged = _regime("linear_packed_w4a4_mma_chunked_staged",
+                                                can_use_w4a4_mma_chunked_staged)
+
+
+def linear_packed_w4a4_gemv_m1_fp32_probe(activation, weight) -> torch.Tensor:
+    _check_types(activation, weight)
+    if not can_use_w4a4_gemv_m1(activation, weight):
+        raise ValueError("activation or packed weight is unsupported by W4A4 M1")
+    return linear_packed_w4a4_fp32(activation, weight)
+
+
+def decode_packed_a4(activation: PreparedNQA4Activation, *, dtype: torch.dtype | None = None) -> torch.Tensor:
+    """Decode packed A4 rows with the production arithmetic (diagnostic).
+
+    Bit-identical to ``QuantizedRows.dequantize`` of the reference in float32;
+    ``dtype`` defaults to the activation's output dtype (reference:
+    ``decode_packed_a4_m16``, cuda_w4a4_mma.py:688-696).
+    """
+    if not isinstance(activation, PreparedNQA4Activation):
+        raise TypeError("activation must be PreparedNQA4Activation")
+    dtype = activation.output_dtype if dtype is None else dtype
+    kernel_dtype = torch.bfloat16 if dtype == torch.bfloat16 else torch.float32
+    m, k = activation.token_count, activation.feature_count
+    device = activation.code_payload.device
+    out = torch.empty((m, k), dtype=kernel_dtype, device=device)
+    status = _lib.lib().nq_a4_decode(
+        _ptr(activation.code_payload), _ptr(activation.beta_payload), _ptr(activation.row_norms),
+        _ptr(activation.beta_table), _I64(m), _I64(k), _ptr(out), _DTYPE_TAG[kernel_dtype], _stream(device))
+    _lib.check(status, "decode_packed_a4")
+    return out.to(dtype).reshape(*activation.original_shape)
+
+
+decode_packed_a4_m16 = decode_packed_a4
+
+
+def decode_packed_weight(weight: PreparedNQRTLinear) -> torch.Tensor:
+    """BF16 ``[N, K]`` reconstruction of a packed weight (dither regenerated)."""
+    if not isinstance(weight, PreparedNQRTLinear):
+        raise TypeError("weight must be PreparedNQRTLinear")
+    record = weight.record
+    n, k = int(record.indices.shape[0]), int(record.feature_count)
+    device = weight.code_payload.device
+    out = torch.empty((n, k), dtype=torch.bfloat16, device=device)
+    status = _lib.lib().nq_w4_decode(
+        _ptr(weight.code_payload), _ptr(weight.beta_payload), _ptr(weight.row_norms), _ptr(weight.beta_table),
+        _I64(n), _I64(k), _I64(0), _I64(int(record.dither_seed)), _ptr(out), _stream(device))
+    _lib.check(status, "decode_packed_weight")
+    return out

@@ -1,0 +1,36 @@
+// Host build of the device codec header, so the CPU test-suite can compare the
+// exact source the kernels use against the CPU checker.  Built by the test
+// with: g++ -O2 -shared -fPIC -ffp-contract=off.
+#include "nq_e8.cuh"
+
+extern "C" {
+
+void shim_nearest_e8(const float* x, float* out, long n) {
+    for (long i = 0; i < n; ++i) nq_e8_nearest_exact(x + 8 * i, out + 8 * i);
+}
+
+void shim_dither(long first_block, long blocks, long seed, float* out) {
+    for (long b = 0; b < blocks; ++b)
+        nq_dither_block((uint32_t)((uint64_t)(first_block + b) * 8u + (uint64_t)seed), out + 8 * b);
+}
+
+void shim_decode(const uint32_t* words, long n, float* out) {
+    for (long i = 0; i < n; ++i) nq_decode_codeword_exact(words[i], nullptr, out + 8 * i);
+}
+
+// x: normalised blocks [n,8]; seed < 0 -> no dither.
+void shim_encode_blocks(const float* x, long n, const float* beta, long seed, long first_block,
+                        uint32_t* words, int* beta_ids, float* recon) {
+    for (long i = 0; i < n; ++i) {
+        float d[8];
+        const float* dp = nullptr;
+        if (seed >= 0) {
+            nq_dither_block((uint32_t)((uint64_t)(first_block + i) * 8u + (uint64_t)seed), d);
+            dp = d;
+        }
+        words[i] = nq_encode_block(x + 8 * i, beta, dp, beta_ids[i], recon + 8 * i);
+    }
+}
+
+float shim_bf16_round(float v) { return nq_bf16_round(v); }
+}
