@@ -88,8 +88,10 @@ int nq_a4_decode(const uint8_t* codes, const uint8_t* beta_ids, const float* nor
  *   workspace  at least nq_w4a4_workspace_bytes(m,n,k) bytes; its first
  *              NQ_WS_COUNTER_BYTES bytes must be zero before the FIRST use and are
  *              left zero by every call.
- * Requirements: k % 32 == 0, n % 8 == 0. */
+ * Requirements: k % 32 == 0, n % 8 == 0, n <= 131064.  The tcgen05 path is taken for
+ * m > 16 when n % 128 == 0 and k % 64 == 0. */
 #define NQ_WS_COUNTER_BYTES 65536
+#define NQ_WS_STATUS_OFFSET 65532 /* last word of the counter area: device status, 0 = ok */
 size_t nq_w4a4_workspace_bytes(int64_t m, int64_t n, int64_t k);
 int nq_w4a4_gemm(const uint8_t* act_codes, const uint8_t* act_beta_ids, const float* act_norms,
                  const float* act_betas, const void* act_decoded,
@@ -97,6 +99,14 @@ int nq_w4a4_gemm(const uint8_t* act_codes, const uint8_t* act_beta_ids, const fl
                  const float* w_betas, int64_t m, int64_t n, int64_t k,
                  int64_t w_block_offset, int64_t seed, void* out, int out_dtype,
                  void* workspace, size_t workspace_bytes, nq_stream_t stream);
+
+/* Copy the device status word of a workspace to the host and synchronise the
+ * stream (the only entry point that synchronises).  Non-zero means a bounded
+ * wait inside the tcgen05 kernel gave up: 1 = producer waiting for a free
+ * stage, 2 = MMA waiting for a free accumulator, 3 = MMA waiting for a TMA
+ * stage, 4 = epilogue waiting for the accumulator.  No counterpart in the
+ * reference (its kernels have no device-side waits). */
+int nq_w4a4_status(const void* workspace, uint32_t* status_host, nq_stream_t stream);
 
 /* Decode a packed NQRT4 weight to bf16 [n,k] (dither regenerated on the fly);
  * bit-identical to bf16(QuantizedRows.dequantize) of the record

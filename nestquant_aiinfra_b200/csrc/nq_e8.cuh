@@ -69,6 +69,28 @@ NQ_HD float nq_sqrt(float a) {
     return sqrtf(a);
 #endif
 }
+NQ_HD float nq_fma(float a, float b, float c) {
+#if defined(__CUDA_ARCH__)
+    return __fmaf_rn(a, b, c);
+#else
+    return fmaf(a, b, c);
+#endif
+}
+
+// Correctly rounded a / b from the correctly rounded reciprocal rb = RN(1/b):
+// two FMA residual corrections (Markstein).  Identical to IEEE division for
+// normal-range operands (no overflow / underflow handling, which the
+// normalised values of this codec never need); 5 instructions instead of the
+// ~25 of the generic division.
+NQ_HD float nq_div_by(float a, float b, float rb) {
+    const float q0 = nq_mul(a, rb);
+    const float r0 = nq_fma(-b, q0, a);
+    const float q1 = nq_fma(r0, rb, q0);
+    const float r1 = nq_fma(-b, q1, a);
+    return nq_fma(r1, rb, q1);
+}
+#define NQ_RCP14 0.0714285746216774f /* RN(1/14) */
+
 NQ_HD int nq_float_bits(float v) {
 #if defined(__CUDA_ARCH__)
     return __float_as_int(v);
@@ -157,6 +179,55 @@ NQ_HD void nq_e8_nearest_exact(const float x[8], float out[8]) {
     for (int j = 0; j < 8; ++j) out[j] = integer_coset ? p0[j] : p1[j];
 }
 
+// Nearest E8 point for continuous inputs (dithered weights): same roundings,
+// parity rule and first-max rule as the exact function, but the two coset
+// distances are formed from the rounding residuals with FMAs, and only the
+// winning coset is repaired.  Whenever the distances are closer than 1e-4
+// (summation-order effects are below 1e-6) the exact function decides, so the
+// result always equals nq_e8_nearest_exact.
+NQ_HD void nq_e8_nearest_guarded(const float x[8], float out[8]) {
+    float r0[8], e0[8], r1[8], e1[8];
+    int par0 = 0, par1 = 0;
+    float s0 = 0.0f, s1 = 0.0f, m0 = 0.0f, m1 = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const float t0 = nq_add(x[j], NQ_MAGIC);
+        r0[j] = nq_sub(t0, NQ_MAGIC);
+        par0 ^= nq_float_bits(t0);
+        e0[j] = nq_sub(x[j], r0[j]);
+        s0 = nq_fma(e0[j], e0[j], s0);
+        m0 = fmaxf(m0, fabsf(e0[j]));
+        const float y = nq_sub(x[j], 0.5f);
+        const float t1 = nq_add(y, NQ_MAGIC);
+        r1[j] = nq_sub(t1, NQ_MAGIC);
+        par1 ^= nq_float_bits(t1);
+        e1[j] = nq_sub(y, r1[j]);
+        s1 = nq_fma(e1[j], e1[j], s1);
+        m1 = fmaxf(m1, fabsf(e1[j]));
+    }
+    if (par0 & 1) s0 += 1.0f - 2.0f * m0;
+    if (par1 & 1) s1 += 1.0f - 2.0f * m1;
+    const float diff = s0 - s1;
+    if (fabsf(diff) < 1e-4f) {
+        nq_e8_nearest_exact(x, out);
+        return;
+    }
+    const bool integer_coset = diff < 0.0f;
+    const bool odd = ((integer_coset ? par0 : par1) & 1) != 0;
+    const float m = integer_coset ? m0 : m1;
+    const float half = integer_coset ? 0.0f : 0.5f;
+    bool pending = odd;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const float e = integer_coset ? e0[j] : e1[j];
+        float r = integer_coset ? r0[j] : r1[j];
+        const bool hit = pending && fabsf(e) == m;  // first coordinate reaching the maximum
+        r += hit ? (e >= 0.0f ? 1.0f : -1.0f) : 0.0f;
+        pending = pending && !hit;
+        out[j] = r + half;
+    }
+}
+
 // Exact int -> float for |v| < 2^22 without the (slow) conversion unit: the
 // integer is added into the mantissa of the magic constant.
 NQ_HD float nq_small_int_to_float(int v) {
@@ -216,7 +287,7 @@ NQ_HD void nq_decode_codeword_exact(uint32_t word, const float* dither, float r[
         for (int j = 0; j < 8; ++j) t[j] = nq_sub(t[j], dither[j]);
     }
 #pragma unroll
-    for (int j = 0; j < 8; ++j) s[j] = nq_div(t[j], 14.0f);
+    for (int j = 0; j < 8; ++j) s[j] = nq_div_by(t[j], 14.0f, NQ_RCP14);
     nq_e8_nearest_exact(s, n);
 #pragma unroll
     for (int j = 0; j < 8; ++j) r[j] = nq_sub(t[j], nq_mul(14.0f, n[j]));
@@ -246,6 +317,30 @@ NQ_HD void nq_dither_block(uint32_t base, float d[8]) {
     for (int j = 0; j < 8; ++j) d[j] = nq_sub(u[j], n[j]);
 }
 
+// Weight-path variants (continuous arguments): guarded nearest-point search.
+NQ_HD void nq_dither_block_fast(uint32_t base, float d[8]) {
+    float u[8], n[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) u[j] = (float)nq_lcg31_mix(base + (uint32_t)j) * (2.0f / 2147483648.0f);
+    nq_e8_nearest_guarded(u, n);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) d[j] = nq_sub(u[j], n[j]);
+}
+
+NQ_HD void nq_decode_weight_block(uint32_t word, uint32_t counter_base, float r[8]) {
+    float d[8], t[8], s[8], n[8];
+    nq_dither_block_fast(counter_base, d);
+    nq_codeword_coset(word, t);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        t[j] = nq_sub(t[j], d[j]);
+        s[j] = nq_div_by(t[j], 14.0f, NQ_RCP14);
+    }
+    nq_e8_nearest_guarded(s, n);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) r[j] = nq_sub(t[j], nq_mul(14.0f, n[j]));
+}
+
 // ----------------------------------------------------------- encoder ------
 
 // Multi-beta search for one normalised block x (quantizer.py:275-283): for
@@ -261,9 +356,10 @@ NQ_HD uint32_t nq_encode_block(const float x[8], const float* beta, const float*
 #pragma unroll 1
     for (int b = 0; b < 4; ++b) {
         float y[8], lam[8], r[8];
+        const float rbeta = nq_rcp(beta[b]);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-            y[j] = nq_div(x[j], beta[b]);
+            y[j] = nq_div_by(x[j], beta[b], rbeta);
             if (dither) y[j] = nq_add(y[j], dither[j]);
         }
         nq_e8_nearest_exact(y, lam);

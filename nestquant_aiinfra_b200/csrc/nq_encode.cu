@@ -62,13 +62,13 @@ nq_encode_rows_kernel(const T* __restrict__ x, int64_t rows, int k, int64_t row_
     }
     __syncthreads();
 
-    if (tid < nrows * 8) {
-        const int r = tid >> 3, l = tid & 7;
+    for (int t = tid; t < nrows * 8; t += 256) {
+        const int r = t >> 3, l = t & 7;
         const float* p = sq + (size_t)r * pitch + l;
         float acc = 0.0f;
 #pragma unroll 8
         for (int i = 0; i < bpr; ++i) acc = nq_add(acc, p[8 * i]);
-        partial[tid] = acc;
+        partial[t] = acc;
     }
     __syncthreads();
 
@@ -151,9 +151,8 @@ nq_w4_decode_kernel(const uint32_t* __restrict__ codes, const uint8_t* __restric
     const int64_t g = (int64_t)blockIdx.x * 256 + threadIdx.x;
     if (g >= blocks) return;
     const int64_t row = g / bpr;
-    float d[8], r[8];
-    nq_dither_block(counter_base + (uint32_t)g * 8u, d);
-    nq_decode_codeword_exact(__ldg(codes + g), d, r);
+    float r[8];
+    nq_decode_weight_block(__ldg(codes + g), counter_base + (uint32_t)g * 8u, r);
     const float beta = __ldg(beta_table + nq_beta_id(beta_ids, g));
     const float ds = nq_div(__ldg(norms + row), sqrt_k);
 #pragma unroll

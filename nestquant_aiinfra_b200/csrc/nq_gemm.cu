@@ -57,8 +57,8 @@ extern "C" int nq_w4a4_gemm(const uint8_t* act_codes, const uint8_t* act_beta_id
     NQ_REQUIRE(w_codes && w_beta_ids && w_norms && w_betas && out, NQ_ERR_ARG, "nq_w4a4_gemm: null pointer");
     NQ_REQUIRE(act_decoded || (act_codes && act_beta_ids && act_norms && act_betas), NQ_ERR_ARG,
                "nq_w4a4_gemm: activation streams missing");
-    NQ_REQUIRE(m >= 1 && n >= 8 && n % 8 == 0 && n <= 131072, NQ_ERR_ARG,
-               "nq_w4a4_gemm: m=%lld n=%lld unsupported (n must be a multiple of 8, <= 131072)",
+    NQ_REQUIRE(m >= 1 && n >= 8 && n % 8 == 0 && n <= 131064, NQ_ERR_ARG,
+               "nq_w4a4_gemm: m=%lld n=%lld unsupported (n must be a multiple of 8, <= 131064)",
                (long long)m, (long long)n);
     NQ_REQUIRE(k >= 32 && k % 32 == 0, NQ_ERR_ARG, "nq_w4a4_gemm: k=%lld must be a multiple of 32", (long long)k);
     NQ_REQUIRE(out_dtype == NQ_F32 || out_dtype == NQ_BF16, NQ_ERR_ARG, "nq_w4a4_gemm: out_dtype must be f32 or bf16");
@@ -85,7 +85,7 @@ extern "C" int nq_w4a4_gemm(const uint8_t* act_codes, const uint8_t* act_beta_id
     if (m > kSmallMMax && nq_tc_supported(m, n, k)) {
         int rc = nq_w4_decode(w_codes, w_beta_ids, w_norms, w_betas, n, k, w_block_offset, seed, ws + c.w_dec, stream);
         if (rc) return rc;
-        return nq_launch_tc_gemm(a_dec, ws + c.w_dec, m, n, k, out, out_dtype, ws + c.tc, s);
+        return nq_launch_tc_gemm(a_dec, ws + c.w_dec, m, n, k, out, out_dtype, ws + NQ_WS_STATUS_OFFSET, s);
     }
 
     // CUDA-core path; rows beyond 16 are processed 16 at a time
@@ -97,6 +97,19 @@ extern "C" int nq_w4a4_gemm(const uint8_t* act_codes, const uint8_t* act_beta_id
                                    reinterpret_cast<char*>(out) + (size_t)m0 * n * out_elem, out_dtype,
                                    reinterpret_cast<float*>(ws + c.partial), counters, s);
         if (rc) return rc;
+    }
+    return NQ_OK;
+}
+
+extern "C" int nq_w4a4_status(const void* workspace, uint32_t* status_host, nq_stream_t stream) {
+    NQ_REQUIRE(workspace && status_host, NQ_ERR_ARG, "nq_w4a4_status: null pointer");
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    cudaError_t e = cudaMemcpyAsync(status_host, reinterpret_cast<const char*>(workspace) + NQ_WS_STATUS_OFFSET,
+                                    sizeof(uint32_t), cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    if (e != cudaSuccess) {
+        nq_set_error("nq_w4a4_status: %s", cudaGetErrorString(e));
+        return (int)e;
     }
     return NQ_OK;
 }

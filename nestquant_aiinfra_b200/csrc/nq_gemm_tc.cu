@@ -1,4 +1,304 @@
+// Large-M packed W4A4 projection: tcgen05 GEMM over the BF16 reconstructions
+// of both operands (the weight is decoded once per call by nq_w4_decode, the
+// activation by the encoder or nq_a4_decode).
+//
+//   out[t, n] = sum_k A^[t, k] * W^[n, k]        (both operands K-major BF16)
+//
+// Mapping ("swap-AB"): the 128 output channels of a tile are the UMMA M side
+// (TMEM lanes), the tokens are the UMMA N side (up to 256 TMEM columns), so a
+// short token tile does not waste tensor-core rows.
+//
+// Persistent, warp-specialised CTA (one per SM, 192 threads):
+//   warp 0      TMA producer: 128B-swizzled [rows x 64] BF16 tiles of W^ and A^
+//               into a multi-stage shared-memory ring (no multicast)
+//   warp 1      allocates TMEM, then one elected thread issues tcgen05.mma
+//               (4 x K16 per stage) and tcgen05.commit to recycle stages
+//   warps 2..5  epilogue: tcgen05.ld of one accumulator buffer while the next
+//               tile's MMAs fill the other one (2 x 256 TMEM columns)
+// Every mbarrier wait is bounded; on a time-out the role records a code in
+// the status word, raises the CTA abort flag, in-flight copies are drained and
+// TMEM is released before the CTA returns.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <math.h>
+
 #include "nq_common.cuh"
-bool nq_tc_supported(int64_t, int64_t, int64_t) { return false; }
-size_t nq_tc_workspace_bytes(int64_t, int64_t, int64_t) { return 0; }
-int nq_launch_tc_gemm(const void*, const void*, int64_t, int64_t, int64_t, void*, int, void*, cudaStream_t) { return NQ_ERR_ARG; }
+#include "nq_sm100.cuh"
+
+namespace {
+
+using namespace nq100;
+
+constexpr int kTileN = 128;      // output channels per tile (UMMA M)
+constexpr int kTileK = 64;       // K elements per stage (one 128-byte swizzle row)
+constexpr int kThreadsTc = 192;  // 6 warps
+constexpr int kAccCols = 256;    // TMEM columns per accumulator buffer
+constexpr int kMaxStages = 8;
+
+struct TcParams {
+    int m, n, k;        // tokens, channels, features
+    int tile_t;         // tokens per tile (32, 64, 128 or 256)
+    int stages;
+    int n_tiles, t_tiles;
+    void* out;          // [m, n]
+    int out_bf16;
+    unsigned* status;   // 0 = ok
+};
+
+struct __align__(8) TcBarriers {
+    uint64_t full[kMaxStages];
+    uint64_t empty[kMaxStages];
+    uint64_t acc_full[2];
+    uint64_t acc_empty[2];
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+__device__ __forceinline__ void tc_fail(const TcParams& p, TcBarriers* bars, unsigned code) {
+    atomicCAS(p.status, 0u, code);
+    *reinterpret_cast<volatile int*>(&bars->abort_flag) = 1;
+}
+
+__global__ void __launch_bounds__(kThreadsTc, 1)
+nq_w4a4_tc_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
+                       const TcParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    // 1024-byte alignment required by the 128-byte swizzle
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const uint32_t w_bytes = kTileN * kTileK * 2;
+    const uint32_t a_bytes = (uint32_t)p.tile_t * kTileK * 2;
+    const uint32_t stage_bytes = w_bytes + a_bytes;
+    TcBarriers* bars = reinterpret_cast<TcBarriers*>(smem + (size_t)p.stages * stage_bytes);
+    volatile int* abort_flag = &bars->abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int k_steps = p.k / kTileK;
+    const int total_tiles = p.n_tiles * p.t_tiles;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < p.stages; ++s) {
+            mbar_init(&bars->full[s], 1);
+            mbar_init(&bars->empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&bars->acc_full[b], 1);
+            mbar_init(&bars->acc_empty[b], 4);  // one arrival per epilogue warp
+        }
+        bars->abort_flag = 0;
+        fence_barrier_init();
+        prefetch_tensormap(&map_w);
+        prefetch_tensormap(&map_a);
+    }
+    if (warp == 1) {
+        tmem_alloc(&bars->tmem_base, 2 * kAccCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ producer
+        if (lane == 0) {
+            uint32_t fill = 0;  // running stage-fill counter
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int n0 = (tile % p.n_tiles) * kTileN;
+                const int t0 = (tile / p.n_tiles) * p.tile_t;
+                for (int ks = 0; ks < k_steps; ++ks, ++fill) {
+                    const int s = fill % p.stages;
+                    const uint32_t use = fill / p.stages;
+                    if (use > 0 && !mbar_wait_bounded(&bars->empty[s], (use - 1) & 1, abort_flag)) {
+                        tc_fail(p, bars, 1);
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* dst = smem + (size_t)s * stage_bytes;
+                    mbar_arrive_expect_tx(&bars->full[s], stage_bytes);
+                    tma_load_2d(dst, &map_w, ks * kTileK, n0, &bars->full[s]);
+                    tma_load_2d(dst + w_bytes, &map_a, ks * kTileK, t0, &bars->full[s]);
+                }
+            }
+            if (*abort_flag) {
+                // drain: wait (bounded) for every copy this thread armed
+                for (int s = 0; s < p.stages && (uint32_t)s < fill; ++s) {
+                    const uint32_t uses = (fill - 1 - s) / p.stages + 1;
+                    mbar_wait_limit(&bars->full[s], (uses - 1) & 1, 1u << 16);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc_bf16(kTileN, (uint32_t)p.tile_t);
+            uint32_t fill = 0, local_tile = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local_tile) {
+                const uint32_t buf = local_tile & 1, use = local_tile >> 1;
+                if (use > 0 && !mbar_wait_bounded(&bars->acc_empty[buf], (use - 1) & 1, abort_flag)) {
+                    tc_fail(p, bars, 2);
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t acc = tmem_base + buf * kAccCols;
+                for (int ks = 0; ks < k_steps; ++ks, ++fill) {
+                    const int s = fill % p.stages;
+                    if (!mbar_wait_bounded(&bars->full[s], (fill / p.stages) & 1, abort_flag)) {
+                        tc_fail(p, bars, 3);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t base = smem_u32(smem + (size_t)s * stage_bytes);
+                    const uint64_t desc_w = umma_desc_sw128(base);
+                    const uint64_t desc_a = umma_desc_sw128(base + w_bytes);
+#pragma unroll
+                    for (int kk = 0; kk < kTileK / 16; ++kk) {
+                        // +32 bytes per K16 step inside the 128-byte swizzle row (16-byte units)
+                        umma_bf16(acc, desc_w + (uint64_t)(kk * 2), desc_a + (uint64_t)(kk * 2), idesc,
+                                  (ks > 0 || kk > 0) ? 1u : 0u);
+                    }
+                    umma_commit(&bars->empty[s]);
+                }
+                if (ok) umma_commit(&bars->acc_full[buf]);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue
+        const int quarter = warp & 3;  // TMEM lane quarter this warp may read
+        uint32_t local_tile = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local_tile) {
+            const uint32_t buf = local_tile & 1, use = local_tile >> 1;
+            const int n0 = (tile % p.n_tiles) * kTileN;
+            const int t0 = (tile / p.n_tiles) * p.tile_t;
+            if (!mbar_wait_bounded(&bars->acc_full[buf], use & 1, abort_flag)) {
+                if (lane == 0) tc_fail(p, bars, 4);
+                break;
+            }
+            tc_fence_after();
+            const int channel = n0 + quarter * 32 + lane;
+            const uint32_t taddr = tmem_base + buf * kAccCols + ((uint32_t)(quarter * 32) << 16);
+            for (int c = 0; c < p.tile_t; c += 32) {
+                if (t0 + c >= p.m) break;  // warp-uniform
+                uint32_t r[32];
+                tmem_ld_32x32(taddr + (uint32_t)c, r);
+                tmem_ld_wait();
+                if (p.out_bf16) {
+                    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + (int64_t)(t0 + c) * p.n + channel;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (t0 + c + j < p.m) o[(int64_t)j * p.n] = __float2bfloat16_rn(__uint_as_float(r[j]));
+                } else {
+                    float* o = reinterpret_cast<float*>(p.out) + (int64_t)(t0 + c) * p.n + channel;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (t0 + c + j < p.m) o[(int64_t)j * p.n] = __uint_as_float(r[j]);
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->acc_empty[buf]);
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 2 * kAccCols);
+    }
+}
+
+// ---- host side -----------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+    return fn;
+}
+
+// [rows, k] BF16 row-major matrix, box = [box_rows, 64], 128-byte swizzle, zero fill out of bounds.
+int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t k, int box_rows) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    NQ_REQUIRE(fn != nullptr, NQ_ERR_DEVICE, "nq_w4a4_gemm: cuTensorMapEncodeTiled is unavailable");
+    const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)k * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)kTileK, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    NQ_REQUIRE(r == CUDA_SUCCESS, NQ_ERR_ARG, "nq_w4a4_gemm: cuTensorMapEncodeTiled failed with %d", (int)r);
+    return NQ_OK;
+}
+
+int sm_count() {
+    static int count = 0;
+    if (count == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, dev);
+        if (count <= 0) count = 148;
+    }
+    return count;
+}
+
+}  // namespace
+
+bool nq_tc_supported(int64_t m, int64_t n, int64_t k) {
+    return m >= 1 && n % kTileN == 0 && k % kTileK == 0 && k >= kTileK;
+}
+
+// status word + padding
+size_t nq_tc_workspace_bytes(int64_t, int64_t, int64_t) { return 256; }
+
+int nq_launch_tc_gemm(const void* a_dec, const void* w_dec, int64_t m, int64_t n, int64_t k, void* out,
+                      int out_dtype, void* workspace, cudaStream_t stream) {
+    TcParams p;
+    p.m = (int)m; p.n = (int)n; p.k = (int)k;
+    p.tile_t = m > 128 ? 256 : (m > 64 ? 128 : (m > 32 ? 64 : 32));
+    p.n_tiles = (int)(n / kTileN);
+    p.t_tiles = (int)((m + p.tile_t - 1) / p.tile_t);
+    const size_t stage_bytes = (size_t)(kTileN + p.tile_t) * kTileK * 2;
+    int stages = (int)((200 * 1024) / stage_bytes);
+    if (stages > kMaxStages) stages = kMaxStages;
+    p.stages = stages;
+    p.out = out;
+    p.out_bf16 = out_dtype == NQ_BF16;
+    p.status = reinterpret_cast<unsigned*>(workspace);
+    CUtensorMap map_w, map_a;
+    int rc = make_map(&map_w, w_dec, n, k, kTileN);
+    if (rc) return rc;
+    rc = make_map(&map_a, a_dec, m, k, p.tile_t);
+    if (rc) return rc;
+    const size_t smem = (size_t)stages * stage_bytes + sizeof(TcBarriers) + 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(nq_w4a4_tc_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             227 * 1024);
+        if (e != cudaSuccess) {
+            nq_set_error("nq_w4a4_gemm: cannot reserve shared memory: %s", cudaGetErrorString(e));
+            return (int)e;
+        }
+        configured = true;
+    }
+    const int total = p.n_tiles * p.t_tiles;
+    const int grid = total < sm_count() ? total : sm_count();
+    nq_w4a4_tc_gemm_kernel<<<grid, kThreadsTc, smem, stream>>>(map_w, map_a, p);
+    NQ_CHECK_LAUNCH("nq_w4a4_gemm(tcgen05)");
+    return NQ_OK;
+}

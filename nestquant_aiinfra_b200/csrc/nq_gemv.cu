@@ -69,9 +69,8 @@ __global__ void __launch_bounds__(kThreads) nq_w4a4_small_m_kernel(const SmallMP
 
     for (int b = lane; b < slice_n; b += 32) {
         const int64_t g = (int64_t)row * bpr + slice0 + b;
-        float d[8], w[8];
-        nq_dither_block(p.counter_base + (uint32_t)g * 8u, d);
-        nq_decode_codeword_exact(__ldg(p.w_codes + g), d, w);
+        float w[8];
+        nq_decode_weight_block(__ldg(p.w_codes + g), p.counter_base + (uint32_t)g * 8u, w);
         const float bt = __ldg(p.w_betas + nq_beta_id(p.w_beta_ids, g));
 #pragma unroll
         for (int j = 0; j < 8; ++j) w[j] = nq_bf16_round(nq_mul(nq_mul(w[j], bt), ds));

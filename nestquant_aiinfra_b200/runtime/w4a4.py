@@ -265,6 +265,17 @@ def _run(activation: PreparedNQA4Activation, weight: PreparedNQRTLinear, out_dty
     return out
 
 
+def read_status(device: torch.device | str = "cuda") -> int:
+    """Device status word of the current stream's workspace (synchronises); 0 = ok."""
+    device = torch.device(device)
+    if device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    workspace = workspace_for(device, 1)
+    value = ctypes.c_uint32(0)
+    _lib.check(_lib.lib().nq_w4a4_status(_ptr(workspace), ctypes.byref(value), _stream(device)), "read_status")
+    return int(value.value)
+
+
 def _check_types(activation, weight) -> None:
     if not isinstance(activation, PreparedNQA4Activation):
         raise TypeError("activation must be PreparedNQA4Activation")

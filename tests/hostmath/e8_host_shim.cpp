@@ -34,3 +34,15 @@ void shim_encode_blocks(const float* x, long n, const float* beta, long seed, lo
 
 float shim_bf16_round(float v) { return nq_bf16_round(v); }
 }
+
+extern "C" {
+void shim_nearest_e8_guarded(const float* x, float* out, long n) {
+    for (long i = 0; i < n; ++i) nq_e8_nearest_guarded(x + 8 * i, out + 8 * i);
+}
+
+// Weight-path decode of packed codewords: r = t - d - 14 Q((t - d)/14).
+void shim_decode_weight(const uint32_t* words, long n, long first_block, long seed, float* out) {
+    for (long i = 0; i < n; ++i)
+        nq_decode_weight_block(words[i], (uint32_t)((uint64_t)(first_block + i) * 8u + (uint64_t)seed), out + 8 * i);
+}
+}

@@ -122,6 +122,7 @@ def _projection_case(rt, oracle, m, n, k):
     expected = oracle.gemm_bf16_operands(a_deq, w_deq)
     actual = rt.linear_packed_w4a4_fp32(act, weight).cpu().numpy()
     assert actual.shape == (m, n)
+    assert rt.read_status() == 0
     assert max_abs(actual, expected) <= MAX_ABS_TOL, (max_abs(actual, expected), rel_fro(actual, expected))
     assert rel_fro(actual, expected) <= REL_FRO_TOL, rel_fro(actual, expected)
     # same result when the kernel decodes the packed activation itself

@@ -19,7 +19,7 @@ ROOT = Path(__file__).resolve().parents[1]
 @pytest.fixture(scope="module")
 def shim(tmp_path_factory):
     out = tmp_path_factory.mktemp("shim") / "libshim.so"
-    subprocess.run(["g++", "-O2", "-shared", "-fPIC", "-ffp-contract=off",
+    subprocess.run(["g++", "-O2", "-shared", "-fPIC", "-ffp-contract=off", "-mfma",
                     "-I", str(ROOT / "nestquant_aiinfra_b200" / "csrc"), "-o", str(out),
                     str(ROOT / "tests" / "hostmath" / "e8_host_shim.cpp")], check=True)
     return ctypes.CDLL(str(out))
@@ -65,3 +65,26 @@ def test_bf16_rounding(shim, oracle):
     values = np.array([1.0, 1.00390625, 1.01171875, -3.1415927, 1e-20, 65504.0], np.float32)
     got = np.array([shim.shim_bf16_round(ctypes.c_float(v)) for v in values], np.float32)
     assert np.array_equal(got, oracle.round_bf16(values))
+
+
+def test_guarded_nearest_equals_exact(shim, oracle, golden):
+    x = golden["e8_in"]
+    out = np.empty_like(x)
+    shim.shim_nearest_e8_guarded(_p(x), _p(out), ctypes.c_long(len(x)))
+    assert np.array_equal(out, golden["e8_out"])
+    x = (np.random.default_rng(1).standard_normal((500000, 8)) * 2).astype(np.float32)
+    out = np.empty_like(x)
+    shim.shim_nearest_e8_guarded(_p(x), _p(out), ctypes.c_long(len(x)))
+    assert np.array_equal(out, oracle.nearest_e8(x))
+
+
+def test_weight_block_decode_matches_checker(shim, oracle):
+    n = 300000
+    codes = np.random.default_rng(2).integers(0, 14, (n, 8)).astype(np.uint8)
+    words = np.ascontiguousarray(oracle.pack(codes, 4)).view(np.uint32)
+    out = np.empty((n, 8), np.float32)
+    shim.shim_decode_weight(_p(words), ctypes.c_long(n), ctypes.c_long(77), ctypes.c_long(4242), _p(out))
+    ref = oracle.dequantize_rows(oracle.pack(codes, 4), np.zeros(n // 4, np.uint8),
+                                 np.full(1, np.float32(np.sqrt(8 * n))), [1.0] * 4, 1, 8 * n, seed=4242,
+                                 block_offset=77)
+    assert np.array_equal(out.reshape(-1), ref.reshape(-1))
