@@ -61,6 +61,17 @@ int nq_a4_encode(const void* x, int x_dtype, int64_t rows, int64_t k, int64_t ro
                  const float* beta_table, uint8_t* out_codes, uint8_t* out_beta_ids,
                  float* out_norms, void* out_decoded, nq_stream_t stream);
 
+/* Weight encoder: the same search with the stateless subtractive dither of
+ * global block  w_block_offset + row*k/8 + block  ("lcg31_mix_v1",
+ * core/codec.py:176-224).  Bit-exact with quantize_rows(W, 14, betas,
+ * dither=generate_e8_dither_stateless(...)) + pack_nestquant_indices, i.e. with
+ * the streams PackedNestQuantTensor.from_quantized_rows stores
+ * (core/tensor_checkpoint.py:59-118).  Replaces the CPU-only offline encode of
+ * models/quantization.py for synthetic / re-sharded weights. */
+int nq_w4_encode(const void* w, int w_dtype, int64_t rows, int64_t k, int64_t row_stride,
+                 const float* beta_table, int64_t seed, int64_t w_block_offset,
+                 uint8_t* out_codes, uint8_t* out_beta_ids, float* out_norms, nq_stream_t stream);
+
 /* Diagnostic / operand decode of a packed undithered stream.
  * Replaces decode_packed_a4_m16 (runtime/cuda_w4a4_mma.py:688-696, kernel
  * nqrt4_w4a4_mma.cu:83-93) and dequantize_nqkv_page_triton
@@ -115,6 +126,13 @@ int nq_w4a4_status(const void* workspace, uint32_t* status_host, nq_stream_t str
 int nq_w4_decode(const uint8_t* w_codes, const uint8_t* w_beta_ids, const float* w_norms,
                  const float* w_betas, int64_t n, int64_t k, int64_t w_block_offset,
                  int64_t seed, void* out_bf16, nq_stream_t stream);
+
+/* -------------------------------------------------------------------------
+ * Normalised Sylvester Hadamard along the last axis of a contiguous [rows, n]
+ * tensor, n a power of two <= 32768, computed in the tensor's dtype exactly as
+ * hadamard() does (core/rotation.py:12-27): every butterfly stage rounded to
+ * the dtype, final IEEE division by float32(sqrt(n)).  x may equal out. */
+int nq_hadamard(const void* x, void* out, int dtype, int64_t rows, int64_t n, nq_stream_t stream);
 
 #ifdef __cplusplus
 }

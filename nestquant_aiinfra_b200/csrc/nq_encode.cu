@@ -36,7 +36,7 @@ nq_encode_rows_kernel(const T* __restrict__ x, int64_t rows, int k, int64_t row_
                       const float* __restrict__ beta_table, float sqrt_k,
                       uint32_t* __restrict__ codes, uint8_t* __restrict__ beta_ids,
                       float* __restrict__ norms, __nv_bfloat16* __restrict__ decoded,
-                      int rows_per_cta) {
+                      int rows_per_cta, int use_dither, uint32_t counter_base) {
     extern __shared__ float smem[];
     const int bpr = k >> 3;
     const int pitch = k + 8;  // de-conflicts the strided chain reads of neighbouring rows
@@ -95,8 +95,15 @@ nq_encode_rows_kernel(const T* __restrict__ x, int64_t rows, int k, int64_t row_
             const float s = scale[r];
 #pragma unroll
             for (int j = 0; j < 8; ++j) v[j] = nq_mul(v[j], s);
-            const uint32_t word = nq_encode_block(v, beta_table, nullptr, bid, recon);
             const int64_t g = row0 * bpr + b;
+            uint32_t word;
+            if (use_dither) {  // weights: subtractive dither of global block g (warp-uniform branch)
+                float d[8];
+                nq_dither_block(counter_base + (uint32_t)g * 8u, d);
+                word = nq_encode_block(v, beta_table, d, bid, recon);
+            } else {
+                word = nq_encode_block(v, beta_table, nullptr, bid, recon);
+            }
             codes[g] = word;
             if (decoded != nullptr) {
                 const float ds = dscale[r];
@@ -170,7 +177,8 @@ static int encode_rows_per_cta(int64_t k) {
 template <typename T>
 static int launch_encode(const void* x, int64_t rows, int64_t k, int64_t row_stride,
                          const float* beta_table, uint8_t* out_codes, uint8_t* out_beta_ids,
-                         float* out_norms, void* out_decoded, cudaStream_t stream) {
+                         float* out_norms, void* out_decoded, cudaStream_t stream,
+                         int use_dither = 0, uint32_t counter_base = 0) {
     const int rpc = encode_rows_per_cta(k);
     const size_t smem = ((size_t)rpc * (k + 8) + (size_t)rpc * 10) * sizeof(float);
     auto kernel = nq_encode_rows_kernel<T>;
@@ -185,7 +193,7 @@ static int launch_encode(const void* x, int64_t rows, int64_t k, int64_t row_str
     kernel<<<(unsigned)grid, 256, smem, stream>>>(
         reinterpret_cast<const T*>(x), rows, (int)k, row_stride, beta_table,
         (float)sqrt((double)k), reinterpret_cast<uint32_t*>(out_codes), out_beta_ids, out_norms,
-        reinterpret_cast<__nv_bfloat16*>(out_decoded), rpc);
+        reinterpret_cast<__nv_bfloat16*>(out_decoded), rpc, use_dither, counter_base);
     NQ_CHECK_LAUNCH("nq_a4_encode");
     return NQ_OK;
 }
@@ -210,6 +218,28 @@ extern "C" int nq_a4_encode(const void* x, int x_dtype, int64_t rows, int64_t k,
         case NQ_BF16: return launch_encode<__nv_bfloat16>(x, rows, k, row_stride, beta_table, out_codes, out_beta_ids, out_norms, out_decoded, s);
         case NQ_F16: return launch_encode<__half>(x, rows, k, row_stride, beta_table, out_codes, out_beta_ids, out_norms, out_decoded, s);
         default: nq_set_error("nq_a4_encode: unknown dtype %d", x_dtype); return NQ_ERR_ARG;
+    }
+}
+
+extern "C" int nq_w4_encode(const void* w, int w_dtype, int64_t rows, int64_t k, int64_t row_stride,
+                            const float* beta_table, int64_t seed, int64_t w_block_offset,
+                            uint8_t* out_codes, uint8_t* out_beta_ids, float* out_norms, nq_stream_t stream) {
+    NQ_REQUIRE(w && beta_table && out_codes && out_beta_ids && out_norms, NQ_ERR_ARG, "nq_w4_encode: null pointer");
+    NQ_REQUIRE(rows >= 1 && k >= 32 && k <= 32768 && k % 32 == 0 && row_stride >= k, NQ_ERR_ARG,
+               "nq_w4_encode: bad shape rows=%lld k=%lld", (long long)rows, (long long)k);
+    NQ_REQUIRE(seed >= 0 && seed < ((int64_t)1 << 31) && w_block_offset >= 0 &&
+                   w_block_offset + rows * (k / 8) <= ((int64_t)1 << 28),
+               NQ_ERR_ARG, "nq_w4_encode: dither seed / block range outside the 31-bit counter space");
+    const int64_t esize = w_dtype == NQ_F32 ? 4 : 2;
+    NQ_REQUIRE(nq_aligned16(w) && (row_stride * esize) % 16 == 0 && nq_aligned16(out_codes), NQ_ERR_ALIGN,
+               "nq_w4_encode: 16-byte alignment required");
+    const uint32_t base = (uint32_t)((uint64_t)w_block_offset * 8u + (uint64_t)seed);
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    switch (w_dtype) {
+        case NQ_F32: return launch_encode<float>(w, rows, k, row_stride, beta_table, out_codes, out_beta_ids, out_norms, nullptr, s, 1, base);
+        case NQ_BF16: return launch_encode<__nv_bfloat16>(w, rows, k, row_stride, beta_table, out_codes, out_beta_ids, out_norms, nullptr, s, 1, base);
+        case NQ_F16: return launch_encode<__half>(w, rows, k, row_stride, beta_table, out_codes, out_beta_ids, out_norms, nullptr, s, 1, base);
+        default: nq_set_error("nq_w4_encode: unknown dtype %d", w_dtype); return NQ_ERR_ARG;
     }
 }
 

@@ -192,6 +192,45 @@ def quantize_activation_cuda(
         output_dtype=inputs.dtype, decoded=decoded)
 
 
+def quantize_weight_cuda(weight: torch.Tensor, *, betas: Sequence[float], dither_seed: int,
+                         tensor_name: str = "weight", q: int = 14) -> PreparedNQRTLinear:
+    """Encode a ``[N, K]`` weight on the GPU into NQRT4 streams (stateless dither).
+
+    Bit-exact with the reference's CPU encode
+    (``quantize_rows(W, 14, betas, dither=generate_e8_dither_stateless(N*K/8, seed))``
+    followed by ``PackedNestQuantTensor.from_quantized_rows``).  Returns the prepared
+    (device-resident) weight; ``.record`` carries the metadata and host copies are made
+    lazily by ``record.indices`` consumers only.
+    """
+    from ..formats import PackedNestQuantIndices, PackedNestQuantTensor
+
+    if not isinstance(weight, torch.Tensor) or not weight.is_floating_point() or weight.ndim != 2:
+        raise TypeError("weight must be a floating-point [N, K] tensor")
+    if weight.device.type != "cuda":
+        raise ValueError("weight must be a CUDA tensor")
+    if q != 14 or len(tuple(betas)) != 4:
+        raise ValueError("the sm_100a encoder implements q=14 with four betas")
+    if weight.dtype not in _DTYPE_TAG:
+        raise ValueError("weight must use float16, bfloat16, or float32")
+    w = weight.contiguous()
+    n, k = w.shape
+    device = w.device
+    beta_table = torch.tensor(tuple(float(b) for b in betas), device=device, dtype=torch.float32)
+    codes = torch.empty(n * k // 2, dtype=torch.uint8, device=device)
+    beta_ids = torch.empty(n * k // 32, dtype=torch.uint8, device=device)
+    norms = torch.empty(n, dtype=torch.float32, device=device)
+    status = _lib.lib().nq_w4_encode(_ptr(w), _DTYPE_TAG[w.dtype], _I64(n), _I64(k), _I64(k), _ptr(beta_table),
+                                     _I64(int(dither_seed)), _I64(0), _ptr(codes), _ptr(beta_ids), _ptr(norms),
+                                     _stream(device))
+    _lib.check(status, "quantize_weight_cuda")
+    record = PackedNestQuantTensor(
+        tensor_name=tensor_name,
+        indices=PackedNestQuantIndices((n, k // 8, 8), 14, 4, b"", b""),
+        row_norms=norms, betas=tuple(float(b) for b in betas), feature_count=k, dither_seed=int(dither_seed))
+    return PreparedNQRTLinear(record=record, code_payload=codes, beta_payload=beta_ids, row_norms=norms,
+                              beta_table=beta_table)
+
+
 # ---------------------------------------------------------------------------
 # predicates (host only; return False instead of raising, as the reference does)
 # ---------------------------------------------------------------------------

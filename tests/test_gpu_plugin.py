@@ -1,0 +1,98 @@
+"""GPU parity of the Hadamard kernel and of the FusedNQRTLinear plugin boundary."""
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import ACT_BETAS, MAX_ABS_TOL, REL_FRO_TOL, make_weight_record, max_abs, rel_fro, rng
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("rows,n,dtype", [(3, 2048, torch.float32), (3, 2048, torch.bfloat16), (5, 64, torch.float32),
+                                          (257, 64, torch.bfloat16), (4, 8192, torch.bfloat16), (7, 128, torch.float16),
+                                          (2, 16384, torch.float32), (9, 8, torch.float32)])
+def test_hadamard_bit_exact(oracle, golden, rows, n, dtype):
+    from nestquant_aiinfra_b200.rotation import hadamard, hadamard_butterflies
+
+    if (rows, n) == (3, 2048):
+        key = "had_f32" if dtype == torch.float32 else "had_bf16"
+        x = torch.from_numpy(golden[key + "_in"]).to(dtype)
+        expected = torch.from_numpy(golden[key + "_out"]).to(dtype)
+    elif (rows, n) == (5, 64):
+        x, expected = torch.from_numpy(golden["had_64_in"]), torch.from_numpy(golden["had_64_out"])
+    else:
+        x = torch.randn(rows, n, generator=rng(n + rows)).to(dtype)
+        expected = hadamard_butterflies(x)  # the reference's own op sequence, on the CPU
+    got = hadamard(x.cuda()).cpu()
+    assert got.dtype == dtype and torch.equal(got, expected)
+
+
+def test_hadamard_rejects_non_power_of_two():
+    from nestquant_aiinfra_b200.rotation import hadamard
+
+    with pytest.raises(ValueError):
+        hadamard(torch.zeros(2, 24, device="cuda"))
+
+
+def _linear_oracle(oracle, x_bf16: torch.Tensor, w_deq: np.ndarray) -> np.ndarray:
+    m, k = x_bf16.shape
+    rotated = oracle.hadamard(x_bf16.float().numpy(), round_bf16=True)
+    ac, ab, an = oracle.encode_packed(rotated, ACT_BETAS)
+    a_deq = oracle.dequantize_rows(ac, ab, an, ACT_BETAS, m, k)
+    return oracle.gemm_bf16_operands(a_deq, w_deq)
+
+
+@pytest.mark.parametrize("m", [1, 5, 48, 300])
+def test_fused_linear_forward_matches_checker(oracle, m):
+    from nestquant_aiinfra_b200.fused_linear import FusedNQRTLinear
+
+    n, k = 256, 1024
+    record, w_deq = make_weight_record(oracle, n, k, seed=11, dither_seed=123)
+    layer = FusedNQRTLinear(record, input_hadamard=True, activation_betas=ACT_BETAS).cuda()
+    x = torch.randn(2, m, k, generator=rng(m)).bfloat16()
+    with torch.no_grad():
+        y = layer(x.cuda())
+    assert y.dtype == torch.bfloat16 and tuple(y.shape) == (2, m, n)
+    expected = _linear_oracle(oracle, x.reshape(-1, k), w_deq)
+    actual = y.float().cpu().numpy().reshape(-1, n)
+    # output is BF16-rounded: allow one BF16 ulp of the largest output on top of the accumulator bar
+    bar = MAX_ABS_TOL + float(np.abs(expected).max()) * 2 ** -8
+    assert max_abs(actual, expected) <= bar
+    assert rel_fro(actual, expected) <= 4e-3  # BF16 output rounding alone costs ~1.7e-3
+    assert layer.a4_encode_count == 1 and layer.w4a4_cuda_mma_dispatch_count == 1
+
+
+def test_shared_caches_encode_once(oracle):
+    from nestquant_aiinfra_b200.fused_linear import (FusedNQRTLinear, SharedHadamardCache,
+                                                       SharedPackedActivationCache)
+
+    k = 512
+    rec_a, _ = make_weight_record(oracle, 64, k, seed=1, dither_seed=1)
+    rec_b, _ = make_weight_record(oracle, 128, k, seed=2, dither_seed=2)
+    hcache, acache = SharedHadamardCache(2), SharedPackedActivationCache(2)
+    kwargs = dict(input_hadamard=True, input_transform_cache=hcache, packed_activation_cache=acache,
+                  activation_betas=ACT_BETAS)
+    a, b = FusedNQRTLinear(rec_a, **kwargs).cuda(), FusedNQRTLinear(rec_b, **kwargs).cuda()
+    solo = FusedNQRTLinear(rec_b, input_hadamard=True, activation_betas=ACT_BETAS).cuda()
+    x = torch.randn(3, k, generator=rng(9)).bfloat16().cuda()
+    with torch.no_grad():
+        ya, yb, ys = a(x), b(x), solo(x)
+    assert (hcache.misses, hcache.hits, acache.misses, acache.hits) == (1, 1, 1, 1)
+    assert a.a4_encode_count == 1 and b.a4_encode_count == 0
+    assert torch.equal(yb, ys) and ya.shape == (3, 64)
+
+
+def test_fused_linear_errors(oracle):
+    from nestquant_aiinfra_b200.fused_linear import FusedNQRTLinear
+
+    record, _ = make_weight_record(oracle, 64, 256, seed=1, dither_seed=1)
+    with pytest.raises(ValueError):
+        FusedNQRTLinear(record, activation_betas=None)
+    with pytest.raises(ValueError):
+        FusedNQRTLinear(record, compute_backend="tensor_core_dot", activation_betas=ACT_BETAS)
+    layer = FusedNQRTLinear(record, activation_betas=ACT_BETAS).cuda()
+    with pytest.raises(ValueError):
+        layer(torch.zeros(1, 128, device="cuda"))
+    with pytest.raises(ValueError):
+        layer(torch.zeros(1, 256))

@@ -95,6 +95,24 @@ def test_weight_decode_bit_exact(rt, oracle):
     assert torch.equal(got, torch.from_numpy(deq).bfloat16())
 
 
+@pytest.mark.parametrize("n,k,dtype", [(96, 512, torch.float32), (64, 2048, torch.float32), (40, 8192, torch.bfloat16)])
+def test_weight_encoder_bit_exact(rt, oracle, golden, n, k, dtype):
+    if (n, k) == (96, 512):
+        w = torch.from_numpy(golden["w_x"])
+    else:
+        w = torch.from_numpy(oracle.hadamard((0.02 * torch.randn(n, k, generator=rng(n + k))).numpy())).to(dtype)
+    seed = int(golden["dither_seed"][0])
+    prepared = rt.quantize_weight_cuda(w.cuda(), betas=W_BETAS, dither_seed=seed)
+    codes, beta_ids, norms = oracle.encode_packed(w.float().numpy(), W_BETAS, seed=seed)
+    assert np.array_equal(prepared.code_payload.cpu().numpy(), codes)
+    assert np.array_equal(prepared.beta_payload.cpu().numpy(), beta_ids)
+    assert np.array_equal(prepared.row_norms.cpu().numpy(), norms)
+    if (n, k) == (96, 512):
+        assert np.array_equal(codes, golden["w_codes"]) and np.array_equal(beta_ids, golden["w_beta_ids"])
+    deq = oracle.dequantize_rows(codes, beta_ids, norms, W_BETAS, n, k, seed=seed)
+    assert torch.equal(rt.decode_packed_weight(prepared).cpu(), torch.from_numpy(deq).bfloat16())
+
+
 SHAPES = [(64, 256), (512, 2048), (2048, 2048), (256, 8192), (96, 96 * 32)]
 
 
@@ -104,7 +122,7 @@ def test_projection_small_shapes(rt, oracle, m, n, k):
     _projection_case(rt, oracle, m, n, k)
 
 
-@pytest.mark.parametrize("m,n,k", [(1, 256, 8192), (16, 256, 8192), (1, 96, 3072), (64, 512, 2048), (128, 2048, 2048),
+@pytest.mark.parametrize("m,n,k", [(1, 256, 8192), (16, 256, 8192), (1, 96, 4096), (64, 512, 2048), (128, 2048, 2048),
                                    (200, 512, 2048), (512, 512, 2048), (384, 256, 8192)])
 def test_projection_more_shapes(rt, oracle, m, n, k):
     _projection_case(rt, oracle, m, n, k)
