@@ -1,0 +1,412 @@
+#!/usr/bin/env python
+"""Benchmark of the packed W4A4 projection sweep (one JSON line on stdout).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload ("w4a4_projection_sweep"): the four Llama-3.2-1B projection shapes
+(N x K: 2048x2048, 512x2048, 8192x2048, 2048x8192), weights N(0, 0.02^2)
+Hadamard-rotated and NQRT4-encoded with the stateless dither, activations
+seeded BF16 N(0,1) Hadamard-rotated with M in {1,8,16,64,128,512,2048,8192}
+rows.  One step = on-the-fly A4 encode + packed projection for all 32 cells.
+`value` is 2*M*N*K summed over the cells divided by the device time of a step,
+inputs already resident in HBM; `e2e` is the same sweep through the
+FusedNQRTLinear plugin call with pinned host inputs and outputs (copies timed).
+With N > 1 GPUs (torchrun) every rank runs the same sweep on its own GPU: the
+projections are independent, so there is no data-path collective.
+
+`--impl reference` times the CPU checker (a C restatement of the reference's
+PyTorch-CPU path, all host threads) on a bounded sample of the same sweep.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+SHAPES = (("q_o", 2048, 2048), ("k_v", 512, 2048), ("gate_up", 8192, 2048), ("down", 2048, 8192))
+TOKENS = (1, 8, 16, 64, 128, 512, 2048, 8192)
+CPU_SAMPLE_TOKENS = (1, 16, 128, 512)
+ACT_BETAS = tuple(v / 14 for v in (3.47, 4.74, 6.90, 18.11))
+W_BETAS = tuple(v / 14 for v in (4.0, 5.5, 7.0, 18.0))
+METRIC = "w4a4_e8_gemm_sweep_tflops"
+UNIT = "TFLOP/s"
+
+
+def sweep_flops(tokens=TOKENS) -> float:
+    return float(sum(2 * m * n * k for _, n, k in SHAPES for m in tokens))
+
+
+def peaks() -> dict:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        data = json.loads(path.read_text())
+        return {"hbm_gbs": float(data["hbm_gbs"]), "bf16_tflops": float(data["bf16_tflops"]),
+                "bf16_tflops_sustained": float(data.get("bf16_tflops_sustained", data["bf16_tflops"])),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+# --------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int) -> None:
+        self.gpu_index = gpu_index
+        self.lines: list[str] = []
+        self.proc = None
+        self.thread = None
+
+    def start(self) -> None:
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._pump, daemon=True)
+        self.thread.start()
+
+    def _pump(self) -> None:
+        assert self.proc is not None and self.proc.stdout is not None
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, sm_max, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                sm_max.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[5:9]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(sm_max) if sm_max else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------- CPU arm
+def cpu_sample_once(oracle, np, weights, activations) -> None:
+    """One pass of the bounded CPU sample: encode A, dequantise both operands, product."""
+    for (name, n, k), (wc, wb, wn, seed) in zip(SHAPES, weights):
+        w_deq = oracle.dequantize_rows(wc, wb, wn, W_BETAS, n, k, seed=seed)
+        for m in CPU_SAMPLE_TOKENS:
+            x = activations[(k, m)]
+            ac, ab, an = oracle.encode_packed(x, ACT_BETAS)
+            a_deq = oracle.dequantize_rows(ac, ab, an, ACT_BETAS, m, k)
+            oracle.gemm_f32(a_deq, w_deq)
+
+
+def cpu_setup():
+    import numpy as np
+
+    from oracle import nq_oracle as oracle
+
+    oracle.build()
+    rng = np.random.default_rng(1000)
+    weights, activations = [], {}
+    for i, (name, n, k) in enumerate(SHAPES):
+        w = oracle.hadamard((0.02 * rng.standard_normal((n, k))).astype(np.float32))
+        seed = 20261029 + i
+        wc, wb, wn = oracle.encode_packed(w, W_BETAS, seed=seed)
+        weights.append((wc, wb, wn, seed))
+        for m in CPU_SAMPLE_TOKENS:
+            if (k, m) not in activations:
+                x = oracle.round_bf16(rng.standard_normal((m, k)).astype(np.float32))
+                activations[(k, m)] = oracle.hadamard(x, round_bf16=True)
+    return oracle, np, weights, activations
+
+
+def cpu_baseline(repeats: int = 1, warmup: int = 0) -> dict:
+    oracle, np, weights, activations = cpu_setup()
+    for _ in range(warmup):
+        cpu_sample_once(oracle, np, weights, activations)
+    start = time.perf_counter()
+    for _ in range(repeats):
+        cpu_sample_once(oracle, np, weights, activations)
+    seconds = (time.perf_counter() - start) / repeats
+    flops = sweep_flops(CPU_SAMPLE_TOKENS)
+    return {"value": flops / seconds / 1e12, "unit": UNIT, "cores": oracle.thread_count(), "kind": "port",
+            "sample": f"cells M in {list(CPU_SAMPLE_TOKENS)} x 4 shapes: A4 encode + dequantise W and A + fp32 product "
+                      f"({seconds:.2f} s per pass)", "seconds_per_pass": seconds}
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    base = cpu_baseline(repeats=max(1, args.steps), warmup=min(args.warmup, 1))
+    seconds = base.pop("seconds_per_pass")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": seconds * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "w4a4_projection_sweep", "shapes": [list(s) for s in SHAPES],
+                   "tokens": list(CPU_SAMPLE_TOKENS), "note": "bounded CPU sample of the GPU arm's sweep"},
+        "cpu_baseline": base,
+        "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------- GPU arm
+def gpu_setup(torch, rt, device):
+    from nestquant_aiinfra_b200.rotation import hadamard
+
+    gen = torch.Generator(device="cpu").manual_seed(1000)
+    weights, inputs = [], {}
+    for i, (name, n, k) in enumerate(SHAPES):
+        w = hadamard((0.02 * torch.randn(n, k, generator=gen)).to(device))
+        weights.append(rt.quantize_weight_cuda(w, betas=W_BETAS, dither_seed=20261029 + i, tensor_name=name))
+        del w
+    for k in sorted({k for _, _, k in SHAPES}):
+        for m in TOKENS:
+            x = torch.randn(m, k, generator=torch.Generator().manual_seed(2000 + m)).bfloat16().to(device)
+            inputs[(k, m)] = hadamard(x)
+    beta_table = torch.tensor(ACT_BETAS, dtype=torch.float32, device=device)
+    torch.cuda.synchronize(device)
+    return weights, inputs, beta_table
+
+
+def run_gpu(args) -> None:
+    import torch
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback (use --impl reference for the CPU arm)")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    distributed = world > 1
+    if distributed:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=device)
+    import nestquant_aiinfra_b200.runtime as rt
+    from nestquant_aiinfra_b200.fused_linear import FusedNQRTLinear
+
+    weights, inputs, beta_table = gpu_setup(torch, rt, device)
+    cells = [(si, m) for si in range(len(SHAPES)) for m in TOKENS]
+    stream = torch.cuda.current_stream(device)
+
+    encode_events: list = []
+
+    def step(record: bool) -> None:
+        for si, m in cells:
+            _, n, k = SHAPES[si]
+            x = inputs[(k, m)]
+            if record:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+            act = rt.quantize_activation_cuda(x, q=14, betas=ACT_BETAS, beta_table=beta_table)
+            if record:
+                e1.record(stream)
+                encode_events.append((m, k, e0, e1))
+            rt.linear_packed_w4a4(act, weights[si])
+
+    def barrier() -> None:
+        if distributed:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+
+    for _ in range(max(args.warmup, 3)):
+        step(False)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    launches0 = rt.launch_count()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    start.record(stream)
+    for _ in range(args.steps):
+        step(True)
+    stop.record(stream)
+    barrier()
+    launches = rt.launch_count() - launches0
+    clocks = sampler.stop()
+    elapsed_ms = start.elapsed_time(stop)
+    if rt.read_status(device) != 0:
+        raise SystemExit("device status word is non-zero: a bounded wait in the GEMM gave up")
+    if distributed:
+        t = torch.tensor([elapsed_ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms = float(t.item())
+    ms_per_step = elapsed_ms / args.steps
+    value = world * sweep_flops() / (ms_per_step * 1e-3) / 1e12
+
+    # dominant kernel (by device time): the A4 encoder, HBM-bound by bytes
+    pk = peaks()
+    enc_bytes = sum(m * k * 2 + m * (17 * k // 32 + 4) for m, k, _, _ in encode_events)
+    enc_ms = sum(e0.elapsed_time(e1) for _, _, e0, e1 in encode_events)
+    enc_gbs = enc_bytes / (enc_ms * 1e-3) / 1e9
+    roofline = {"kernel": "nq_encode_rows_kernel", "bound": "hbm", "achieved": enc_gbs, "peak": pk["hbm_gbs"],
+                "unit": "GB/s", "frac": enc_gbs / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"],
+                "share_of_step": enc_ms / elapsed_ms, "launches": len(encode_events)}
+
+    # per-cell table and the tensor-bound kernel alone (outside the timed region)
+    table, gemm = ([], None) if args.skip_extras else cell_table(torch, rt, weights, inputs, beta_table, device, pk)
+
+    e2e = ({"ms": float("nan"), "h2d": 0, "d2h": 0} if args.skip_extras else
+           run_e2e(torch, rt, FusedNQRTLinear, weights, device, min(args.steps, 3), distributed))
+    if distributed:
+        t = torch.tensor([e2e["ms"]], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e["ms"] = float(t.item())
+    e2e_value = world * sweep_flops() / (e2e["ms"] * 1e-3) / 1e12
+
+    if rank == 0:
+        base = cpu_baseline(repeats=2) if world == 1 and not args.skip_extras else None
+        if base:
+            base.pop("seconds_per_pass", None)
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "w4a4_projection_sweep", "shapes": [list(s) for s in SHAPES],
+                       "tokens": list(TOKENS), "q": 14, "betas": 4, "encode": "on the fly every call",
+                       "l2": "one step touches > 1 GB of distinct operands, so inputs of a cell are evicted from the "
+                             "126 MB L2 before the cell repeats", "parallelism": f"replicas{world}"},
+            "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],
+                    "ms_per_step": e2e["ms"]},
+            "gpu_launches": int(launches),
+            "roofline": roofline,
+            "roofline_gemm": gemm,
+            "cpu_baseline": base,
+            "cells": table,
+        }
+        print(json.dumps(line), flush=True)
+    if distributed:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def _time_graph(torch, fn, device, reps: int = 5) -> float:
+    """Average device time of fn() in microseconds (CUDA-graph replay of `reps` calls)."""
+    side = torch.cuda.Stream(device)
+    with torch.cuda.stream(side):
+        fn()
+        torch.cuda.synchronize(device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            for _ in range(reps):
+                fn()
+        graph.replay()
+        torch.cuda.synchronize(device)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(side)
+        graph.replay()
+        e1.record(side)
+        torch.cuda.synchronize(device)
+    return e0.elapsed_time(e1) * 1e3 / reps
+
+
+def cell_table(torch, rt, weights, inputs, beta_table, device, pk):
+    """Per-cell device times: encode, projection (decode + GEMM), GB/s of packed weights, TFLOP/s."""
+    table, best = [], None
+    for si, (name, n, k) in enumerate(SHAPES):
+        w = weights[si]
+        w_dec = rt.decode_packed_weight(w)
+        w_bytes = n * k * 17 // 32 + 4 * n + 32
+        for m in TOKENS:
+            x = inputs[(k, m)]
+            act = rt.quantize_activation_cuda(x, q=14, betas=ACT_BETAS, beta_table=beta_table)
+            t_enc = _time_graph(torch, lambda: rt.quantize_activation_cuda(x, q=14, betas=ACT_BETAS, beta_table=beta_table), device)
+            t_proj = _time_graph(torch, lambda: rt.linear_packed_w4a4(act, w), device)
+            row = {"shape": name, "M": m, "encode_us": round(t_enc, 2), "proj_us": round(t_proj, 2),
+                   "w_gbs": round((w_bytes + m * k * 2 + m * n * 2) / t_proj / 1e3, 1),
+                   "tflops": round(2 * m * n * k / t_proj / 1e6, 2)}
+            if m >= 512:
+                t_mma = _time_graph(torch, lambda: rt.gemm_bf16_tc(act.decoded, w_dec), device)
+                row["mma_us"] = round(t_mma, 2)
+                row["mma_tflops"] = round(2 * m * n * k / t_mma / 1e6, 1)
+                if best is None or row["mma_tflops"] > best["achieved"]:
+                    best = {"kernel": "nq_w4a4_tc_gemm_kernel", "bound": "tensor", "achieved": row["mma_tflops"],
+                            "peak": pk["bf16_tflops"], "unit": "TFLOP/s", "frac": row["mma_tflops"] / pk["bf16_tflops"],
+                            "cell": f"{name} M={m}", "peak_source": pk["source"]}
+            table.append(row)
+        del w_dec
+    return table, best
+
+
+def run_e2e(torch, rt, FusedNQRTLinear, weights, device, steps: int, distributed: bool) -> dict:
+    """The sweep through the plugin call with pinned host inputs and outputs."""
+    layers = [FusedNQRTLinear(w, input_hadamard=True, activation_betas=ACT_BETAS).to(device) for w in weights]
+    host_in, host_out = {}, {}
+    for _, _, k in SHAPES:
+        for m in TOKENS:
+            if (k, m) not in host_in:
+                host_in[(k, m)] = torch.randn(m, k, generator=torch.Generator().manual_seed(3000 + m)).bfloat16().pin_memory()
+    for si, (_, n, _) in enumerate(SHAPES):
+        for m in TOKENS:
+            host_out[(si, m)] = torch.empty(m, n, dtype=torch.bfloat16).pin_memory()
+    h2d = sum(host_in[(k, m)].numel() * 2 for _, _, k in SHAPES for m in TOKENS)
+    d2h = sum(t.numel() * 2 for t in host_out.values())
+    stream = torch.cuda.current_stream(device)
+
+    def step() -> None:
+        with torch.no_grad():
+            for si, (_, n, k) in enumerate(SHAPES):
+                for m in TOKENS:
+                    x = host_in[(k, m)].to(device, non_blocking=True)
+                    y = layers[si](x)
+                    host_out[(si, m)].copy_(y, non_blocking=True)
+
+    step()
+    torch.cuda.synchronize(device)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(steps):
+        step()
+    e1.record(stream)
+    torch.cuda.synchronize(device)
+    return {"ms": e0.elapsed_time(e1) / steps, "h2d": h2d, "d2h": d2h}
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=5)
+    parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--impl", choices=("native", "reference"), default="native")
+    parser.add_argument("--skip-extras", action="store_true",
+                        help="timed sweep only: no per-cell table, no end-to-end pass, no CPU baseline (profiling runs)")
+    args = parser.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -42,6 +42,9 @@ enum {
 
 int nq_abi_version(void);
 const char* nq_last_error(void);
+/* Number of kernels this library has launched in the process so far (host-side
+ * counter; benchmarks report the difference over their timed region). */
+unsigned long long nq_launch_count(void);
 
 /* -------------------------------------------------------------------------
  * On-the-fly E8 encoder (activations, and K/V rows with k = head_dim).
@@ -110,6 +113,15 @@ int nq_w4a4_gemm(const uint8_t* act_codes, const uint8_t* act_beta_ids, const fl
                  const float* w_betas, int64_t m, int64_t n, int64_t k,
                  int64_t w_block_offset, int64_t seed, void* out, int out_dtype,
                  void* workspace, size_t workspace_bytes, nq_stream_t stream);
+
+/* The tcgen05 GEMM of the large-M path alone: out[m,n] = A[m,k] * W[n,k]^T on
+ * BF16 row-major operands that were already decoded (nq_a4_encode's
+ * out_decoded / nq_w4_decode).  Building block exposed for measurement and
+ * tests; the reference has no counterpart (its large-M kernel decodes in the
+ * MMA loop, runtime/nqrt4_w4a4_mma.cu:606-723).  workspace as for nq_w4a4_gemm
+ * (only the status word is used).  Requires n % 128 == 0, k % 64 == 0. */
+int nq_bf16_gemm_tc(const void* a_bf16, const void* w_bf16, int64_t m, int64_t n, int64_t k,
+                    void* out, int out_dtype, void* workspace, size_t workspace_bytes, nq_stream_t stream);
 
 /* Copy the device status word of a workspace to the host and synchronise the
  * stream (the only entry point that synchronises).  Non-zero means a bounded

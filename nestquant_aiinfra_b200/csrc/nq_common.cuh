@@ -13,6 +13,7 @@
 
 // ---- host-side error plumbing --------------------------------------------
 void nq_set_error(const char* fmt, ...);
+void nq_count_launch();  // bumps the process-wide kernel-launch counter (nq_launch_count)
 
 #define NQ_REQUIRE(cond, code, ...)          \
     do {                                     \
@@ -29,6 +30,7 @@ void nq_set_error(const char* fmt, ...);
             nq_set_error("%s: %s", (name), cudaGetErrorString(nq_e_));         \
             return (int)nq_e_;                                                 \
         }                                                                      \
+        nq_count_launch();                                                     \
     } while (0)
 
 static inline bool nq_aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }

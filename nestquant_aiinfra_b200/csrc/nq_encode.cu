@@ -17,6 +17,11 @@ void nq_set_error(const char* fmt, ...) {
     va_end(args);
 }
 
+#include <atomic>
+static std::atomic<unsigned long long> g_nq_launches{0};
+void nq_count_launch() { g_nq_launches.fetch_add(1, std::memory_order_relaxed); }
+extern "C" unsigned long long nq_launch_count(void) { return g_nq_launches.load(std::memory_order_relaxed); }
+
 extern "C" const char* nq_last_error(void) { return g_nq_error; }
 extern "C" int nq_abi_version(void) { return 1; }
 

@@ -113,3 +113,19 @@ extern "C" int nq_w4a4_status(const void* workspace, uint32_t* status_host, nq_s
     }
     return NQ_OK;
 }
+
+// Building block of the large-M path, exposed for measurement and tests: the
+// tcgen05 GEMM alone on already decoded BF16 operands.
+extern "C" int nq_bf16_gemm_tc(const void* a_bf16, const void* w_bf16, int64_t m, int64_t n, int64_t k,
+                               void* out, int out_dtype, void* workspace, size_t workspace_bytes,
+                               nq_stream_t stream) {
+    NQ_REQUIRE(a_bf16 && w_bf16 && out && workspace, NQ_ERR_ARG, "nq_bf16_gemm_tc: null pointer");
+    NQ_REQUIRE(nq_tc_supported(m, n, k), NQ_ERR_ARG, "nq_bf16_gemm_tc: needs n %% 128 == 0 and k %% 64 == 0");
+    NQ_REQUIRE(out_dtype == NQ_F32 || out_dtype == NQ_BF16, NQ_ERR_ARG, "nq_bf16_gemm_tc: out_dtype");
+    NQ_REQUIRE(workspace_bytes >= NQ_WS_COUNTER_BYTES, NQ_ERR_WORKSPACE, "nq_bf16_gemm_tc: workspace too small");
+    NQ_REQUIRE(nq_aligned16(a_bf16) && nq_aligned16(w_bf16) && nq_aligned16(out), NQ_ERR_ALIGN,
+               "nq_bf16_gemm_tc: 16-byte alignment required");
+    return nq_launch_tc_gemm(a_bf16, w_bf16, m, n, k, out, out_dtype,
+                             reinterpret_cast<char*>(workspace) + NQ_WS_STATUS_OFFSET,
+                             reinterpret_cast<cudaStream_t>(stream));
+}

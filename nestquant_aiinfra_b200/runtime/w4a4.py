@@ -410,3 +410,26 @@ def decode_packed_weight(weight: PreparedNQRTLinear) -> torch.Tensor:
         _I64(n), _I64(k), _I64(0), _I64(int(record.dither_seed)), _ptr(out), _stream(device))
     _lib.check(status, "decode_packed_weight")
     return out
+
+
+def gemm_bf16_tc(a_dec: torch.Tensor, w_dec: torch.Tensor, *, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """tcgen05 GEMM on decoded BF16 operands ``A[m,k]``, ``W[n,k]`` (measurement / test building block)."""
+    if a_dec.dtype != torch.bfloat16 or w_dec.dtype != torch.bfloat16:
+        raise TypeError("operands must be bfloat16")
+    if a_dec.ndim != 2 or w_dec.ndim != 2 or a_dec.shape[1] != w_dec.shape[1]:
+        raise ValueError("operands must be [m,k] and [n,k]")
+    a_dec, w_dec = a_dec.contiguous(), w_dec.contiguous()
+    (m, k), n = a_dec.shape, w_dec.shape[0]
+    device = a_dec.device
+    workspace = workspace_for(device, _lib.WS_COUNTER_BYTES)
+    out = torch.empty((m, n), dtype=out_dtype, device=device)
+    status = _lib.lib().nq_bf16_gemm_tc(_ptr(a_dec), _ptr(w_dec), _I64(m), _I64(n), _I64(k), _ptr(out),
+                                        _DTYPE_TAG[out_dtype], _ptr(workspace), ctypes.c_size_t(workspace.numel()),
+                                        _stream(device))
+    _lib.check(status, "gemm_bf16_tc")
+    return out
+
+
+def launch_count() -> int:
+    """Kernels launched by the library in this process so far."""
+    return int(_lib.lib().nq_launch_count())
