@@ -276,13 +276,13 @@ def run_gpu(args) -> None:
     # per-cell table and the tensor-bound kernel alone (outside the timed region)
     table, gemm = ([], None) if args.skip_extras else cell_table(torch, rt, weights, inputs, beta_table, device, pk)
 
-    e2e = ({"ms": float("nan"), "h2d": 0, "d2h": 0} if args.skip_extras else
+    e2e = ({"ms": None, "h2d": 0, "d2h": 0} if args.skip_extras else
            run_e2e(torch, rt, FusedNQRTLinear, weights, device, min(args.steps, 3), distributed))
-    if distributed:
+    if distributed and e2e["ms"] is not None:
         t = torch.tensor([e2e["ms"]], device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e["ms"] = float(t.item())
-    e2e_value = world * sweep_flops() / (e2e["ms"] * 1e-3) / 1e12
+    e2e_value = None if e2e["ms"] is None else world * sweep_flops() / (e2e["ms"] * 1e-3) / 1e12
 
     if rank == 0:
         base = cpu_baseline(repeats=2) if world == 1 and not args.skip_extras else None

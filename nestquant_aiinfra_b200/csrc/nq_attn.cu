@@ -1,0 +1,353 @@
+// Paged GQA attention that reads NQKV4 pages directly (decode and chunked
+// causal prefill).  One CTA owns one (query token, KV head, page-range split):
+// every K/V vector is decoded ONCE for all query heads of its GQA group, with
+// the exact codec arithmetic (undithered streams have real Voronoi ties), FP32
+// online softmax, and a BF16 hot tail as the last "page".  No page-count cap.
+//
+// Lane mapping: a warp covers 32 / (D/8) tokens per step; lane = (token, E8
+// block of the head vector).  Score = shuffle-reduced dot over the D/8 lanes of
+// a token.  Split partials (m, l, acc[D]) are merged by a second small kernel
+// (skipped when there is a single split).
+//
+// Replaces runtime/nqkv_attention_k1.py:243-471 (page / hot / reduce Triton
+// kernels, 127-page cap at :807-809) and adds the page-reading prefill the
+// reference only has as materialise + SDPA (runtime/nqkv_hf_backend.py:127-150).
+#include <math.h>
+
+#include "nq_common.cuh"
+
+namespace {
+
+constexpr int kAttnWarps = 4;
+constexpr int kAttnThreads = kAttnWarps * 32;
+
+struct AttnParams {
+    const void* query;  // [B, Tq, Hq, D]
+    int q_dtype;
+    int batch, q_tokens, q_heads, kv_heads, dim, page_size;
+    const int32_t* slot_ids;      // [B]
+    const uint8_t* active_mask;   // [B] or null (all active)
+    const int32_t* q_lens;        // [B] or null (decode: one token, full context)
+    const uint8_t* cache_active;  // [S]
+    const int32_t* sequence_lengths;
+    const int32_t* page_indices;  // [S, max_pages]
+    const int32_t* page_counts;
+    const int32_t* last_page_lens;
+    const int32_t* hot_lengths;
+    const uint8_t *key_codes, *key_betas, *value_codes, *value_betas;
+    const float *key_norms, *value_norms, *key_beta_table, *value_beta_table;
+    const void *hot_keys, *hot_values;  // [S, P, H, D] bf16
+    int max_sequences, max_pages, pool_capacity;
+    float scale_log2e;  // attention scale * log2(e)
+    float sqrt_dim;
+    int splits;
+    float* partial;  // [B*Tq, Hq, splits, D + 2]
+    void* out;       // [B, Tq, Hq, D]
+    int out_dtype;
+};
+
+__device__ __forceinline__ void store_out(void* out, int out_dtype, int64_t index, const float v[8]) {
+    if (out_dtype == NQ_BF16) {
+        reinterpret_cast<uint4*>(out)[index] = nq_pack_bf16x8(v);
+    } else {
+        float4* o = reinterpret_cast<float4*>(out) + 2 * index;
+        o[0] = make_float4(v[0], v[1], v[2], v[3]);
+        o[1] = make_float4(v[4], v[5], v[6], v[7]);
+    }
+}
+
+// Resolve the query row: returns false when the row is inactive (output zero).
+__device__ __forceinline__ bool resolve_query(const AttnParams& p, int qi, int& slot, int& limit, int& total_slots,
+                                              int& page_count, int& last_len, int& hot_len) {
+    const int b = qi / p.q_tokens, i = qi - b * p.q_tokens;
+    const int requested = p.slot_ids[b];
+    const bool in_range = requested >= 0 && requested < p.max_sequences;
+    slot = min(max(requested, 0), p.max_sequences - 1);
+    bool active = in_range && p.cache_active[slot] != 0 && p.sequence_lengths[slot] > 0;
+    if (p.active_mask) active = active && p.active_mask[b] != 0;
+    page_count = min(max(p.page_counts[slot], 0), p.max_pages);
+    last_len = p.last_page_lens[slot];
+    hot_len = min(max(p.hot_lengths[slot], 0), p.page_size);
+    const int cold = page_count > 0 ? (page_count - 1) * p.page_size + last_len : 0;
+    const int total = cold + hot_len;
+    limit = total;
+    if (p.q_lens) {
+        const int ql = p.q_lens[b];
+        active = active && i < ql;
+        limit = total - ql + i + 1;  // causal: query i of the chunk sees the first `limit` tokens
+    }
+    total_slots = page_count + (hot_len > 0 ? 1 : 0);
+    return active && limit > 0;
+}
+
+template <int G, int BPR>
+__global__ void __launch_bounds__(kAttnThreads) nq_attn_paged_kernel(const AttnParams p) {
+    constexpr int TPW = 32 / BPR;  // tokens per warp step
+    constexpr int D = BPR * 8;
+    __shared__ float s_merge[kAttnWarps][G][D + 2];
+
+    const int qi = blockIdx.x / p.kv_heads, h = blockIdx.x - qi * p.kv_heads;
+    const int split = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int blk = lane % BPR, tsub = lane / BPR;
+
+    int slot, limit, total_slots, page_count, last_len, hot_len;
+    const bool active = resolve_query(p, qi, slot, limit, total_slots, page_count, last_len, hot_len);
+    const int cold = page_count > 0 ? (page_count - 1) * p.page_size + last_len : 0;
+
+    float m[G], l[G], acc[G][8], q[G][8];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        m[g] = -INFINITY;
+        l[g] = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[g][j] = 0.0f;
+        const int64_t qoff = ((int64_t)qi * p.q_heads + h * G + g) * D + blk * 8;
+        if (p.q_dtype == NQ_BF16) nq_load8<__nv_bfloat16>(reinterpret_cast<const __nv_bfloat16*>(p.query) + qoff, q[g]);
+        else if (p.q_dtype == NQ_F16) nq_load8<__half>(reinterpret_cast<const __half*>(p.query) + qoff, q[g]);
+        else nq_load8<float>(reinterpret_cast<const float*>(p.query) + qoff, q[g]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) q[g][j] *= p.scale_log2e;
+    }
+
+    if (active) {
+        const int per = (total_slots + p.splits - 1) / p.splits;
+        const int s_begin = split * per, s_end = min(total_slots, s_begin + per);
+        const int rows = p.page_size * p.kv_heads;
+        const int64_t code_bytes = (int64_t)rows * D / 2, beta_bytes = (int64_t)rows * D / 32;
+        for (int ps = s_begin + warp; ps < s_end; ps += kAttnWarps) {
+            const bool is_hot = ps >= page_count;
+            const int base_token = is_hot ? cold : ps * p.page_size;
+            if (base_token >= limit) break;  // warp-uniform: later slots are later tokens
+            const int tlimit = is_hot ? hot_len : (ps == page_count - 1 ? last_len : p.page_size);
+            int page_id = 0;
+            if (!is_hot) {
+                page_id = p.page_indices[(int64_t)slot * p.max_pages + ps];
+                if (page_id < 0 || page_id >= p.pool_capacity) continue;  // defensive: never read outside the pool
+            }
+            for (int t0 = 0; t0 < tlimit; t0 += TPW) {
+                const int t = t0 + tsub;
+                const bool valid = t < tlimit && base_token + t < limit;
+                float kvec[8], vvec[8];
+                if (is_hot) {
+                    const int64_t off = (((int64_t)slot * p.page_size + min(t, p.page_size - 1)) * p.kv_heads + h) * D + blk * 8;
+                    nq_load8<__nv_bfloat16>(reinterpret_cast<const __nv_bfloat16*>(p.hot_keys) + off, kvec);
+                    nq_load8<__nv_bfloat16>(reinterpret_cast<const __nv_bfloat16*>(p.hot_values) + off, vvec);
+                } else {
+                    const int row = min(t, p.page_size - 1) * p.kv_heads + h;
+                    const int64_t g = (int64_t)row * BPR + blk;
+                    const uint32_t kw = __ldg(reinterpret_cast<const uint32_t*>(p.key_codes + page_id * code_bytes) + g);
+                    const uint32_t vw = __ldg(reinterpret_cast<const uint32_t*>(p.value_codes + page_id * code_bytes) + g);
+                    const float kb = __ldg(p.key_beta_table + nq_beta_id(p.key_betas + page_id * beta_bytes, g));
+                    const float vb = __ldg(p.value_beta_table + nq_beta_id(p.value_betas + page_id * beta_bytes, g));
+                    const float kds = nq_div(__ldg(p.key_norms + (int64_t)page_id * rows + row), p.sqrt_dim);
+                    const float vds = nq_div(__ldg(p.value_norms + (int64_t)page_id * rows + row), p.sqrt_dim);
+                    nq_decode_codeword_exact(kw, nullptr, kvec);
+                    nq_decode_codeword_exact(vw, nullptr, vvec);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        kvec[j] = nq_mul(nq_mul(kvec[j], kb), kds);
+                        vvec[j] = nq_mul(nq_mul(vvec[j], vb), vds);
+                    }
+                }
+#pragma unroll
+                for (int g = 0; g < G; ++g) {
+                    float s = 0.0f;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) s = fmaf(q[g][j], kvec[j], s);
+#pragma unroll
+                    for (int off = 1; off < BPR; off <<= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+                    if (valid) {
+                        const float mn = fmaxf(m[g], s);
+                        const float corr = exp2f(m[g] - mn);  // exp2(-inf) = 0 on the first token
+                        const float pr = exp2f(s - mn);
+                        l[g] = l[g] * corr + pr;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) acc[g][j] = acc[g][j] * corr + pr * vvec[j];
+                        m[g] = mn;
+                    }
+                }
+            }
+        }
+    }
+
+    // merge the token sub-groups of the warp (same block index, different tokens)
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+#pragma unroll
+        for (int off = BPR; off < 32; off <<= 1) {
+            const float mo = __shfl_xor_sync(0xffffffffu, m[g], off);
+            const float lo = __shfl_xor_sync(0xffffffffu, l[g], off);
+            const float mn = fmaxf(m[g], mo);
+            const float c0 = mn == -INFINITY ? 0.0f : exp2f(m[g] - mn);
+            const float c1 = mn == -INFINITY ? 0.0f : exp2f(mo - mn);
+            l[g] = l[g] * c0 + lo * c1;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float ao = __shfl_xor_sync(0xffffffffu, acc[g][j], off);
+                acc[g][j] = acc[g][j] * c0 + ao * c1;
+            }
+            m[g] = mn;
+        }
+        if (tsub == 0) {
+            if (blk == 0) {
+                s_merge[warp][g][D] = m[g];
+                s_merge[warp][g][D + 1] = l[g];
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) s_merge[warp][g][blk * 8 + j] = acc[g][j];
+        }
+    }
+    __syncthreads();
+
+    // merge the warps; thread (g, blk) handles 8 output features
+    for (int item = threadIdx.x; item < G * BPR; item += kAttnThreads) {
+        const int g = item / BPR, b8 = item - g * BPR;
+        float mm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kAttnWarps; ++w) mm = fmaxf(mm, s_merge[w][g][D]);
+        float ll = 0.0f, a[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+        for (int w = 0; w < kAttnWarps; ++w) {
+            const float c = mm == -INFINITY ? 0.0f : exp2f(s_merge[w][g][D] - mm);
+            ll += s_merge[w][g][D + 1] * c;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) a[j] += s_merge[w][g][b8 * 8 + j] * c;
+        }
+        const int head = h * G + g;
+        if (p.splits == 1) {
+            const float inv = (active && ll > 0.0f) ? 1.0f / ll : 0.0f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) a[j] *= inv;
+            store_out(p.out, p.out_dtype, ((int64_t)qi * p.q_heads + head) * BPR + b8, a);
+        } else {
+            float* dst = p.partial + (((int64_t)qi * p.q_heads + head) * p.splits + split) * (D + 2);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) dst[b8 * 8 + j] = a[j];
+            if (b8 == 0) {
+                dst[D] = mm;
+                dst[D + 1] = ll;
+            }
+        }
+    }
+}
+
+// Merge the split partials of one (query, head): log-sum-exp weights, inactive rows -> 0.
+__global__ void __launch_bounds__(128) nq_attn_reduce_kernel(const AttnParams p) {
+    const int row = blockIdx.x;  // qi * q_heads + head
+    const int D = p.dim, bpr = D >> 3;
+    const float* src = p.partial + (int64_t)row * p.splits * (D + 2);
+    float mm = -INFINITY;
+    for (int s = 0; s < p.splits; ++s) mm = fmaxf(mm, src[(int64_t)s * (D + 2) + D]);
+    for (int b8 = threadIdx.x; b8 < bpr; b8 += blockDim.x) {
+        float ll = 0.0f, a[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (int s = 0; s < p.splits; ++s) {
+            const float* ps = src + (int64_t)s * (D + 2);
+            const float c = mm == -INFINITY ? 0.0f : exp2f(ps[D] - mm);
+            ll += ps[D + 1] * c;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) a[j] += ps[b8 * 8 + j] * c;
+        }
+        const float inv = ll > 0.0f ? 1.0f / ll : 0.0f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) a[j] *= inv;
+        store_out(p.out, p.out_dtype, (int64_t)row * bpr + b8, a);
+    }
+}
+
+template <int G>
+int launch_attn(const AttnParams& p, dim3 grid, cudaStream_t s) {
+    if (p.dim == 64) nq_attn_paged_kernel<G, 8><<<grid, kAttnThreads, 0, s>>>(p);
+    else if (p.dim == 128) nq_attn_paged_kernel<G, 16><<<grid, kAttnThreads, 0, s>>>(p);
+    else if (p.dim == 32) nq_attn_paged_kernel<G, 4><<<grid, kAttnThreads, 0, s>>>(p);
+    else if (p.dim == 256) nq_attn_paged_kernel<G, 32><<<grid, kAttnThreads, 0, s>>>(p);
+    else {
+        nq_set_error("nq_kv_attention: head_dim must be 32, 64, 128 or 256");
+        return NQ_ERR_ARG;
+    }
+    return NQ_OK;
+}
+
+int choose_splits(int queries, int kv_heads, int max_pages) {
+    const int ctas = queries * kv_heads;
+    int splits = (4 * 148 + ctas - 1) / ctas;       // aim at >= 4 CTAs per SM
+    const int cap = (max_pages + 1 + 7) / 8;        // at least ~8 page slots per split
+    if (splits > cap) splits = cap;
+    if (splits > 64) splits = 64;
+    return splits < 1 ? 1 : splits;
+}
+
+}  // namespace
+
+extern "C" size_t nq_kv_attention_workspace_bytes(int batch, int q_tokens, int q_heads, int kv_heads, int dim,
+                                                  int max_pages) {
+    if (batch < 1 || q_tokens < 1 || q_heads < 1 || kv_heads < 1) return 0;
+    const int splits = choose_splits(batch * q_tokens, kv_heads, max_pages);
+    return (size_t)batch * q_tokens * q_heads * splits * (dim + 2) * sizeof(float) + 256;
+}
+
+extern "C" int nq_kv_attention(const void* query, int q_dtype, int batch, int q_tokens, int q_heads,
+                               const int32_t* slot_ids, const uint8_t* active_mask, const int32_t* q_lens,
+                               const uint8_t* cache_active, const int32_t* sequence_lengths,
+                               const int32_t* page_indices, const int32_t* page_counts,
+                               const int32_t* last_page_lens, const int32_t* hot_lengths,
+                               const uint8_t* key_codes, const uint8_t* key_betas, const float* key_norms,
+                               const uint8_t* value_codes, const uint8_t* value_betas, const float* value_norms,
+                               const float* key_beta_table, const float* value_beta_table,
+                               const void* hot_keys, const void* hot_values, int max_sequences, int max_pages,
+                               int pool_capacity, int page_size, int kv_heads, int dim, float scale,
+                               void* workspace, size_t workspace_bytes, void* out, int out_dtype,
+                               nq_stream_t stream) {
+    NQ_REQUIRE(query && slot_ids && cache_active && sequence_lengths && page_indices && page_counts &&
+                   last_page_lens && hot_lengths && key_codes && key_betas && key_norms && value_codes &&
+                   value_betas && value_norms && key_beta_table && value_beta_table && hot_keys && hot_values && out,
+               NQ_ERR_ARG, "nq_kv_attention: null pointer");
+    NQ_REQUIRE(batch >= 1 && q_tokens >= 1 && q_heads >= 1 && kv_heads >= 1 && q_heads % kv_heads == 0, NQ_ERR_ARG,
+               "nq_kv_attention: query_heads must be a positive multiple of num_kv_heads");
+    NQ_REQUIRE(max_sequences >= 1 && max_pages >= 1 && pool_capacity >= 1 && page_size >= 1, NQ_ERR_ARG,
+               "nq_kv_attention: bad cache geometry");
+    NQ_REQUIRE(out_dtype == NQ_BF16 || out_dtype == NQ_F32, NQ_ERR_ARG, "nq_kv_attention: out_dtype must be bf16 or f32");
+    NQ_REQUIRE(nq_aligned16(query) && nq_aligned16(out) && nq_aligned16(hot_keys) && nq_aligned16(hot_values) &&
+                   nq_aligned16(key_codes) && nq_aligned16(value_codes),
+               NQ_ERR_ALIGN, "nq_kv_attention: 16-byte alignment required");
+    const int group = q_heads / kv_heads;
+    NQ_REQUIRE(group == 1 || group == 2 || group == 4 || group == 8, NQ_ERR_ARG,
+               "nq_kv_attention: GQA group size must be 1, 2, 4 or 8");
+    AttnParams p;
+    p.query = query; p.q_dtype = q_dtype; p.batch = batch; p.q_tokens = q_tokens; p.q_heads = q_heads;
+    p.kv_heads = kv_heads; p.dim = dim; p.page_size = page_size;
+    p.slot_ids = slot_ids; p.active_mask = active_mask; p.q_lens = q_lens; p.cache_active = cache_active;
+    p.sequence_lengths = sequence_lengths; p.page_indices = page_indices; p.page_counts = page_counts;
+    p.last_page_lens = last_page_lens; p.hot_lengths = hot_lengths;
+    p.key_codes = key_codes; p.key_betas = key_betas; p.value_codes = value_codes; p.value_betas = value_betas;
+    p.key_norms = key_norms; p.value_norms = value_norms;
+    p.key_beta_table = key_beta_table; p.value_beta_table = value_beta_table;
+    p.hot_keys = hot_keys; p.hot_values = hot_values;
+    p.max_sequences = max_sequences; p.max_pages = max_pages; p.pool_capacity = pool_capacity;
+    p.scale_log2e = scale * 1.4426950408889634f;
+    p.sqrt_dim = (float)sqrt((double)dim);
+    p.splits = choose_splits(batch * q_tokens, kv_heads, max_pages);
+    p.out = out; p.out_dtype = out_dtype;
+    p.partial = reinterpret_cast<float*>(workspace);
+    if (p.splits > 1) {
+        const size_t need = (size_t)batch * q_tokens * q_heads * p.splits * (dim + 2) * sizeof(float);
+        NQ_REQUIRE(workspace && workspace_bytes >= need && nq_aligned16(workspace), NQ_ERR_WORKSPACE,
+                   "nq_kv_attention: workspace of %zu bytes needed, %zu given", need, workspace_bytes);
+    }
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    dim3 grid((unsigned)(batch * q_tokens * kv_heads), (unsigned)p.splits);
+    int rc;
+    switch (group) {
+        case 1: rc = launch_attn<1>(p, grid, s); break;
+        case 2: rc = launch_attn<2>(p, grid, s); break;
+        case 4: rc = launch_attn<4>(p, grid, s); break;
+        default: rc = launch_attn<8>(p, grid, s); break;
+    }
+    if (rc) return rc;
+    NQ_CHECK_LAUNCH("nq_kv_attention");
+    if (p.splits > 1) {
+        nq_attn_reduce_kernel<<<(unsigned)(batch * q_tokens * q_heads), 128, 0, s>>>(p);
+        NQ_CHECK_LAUNCH("nq_kv_attention(reduce)");
+    }
+    return NQ_OK;
+}

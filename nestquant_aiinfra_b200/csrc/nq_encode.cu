@@ -6,6 +6,7 @@
 #include <math.h>
 
 #include "nq_common.cuh"
+#include "nq_encode_core.cuh"
 
 // ---- error message storage (one per host thread) ---------------------------
 static thread_local char g_nq_error[512] = "";
@@ -26,14 +27,7 @@ extern "C" const char* nq_last_error(void) { return g_nq_error; }
 extern "C" int nq_abi_version(void) { return 1; }
 
 // ---------------------------------------------------------------------------
-// Encoder.  One CTA of 256 threads owns `rows_per_cta` consecutive rows
-// (256 / (k/8) rows for short rows, one row otherwise).
-//   phase 1  every thread squares its blocks into shared memory
-//   phase 2  8 threads per row run the reference's 8-lane strided accumulation
-//            (the order PyTorch's CPU vector_norm uses; it decides the last
-//            bit of the norm and therefore the emitted codes)
-//   phase 3  every thread runs the 4-beta search on its blocks and stores the
-//            codeword; beta ids of 4 neighbouring blocks are merged by shuffle.
+// Encoder kernel: one CTA per group of rows (see nq_encode_core.cuh).
 // ---------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -41,89 +35,16 @@ nq_encode_rows_kernel(const T* __restrict__ x, int64_t rows, int k, int64_t row_
                       const float* __restrict__ beta_table, float sqrt_k,
                       uint32_t* __restrict__ codes, uint8_t* __restrict__ beta_ids,
                       float* __restrict__ norms, __nv_bfloat16* __restrict__ decoded,
-                      int rows_per_cta, int use_dither, uint32_t counter_base) {
+                      int use_dither, uint32_t counter_base) {
     extern __shared__ float smem[];
+    const int rpc = nq_encode_rows_per_cta(k);
     const int bpr = k >> 3;
-    const int pitch = k + 8;  // de-conflicts the strided chain reads of neighbouring rows
-    float* sq = smem;
-    float* partial = smem + (size_t)rows_per_cta * pitch;
-    float* scale = partial + rows_per_cta * 8;
-    float* dscale = scale + rows_per_cta;
-
-    const int tid = threadIdx.x;
-    const int64_t row0 = (int64_t)blockIdx.x * rows_per_cta;
-    const int nrows = (int)min((int64_t)rows_per_cta, rows - row0);
-    const int nblocks = nrows * bpr;
-
-    for (int b = tid; b < nblocks; b += 256) {
-        const int r = b / bpr, bb = b - r * bpr;
-        float v[8];
-        nq_load8<T>(x + (row0 + r) * row_stride + (int64_t)bb * 8, v);
-        float4 lo = make_float4(nq_mul(v[0], v[0]), nq_mul(v[1], v[1]), nq_mul(v[2], v[2]), nq_mul(v[3], v[3]));
-        float4 hi = make_float4(nq_mul(v[4], v[4]), nq_mul(v[5], v[5]), nq_mul(v[6], v[6]), nq_mul(v[7], v[7]));
-        float4* dst = reinterpret_cast<float4*>(sq + (size_t)r * pitch + bb * 8);
-        dst[0] = lo;
-        dst[1] = hi;
-    }
-    __syncthreads();
-
-    for (int t = tid; t < nrows * 8; t += 256) {
-        const int r = t >> 3, l = t & 7;
-        const float* p = sq + (size_t)r * pitch + l;
-        float acc = 0.0f;
-#pragma unroll 8
-        for (int i = 0; i < bpr; ++i) acc = nq_add(acc, p[8 * i]);
-        partial[t] = acc;
-    }
-    __syncthreads();
-
-    if (tid < nrows) {
-        float total = partial[tid * 8];
-#pragma unroll
-        for (int l = 1; l < 8; ++l) total = nq_add(total, partial[tid * 8 + l]);
-        const float norm = nq_sqrt(total);
-        norms[row0 + tid] = norm;
-        // sqrt(K)/norm is evaluated as reciprocal(norm) * sqrt(K) by the reference.
-        scale[tid] = norm > 0.0f ? nq_mul(nq_rcp(norm), sqrt_k) : 0.0f;
-        dscale[tid] = nq_div(norm, sqrt_k);
-    }
-    __syncthreads();
-
-    const int padded = (nblocks + 31) & ~31;
-    for (int b = tid; b < padded; b += 256) {
-        const bool valid = b < nblocks;
-        int bid = 0;
-        if (valid) {
-            const int r = b / bpr, bb = b - r * bpr;
-            float v[8], recon[8];
-            nq_load8<T>(x + (row0 + r) * row_stride + (int64_t)bb * 8, v);
-            const float s = scale[r];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = nq_mul(v[j], s);
-            const int64_t g = row0 * bpr + b;
-            uint32_t word;
-            if (use_dither) {  // weights: subtractive dither of global block g (warp-uniform branch)
-                float d[8];
-                nq_dither_block(counter_base + (uint32_t)g * 8u, d);
-                word = nq_encode_block(v, beta_table, d, bid, recon);
-            } else {
-                word = nq_encode_block(v, beta_table, nullptr, bid, recon);
-            }
-            codes[g] = word;
-            if (decoded != nullptr) {
-                const float ds = dscale[r];
-#pragma unroll
-                for (int j = 0; j < 8; ++j) recon[j] = nq_mul(recon[j], ds);
-                *reinterpret_cast<uint4*>(decoded + g * 8) = nq_pack_bf16x8(recon);
-            }
-        }
-        // four neighbouring blocks share one beta byte (block i -> bits 2i..2i+1)
-        unsigned merged = (unsigned)bid;
-        merged |= __shfl_down_sync(0xffffffffu, (unsigned)bid, 1) << 2;
-        merged |= __shfl_down_sync(0xffffffffu, (unsigned)bid, 2) << 4;
-        merged |= __shfl_down_sync(0xffffffffu, (unsigned)bid, 3) << 6;
-        if (valid && (tid & 3) == 0) beta_ids[(row0 * bpr + b) >> 2] = (uint8_t)merged;
-    }
+    const int64_t row0 = (int64_t)blockIdx.x * rpc;
+    const int nrows = (int)min((int64_t)rpc, rows - row0);
+    const int64_t g0 = row0 * bpr;
+    nq_encode_rows_cta<T>(x + row0 * row_stride, row_stride, nrows, nrows, k, beta_table, sqrt_k, codes + g0,
+                          beta_ids + (g0 >> 2), norms + row0, decoded ? decoded + g0 * 8 : nullptr, use_dither,
+                          counter_base + (uint32_t)g0 * 8u, smem);
 }
 
 // ---------------------------------------------------------------------------
@@ -174,18 +95,14 @@ nq_w4_decode_kernel(const uint32_t* __restrict__ codes, const uint8_t* __restric
 
 // ---- C ABI ------------------------------------------------------------------
 
-static int encode_rows_per_cta(int64_t k) {
-    const int bpr = (int)(k / 8);
-    return bpr >= 256 ? 1 : 256 / bpr;
-}
 
 template <typename T>
 static int launch_encode(const void* x, int64_t rows, int64_t k, int64_t row_stride,
                          const float* beta_table, uint8_t* out_codes, uint8_t* out_beta_ids,
                          float* out_norms, void* out_decoded, cudaStream_t stream,
                          int use_dither = 0, uint32_t counter_base = 0) {
-    const int rpc = encode_rows_per_cta(k);
-    const size_t smem = ((size_t)rpc * (k + 8) + (size_t)rpc * 10) * sizeof(float);
+    const int rpc = nq_encode_rows_per_cta((int)k);
+    const size_t smem = nq_encode_smem_floats((int)k) * sizeof(float);
     auto kernel = nq_encode_rows_kernel<T>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -198,7 +115,7 @@ static int launch_encode(const void* x, int64_t rows, int64_t k, int64_t row_str
     kernel<<<(unsigned)grid, 256, smem, stream>>>(
         reinterpret_cast<const T*>(x), rows, (int)k, row_stride, beta_table,
         (float)sqrt((double)k), reinterpret_cast<uint32_t*>(out_codes), out_beta_ids, out_norms,
-        reinterpret_cast<__nv_bfloat16*>(out_decoded), rpc, use_dither, counter_base);
+        reinterpret_cast<__nv_bfloat16*>(out_decoded), use_dither, counter_base);
     NQ_CHECK_LAUNCH("nq_a4_encode");
     return NQ_OK;
 }

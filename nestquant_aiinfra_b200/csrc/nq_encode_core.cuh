@@ -1,0 +1,119 @@
+// Row encoder shared by the activation / weight encoder and the KV page
+// writers.  One CTA of 256 threads owns `nrows` consecutive rows of k features
+// (256 / (k/8) rows for short rows, one row otherwise).
+//   phase 1  every thread squares its blocks into shared memory
+//   phase 2  8 threads per row run the reference's 8-lane strided accumulation
+//            (the order PyTorch's CPU vector_norm uses; it decides the last
+//            bit of the norm and therefore the emitted codes)
+//   phase 3  every thread runs the 4-beta search on its blocks and stores the
+//            codeword; beta ids of 4 neighbouring blocks are merged by shuffle.
+// All pointers address the CTA's first row.  Rows >= valid_rows read as zero
+// (partially filled KV pages).  Shared memory: nq_encode_smem_floats() floats.
+#pragma once
+
+#include "nq_common.cuh"
+
+__host__ __device__ inline int nq_encode_rows_per_cta(int k) {
+    const int bpr = k / 8;
+    return bpr >= 256 ? 1 : 256 / bpr;
+}
+__host__ __device__ inline size_t nq_encode_smem_floats(int k) {
+    const int rpc = nq_encode_rows_per_cta(k);
+    return (size_t)rpc * (k + 8) + (size_t)rpc * 10;
+}
+
+template <typename T>
+__device__ __forceinline__ void nq_encode_rows_cta(
+    const T* __restrict__ x, int64_t row_stride, int nrows, int valid_rows, int k,
+    const float* __restrict__ beta_table, float sqrt_k, uint32_t* __restrict__ codes,
+    uint8_t* __restrict__ beta_ids, float* __restrict__ norms, __nv_bfloat16* __restrict__ decoded,
+    int use_dither, uint32_t counter_base, float* smem) {
+    const int rows_per_cta = nq_encode_rows_per_cta(k);
+    const int bpr = k >> 3;
+    const int pitch = k + 8;  // de-conflicts the strided chain reads of neighbouring rows
+    float* sq = smem;
+    float* partial = smem + (size_t)rows_per_cta * pitch;
+    float* scale = partial + rows_per_cta * 8;
+    float* dscale = scale + rows_per_cta;
+    const int tid = threadIdx.x;
+    const int nblocks = nrows * bpr;
+
+    for (int b = tid; b < nblocks; b += 256) {
+        const int r = b / bpr, bb = b - r * bpr;
+        float v[8];
+        if (r < valid_rows) {
+            nq_load8<T>(x + (int64_t)r * row_stride + (int64_t)bb * 8, v);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = 0.0f;
+        }
+        float4 lo = make_float4(nq_mul(v[0], v[0]), nq_mul(v[1], v[1]), nq_mul(v[2], v[2]), nq_mul(v[3], v[3]));
+        float4 hi = make_float4(nq_mul(v[4], v[4]), nq_mul(v[5], v[5]), nq_mul(v[6], v[6]), nq_mul(v[7], v[7]));
+        float4* dst = reinterpret_cast<float4*>(sq + (size_t)r * pitch + bb * 8);
+        dst[0] = lo;
+        dst[1] = hi;
+    }
+    __syncthreads();
+
+    for (int t = tid; t < nrows * 8; t += 256) {
+        const int r = t >> 3, l = t & 7;
+        const float* p = sq + (size_t)r * pitch + l;
+        float acc = 0.0f;
+#pragma unroll 8
+        for (int i = 0; i < bpr; ++i) acc = nq_add(acc, p[8 * i]);
+        partial[t] = acc;
+    }
+    __syncthreads();
+
+    for (int t = tid; t < nrows; t += 256) {
+        float total = partial[t * 8];
+#pragma unroll
+        for (int l = 1; l < 8; ++l) total = nq_add(total, partial[t * 8 + l]);
+        const float norm = nq_sqrt(total);
+        norms[t] = norm;
+        // sqrt(K)/norm is evaluated as reciprocal(norm) * sqrt(K) by the reference.
+        scale[t] = norm > 0.0f ? nq_mul(nq_rcp(norm), sqrt_k) : 0.0f;
+        dscale[t] = nq_div(norm, sqrt_k);
+    }
+    __syncthreads();
+
+    const int padded = (nblocks + 31) & ~31;
+    for (int b = tid; b < padded; b += 256) {
+        const bool valid = b < nblocks;
+        int bid = 0;
+        if (valid) {
+            const int r = b / bpr, bb = b - r * bpr;
+            float v[8], recon[8];
+            if (r < valid_rows) {
+                nq_load8<T>(x + (int64_t)r * row_stride + (int64_t)bb * 8, v);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = 0.0f;
+            }
+            const float s = scale[r];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = nq_mul(v[j], s);
+            uint32_t word;
+            if (use_dither) {  // weights: subtractive dither of the global block (warp-uniform branch)
+                float d[8];
+                nq_dither_block(counter_base + (uint32_t)b * 8u, d);
+                word = nq_encode_block(v, beta_table, d, bid, recon);
+            } else {
+                word = nq_encode_block(v, beta_table, nullptr, bid, recon);
+            }
+            codes[b] = word;
+            if (decoded != nullptr) {
+                const float ds = dscale[r];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) recon[j] = nq_mul(recon[j], ds);
+                *reinterpret_cast<uint4*>(decoded + (int64_t)b * 8) = nq_pack_bf16x8(recon);
+            }
+        }
+        // four neighbouring blocks share one beta byte (block i -> bits 2i..2i+1)
+        unsigned merged = (unsigned)bid;
+        merged |= __shfl_down_sync(0xffffffffu, (unsigned)bid, 1) << 2;
+        merged |= __shfl_down_sync(0xffffffffu, (unsigned)bid, 2) << 4;
+        merged |= __shfl_down_sync(0xffffffffu, (unsigned)bid, 3) << 6;
+        if (valid && (tid & 3) == 0) beta_ids[b >> 2] = (uint8_t)merged;
+    }
+}
