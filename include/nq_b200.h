@@ -140,6 +140,74 @@ int nq_w4_decode(const uint8_t* w_codes, const uint8_t* w_beta_ids, const float*
                  int64_t seed, void* out_bf16, nq_stream_t stream);
 
 /* -------------------------------------------------------------------------
+ * NQKV4 paged cache.  Device data model (unchanged from the reference):
+ *   pool   key_codes/value_codes u8[capacity, P*H*D/2], key_betas/value_betas u8[capacity, P*H*D/32],
+ *          key_norms/value_norms f32[capacity, P*H]            (runtime/nqkv_pool.py:100-110)
+ *   tables page_indices i32[S, max_pages] (-1 = empty), page_counts, last_page_lens, hot_lengths,
+ *          sequence_lengths i32[S], cache_active bool[S]        (runtime/paged_nqkv_cache.py:26-79)
+ *   hot    hot_keys/hot_values [S, P, H, D] in the KV dtype, target_page_ids i32[S]
+ *                                                               (runtime/nqkv_hot_cache.py:22-35)
+ * S = max_sequences, P = page_size, H = kv heads, D = head_dim (multiple of 32).
+ * Masks are 1-byte booleans.
+ *
+ * nq_kv_append: write new K/V tokens into the hot tail and bump hot/sequence lengths, one launch.
+ *   mode 0  one token per row, key/value [B, H, D], mask = active_mask[B]
+ *           (_launch_append_hot_k1_graph_safe, runtime/nqkv_graph_writer.py:291-332)
+ *   mode 1  key/value [B, T, H, D], mask = prefix write_mask[B, T]  (:373-419)
+ *   mode 2  key/value [B, T, H, D], per-row (source_starts, segment_counts)  (:422-473)
+ * Active slot ids must be unique (the reference's control plane guarantees it). */
+int nq_kv_append(const void* key, const void* value, int kv_dtype, int batch, int tokens, int mode,
+                 const int32_t* slot_ids, const uint8_t* mask, const int32_t* source_starts,
+                 const int32_t* segment_counts, const uint8_t* cache_active, void* hot_keys,
+                 void* hot_values, int32_t* hot_lengths, int32_t* sequence_lengths, int max_sequences,
+                 int page_size, int heads, int dim, nq_stream_t stream);
+
+/* For every slot with boundary_mask[s] && hot_lengths[s] == P: encode its hot page, store the six
+ * payload rows at pool[target_page_ids[s]], append the page id to the page table, set
+ * last_page_lens = P and hot_lengths = 0 (publish only while page_counts < max_pages).  Only the
+ * selected slots are encoded.  Payload bytes equal PackedNQKVPage.from_tensors
+ * (core/kv_format.py:71-131).  Replaces launch_pack_full_hot_pages_graph_safe
+ * (runtime/nqkv_graph_pack.py:76-135: encode of all slots + 6 copies + publish). */
+int nq_kv_pack_publish(const void* hot_keys, const void* hot_values, int kv_dtype, int32_t* hot_lengths,
+                       const uint8_t* boundary_mask, const int32_t* target_page_ids,
+                       uint8_t* key_codes, uint8_t* key_betas, float* key_norms, uint8_t* value_codes,
+                       uint8_t* value_betas, float* value_norms, const float* key_beta_table,
+                       const float* value_beta_table, int32_t* page_indices, int32_t* page_counts,
+                       int32_t* last_page_lens, int max_sequences, int max_pages, int pool_capacity,
+                       int page_size, int heads, int dim, nq_stream_t stream);
+
+/* Quantise and bit-pack one NHD page prefix key/value [valid_tokens, H, D] (rows after the prefix
+ * are zero) into six caller-provided payload buffers of one page.  Replaces
+ * quantize_nqkv_page_cuda (runtime/nqkv_page.py:241-329). */
+int nq_kv_quantize_page(const void* key, const void* value, int kv_dtype, int valid_tokens, int page_size,
+                        int heads, int dim, const float* key_beta_table, const float* value_beta_table,
+                        uint8_t* key_codes, uint8_t* key_betas, float* key_norms, uint8_t* value_codes,
+                        uint8_t* value_betas, float* value_norms, nq_stream_t stream);
+
+/* Paged GQA attention over NQKV4 pages plus the BF16 hot tail.
+ *   query  [B, Tq, Hq, D]; out [B, Tq, Hq, D] (NQ_BF16 or NQ_F32); rows that are inactive are zero.
+ *   decode q_lens = NULL, Tq = 1: every active row attends to its whole sequence
+ *          (nqkv_decode_attention_batched_k1, runtime/nqkv_attention_k1.py:763-942; no 127-page cap)
+ *   prefill q_lens[b] <= Tq new tokens per row whose K/V are already appended: query i attends to
+ *          the first  total - q_lens[b] + i + 1  tokens (causal), reading pages directly
+ *          (semantic of NQKVLlamaCache.prefill, runtime/nqkv_hf_backend.py:127-150).
+ * K/V of cold pages are the float32 reconstruction; softmax and accumulation in float32.
+ * workspace: nq_kv_attention_workspace_bytes(...) bytes (split partials). */
+size_t nq_kv_attention_workspace_bytes(int batch, int q_tokens, int q_heads, int kv_heads, int dim, int max_pages);
+int nq_kv_attention(const void* query, int q_dtype, int batch, int q_tokens, int q_heads,
+                    const int32_t* slot_ids, const uint8_t* active_mask, const int32_t* q_lens,
+                    const uint8_t* cache_active, const int32_t* sequence_lengths,
+                    const int32_t* page_indices, const int32_t* page_counts,
+                    const int32_t* last_page_lens, const int32_t* hot_lengths,
+                    const uint8_t* key_codes, const uint8_t* key_betas, const float* key_norms,
+                    const uint8_t* value_codes, const uint8_t* value_betas, const float* value_norms,
+                    const float* key_beta_table, const float* value_beta_table,
+                    const void* hot_keys, const void* hot_values, int max_sequences, int max_pages,
+                    int pool_capacity, int page_size, int kv_heads, int dim, float scale,
+                    void* workspace, size_t workspace_bytes, void* out, int out_dtype,
+                    nq_stream_t stream);
+
+/* -------------------------------------------------------------------------
  * Normalised Sylvester Hadamard along the last axis of a contiguous [rows, n]
  * tensor, n a power of two <= 32768, computed in the tensor's dtype exactly as
  * hadamard() does (core/rotation.py:12-27): every butterfly stage rounded to

@@ -74,7 +74,7 @@ def lib() -> ctypes.CDLL:
         handle.nq_last_error.restype = ctypes.c_char_p
         handle.nq_w4a4_workspace_bytes.restype = ctypes.c_size_t
         handle.nq_launch_count.restype = ctypes.c_ulonglong
-        for name in ("nq_attn_workspace_bytes",):
+        for name in ("nq_kv_attention_workspace_bytes",):
             if hasattr(handle, name):
                 getattr(handle, name).restype = ctypes.c_size_t
         _LIB = handle

@@ -9,3 +9,11 @@ from .w4a4 import (  # noqa: F401
     linear_packed_w4a4_mma_large_m_staged, linear_packed_w4a4_mma_chunked_staged,
     decode_packed_a4, decode_packed_a4_m16, decode_packed_weight, workspace_for, read_status, gemm_bf16_tc, launch_count,
 )
+from .kv import (  # noqa: F401,E402
+    NQKVPagePool, NQKVHotColdCache, PreparedNQKVPage, quantize_nqkv_page_cuda,
+    _launch_append_hot_k1_graph_safe, _launch_append_hot_ragged_subpage_graph_safe,
+    _launch_append_hot_ragged_segment_graph_safe, append_hot_k1_graph_safe,
+    launch_pack_full_hot_pages_graph_safe, BatchedNQKVAttentionWorkspace,
+    nqkv_decode_attention_batched_k1, _launch_nqkv_decode_attention_batched_k1, nqkv_prefill_attention,
+    cache_arrays,
+)
