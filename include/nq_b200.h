@@ -114,6 +114,23 @@ int nq_w4a4_gemm(const uint8_t* act_codes, const uint8_t* act_beta_ids, const fl
                  int64_t w_block_offset, int64_t seed, void* out, int out_dtype,
                  void* workspace, size_t workspace_bytes, nq_stream_t stream);
 
+/* Small-M projection for callers that cannot allocate or pass a workspace (a plugin slot that
+ * only receives inputs and outputs, a thread that must never reach cudaMalloc): same result as
+ * nq_w4a4_gemm for m <= NQ_STATIC_MAX_M, but the scratch (decoded activation rows, split-K
+ * partial sums, arrival counters) is a fixed array inside the library's device image, about
+ * 8.6 MiB held by every GPU that loads the library until the process exits.  Shapes beyond
+ * the limits below are rejected with NQ_ERR_ARG.  The first call on a device resolves the
+ * array's address (do it during set-up, before any stream capture).  All calls share the one
+ * array: calls that overlap on the GPU race on it.  Allocates nothing.
+ * This entry point has no counterpart in the reference. */
+#define NQ_STATIC_MAX_M 16
+#define NQ_STATIC_MAX_N 8192
+#define NQ_STATIC_MAX_K 8192
+int nq_w4a4_gemv_static(const uint8_t* act_codes, const uint8_t* act_beta_ids, const float* act_norms,
+                        const float* act_betas, const uint8_t* w_codes, const uint8_t* w_beta_ids,
+                        const float* w_norms, const float* w_betas, int64_t m, int64_t n, int64_t k,
+                        int64_t w_block_offset, int64_t seed, void* out, int out_dtype, nq_stream_t stream);
+
 /* The tcgen05 GEMM of the large-M path alone: out[m,n] = A[m,k] * W[n,k]^T on
  * BF16 row-major operands that were already decoded (nq_a4_encode's
  * out_decoded / nq_w4_decode).  Building block exposed for measurement and
