@@ -341,6 +341,147 @@ NQ_HD void nq_decode_weight_block(uint32_t word, uint32_t counter_base, float r[
     for (int j = 0; j < 8; ++j) r[j] = nq_sub(t[j], nq_mul(14.0f, n[j]));
 }
 
+// Position of a lattice point lam relative to the scaled Voronoi cell 14*V(E8):
+// +1 strictly inside, -1 strictly outside, 0 on the boundary.  V(E8) is cut out
+// by its 2400 relevant vectors (240 roots, 2160 vectors of norm 4); for each
+// class the largest inner product with lam has a closed form in the sorted
+// absolute coordinates.  All quantities are exact multiples of 1/4 in float32.
+//   roots  (+-1,+-1,0^6)              a1+a2                      vs 14
+//          (+-1/2)^8, even # minus    (S - [odd negatives]*2*amin)/2   vs 14
+//   norm 4 (+-1)^4 on four coords     a1+a2+a3+a4                vs 28
+//          (+-3/2,(+-1/2)^7), odd #   S/2 + a1 - [even negatives]*amin vs 28
+//          (+-2,0^7)                  implied by the first row
+// Strictly inside means t/14 reduces to lam itself with a margin of >= 0.0126 in
+// distance, far above float32 rounding, so the re-decode can be skipped exactly.
+NQ_HD int nq_e8_cell_class(const float lam[8]) {
+    float a[8];
+    float sum = 0.0f, amin = fabsf(lam[0]);
+    int negatives = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        a[j] = fabsf(lam[j]);
+        sum += a[j];
+        amin = fminf(amin, a[j]);
+        negatives ^= nq_float_bits(lam[j]) >> 31;  // sign bit; zeros force amin = 0, where parity is irrelevant
+    }
+    // four largest absolute values by partial selection
+    float t1 = 0.0f, t2 = 0.0f, t3 = 0.0f, t4 = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        float v = a[j];
+        float hi = fmaxf(t1, v); v = fminf(t1, v); t1 = hi;
+        hi = fmaxf(t2, v); v = fminf(t2, v); t2 = hi;
+        hi = fmaxf(t3, v); v = fminf(t3, v); t3 = hi;
+        t4 = fmaxf(t4, v);
+    }
+    const bool odd = (negatives & 1) != 0;
+    const float c1 = t1 + t2;                                   // vs 14
+    const float c2 = 0.5f * (sum - (odd ? 2.0f * amin : 0.0f)); // vs 14
+    const float c3 = t1 + t2 + t3 + t4;                         // vs 28
+    const float c4 = 0.5f * sum + t1 - (odd ? 0.0f : amin);     // vs 28
+    const float m14 = fmaxf(c1, c2), m28 = fmaxf(c3, c4);
+    if (m14 < 14.0f && m28 < 28.0f) return 1;
+    if (m14 > 14.0f || m28 > 28.0f) return -1;
+    return 0;
+}
+
+// One beta candidate evaluated exactly as the reference does (quantise,
+// reduce modulo q, reconstruct, error).  Returns the codeword.
+NQ_HD uint32_t nq_encode_candidate_exact(const float x[8], float beta, const float* dither, float r[8], float& err) {
+    float y[8], lam[8];
+    const float rbeta = nq_rcp(beta);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        y[j] = nq_div_by(x[j], beta, rbeta);
+        if (dither) y[j] = nq_add(y[j], dither[j]);
+    }
+    nq_e8_nearest_exact(y, lam);
+    const uint32_t word = nq_lattice_to_codeword(lam);
+    nq_decode_codeword_exact(word, dither, r);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) r[j] = nq_mul(r[j], beta);
+    err = nq_sqdist8_seq(r, x);
+    return word;
+}
+
+// Undithered multi-beta search with exact pruning.  For every beta the
+// lattice point lam and the error "as if lam were reproduced" are computed;
+// then
+//   * lam strictly inside 14*V: the reconstruction IS lam, the error is final;
+//   * lam strictly outside: the reconstruction differs from lam by a vector of
+//     14*E8 (norm >= 14*sqrt(2)), so its error is >= (14*sqrt(2)-1)^2 beta^2 >
+//     353 beta^2 and it cannot beat a candidate whose error is below that;
+//   * lam on the boundary, or nothing to prune against: full exact evaluation.
+// The result (codeword, beta index, reconstruction) is identical to
+// nq_encode_block for every input.
+NQ_HD uint32_t nq_encode_block_pruned(const float x[8], const float* beta, int& beta_id, float recon[8]) {
+    float best_err = 0.0f, best_lam[8];
+    int best = -1;
+    unsigned pending = 0;   // candidates that need the full evaluation
+    unsigned outside = 0;
+    float asif[4];
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+        const float bt = beta[b], rbeta = nq_rcp(bt);
+        float y[8], lam[8], r[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) y[j] = nq_div_by(x[j], bt, rbeta);
+        nq_e8_nearest_guarded(y, lam);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) r[j] = nq_mul(lam[j], bt);
+        asif[b] = nq_sqdist8_seq(r, x);
+        const int cls = nq_e8_cell_class(lam);
+        if (cls > 0) {
+            if (best < 0 || asif[b] < best_err) {
+                best = b;
+                best_err = asif[b];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) best_lam[j] = lam[j];
+            }
+        } else if (cls == 0) {
+            pending |= 1u << b;
+        } else {
+            outside |= 1u << b;
+        }
+    }
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+        const float bt = beta[b];
+        // an outside candidate's true error exceeds 353*beta^2; a boundary candidate's is >= its as-if error
+        if ((outside >> b) & 1u) {
+            if (!(best >= 0 && 353.0f * bt * bt > best_err)) pending |= 1u << b;
+        } else if ((pending >> b) & 1u) {
+            if (best >= 0 && asif[b] > best_err) pending &= ~(1u << b);
+        }
+    }
+    uint32_t best_word = 0;
+    bool have_word = false;
+    if (pending) {
+#pragma unroll 1
+        for (int b = 0; b < 4; ++b) {
+            if (!((pending >> b) & 1u)) continue;
+            float r[8], err;
+            const uint32_t word = nq_encode_candidate_exact(x, beta[b], nullptr, r, err);
+            if (best < 0 || err < best_err || (err == best_err && b < best)) {
+                best = b;
+                best_err = err;
+                best_word = word;
+                have_word = true;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) recon[j] = r[j];
+            }
+        }
+    }
+    beta_id = best;
+    if (!have_word) {
+        best_word = nq_lattice_to_codeword(best_lam);
+        const float bt = beta[best];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) recon[j] = nq_mul(best_lam[j], bt);
+    }
+    return best_word;
+}
+
 // ----------------------------------------------------------- encoder ------
 
 // Multi-beta search for one normalised block x (quantizer.py:275-283): for

@@ -46,3 +46,15 @@ void shim_decode_weight(const uint32_t* words, long n, long first_block, long se
         nq_decode_weight_block(words[i], (uint32_t)((uint64_t)(first_block + i) * 8u + (uint64_t)seed), out + 8 * i);
 }
 }
+
+extern "C" {
+// Pruned undithered search; must equal shim_encode_blocks(seed < 0) on every input.
+void shim_encode_blocks_pruned(const float* x, long n, const float* beta, uint32_t* words, int* beta_ids,
+                               float* recon) {
+    for (long i = 0; i < n; ++i) words[i] = nq_encode_block_pruned(x + 8 * i, beta, beta_ids[i], recon + 8 * i);
+}
+
+void shim_cell_class(const float* lam, long n, int* out) {
+    for (long i = 0; i < n; ++i) out[i] = nq_e8_cell_class(lam + 8 * i);
+}
+}

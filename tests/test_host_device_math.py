@@ -88,3 +88,53 @@ def test_weight_block_decode_matches_checker(shim, oracle):
                                  np.full(1, np.float32(np.sqrt(8 * n))), [1.0] * 4, 1, 8 * n, seed=4242,
                                  block_offset=77)
     assert np.array_equal(out.reshape(-1), ref.reshape(-1))
+
+
+def _encode_both(shim, x, betas):
+    x = np.ascontiguousarray(x, np.float32)
+    betas = np.array(betas, np.float32)
+    n = len(x)
+    out = []
+    for pruned in (False, True):
+        words, ids, rec = np.empty(n, np.uint32), np.empty(n, np.int32), np.empty_like(x)
+        if pruned:
+            shim.shim_encode_blocks_pruned(_p(x), ctypes.c_long(n), _p(betas), _p(words), _p(ids), _p(rec))
+        else:
+            shim.shim_encode_blocks(_p(x), ctypes.c_long(n), _p(betas), ctypes.c_long(-1), ctypes.c_long(0),
+                                    _p(words), _p(ids), _p(rec))
+        out.append((words, ids, rec))
+    return out
+
+
+@pytest.mark.parametrize("case", ["gauss", "heavy", "huge", "tiny", "grid", "boundary"])
+def test_pruned_search_equals_full_search(shim, case):
+    """The pruned 4-beta search (interior test + error bounds) must never change a bit."""
+    rng = np.random.default_rng(11)
+    unit = (0.25, 0.5, 0.75, 1.0)
+    if case == "gauss":
+        x, betas = rng.standard_normal((300000, 8)), ACT_BETAS
+    elif case == "heavy":
+        x, betas = rng.standard_t(2, (300000, 8)), ACT_BETAS
+    elif case == "huge":
+        x, betas = rng.standard_normal((100000, 8)) * 30, ACT_BETAS
+    elif case == "tiny":
+        x, betas = rng.standard_normal((100000, 8)) * 1e-3, ACT_BETAS
+    elif case == "grid":  # inputs on beta * (half-integer grid): dense coset ties and cell-boundary points
+        x = np.concatenate([rng.integers(-30, 31, (100000, 8)) * 0.5 * b for b in unit])
+        betas = unit
+    else:
+        a = np.zeros((8, 8)); a[:, 0] = 7; a[:, 1] = 7          # |lam|^2 = 98, on the boundary of 14 V
+        b = np.full((8, 8), 3.5)
+        x, betas = np.concatenate([a, b, a * 0.5, b * 0.75]), unit
+    (w1, i1, r1), (w2, i2, r2) = _encode_both(shim, x, betas)
+    assert np.array_equal(w1, w2) and np.array_equal(i1, i2) and np.array_equal(r1, r2)
+
+
+def test_cell_class_known_points(shim):
+    pts = np.array([[0] * 8, [7, 7, 0, 0, 0, 0, 0, 0], [3.5] * 8, [7, 6, 0, 0, 0, 0, 0, 0], [8, 7, 0, 0, 0, 0, 0, 0],
+                    [3.5] * 7 + [-3.5], [14, 0, 0, 0, 0, 0, 0, 0], [13, 0, 0, 0, 0, 0, 0, 0], [7, 7, 7, 7, 0, 0, 0, 0]],
+                   np.float32)
+    out = np.empty(len(pts), np.int32)
+    shim.shim_cell_class(_p(pts), ctypes.c_long(len(pts)), _p(out))
+    #            origin  root facet  half facet  inside  outside  odd half      (2,0..) facet  inside  norm-4 facet
+    assert out.tolist() == [1, 0, 0, 1, -1, 1, 0, 1, 0]
