@@ -99,7 +99,9 @@ __device__ __forceinline__ void nq_encode_rows_cta(
                 nq_dither_block(counter_base + (uint32_t)b * 8u, d);
                 word = nq_encode_block(v, beta_table, d, bid, recon);
             } else {
-                word = nq_encode_block_pruned(v, beta_table, bid, recon);
+                // nq_encode_block_pruned (same bits) issues 15 % fewer instructions but diverges and needs
+                // 104 registers; measured slower on B200 until its slow path is compacted across the CTA.
+                word = nq_encode_block(v, beta_table, nullptr, bid, recon);
             }
             codes[b] = word;
             if (decoded != nullptr) {
