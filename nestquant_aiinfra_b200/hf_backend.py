@@ -1,0 +1,248 @@
+"""Hugging Face plugin boundary of the NQKV4 cache: ``Cache`` subclass + attention interface.
+
+Mirror of ``nestquant.runtime.nqkv_batched_hf_backend`` (BatchedNQKVLlamaCache :26-631,
+_batched_nqkv_attention_interface :633-651, install_batched_nqkv_llama_backend :654-680):
+``update`` rotates K with the Hadamard transform (V is not rotated), appends the new tokens to
+the BF16 hot tail and packs full pages; the attention interface rotates Q and runs the paged
+kernel for decode (one token) or for a whole-prompt chunk.
+
+Differences from the reference, all on the host side: page ids are assigned statically
+(``slot * max_pages + page``), so the page writer needs no host reservation and the same
+captured graph serves boundary and non-boundary steps; prefill attention reads the pages it
+has just written (the reference runs SDPA over the current BF16 K/V).
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Hashable, Sequence
+
+import torch
+from transformers.cache_utils import Cache
+
+from .rotation import hadamard
+from .runtime.kv import (BatchedNQKVAttentionWorkspace, NQKVHotColdCache, NQKVPagePool,
+                         _launch_append_hot_k1_graph_safe, _launch_append_hot_ragged_segment_graph_safe,
+                         _launch_nqkv_decode_attention_batched_k1, launch_pack_full_hot_pages_graph_safe,
+                         nqkv_prefill_attention)
+
+BATCHED_NQKV_ATTENTION_NAME = "nestquant_batched_nqkv_k1"
+
+
+class BatchedNQKVLlamaCache(Cache):
+    """Multi-layer fixed-capacity NQKV cache driven by scheduler slot state."""
+
+    def __init__(self, *, capacity: int, num_layers: int, num_query_heads: int, num_kv_heads: int, head_dim: int,
+                 max_cache_len: int, page_size: int = 16, q: int = 14, key_betas: Sequence[float],
+                 value_betas: Sequence[float], dtype: torch.dtype = torch.bfloat16,
+                 device: torch.device | str = "cuda") -> None:
+        super().__init__(layers=[])
+        for name, value in (("capacity", capacity), ("num_layers", num_layers), ("num_query_heads", num_query_heads),
+                            ("num_kv_heads", num_kv_heads), ("head_dim", head_dim), ("max_cache_len", max_cache_len),
+                            ("page_size", page_size)):
+            if isinstance(value, bool) or not isinstance(value, int) or value < 1:
+                raise ValueError(f"{name} must be a positive integer")
+        if num_query_heads % num_kv_heads:
+            raise ValueError("num_query_heads must be divisible by num_kv_heads")
+        target = torch.device(device)
+        if target.type == "cuda" and target.index is None:
+            target = torch.device("cuda", torch.cuda.current_device())
+        max_pages = math.ceil(max_cache_len / page_size)
+        self.layer_caches: list[NQKVHotColdCache] = []
+        for _ in range(num_layers):
+            pool = NQKVPagePool(capacity=capacity * max_pages, page_size=page_size, num_kv_heads=num_kv_heads,
+                                head_dim=head_dim, q=q, key_betas=key_betas, value_betas=value_betas,
+                                output_dtype=dtype, device=target)
+            self.layer_caches.append(NQKVHotColdCache(pool, max_sequences=capacity, max_pages_per_sequence=max_pages))
+        self.capacity, self.num_layers = capacity, num_layers
+        self.num_query_heads, self.num_kv_heads, self.head_dim = num_query_heads, num_kv_heads, head_dim
+        self._max_cache_len, self.page_size, self.max_pages = max_cache_len, page_size, max_pages
+        self.dtype, self.device = dtype, target
+        self.slot_ids = torch.arange(capacity, device=target, dtype=torch.int32)
+        self.active_mask = torch.zeros(capacity, device=target, dtype=torch.bool)
+        self.execution_slot_ids = self.slot_ids
+        self.execution_active_mask = self.active_mask
+        self._all_slots = torch.ones(capacity, device=target, dtype=torch.bool)
+        self._page_base = torch.arange(capacity, device=target, dtype=torch.int32) * max_pages
+        self._decode_workspace = BatchedNQKVAttentionWorkspace.create(
+            self.layer_caches[0], batch_size=capacity, query_heads=num_query_heads, output_dtype=dtype)
+        self._prefill: tuple[torch.Tensor, torch.Tensor] | None = None  # (slot_ids, query_lengths)
+        self._prefill_workspace: BatchedNQKVAttentionWorkspace | None = None
+        self._sequence_of_slot: dict[int, Hashable] = {}
+
+    # ------------------------------------------------------------------ host control plane
+    def register(self, sequence_id: Hashable, *, slot: int) -> None:
+        if slot in self._sequence_of_slot:
+            raise RuntimeError(f"slot {slot} is already registered")
+        for cache in self.layer_caches:
+            cache.register(slot)
+        self.active_mask[slot] = True
+        self._sequence_of_slot[slot] = sequence_id
+
+    def register_batch(self, assignments: Sequence[tuple[Hashable, int]]) -> None:
+        for sequence_id, slot in assignments:
+            self.register(sequence_id, slot=slot)
+
+    def release_slots(self, slots: Sequence[int]) -> tuple[Hashable, ...]:
+        released = []
+        for slot in slots:
+            if slot not in self._sequence_of_slot:
+                continue
+            released.append(self._sequence_of_slot.pop(slot))
+            for cache in self.layer_caches:
+                cache.active[slot] = False
+                cache.sequence_lengths[slot] = 0
+                cache.hot_lengths[slot] = 0
+                cache.page_counts[slot] = 0
+            self.active_mask[slot] = False
+        return tuple(released)
+
+    def set_decode_state(self, *, slot_ids: torch.Tensor | None = None, active_mask: torch.Tensor | None = None) -> None:
+        """Rows of the next one-token forwards: row i serves slot ``slot_ids[i]`` when ``active_mask[i]``."""
+        self.execution_slot_ids = self.slot_ids if slot_ids is None else slot_ids
+        self.execution_active_mask = self.active_mask if active_mask is None else active_mask
+        self._prefill = None
+
+    def set_prefill_state(self, *, slot_ids: torch.Tensor, query_lengths: torch.Tensor) -> None:
+        """Rows of the next multi-token forward: row i appends ``query_lengths[i]`` tokens to ``slot_ids[i]``."""
+        if slot_ids.dtype != torch.int32 or query_lengths.dtype != torch.int32 or slot_ids.shape != query_lengths.shape:
+            raise ValueError("slot_ids and query_lengths must be int32 tensors of the same shape")
+        self._prefill = (slot_ids, query_lengths)
+
+    # ------------------------------------------------------------------ Cache interface
+    def _pack_full_pages(self, cache: NQKVHotColdCache) -> None:
+        torch.add(self._page_base, cache.page_counts, out=cache.graph_target_page_ids)
+        launch_pack_full_hot_pages_graph_safe(cache, boundary_mask=self._all_slots)
+
+    def update(self, key_states: torch.Tensor, value_states: torch.Tensor, layer_idx: int, cache_kwargs=None):
+        self._validate_layer(layer_idx)
+        cache = self.layer_caches[layer_idx]
+        rows, heads, tokens, dim = key_states.shape
+        if heads != self.num_kv_heads or dim != self.head_dim:
+            raise ValueError("key/value states do not match the cache geometry")
+        rotated_key = hadamard(key_states.float()).to(self.dtype)
+        if tokens == 1 and self._prefill is None:
+            if rows != self.execution_slot_ids.numel():
+                raise ValueError("decode rows do not match the execution slot ids")
+            _launch_append_hot_k1_graph_safe(rotated_key[:, :, 0], value_states[:, :, 0].to(self.dtype), cache,
+                                             slot_ids=self.execution_slot_ids, active_mask=self.execution_active_mask)
+            self._pack_full_pages(cache)
+            return rotated_key, value_states
+        if self._prefill is None:
+            raise RuntimeError("multi-token update needs set_prefill_state(slot_ids, query_lengths)")
+        slot_ids, query_lengths = self._prefill
+        if rows != slot_ids.numel():
+            raise ValueError("prefill rows do not match the prefill slot ids")
+        key_nhd = rotated_key.permute(0, 2, 1, 3).contiguous()
+        value_nhd = value_states.to(self.dtype).permute(0, 2, 1, 3).contiguous()
+        consumed = torch.zeros_like(query_lengths)
+        index = slot_ids.long()
+        for _ in range(math.ceil(tokens / self.page_size) + 1):
+            room = self.page_size - cache.hot_lengths[index]
+            counts = torch.clamp(torch.minimum(room, query_lengths - consumed), min=0).to(torch.int32)
+            _launch_append_hot_ragged_segment_graph_safe(key_nhd, value_nhd, cache, slot_ids=slot_ids,
+                                                         source_starts=consumed, segment_counts=counts)
+            self._pack_full_pages(cache)
+            consumed = consumed + counts
+        return rotated_key, value_states
+
+    def attend(self, layer_idx: int, query_states: torch.Tensor, *, scale: float) -> torch.Tensor:
+        """Decode: ``query_states [rows, Hq, 1, D]`` -> ``[rows, 1, Hq, D]``."""
+        self._validate_layer(layer_idx)
+        expected = (self.execution_slot_ids.numel(), self.num_query_heads, 1, self.head_dim)
+        if tuple(query_states.shape) != expected:
+            raise ValueError("batched NQKV decode requires [rows, heads, 1, dim]")
+        query = hadamard(query_states.float()).to(self.dtype)[:, :, 0].contiguous()
+        workspace = self._decode_workspace
+        if query.shape[0] != workspace.batch_size:
+            workspace = BatchedNQKVAttentionWorkspace.create(self.layer_caches[layer_idx], batch_size=query.shape[0],
+                                                             query_heads=self.num_query_heads, output_dtype=self.dtype)
+        output = _launch_nqkv_decode_attention_batched_k1(
+            query, self.layer_caches[layer_idx], slot_ids=self.execution_slot_ids,
+            active_mask=self.execution_active_mask, attention_scale=scale, workspace=workspace)
+        return output.unsqueeze(1)
+
+    def prefill(self, layer_idx: int, query_states: torch.Tensor, *, scale: float) -> torch.Tensor:
+        """Whole-chunk causal attention over the pages just written: ``[rows, Hq, T, D]`` -> ``[rows, T, Hq, D]``."""
+        self._validate_layer(layer_idx)
+        if self._prefill is None:
+            raise RuntimeError("prefill attention needs set_prefill_state(slot_ids, query_lengths)")
+        slot_ids, query_lengths = self._prefill
+        query = hadamard(query_states.float()).to(self.dtype).permute(0, 2, 1, 3).contiguous()
+        rows, tokens = query.shape[0], query.shape[1]
+        ws = self._prefill_workspace
+        if ws is None or (ws.batch_size, ws.query_tokens) != (rows, tokens):
+            ws = self._prefill_workspace = BatchedNQKVAttentionWorkspace.create(
+                self.layer_caches[layer_idx], batch_size=rows, query_heads=self.num_query_heads,
+                output_dtype=self.dtype, query_tokens=tokens)
+        out = nqkv_prefill_attention(query, self.layer_caches[layer_idx], slot_ids=slot_ids,
+                                     query_lengths=query_lengths, scale=scale, workspace=ws)
+        return out.view(rows, tokens, self.num_query_heads, self.head_dim)
+
+    def get_seq_length(self, layer_idx: int = 0) -> int:
+        self._validate_layer(layer_idx)
+        lengths = self.layer_caches[layer_idx].sequence_lengths
+        return int(lengths.max().item()) if self._sequence_of_slot else 0
+
+    def get_max_length(self, layer_idx: int | None = None) -> int:
+        return self._max_cache_len
+
+    def get_max_cache_shape(self, layer_idx: int = 0) -> int:
+        return self._max_cache_len
+
+    def get_mask_sizes(self, query_length, layer_idx: int = 0) -> tuple[int, int]:
+        return self._max_cache_len, 0
+
+    @property
+    def batch_size(self) -> int:
+        return self.capacity
+
+    @property
+    def is_compileable(self) -> bool:
+        return False
+
+    def reorder_cache(self, beam_idx) -> None:
+        raise NotImplementedError("batched NQKV backend does not support beam search")
+
+    def _validate_layer(self, layer_idx: int) -> None:
+        if isinstance(layer_idx, bool) or not isinstance(layer_idx, int):
+            raise TypeError("layer_idx must be an integer")
+        if not 0 <= layer_idx < self.num_layers:
+            raise ValueError("layer_idx is outside the batched NQKV layer range")
+
+
+def _batched_nqkv_attention_interface(module, query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
+                                      attention_mask: torch.Tensor | None, **kwargs):
+    cache = getattr(module, "_nestquant_batched_nqkv_cache", None)
+    if not isinstance(cache, BatchedNQKVLlamaCache):
+        raise RuntimeError("Llama attention module has no batched NQKV cache")
+    if kwargs.get("dropout", 0.0) != 0.0:
+        raise ValueError("batched NQKV backend supports inference dropout=0 only")
+    scale = float(kwargs.get("scaling", module.scaling))
+    if query.shape[2] == 1 and cache._prefill is None:
+        return cache.attend(module.layer_idx, query, scale=scale), None
+    return cache.prefill(module.layer_idx, query, scale=scale), None
+
+
+def install_batched_nqkv_llama_backend(model: torch.nn.Module, cache: BatchedNQKVLlamaCache) -> str:
+    """Attach fixed-capacity batched NQKV attention to every Llama layer."""
+    from transformers.modeling_utils import ALL_ATTENTION_FUNCTIONS
+
+    if not isinstance(model, torch.nn.Module):
+        raise TypeError("model must be a torch module")
+    if not isinstance(cache, BatchedNQKVLlamaCache):
+        raise TypeError("cache must be a BatchedNQKVLlamaCache")
+    ALL_ATTENTION_FUNCTIONS.register(BATCHED_NQKV_ATTENTION_NAME, _batched_nqkv_attention_interface)
+    attached = 0
+    for module in model.modules():
+        if module.__class__.__name__ == "LlamaAttention":
+            if not 0 <= module.layer_idx < cache.num_layers:
+                raise ValueError("Llama layer index disagrees with batched NQKV cache")
+            module._nestquant_batched_nqkv_cache = cache
+            module.config._attn_implementation = BATCHED_NQKV_ATTENTION_NAME
+            attached += 1
+    if attached != cache.num_layers:
+        raise ValueError(f"expected {cache.num_layers} LlamaAttention modules, found {attached}")
+    if hasattr(model, "config"):
+        model.config._attn_implementation = BATCHED_NQKV_ATTENTION_NAME
+    return BATCHED_NQKV_ATTENTION_NAME

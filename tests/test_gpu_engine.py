@@ -1,0 +1,105 @@
+"""End-to-end W4A4KV4 Llama: HF plugin boundary, ragged prefill, CUDA-graph decode."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+TINY = dict(hidden_size=256, intermediate_size=512, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=64,
+            vocab_size=512)
+
+
+def _build(capacity=4, max_cache_len=128, seed=3):
+    from nestquant_aiinfra_b200.engine import BatchedNQKVLlamaRunner, build_llama_w4a4kv4
+
+    model, cache = build_llama_w4a4kv4(**TINY, capacity=capacity, max_cache_len=max_cache_len, seed=seed)
+    return model, cache, BatchedNQKVLlamaRunner(model, cache)
+
+
+def _prompts(lengths, seed=11):
+    gen = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, TINY["vocab_size"], (n,), generator=gen) for n in lengths]
+
+
+def test_projections_are_converted_and_backend_installed():
+    from nestquant_aiinfra_b200.fused_linear import FusedNQRTLinear
+    from nestquant_aiinfra_b200.hf_backend import BATCHED_NQKV_ATTENTION_NAME
+
+    model, cache, _ = _build()
+    fused = [m for m in model.modules() if isinstance(m, FusedNQRTLinear)]
+    assert len(fused) == 7 * TINY["num_layers"]
+    assert model.config._attn_implementation == BATCHED_NQKV_ATTENTION_NAME
+    assert all(m.packed_device_bytes > 0 for m in fused)
+
+
+def test_prefill_tracks_the_unquantised_model():
+    """Last-token logits of the W4A4KV4 prefill stay close to the BF16 model they were quantised from."""
+    from transformers import LlamaConfig, LlamaForCausalLM
+
+    model, cache, runner = _build(seed=5)
+    prompts = _prompts([5, 21, 40])
+    runner.prefill_slots([0, 2, 3], prompts)
+    lengths = cache.layer_caches[0].sequence_lengths.tolist()
+    assert lengths == [5, 0, 21, 40]
+    assert cache.layer_caches[1].page_counts.tolist() == [0, 0, 1, 2]
+    assert cache.layer_caches[1].hot_lengths.tolist() == [5, 0, 5, 8]
+    config = LlamaConfig(hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=4,
+                         num_key_value_heads=2, head_dim=64, vocab_size=512, max_position_embeddings=2048,
+                         tie_word_embeddings=False, attention_bias=False, mlp_bias=False)
+    torch.manual_seed(5)
+    with torch.device("cuda"):
+        reference = LlamaForCausalLM(config).to(torch.bfloat16).eval()
+    with torch.no_grad():
+        for slot, prompt in zip([0, 2, 3], prompts):
+            ids = prompt.cuda().unsqueeze(0)
+            expected = reference(input_ids=ids).logits[0, -1].float()
+            runner.cache.release_slots([slot])
+            model2_logits = None
+            # re-run the quantised prefill for this prompt alone and read the logits
+            runner.cache.register("probe", slot=slot)
+            slot_ids = torch.tensor([slot], dtype=torch.int32, device="cuda")
+            q_lens = torch.tensor([prompt.numel()], dtype=torch.int32, device="cuda")
+            cache.set_prefill_state(slot_ids=slot_ids, query_lengths=q_lens)
+            pos = torch.arange(prompt.numel(), device="cuda").unsqueeze(0)
+            model2_logits = model(input_ids=ids, position_ids=pos, past_key_values=cache, use_cache=True).logits[0, -1].float()
+            cache.set_decode_state()
+            cosine = torch.nn.functional.cosine_similarity(model2_logits, expected, dim=0).item()
+            assert cosine > 0.9, cosine
+
+
+def test_graph_decode_equals_eager_decode():
+    prompts = _prompts([7, 16, 33, 50])
+    outputs = []
+    for use_graph in (False, True):
+        model, cache, runner = _build(seed=9)
+        first = runner.prefill_slots([0, 1, 2, 3], prompts)
+        if use_graph:
+            runner.capture_decode_graph()
+        tokens = [first.clone()]
+        for _ in range(20):  # crosses page boundaries for every slot
+            tokens.append(runner.decode().clone())
+        torch.cuda.synchronize()
+        state = [(c.sequence_lengths.clone(), c.page_counts.clone(), c.hot_lengths.clone(), c.hot_keys.clone())
+                 for c in cache.layer_caches]
+        outputs.append((torch.stack(tokens), state))
+    (eager_tokens, eager_state), (graph_tokens, graph_state) = outputs
+    assert torch.equal(eager_tokens, graph_tokens)
+    for (a, b, c, d), (e, f, g, h) in zip(eager_state, graph_state):
+        assert torch.equal(a, e) and torch.equal(b, f) and torch.equal(c, g) and torch.equal(d, h)
+    assert eager_state[0][0].tolist() == [27, 36, 53, 70]
+
+
+def test_released_slot_is_reused_and_inactive_rows_do_not_move():
+    model, cache, runner = _build(seed=1)
+    runner.prefill_slots([1], _prompts([9]))
+    runner.capture_decode_graph()
+    for _ in range(3):
+        runner.decode()
+    assert cache.layer_caches[0].sequence_lengths.tolist() == [0, 12, 0, 0]
+    cache.release_slots([1])
+    runner.prefill_slots([1, 3], _prompts([4, 18], seed=2))
+    runner.decode()
+    torch.cuda.synchronize()
+    assert cache.layer_caches[0].sequence_lengths.tolist() == [0, 5, 0, 19]
+    with pytest.raises(RuntimeError):
+        cache.register("again", slot=3)
