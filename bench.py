@@ -305,6 +305,14 @@ def run_gpu(args) -> None:
             "cpu_baseline": base,
             "cells": table,
         }
+        if not args.skip_extras:
+            for key, fn in (("kv", lambda: kv_workload(torch, rt, device, pk)),
+                            ("decode", lambda: decode_workload(torch, device))):
+                try:
+                    line[key] = fn()
+                except Exception as error:  # keep the headline line even if an extra workload fails
+                    line[key] = {"error": f"{type(error).__name__}: {error}"[:300]}
+                torch.cuda.empty_cache()
         print(json.dumps(line), flush=True)
     if distributed:
         dist.barrier()
@@ -391,6 +399,114 @@ def run_e2e(torch, rt, FusedNQRTLinear, weights, device, steps: int, distributed
     e1.record(stream)
     torch.cuda.synchronize(device)
     return {"ms": e0.elapsed_time(e1) / steps, "h2d": h2d, "d2h": d2h}
+
+
+def kv_workload(torch, rt, device, pk) -> dict:
+    """NQKV4 pack + quantized-KV decode attention (batch 32, 8 KV heads, ctx 4096 + 1 hot token, head_dim 64)."""
+    from nestquant_aiinfra_b200.formats import KEY_BETAS, VALUE_BETAS
+    from nestquant_aiinfra_b200.rotation import hadamard
+
+    batch, heads, q_heads, dim, page, ctx = 32, 8, 32, 64, 16, 4096
+    pages_per_seq = ctx // page
+    capacity = batch * pages_per_seq
+    pool = rt.NQKVPagePool(capacity=capacity, page_size=page, num_kv_heads=heads, head_dim=dim, key_betas=KEY_BETAS,
+                           value_betas=VALUE_BETAS, device=device)
+    cache = rt.NQKVHotColdCache(pool, max_sequences=batch, max_pages_per_sequence=pages_per_seq + 1)
+    gen = torch.Generator().manual_seed(4096)
+    perm = torch.randperm(capacity, generator=gen).to(device)
+    rows = capacity * page * heads
+    for which, (codes, betas, norms, table, tbl_vals) in enumerate((
+            (pool.key_codes, pool.key_betas, pool.key_norms, pool.beta_table, KEY_BETAS),
+            (pool.value_codes, pool.value_betas, pool.value_norms, pool.value_beta_table, VALUE_BETAS))):
+        x = torch.randn(batch, ctx, heads, dim, generator=gen)
+        flat = torch.randperm(heads * dim, generator=gen)[:6]
+        x.view(batch, ctx, heads * dim)[:, :, flat] *= 8.0          # 1 % outlier channels
+        x = x.to(device)
+        x = hadamard(x) if which == 0 else x                        # keys are rotated per head, values are not
+        act = rt.quantize_activation_cuda(x.bfloat16().reshape(rows, dim), q=14, betas=tbl_vals, beta_table=table,
+                                          keep_decoded=False)
+        codes[perm] = act.code_payload.view(capacity, -1)
+        betas[perm] = act.beta_payload.view(capacity, -1)
+        norms[perm] = act.row_norms.view(capacity, -1)
+        del x, act
+    for slot in range(batch):
+        cache.register(slot)
+    cache.page_indices[:, :pages_per_seq] = perm.view(batch, pages_per_seq).to(torch.int32)
+    cache.page_counts.fill_(pages_per_seq)
+    cache.last_page_len.fill_(page)
+    cache.hot_lengths.fill_(1)
+    cache.sequence_lengths.fill_(ctx + 1)
+    cache.hot_keys[:, 0] = torch.randn(batch, heads, dim, generator=gen).bfloat16().to(device)
+    cache.hot_values[:, 0] = torch.randn(batch, heads, dim, generator=gen).bfloat16().to(device)
+    q = hadamard(torch.randn(batch, q_heads, dim, generator=gen).to(device)).bfloat16()
+    slot_ids = torch.arange(batch, dtype=torch.int32, device=device)
+    active = torch.ones(batch, dtype=torch.bool, device=device)
+    ws = rt.BatchedNQKVAttentionWorkspace.create(cache, batch_size=batch, query_heads=q_heads)
+    t_attn = _time_graph(torch, lambda: rt._launch_nqkv_decode_attention_batched_k1(
+        q, cache, slot_ids=slot_ids, active_mask=active, attention_scale=0.125, workspace=ws), device)
+    attn_bytes = batch * pages_per_seq * pool.page_payload_bytes + batch * 2 * heads * dim * 2 + 2 * batch * q_heads * dim * 2
+    # page pack: all 32 hot tails full, packed into fresh pages of a second pool region (re-armed every launch)
+    pack_pool = rt.NQKVPagePool(capacity=batch, page_size=page, num_kv_heads=heads, head_dim=dim, key_betas=KEY_BETAS,
+                                value_betas=VALUE_BETAS, device=device)
+    pack_cache = rt.NQKVHotColdCache(pack_pool, max_sequences=batch, max_pages_per_sequence=4)
+    for slot in range(batch):
+        pack_cache.register(slot)
+    pack_cache.hot_keys.copy_(torch.randn(pack_cache.hot_keys.shape, generator=gen).bfloat16())
+    pack_cache.hot_values.copy_(torch.randn(pack_cache.hot_values.shape, generator=gen).bfloat16())
+    pack_cache.graph_target_page_ids.copy_(torch.arange(batch, dtype=torch.int32))
+
+    def pack_once():
+        pack_cache.hot_lengths.fill_(page)
+        pack_cache.page_counts.zero_()
+        rt.launch_pack_full_hot_pages_graph_safe(pack_cache, boundary_mask=active)
+
+    t_pack = _time_graph(torch, pack_once, device)
+    pack_bytes = batch * (2 * page * heads * dim * 2 + pack_pool.page_payload_bytes)
+    return {
+        "attention_decode": {"batch": batch, "ctx": ctx + 1, "q_heads": q_heads, "kv_heads": heads, "head_dim": dim,
+                             "pages_per_seq": pages_per_seq, "us": round(t_attn, 2),
+                             "gbs": round(attn_bytes / t_attn / 1e3, 1),
+                             "frac_of_hbm": round(attn_bytes / t_attn / 1e3 / pk["hbm_gbs"], 4)},
+        "page_pack_publish": {"pages": batch, "us": round(t_pack, 2), "us_per_page": round(t_pack / batch, 3),
+                              "gbs": round(pack_bytes / t_pack / 1e3, 1), "note": "includes two small fill kernels"},
+    }
+
+
+def decode_workload(torch, device, *, requests: int = 64, new_tokens: int = 256) -> dict:
+    """Llama-3.2-1B architecture, random init, W4A4KV4: ragged prefill then graph decode of `requests` rows."""
+    from nestquant_aiinfra_b200.engine import BatchedNQKVLlamaRunner, build_llama_w4a4kv4
+
+    model, cache = build_llama_w4a4kv4(hidden_size=2048, intermediate_size=8192, num_layers=16, num_heads=32,
+                                       num_kv_heads=8, head_dim=64, vocab_size=128256, capacity=requests,
+                                       max_cache_len=2048 + new_tokens + 16, device=device, seed=0)
+    runner = BatchedNQKVLlamaRunner(model, cache)
+    gen = torch.Generator().manual_seed(128)
+    lengths = torch.randint(128, 2049, (requests,), generator=gen).tolist()
+    prompts = [torch.randint(0, 128256, (n,), generator=gen) for n in lengths]
+    order = sorted(range(requests), key=lambda i: lengths[i])
+    torch.cuda.synchronize(device)
+    t0 = time.perf_counter()
+    for start in range(0, requests, 8):  # 8 prompts of similar length per prefill call
+        group = order[start:start + 8]
+        runner.prefill_slots(group, [prompts[i] for i in group])
+    torch.cuda.synchronize(device)
+    prefill_s = time.perf_counter() - t0
+    runner.capture_decode_graph()
+    for _ in range(3):
+        runner.decode()
+    torch.cuda.synchronize(device)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    steps = new_tokens - 3
+    for _ in range(steps):
+        runner.decode()
+    e1.record()
+    torch.cuda.synchronize(device)
+    ms = e0.elapsed_time(e1)
+    return {"model": "llama-3.2-1b-arch random init, W4A4KV4, 112 NQRT4 projections", "requests": requests,
+            "prompt_tokens": int(sum(lengths)), "decode_steps": steps, "ms_per_step": round(ms / steps, 3),
+            "decode_tok_s": round(requests * steps / (ms * 1e-3), 1), "prefill_s": round(prefill_s, 2),
+            "prefill_tok_s": round(sum(lengths) / prefill_s, 1), "cuda_graph": True}
 
 
 def main() -> None:
