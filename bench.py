@@ -284,6 +284,26 @@ def run_gpu(args) -> None:
         e2e["ms"] = float(t.item())
     e2e_value = None if e2e["ms"] is None else world * sweep_flops() / (e2e["ms"] * 1e-3) / 1e12
 
+    extras = {}
+    if not args.skip_extras:
+        try:
+            if rank == 0:
+                extras["kv"] = kv_workload(torch, rt, device, pk)
+        except Exception as error:  # keep the headline line even if an extra workload fails
+            extras["kv"] = {"error": f"{type(error).__name__}: {error}"[:300]}
+        torch.cuda.empty_cache()
+        try:
+            dec = decode_workload(torch, device)
+            if distributed:  # independent replicas: total tokens over the slowest rank's time
+                t = torch.tensor([dec["ms_per_step"]], device=device)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                dec["ms_per_step"] = round(float(t.item()), 3)
+                dec["decode_tok_s"] = round(world * dec["requests"] / (dec["ms_per_step"] * 1e-3), 1)
+                dec["replicas"] = world
+            extras["decode"] = dec
+        except Exception as error:
+            extras["decode"] = {"error": f"{type(error).__name__}: {error}"[:300]}
+        torch.cuda.empty_cache()
     if rank == 0:
         base = cpu_baseline(repeats=2) if world == 1 and not args.skip_extras else None
         if base:
@@ -305,14 +325,7 @@ def run_gpu(args) -> None:
             "cpu_baseline": base,
             "cells": table,
         }
-        if not args.skip_extras:
-            for key, fn in (("kv", lambda: kv_workload(torch, rt, device, pk)),
-                            ("decode", lambda: decode_workload(torch, device))):
-                try:
-                    line[key] = fn()
-                except Exception as error:  # keep the headline line even if an extra workload fails
-                    line[key] = {"error": f"{type(error).__name__}: {error}"[:300]}
-                torch.cuda.empty_cache()
+        line.update(extras)
         print(json.dumps(line), flush=True)
     if distributed:
         dist.barrier()

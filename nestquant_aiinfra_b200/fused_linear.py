@@ -126,7 +126,7 @@ class FusedNQRTLinear(nn.Module):
         self.reader = None
         if isinstance(source, PreparedNQRTLinear):
             self._prepared = source
-            shape = (int(source.record.indices.shape[0]), int(source.record.feature_count))
+            shape = (source.rows, int(source.record.feature_count))
         elif hasattr(source, "read_named_record"):
             self.reader = source
             entry = source.get_entry(weight_name)

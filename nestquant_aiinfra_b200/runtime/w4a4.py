@@ -106,6 +106,14 @@ class PreparedNQRTLinear:
     beta_payload: torch.Tensor
     row_norms: torch.Tensor
     beta_table: torch.Tensor
+    # Global index of this view's first E8 block inside its record: a row-range shard keeps the
+    # dither counter of the unsharded weight (the reference always passes 0, cuda_w4a4_mma.py:243).
+    block_offset: int = 0
+    out_features: int | None = None
+
+    @property
+    def rows(self) -> int:
+        return int(self.record.indices.shape[0]) if self.out_features is None else int(self.out_features)
 
 
 def _payload_tensor(payload, device: torch.device) -> torch.Tensor:
@@ -249,7 +257,7 @@ def can_use_w4a4(activation: PreparedNQA4Activation, weight: PreparedNQRTLinear)
         and activation.q == 14 and activation.code_width == 4 and activation.beta_width == 2
         and activation.beta_table.numel() == 4
         and record.feature_count % 32 == 0
-        and record.indices.shape[0] % 8 == 0
+        and weight.rows % 8 == 0
         and record.indices.q == 14 and record.indices.code_bit_width == 4
         and record.indices.beta_count == 4 and record.indices.beta_index_bit_width == 2
         and record.dither_seed is not None
@@ -287,7 +295,7 @@ def can_use_w4a4_mma_chunked_staged(activation, weight) -> bool:
 def _run(activation: PreparedNQA4Activation, weight: PreparedNQRTLinear, out_dtype: torch.dtype,
          *, use_decoded: bool = True) -> torch.Tensor:
     record = weight.record
-    m, k, n = activation.token_count, activation.feature_count, int(record.indices.shape[0])
+    m, k, n = activation.token_count, activation.feature_count, weight.rows
     device = activation.code_payload.device
     library = _lib.lib()
     nbytes = library.nq_w4a4_workspace_bytes(_I64(m), _I64(n), _I64(k))
@@ -298,7 +306,7 @@ def _run(activation: PreparedNQA4Activation, weight: PreparedNQRTLinear, out_dty
         _ptr(activation.code_payload), _ptr(activation.beta_payload), _ptr(activation.row_norms),
         _ptr(activation.beta_table), _ptr(decoded),
         _ptr(weight.code_payload), _ptr(weight.beta_payload), _ptr(weight.row_norms), _ptr(weight.beta_table),
-        _I64(m), _I64(n), _I64(k), _I64(0), _I64(int(record.dither_seed)),
+        _I64(m), _I64(n), _I64(k), _I64(int(weight.block_offset)), _I64(int(record.dither_seed)),
         _ptr(out), _DTYPE_TAG[out_dtype], _ptr(workspace), ctypes.c_size_t(workspace.numel()), _stream(device))
     _lib.check(status, "linear_packed_w4a4")
     return out
@@ -332,7 +340,7 @@ def linear_packed_w4a4(activation: PreparedNQA4Activation, weight: PreparedNQRTL
     if not can_use_w4a4(activation, weight):
         raise ValueError("activation or packed weight is unsupported by the W4A4 kernels")
     out = _run(activation, weight, _output_dtype(activation))
-    n = int(weight.record.indices.shape[0])
+    n = weight.rows
     return out.to(activation.output_dtype).reshape(*activation.original_shape[:-1], n)
 
 
@@ -341,7 +349,7 @@ def linear_packed_w4a4_fp32(activation: PreparedNQA4Activation, weight: Prepared
     _check_types(activation, weight)
     if not can_use_w4a4(activation, weight):
         raise ValueError("activation or packed weight is unsupported by the W4A4 kernels")
-    n = int(weight.record.indices.shape[0])
+    n = weight.rows
     return _run(activation, weight, torch.float32).reshape(*activation.original_shape[:-1], n)
 
 
@@ -402,12 +410,12 @@ def decode_packed_weight(weight: PreparedNQRTLinear) -> torch.Tensor:
     if not isinstance(weight, PreparedNQRTLinear):
         raise TypeError("weight must be PreparedNQRTLinear")
     record = weight.record
-    n, k = int(record.indices.shape[0]), int(record.feature_count)
+    n, k = weight.rows, int(record.feature_count)
     device = weight.code_payload.device
     out = torch.empty((n, k), dtype=torch.bfloat16, device=device)
     status = _lib.lib().nq_w4_decode(
         _ptr(weight.code_payload), _ptr(weight.beta_payload), _ptr(weight.row_norms), _ptr(weight.beta_table),
-        _I64(n), _I64(k), _I64(0), _I64(int(record.dither_seed)), _ptr(out), _stream(device))
+        _I64(n), _I64(k), _I64(int(weight.block_offset)), _I64(int(record.dither_seed)), _ptr(out), _stream(device))
     _lib.check(status, "decode_packed_weight")
     return out
 
