@@ -414,10 +414,15 @@ NQ_HD uint32_t nq_encode_candidate_exact(const float x[8], float beta, const flo
 //   * lam on the boundary, or nothing to prune against: full exact evaluation.
 // The result (codeword, beta index, reconstruction) is identical to
 // nq_encode_block for every input.
-NQ_HD uint32_t nq_encode_block_pruned(const float x[8], const float* beta, int& beta_id, float recon[8]) {
-    float best_err = 0.0f, best_lam[8];
-    int best = -1;
-    unsigned pending = 0;   // candidates that need the full evaluation
+// First half of the pruned search: classifies the four candidates.  On return
+// `best` (or -1) / best_err / best_lam describe the best candidate whose lattice
+// point is strictly inside 14*V, and bit b of `pending` is set for every
+// candidate that still needs the full evaluation (nq_encode_candidate_exact).
+NQ_HD void nq_encode_block_fastpass(const float x[8], const float* beta, int& best, float& best_err,
+                                    float best_lam[8], unsigned& pending) {
+    best = -1;
+    best_err = 0.0f;
+    pending = 0;
     unsigned outside = 0;
     float asif[4];
 #pragma unroll
@@ -454,6 +459,18 @@ NQ_HD uint32_t nq_encode_block_pruned(const float x[8], const float* beta, int& 
             if (best >= 0 && asif[b] > best_err) pending &= ~(1u << b);
         }
     }
+}
+
+// Merge rule of the search: smaller error wins, equal errors go to the smaller beta index.
+NQ_HD bool nq_candidate_wins(int b, float err, int best, float best_err) {
+    return best < 0 || err < best_err || (err == best_err && b < best);
+}
+
+NQ_HD uint32_t nq_encode_block_pruned(const float x[8], const float* beta, int& beta_id, float recon[8]) {
+    float best_err, best_lam[8];
+    int best;
+    unsigned pending;
+    nq_encode_block_fastpass(x, beta, best, best_err, best_lam, pending);
     uint32_t best_word = 0;
     bool have_word = false;
     if (pending) {
@@ -462,7 +479,7 @@ NQ_HD uint32_t nq_encode_block_pruned(const float x[8], const float* beta, int& 
             if (!((pending >> b) & 1u)) continue;
             float r[8], err;
             const uint32_t word = nq_encode_candidate_exact(x, beta[b], nullptr, r, err);
-            if (best < 0 || err < best_err || (err == best_err && b < best)) {
+            if (nq_candidate_wins(b, err, best, best_err)) {
                 best = b;
                 best_err = err;
                 best_word = word;

@@ -30,7 +30,7 @@ extern "C" int nq_abi_version(void) { return 1; }
 // Encoder kernel: one CTA per group of rows (see nq_encode_core.cuh).
 // ---------------------------------------------------------------------------
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 3)
 nq_encode_rows_kernel(const T* __restrict__ x, int64_t rows, int k, int64_t row_stride,
                       const float* __restrict__ beta_table, float sqrt_k,
                       uint32_t* __restrict__ codes, uint8_t* __restrict__ beta_ids,

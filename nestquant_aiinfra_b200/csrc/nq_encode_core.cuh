@@ -13,13 +13,17 @@
 
 #include "nq_common.cuh"
 
+// Staging area of the compacted slow path (per CTA of 256 threads): normalised blocks,
+// per-(thread, beta) results of the full evaluation, the work queue and its counter.
+#define NQ_ENCODE_STAGE_FLOATS (256 * 8 + 1024 + 1024 + 256 * 4 * 4 + 512 + 4)
+
 __host__ __device__ inline int nq_encode_rows_per_cta(int k) {
     const int bpr = k / 8;
     return bpr >= 256 ? 1 : 256 / bpr;
 }
 __host__ __device__ inline size_t nq_encode_smem_floats(int k) {
     const int rpc = nq_encode_rows_per_cta(k);
-    return (size_t)rpc * (k + 8) + (size_t)rpc * 10;
+    return (size_t)rpc * (k + 8) + (size_t)rpc * 10 + NQ_ENCODE_STAGE_FLOATS;
 }
 
 template <typename T>
@@ -78,38 +82,126 @@ __device__ __forceinline__ void nq_encode_rows_cta(
     __syncthreads();
 
     const int padded = (nblocks + 31) & ~31;
-    for (int b = tid; b < padded; b += 256) {
+    if (use_dither) {
+        // weights: straight per-thread search with the subtractive dither of the global block
+        for (int b = tid; b < padded; b += 256) {
+            const bool valid = b < nblocks;
+            int bid = 0;
+            if (valid) {
+                const int r = b / bpr, bb = b - r * bpr;
+                float v[8], recon[8], d[8];
+                if (r < valid_rows) {
+                    nq_load8<T>(x + (int64_t)r * row_stride + (int64_t)bb * 8, v);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) v[j] = 0.0f;
+                }
+                const float s = scale[r];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = nq_mul(v[j], s);
+                nq_dither_block(counter_base + (uint32_t)b * 8u, d);
+                codes[b] = nq_encode_block(v, beta_table, d, bid, recon);
+                if (decoded != nullptr) {
+                    const float ds = dscale[r];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) recon[j] = nq_mul(recon[j], ds);
+                    *reinterpret_cast<uint4*>(decoded + (int64_t)b * 8) = nq_pack_bf16x8(recon);
+                }
+            }
+            unsigned merged = (unsigned)bid;
+            merged |= __shfl_down_sync(0xffffffffu, (unsigned)bid, 1) << 2;
+            merged |= __shfl_down_sync(0xffffffffu, (unsigned)bid, 2) << 4;
+            merged |= __shfl_down_sync(0xffffffffu, (unsigned)bid, 3) << 6;
+            if (valid && (tid & 3) == 0) beta_ids[b >> 2] = (uint8_t)merged;
+        }
+        return;
+    }
+
+    // Undithered rows (activations, K/V): every thread classifies its four candidates with the
+    // cheap exact tests; the few (thread, beta) pairs that need the full evaluation are queued in
+    // shared memory and evaluated densely by the whole CTA, so no warp idles behind one slow lane.
+    float* stage = dscale + rows_per_cta;
+    float* xs = stage;                                             // [256][8] normalised blocks
+    float* res_err = xs + 256 * 8;                                 // [256][4]
+    uint32_t* res_word = reinterpret_cast<uint32_t*>(res_err + 1024);  // [256][4]
+    uint4* res_dec = reinterpret_cast<uint4*>(res_word + 1024);    // [256][4] scaled BF16 reconstruction
+    unsigned short* queue = reinterpret_cast<unsigned short*>(res_dec + 1024);  // [1024] (thread << 2) | beta
+    unsigned* queue_count = reinterpret_cast<unsigned*>(queue + 1024);
+    for (int base = 0; base < padded; base += 256) {
+        const int b = base + tid;
         const bool valid = b < nblocks;
-        int bid = 0;
+        if (tid == 0) *queue_count = 0u;
+        __syncthreads();
+        int best = 0, row_r = 0;
+        float best_err = 0.0f, best_lam[8];
+        unsigned pending = 0;
         if (valid) {
-            const int r = b / bpr, bb = b - r * bpr;
-            float v[8], recon[8];
-            if (r < valid_rows) {
-                nq_load8<T>(x + (int64_t)r * row_stride + (int64_t)bb * 8, v);
+            row_r = b / bpr;
+            const int bb = b - row_r * bpr;
+            float v[8];
+            if (row_r < valid_rows) {
+                nq_load8<T>(x + (int64_t)row_r * row_stride + (int64_t)bb * 8, v);
             } else {
 #pragma unroll
                 for (int j = 0; j < 8; ++j) v[j] = 0.0f;
             }
-            const float s = scale[r];
+            const float s = scale[row_r];
 #pragma unroll
             for (int j = 0; j < 8; ++j) v[j] = nq_mul(v[j], s);
-            uint32_t word;
-            if (use_dither) {  // weights: subtractive dither of the global block (warp-uniform branch)
-                float d[8];
-                nq_dither_block(counter_base + (uint32_t)b * 8u, d);
-                word = nq_encode_block(v, beta_table, d, bid, recon);
-            } else {
-                // nq_encode_block_pruned (same bits) issues 15 % fewer instructions but diverges and needs
-                // 104 registers; measured slower on B200 until its slow path is compacted across the CTA.
-                word = nq_encode_block(v, beta_table, nullptr, bid, recon);
-            }
-            codes[b] = word;
-            if (decoded != nullptr) {
-                const float ds = dscale[r];
+            float4* dst = reinterpret_cast<float4*>(xs + tid * 8);
+            dst[0] = make_float4(v[0], v[1], v[2], v[3]);
+            dst[1] = make_float4(v[4], v[5], v[6], v[7]);
+            nq_encode_block_fastpass(v, beta_table, best, best_err, best_lam, pending);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) recon[j] = nq_mul(recon[j], ds);
-                *reinterpret_cast<uint4*>(decoded + (int64_t)b * 8) = nq_pack_bf16x8(recon);
+            for (int c = 0; c < 4; ++c)
+                if ((pending >> c) & 1u) queue[atomicAdd(queue_count, 1u)] = (unsigned short)((tid << 2) | c);
+        }
+        __syncthreads();
+        const int items = (int)*queue_count;
+        for (int it = tid; it < items; it += 256) {
+            const int owner = queue[it] >> 2, c = queue[it] & 3;
+            float v[8], r[8], err;
+            const float4 lo = reinterpret_cast<const float4*>(xs + owner * 8)[0];
+            const float4 hi = reinterpret_cast<const float4*>(xs + owner * 8)[1];
+            v[0] = lo.x; v[1] = lo.y; v[2] = lo.z; v[3] = lo.w; v[4] = hi.x; v[5] = hi.y; v[6] = hi.z; v[7] = hi.w;
+            res_word[owner * 4 + c] = nq_encode_candidate_exact(v, beta_table[c], nullptr, r, err);
+            res_err[owner * 4 + c] = err;
+            const float ds = dscale[(base + owner) / bpr];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) r[j] = nq_mul(r[j], ds);
+            res_dec[owner * 4 + c] = nq_pack_bf16x8(r);
+        }
+        __syncthreads();
+        int bid = 0;
+        if (valid) {
+            uint32_t word = 0;
+            uint4 dec = make_uint4(0, 0, 0, 0);
+            bool from_queue = false;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                if (!((pending >> c) & 1u)) continue;
+                const float err = res_err[tid * 4 + c];
+                if (nq_candidate_wins(c, err, best, best_err)) {
+                    best = c;
+                    best_err = err;
+                    word = res_word[tid * 4 + c];
+                    dec = res_dec[tid * 4 + c];
+                    from_queue = true;
+                }
             }
+            if (!from_queue) {
+                word = nq_lattice_to_codeword(best_lam);
+                if (decoded != nullptr) {
+                    const float bt = beta_table[best], ds = dscale[row_r];
+                    float recon[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) recon[j] = nq_mul(nq_mul(best_lam[j], bt), ds);
+                    dec = nq_pack_bf16x8(recon);
+                }
+            }
+            bid = best;
+            codes[b] = word;
+            if (decoded != nullptr) *reinterpret_cast<uint4*>(decoded + (int64_t)b * 8) = dec;
         }
         // four neighbouring blocks share one beta byte (block i -> bits 2i..2i+1)
         unsigned merged = (unsigned)bid;
