@@ -103,7 +103,7 @@ int nq_a4_decode(const uint8_t* codes, const uint8_t* beta_ids, const float* nor
  *              NQ_WS_COUNTER_BYTES bytes must be zero before the FIRST use and are
  *              left zero by every call.
  * Requirements: k % 32 == 0, n % 8 == 0, n <= 131064.  The tcgen05 path is taken for
- * m > 16 when n % 128 == 0 and k % 64 == 0. */
+ * m >= 8 when n % 128 == 0 and k % 64 == 0 (split-K with a deterministic reduction when few tiles). */
 #define NQ_WS_COUNTER_BYTES 65536
 #define NQ_WS_STATUS_OFFSET 65532 /* last word of the counter area: device status, 0 = ok */
 size_t nq_w4a4_workspace_bytes(int64_t m, int64_t n, int64_t k);

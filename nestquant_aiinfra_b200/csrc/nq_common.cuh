@@ -81,7 +81,10 @@ __device__ __forceinline__ void nq_load8<__half>(const __half* p, float v[8]) {
 __device__ __forceinline__ uint4 nq_pack_bf16x8(const float v[8]) {
     uint32_t w[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) w[i] = nq_bf16_bits(v[2 * i]) | (nq_bf16_bits(v[2 * i + 1]) << 16);
+    for (int i = 0; i < 4; ++i) {
+        const __nv_bfloat162 pair = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);  // one cvt.rn.bf16x2.f32
+        w[i] = *reinterpret_cast<const uint32_t*>(&pair);
+    }
     return make_uint4(w[0], w[1], w[2], w[3]);
 }
 

@@ -36,7 +36,7 @@ nq_encode_rows_kernel(const T* __restrict__ x, int64_t rows, int k, int64_t row_
                       uint32_t* __restrict__ codes, uint8_t* __restrict__ beta_ids,
                       float* __restrict__ norms, __nv_bfloat16* __restrict__ decoded,
                       int use_dither, uint32_t counter_base) {
-    extern __shared__ float smem[];
+    extern __shared__ __align__(16) float smem[];
     const int rpc = nq_encode_rows_per_cta(k);
     const int bpr = k >> 3;
     const int64_t row0 = (int64_t)blockIdx.x * rpc;

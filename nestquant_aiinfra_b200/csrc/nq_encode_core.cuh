@@ -15,7 +15,7 @@
 
 // Staging area of the compacted slow path (per CTA of 256 threads): normalised blocks,
 // per-(thread, beta) results of the full evaluation, the work queue and its counter.
-#define NQ_ENCODE_STAGE_FLOATS (256 * 8 + 1024 + 1024 + 256 * 4 * 4 + 512 + 4)
+#define NQ_ENCODE_STAGE_FLOATS (256 * 8 + 1024 + 1024 + 256 * 4 * 4 + 512 + 4 + 4 /* alignment slack */)
 
 __host__ __device__ inline int nq_encode_rows_per_cta(int k) {
     const int bpr = k / 8;
@@ -120,7 +120,8 @@ __device__ __forceinline__ void nq_encode_rows_cta(
     // Undithered rows (activations, K/V): every thread classifies its four candidates with the
     // cheap exact tests; the few (thread, beta) pairs that need the full evaluation are queued in
     // shared memory and evaluated densely by the whole CTA, so no warp idles behind one slow lane.
-    float* stage = dscale + rows_per_cta;
+    // 16-byte aligned: the staging arrays are accessed with 128-bit loads and stores
+    float* stage = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(dscale + rows_per_cta) + 15) & ~(uintptr_t)15);
     float* xs = stage;                                             // [256][8] normalised blocks
     float* res_err = xs + 256 * 8;                                 // [256][4]
     uint32_t* res_word = reinterpret_cast<uint32_t*>(res_err + 1024);  // [256][4]

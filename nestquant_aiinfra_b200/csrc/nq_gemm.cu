@@ -12,12 +12,13 @@ int nq_launch_small_m(const void* a_dec, const uint8_t* w_codes, const uint8_t* 
 // tcgen05 path (nq_gemm_tc.cu)
 bool nq_tc_supported(int64_t m, int64_t n, int64_t k);
 size_t nq_tc_workspace_bytes(int64_t m, int64_t n, int64_t k);
-int nq_launch_tc_gemm(const void* a_dec, const void* w_dec, int64_t m, int64_t n, int64_t k,
-                      void* out, int out_dtype, void* workspace, cudaStream_t stream);
+int nq_launch_tc_gemm(const void* a_dec, const void* w_dec, int64_t m, int64_t n, int64_t k, void* out,
+                      int out_dtype, void* status_word, void* partial, unsigned* counters, cudaStream_t stream);
 
 namespace {
 
-constexpr int64_t kSmallMMax = 16;
+constexpr int64_t kSmallMMax = 16;  // rows handled by one launch of the CUDA-core kernel
+constexpr int64_t kTcMinM = 8;     // from here on decode-once + tcgen05 is faster than the per-row GEMV
 
 inline size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 
@@ -30,7 +31,7 @@ Carve carve(int64_t m, int64_t n, int64_t k) {
     size_t off = NQ_WS_COUNTER_BYTES;
     c.a_dec = off;
     off += align256((size_t)m * k * 2);
-    const bool tc = m > kSmallMMax && nq_tc_supported(m, n, k);
+    const bool tc = m >= kTcMinM && nq_tc_supported(m, n, k);
     c.w_dec = off;
     if (tc) off += align256((size_t)n * k * 2);
     c.partial = off;
@@ -82,10 +83,11 @@ extern "C" int nq_w4a4_gemm(const uint8_t* act_codes, const uint8_t* act_beta_id
         a_dec = ws + c.a_dec;
     }
 
-    if (m > kSmallMMax && nq_tc_supported(m, n, k)) {
+    if (m >= kTcMinM && nq_tc_supported(m, n, k)) {
         int rc = nq_w4_decode(w_codes, w_beta_ids, w_norms, w_betas, n, k, w_block_offset, seed, ws + c.w_dec, stream);
         if (rc) return rc;
-        return nq_launch_tc_gemm(a_dec, ws + c.w_dec, m, n, k, out, out_dtype, ws + NQ_WS_STATUS_OFFSET, s);
+        return nq_launch_tc_gemm(a_dec, ws + c.w_dec, m, n, k, out, out_dtype, ws + NQ_WS_STATUS_OFFSET, ws + c.tc,
+                                 counters, s);
     }
 
     // CUDA-core path; rows beyond 16 are processed 16 at a time
@@ -125,7 +127,9 @@ extern "C" int nq_bf16_gemm_tc(const void* a_bf16, const void* w_bf16, int64_t m
     NQ_REQUIRE(workspace_bytes >= NQ_WS_COUNTER_BYTES, NQ_ERR_WORKSPACE, "nq_bf16_gemm_tc: workspace too small");
     NQ_REQUIRE(nq_aligned16(a_bf16) && nq_aligned16(w_bf16) && nq_aligned16(out), NQ_ERR_ALIGN,
                "nq_bf16_gemm_tc: 16-byte alignment required");
-    return nq_launch_tc_gemm(a_bf16, w_bf16, m, n, k, out, out_dtype,
-                             reinterpret_cast<char*>(workspace) + NQ_WS_STATUS_OFFSET,
+    char* ws = reinterpret_cast<char*>(workspace);
+    const bool room = workspace_bytes >= NQ_WS_COUNTER_BYTES + nq_tc_workspace_bytes(m, n, k);
+    return nq_launch_tc_gemm(a_bf16, w_bf16, m, n, k, out, out_dtype, ws + NQ_WS_STATUS_OFFSET,
+                             room ? ws + NQ_WS_COUNTER_BYTES : nullptr, reinterpret_cast<unsigned*>(ws),
                              reinterpret_cast<cudaStream_t>(stream));
 }

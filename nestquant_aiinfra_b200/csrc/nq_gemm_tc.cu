@@ -43,6 +43,9 @@ struct TcParams {
     void* out;          // [m, n]
     int out_bf16;
     unsigned* status;   // 0 = ok
+    int splits;         // K splits per output tile (1 = none); work item = tile * splits + split
+    float* partial;     // [splits, m, n] float32 partial sums when splits > 1
+    unsigned* counters; // per-tile arrival counters (zero on entry, zero on exit)
 };
 
 struct __align__(8) TcBarriers {
@@ -52,6 +55,7 @@ struct __align__(8) TcBarriers {
     uint64_t acc_empty[2];
     uint32_t tmem_base;
     int abort_flag;
+    unsigned ticket;
 };
 
 __device__ __forceinline__ void tc_fail(const TcParams& p, TcBarriers* bars, unsigned code) {
@@ -72,8 +76,8 @@ nq_w4a4_tc_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
     volatile int* abort_flag = &bars->abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int k_steps = p.k / kTileK;
-    const int total_tiles = p.n_tiles * p.t_tiles;
+    const int k_steps_all = p.k / kTileK;
+    const int total_tiles = p.n_tiles * p.t_tiles * p.splits;  // work items
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.stages; ++s) {
@@ -103,10 +107,12 @@ nq_w4a4_tc_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
         if (lane == 0) {
             uint32_t fill = 0;  // running stage-fill counter
             bool ok = true;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            for (int item = blockIdx.x; item < total_tiles && ok; item += gridDim.x) {
+                const int tile = item / p.splits, split = item - tile * p.splits;
                 const int n0 = (tile % p.n_tiles) * kTileN;
                 const int t0 = (tile / p.n_tiles) * p.tile_t;
-                for (int ks = 0; ks < k_steps; ++ks, ++fill) {
+                const int ks0 = split * k_steps_all / p.splits, ks1 = (split + 1) * k_steps_all / p.splits;
+                for (int ks = ks0; ks < ks1; ++ks, ++fill) {
                     const int s = fill % p.stages;
                     const uint32_t use = fill / p.stages;
                     if (use > 0 && !mbar_wait_bounded(&bars->empty[s], (use - 1) & 1, abort_flag)) {
@@ -134,7 +140,7 @@ nq_w4a4_tc_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
             const uint32_t idesc = umma_idesc_bf16(kTileN, (uint32_t)p.tile_t);
             uint32_t fill = 0, local_tile = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local_tile) {
+            for (int item = blockIdx.x; item < total_tiles && ok; item += gridDim.x, ++local_tile) {
                 const uint32_t buf = local_tile & 1, use = local_tile >> 1;
                 if (use > 0 && !mbar_wait_bounded(&bars->acc_empty[buf], (use - 1) & 1, abort_flag)) {
                     tc_fail(p, bars, 2);
@@ -142,7 +148,9 @@ nq_w4a4_tc_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
                 }
                 tc_fence_after();
                 const uint32_t acc = tmem_base + buf * kAccCols;
-                for (int ks = 0; ks < k_steps; ++ks, ++fill) {
+                const int split = item % p.splits;
+                const int ks0 = split * k_steps_all / p.splits, ks1 = (split + 1) * k_steps_all / p.splits;
+                for (int ks = ks0; ks < ks1; ++ks, ++fill) {
                     const int s = fill % p.stages;
                     if (!mbar_wait_bounded(&bars->full[s], (fill / p.stages) & 1, abort_flag)) {
                         tc_fail(p, bars, 3);
@@ -157,7 +165,7 @@ nq_w4a4_tc_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
                     for (int kk = 0; kk < kTileK / 16; ++kk) {
                         // +32 bytes per K16 step inside the 128-byte swizzle row (16-byte units)
                         umma_bf16(acc, desc_w + (uint64_t)(kk * 2), desc_a + (uint64_t)(kk * 2), idesc,
-                                  (ks > 0 || kk > 0) ? 1u : 0u);
+                                  (ks > ks0 || kk > 0) ? 1u : 0u);
                     }
                     umma_commit(&bars->empty[s]);
                 }
@@ -168,23 +176,30 @@ nq_w4a4_tc_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
         // ------------------------------------------------------------ epilogue
         const int quarter = warp & 3;  // TMEM lane quarter this warp may read
         uint32_t local_tile = 0;
-        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local_tile) {
+        for (int item = blockIdx.x; item < total_tiles; item += gridDim.x, ++local_tile) {
             const uint32_t buf = local_tile & 1, use = local_tile >> 1;
+            const int tile = item / p.splits, split = item - tile * p.splits;
             const int n0 = (tile % p.n_tiles) * kTileN;
             const int t0 = (tile / p.n_tiles) * p.tile_t;
-            if (!mbar_wait_bounded(&bars->acc_full[buf], use & 1, abort_flag)) {
+            const bool ready = mbar_wait_bounded(&bars->acc_full[buf], use & 1, abort_flag);
+            if (!ready) {
                 if (lane == 0) tc_fail(p, bars, 4);
-                break;
+                if (p.splits == 1) break;  // with splits the warps leave together after the barrier below
             }
             tc_fence_after();
             const int channel = n0 + quarter * 32 + lane;
             const uint32_t taddr = tmem_base + buf * kAccCols + ((uint32_t)(quarter * 32) << 16);
-            for (int c = 0; c < p.tile_t; c += 32) {
+            for (int c = 0; ready && c < p.tile_t; c += 32) {
                 if (t0 + c >= p.m) break;  // warp-uniform
                 uint32_t r[32];
                 tmem_ld_32x32(taddr + (uint32_t)c, r);
                 tmem_ld_wait();
-                if (p.out_bf16) {
+                if (p.splits > 1) {
+                    float* o = p.partial + ((int64_t)split * p.m + t0 + c) * p.n + channel;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (t0 + c + j < p.m) o[(int64_t)j * p.n] = __uint_as_float(r[j]);
+                } else if (p.out_bf16) {
                     __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + (int64_t)(t0 + c) * p.n + channel;
 #pragma unroll
                     for (int j = 0; j < 32; ++j)
@@ -199,6 +214,29 @@ nq_w4a4_tc_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars->acc_empty[buf]);
+            if (p.splits > 1) {
+                // the last CTA to finish a tile adds the K-split partials in split order (deterministic)
+                __threadfence();
+                asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
+                if (threadIdx.x == 64) bars->ticket = atomicAdd(p.counters + tile, 1u);
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (*abort_flag) break;  // uniform: the flag was raised before the first barrier
+                if (bars->ticket == (unsigned)(p.splits - 1)) {
+                    __threadfence();
+                    const int ch = n0 + (int)threadIdx.x - 64;
+                    const int t_end = min(p.tile_t, p.m - t0);
+                    for (int t = 0; t < t_end; ++t) {
+                        float total = 0.0f;
+                        for (int sp = 0; sp < p.splits; ++sp)
+                            total += __ldcg(p.partial + ((int64_t)sp * p.m + t0 + t) * p.n + ch);
+                        const int64_t o = (int64_t)(t0 + t) * p.n + ch;
+                        if (p.out_bf16) reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(total);
+                        else reinterpret_cast<float*>(p.out)[o] = total;
+                    }
+                    if (threadIdx.x == 64) p.counters[tile] = 0u;
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");  // ticket may be overwritten by the next item
+            }
         }
     }
 
@@ -263,12 +301,31 @@ bool nq_tc_supported(int64_t m, int64_t n, int64_t k) {
     return m >= 1 && n % kTileN == 0 && k % kTileK == 0 && k >= kTileK;
 }
 
-// status word + padding
-size_t nq_tc_workspace_bytes(int64_t, int64_t, int64_t) { return 256; }
+namespace {
+// K splits for grids that would leave most SMs idle (few output tiles, long K).
+int tc_splits(int64_t m, int64_t n, int64_t k) {
+    const int tile_t = m > 128 ? 256 : (m > 64 ? 128 : (m > 32 ? 64 : 32));
+    const int tiles = (int)(n / kTileN) * (int)((m + tile_t - 1) / tile_t);
+    const int k_steps = (int)(k / kTileK);
+    int splits = sm_count() / tiles;
+    if (splits > k_steps / 4) splits = k_steps / 4;
+    if (splits > 16) splits = 16;
+    return splits < 2 ? 1 : splits;
+}
+}  // namespace
+
+// float32 partial sums of the split-K variant
+size_t nq_tc_workspace_bytes(int64_t m, int64_t n, int64_t k) {
+    const int splits = tc_splits(m, n, k);
+    return splits > 1 ? (size_t)splits * m * n * sizeof(float) : 256;
+}
 
 int nq_launch_tc_gemm(const void* a_dec, const void* w_dec, int64_t m, int64_t n, int64_t k, void* out,
-                      int out_dtype, void* workspace, cudaStream_t stream) {
+                      int out_dtype, void* status_word, void* partial, unsigned* counters, cudaStream_t stream) {
     TcParams p;
+    p.splits = (partial && counters) ? tc_splits(m, n, k) : 1;
+    p.partial = reinterpret_cast<float*>(partial);
+    p.counters = counters;
     p.m = (int)m; p.n = (int)n; p.k = (int)k;
     p.tile_t = m > 128 ? 256 : (m > 64 ? 128 : (m > 32 ? 64 : 32));
     p.n_tiles = (int)(n / kTileN);
@@ -279,7 +336,7 @@ int nq_launch_tc_gemm(const void* a_dec, const void* w_dec, int64_t m, int64_t n
     p.stages = stages;
     p.out = out;
     p.out_bf16 = out_dtype == NQ_BF16;
-    p.status = reinterpret_cast<unsigned*>(workspace);
+    p.status = reinterpret_cast<unsigned*>(status_word);
     CUtensorMap map_w, map_a;
     int rc = make_map(&map_w, w_dec, n, k, kTileN);
     if (rc) return rc;
@@ -296,7 +353,7 @@ int nq_launch_tc_gemm(const void* a_dec, const void* w_dec, int64_t m, int64_t n
         }
         configured = true;
     }
-    const int total = p.n_tiles * p.t_tiles;
+    const int total = p.n_tiles * p.t_tiles * p.splits;
     const int grid = total < sm_count() ? total : sm_count();
     nq_w4a4_tc_gemm_kernel<<<grid, kThreadsTc, smem, stream>>>(map_w, map_a, p);
     NQ_CHECK_LAUNCH("nq_w4a4_gemm(tcgen05)");

@@ -100,7 +100,7 @@ struct PackParams {
 
 template <typename T>
 __global__ void __launch_bounds__(256) nq_kv_pack_pages_kernel(const PackParams p) {
-    extern __shared__ float smem[];
+    extern __shared__ __align__(16) float smem[];
     const int slot = blockIdx.x;
     const bool full = p.boundary_mask[slot] != 0 && p.hot_lengths[slot] == p.page_size;
     const int page_id = p.target_page_ids[slot];
@@ -145,7 +145,7 @@ struct PageParams {
 
 template <typename T>
 __global__ void __launch_bounds__(256) nq_kv_quantize_page_kernel(const PageParams p) {
-    extern __shared__ float smem[];
+    extern __shared__ __align__(16) float smem[];
     const int is_value = blockIdx.x / p.ctas_per_stream;
     const int chunk = blockIdx.x - is_value * p.ctas_per_stream;
     const int rows = p.page_size * p.heads, rpc = nq_encode_rows_per_cta(p.dim), bpr = p.dim >> 3;
