@@ -39,7 +39,7 @@ struct AttnParams {
     const void *hot_keys, *hot_values;  // [S, P, H, D] bf16
     int max_sequences, max_pages, pool_capacity;
     float scale_log2e;  // attention scale * log2(e)
-    float sqrt_dim;
+    float sqrt_dim, inv_sqrt_dim;
     int splits;
     float* partial;  // [B*Tq, Hq, splits, D + 2]
     void* out;       // [B, Tq, Hq, D]
@@ -140,8 +140,8 @@ __global__ void __launch_bounds__(kAttnThreads) nq_attn_paged_kernel(const AttnP
                     const uint32_t vw = __ldg(reinterpret_cast<const uint32_t*>(p.value_codes + page_id * code_bytes) + g);
                     const float kb = __ldg(p.key_beta_table + nq_beta_id(p.key_betas + page_id * beta_bytes, g));
                     const float vb = __ldg(p.value_beta_table + nq_beta_id(p.value_betas + page_id * beta_bytes, g));
-                    const float kds = nq_div(__ldg(p.key_norms + (int64_t)page_id * rows + row), p.sqrt_dim);
-                    const float vds = nq_div(__ldg(p.value_norms + (int64_t)page_id * rows + row), p.sqrt_dim);
+                    const float kds = nq_div_by(__ldg(p.key_norms + (int64_t)page_id * rows + row), p.sqrt_dim, p.inv_sqrt_dim);
+                    const float vds = nq_div_by(__ldg(p.value_norms + (int64_t)page_id * rows + row), p.sqrt_dim, p.inv_sqrt_dim);
                     nq_decode_codeword_exact(kw, nullptr, kvec);
                     nq_decode_codeword_exact(vw, nullptr, vvec);
 #pragma unroll
@@ -326,6 +326,7 @@ extern "C" int nq_kv_attention(const void* query, int q_dtype, int batch, int q_
     p.max_sequences = max_sequences; p.max_pages = max_pages; p.pool_capacity = pool_capacity;
     p.scale_log2e = scale * 1.4426950408889634f;
     p.sqrt_dim = (float)sqrt((double)dim);
+    p.inv_sqrt_dim = 1.0f / p.sqrt_dim;
     p.splits = choose_splits(batch * q_tokens, kv_heads, max_pages);
     p.out = out; p.out_dtype = out_dtype;
     p.partial = reinterpret_cast<float*>(workspace);

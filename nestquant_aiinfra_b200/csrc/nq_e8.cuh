@@ -288,9 +288,9 @@ NQ_HD void nq_decode_codeword_exact(uint32_t word, const float* dither, float r[
     }
 #pragma unroll
     for (int j = 0; j < 8; ++j) s[j] = nq_div_by(t[j], 14.0f, NQ_RCP14);
-    nq_e8_nearest_exact(s, n);
+    nq_e8_nearest_guarded(s, n);  // same result as the exact search, cheaper away from coset ties
 #pragma unroll
-    for (int j = 0; j < 8; ++j) r[j] = nq_sub(t[j], nq_mul(14.0f, n[j]));
+    for (int j = 0; j < 8; ++j) r[j] = nq_fma(-14.0f, n[j], t[j]);  // 14*n is exact, so one rounding either way
 }
 
 // ------------------------------------------------------------ dither ------
