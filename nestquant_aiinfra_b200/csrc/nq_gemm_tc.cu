@@ -45,7 +45,7 @@ struct TcParams {
     unsigned* status;   // 0 = ok
     int splits;         // K splits per output tile (1 = none); work item = tile * splits + split
     float* partial;     // [splits, m, n] float32 partial sums when splits > 1
-    unsigned* counters; // per-tile arrival counters (zero on entry, zero on exit)
+    unsigned* counters; // unused
 };
 
 struct __align__(8) TcBarriers {
@@ -184,12 +184,12 @@ nq_w4a4_tc_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
             const bool ready = mbar_wait_bounded(&bars->acc_full[buf], use & 1, abort_flag);
             if (!ready) {
                 if (lane == 0) tc_fail(p, bars, 4);
-                if (p.splits == 1) break;  // with splits the warps leave together after the barrier below
+                break;
             }
             tc_fence_after();
             const int channel = n0 + quarter * 32 + lane;
             const uint32_t taddr = tmem_base + buf * kAccCols + ((uint32_t)(quarter * 32) << 16);
-            for (int c = 0; ready && c < p.tile_t; c += 32) {
+            for (int c = 0; c < p.tile_t; c += 32) {
                 if (t0 + c >= p.m) break;  // warp-uniform
                 uint32_t r[32];
                 tmem_ld_32x32(taddr + (uint32_t)c, r);
@@ -214,29 +214,6 @@ nq_w4a4_tc_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars->acc_empty[buf]);
-            if (p.splits > 1) {
-                // the last CTA to finish a tile adds the K-split partials in split order (deterministic)
-                __threadfence();
-                asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
-                if (threadIdx.x == 64) bars->ticket = atomicAdd(p.counters + tile, 1u);
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                if (*abort_flag) break;  // uniform: the flag was raised before the first barrier
-                if (bars->ticket == (unsigned)(p.splits - 1)) {
-                    __threadfence();
-                    const int ch = n0 + (int)threadIdx.x - 64;
-                    const int t_end = min(p.tile_t, p.m - t0);
-                    for (int t = 0; t < t_end; ++t) {
-                        float total = 0.0f;
-                        for (int sp = 0; sp < p.splits; ++sp)
-                            total += __ldcg(p.partial + ((int64_t)sp * p.m + t0 + t) * p.n + ch);
-                        const int64_t o = (int64_t)(t0 + t) * p.n + ch;
-                        if (p.out_bf16) reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(total);
-                        else reinterpret_cast<float*>(p.out)[o] = total;
-                    }
-                    if (threadIdx.x == 64) p.counters[tile] = 0u;
-                }
-                asm volatile("bar.sync 1, 128;" ::: "memory");  // ticket may be overwritten by the next item
-            }
         }
     }
 
@@ -246,6 +223,26 @@ nq_w4a4_tc_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
         __syncwarp();
         tc_fence_after();
         tmem_dealloc(tmem_base, 2 * kAccCols);
+    }
+}
+
+// Sum the K-split partial tiles in split order (deterministic) and cast to the output dtype.
+__global__ void __launch_bounds__(256)
+nq_tc_splitk_reduce_kernel(const float4* __restrict__ partial, int splits, int64_t quads, void* __restrict__ out,
+                           int out_bf16) {
+    const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    if (i >= quads) return;
+    float4 acc = __ldcg(partial + i);
+    for (int s = 1; s < splits; ++s) {
+        const float4 v = __ldcg(partial + (int64_t)s * quads + i);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    if (out_bf16) {
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
+        reinterpret_cast<uint2*>(out)[i] = make_uint2(*reinterpret_cast<const uint32_t*>(&lo),
+                                                      *reinterpret_cast<const uint32_t*>(&hi));
+    } else {
+        reinterpret_cast<float4*>(out)[i] = acc;
     }
 }
 
@@ -323,7 +320,7 @@ size_t nq_tc_workspace_bytes(int64_t m, int64_t n, int64_t k) {
 int nq_launch_tc_gemm(const void* a_dec, const void* w_dec, int64_t m, int64_t n, int64_t k, void* out,
                       int out_dtype, void* status_word, void* partial, unsigned* counters, cudaStream_t stream) {
     TcParams p;
-    p.splits = (partial && counters) ? tc_splits(m, n, k) : 1;
+    p.splits = partial ? tc_splits(m, n, k) : 1;
     p.partial = reinterpret_cast<float*>(partial);
     p.counters = counters;
     p.m = (int)m; p.n = (int)n; p.k = (int)k;
@@ -357,5 +354,11 @@ int nq_launch_tc_gemm(const void* a_dec, const void* w_dec, int64_t m, int64_t n
     const int grid = total < sm_count() ? total : sm_count();
     nq_w4a4_tc_gemm_kernel<<<grid, kThreadsTc, smem, stream>>>(map_w, map_a, p);
     NQ_CHECK_LAUNCH("nq_w4a4_gemm(tcgen05)");
+    if (p.splits > 1) {
+        const int64_t quads = m * n / 4;  // n % 128 == 0
+        nq_tc_splitk_reduce_kernel<<<(unsigned)((quads + 255) / 256), 256, 0, stream>>>(
+            reinterpret_cast<const float4*>(p.partial), p.splits, quads, out, p.out_bf16);
+        NQ_CHECK_LAUNCH("nq_w4a4_gemm(split-K reduce)");
+    }
     return NQ_OK;
 }
