@@ -211,6 +211,8 @@ def run_gpu(args) -> None:
     if distributed:
         import torch.distributed as dist
 
+        # NCCL's banner / debug lines must not land on stdout next to the JSON line
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=device)
     import nestquant_aiinfra_b200.runtime as rt
     from nestquant_aiinfra_b200.fused_linear import FusedNQRTLinear
@@ -239,11 +241,11 @@ def run_gpu(args) -> None:
             dist.barrier()
         torch.cuda.synchronize(device)
 
+    sampler = ClockSampler(local_rank)  # samples from the warm-up on, so the timed region is always covered
+    sampler.start()
     for _ in range(max(args.warmup, 3)):
         step(False)
     barrier()
-    sampler = ClockSampler(local_rank)
-    sampler.start()
     launches0 = rt.launch_count()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()

@@ -1,0 +1,107 @@
+"""Parity at the benchmark's full sizes through size-independent properties.
+
+The CPU checker would need minutes at these sizes, so the tests use properties that pin the result
+without it: two independent kernels must agree bit for bit (encoder reconstruction vs decode of the
+emitted streams; weight encode -> decode -> encode idempotence), the tensor-core GEMM must match a
+float32 product of the same BF16 operands, and sampled rows are still checked against the checker.
+"""
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import ACT_BETAS, MAX_ABS_TOL, REL_FRO_TOL, W_BETAS, max_abs, rel_fro, rng
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def rt():
+    import nestquant_aiinfra_b200.runtime as runtime
+
+    return runtime
+
+
+@pytest.mark.parametrize("m,k", [(8192, 2048), (8192, 8192)])
+def test_full_size_encode_streams(rt, oracle, m, k):
+    from nestquant_aiinfra_b200.rotation import hadamard
+
+    x = hadamard(torch.randn(m, k, generator=rng(2000 + m)).bfloat16().cuda())
+    act = rt.quantize_activation_cuda(x, q=14, betas=ACT_BETAS)
+    # (1) the BF16 reconstruction written by the encoder == decode kernel applied to the emitted streams
+    assert torch.equal(act.decoded, rt.decode_packed_a4(act, dtype=torch.bfloat16))
+    # (2) every code is a valid residue (< 14) and norms are finite and positive
+    codes = act.code_payload
+    assert int(((codes & 15) >= 14).sum()) == 0 and int(((codes >> 4) >= 14).sum()) == 0
+    assert bool(torch.isfinite(act.row_norms).all()) and float(act.row_norms.min()) > 0
+    # (3) deterministic: a second launch reproduces the streams bit for bit
+    again = rt.quantize_activation_cuda(x, q=14, betas=ACT_BETAS)
+    assert torch.equal(again.code_payload, act.code_payload) and torch.equal(again.beta_payload, act.beta_payload)
+    # (4) sampled rows against the CPU checker (first, last, a few in between)
+    rows = [0, 1, m // 3, m // 2 + 1, m - 2, m - 1]
+    sample = x[rows].float().cpu().numpy()
+    ec, eb, en = oracle.encode_packed(sample, ACT_BETAS)
+    got_codes = act.code_payload.view(m, k // 2)[rows].cpu().numpy().reshape(-1)
+    got_betas = act.beta_payload.view(m, k // 32)[rows].cpu().numpy().reshape(-1)
+    assert np.array_equal(got_codes, ec) and np.array_equal(got_betas, eb)
+    assert np.array_equal(act.row_norms[rows].cpu().numpy(), en)
+
+
+def test_full_size_weight_encode_is_idempotent(rt, oracle):
+    """encode(decode(encode(W))) == encode(W) up to the fixed point: the float32 reconstruction of a
+    dithered encode re-encodes to the same codes; sampled rows match the checker."""
+    n, k, seed = 8192, 2048, 20261031
+    from nestquant_aiinfra_b200.rotation import hadamard
+
+    w = hadamard((0.02 * torch.randn(n, k, generator=rng(1002))).cuda())
+    first = rt.quantize_weight_cuda(w, betas=W_BETAS, dither_seed=seed)
+    rows = [0, 17, n // 2, n - 1]
+    for r in rows:  # the dither counter is global: row r starts at block r * k / 8
+        ec, eb, en = oracle.encode_packed(w[r:r + 1].cpu().numpy(), W_BETAS, seed=seed, block_offset=r * (k // 8))
+        assert np.array_equal(first.code_payload.view(n, k // 2)[r].cpu().numpy(), ec)
+        assert np.array_equal(first.beta_payload.view(n, k // 32)[r].cpu().numpy(), eb)
+        assert np.array_equal(first.row_norms[r:r + 1].cpu().numpy(), en)
+    decoded = rt.decode_packed_weight(first)
+    assert bool(torch.isfinite(decoded.float()).all())
+    rel = float((decoded.float() - w).norm() / w.norm())
+    assert 0.01 < rel < 0.2, rel  # 4.25-bit reconstruction error of a Gaussian matrix
+
+
+@pytest.mark.parametrize("m,n,k", [(8192, 8192, 2048), (8192, 2048, 8192), (2048, 512, 2048)])
+def test_full_size_tensor_core_gemm_matches_float32_product(rt, m, n, k):
+    a = (torch.randn(m, k, generator=rng(m + 1)) * 0.7).bfloat16().cuda()
+    w = (torch.randn(n, k, generator=rng(n + 2)) * 0.02).bfloat16().cuda()
+    out = rt.gemm_bf16_tc(a, w, out_dtype=torch.float32)
+    assert rt.read_status() == 0
+    previous = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        expected = a.float() @ w.float().T  # plain float32 reference of the same BF16 operands
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = previous
+    err = float((out - expected).abs().max())
+    fro = float((out - expected).norm() / expected.norm())
+    assert err <= MAX_ABS_TOL and fro <= REL_FRO_TOL, (err, fro)
+
+
+def test_full_size_projection_tails_and_paths_agree(rt, oracle):
+    """The same packed operands through the tensor path (M = 520, ragged tail) and row by row through
+    the CUDA-core path (M = 1 calls) give the same projection within the accumulation tolerance."""
+    from dataclasses import replace
+
+    from helpers import make_weight_record
+
+    n, k, m = 2048, 2048, 520
+    record, _ = make_weight_record(oracle, n, k, seed=31, dither_seed=32)
+    weight = rt.prepare_fused_linear(record)
+    x = torch.randn(m, k, generator=rng(33)).bfloat16().cuda()
+    act = rt.quantize_activation_cuda(x, q=14, betas=ACT_BETAS)
+    full = rt.linear_packed_w4a4_fp32(act, weight).cpu().numpy()
+    rows = [0, 255, 256, 511, 512, 519]
+    for r in rows:
+        one = replace(act, code_payload=act.code_payload.view(m, -1)[r].contiguous(),
+                      beta_payload=act.beta_payload.view(m, -1)[r].contiguous(),
+                      row_norms=act.row_norms[r:r + 1].contiguous(), original_shape=(1, k),
+                      decoded=act.decoded[r:r + 1].contiguous())
+        single = rt.linear_packed_w4a4_fp32(one, weight).cpu().numpy()[0]
+        assert max_abs(single, full[r]) <= MAX_ABS_TOL and rel_fro(single, full[r]) <= REL_FRO_TOL
