@@ -545,17 +545,33 @@ def decode_workload(torch, device, *, requests: int = 64, new_tokens: int = 256)
             "prefill_tok_s": round(sum(lengths) / prefill_s, 1), "cuda_graph": True}
 
 
+def run_single_extra(args) -> None:
+    """One extra workload alone on GPU 0 (used for profiling captures)."""
+    import torch
+
+    import nestquant_aiinfra_b200.runtime as rt
+
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    result = kv_workload(torch, rt, device, peaks()) if args.workload == "kv" else decode_workload(torch, device)
+    print(json.dumps({"workload": args.workload, **result}), flush=True)
+
+
 def main() -> None:
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=5)
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", choices=("native", "reference"), default="native")
+    parser.add_argument("--workload", choices=("all", "kv", "decode"), default="all",
+                        help="all = sweep (+ extras); kv / decode = only that extra workload, for profiling")
     parser.add_argument("--skip-extras", action="store_true",
                         help="timed sweep only: no per-cell table, no end-to-end pass, no CPU baseline (profiling runs)")
     args = parser.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload != "all":
+        run_single_extra(args)
     else:
         run_gpu(args)
 
