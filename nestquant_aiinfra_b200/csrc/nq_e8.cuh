@@ -435,7 +435,11 @@ NQ_HD void nq_encode_block_fastpass(const float x[8], const float* beta, int& be
 #pragma unroll
         for (int j = 0; j < 8; ++j) r[j] = nq_mul(lam[j], bt);
         asif[b] = nq_sqdist8_seq(r, x);
-        const int cls = nq_e8_cell_class(lam);
+        // |lam|^2 <= 96 < (14/sqrt(2))^2 puts lam inside the inscribed ball of 14*V: no facet test needed
+        float norm2 = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) norm2 = nq_fma(lam[j], lam[j], norm2);
+        const int cls = norm2 <= 96.0f ? 1 : nq_e8_cell_class(lam);
         if (cls > 0) {
             if (best < 0 || asif[b] < best_err) {
                 best = b;

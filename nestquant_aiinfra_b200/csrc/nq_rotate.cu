@@ -19,40 +19,99 @@ template <> __device__ __forceinline__ float round_to<float>(float v) { return v
 template <> __device__ __forceinline__ float round_to<__nv_bfloat16>(float v) { return nq_bf16_round(v); }
 template <> __device__ __forceinline__ float round_to<__half>(float v) { return __half2float(__float2half_rn(v)); }
 
-template <typename T> __device__ __forceinline__ float load_as_float(const T* p, int64_t i);
-template <> __device__ __forceinline__ float load_as_float<float>(const float* p, int64_t i) { return p[i]; }
-template <> __device__ __forceinline__ float load_as_float<__nv_bfloat16>(const __nv_bfloat16* p, int64_t i) { return __bfloat162float(p[i]); }
-template <> __device__ __forceinline__ float load_as_float<__half>(const __half* p, int64_t i) { return __half2float(p[i]); }
+// store 8 consecutive results (16-byte aligned) in the tensor dtype
+template <typename T> __device__ __forceinline__ void store8(T* p, const float v[8]);
+template <> __device__ __forceinline__ void store8<float>(float* p, const float v[8]) {
+    reinterpret_cast<float4*>(p)[0] = make_float4(v[0], v[1], v[2], v[3]);
+    reinterpret_cast<float4*>(p)[1] = make_float4(v[4], v[5], v[6], v[7]);
+}
+template <> __device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16* p, const float v[8]) {
+    *reinterpret_cast<uint4*>(p) = nq_pack_bf16x8(v);
+}
+template <> __device__ __forceinline__ void store8<__half>(__half* p, const float v[8]) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+        w[i] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+}
 
-template <typename T> __device__ __forceinline__ void store_from_float(T* p, int64_t i, float v);
-template <> __device__ __forceinline__ void store_from_float<float>(float* p, int64_t i, float v) { p[i] = v; }
-template <> __device__ __forceinline__ void store_from_float<__nv_bfloat16>(__nv_bfloat16* p, int64_t i, float v) { p[i] = __float2bfloat16_rn(v); }
-template <> __device__ __forceinline__ void store_from_float<__half>(__half* p, int64_t i, float v) { p[i] = __float2half_rn(v); }
+
+// Radix-8 passes: a thread takes 8 elements spaced `w` apart, runs three butterfly stages
+// (widths w, 2w, 4w -- exactly the reference's stage order, every result rounded to the
+// tensor dtype) in registers and writes them back, so a row needs log2(n)/3 shared-memory
+// round trips instead of log2(n).  The first pass reads its 8 consecutive elements straight
+// from global memory, the last pass applies the 1/sqrt(n) division and stores to global.
+template <typename T, int STAGES>
+__device__ __forceinline__ void butterflies(float v[8]) {
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) {
+        const int h = 1 << s;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            if ((j & h) == 0) {
+                const float l = v[j], r = v[j | h];
+                v[j] = round_to<T>(nq_add(l, r));
+                v[j | h] = round_to<T>(nq_sub(l, r));
+            }
+        }
+    }
+}
 
 template <typename T>
 __global__ void __launch_bounds__(256)
 nq_hadamard_kernel(const T* __restrict__ x, T* __restrict__ out, int64_t rows, int n, int rows_per_cta,
                    float root, float inv_root) {
-    extern __shared__ float buf[];
+    extern __shared__ __align__(16) float buf[];
     const int64_t row0 = (int64_t)blockIdx.x * rows_per_cta;
     const int nrows = (int)min((int64_t)rows_per_cta, rows - row0);
-    const int total = nrows * n;
-    for (int i = threadIdx.x; i < total; i += 256) buf[i] = load_as_float<T>(x, row0 * n + i);
+    const int total = nrows * n;           // elements of this CTA (rows are independent, n >= 8)
+    const int groups = total >> 3;
+    int log_n = 0;
+    while ((1 << log_n) < n) ++log_n;
+
+    // pass 0: widths 1, 2, 4 on 8 consecutive elements loaded from global memory
+    for (int g = threadIdx.x; g < groups; g += 256) {
+        float v[8];
+        nq_load8<T>(x + row0 * n + (int64_t)g * 8, v);
+        butterflies<T, 3>(v);
+        float4* dst = reinterpret_cast<float4*>(buf + g * 8);
+        dst[0] = make_float4(v[0], v[1], v[2], v[3]);
+        dst[1] = make_float4(v[4], v[5], v[6], v[7]);
+    }
     __syncthreads();
-    const int pairs = total >> 1, half_n = n >> 1;
-    for (int w = 1; w < n; w <<= 1) {
-        for (int p = threadIdx.x; p < pairs; p += 256) {
-            const int r = p / half_n, q = p - r * half_n;
-            const int g = q / w, i = q - g * w;
-            const int a = r * n + g * 2 * w + i, b = a + w;
-            const float l = buf[a], rr = buf[b];
-            buf[a] = round_to<T>(nq_add(l, rr));
-            buf[b] = round_to<T>(nq_sub(l, rr));
+    int done = 3;
+    while (done < log_n) {
+        const int stages = min(3, log_n - done);
+        const int w = 1 << done;               // spacing of the elements a thread combines
+        const int span = w << stages;          // elements covered by one group family
+        const int per = 1 << stages;           // elements per thread in this pass
+        const int work = total >> stages;
+        for (int t = threadIdx.x; t < work; t += 256) {
+            const int base = (t / w) * span + (t % w);
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = j < per ? buf[base + j * w] : 0.0f;
+            if (stages == 3) butterflies<T, 3>(v);
+            else if (stages == 2) butterflies<T, 2>(v);
+            else butterflies<T, 1>(v);
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (j < per) buf[base + j * w] = v[j];
         }
         __syncthreads();
+        done += stages;
     }
-    for (int i = threadIdx.x; i < total; i += 256)
-        store_from_float<T>(out, row0 * n + i, nq_div_by(buf[i], root, inv_root));
+    for (int g = threadIdx.x; g < groups; g += 256) {
+        const float4 lo = reinterpret_cast<const float4*>(buf + g * 8)[0];
+        const float4 hi = reinterpret_cast<const float4*>(buf + g * 8)[1];
+        float v[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = nq_div_by(v[j], root, inv_root);
+        store8<T>(out + row0 * n + (int64_t)g * 8, v);
+    }
 }
 
 template <typename T>
@@ -79,8 +138,9 @@ int launch_hadamard(const void* x, void* out, int64_t rows, int64_t n, cudaStrea
 
 extern "C" int nq_hadamard(const void* x, void* out, int dtype, int64_t rows, int64_t n, nq_stream_t stream) {
     NQ_REQUIRE(x && out, NQ_ERR_ARG, "nq_hadamard: null pointer");
-    NQ_REQUIRE(rows >= 1 && n >= 2 && n <= 32768 && (n & (n - 1)) == 0, NQ_ERR_ARG,
-               "nq_hadamard: n=%lld must be a power of two in [2, 32768]", (long long)n);
+    NQ_REQUIRE(rows >= 1 && n >= 8 && n <= 32768 && (n & (n - 1)) == 0, NQ_ERR_ARG,
+               "nq_hadamard: n=%lld must be a power of two in [8, 32768]", (long long)n);
+    NQ_REQUIRE(nq_aligned16(x) && nq_aligned16(out), NQ_ERR_ALIGN, "nq_hadamard: 16-byte alignment required");
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     switch (dtype) {
         case NQ_F32: return launch_hadamard<float>(x, out, rows, n, s);
