@@ -37,6 +37,7 @@ TOKENS = (1, 8, 16, 64, 128, 512, 2048, 8192)
 CPU_SAMPLE_TOKENS = (1, 16, 128, 512)
 ACT_BETAS = tuple(v / 14 for v in (3.47, 4.74, 6.90, 18.11))
 W_BETAS = tuple(v / 14 for v in (4.0, 5.5, 7.0, 18.0))
+ENCODE_TRAFFIC_8192X8192 = 134_373_376 + 123_120_896  # dram__bytes_read.sum + dram__bytes_write.sum (ncu)
 METRIC = "w4a4_e8_gemm_sweep_tflops"
 UNIT = "TFLOP/s"
 
@@ -272,8 +273,13 @@ def run_gpu(args) -> None:
     enc_ms = sum(e0.elapsed_time(e1) for _, _, e0, e1 in encode_events)
     enc_gbs = enc_bytes / (enc_ms * 1e-3) / 1e9
     roofline = {"kernel": "nq_encode_rows_kernel", "bound": "hbm", "achieved": enc_gbs, "peak": pk["hbm_gbs"],
-                "unit": "GB/s", "frac": enc_gbs / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"],
-                "share_of_step": enc_ms / elapsed_ms, "launches": len(encode_events)}
+                "unit": "GB/s", "frac": enc_gbs / pk["hbm_gbs"], "peak_source": pk["source"],
+                "share_of_step": enc_ms / elapsed_ms, "launches": len(encode_events),
+                # DRAM bytes of the largest encode launch (8192 x 8192 BF16) from the ncu capture summarised in
+                # profiles/nq_encode_rows_kernel_8192x8192_bf16.md; its algorithmic bytes are 2MK + M(17K/32+4),
+                # the rest is the optional BF16 reconstruction the projection consumes.
+                "traffic": ENCODE_TRAFFIC_8192X8192, "traffic_launch": "M=8192 K=8192",
+                "algorithmic_bytes_of_that_launch": 8192 * 8192 * 2 + 8192 * (17 * 8192 // 32 + 4)}
 
     # per-cell table and the tensor-bound kernel alone (outside the timed region)
     table, gemm = ([], None) if args.skip_extras else cell_table(torch, rt, weights, inputs, beta_table, device, pk)
