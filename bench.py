@@ -551,6 +551,78 @@ def decode_workload(torch, device, *, requests: int = 64, new_tokens: int = 256)
             "prefill_tok_s": round(sum(lengths) / prefill_s, 1), "cuda_graph": True}
 
 
+def run_tp70b(args) -> None:
+    """Config 4: Llama-3-70B architecture, random init, W4A4KV4, tensor parallel over the ranks of torchrun."""
+    import torch
+    import torch.distributed as dist
+
+    from nestquant_aiinfra_b200.tp_engine import TensorParallelRunner, build_llama_tp_shard, fill_cache_synthetic
+
+    rank, local_rank = int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    steps = max(args.steps, 1)
+    t0 = time.perf_counter()
+    model, cache = build_llama_tp_shard(hidden_size=8192, intermediate_size=28672, num_layers=args.tp_layers,
+                                        num_heads=64, num_kv_heads=8, head_dim=128, vocab_size=128256, rank=rank,
+                                        world=world, capacity=args.tp_batch,
+                                        max_cache_len=args.tp_context + steps + max(args.warmup, 3) + 32, device=device)
+    fill_cache_synthetic(cache, args.tp_context)
+    runner = TensorParallelRunner(model, cache)
+    runner.start_decode(args.tp_context)
+    torch.cuda.synchronize(device)
+    build_s = time.perf_counter() - t0
+    graph = True
+    try:
+        runner.capture_decode_graph()
+    except Exception as error:  # collectives inside a capture are not available everywhere
+        graph = f"eager ({type(error).__name__})"
+        runner.graph = None
+        runner.cache.set_decode_state()
+    for _ in range(max(args.warmup, 3)):
+        runner.decode()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize(device)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        runner.decode()
+    e1.record()
+    torch.cuda.synchronize(device)
+    ms = torch.tensor([e0.elapsed_time(e1) / steps], device=device)
+    tokens = runner.next_tokens.clone()
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        reference = tokens.clone()
+        dist.broadcast(reference, src=0)
+        same = torch.tensor([int(torch.equal(reference, tokens))], device=device)
+        dist.all_reduce(same, op=dist.ReduceOp.MIN)
+    else:
+        same = torch.tensor([1])
+    if rank == 0:
+        ms_step = float(ms.item())
+        packed = sum(m.packed_device_bytes for m in model.modules() if hasattr(m, "packed_device_bytes"))
+        print(json.dumps({
+            "metric": "w4a4kv4_tp_decode_tok_s", "value": args.tp_batch / (ms_step * 1e-3), "unit": "tok/s",
+            "n_gpus": world, "steps": steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
+            "higher_is_better": True, "scaling": "strong", "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "llama-3-70b-arch W4A4KV4 tensor-parallel decode", "layers": args.tp_layers,
+                       "batch": args.tp_batch, "context": args.tp_context, "parallelism": f"tp{world}",
+                       "all_reduce": "NCCL after o_proj and down_proj", "cuda_graph": graph,
+                       "kv": "pages pre-filled by the page encoder with synthetic K/V"},
+            "packed_weight_bytes_per_rank": int(packed), "build_s": round(build_s, 1),
+            "ranks_agree_on_tokens": bool(same.item()),
+        }), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def run_single_extra(args) -> None:
     """One extra workload alone on GPU 0 (used for profiling captures)."""
     import torch
@@ -569,13 +641,19 @@ def main() -> None:
     parser.add_argument("--steps", type=int, default=5)
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", choices=("native", "reference"), default="native")
-    parser.add_argument("--workload", choices=("all", "kv", "decode"), default="all",
-                        help="all = sweep (+ extras); kv / decode = only that extra workload, for profiling")
+    parser.add_argument("--workload", choices=("all", "kv", "decode", "tp70b"), default="all",
+                        help="all = sweep (+ extras); kv / decode = only that extra workload, for profiling; "
+                             "tp70b = Llama-3-70B-architecture tensor-parallel decode (run under torchrun)")
+    parser.add_argument("--tp-layers", type=int, default=80, help="decoder layers of the tp70b workload")
+    parser.add_argument("--tp-batch", type=int, default=128)
+    parser.add_argument("--tp-context", type=int, default=4096)
     parser.add_argument("--skip-extras", action="store_true",
                         help="timed sweep only: no per-cell table, no end-to-end pass, no CPU baseline (profiling runs)")
     args = parser.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "tp70b":
+        run_tp70b(args)
     elif args.workload != "all":
         run_single_extra(args)
     else:

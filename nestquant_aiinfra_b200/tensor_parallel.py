@@ -112,6 +112,10 @@ class RowParallelNQRTLinear(nn.Module):
             prepared = quantize_weight_cuda(rotated, betas=weight_betas, dither_seed=dither_seed)
             self.inner = FusedNQRTLinear(prepared, input_hadamard=False, activation_betas=tuple(activation_betas))
 
+    @property
+    def packed_device_bytes(self) -> int:
+        return 0 if self.inner is None else self.inner.packed_device_bytes
+
     def forward(self, x_slice: torch.Tensor) -> torch.Tensor:
         if x_slice.shape[-1] != self.in_features:
             raise ValueError(f"input feature dimension {x_slice.shape[-1]} does not match the shard {self.in_features}")

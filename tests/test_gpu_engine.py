@@ -103,3 +103,26 @@ def test_released_slot_is_reused_and_inactive_rows_do_not_move():
     assert cache.layer_caches[0].sequence_lengths.tolist() == [0, 5, 0, 19]
     with pytest.raises(RuntimeError):
         cache.register("again", slot=3)
+
+
+def test_tp_shard_runs_single_rank():
+    """world = 1 shard of a tiny architecture: row-parallel modules, synthetic KV fill, graph decode."""
+    from nestquant_aiinfra_b200.tensor_parallel import RowParallelNQRTLinear
+    from nestquant_aiinfra_b200.tp_engine import TensorParallelRunner, build_llama_tp_shard, fill_cache_synthetic
+
+    model, cache = build_llama_tp_shard(hidden_size=256, intermediate_size=7 * 64, num_layers=2, num_heads=4,
+                                        num_kv_heads=2, head_dim=64, vocab_size=512, rank=0, world=1, capacity=3,
+                                        max_cache_len=96, device="cuda")
+    rows = [m for m in model.modules() if isinstance(m, RowParallelNQRTLinear)]
+    assert len(rows) == 4 and {m.hadamard_block for m in rows} == {256, 64}   # 448 = 7 * 64
+    fill_cache_synthetic(cache, 37)
+    assert cache.layer_caches[1].page_counts.tolist() == [2, 2, 2] and cache.layer_caches[1].hot_lengths.tolist() == [5, 5, 5]
+    runner = TensorParallelRunner(model, cache)
+    runner.start_decode(37)
+    eager = [runner.decode_eager().clone() for _ in range(3)]
+    fill_cache_synthetic(cache, 37)
+    runner.start_decode(37)
+    runner.capture_decode_graph()
+    graph = [runner.decode().clone() for _ in range(3)]
+    assert all(torch.equal(a, b) for a, b in zip(eager, graph))
+    assert cache.layer_caches[0].sequence_lengths.tolist() == [40, 40, 40]
