@@ -606,7 +606,9 @@ def run_tp70b(args) -> None:
         same = torch.tensor([1])
     if rank == 0:
         ms_step = float(ms.item())
-        packed = sum(m.packed_device_bytes for m in model.modules() if hasattr(m, "packed_device_bytes"))
+        from nestquant_aiinfra_b200.fused_linear import FusedNQRTLinear
+
+        packed = sum(m.packed_device_bytes for m in model.modules() if isinstance(m, FusedNQRTLinear))
         print(json.dumps({
             "metric": "w4a4kv4_tp_decode_tok_s", "value": args.tp_batch / (ms_step * 1e-3), "unit": "tok/s",
             "n_gpus": world, "steps": steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
