@@ -226,7 +226,7 @@ int nq_kv_attention(const void* query, int q_dtype, int batch, int q_tokens, int
 
 /* -------------------------------------------------------------------------
  * Normalised Sylvester Hadamard along the last axis of a contiguous [rows, n]
- * tensor, n a power of two <= 32768, computed in the tensor's dtype exactly as
+ * tensor, n a power of two in [8, 32768], computed in the tensor's dtype exactly as
  * hadamard() does (core/rotation.py:12-27): every butterfly stage rounded to
  * the dtype, final IEEE division by float32(sqrt(n)).  x may equal out. */
 int nq_hadamard(const void* x, void* out, int dtype, int64_t rows, int64_t n, nq_stream_t stream);

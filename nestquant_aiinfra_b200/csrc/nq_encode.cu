@@ -30,7 +30,7 @@ extern "C" int nq_abi_version(void) { return 1; }
 // Encoder kernel: one CTA per group of rows (see nq_encode_core.cuh).
 // ---------------------------------------------------------------------------
 template <typename T>
-__global__ void __launch_bounds__(256, 3)
+__global__ void __launch_bounds__(NQ_ENC_THREADS, 5)
 nq_encode_rows_kernel(const T* __restrict__ x, int64_t rows, int k, int64_t row_stride,
                       const float* __restrict__ beta_table, float sqrt_k,
                       uint32_t* __restrict__ codes, uint8_t* __restrict__ beta_ids,
@@ -112,7 +112,7 @@ static int launch_encode(const void* x, int64_t rows, int64_t k, int64_t row_str
         }
     }
     const int64_t grid = (rows + rpc - 1) / rpc;
-    kernel<<<(unsigned)grid, 256, smem, stream>>>(
+    kernel<<<(unsigned)grid, NQ_ENC_THREADS, smem, stream>>>(
         reinterpret_cast<const T*>(x), rows, (int)k, row_stride, beta_table,
         (float)sqrt((double)k), reinterpret_cast<uint32_t*>(out_codes), out_beta_ids, out_norms,
         reinterpret_cast<__nv_bfloat16*>(out_decoded), use_dither, counter_base);

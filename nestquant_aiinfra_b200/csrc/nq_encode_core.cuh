@@ -1,6 +1,7 @@
 // Row encoder shared by the activation / weight encoder and the KV page
-// writers.  One CTA of 256 threads owns `nrows` consecutive rows of k features
-// (256 / (k/8) rows for short rows, one row otherwise).
+// writers.  One CTA of NQ_ENC_THREADS threads owns `nrows` consecutive rows of k features
+// (NQ_ENC_THREADS / (k/8) rows for short rows, one row otherwise).  Small CTAs (six per SM)
+// keep other CTAs issuing while one waits at a barrier of its compaction rounds.
 //   phase 1  every thread squares its blocks into shared memory
 //   phase 2  8 threads per row run the reference's 8-lane strided accumulation
 //            (the order PyTorch's CPU vector_norm uses; it decides the last
@@ -13,17 +14,21 @@
 
 #include "nq_common.cuh"
 
-// Staging area of the compacted slow path (per CTA of 256 threads): normalised blocks,
-// per-(thread, beta) results of the full evaluation, the work queue and its counter.
-#define NQ_ENCODE_STAGE_FLOATS (256 * 8 + 1024 + 1024 + 256 * 4 * 4 + 512 + 4 + 4 /* alignment slack */)
+#define NQ_ENC_THREADS 128
+// Staging area of the compacted slow path (per CTA): normalised blocks, per-(thread, beta) results
+// of the full evaluation, the work queue and its counter.  It ALIASES the squares buffer of the
+// norm phase, which is dead once the row scales are known.
+#define NQ_ENCODE_STAGE_FLOATS (NQ_ENC_THREADS * 8 + NQ_ENC_THREADS * 4 * 2 + NQ_ENC_THREADS * 4 * 4 + NQ_ENC_THREADS * 2 + 4)
 
 __host__ __device__ inline int nq_encode_rows_per_cta(int k) {
     const int bpr = k / 8;
-    return bpr >= 256 ? 1 : 256 / bpr;
+    return bpr >= NQ_ENC_THREADS ? 1 : NQ_ENC_THREADS / bpr;
 }
 __host__ __device__ inline size_t nq_encode_smem_floats(int k) {
     const int rpc = nq_encode_rows_per_cta(k);
-    return (size_t)rpc * (k + 8) + (size_t)rpc * 10 + NQ_ENCODE_STAGE_FLOATS;
+    const size_t squares = (size_t)rpc * (k + 8);
+    const size_t body = squares > (size_t)NQ_ENCODE_STAGE_FLOATS ? squares : (size_t)NQ_ENCODE_STAGE_FLOATS;
+    return body + (size_t)rpc * 10 + 4;
 }
 
 template <typename T>
@@ -35,14 +40,15 @@ __device__ __forceinline__ void nq_encode_rows_cta(
     const int rows_per_cta = nq_encode_rows_per_cta(k);
     const int bpr = k >> 3;
     const int pitch = k + 8;  // de-conflicts the strided chain reads of neighbouring rows
-    float* sq = smem;
-    float* partial = smem + (size_t)rows_per_cta * pitch;
+    float* partial = smem;
     float* scale = partial + rows_per_cta * 8;
     float* dscale = scale + rows_per_cta;
+    // 16-byte aligned body: squares during the norm phase, staging arrays afterwards
+    float* sq = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(dscale + rows_per_cta) + 15) & ~(uintptr_t)15);
     const int tid = threadIdx.x;
     const int nblocks = nrows * bpr;
 
-    for (int b = tid; b < nblocks; b += 256) {
+    for (int b = tid; b < nblocks; b += NQ_ENC_THREADS) {
         const int r = b / bpr, bb = b - r * bpr;
         float v[8];
         if (r < valid_rows) {
@@ -59,7 +65,7 @@ __device__ __forceinline__ void nq_encode_rows_cta(
     }
     __syncthreads();
 
-    for (int t = tid; t < nrows * 8; t += 256) {
+    for (int t = tid; t < nrows * 8; t += NQ_ENC_THREADS) {
         const int r = t >> 3, l = t & 7;
         const float* p = sq + (size_t)r * pitch + l;
         float acc = 0.0f;
@@ -69,7 +75,7 @@ __device__ __forceinline__ void nq_encode_rows_cta(
     }
     __syncthreads();
 
-    for (int t = tid; t < nrows; t += 256) {
+    for (int t = tid; t < nrows; t += NQ_ENC_THREADS) {
         float total = partial[t * 8];
 #pragma unroll
         for (int l = 1; l < 8; ++l) total = nq_add(total, partial[t * 8 + l]);
@@ -84,7 +90,7 @@ __device__ __forceinline__ void nq_encode_rows_cta(
     const int padded = (nblocks + 31) & ~31;
     if (use_dither) {
         // weights: straight per-thread search with the subtractive dither of the global block
-        for (int b = tid; b < padded; b += 256) {
+        for (int b = tid; b < padded; b += NQ_ENC_THREADS) {
             const bool valid = b < nblocks;
             int bid = 0;
             if (valid) {
@@ -120,15 +126,15 @@ __device__ __forceinline__ void nq_encode_rows_cta(
     // Undithered rows (activations, K/V): every thread classifies its four candidates with the
     // cheap exact tests; the few (thread, beta) pairs that need the full evaluation are queued in
     // shared memory and evaluated densely by the whole CTA, so no warp idles behind one slow lane.
-    // 16-byte aligned: the staging arrays are accessed with 128-bit loads and stores
-    float* stage = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(dscale + rows_per_cta) + 15) & ~(uintptr_t)15);
-    float* xs = stage;                                             // [256][8] normalised blocks
-    float* res_err = xs + 256 * 8;                                 // [256][4]
-    uint32_t* res_word = reinterpret_cast<uint32_t*>(res_err + 1024);  // [256][4]
-    uint4* res_dec = reinterpret_cast<uint4*>(res_word + 1024);    // [256][4] scaled BF16 reconstruction
-    unsigned short* queue = reinterpret_cast<unsigned short*>(res_dec + 1024);  // [1024] (thread << 2) | beta
-    unsigned* queue_count = reinterpret_cast<unsigned*>(queue + 1024);
-    for (int base = 0; base < padded; base += 256) {
+    float* stage = sq;  // the squares are dead: every row scale has been computed (barrier above)
+    constexpr int NT = NQ_ENC_THREADS;
+    float* xs = stage;                                                    // [NT][8] normalised blocks
+    uint4* res_dec = reinterpret_cast<uint4*>(xs + NT * 8);               // [NT][4] scaled BF16 reconstruction
+    float* res_err = reinterpret_cast<float*>(res_dec + NT * 4);          // [NT][4]
+    uint32_t* res_word = reinterpret_cast<uint32_t*>(res_err + NT * 4);   // [NT][4]
+    unsigned short* queue = reinterpret_cast<unsigned short*>(res_word + NT * 4);  // [4 NT] (thread << 2) | beta
+    unsigned* queue_count = reinterpret_cast<unsigned*>(queue + NT * 4);
+    for (int base = 0; base < padded; base += NQ_ENC_THREADS) {
         const int b = base + tid;
         const bool valid = b < nblocks;
         if (tid == 0) *queue_count = 0u;
@@ -159,7 +165,7 @@ __device__ __forceinline__ void nq_encode_rows_cta(
         }
         __syncthreads();
         const int items = (int)*queue_count;
-        for (int it = tid; it < items; it += 256) {
+        for (int it = tid; it < items; it += NQ_ENC_THREADS) {
             const int owner = queue[it] >> 2, c = queue[it] & 3;
             float v[8], r[8], err;
             const float4 lo = reinterpret_cast<const float4*>(xs + owner * 8)[0];

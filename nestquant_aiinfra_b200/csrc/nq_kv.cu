@@ -99,7 +99,7 @@ struct PackParams {
 };
 
 template <typename T>
-__global__ void __launch_bounds__(256) nq_kv_pack_pages_kernel(const PackParams p) {
+__global__ void __launch_bounds__(NQ_ENC_THREADS, 5) nq_kv_pack_pages_kernel(const PackParams p) {
     extern __shared__ __align__(16) float smem[];
     const int slot = blockIdx.x;
     const bool full = p.boundary_mask[slot] != 0 && p.hot_lengths[slot] == p.page_size;
@@ -144,7 +144,7 @@ struct PageParams {
 };
 
 template <typename T>
-__global__ void __launch_bounds__(256) nq_kv_quantize_page_kernel(const PageParams p) {
+__global__ void __launch_bounds__(NQ_ENC_THREADS, 5) nq_kv_quantize_page_kernel(const PageParams p) {
     extern __shared__ __align__(16) float smem[];
     const int is_value = blockIdx.x / p.ctas_per_stream;
     const int chunk = blockIdx.x - is_value * p.ctas_per_stream;
@@ -246,11 +246,11 @@ extern "C" int nq_kv_pack_publish(const void* hot_keys, const void* hot_values, 
     if (kv_dtype == NQ_BF16) {
         int rc = set_smem(nq_kv_pack_pages_kernel<__nv_bfloat16>, smem, "nq_kv_pack_publish");
         if (rc) return rc;
-        nq_kv_pack_pages_kernel<__nv_bfloat16><<<grid, 256, smem, s>>>(p);
+        nq_kv_pack_pages_kernel<__nv_bfloat16><<<grid, NQ_ENC_THREADS, smem, s>>>(p);
     } else {
         int rc = set_smem(nq_kv_pack_pages_kernel<__half>, smem, "nq_kv_pack_publish");
         if (rc) return rc;
-        nq_kv_pack_pages_kernel<__half><<<grid, 256, smem, s>>>(p);
+        nq_kv_pack_pages_kernel<__half><<<grid, NQ_ENC_THREADS, smem, s>>>(p);
     }
     NQ_CHECK_LAUNCH("nq_kv_pack_publish(pack)");
     nq_kv_publish_kernel<<<(max_sequences + 255) / 256, 256, 0, s>>>(p);
@@ -284,15 +284,15 @@ extern "C" int nq_kv_quantize_page(const void* key, const void* value, int kv_dt
     switch (kv_dtype) {
         case NQ_BF16:
             if ((rc = set_smem(nq_kv_quantize_page_kernel<__nv_bfloat16>, smem, "nq_kv_quantize_page"))) return rc;
-            nq_kv_quantize_page_kernel<__nv_bfloat16><<<grid, 256, smem, s>>>(p);
+            nq_kv_quantize_page_kernel<__nv_bfloat16><<<grid, NQ_ENC_THREADS, smem, s>>>(p);
             break;
         case NQ_F16:
             if ((rc = set_smem(nq_kv_quantize_page_kernel<__half>, smem, "nq_kv_quantize_page"))) return rc;
-            nq_kv_quantize_page_kernel<__half><<<grid, 256, smem, s>>>(p);
+            nq_kv_quantize_page_kernel<__half><<<grid, NQ_ENC_THREADS, smem, s>>>(p);
             break;
         case NQ_F32:
             if ((rc = set_smem(nq_kv_quantize_page_kernel<float>, smem, "nq_kv_quantize_page"))) return rc;
-            nq_kv_quantize_page_kernel<float><<<grid, 256, smem, s>>>(p);
+            nq_kv_quantize_page_kernel<float><<<grid, NQ_ENC_THREADS, smem, s>>>(p);
             break;
         default:
             nq_set_error("nq_kv_quantize_page: unknown dtype %d", kv_dtype);
