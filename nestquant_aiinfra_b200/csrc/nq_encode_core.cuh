@@ -36,7 +36,8 @@ __device__ __forceinline__ void nq_encode_rows_cta(
     const T* __restrict__ x, int64_t row_stride, int nrows, int valid_rows, int k,
     const float* __restrict__ beta_table, float sqrt_k, uint32_t* __restrict__ codes,
     uint8_t* __restrict__ beta_ids, float* __restrict__ norms, __nv_bfloat16* __restrict__ decoded,
-    int use_dither, uint32_t counter_base, float* smem) {
+    int use_dither, uint32_t counter_base, float* smem, int blk_begin = 0, int blk_end = 0x7fffffff,
+    bool write_norms = true) {
     const int rows_per_cta = nq_encode_rows_per_cta(k);
     const int bpr = k >> 3;
     const int pitch = k + 8;  // de-conflicts the strided chain reads of neighbouring rows
@@ -80,18 +81,21 @@ __device__ __forceinline__ void nq_encode_rows_cta(
 #pragma unroll
         for (int l = 1; l < 8; ++l) total = nq_add(total, partial[t * 8 + l]);
         const float norm = nq_sqrt(total);
-        norms[t] = norm;
+        if (write_norms) norms[t] = norm;
         // sqrt(K)/norm is evaluated as reciprocal(norm) * sqrt(K) by the reference.
         scale[t] = norm > 0.0f ? nq_mul(nq_rcp(norm), sqrt_k) : 0.0f;
         dscale[t] = nq_div(norm, sqrt_k);
     }
     __syncthreads();
 
-    const int padded = (nblocks + 31) & ~31;
+    // Phase 3 covers blocks [blk_begin, blk_end) of the CTA's rows (a long row can be split over
+    // several CTAs, each recomputing the cheap norm); blk_begin is a multiple of the CTA size.
+    const int enc_end = min(nblocks, blk_end);
+    const int padded = blk_begin + ((max(enc_end - blk_begin, 0) + 31) & ~31);
     if (use_dither) {
         // weights: straight per-thread search with the subtractive dither of the global block
-        for (int b = tid; b < padded; b += NQ_ENC_THREADS) {
-            const bool valid = b < nblocks;
+        for (int b = blk_begin + tid; b < padded; b += NQ_ENC_THREADS) {
+            const bool valid = b < enc_end;
             int bid = 0;
             if (valid) {
                 const int r = b / bpr, bb = b - r * bpr;
@@ -134,9 +138,9 @@ __device__ __forceinline__ void nq_encode_rows_cta(
     uint32_t* res_word = reinterpret_cast<uint32_t*>(res_err + NT * 4);   // [NT][4]
     unsigned short* queue = reinterpret_cast<unsigned short*>(res_word + NT * 4);  // [4 NT] (thread << 2) | beta
     unsigned* queue_count = reinterpret_cast<unsigned*>(queue + NT * 4);
-    for (int base = 0; base < padded; base += NQ_ENC_THREADS) {
+    for (int base = blk_begin; base < padded; base += NQ_ENC_THREADS) {
         const int b = base + tid;
-        const bool valid = b < nblocks;
+        const bool valid = b < enc_end;
         if (tid == 0) *queue_count = 0u;
         __syncthreads();
         int best = 0, row_r = 0;
