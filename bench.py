@@ -621,8 +621,20 @@ def run_tp70b(args) -> None:
             "ranks_agree_on_tokens": bool(same.item()),
         }), flush=True)
     if world > 1:
+        # A live CUDA graph that captured NCCL kernels keeps the communicator busy: release it before
+        # the teardown, and bound the teardown so that a stuck finalize cannot hold the GPUs.
+        if isinstance(runner.graph, torch.cuda.CUDAGraph):
+            runner.graph.reset()
+        runner.graph = None
+        torch.cuda.synchronize(device)
         dist.barrier()
+        torch.cuda.synchronize(device)
+        sys.stdout.flush()
+        watchdog = threading.Timer(45.0, lambda: os._exit(0))
+        watchdog.daemon = True
+        watchdog.start()
         dist.destroy_process_group()
+        watchdog.cancel()
 
 
 def run_single_extra(args) -> None:

@@ -74,8 +74,13 @@ def build_llama_w4a4kv4(*, hidden_size: int, intermediate_size: int, num_layers:
                          tie_word_embeddings=False, attention_bias=False, mlp_bias=False)
     torch.manual_seed(seed)
     device = torch.device(device)
-    with torch.device(device):
-        model = LlamaForCausalLM(config).to(torch.bfloat16)
+    previous = torch.get_default_dtype()
+    torch.set_default_dtype(torch.bfloat16)  # create the parameters in BF16 (a 70B shard in FP32 would not fit)
+    try:
+        with torch.device(device):
+            model = LlamaForCausalLM(config).to(torch.bfloat16)
+    finally:
+        torch.set_default_dtype(previous)
     model.eval()
     quantize_llama_projections_(model)
     cache = BatchedNQKVLlamaCache(capacity=capacity, num_layers=num_layers, num_query_heads=num_heads,

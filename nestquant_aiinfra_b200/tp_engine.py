@@ -43,8 +43,13 @@ def build_llama_tp_shard(*, hidden_size: int, intermediate_size: int, num_layers
                          max_position_embeddings=max(max_cache_len, 2048), tie_word_embeddings=False,
                          attention_bias=False, mlp_bias=False)
     torch.manual_seed(seed)  # replicated tensors (embeddings, norms, lm_head) must agree across ranks
-    with torch.device(device):
-        model = LlamaForCausalLM(config).to(torch.bfloat16)
+    previous = torch.get_default_dtype()
+    torch.set_default_dtype(torch.bfloat16)  # create the parameters in BF16 (a 70B shard in FP32 would not fit)
+    try:
+        with torch.device(device):
+            model = LlamaForCausalLM(config).to(torch.bfloat16)
+    finally:
+        torch.set_default_dtype(previous)
     model.eval()
     for index, layer in enumerate(model.model.layers):
         caches = {}
