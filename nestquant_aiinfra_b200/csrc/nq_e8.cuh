@@ -465,6 +465,78 @@ NQ_HD void nq_encode_block_fastpass(const float x[8], const float* beta, int& be
     }
 }
 
+// Search key of a candidate: the rule "smallest error, first beta on ties" is the minimum of
+// (error bits << 8 | beta index); errors are sums of squares, so their bit patterns order like the values.
+NQ_HD unsigned long long nq_candidate_key(float err, int b) {
+    return ((unsigned long long)(uint32_t)nq_float_bits(err) << 8) | (unsigned)b;
+}
+
+// Full evaluation of one candidate whose lattice point lam = Q(x / beta) is already known:
+// codeword, reconstruction r (times beta) and error, bit-identical to nq_encode_candidate_exact.
+// Used for lattice points on the boundary of 14*V(E8), where the reduction modulo 14*E8 meets
+// exact ties -- the guarded search would fall back to the exact one anyway, so it is skipped.
+NQ_HD uint32_t nq_eval_candidate_from_lam(const float x[8], const float lam[8], float beta, float r[8], float& err) {
+    float t[8], s[8], n[8];
+    const uint32_t word = nq_lattice_to_codeword(lam);
+    nq_codeword_coset(word, t);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s[j] = nq_div_by(t[j], 14.0f, NQ_RCP14);
+    nq_e8_nearest_exact(s, n);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) r[j] = nq_mul(nq_fma(-14.0f, n[j], t[j]), beta);
+    err = nq_sqdist8_seq(r, x);
+    return word;
+}
+
+// Variant of nq_encode_block_fastpass for a caller with a work queue: every candidate whose
+// lattice point lies ON the boundary of 14*V(E8) is handed to on_boundary(b, lam) as soon as it
+// is found (unless a better finished candidate already rules it out), the caller evaluates it
+// with nq_eval_candidate_from_lam and merges by key.  `pending` only holds the rare candidates
+// strictly outside the cell that no finished candidate rules out; those take the generic
+// nq_encode_candidate_exact.  best / best_err / best_lam: best candidate strictly inside, or -1.
+template <class OnBoundary>
+NQ_HD void nq_encode_block_fastpass_push(const float x[8], const float* beta, int& best, float& best_err,
+                                         float best_lam[8], unsigned& pending, OnBoundary&& on_boundary) {
+    best = -1;
+    best_err = 0.0f;
+    pending = 0;
+    unsigned outside = 0;
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+        const float bt = beta[b], rbeta = nq_rcp(bt);
+        float y[8], lam[8], r[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) y[j] = nq_div_by(x[j], bt, rbeta);
+        nq_e8_nearest_guarded(y, lam);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) r[j] = nq_mul(lam[j], bt);
+        const float asif = nq_sqdist8_seq(r, x);
+        float norm2 = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) norm2 = nq_fma(lam[j], lam[j], norm2);
+        const int cls = norm2 <= 96.0f ? 1 : nq_e8_cell_class(lam);
+        if (cls > 0) {
+            if (best < 0 || asif < best_err) {
+                best = b;
+                best_err = asif;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) best_lam[j] = lam[j];
+            }
+        } else if (cls == 0) {
+            // its error is at least the as-if error: an earlier finished candidate below that wins anyway
+            if (!(best >= 0 && asif > best_err)) on_boundary(b, lam);
+        } else {
+            outside |= 1u << b;
+        }
+    }
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+        const float bt = beta[b];
+        // an outside candidate's true error exceeds 353*beta^2
+        if (((outside >> b) & 1u) && !(best >= 0 && 353.0f * bt * bt > best_err)) pending |= 1u << b;
+    }
+}
+
 // Merge rule of the search: smaller error wins, equal errors go to the smaller beta index.
 NQ_HD bool nq_candidate_wins(int b, float err, int best, float best_err) {
     return best < 0 || err < best_err || (err == best_err && b < best);

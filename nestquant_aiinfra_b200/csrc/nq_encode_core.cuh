@@ -1,31 +1,46 @@
 // Row encoder shared by the activation / weight encoder and the KV page
 // writers.  One CTA of NQ_ENC_THREADS threads owns `nrows` consecutive rows of k features
-// (NQ_ENC_THREADS / (k/8) rows for short rows, one row otherwise).  Small CTAs (six per SM)
-// keep other CTAs issuing while one waits at a barrier of its compaction rounds.
+// (NQ_ENC_THREADS / (k/8) rows for short rows, one or a few rows otherwise).  Small CTAs (five
+// per SM) keep other CTAs issuing while one waits at a barrier.
 //   phase 1  every thread squares its blocks into shared memory
 //   phase 2  8 threads per row run the reference's 8-lane strided accumulation
 //            (the order PyTorch's CPU vector_norm uses; it decides the last
 //            bit of the norm and therefore the emitted codes)
-//   phase 3  every thread runs the 4-beta search on its blocks and stores the
-//            codeword; beta ids of 4 neighbouring blocks are merged by shuffle.
+//   phase 3  every thread runs the 4-beta search on its blocks; codeword, optional BF16
+//            reconstruction and four 2-bit beta ids per byte are written out.
 // All pointers address the CTA's first row.  Rows >= valid_rows read as zero
 // (partially filled KV pages).  Shared memory: nq_encode_smem_floats() floats.
 #pragma once
 
 #include "nq_common.cuh"
 
+#ifndef NQ_ENC_THREADS
 #define NQ_ENC_THREADS 128
-// Staging area of the compacted slow path (per CTA): normalised blocks, per-(thread, beta) results
-// of the full evaluation, the work queue and its counter.  It ALIASES the squares buffer of the
+#endif
+#ifndef NQ_ENC_ROUNDS
+#define NQ_ENC_ROUNDS 4      /* rounds of NQ_ENC_THREADS blocks per batch of the undithered search */
+#endif
+#ifndef NQ_ENC_QUEUE_CAP
+#define NQ_ENC_QUEUE_CAP 256 /* queued boundary candidates per batch; overflow is evaluated in place */
+#endif
+// Batch results and the queue of the slow path (per CTA).  They ALIAS the squares buffer of the
 // norm phase, which is dead once the row scales are known.
-#define NQ_ENCODE_STAGE_FLOATS (NQ_ENC_THREADS * 8 + NQ_ENC_THREADS * 4 * 2 + NQ_ENC_THREADS * 4 * 4 + NQ_ENC_THREADS * 2 + 4)
+#define NQ_ENCODE_STAGE_FLOATS (NQ_ENC_THREADS * NQ_ENC_ROUNDS * (2 + 4 + 1) + NQ_ENC_QUEUE_CAP * (8 + 8 + 1) + 4)
+#define NQ_ENC_MAX_LAYOUT_FLOATS 8192 /* squares buffer of a CTA that takes several long rows */
 
+// Rows per CTA: short rows fill the CTA's threads once; long rows default to one per CTA and a
+// launch with many rows may ask for more (nq_encode_rows_per_cta_many) to fill the batches.
 __host__ __device__ inline int nq_encode_rows_per_cta(int k) {
     const int bpr = k / 8;
     return bpr >= NQ_ENC_THREADS ? 1 : NQ_ENC_THREADS / bpr;
 }
-__host__ __device__ inline size_t nq_encode_smem_floats(int k) {
-    const int rpc = nq_encode_rows_per_cta(k);
+__host__ __device__ inline int nq_encode_rows_per_cta_many(int k) {
+    const int base = nq_encode_rows_per_cta(k);
+    const int wide = NQ_ENC_MAX_LAYOUT_FLOATS / k;
+    return wide > base ? wide : base;
+}
+__host__ __device__ inline size_t nq_encode_smem_floats(int k, int rows_layout = 0) {
+    const int rpc = rows_layout > 0 ? rows_layout : nq_encode_rows_per_cta(k);
     const size_t squares = (size_t)rpc * (k + 8);
     const size_t body = squares > (size_t)NQ_ENCODE_STAGE_FLOATS ? squares : (size_t)NQ_ENCODE_STAGE_FLOATS;
     return body + (size_t)rpc * 10 + 4;
@@ -37,8 +52,8 @@ __device__ __forceinline__ void nq_encode_rows_cta(
     const float* __restrict__ beta_table, float sqrt_k, uint32_t* __restrict__ codes,
     uint8_t* __restrict__ beta_ids, float* __restrict__ norms, __nv_bfloat16* __restrict__ decoded,
     int use_dither, uint32_t counter_base, float* smem, int blk_begin = 0, int blk_end = 0x7fffffff,
-    bool write_norms = true) {
-    const int rows_per_cta = nq_encode_rows_per_cta(k);
+    bool write_norms = true, int rows_layout = 0) {
+    const int rows_per_cta = rows_layout > 0 ? rows_layout : nq_encode_rows_per_cta(k);
     const int bpr = k >> 3;
     const int pitch = k + 8;  // de-conflicts the strided chain reads of neighbouring rows
     float* partial = smem;
@@ -127,28 +142,33 @@ __device__ __forceinline__ void nq_encode_rows_cta(
         return;
     }
 
-    // Undithered rows (activations, K/V): every thread classifies its four candidates with the
-    // cheap exact tests; the few (thread, beta) pairs that need the full evaluation are queued in
-    // shared memory and evaluated densely by the whole CTA, so no warp idles behind one slow lane.
-    float* stage = sq;  // the squares are dead: every row scale has been computed (barrier above)
+    // Undithered rows (activations, K/V).  Work proceeds in batches of NQ_ENC_ROUNDS rounds of
+    // NQ_ENC_THREADS blocks.  Every thread classifies the four candidates of its block with the
+    // cheap exact tests and posts a provisional result (codeword, scaled reconstruction, search
+    // key) in shared memory.  Candidates whose lattice point lies ON the boundary of 14*V(E8)
+    // -- about one block in seven on Gaussian rows -- need the full evaluation: they are queued
+    // with their lattice point and evaluated densely by the whole CTA once per batch, so no warp
+    // idles behind one slow lane and the barriers are paid once per batch.  The search rule is
+    // the minimum of nq_candidate_key(), taken with a shared-memory atomic.
     constexpr int NT = NQ_ENC_THREADS;
-    float* xs = stage;                                                    // [NT][8] normalised blocks
-    uint4* res_dec = reinterpret_cast<uint4*>(xs + NT * 8);               // [NT][4] scaled BF16 reconstruction
-    float* res_err = reinterpret_cast<float*>(res_dec + NT * 4);          // [NT][4]
-    uint32_t* res_word = reinterpret_cast<uint32_t*>(res_err + NT * 4);   // [NT][4]
-    unsigned short* queue = reinterpret_cast<unsigned short*>(res_word + NT * 4);  // [4 NT] (thread << 2) | beta
-    unsigned* queue_count = reinterpret_cast<unsigned*>(queue + NT * 4);
-    for (int base = blk_begin; base < padded; base += NQ_ENC_THREADS) {
-        const int b = base + tid;
-        const bool valid = b < enc_end;
+    constexpr int BATCH = NT * NQ_ENC_ROUNDS;
+    constexpr int CAP = NQ_ENC_QUEUE_CAP;
+    float* stage = sq;  // the squares are dead: every row scale has been computed (barrier above)
+    unsigned long long* out_key = reinterpret_cast<unsigned long long*>(stage);  // [BATCH]
+    uint4* out_dec = reinterpret_cast<uint4*>(out_key + BATCH);                  // [BATCH]
+    float* item_x = reinterpret_cast<float*>(out_dec + BATCH);                   // [CAP][8]; after evaluation: key, word
+    float* item_lam = item_x + CAP * 8;                                          // [CAP][8]; after evaluation: BF16 reconstruction
+    uint32_t* out_word = reinterpret_cast<uint32_t*>(item_lam + CAP * 8);        // [BATCH]
+    unsigned short* item_meta = reinterpret_cast<unsigned short*>(out_word + BATCH);  // [CAP] (slot << 2) | beta
+    unsigned* queue_count = reinterpret_cast<unsigned*>(item_meta + CAP);
+    const bool want_dec = decoded != nullptr;
+    for (int base = blk_begin; base < enc_end; base += BATCH) {
         if (tid == 0) *queue_count = 0u;
-        __syncthreads();
-        int best = 0, row_r = 0;
-        float best_err = 0.0f, best_lam[8];
-        unsigned pending = 0;
-        if (valid) {
-            row_r = b / bpr;
-            const int bb = b - row_r * bpr;
+        __syncthreads();  // also: the previous batch has been written out
+        const int batch_n = min(BATCH, enc_end - base);
+        for (int slot = tid; slot < batch_n; slot += NT) {
+            const int b = base + slot;
+            const int row_r = b / bpr, bb = b - row_r * bpr;
             float v[8];
             if (row_r < valid_rows) {
                 nq_load8<T>(x + (int64_t)row_r * row_stride + (int64_t)bb * 8, v);
@@ -156,69 +176,104 @@ __device__ __forceinline__ void nq_encode_rows_cta(
 #pragma unroll
                 for (int j = 0; j < 8; ++j) v[j] = 0.0f;
             }
-            const float s = scale[row_r];
+            const float s = scale[row_r], ds = dscale[row_r];
 #pragma unroll
             for (int j = 0; j < 8; ++j) v[j] = nq_mul(v[j], s);
-            float4* dst = reinterpret_cast<float4*>(xs + tid * 8);
-            dst[0] = make_float4(v[0], v[1], v[2], v[3]);
-            dst[1] = make_float4(v[4], v[5], v[6], v[7]);
-            nq_encode_block_fastpass(v, beta_table, best, best_err, best_lam, pending);
-#pragma unroll
-            for (int c = 0; c < 4; ++c)
-                if ((pending >> c) & 1u) queue[atomicAdd(queue_count, 1u)] = (unsigned short)((tid << 2) | c);
-        }
-        __syncthreads();
-        const int items = (int)*queue_count;
-        for (int it = tid; it < items; it += NQ_ENC_THREADS) {
-            const int owner = queue[it] >> 2, c = queue[it] & 3;
-            float v[8], r[8], err;
-            const float4 lo = reinterpret_cast<const float4*>(xs + owner * 8)[0];
-            const float4 hi = reinterpret_cast<const float4*>(xs + owner * 8)[1];
-            v[0] = lo.x; v[1] = lo.y; v[2] = lo.z; v[3] = lo.w; v[4] = hi.x; v[5] = hi.y; v[6] = hi.z; v[7] = hi.w;
-            res_word[owner * 4 + c] = nq_encode_candidate_exact(v, beta_table[c], nullptr, r, err);
-            res_err[owner * 4 + c] = err;
-            const float ds = dscale[(base + owner) / bpr];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) r[j] = nq_mul(r[j], ds);
-            res_dec[owner * 4 + c] = nq_pack_bf16x8(r);
-        }
-        __syncthreads();
-        int bid = 0;
-        if (valid) {
+            int best;
+            float best_err, best_lam[8];
+            unsigned pending, overflow = 0;
+            nq_encode_block_fastpass_push(v, beta_table, best, best_err, best_lam, pending,
+                                          [&](int c, const float* lam) {
+                const unsigned idx = atomicAdd(queue_count, 1u);
+                if (idx < (unsigned)CAP) {
+                    float4* dx = reinterpret_cast<float4*>(item_x + idx * 8);
+                    dx[0] = make_float4(v[0], v[1], v[2], v[3]);
+                    dx[1] = make_float4(v[4], v[5], v[6], v[7]);
+                    float4* dl = reinterpret_cast<float4*>(item_lam + idx * 8);
+                    dl[0] = make_float4(lam[0], lam[1], lam[2], lam[3]);
+                    dl[1] = make_float4(lam[4], lam[5], lam[6], lam[7]);
+                    item_meta[idx] = (unsigned short)((slot << 2) | c);
+                } else {
+                    overflow |= 1u << c;  // queue full (degenerate inputs): generic evaluation below
+                }
+            });
+            pending |= overflow;
             uint32_t word = 0;
             uint4 dec = make_uint4(0, 0, 0, 0);
-            bool from_queue = false;
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                if (!((pending >> c) & 1u)) continue;
-                const float err = res_err[tid * 4 + c];
-                if (nq_candidate_wins(c, err, best, best_err)) {
-                    best = c;
-                    best_err = err;
-                    word = res_word[tid * 4 + c];
-                    dec = res_dec[tid * 4 + c];
-                    from_queue = true;
-                }
-            }
-            if (!from_queue) {
+            unsigned long long key = ~0ull;
+            if (best >= 0) {
                 word = nq_lattice_to_codeword(best_lam);
-                if (decoded != nullptr) {
-                    const float bt = beta_table[best], ds = dscale[row_r];
+                key = nq_candidate_key(best_err, best);
+                if (want_dec) {
+                    const float bt = beta_table[best];
                     float recon[8];
 #pragma unroll
                     for (int j = 0; j < 8; ++j) recon[j] = nq_mul(nq_mul(best_lam[j], bt), ds);
                     dec = nq_pack_bf16x8(recon);
                 }
             }
-            bid = best;
-            codes[b] = word;
-            if (decoded != nullptr) *reinterpret_cast<uint4*>(decoded + (int64_t)b * 8) = dec;
+            if (pending) {  // rare: candidates outside the cell that nothing rules out, or a full queue
+#pragma unroll 1
+                for (int c = 0; c < 4; ++c) {
+                    if (!((pending >> c) & 1u)) continue;
+                    float r[8], err;
+                    const uint32_t w = nq_encode_candidate_exact(v, beta_table[c], nullptr, r, err);
+                    const unsigned long long k2 = nq_candidate_key(err, c);
+                    if (k2 < key) {
+                        key = k2;
+                        word = w;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) r[j] = nq_mul(r[j], ds);
+                        dec = nq_pack_bf16x8(r);
+                    }
+                }
+            }
+            out_key[slot] = key;
+            out_word[slot] = word;
+            out_dec[slot] = dec;
         }
-        // four neighbouring blocks share one beta byte (block i -> bits 2i..2i+1)
-        unsigned merged = (unsigned)bid;
-        merged |= __shfl_down_sync(0xffffffffu, (unsigned)bid, 1) << 2;
-        merged |= __shfl_down_sync(0xffffffffu, (unsigned)bid, 2) << 4;
-        merged |= __shfl_down_sync(0xffffffffu, (unsigned)bid, 3) << 6;
-        if (valid && (tid & 3) == 0) beta_ids[b >> 2] = (uint8_t)merged;
+        __syncthreads();
+        const int items = (int)min(*queue_count, (unsigned)CAP);
+        for (int it = tid; it < items; it += NT) {
+            const int slot = item_meta[it] >> 2, c = item_meta[it] & 3;
+            float v[8], lam[8], r[8], err;
+            float4 lo = reinterpret_cast<const float4*>(item_x + it * 8)[0];
+            float4 hi = reinterpret_cast<const float4*>(item_x + it * 8)[1];
+            v[0] = lo.x; v[1] = lo.y; v[2] = lo.z; v[3] = lo.w; v[4] = hi.x; v[5] = hi.y; v[6] = hi.z; v[7] = hi.w;
+            lo = reinterpret_cast<const float4*>(item_lam + it * 8)[0];
+            hi = reinterpret_cast<const float4*>(item_lam + it * 8)[1];
+            lam[0] = lo.x; lam[1] = lo.y; lam[2] = lo.z; lam[3] = lo.w; lam[4] = hi.x; lam[5] = hi.y; lam[6] = hi.z; lam[7] = hi.w;
+            const uint32_t word = nq_eval_candidate_from_lam(v, lam, beta_table[c], r, err);
+            const unsigned long long key = nq_candidate_key(err, c);
+            const float ds = dscale[(base + slot) / bpr];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) r[j] = nq_mul(r[j], ds);
+            // the item's inputs are in registers: its storage now holds the result
+            *reinterpret_cast<unsigned long long*>(item_x + it * 8) = key;
+            *reinterpret_cast<uint32_t*>(item_x + it * 8 + 2) = word;
+            *reinterpret_cast<uint4*>(item_lam + it * 8) = nq_pack_bf16x8(r);
+            atomicMin(out_key + slot, key);
+        }
+        __syncthreads();
+        for (int it = tid; it < items; it += NT) {
+            const int slot = item_meta[it] >> 2;
+            // keys of one block differ in the beta index: at most one item equals the minimum
+            if (out_key[slot] == *reinterpret_cast<const unsigned long long*>(item_x + it * 8)) {
+                out_word[slot] = *reinterpret_cast<const uint32_t*>(item_x + it * 8 + 2);
+                out_dec[slot] = *reinterpret_cast<const uint4*>(item_lam + it * 8);
+            }
+        }
+        __syncthreads();
+        for (int slot = tid; slot < batch_n; slot += NT) {
+            codes[base + slot] = out_word[slot];
+            if (want_dec) *reinterpret_cast<uint4*>(decoded + (int64_t)(base + slot) * 8) = out_dec[slot];
+        }
+        // four neighbouring blocks share one beta byte (block i -> bits 2i..2i+1); batch_n is a multiple of 4
+        for (int q4 = tid; q4 < (batch_n >> 2); q4 += NT) {
+            unsigned merged = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) merged |= ((unsigned)out_key[q4 * 4 + i] & 3u) << (2 * i);
+            beta_ids[(base >> 2) + q4] = (uint8_t)merged;
+        }
     }
 }

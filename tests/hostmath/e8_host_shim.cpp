@@ -54,6 +54,53 @@ void shim_encode_blocks_pruned(const float* x, long n, const float* beta, uint32
     for (long i = 0; i < n; ++i) words[i] = nq_encode_block_pruned(x + 8 * i, beta, beta_ids[i], recon + 8 * i);
 }
 
+// The search as the encoder kernel runs it: cheap pass, boundary candidates evaluated from
+// their lattice point, leftovers by the generic evaluation, everything merged by key.
+// Must equal shim_encode_blocks(seed < 0) on every input.
+void shim_encode_blocks_queued(const float* xs, long n, const float* beta, uint32_t* words, int* beta_ids,
+                               float* recon, long* boundary_items) {
+    long items = 0;
+    for (long i = 0; i < n; ++i) {
+        const float* x = xs + 8 * i;
+        int best;
+        float best_err, best_lam[8];
+        unsigned pending;
+        int qn = 0, qb[4];
+        float qlam[4][8];
+        nq_encode_block_fastpass_push(x, beta, best, best_err, best_lam, pending, [&](int b, const float* lam) {
+            qb[qn] = b;
+            for (int j = 0; j < 8; ++j) qlam[qn][j] = lam[j];
+            ++qn;
+        });
+        unsigned long long key = ~0ull;
+        uint32_t word = 0;
+        float rec[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        if (best >= 0) {
+            key = nq_candidate_key(best_err, best);
+            word = nq_lattice_to_codeword(best_lam);
+            for (int j = 0; j < 8; ++j) rec[j] = nq_mul(best_lam[j], beta[best]);
+        }
+        for (int q = 0; q < qn; ++q) {
+            float r[8], err;
+            const uint32_t w = nq_eval_candidate_from_lam(x, qlam[q], beta[qb[q]], r, err);
+            const unsigned long long k2 = nq_candidate_key(err, qb[q]);
+            if (k2 < key) { key = k2; word = w; for (int j = 0; j < 8; ++j) rec[j] = r[j]; }
+        }
+        for (int c = 0; c < 4; ++c) {
+            if (!((pending >> c) & 1u)) continue;
+            float r[8], err;
+            const uint32_t w = nq_encode_candidate_exact(x, beta[c], nullptr, r, err);
+            const unsigned long long k2 = nq_candidate_key(err, c);
+            if (k2 < key) { key = k2; word = w; for (int j = 0; j < 8; ++j) rec[j] = r[j]; }
+        }
+        items += qn;
+        words[i] = word;
+        beta_ids[i] = (int)(key & 3u);
+        for (int j = 0; j < 8; ++j) recon[8 * i + j] = rec[j];
+    }
+    if (boundary_items) *boundary_items = items;
+}
+
 void shim_cell_class(const float* lam, long n, int* out) {
     for (long i = 0; i < n; ++i) out[i] = nq_e8_cell_class(lam + 8 * i);
 }

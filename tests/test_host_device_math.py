@@ -95,10 +95,12 @@ def _encode_both(shim, x, betas):
     betas = np.array(betas, np.float32)
     n = len(x)
     out = []
-    for pruned in (False, True):
+    for variant in ("full", "pruned", "queued"):
         words, ids, rec = np.empty(n, np.uint32), np.empty(n, np.int32), np.empty_like(x)
-        if pruned:
+        if variant == "pruned":
             shim.shim_encode_blocks_pruned(_p(x), ctypes.c_long(n), _p(betas), _p(words), _p(ids), _p(rec))
+        elif variant == "queued":
+            shim.shim_encode_blocks_queued(_p(x), ctypes.c_long(n), _p(betas), _p(words), _p(ids), _p(rec), None)
         else:
             shim.shim_encode_blocks(_p(x), ctypes.c_long(n), _p(betas), ctypes.c_long(-1), ctypes.c_long(0),
                                     _p(words), _p(ids), _p(rec))
@@ -108,7 +110,7 @@ def _encode_both(shim, x, betas):
 
 @pytest.mark.parametrize("case", ["gauss", "heavy", "huge", "tiny", "grid", "boundary"])
 def test_pruned_search_equals_full_search(shim, case):
-    """The pruned 4-beta search (interior test + error bounds) must never change a bit."""
+    """The pruned 4-beta searches (interior test + error bounds) must never change a bit."""
     rng = np.random.default_rng(11)
     unit = (0.25, 0.5, 0.75, 1.0)
     if case == "gauss":
@@ -126,8 +128,9 @@ def test_pruned_search_equals_full_search(shim, case):
         a = np.zeros((8, 8)); a[:, 0] = 7; a[:, 1] = 7          # |lam|^2 = 98, on the boundary of 14 V
         b = np.full((8, 8), 3.5)
         x, betas = np.concatenate([a, b, a * 0.5, b * 0.75]), unit
-    (w1, i1, r1), (w2, i2, r2) = _encode_both(shim, x, betas)
-    assert np.array_equal(w1, w2) and np.array_equal(i1, i2) and np.array_equal(r1, r2)
+    (w1, i1, r1), *others = _encode_both(shim, x, betas)
+    for w2, i2, r2 in others:  # pruned per-thread search, and the search as the kernel's work queue runs it
+        assert np.array_equal(w1, w2) and np.array_equal(i1, i2) and np.array_equal(r1, r2)
 
 
 def test_cell_class_known_points(shim):
