@@ -501,7 +501,9 @@ NQ_HD void nq_encode_block_fastpass_push(const float x[8], const float* beta, in
     best_err = 0.0f;
     pending = 0;
     unsigned outside = 0;
-#pragma unroll
+    // One copy of the candidate body (the loop is kept rolled): laid out four times the search
+    // stalls on instruction fetch.
+#pragma unroll 1
     for (int b = 0; b < 4; ++b) {
         const float bt = beta[b], rbeta = nq_rcp(bt);
         float y[8], lam[8], r[8];

@@ -29,13 +29,13 @@ extern "C" int nq_abi_version(void) { return 1; }
 // ---------------------------------------------------------------------------
 // Encoder kernel: one CTA per group of rows (see nq_encode_core.cuh).
 // ---------------------------------------------------------------------------
-template <typename T>
+template <typename T, bool DITHER>
 __global__ void __launch_bounds__(NQ_ENC_THREADS, 5)
 nq_encode_rows_kernel(const T* __restrict__ x, int64_t rows, int k, int64_t row_stride,
                       const float* __restrict__ beta_table, float sqrt_k,
                       uint32_t* __restrict__ codes, uint8_t* __restrict__ beta_ids,
                       float* __restrict__ norms, __nv_bfloat16* __restrict__ decoded,
-                      int use_dither, uint32_t counter_base, int blocks_per_split, int rpc) {
+                      uint32_t counter_base, int blocks_per_split, int rpc) {
     extern __shared__ __align__(16) float smem[];
     const int bpr = k >> 3;
     const int64_t row0 = (int64_t)blockIdx.x * rpc;
@@ -43,8 +43,8 @@ nq_encode_rows_kernel(const T* __restrict__ x, int64_t rows, int k, int64_t row_
     const int64_t g0 = row0 * bpr;
     // gridDim.y > 1: a few long rows are split over several CTAs so the launch fills the GPU
     const int blk_begin = (int)blockIdx.y * blocks_per_split;
-    nq_encode_rows_cta<T>(x + row0 * row_stride, row_stride, nrows, nrows, k, beta_table, sqrt_k, codes + g0,
-                          beta_ids + (g0 >> 2), norms + row0, decoded ? decoded + g0 * 8 : nullptr, use_dither,
+    nq_encode_rows_cta<T, DITHER>(x + row0 * row_stride, row_stride, nrows, nrows, k, beta_table, sqrt_k, codes + g0,
+                          beta_ids + (g0 >> 2), norms + row0, decoded ? decoded + g0 * 8 : nullptr,
                           counter_base + (uint32_t)g0 * 8u, smem, blk_begin, blk_begin + blocks_per_split,
                           blockIdx.y == 0, rpc);
 }
@@ -109,7 +109,7 @@ static int launch_encode(const void* x, int64_t rows, int64_t k, int64_t row_str
     const int many = nq_encode_rows_per_cta_many((int)k);
     if (!use_dither && many > rpc && rows / many >= 5 * 148) rpc = many;
     const size_t smem = nq_encode_smem_floats((int)k, rpc) * sizeof(float);
-    auto kernel = nq_encode_rows_kernel<T>;
+    auto kernel = use_dither ? nq_encode_rows_kernel<T, true> : nq_encode_rows_kernel<T, false>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) {
@@ -134,7 +134,7 @@ static int launch_encode(const void* x, int64_t rows, int64_t k, int64_t row_str
     kernel<<<dim3((unsigned)grid, (unsigned)splits), NQ_ENC_THREADS, smem, stream>>>(
         reinterpret_cast<const T*>(x), rows, (int)k, row_stride, beta_table,
         (float)sqrt((double)k), reinterpret_cast<uint32_t*>(out_codes), out_beta_ids, out_norms,
-        reinterpret_cast<__nv_bfloat16*>(out_decoded), use_dither, counter_base, blocks_per_split, rpc);
+        reinterpret_cast<__nv_bfloat16*>(out_decoded), counter_base, blocks_per_split, rpc);
     NQ_CHECK_LAUNCH("nq_a4_encode");
     return NQ_OK;
 }

@@ -2,7 +2,8 @@
 // writers.  One CTA of NQ_ENC_THREADS threads owns `nrows` consecutive rows of k features
 // (NQ_ENC_THREADS / (k/8) rows for short rows, one or a few rows otherwise).  Small CTAs (five
 // per SM) keep other CTAs issuing while one waits at a barrier.
-//   phase 1  every thread squares its blocks into shared memory
+//   phase 1  every thread squares its blocks into shared memory, transposed so that the
+//            elements j, j+8, j+16, ... of a row (one "lane sequence") are contiguous
 //   phase 2  8 threads per row run the reference's 8-lane strided accumulation
 //            (the order PyTorch's CPU vector_norm uses; it decides the last
 //            bit of the norm and therefore the emitted codes)
@@ -41,21 +42,24 @@ __host__ __device__ inline int nq_encode_rows_per_cta_many(int k) {
 }
 __host__ __device__ inline size_t nq_encode_smem_floats(int k, int rows_layout = 0) {
     const int rpc = rows_layout > 0 ? rows_layout : nq_encode_rows_per_cta(k);
-    const size_t squares = (size_t)rpc * (k + 8);
+    const size_t squares = (size_t)rpc * (k + 40);  // per row: 8 lane sequences of k/8 + 4 floats, + 8
     const size_t body = squares > (size_t)NQ_ENCODE_STAGE_FLOATS ? squares : (size_t)NQ_ENCODE_STAGE_FLOATS;
     return body + (size_t)rpc * 10 + 4;
 }
 
-template <typename T>
+// DITHER selects the weight path (subtractive dither, straight search) at compile time, so that
+// each kernel carries only the code of its own search.
+template <typename T, bool DITHER = false>
 __device__ __forceinline__ void nq_encode_rows_cta(
     const T* __restrict__ x, int64_t row_stride, int nrows, int valid_rows, int k,
     const float* __restrict__ beta_table, float sqrt_k, uint32_t* __restrict__ codes,
     uint8_t* __restrict__ beta_ids, float* __restrict__ norms, __nv_bfloat16* __restrict__ decoded,
-    int use_dither, uint32_t counter_base, float* smem, int blk_begin = 0, int blk_end = 0x7fffffff,
+    uint32_t counter_base, float* smem, int blk_begin = 0, int blk_end = 0x7fffffff,
     bool write_norms = true, int rows_layout = 0) {
     const int rows_per_cta = rows_layout > 0 ? rows_layout : nq_encode_rows_per_cta(k);
     const int bpr = k >> 3;
-    const int pitch = k + 8;  // de-conflicts the strided chain reads of neighbouring rows
+    const int lane_pitch = bpr + 4;    // k/8 squares per lane sequence; +4 keeps the 16-byte chain reads conflict-free
+    const int pitch = 8 * lane_pitch + 8;  // floats per row; +8 spreads the rows of one warp over the banks
     float* partial = smem;
     float* scale = partial + rows_per_cta * 8;
     float* dscale = scale + rows_per_cta;
@@ -73,20 +77,22 @@ __device__ __forceinline__ void nq_encode_rows_cta(
 #pragma unroll
             for (int j = 0; j < 8; ++j) v[j] = 0.0f;
         }
-        float4 lo = make_float4(nq_mul(v[0], v[0]), nq_mul(v[1], v[1]), nq_mul(v[2], v[2]), nq_mul(v[3], v[3]));
-        float4 hi = make_float4(nq_mul(v[4], v[4]), nq_mul(v[5], v[5]), nq_mul(v[6], v[6]), nq_mul(v[7], v[7]));
-        float4* dst = reinterpret_cast<float4*>(sq + (size_t)r * pitch + bb * 8);
-        dst[0] = lo;
-        dst[1] = hi;
+        // transposed: lane sequence j of row r (elements j, j+8, j+16, ...) is contiguous
+        float* dst = sq + (size_t)r * pitch + bb;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) dst[j * lane_pitch] = nq_mul(v[j], v[j]);
     }
     __syncthreads();
 
     for (int t = tid; t < nrows * 8; t += NQ_ENC_THREADS) {
         const int r = t >> 3, l = t & 7;
-        const float* p = sq + (size_t)r * pitch + l;
+        const float4* p = reinterpret_cast<const float4*>(sq + (size_t)r * pitch + l * lane_pitch);
         float acc = 0.0f;
-#pragma unroll 8
-        for (int i = 0; i < bpr; ++i) acc = nq_add(acc, p[8 * i]);
+#pragma unroll 4
+        for (int i = 0; i < (bpr >> 2); ++i) {
+            const float4 q = p[i];
+            acc = nq_add(nq_add(nq_add(nq_add(acc, q.x), q.y), q.z), q.w);
+        }
         partial[t] = acc;
     }
     __syncthreads();
@@ -107,7 +113,7 @@ __device__ __forceinline__ void nq_encode_rows_cta(
     // several CTAs, each recomputing the cheap norm); blk_begin is a multiple of the CTA size.
     const int enc_end = min(nblocks, blk_end);
     const int padded = blk_begin + ((max(enc_end - blk_begin, 0) + 31) & ~31);
-    if (use_dither) {
+    if (DITHER) {
         // weights: straight per-thread search with the subtractive dither of the global block
         for (int b = blk_begin + tid; b < padded; b += NQ_ENC_THREADS) {
             const bool valid = b < enc_end;

@@ -118,7 +118,7 @@ __global__ void __launch_bounds__(NQ_ENC_THREADS, 5) nq_kv_pack_pages_kernel(con
     uint8_t* betas = (is_value ? p.value_betas : p.key_betas) + page_id * beta_bytes + (int64_t)r0 * bpr / 4;
     float* norms = (is_value ? p.value_norms : p.key_norms) + (int64_t)page_id * rows + r0;
     nq_encode_rows_cta<T>(src, p.dim, nrows, nrows, p.dim, is_value ? p.value_beta_table : p.key_beta_table,
-                          p.sqrt_dim, reinterpret_cast<uint32_t*>(codes), betas, norms, nullptr, 0, 0u, smem);
+                          p.sqrt_dim, reinterpret_cast<uint32_t*>(codes), betas, norms, nullptr, 0u, smem);
 }
 
 __global__ void __launch_bounds__(256) nq_kv_publish_kernel(const PackParams p) {
@@ -158,7 +158,7 @@ __global__ void __launch_bounds__(NQ_ENC_THREADS, 5) nq_kv_quantize_page_kernel(
     uint8_t* betas = (is_value ? p.value_betas : p.key_betas) + (int64_t)r0 * bpr / 4;
     float* norms = (is_value ? p.value_norms : p.key_norms) + r0;
     nq_encode_rows_cta<T>(src, p.dim, nrows, valid_rows, p.dim, is_value ? p.value_beta_table : p.key_beta_table,
-                          p.sqrt_dim, reinterpret_cast<uint32_t*>(codes), betas, norms, nullptr, 0, 0u, smem);
+                          p.sqrt_dim, reinterpret_cast<uint32_t*>(codes), betas, norms, nullptr, 0u, smem);
 }
 
 template <typename K>
