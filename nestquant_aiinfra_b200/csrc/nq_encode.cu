@@ -124,11 +124,11 @@ static int launch_encode(const void* x, int64_t rows, int64_t k, int64_t row_str
     int splits = 1;
     if (one_long_row && grid < 148) {
         splits = (int)((2 * 148 + grid - 1) / grid);
-        const int max_splits = bpr / NQ_ENC_THREADS;
+        const int max_splits = bpr / 32;  // one warp step per CTA at the finest
         if (splits > max_splits) splits = max_splits;
         if (splits < 1) splits = 1;
     }
-    int blocks_per_split = ((bpr + splits - 1) / splits + NQ_ENC_THREADS - 1) / NQ_ENC_THREADS * NQ_ENC_THREADS;
+    int blocks_per_split = ((bpr + splits - 1) / splits + 31) / 32 * 32;
     if (!one_long_row) blocks_per_split = 0x40000000;
     splits = one_long_row ? (bpr + blocks_per_split - 1) / blocks_per_split : 1;
     kernel<<<dim3((unsigned)grid, (unsigned)splits), NQ_ENC_THREADS, smem, stream>>>(

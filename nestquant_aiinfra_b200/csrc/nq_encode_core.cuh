@@ -110,7 +110,7 @@ __device__ __forceinline__ void nq_encode_rows_cta(
     __syncthreads();
 
     // Phase 3 covers blocks [blk_begin, blk_end) of the CTA's rows (a long row can be split over
-    // several CTAs, each recomputing the cheap norm); blk_begin is a multiple of the CTA size.
+    // several CTAs, each recomputing the cheap norm); blk_begin is a multiple of 32.
     const int enc_end = min(nblocks, blk_end);
     const int padded = blk_begin + ((max(enc_end - blk_begin, 0) + 31) & ~31);
     if (DITHER) {
