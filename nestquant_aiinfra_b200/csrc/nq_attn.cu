@@ -129,6 +129,7 @@ __global__ void __launch_bounds__(kAttnThreads) nq_attn_paged_kernel(const AttnP
                 const int t = t0 + tsub;
                 const bool valid = t < tlimit && base_token + t < limit;
                 float kvec[8], vvec[8];
+                float kscale = 1.0f, vscale = 1.0f;  // beta * norm / sqrt(D) of the row, applied after the dot product
                 if (is_hot) {
                     const int64_t off = (((int64_t)slot * p.page_size + min(t, p.page_size - 1)) * p.kv_heads + h) * D + blk * 8;
                     nq_load8<__nv_bfloat16>(reinterpret_cast<const __nv_bfloat16*>(p.hot_keys) + off, kvec);
@@ -144,17 +145,15 @@ __global__ void __launch_bounds__(kAttnThreads) nq_attn_paged_kernel(const AttnP
                     const float vds = nq_div_by(__ldg(p.value_norms + (int64_t)page_id * rows + row), p.sqrt_dim, p.inv_sqrt_dim);
                     nq_decode_codeword_exact(kw, nullptr, kvec);
                     nq_decode_codeword_exact(vw, nullptr, vvec);
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        kvec[j] = nq_mul(nq_mul(kvec[j], kb), kds);
-                        vvec[j] = nq_mul(nq_mul(vvec[j], vb), vds);
-                    }
+                    kscale = kb * kds;
+                    vscale = vb * vds;
                 }
 #pragma unroll
                 for (int g = 0; g < G; ++g) {
                     float s = 0.0f;
 #pragma unroll
                     for (int j = 0; j < 8; ++j) s = fmaf(q[g][j], kvec[j], s);
+                    s *= kscale;  // the beta of this lane's block, the norm of its row
 #pragma unroll
                     for (int off = 1; off < BPR; off <<= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
                     if (valid) {
@@ -162,8 +161,9 @@ __global__ void __launch_bounds__(kAttnThreads) nq_attn_paged_kernel(const AttnP
                         const float corr = exp2f(m[g] - mn);  // exp2(-inf) = 0 on the first token
                         const float pr = exp2f(s - mn);
                         l[g] = l[g] * corr + pr;
+                        const float pv = pr * vscale;
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) acc[g][j] = acc[g][j] * corr + pr * vvec[j];
+                        for (int j = 0; j < 8; ++j) acc[g][j] = acc[g][j] * corr + pv * vvec[j];
                         m[g] = mn;
                     }
                 }

@@ -183,8 +183,9 @@ NQ_HD void nq_e8_nearest_exact(const float x[8], float out[8]) {
 // parity rule and first-max rule as the exact function, but the two coset
 // distances are formed from the rounding residuals with FMAs, and only the
 // winning coset is repaired.  Whenever the distances are closer than 1e-4
-// (summation-order effects are below 1e-6) the exact function decides, so the
-// result always equals nq_e8_nearest_exact.
+// (summation-order effects are below 1e-6) the reference's comparison decides,
+// evaluated from the roundings already at hand, so the result always equals
+// nq_e8_nearest_exact.
 NQ_HD void nq_e8_nearest_guarded(const float x[8], float out[8]) {
     float r0[8], e0[8], r1[8], e1[8];
     int par0 = 0, par1 = 0;
@@ -205,15 +206,32 @@ NQ_HD void nq_e8_nearest_guarded(const float x[8], float out[8]) {
         s1 = nq_fma(e1[j], e1[j], s1);
         m1 = fmaxf(m1, fabsf(e1[j]));
     }
-    if (par0 & 1) s0 += 1.0f - 2.0f * m0;
-    if (par1 & 1) s1 += 1.0f - 2.0f * m1;
+    const bool odd0 = (par0 & 1) != 0, odd1 = (par1 & 1) != 0;
+    if (odd0) s0 += 1.0f - 2.0f * m0;
+    if (odd1) s1 += 1.0f - 2.0f * m1;
     const float diff = s0 - s1;
+    bool integer_coset = diff < 0.0f;
     if (fabsf(diff) < 1e-4f) {
-        nq_e8_nearest_exact(x, out);
-        return;
+        // too close to call from the residuals: the reference's own comparison, i.e. both repaired
+        // points and their sequentially summed distances (same roundings as nq_e8_nearest_exact)
+        float d0 = 0.0f, d1 = 0.0f;
+        bool pend0 = odd0, pend1 = odd1;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const bool hit0 = pend0 && fabsf(e0[j]) == m0;
+            const bool hit1 = pend1 && fabsf(e1[j]) == m1;
+            pend0 = pend0 && !hit0;
+            pend1 = pend1 && !hit1;
+            const float p0 = hit0 ? nq_add(r0[j], e0[j] >= 0.0f ? 1.0f : -1.0f) : r0[j];
+            const float q1 = hit1 ? nq_add(r1[j], e1[j] >= 0.0f ? 1.0f : -1.0f) : r1[j];
+            const float p1 = nq_add(q1, 0.5f);
+            const float a = nq_sub(x[j], p0), b = nq_sub(x[j], p1);
+            d0 = nq_add(d0, nq_mul(a, a));
+            d1 = nq_add(d1, nq_mul(b, b));
+        }
+        integer_coset = d0 < d1;
     }
-    const bool integer_coset = diff < 0.0f;
-    const bool odd = ((integer_coset ? par0 : par1) & 1) != 0;
+    const bool odd = integer_coset ? odd0 : odd1;
     const float m = integer_coset ? m0 : m1;
     const float half = integer_coset ? 0.0f : 0.5f;
     bool pending = odd;
@@ -288,7 +306,7 @@ NQ_HD void nq_decode_codeword_exact(uint32_t word, const float* dither, float r[
     }
 #pragma unroll
     for (int j = 0; j < 8; ++j) s[j] = nq_div_by(t[j], 14.0f, NQ_RCP14);
-    nq_e8_nearest_guarded(s, n);  // same result as the exact search, cheaper away from coset ties
+    nq_e8_nearest_guarded(s, n);  // same result as the exact search
 #pragma unroll
     for (int j = 0; j < 8; ++j) r[j] = nq_fma(-14.0f, n[j], t[j]);  // 14*n is exact, so one rounding either way
 }

@@ -42,21 +42,26 @@ _I64 = ctypes.c_int64
 # The first WS_COUNTER_BYTES hold the split-K arrival counters; kernels leave
 # them zero, so the buffer can be reused by every later call.
 # ---------------------------------------------------------------------------
-_WORKSPACES: dict[tuple[int, int], torch.Tensor] = {}
+_WORKSPACES: dict[tuple[int, int, bool], torch.Tensor] = {}
 
 
 def workspace_for(device: torch.device, nbytes: int) -> torch.Tensor:
+    """Zero-initialised scratch for the projection kernels, one per (device, stream, eager | capture).
+
+    Only the counter words at the front have to start at zero, and every kernel leaves them at
+    zero, so one buffer serves all calls of a stream.  Buffers requested while a CUDA graph is being
+    captured come from the graph's private pool and are kept apart from the eager one; they are
+    reused by later calls of the same and of later captures on that stream (graphs captured on
+    one stream replay one after the other, like eager calls).
+    """
     capturing = torch.cuda.is_current_stream_capturing()
     key = (device.index if device.index is not None else torch.cuda.current_device(),
-           torch.cuda.current_stream(device).cuda_stream)
+           torch.cuda.current_stream(device).cuda_stream, capturing)
     buffer = _WORKSPACES.get(key)
-    if buffer is None or buffer.numel() < nbytes or capturing:
-        # Under graph capture the allocation comes from the graph's private pool
-        # and must not be shared with eager code.
-        size = max(nbytes, 1 << 20)
+    if buffer is None or buffer.numel() < nbytes:
+        size = max(nbytes, (64 << 20) if capturing else (1 << 20))  # a capture rarely has to grow it: each growth is a fill node
         buffer = torch.zeros(size, dtype=torch.uint8, device=device)
-        if not capturing:
-            _WORKSPACES[key] = buffer
+        _WORKSPACES[key] = buffer
     return buffer
 
 
