@@ -64,6 +64,19 @@ int nq_a4_encode(const void* x, int x_dtype, int64_t rows, int64_t k, int64_t ro
                  const float* beta_table, uint8_t* out_codes, uint8_t* out_beta_ids,
                  float* out_norms, void* out_decoded, nq_stream_t stream);
 
+/* Rotate-then-encode: the normalised Hadamard transform FusedNQRTLinear applies to its input
+ * (models/fused_linear.py:287-290 -> core/rotation.py:12-27) and nq_a4_encode in one launch.
+ * Outputs are bit-identical to nq_hadamard(x) followed by nq_a4_encode; the rotated rows are
+ * not written out.  hadamard_block = k rotates whole rows; a smaller power of two dividing k
+ * rotates consecutive blocks of that size (block-diagonal rotation of a tensor-parallel K
+ * shard).  x is [rows, k] contiguous.  No counterpart in the reference, which runs the
+ * transform as separate tensor ops.
+ * Requirements: k % 32 == 0, 32 <= k <= NQ_ROTATED_MAX_K, 16-byte aligned pointers. */
+#define NQ_ROTATED_MAX_K 16384
+int nq_a4_encode_rotated(const void* x, int x_dtype, int64_t rows, int64_t k, int64_t hadamard_block,
+                         const float* beta_table, uint8_t* out_codes, uint8_t* out_beta_ids,
+                         float* out_norms, void* out_decoded, nq_stream_t stream);
+
 /* Weight encoder: the same search with the stateless subtractive dither of
  * global block  w_block_offset + row*k/8 + block  ("lcg31_mix_v1",
  * core/codec.py:176-224).  Bit-exact with quantize_rows(W, 14, betas,
@@ -230,6 +243,15 @@ int nq_kv_attention(const void* query, int q_dtype, int batch, int q_tokens, int
  * hadamard() does (core/rotation.py:12-27): every butterfly stage rounded to
  * the dtype, final IEEE division by float32(sqrt(n)).  x may equal out. */
 int nq_hadamard(const void* x, void* out, int dtype, int64_t rows, int64_t n, nq_stream_t stream);
+
+/* RMS normalisation of rows as Hugging Face's LlamaRMSNorm computes it, in one launch:
+ *   out = weight * dtype(x * rsqrt(mean(x^2) + eps))      (mean and product in float32)
+ * It precedes every rotate-then-encode launch of a decoder layer; the reference leaves it to
+ * the model's tensor ops, so there is no counterpart in the reference.  The sum of squares has
+ * a fixed order of its own: deterministic, not bit-identical to the tensor-op reduction.
+ *   x, out [rows, n] contiguous, weight [n], all of `dtype`; n % 8 == 0; 16-byte aligned. */
+int nq_rmsnorm(const void* x, const void* weight, int dtype, int64_t rows, int64_t n, float eps, void* out,
+               nq_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -47,15 +47,30 @@ __host__ __device__ inline size_t nq_encode_smem_floats(int k, int rows_layout =
     return body + (size_t)rpc * 10 + 4;
 }
 
+// Block load of the encoder: from global memory in the tensor dtype, or (GLOBAL_IN = false)
+// float32 values that an earlier phase of the same kernel left in shared memory.
+template <typename T, bool GLOBAL_IN>
+__device__ __forceinline__ void nq_encode_load8(const T* p, float v[8]) {
+    if (GLOBAL_IN) {
+        nq_load8<T>(p, v);
+    } else {
+        const float4 a = reinterpret_cast<const float4*>(p)[0];
+        const float4 b = reinterpret_cast<const float4*>(p)[1];
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+        v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    }
+}
+
 // DITHER selects the weight path (subtractive dither, straight search) at compile time, so that
 // each kernel carries only the code of its own search.
-template <typename T, bool DITHER = false>
+template <typename T, bool DITHER = false, bool GLOBAL_IN = true>
 __device__ __forceinline__ void nq_encode_rows_cta(
     const T* __restrict__ x, int64_t row_stride, int nrows, int valid_rows, int k,
     const float* __restrict__ beta_table, float sqrt_k, uint32_t* __restrict__ codes,
     uint8_t* __restrict__ beta_ids, float* __restrict__ norms, __nv_bfloat16* __restrict__ decoded,
     uint32_t counter_base, float* smem, int blk_begin = 0, int blk_end = 0x7fffffff,
     bool write_norms = true, int rows_layout = 0) {
+    static_assert(GLOBAL_IN || sizeof(T) == 4, "shared-memory input is float32");
     const int rows_per_cta = rows_layout > 0 ? rows_layout : nq_encode_rows_per_cta(k);
     const int bpr = k >> 3;
     const int lane_pitch = bpr + 4;    // k/8 squares per lane sequence; +4 keeps the 16-byte chain reads conflict-free
@@ -72,7 +87,7 @@ __device__ __forceinline__ void nq_encode_rows_cta(
         const int r = b / bpr, bb = b - r * bpr;
         float v[8];
         if (r < valid_rows) {
-            nq_load8<T>(x + (int64_t)r * row_stride + (int64_t)bb * 8, v);
+            nq_encode_load8<T, GLOBAL_IN>(x + (int64_t)r * row_stride + (int64_t)bb * 8, v);
         } else {
 #pragma unroll
             for (int j = 0; j < 8; ++j) v[j] = 0.0f;
@@ -122,7 +137,7 @@ __device__ __forceinline__ void nq_encode_rows_cta(
                 const int r = b / bpr, bb = b - r * bpr;
                 float v[8], recon[8], d[8];
                 if (r < valid_rows) {
-                    nq_load8<T>(x + (int64_t)r * row_stride + (int64_t)bb * 8, v);
+                    nq_encode_load8<T, GLOBAL_IN>(x + (int64_t)r * row_stride + (int64_t)bb * 8, v);
                 } else {
 #pragma unroll
                     for (int j = 0; j < 8; ++j) v[j] = 0.0f;
@@ -177,7 +192,7 @@ __device__ __forceinline__ void nq_encode_rows_cta(
             const int row_r = b / bpr, bb = b - row_r * bpr;
             float v[8];
             if (row_r < valid_rows) {
-                nq_load8<T>(x + (int64_t)row_r * row_stride + (int64_t)bb * 8, v);
+                nq_encode_load8<T, GLOBAL_IN>(x + (int64_t)row_r * row_stride + (int64_t)bb * 8, v);
             } else {
 #pragma unroll
                 for (int j = 0; j < 8; ++j) v[j] = 0.0f;

@@ -1,0 +1,106 @@
+// Rotate-then-encode in one launch: the normalised Hadamard transform of every activation row
+// (what FusedNQRTLinear applies to its input, models/fused_linear.py:287-290) followed by the A4
+// row encoder, without the round trip of the rotated rows through HBM and without a second
+// launch.  The rows are transformed in shared memory with the arithmetic of nq_hadamard
+// (per-stage rounding to the tensor dtype, IEEE division by sqrt(n)) and the encoder body reads
+// them from there, so codes, beta ids, norms and reconstruction are bit-identical to
+// nq_hadamard followed by nq_a4_encode.
+//
+// hadamard_block < k applies the transform to consecutive blocks of that size (the
+// block-diagonal rotation of a tensor-parallel K shard).
+#include <math.h>
+
+#include "nq_common.cuh"
+#include "nq_encode_core.cuh"
+#include "nq_rotate_core.cuh"
+
+namespace {
+
+template <typename T>
+__global__ void __launch_bounds__(NQ_ENC_THREADS, 5)
+nq_encode_rotated_kernel(const T* __restrict__ x, int64_t rows, int k, int hadamard_block, float root, float inv_root,
+                         const float* __restrict__ beta_table, float sqrt_k, uint32_t* __restrict__ codes,
+                         uint8_t* __restrict__ beta_ids, float* __restrict__ norms,
+                         __nv_bfloat16* __restrict__ decoded, int blocks_per_split, int rpc) {
+    extern __shared__ __align__(16) float smem[];
+    float* rotated = smem;                       // [rpc][k] float32 values of dtype T
+    float* encoder_smem = smem + (size_t)rpc * k;
+    const int bpr = k >> 3;
+    const int64_t row0 = (int64_t)blockIdx.x * rpc;
+    const int nrows = (int)min((int64_t)rpc, rows - row0);
+    const int total = nrows * k;
+    nq_fwht_rows_to_smem<T>(x + row0 * k, rotated, total, hadamard_block);
+    for (int i = threadIdx.x; i < total; i += NQ_ENC_THREADS)
+        rotated[i] = nq_round_to<T>(nq_div_by(rotated[i], root, inv_root));
+    __syncthreads();
+    const int64_t g0 = row0 * bpr;
+    const int blk_begin = (int)blockIdx.y * blocks_per_split;
+    nq_encode_rows_cta<float, false, false>(rotated, k, nrows, nrows, k, beta_table, sqrt_k, codes + g0,
+                                            beta_ids + (g0 >> 2), norms + row0,
+                                            decoded ? decoded + g0 * 8 : nullptr, 0u, encoder_smem, blk_begin,
+                                            blk_begin + blocks_per_split, blockIdx.y == 0, rpc);
+}
+
+template <typename T>
+int launch_encode_rotated(const void* x, int64_t rows, int64_t k, int64_t hadamard_block, const float* beta_table,
+                          uint8_t* out_codes, uint8_t* out_beta_ids, float* out_norms, void* out_decoded,
+                          cudaStream_t stream) {
+    int rpc = nq_encode_rows_per_cta((int)k);
+    const int many = nq_encode_rows_per_cta_many((int)k);
+    if (many > rpc && rows / many >= 5 * 148) rpc = many;
+    const size_t smem = ((size_t)rpc * k + nq_encode_smem_floats((int)k, rpc)) * sizeof(float);
+    auto kernel = nq_encode_rotated_kernel<T>;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) {
+            nq_set_error("nq_a4_encode_rotated: cannot reserve %zu bytes of shared memory: %s", smem,
+                         cudaGetErrorString(e));
+            return (int)e;
+        }
+    }
+    const int64_t grid = (rows + rpc - 1) / rpc;
+    // Few long rows (decode-time activations): split each row's blocks over several CTAs; every
+    // CTA repeats the cheap transform and norm of its row.
+    const int bpr = (int)(k / 8);
+    const bool one_long_row = rpc == 1 && bpr >= NQ_ENC_THREADS;
+    int splits = 1;
+    if (one_long_row && grid < 148) {
+        splits = (int)((2 * 148 + grid - 1) / grid);
+        const int max_splits = bpr / 32;
+        if (splits > max_splits) splits = max_splits;
+        if (splits < 1) splits = 1;
+    }
+    int blocks_per_split = ((bpr + splits - 1) / splits + 31) / 32 * 32;
+    if (!one_long_row) blocks_per_split = 0x40000000;
+    splits = one_long_row ? (bpr + blocks_per_split - 1) / blocks_per_split : 1;
+    const float root = (float)sqrt((double)hadamard_block);
+    kernel<<<dim3((unsigned)grid, (unsigned)splits), NQ_ENC_THREADS, smem, stream>>>(
+        reinterpret_cast<const T*>(x), rows, (int)k, (int)hadamard_block, root, 1.0f / root, beta_table,
+        (float)sqrt((double)k), reinterpret_cast<uint32_t*>(out_codes), out_beta_ids, out_norms,
+        reinterpret_cast<__nv_bfloat16*>(out_decoded), blocks_per_split, rpc);
+    NQ_CHECK_LAUNCH("nq_a4_encode_rotated");
+    return NQ_OK;
+}
+
+}  // namespace
+
+extern "C" int nq_a4_encode_rotated(const void* x, int x_dtype, int64_t rows, int64_t k, int64_t hadamard_block,
+                                    const float* beta_table, uint8_t* out_codes, uint8_t* out_beta_ids,
+                                    float* out_norms, void* out_decoded, nq_stream_t stream) {
+    NQ_REQUIRE(x && beta_table && out_codes && out_beta_ids && out_norms, NQ_ERR_ARG,
+               "nq_a4_encode_rotated: null pointer");
+    NQ_REQUIRE(rows >= 1 && k % 32 == 0 && k >= 32 && k <= NQ_ROTATED_MAX_K, NQ_ERR_ARG,
+               "nq_a4_encode_rotated: k=%lld must be a multiple of 32 in [32, %d]", (long long)k, NQ_ROTATED_MAX_K);
+    NQ_REQUIRE(hadamard_block >= 8 && (hadamard_block & (hadamard_block - 1)) == 0 && k % hadamard_block == 0,
+               NQ_ERR_ARG, "nq_a4_encode_rotated: hadamard_block=%lld must be a power of two >= 8 dividing k",
+               (long long)hadamard_block);
+    NQ_REQUIRE(nq_aligned16(x) && (!out_decoded || nq_aligned16(out_decoded)) && nq_aligned16(out_codes), NQ_ERR_ALIGN,
+               "nq_a4_encode_rotated: 16-byte alignment required");
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    switch (x_dtype) {
+        case NQ_F32: return launch_encode_rotated<float>(x, rows, k, hadamard_block, beta_table, out_codes, out_beta_ids, out_norms, out_decoded, s);
+        case NQ_BF16: return launch_encode_rotated<__nv_bfloat16>(x, rows, k, hadamard_block, beta_table, out_codes, out_beta_ids, out_norms, out_decoded, s);
+        case NQ_F16: return launch_encode_rotated<__half>(x, rows, k, hadamard_block, beta_table, out_codes, out_beta_ids, out_norms, out_decoded, s);
+        default: nq_set_error("nq_a4_encode_rotated: unknown dtype %d", x_dtype); return NQ_ERR_ARG;
+    }
+}

@@ -11,55 +11,12 @@
 #include <math.h>
 
 #include "nq_common.cuh"
+#include "nq_rotate_core.cuh"
 
 namespace {
 
-template <typename T> __device__ __forceinline__ float round_to(float v);
-template <> __device__ __forceinline__ float round_to<float>(float v) { return v; }
-template <> __device__ __forceinline__ float round_to<__nv_bfloat16>(float v) { return nq_bf16_round(v); }
-template <> __device__ __forceinline__ float round_to<__half>(float v) { return __half2float(__float2half_rn(v)); }
-
-// store 8 consecutive results (16-byte aligned) in the tensor dtype
-template <typename T> __device__ __forceinline__ void store8(T* p, const float v[8]);
-template <> __device__ __forceinline__ void store8<float>(float* p, const float v[8]) {
-    reinterpret_cast<float4*>(p)[0] = make_float4(v[0], v[1], v[2], v[3]);
-    reinterpret_cast<float4*>(p)[1] = make_float4(v[4], v[5], v[6], v[7]);
-}
-template <> __device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16* p, const float v[8]) {
-    *reinterpret_cast<uint4*>(p) = nq_pack_bf16x8(v);
-}
-template <> __device__ __forceinline__ void store8<__half>(__half* p, const float v[8]) {
-    uint32_t w[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
-        w[i] = *reinterpret_cast<const uint32_t*>(&h);
-    }
-    *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
-}
-
-
-// Radix-8 passes: a thread takes 8 elements spaced `w` apart, runs three butterfly stages
-// (widths w, 2w, 4w -- exactly the reference's stage order, every result rounded to the
-// tensor dtype) in registers and writes them back, so a row needs log2(n)/3 shared-memory
-// round trips instead of log2(n).  The first pass reads its 8 consecutive elements straight
-// from global memory, the last pass applies the 1/sqrt(n) division and stores to global.
-template <typename T, int STAGES>
-__device__ __forceinline__ void butterflies(float v[8]) {
-#pragma unroll
-    for (int s = 0; s < STAGES; ++s) {
-        const int h = 1 << s;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            if ((j & h) == 0) {
-                const float l = v[j], r = v[j | h];
-                v[j] = round_to<T>(nq_add(l, r));
-                v[j | h] = round_to<T>(nq_sub(l, r));
-            }
-        }
-    }
-}
-
+// The butterfly passes live in nq_rotate_core.cuh; the last pass here applies the 1/sqrt(n)
+// division and stores to global memory in the tensor dtype.
 template <typename T>
 __global__ void __launch_bounds__(256)
 nq_hadamard_kernel(const T* __restrict__ x, T* __restrict__ out, int64_t rows, int n, int rows_per_cta,
@@ -68,49 +25,14 @@ nq_hadamard_kernel(const T* __restrict__ x, T* __restrict__ out, int64_t rows, i
     const int64_t row0 = (int64_t)blockIdx.x * rows_per_cta;
     const int nrows = (int)min((int64_t)rows_per_cta, rows - row0);
     const int total = nrows * n;           // elements of this CTA (rows are independent, n >= 8)
-    const int groups = total >> 3;
-    int log_n = 0;
-    while ((1 << log_n) < n) ++log_n;
-
-    // pass 0: widths 1, 2, 4 on 8 consecutive elements loaded from global memory
-    for (int g = threadIdx.x; g < groups; g += 256) {
-        float v[8];
-        nq_load8<T>(x + row0 * n + (int64_t)g * 8, v);
-        butterflies<T, 3>(v);
-        float4* dst = reinterpret_cast<float4*>(buf + g * 8);
-        dst[0] = make_float4(v[0], v[1], v[2], v[3]);
-        dst[1] = make_float4(v[4], v[5], v[6], v[7]);
-    }
-    __syncthreads();
-    int done = 3;
-    while (done < log_n) {
-        const int stages = min(3, log_n - done);
-        const int w = 1 << done;               // spacing of the elements a thread combines
-        const int span = w << stages;          // elements covered by one group family
-        const int per = 1 << stages;           // elements per thread in this pass
-        const int work = total >> stages;
-        for (int t = threadIdx.x; t < work; t += 256) {
-            const int base = (t / w) * span + (t % w);
-            float v[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = j < per ? buf[base + j * w] : 0.0f;
-            if (stages == 3) butterflies<T, 3>(v);
-            else if (stages == 2) butterflies<T, 2>(v);
-            else butterflies<T, 1>(v);
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-                if (j < per) buf[base + j * w] = v[j];
-        }
-        __syncthreads();
-        done += stages;
-    }
-    for (int g = threadIdx.x; g < groups; g += 256) {
+    nq_fwht_rows_to_smem<T>(x + row0 * n, buf, total, n);
+    for (int g = threadIdx.x; g < (total >> 3); g += 256) {
         const float4 lo = reinterpret_cast<const float4*>(buf + g * 8)[0];
         const float4 hi = reinterpret_cast<const float4*>(buf + g * 8)[1];
         float v[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
 #pragma unroll
         for (int j = 0; j < 8; ++j) v[j] = nq_div_by(v[j], root, inv_root);
-        store8<T>(out + row0 * n + (int64_t)g * 8, v);
+        nq_store8<T>(out + row0 * n + (int64_t)g * 8, v);
     }
 }
 

@@ -18,6 +18,7 @@ from torch import nn
 from .formats import ACTIVATION_BETAS, KEY_BETAS, VALUE_BETAS, WEIGHT_BETAS, tensor_dither_seed
 from .fused_linear import FusedNQRTLinear, SharedHadamardCache, SharedPackedActivationCache
 from .hf_backend import BatchedNQKVLlamaCache, install_batched_nqkv_llama_backend
+from .norm import fuse_rmsnorm_
 from .rotation import hadamard
 from .runtime.w4a4 import quantize_weight_cuda
 
@@ -88,6 +89,7 @@ def build_llama_w4a4kv4(*, hidden_size: int, intermediate_size: int, num_layers:
                                   page_size=page_size, key_betas=KEY_BETAS, value_betas=VALUE_BETAS,
                                   dtype=torch.bfloat16, device=device)
     install_batched_nqkv_llama_backend(model, cache)
+    fuse_rmsnorm_(model)  # one launch per normalisation instead of six tensor kernels
     return model, cache
 
 

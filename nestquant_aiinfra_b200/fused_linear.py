@@ -17,7 +17,7 @@ from torch import nn
 
 from .rotation import hadamard
 from .runtime.w4a4 import (PreparedNQA4Activation, PreparedNQRTLinear, linear_packed_w4a4, prepare_fused_linear,
-                           quantize_activation_cuda)
+                           quantize_activation_cuda, can_rotate_in_encoder)
 
 _BACKENDS = {"packed_w4a4_cuda_mma", "packed_w4a4_cuda_gemv_m1", "packed_w4a4"}
 
@@ -53,6 +53,20 @@ class SharedHadamardCache:
         self.misses += 1
         return output
 
+    def note_rotation_in_encoder(self, inputs: torch.Tensor) -> None:
+        """Same hit / miss accounting as ``transform`` when the encoder launch does the rotation itself."""
+        if torch.is_grad_enabled():
+            raise RuntimeError("shared Hadamard caching requires inference or no-grad mode")
+        if self._input is inputs and self._remaining > 0:
+            self.hits += 1
+            self._remaining -= 1
+            if self._remaining == 0:
+                self.clear()
+            return
+        self._input, self._output = inputs, None
+        self._remaining = self.uses_per_input - 1
+        self.misses += 1
+
     def clear(self) -> None:
         self._input = self._output = None
         self._remaining = 0
@@ -74,7 +88,8 @@ class SharedPackedActivationCache:
         self.misses = 0
 
     def encode(self, inputs: torch.Tensor, *, q: int, betas: tuple[float, ...],
-               beta_table: torch.Tensor | None = None) -> tuple[PreparedNQA4Activation, bool]:
+               beta_table: torch.Tensor | None = None,
+               hadamard_block: int | None = None) -> tuple[PreparedNQA4Activation, bool]:
         if torch.is_grad_enabled():
             raise RuntimeError("shared A4 caching requires inference or no-grad mode")
         if self._input is inputs and self._packed is not None:
@@ -84,7 +99,8 @@ class SharedPackedActivationCache:
             if self._remaining == 0:
                 self.clear()
             return packed, False
-        packed = quantize_activation_cuda(inputs, q=q, betas=betas, beta_table=beta_table)
+        packed = quantize_activation_cuda(inputs, q=q, betas=betas, beta_table=beta_table,
+                                          hadamard_block=hadamard_block)
         self._input, self._packed = inputs, packed
         self._remaining = self.uses_per_input - 1
         self.misses += 1
@@ -151,6 +167,8 @@ class FusedNQRTLinear(nn.Module):
             raise ValueError("output_dtype must be float16, bfloat16, float32, or None")
         self.weight_name = weight_name
         self.input_hadamard = input_hadamard
+        # block-diagonal rotation of the input (tensor-parallel K shards); set by the owner, None = off
+        self.input_rotation_block: int | None = None
         self.input_transform_cache = input_transform_cache
         self.output_dtype = output_dtype
         self.compute_backend = compute_backend
@@ -204,21 +222,39 @@ class FusedNQRTLinear(nn.Module):
         if inputs.device.type != "cuda":
             raise ValueError("FusedNQRTLinear requires CUDA inputs")
         original_dtype = inputs.dtype
-        if self.input_transform_cache is not None:
-            compute_inputs = self.input_transform_cache.transform(inputs)
+        # The rotation of the input runs inside the encoder launch when the sizes allow it
+        # (bit-identical to hadamard() followed by the encoder); otherwise as its own launch.
+        wanted_block = self.in_features if self.input_hadamard else self.input_rotation_block
+        rotate_in_encoder = (wanted_block is not None
+                             and inputs.dtype in (torch.bfloat16, torch.float16, torch.float32)
+                             and can_rotate_in_encoder(self.in_features, wanted_block))
+        if rotate_in_encoder:
+            if self.input_transform_cache is not None:
+                self.input_transform_cache.note_rotation_in_encoder(inputs)
+            compute_inputs, block = inputs, wanted_block
         else:
-            compute_inputs = hadamard(inputs) if self.input_hadamard else inputs
+            block = None
+            if self.input_transform_cache is not None:
+                compute_inputs = self.input_transform_cache.transform(inputs)
+            elif self.input_hadamard:
+                compute_inputs = hadamard(inputs)
+            elif self.input_rotation_block is not None:
+                b = self.input_rotation_block
+                compute_inputs = hadamard(inputs.reshape(*inputs.shape[:-1], self.in_features // b, b)).reshape(inputs.shape)
+            else:
+                compute_inputs = inputs
         prepared = self._prepared_for(inputs.device)
         beta_table = self.activation_beta_table
         if beta_table.device != inputs.device:
             beta_table = beta_table.to(inputs.device)
         if self.packed_activation_cache is None:
             packed = quantize_activation_cuda(compute_inputs, q=self.activation_q, betas=self.activation_betas,
-                                              beta_table=beta_table)
+                                              beta_table=beta_table, hadamard_block=block)
             encoded = True
         else:
             packed, encoded = self.packed_activation_cache.encode(
-                compute_inputs, q=self.activation_q, betas=self.activation_betas, beta_table=beta_table)
+                compute_inputs, q=self.activation_q, betas=self.activation_betas, beta_table=beta_table,
+                hadamard_block=block)
         self.a4_call_count += 1
         self.a4_encode_count += int(encoded)
         outputs = linear_packed_w4a4(packed, prepared)

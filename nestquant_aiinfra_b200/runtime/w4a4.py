@@ -154,14 +154,27 @@ def prepare_fused_linear(record, *, device: torch.device | str = "cuda") -> Prep
     )
 
 
+ROTATED_MAX_K = 16384  # NQ_ROTATED_MAX_K of the library header
+
+
+def can_rotate_in_encoder(feature_count: int, hadamard_block: int) -> bool:
+    """Whether ``quantize_activation_cuda(..., hadamard_block=...)`` can fuse the rotation for these sizes."""
+    return (isinstance(hadamard_block, int) and hadamard_block >= 8 and hadamard_block & (hadamard_block - 1) == 0
+            and feature_count % 32 == 0 and 32 <= feature_count <= ROTATED_MAX_K
+            and feature_count % hadamard_block == 0)
+
+
 def quantize_activation_cuda(
     inputs: torch.Tensor, *, q: int, betas: Sequence[float],
-    beta_table: torch.Tensor | None = None, keep_decoded: bool = True,
+    beta_table: torch.Tensor | None = None, keep_decoded: bool = True, hadamard_block: int | None = None,
 ) -> PreparedNQA4Activation:
     """Encode floating activations into packed NQA4 payloads in one launch.
 
     Bit-exact with ``pack_nestquant_indices(quantize_rows(inputs.float(), q, betas))``
-    of the reference CPU path.
+    of the reference CPU path.  With ``hadamard_block`` the rows are first rotated by the
+    normalised Hadamard transform of that block size (the whole row when it equals the feature
+    count) inside the same launch; the result equals ``quantize_activation_cuda(hadamard(inputs))``
+    bit for bit (see ``can_rotate_in_encoder``).
     """
     if not isinstance(inputs, torch.Tensor) or not inputs.is_floating_point():
         raise TypeError("inputs must be a floating-point tensor")
@@ -182,6 +195,10 @@ def quantize_activation_cuda(
         raise ValueError("inputs must use float16, bfloat16, or float32")
     k = inputs.shape[-1]
     rows = inputs.reshape(-1, k)
+    if hadamard_block is not None:
+        if not can_rotate_in_encoder(k, hadamard_block):
+            raise ValueError("hadamard_block must be a power of two >= 8 dividing a feature count <= 16384")
+        rows = rows.contiguous()
     if rows.stride(-1) != 1 or (rows.stride(0) * rows.element_size()) % 16 or rows.data_ptr() % 16:
         rows = rows.contiguous()
     device = inputs.device
@@ -195,9 +212,14 @@ def quantize_activation_cuda(
     beta_ids = torch.empty(m * k // 32, dtype=torch.uint8, device=device)
     norms = torch.empty(m, dtype=torch.float32, device=device)
     decoded = torch.empty((m, k), dtype=torch.bfloat16, device=device) if keep_decoded else None
-    status = _lib.lib().nq_a4_encode(
-        _ptr(rows), _DTYPE_TAG[inputs.dtype], _I64(m), _I64(k), _I64(rows.stride(0)), _ptr(beta_table),
-        _ptr(codes), _ptr(beta_ids), _ptr(norms), _ptr(decoded), _stream(device))
+    if hadamard_block is None:
+        status = _lib.lib().nq_a4_encode(
+            _ptr(rows), _DTYPE_TAG[inputs.dtype], _I64(m), _I64(k), _I64(rows.stride(0)), _ptr(beta_table),
+            _ptr(codes), _ptr(beta_ids), _ptr(norms), _ptr(decoded), _stream(device))
+    else:
+        status = _lib.lib().nq_a4_encode_rotated(
+            _ptr(rows), _DTYPE_TAG[inputs.dtype], _I64(m), _I64(k), _I64(hadamard_block), _ptr(beta_table),
+            _ptr(codes), _ptr(beta_ids), _ptr(norms), _ptr(decoded), _stream(device))
     _lib.check(status, "quantize_activation_cuda")
     return PreparedNQA4Activation(
         code_payload=codes, beta_payload=beta_ids, row_norms=norms, beta_table=beta_table,

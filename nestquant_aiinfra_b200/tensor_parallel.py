@@ -111,6 +111,7 @@ class RowParallelNQRTLinear(nn.Module):
             rotated = block_hadamard(weight_slice.float(), self.hadamard_block)
             prepared = quantize_weight_cuda(rotated, betas=weight_betas, dither_seed=dither_seed)
             self.inner = FusedNQRTLinear(prepared, input_hadamard=False, activation_betas=tuple(activation_betas))
+            self.inner.input_rotation_block = self.hadamard_block  # rotated inside the encoder launch when it fits
 
     @property
     def packed_device_bytes(self) -> int:
@@ -122,7 +123,7 @@ class RowParallelNQRTLinear(nn.Module):
         if self._project is not None:
             partial = self._project(x_slice)
         else:
-            partial = self.inner(block_hadamard(x_slice, self.hadamard_block))
+            partial = self.inner(x_slice)
         if self.world > 1:
             import torch.distributed as dist
 

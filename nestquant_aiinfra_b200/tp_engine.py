@@ -17,6 +17,7 @@ from .engine import BatchedNQKVLlamaRunner
 from .formats import ACTIVATION_BETAS, KEY_BETAS, VALUE_BETAS, WEIGHT_BETAS, tensor_dither_seed
 from .fused_linear import FusedNQRTLinear, SharedHadamardCache, SharedPackedActivationCache
 from .hf_backend import BatchedNQKVLlamaCache, install_batched_nqkv_llama_backend
+from .norm import fuse_rmsnorm_
 from .rotation import hadamard
 from .runtime.w4a4 import quantize_activation_cuda, quantize_weight_cuda
 from .tensor_parallel import RowParallelNQRTLinear
@@ -80,6 +81,7 @@ def build_llama_tp_shard(*, hidden_size: int, intermediate_size: int, num_layers
                                   num_kv_heads=num_kv_heads // world, head_dim=head_dim, max_cache_len=max_cache_len,
                                   key_betas=KEY_BETAS, value_betas=VALUE_BETAS, dtype=torch.bfloat16, device=device)
     install_batched_nqkv_llama_backend(model, cache)
+    fuse_rmsnorm_(model)  # one launch per normalisation instead of six tensor kernels
     return model, cache
 
 

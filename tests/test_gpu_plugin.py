@@ -96,3 +96,40 @@ def test_fused_linear_errors(oracle):
         layer(torch.zeros(1, 128, device="cuda"))
     with pytest.raises(ValueError):
         layer(torch.zeros(1, 256))
+
+
+@pytest.mark.parametrize("rows,n,dtype", [(64, 2048, torch.bfloat16), (1, 8192, torch.bfloat16), (37, 448, torch.float16),
+                                          (5, 2048, torch.float32)])
+def test_rms_norm_follows_the_llama_formula(rows, n, dtype):
+    """One-launch RMS norm vs the tensor-op formula of LlamaRMSNorm; only the order of the sum of squares differs."""
+    from nestquant_aiinfra_b200.norm import rms_norm
+
+    x = (torch.randn(rows, n, generator=rng(900 + n)) * 3).to(dtype).cuda()
+    w = (1 + 0.1 * torch.randn(n, generator=rng(901))).to(dtype).cuda()
+    eps = 1e-5
+    xf = x.float()
+    expected = w * (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(dtype)
+    got = rms_norm(x, w, eps)
+    assert got.dtype == dtype and got.shape == x.shape and torch.equal(got, rms_norm(x, w, eps))
+    ulp = {torch.bfloat16: 2.0 ** -8, torch.float16: 2.0 ** -11, torch.float32: 2.0 ** -22}[dtype]
+    diff = (got.float() - expected.float()).abs()
+    assert float((diff / expected.float().abs().clamp_min(1e-3)).max()) <= 2.5 * ulp   # at most one rounding step apart
+    assert float((diff > 0).float().mean()) < 0.02
+
+
+def test_fuse_rmsnorm_replaces_llama_norms():
+    from transformers import LlamaConfig, LlamaForCausalLM
+
+    from nestquant_aiinfra_b200.norm import FusedRMSNorm, fuse_rmsnorm_
+
+    config = LlamaConfig(hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=4,
+                         num_key_value_heads=2, head_dim=64, vocab_size=512)
+    torch.manual_seed(0)
+    model = LlamaForCausalLM(config).bfloat16().cuda().eval()
+    ids = torch.randint(0, 512, (2, 9), generator=rng(77)).cuda()
+    with torch.no_grad():
+        before = model(ids).logits.float()
+        assert fuse_rmsnorm_(model) == 5 and fuse_rmsnorm_(model) == 0   # 2 per layer + the final norm
+        assert isinstance(model.model.norm, FusedRMSNorm)
+        after = model(ids).logits.float()
+    assert rel_fro(after.cpu().numpy(), before.cpu().numpy()) < 2e-2

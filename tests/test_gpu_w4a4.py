@@ -69,6 +69,33 @@ def test_encoder_strided_rows_and_leading_dims(rt, oracle):
     assert np.array_equal(act.row_norms.cpu().numpy(), norms)
 
 
+@pytest.mark.parametrize("rows,k,block,dtype", [
+    (1, 2048, 2048, torch.bfloat16), (5, 8192, 8192, torch.bfloat16), (64, 2048, 2048, torch.bfloat16),
+    (3000, 2048, 2048, torch.bfloat16), (300, 64, 64, torch.float32), (33, 4096, 4096, torch.float16),
+    (16, 14336, 2048, torch.bfloat16), (7, 3584, 512, torch.bfloat16), (2, 16384, 16384, torch.float32)])
+def test_rotation_inside_the_encoder_equals_two_launches(rt, rows, k, block, dtype):
+    """nq_a4_encode_rotated == nq_hadamard then nq_a4_encode, bit for bit (whole-row and block-diagonal rotation)."""
+    from nestquant_aiinfra_b200.rotation import hadamard
+
+    x = torch.randn(rows, k, generator=rng(600 + rows)).to(dtype).cuda()
+    rotated = hadamard(x.reshape(rows, k // block, block)).reshape(rows, k)
+    two = rt.quantize_activation_cuda(rotated, q=14, betas=ACT_BETAS)
+    one = rt.quantize_activation_cuda(x, q=14, betas=ACT_BETAS, hadamard_block=block)
+    torch.cuda.synchronize()
+    assert torch.equal(one.code_payload, two.code_payload) and torch.equal(one.beta_payload, two.beta_payload)
+    assert torch.equal(one.row_norms, two.row_norms) and torch.equal(one.decoded, two.decoded)
+
+
+def test_rotation_inside_the_encoder_argument_errors(rt):
+    x = torch.zeros(4, 2048, dtype=torch.bfloat16, device="cuda")
+    assert rt.can_rotate_in_encoder(2048, 2048) and rt.can_rotate_in_encoder(14336, 2048)
+    assert not rt.can_rotate_in_encoder(32768, 32768) and not rt.can_rotate_in_encoder(2048, 96)
+    with pytest.raises(ValueError):
+        rt.quantize_activation_cuda(x, q=14, betas=ACT_BETAS, hadamard_block=96)
+    with pytest.raises(ValueError):
+        rt.quantize_activation_cuda(x, q=14, betas=ACT_BETAS, hadamard_block=4096)
+
+
 def test_activation_decoder_boundary_codewords_exact(rt, oracle):
     # mirrors reference tests/unit/runtime/test_cuda_w4a4_mma.py:78-97
     k = 32
