@@ -506,6 +506,27 @@ NQ_HD uint32_t nq_eval_candidate_from_lam(const float x[8], const float lam[8], 
     return word;
 }
 
+// Cheap exact classification of one candidate of the undithered search: the lattice point
+// lam = Q(x / beta), the error "as if lam were reproduced" (the reference's sequential sum), and
+// the position of lam relative to 14*V(E8): +1 strictly inside (the reconstruction IS lam and
+// asif is the candidate's error), 0 on the boundary (error >= asif), -1 strictly outside
+// (error > 353 beta^2).
+NQ_HD int nq_classify_candidate(const float x[8], float bt, float lam[8], float& asif) {
+    const float rbeta = nq_rcp(bt);
+    float y[8], r[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) y[j] = nq_div_by(x[j], bt, rbeta);
+    nq_e8_nearest_guarded(y, lam);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) r[j] = nq_mul(lam[j], bt);
+    asif = nq_sqdist8_seq(r, x);
+    // |lam|^2 <= 96 < (14/sqrt(2))^2 puts lam inside the inscribed ball of 14*V: no facet test needed
+    float norm2 = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) norm2 = nq_fma(lam[j], lam[j], norm2);
+    return norm2 <= 96.0f ? 1 : nq_e8_cell_class(lam);
+}
+
 // Variant of nq_encode_block_fastpass for a caller with a work queue: every candidate whose
 // lattice point lies ON the boundary of 14*V(E8) is handed to on_boundary(b, lam) as soon as it
 // is found (unless a better finished candidate already rules it out), the caller evaluates it
@@ -523,18 +544,8 @@ NQ_HD void nq_encode_block_fastpass_push(const float x[8], const float* beta, in
     // stalls on instruction fetch.
 #pragma unroll 1
     for (int b = 0; b < 4; ++b) {
-        const float bt = beta[b], rbeta = nq_rcp(bt);
-        float y[8], lam[8], r[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) y[j] = nq_div_by(x[j], bt, rbeta);
-        nq_e8_nearest_guarded(y, lam);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) r[j] = nq_mul(lam[j], bt);
-        const float asif = nq_sqdist8_seq(r, x);
-        float norm2 = 0.0f;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) norm2 = nq_fma(lam[j], lam[j], norm2);
-        const int cls = norm2 <= 96.0f ? 1 : nq_e8_cell_class(lam);
+        float lam[8], asif;
+        const int cls = nq_classify_candidate(x, beta[b], lam, asif);
         if (cls > 0) {
             if (best < 0 || asif < best_err) {
                 best = b;

@@ -35,7 +35,7 @@ nq_encode_rows_kernel(const T* __restrict__ x, int64_t rows, int k, int64_t row_
                       const float* __restrict__ beta_table, float sqrt_k,
                       uint32_t* __restrict__ codes, uint8_t* __restrict__ beta_ids,
                       float* __restrict__ norms, __nv_bfloat16* __restrict__ decoded,
-                      uint32_t counter_base, int blocks_per_split, int rpc) {
+                      uint32_t counter_base, int blocks_per_split, int rpc, int four_lanes) {
     extern __shared__ __align__(16) float smem[];
     const int bpr = k >> 3;
     const int64_t row0 = (int64_t)blockIdx.x * rpc;
@@ -46,7 +46,7 @@ nq_encode_rows_kernel(const T* __restrict__ x, int64_t rows, int k, int64_t row_
     nq_encode_rows_cta<T, DITHER>(x + row0 * row_stride, row_stride, nrows, nrows, k, beta_table, sqrt_k, codes + g0,
                           beta_ids + (g0 >> 2), norms + row0, decoded ? decoded + g0 * 8 : nullptr,
                           counter_base + (uint32_t)g0 * 8u, smem, blk_begin, blk_begin + blocks_per_split,
-                          blockIdx.y == 0, rpc);
+                          blockIdx.y == 0, rpc, four_lanes != 0);
 }
 
 // ---------------------------------------------------------------------------
@@ -103,11 +103,8 @@ static int launch_encode(const void* x, int64_t rows, int64_t k, int64_t row_str
                          const float* beta_table, uint8_t* out_codes, uint8_t* out_beta_ids,
                          float* out_norms, void* out_decoded, cudaStream_t stream,
                          int use_dither = 0, uint32_t counter_base = 0) {
-    // Undithered launches with many long rows give each CTA several rows, so that a batch of the
-    // search queue fills up; otherwise one long row (or one CTA's worth of short rows) per CTA.
-    int rpc = nq_encode_rows_per_cta((int)k);
-    const int many = nq_encode_rows_per_cta_many((int)k);
-    if (!use_dither && many > rpc && rows / many >= 5 * 148) rpc = many;
+    const NqEncodePlan plan = nq_encode_plan(rows, (int)k, use_dither != 0);
+    const int rpc = plan.rpc, splits = plan.splits, blocks_per_split = plan.blocks_per_split;
     const size_t smem = nq_encode_smem_floats((int)k, rpc) * sizeof(float);
     auto kernel = use_dither ? nq_encode_rows_kernel<T, true> : nq_encode_rows_kernel<T, false>;
     if (smem > 48 * 1024) {
@@ -118,23 +115,10 @@ static int launch_encode(const void* x, int64_t rows, int64_t k, int64_t row_str
         }
     }
     const int64_t grid = (rows + rpc - 1) / rpc;
-    // Few long rows (decode-time activations): split each row's blocks over several CTAs.
-    const int bpr = (int)(k / 8);
-    const bool one_long_row = rpc == 1 && bpr >= NQ_ENC_THREADS;
-    int splits = 1;
-    if (one_long_row && grid < 148) {
-        splits = (int)((2 * 148 + grid - 1) / grid);
-        const int max_splits = bpr / 32;  // one warp step per CTA at the finest
-        if (splits > max_splits) splits = max_splits;
-        if (splits < 1) splits = 1;
-    }
-    int blocks_per_split = ((bpr + splits - 1) / splits + 31) / 32 * 32;
-    if (!one_long_row) blocks_per_split = 0x40000000;
-    splits = one_long_row ? (bpr + blocks_per_split - 1) / blocks_per_split : 1;
     kernel<<<dim3((unsigned)grid, (unsigned)splits), NQ_ENC_THREADS, smem, stream>>>(
         reinterpret_cast<const T*>(x), rows, (int)k, row_stride, beta_table,
         (float)sqrt((double)k), reinterpret_cast<uint32_t*>(out_codes), out_beta_ids, out_norms,
-        reinterpret_cast<__nv_bfloat16*>(out_decoded), counter_base, blocks_per_split, rpc);
+        reinterpret_cast<__nv_bfloat16*>(out_decoded), counter_base, blocks_per_split, rpc, plan.four_lanes ? 1 : 0);
     NQ_CHECK_LAUNCH("nq_a4_encode");
     return NQ_OK;
 }

@@ -47,6 +47,46 @@ __host__ __device__ inline size_t nq_encode_smem_floats(int k, int rows_layout =
     return body + (size_t)rpc * 10 + 4;
 }
 
+// Launch geometry of an encoder launch over `rows` rows of k features.
+//   rpc               rows per CTA (also the shared-memory layout)
+//   splits            CTAs per row (gridDim.y); each takes blocks_per_split blocks of phase 3
+//   four_lanes        latency mode of small launches: the four candidates of a block on four lanes
+struct NqEncodePlan {
+    int rpc, splits, blocks_per_split;
+    bool four_lanes;
+};
+inline NqEncodePlan nq_encode_plan(int64_t rows, int k, bool dither) {
+    NqEncodePlan plan;
+    const int bpr = k / 8;
+    const int slots = 148 * 5;  // resident CTAs of the device this library is built for
+    plan.rpc = nq_encode_rows_per_cta(k);
+    plan.four_lanes = !dither && rows * bpr <= (int64_t)slots * (NQ_ENC_THREADS / 4);
+    if (plan.four_lanes) {
+        if (bpr < NQ_ENC_THREADS / 4) plan.rpc = (NQ_ENC_THREADS / 4) / bpr;  // one round of blocks per CTA
+        else plan.rpc = 1;
+    } else if (!dither) {
+        // many long rows: several per CTA, so that a batch of the search queue fills up
+        const int many = nq_encode_rows_per_cta_many(k);
+        if (many > plan.rpc && rows / many >= slots) plan.rpc = many;
+    }
+    const int64_t grid = (rows + plan.rpc - 1) / plan.rpc;
+    // Few long rows (decode-time activations): split each row's blocks over several CTAs, every
+    // one of which repeats the cheap norm of its row.
+    const bool splittable = plan.rpc == 1 && bpr > 32;
+    plan.splits = 1;
+    if (splittable && plan.four_lanes) {
+        plan.splits = bpr / 32;
+    } else if (splittable && bpr >= NQ_ENC_THREADS && grid < 148) {
+        plan.splits = (int)((2 * 148 + grid - 1) / grid);
+        if (plan.splits > bpr / 32) plan.splits = bpr / 32;
+    }
+    if (plan.splits < 1) plan.splits = 1;
+    plan.blocks_per_split = ((bpr + plan.splits - 1) / plan.splits + 31) / 32 * 32;
+    if (plan.splits == 1) plan.blocks_per_split = 0x40000000;
+    else plan.splits = (bpr + plan.blocks_per_split - 1) / plan.blocks_per_split;
+    return plan;
+}
+
 // Block load of the encoder: from global memory in the tensor dtype, or (GLOBAL_IN = false)
 // float32 values that an earlier phase of the same kernel left in shared memory.
 template <typename T, bool GLOBAL_IN>
@@ -69,7 +109,7 @@ __device__ __forceinline__ void nq_encode_rows_cta(
     const float* __restrict__ beta_table, float sqrt_k, uint32_t* __restrict__ codes,
     uint8_t* __restrict__ beta_ids, float* __restrict__ norms, __nv_bfloat16* __restrict__ decoded,
     uint32_t counter_base, float* smem, int blk_begin = 0, int blk_end = 0x7fffffff,
-    bool write_norms = true, int rows_layout = 0) {
+    bool write_norms = true, int rows_layout = 0, bool four_lanes = false) {
     static_assert(GLOBAL_IN || sizeof(T) == 4, "shared-memory input is float32");
     const int rows_per_cta = rows_layout > 0 ? rows_layout : nq_encode_rows_per_cta(k);
     const int bpr = k >> 3;
@@ -183,10 +223,75 @@ __device__ __forceinline__ void nq_encode_rows_cta(
     unsigned short* item_meta = reinterpret_cast<unsigned short*>(out_word + BATCH);  // [CAP] (slot << 2) | beta
     unsigned* queue_count = reinterpret_cast<unsigned*>(item_meta + CAP);
     const bool want_dec = decoded != nullptr;
-    for (int base = blk_begin; base < enc_end; base += BATCH) {
+    // Latency mode for small launches (four_lanes): the four candidates of a block go to four
+    // neighbouring lanes, so a block costs one candidate evaluation of latency instead of four.
+    // A batch then holds at most CAP / 4 blocks, which the queue can always take.
+    const int batch_cap = four_lanes ? CAP / 4 : BATCH;
+    for (int base = blk_begin; base < enc_end; base += batch_cap) {
         if (tid == 0) *queue_count = 0u;
         __syncthreads();  // also: the previous batch has been written out
-        const int batch_n = min(BATCH, enc_end - base);
+        const int batch_n = min(batch_cap, enc_end - base);
+        if (four_lanes) {
+            for (int slot0 = 0; slot0 < batch_n; slot0 += NT / 4) {
+                const int slot = slot0 + (tid >> 2), c = tid & 3;
+                const bool valid = slot < batch_n;
+                const int b = base + (valid ? slot : 0);
+                const int row_r = b / bpr, bb = b - row_r * bpr;
+                float v[8];
+                if (row_r < valid_rows) {
+                    nq_encode_load8<T, GLOBAL_IN>(x + (int64_t)row_r * row_stride + (int64_t)bb * 8, v);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) v[j] = 0.0f;
+                }
+                const float s = scale[row_r], ds = dscale[row_r];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = nq_mul(v[j], s);
+                const float bt = beta_table[c];
+                float lam[8], asif;
+                const int cls = nq_classify_candidate(v, bt, lam, asif);
+                const unsigned long long mine = (valid && cls > 0) ? nq_candidate_key(asif, c) : ~0ull;
+                unsigned long long best_key = mine;
+#pragma unroll
+                for (int off = 1; off < 4; off <<= 1) {
+                    const unsigned long long other = __shfl_xor_sync(0xffffffffu, best_key, off);
+                    best_key = other < best_key ? other : best_key;
+                }
+                if (valid) {
+                    const bool have_best = best_key != ~0ull;
+                    const float best_err = nq_bits_float((uint32_t)(best_key >> 8));
+                    if (cls > 0 && mine == best_key) {  // keys of one block differ in the beta index: one winner
+                        out_key[slot] = mine;
+                        out_word[slot] = nq_lattice_to_codeword(lam);
+                        uint4 dec = make_uint4(0, 0, 0, 0);
+                        if (want_dec) {
+                            float recon[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) recon[j] = nq_mul(nq_mul(lam[j], bt), ds);
+                            dec = nq_pack_bf16x8(recon);
+                        }
+                        out_dec[slot] = dec;
+                    } else if (!have_best && c == 0) {
+                        out_key[slot] = ~0ull;
+                        out_word[slot] = 0u;
+                        out_dec[slot] = make_uint4(0, 0, 0, 0);
+                    }
+                    // boundary: error >= asif; outside: error > 353 beta^2 -- queued unless the best inside candidate rules it out
+                    const bool queue_it = cls == 0 ? !(have_best && asif > best_err)
+                                                   : (cls < 0 && !(have_best && 353.0f * bt * bt > best_err));
+                    if (queue_it) {
+                        const unsigned idx = atomicAdd(queue_count, 1u);  // at most 4 * batch_cap = CAP entries
+                        float4* dx = reinterpret_cast<float4*>(item_x + idx * 8);
+                        dx[0] = make_float4(v[0], v[1], v[2], v[3]);
+                        dx[1] = make_float4(v[4], v[5], v[6], v[7]);
+                        float4* dl = reinterpret_cast<float4*>(item_lam + idx * 8);
+                        dl[0] = make_float4(lam[0], lam[1], lam[2], lam[3]);
+                        dl[1] = make_float4(lam[4], lam[5], lam[6], lam[7]);
+                        item_meta[idx] = (unsigned short)((slot << 2) | c);
+                    }
+                }
+            }
+        } else
         for (int slot = tid; slot < batch_n; slot += NT) {
             const int b = base + slot;
             const int row_r = b / bpr, bb = b - row_r * bpr;

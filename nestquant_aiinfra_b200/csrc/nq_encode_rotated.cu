@@ -21,7 +21,7 @@ __global__ void __launch_bounds__(NQ_ENC_THREADS, 5)
 nq_encode_rotated_kernel(const T* __restrict__ x, int64_t rows, int k, int hadamard_block, float root, float inv_root,
                          const float* __restrict__ beta_table, float sqrt_k, uint32_t* __restrict__ codes,
                          uint8_t* __restrict__ beta_ids, float* __restrict__ norms,
-                         __nv_bfloat16* __restrict__ decoded, int blocks_per_split, int rpc) {
+                         __nv_bfloat16* __restrict__ decoded, int blocks_per_split, int rpc, int four_lanes) {
     extern __shared__ __align__(16) float smem[];
     float* rotated = smem;                       // [rpc][k] float32 values of dtype T
     float* encoder_smem = smem + (size_t)rpc * k;
@@ -38,16 +38,15 @@ nq_encode_rotated_kernel(const T* __restrict__ x, int64_t rows, int k, int hadam
     nq_encode_rows_cta<float, false, false>(rotated, k, nrows, nrows, k, beta_table, sqrt_k, codes + g0,
                                             beta_ids + (g0 >> 2), norms + row0,
                                             decoded ? decoded + g0 * 8 : nullptr, 0u, encoder_smem, blk_begin,
-                                            blk_begin + blocks_per_split, blockIdx.y == 0, rpc);
+                                            blk_begin + blocks_per_split, blockIdx.y == 0, rpc, four_lanes != 0);
 }
 
 template <typename T>
 int launch_encode_rotated(const void* x, int64_t rows, int64_t k, int64_t hadamard_block, const float* beta_table,
                           uint8_t* out_codes, uint8_t* out_beta_ids, float* out_norms, void* out_decoded,
                           cudaStream_t stream) {
-    int rpc = nq_encode_rows_per_cta((int)k);
-    const int many = nq_encode_rows_per_cta_many((int)k);
-    if (many > rpc && rows / many >= 5 * 148) rpc = many;
+    const NqEncodePlan plan = nq_encode_plan(rows, (int)k, false);
+    const int rpc = plan.rpc, splits = plan.splits, blocks_per_split = plan.blocks_per_split;
     const size_t smem = ((size_t)rpc * k + nq_encode_smem_floats((int)k, rpc)) * sizeof(float);
     auto kernel = nq_encode_rotated_kernel<T>;
     if (smem > 48 * 1024) {
@@ -59,25 +58,11 @@ int launch_encode_rotated(const void* x, int64_t rows, int64_t k, int64_t hadama
         }
     }
     const int64_t grid = (rows + rpc - 1) / rpc;
-    // Few long rows (decode-time activations): split each row's blocks over several CTAs; every
-    // CTA repeats the cheap transform and norm of its row.
-    const int bpr = (int)(k / 8);
-    const bool one_long_row = rpc == 1 && bpr >= NQ_ENC_THREADS;
-    int splits = 1;
-    if (one_long_row && grid < 148) {
-        splits = (int)((2 * 148 + grid - 1) / grid);
-        const int max_splits = bpr / 32;
-        if (splits > max_splits) splits = max_splits;
-        if (splits < 1) splits = 1;
-    }
-    int blocks_per_split = ((bpr + splits - 1) / splits + 31) / 32 * 32;
-    if (!one_long_row) blocks_per_split = 0x40000000;
-    splits = one_long_row ? (bpr + blocks_per_split - 1) / blocks_per_split : 1;
     const float root = (float)sqrt((double)hadamard_block);
     kernel<<<dim3((unsigned)grid, (unsigned)splits), NQ_ENC_THREADS, smem, stream>>>(
         reinterpret_cast<const T*>(x), rows, (int)k, (int)hadamard_block, root, 1.0f / root, beta_table,
         (float)sqrt((double)k), reinterpret_cast<uint32_t*>(out_codes), out_beta_ids, out_norms,
-        reinterpret_cast<__nv_bfloat16*>(out_decoded), blocks_per_split, rpc);
+        reinterpret_cast<__nv_bfloat16*>(out_decoded), blocks_per_split, rpc, plan.four_lanes ? 1 : 0);
     NQ_CHECK_LAUNCH("nq_a4_encode_rotated");
     return NQ_OK;
 }

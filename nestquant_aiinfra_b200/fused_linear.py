@@ -17,7 +17,7 @@ from torch import nn
 
 from .rotation import hadamard
 from .runtime.w4a4 import (PreparedNQA4Activation, PreparedNQRTLinear, linear_packed_w4a4, prepare_fused_linear,
-                           quantize_activation_cuda, can_rotate_in_encoder)
+                           quantize_activation_cuda, can_rotate_in_encoder, prefer_rotation_in_encoder)
 
 _BACKENDS = {"packed_w4a4_cuda_mma", "packed_w4a4_cuda_gemv_m1", "packed_w4a4"}
 
@@ -227,7 +227,8 @@ class FusedNQRTLinear(nn.Module):
         wanted_block = self.in_features if self.input_hadamard else self.input_rotation_block
         rotate_in_encoder = (wanted_block is not None
                              and inputs.dtype in (torch.bfloat16, torch.float16, torch.float32)
-                             and can_rotate_in_encoder(self.in_features, wanted_block))
+                             and can_rotate_in_encoder(self.in_features, wanted_block)
+                             and prefer_rotation_in_encoder(inputs.numel() // self.in_features, self.in_features))
         if rotate_in_encoder:
             if self.input_transform_cache is not None:
                 self.input_transform_cache.note_rotation_in_encoder(inputs)

@@ -164,6 +164,15 @@ def can_rotate_in_encoder(feature_count: int, hadamard_block: int) -> bool:
             and feature_count % hadamard_block == 0)
 
 
+def prefer_rotation_in_encoder(rows: int, feature_count: int) -> bool:
+    """Whether the fused launch beats ``hadamard`` + encoder for this shape.
+
+    A launch with few long rows splits every row over several CTAs and each of them would repeat
+    the transform of the whole row; there the two launches are faster.
+    """
+    return feature_count <= 4096 or rows >= 148
+
+
 def quantize_activation_cuda(
     inputs: torch.Tensor, *, q: int, betas: Sequence[float],
     beta_table: torch.Tensor | None = None, keep_decoded: bool = True, hadamard_block: int | None = None,
