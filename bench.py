@@ -514,7 +514,7 @@ def kv_workload(torch, rt, device, pk) -> dict:
     }
 
 
-def decode_workload(torch, device, *, requests: int = 64, new_tokens: int = 256) -> dict:
+def decode_workload(torch, device, *, requests: int = 64, new_tokens: int = 256, kernel_mix: bool = False) -> dict:
     """Llama-3.2-1B architecture, random init, W4A4KV4: ragged prefill then graph decode of `requests` rows."""
     from nestquant_aiinfra_b200.engine import BatchedNQKVLlamaRunner, build_llama_w4a4kv4
 
@@ -545,7 +545,27 @@ def decode_workload(torch, device, *, requests: int = 64, new_tokens: int = 256)
     e1.record()
     torch.cuda.synchronize(device)
     ms = e0.elapsed_time(e1)
-    return {"model": "llama-3.2-1b-arch random init, W4A4KV4, 112 NQRT4 projections", "requests": requests,
+    mix = None
+    if kernel_mix:  # device time per kernel over a few more graph replays (CUPTI through torch.profiler)
+        from torch.profiler import ProfilerActivity, profile
+
+        replays = 5
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            for _ in range(replays):
+                runner.decode()
+            torch.cuda.synchronize(device)
+        rows = []
+        for event in prof.key_averages():
+            total = getattr(event, "device_time_total", None) or getattr(event, "cuda_time_total", 0)
+            if total > 0:
+                rows.append((total / replays, event.count / replays, event.key))
+        rows.sort(reverse=True)
+        whole = sum(r[0] for r in rows)
+        mix = [{"kernel": key[:80], "us_per_step": round(us, 1), "launches_per_step": round(count, 1),
+                "share": round(us / whole, 4)} for us, count, key in rows[:16]]
+        mix.append({"kernel": "all kernels", "us_per_step": round(whole, 1)})
+    return {**({"kernel_mix": mix} if mix else {}),
+            "model": "llama-3.2-1b-arch random init, W4A4KV4, 112 NQRT4 projections", "requests": requests,
             "prompt_tokens": int(sum(lengths)), "decode_steps": steps, "ms_per_step": round(ms / steps, 3),
             "decode_tok_s": round(requests * steps / (ms * 1e-3), 1), "prefill_s": round(prefill_s, 2),
             "prefill_tok_s": round(sum(lengths) / prefill_s, 1), "cuda_graph": True}
@@ -645,7 +665,8 @@ def run_single_extra(args) -> None:
 
     device = torch.device("cuda", 0)
     torch.cuda.set_device(device)
-    result = kv_workload(torch, rt, device, peaks()) if args.workload == "kv" else decode_workload(torch, device)
+    result = (kv_workload(torch, rt, device, peaks()) if args.workload == "kv"
+              else decode_workload(torch, device, kernel_mix=args.kernel_mix))
     print(json.dumps({"workload": args.workload, **result}), flush=True)
 
 
@@ -661,6 +682,8 @@ def main() -> None:
     parser.add_argument("--tp-layers", type=int, default=80, help="decoder layers of the tp70b workload")
     parser.add_argument("--tp-batch", type=int, default=128)
     parser.add_argument("--tp-context", type=int, default=4096)
+    parser.add_argument("--kernel-mix", action="store_true",
+                        help="with --workload decode: add the device time per kernel of a decode step (torch.profiler)")
     parser.add_argument("--skip-extras", action="store_true",
                         help="timed sweep only: no per-cell table, no end-to-end pass, no CPU baseline (profiling runs)")
     args = parser.parse_args()
