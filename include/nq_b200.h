@@ -244,6 +244,20 @@ int nq_kv_attention(const void* query, int q_dtype, int batch, int q_tokens, int
  * the dtype, final IEEE division by float32(sqrt(n)).  x may equal out. */
 int nq_hadamard(const void* x, void* out, int dtype, int64_t rows, int64_t n, nq_stream_t stream);
 
+/* Rotary position embedding of query or key heads and, with apply_hadamard != 0, the float32
+ * Hadamard rotation the KV backend applies to them afterwards, in one launch:
+ *   rope     (x * cos) + (rotate_half(x) * sin), every product and the sum rounded to `dtype`
+ *            (the model's apply_rotary_pos_emb on tensors of that dtype)
+ *   rotation dtype(hadamard(float32(rope)))   (runtime/nqkv_batched_hf_backend.py:381,549)
+ * Result for result identical to that sequence of tensor ops.  The reference leaves the rope to the
+ * model and runs the rotation as tensor ops: no counterpart there.
+ *   x    [batch, heads, tokens, dim] with element strides stride_b/h/t and unit stride along dim
+ *   cos, sin [batch, tokens, dim] contiguous;  out [batch, heads, tokens, dim] contiguous
+ *   dim a power of two in [16, 1024]; pointers and strides 16-byte aligned. */
+int nq_rope_hadamard(const void* x, int dtype, int64_t batch, int64_t heads, int64_t tokens, int64_t dim,
+                     int64_t stride_b, int64_t stride_h, int64_t stride_t, const void* cos, const void* sin,
+                     int apply_hadamard, void* out, nq_stream_t stream);
+
 /* RMS normalisation of rows as Hugging Face's LlamaRMSNorm computes it, in one launch:
  *   out = weight * dtype(x * rsqrt(mean(x^2) + eps))      (mean and product in float32)
  * It precedes every rotate-then-encode launch of a decoder layer; the reference leaves it to

@@ -125,6 +125,21 @@ __global__ void __launch_bounds__(kAttnThreads) nq_attn_paged_kernel(const AttnP
                 page_id = p.page_indices[(int64_t)slot * p.max_pages + ps];
                 if (page_id < 0 || page_id >= p.pool_capacity) continue;  // defensive: never read outside the pool
             }
+            // pull the codes of this warp's NEXT page towards L1 while this one is decoded: lane l asks for
+            // the code row of token l & 15 (keys on lanes 0..15, values on lanes 16..31)
+            {
+                const int nps = ps + kAttnWarps;
+                if (nps < s_end && nps < page_count && (lane & 15) < p.page_size) {
+                    const int next_id = p.page_indices[(int64_t)slot * p.max_pages + nps];
+                    if (next_id >= 0 && next_id < p.pool_capacity) {
+                        const int row = (lane & 15) * p.kv_heads + h;
+                        const uint8_t* src = (lane < 16 ? p.key_codes : p.value_codes) + next_id * code_bytes +
+                                             (int64_t)row * BPR * 4;
+                        asm volatile("prefetch.global.L1 [%0];" ::"l"(src));
+                        if (BPR * 4 > 128) asm volatile("prefetch.global.L1 [%0];" ::"l"(src + 128));
+                    }
+                }
+            }
             for (int t0 = 0; t0 < tlimit; t0 += TPW) {
                 const int t = t0 + tsub;
                 const bool valid = t < tlimit && base_token + t < limit;

@@ -54,20 +54,21 @@ __device__ __forceinline__ void nq_butterflies(float v[8]) {
     }
 }
 
-// All butterfly stages of `total / n` independent rows of n elements (n a power of two >= 8,
-// rows contiguous in `x`), result in buf[0, total) as float32 values of dtype T, NOT yet divided
-// by sqrt(n).  Called by every thread of the CTA; ends with a barrier.
-template <typename T>
-__device__ __forceinline__ void nq_fwht_rows_to_smem(const T* __restrict__ x, float* buf, int total, int n) {
+// All butterfly stages of `total / n` independent rows of n elements (n a power of two >= 8),
+// result in buf[0, total) as float32 values of dtype T, NOT yet divided by sqrt(n).
+// load(g, v) supplies the 8 consecutive elements of group g (elements 8g .. 8g+7 of the CTA's
+// rows) as float32 values of dtype T.  Called by every thread of the CTA; ends with a barrier.
+template <typename T, class Load>
+__device__ __forceinline__ void nq_fwht_groups_to_smem(Load&& load, float* buf, int total, int n) {
     const int nthreads = blockDim.x;
     const int groups = total >> 3;
     int log_n = 0;
     while ((1 << log_n) < n) ++log_n;
 
-    // pass 0: widths 1, 2, 4 on 8 consecutive elements loaded from global memory
+    // pass 0: widths 1, 2, 4 on 8 consecutive elements
     for (int g = threadIdx.x; g < groups; g += nthreads) {
         float v[8];
-        nq_load8<T>(x + (int64_t)g * 8, v);
+        load(g, v);
         nq_butterflies<T, 3>(v);
         float4* dst = reinterpret_cast<float4*>(buf + g * 8);
         dst[0] = make_float4(v[0], v[1], v[2], v[3]);
@@ -96,4 +97,10 @@ __device__ __forceinline__ void nq_fwht_rows_to_smem(const T* __restrict__ x, fl
         __syncthreads();
         done += stages;
     }
+}
+
+// Same with the rows read from global memory (contiguous in `x`).
+template <typename T>
+__device__ __forceinline__ void nq_fwht_rows_to_smem(const T* __restrict__ x, float* buf, int total, int n) {
+    nq_fwht_groups_to_smem<T>([&](int g, float v[8]) { nq_load8<T>(x + (int64_t)g * 8, v); }, buf, total, n);
 }

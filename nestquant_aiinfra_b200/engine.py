@@ -19,6 +19,7 @@ from .formats import ACTIVATION_BETAS, KEY_BETAS, VALUE_BETAS, WEIGHT_BETAS, ten
 from .fused_linear import FusedNQRTLinear, SharedHadamardCache, SharedPackedActivationCache
 from .hf_backend import BatchedNQKVLlamaCache, install_batched_nqkv_llama_backend
 from .norm import fuse_rmsnorm_
+from .rope import fused_rope_scope
 from .rotation import hadamard
 from .runtime.w4a4 import quantize_weight_cuda
 
@@ -122,10 +123,11 @@ class BatchedNQKVLlamaRunner:
         slot_ids = torch.tensor(list(slots), dtype=torch.int32, device=self.device)
         q_lens = torch.tensor(lengths, dtype=torch.int32, device=self.device)
         positions = torch.arange(width, device=self.device).unsqueeze(0).expand(len(slots), width).contiguous()
-        self.cache.set_prefill_state(slot_ids=slot_ids, query_lengths=q_lens)
+        self.cache.set_prefill_state(slot_ids=slot_ids, query_lengths=q_lens, from_empty=True)  # slots were just registered
         try:
-            hidden = self.model.model(input_ids=ids, position_ids=positions, past_key_values=self.cache,
-                                      use_cache=True).last_hidden_state
+            with fused_rope_scope():
+                hidden = self.model.model(input_ids=ids, position_ids=positions, past_key_values=self.cache,
+                                          use_cache=True).last_hidden_state
         finally:
             self.cache.set_decode_state()
         last = hidden[torch.arange(len(slots), device=self.device), q_lens.long() - 1]
@@ -137,8 +139,9 @@ class BatchedNQKVLlamaRunner:
 
     @torch.no_grad()
     def _step(self) -> None:
-        logits = self.model(input_ids=self.tokens, position_ids=self.positions, past_key_values=self.cache,
-                            use_cache=True).logits
+        with fused_rope_scope():  # rope + Q/K Hadamard rotation in one launch per tensor
+            logits = self.model(input_ids=self.tokens, position_ids=self.positions, past_key_values=self.cache,
+                                use_cache=True).logits
         self.next_tokens.copy_(logits[:, -1].argmax(dim=-1))
         active = self.cache.active_mask
         self.tokens[:, 0] = torch.where(active, self.next_tokens, self.tokens[:, 0])

@@ -8,8 +8,10 @@ kernel for decode (one token) or for a whole-prompt chunk.
 
 Differences from the reference, all on the host side: page ids are assigned statically
 (``slot * max_pages + page``), so the page writer needs no host reservation and the same
-captured graph serves boundary and non-boundary steps; prefill attention reads the pages it
-has just written (the reference runs SDPA over the current BF16 K/V).
+captured graph serves boundary and non-boundary steps; a prefill chunk that continues a cached
+sequence reads the pages it has just written plus the hot tail (the reference only prefills from
+empty slots, with SDPA over the chunk's BF16 K/V -- which is what a prefill from empty slots does
+here too).
 """
 
 from __future__ import annotations
@@ -20,6 +22,7 @@ from typing import Hashable, Sequence
 import torch
 from transformers.cache_utils import Cache
 
+from .rope import rotation_done
 from .rotation import hadamard
 from .runtime.kv import (BatchedNQKVAttentionWorkspace, NQKVHotColdCache, NQKVPagePool,
                          _launch_append_hot_k1_graph_safe, _launch_append_hot_ragged_segment_graph_safe,
@@ -67,6 +70,7 @@ class BatchedNQKVLlamaCache(Cache):
         self._decode_workspace = BatchedNQKVAttentionWorkspace.create(
             self.layer_caches[0], batch_size=capacity, query_heads=num_query_heads, output_dtype=dtype)
         self._prefill: tuple[torch.Tensor, torch.Tensor] | None = None  # (slot_ids, query_lengths)
+        self._prefill_from_empty = False
         self._prefill_workspace: BatchedNQKVAttentionWorkspace | None = None
         self._sequence_of_slot: dict[int, Hashable] = {}
 
@@ -103,11 +107,19 @@ class BatchedNQKVLlamaCache(Cache):
         self.execution_active_mask = self.active_mask if active_mask is None else active_mask
         self._prefill = None
 
-    def set_prefill_state(self, *, slot_ids: torch.Tensor, query_lengths: torch.Tensor) -> None:
-        """Rows of the next multi-token forward: row i appends ``query_lengths[i]`` tokens to ``slot_ids[i]``."""
+    def set_prefill_state(self, *, slot_ids: torch.Tensor, query_lengths: torch.Tensor,
+                          from_empty: bool = False) -> None:
+        """Rows of the next multi-token forward: row i appends ``query_lengths[i]`` tokens to ``slot_ids[i]``.
+
+        ``from_empty`` states that every one of these slots holds no tokens yet (a whole-prompt
+        prefill).  Attention then runs over the chunk's own BF16 keys and values, as the reference's
+        ``prefill`` does (runtime/nqkv_batched_hf_backend.py:569-589); otherwise (a chunk that
+        continues a cached sequence) over the quantised pages plus the hot tail.
+        """
         if slot_ids.dtype != torch.int32 or query_lengths.dtype != torch.int32 or slot_ids.shape != query_lengths.shape:
             raise ValueError("slot_ids and query_lengths must be int32 tensors of the same shape")
         self._prefill = (slot_ids, query_lengths)
+        self._prefill_from_empty = bool(from_empty)
 
     # ------------------------------------------------------------------ Cache interface
     def _pack_full_pages(self, cache: NQKVHotColdCache) -> None:
@@ -120,7 +132,9 @@ class BatchedNQKVLlamaCache(Cache):
         rows, heads, tokens, dim = key_states.shape
         if heads != self.num_kv_heads or dim != self.head_dim:
             raise ValueError("key/value states do not match the cache geometry")
-        rotated_key = hadamard(key_states.float()).to(self.dtype)
+        # keys that come out of the fused rope launch are rotated already
+        rotated_key = (key_states if rotation_done(key_states) and key_states.dtype == self.dtype
+                       else hadamard(key_states.float()).to(self.dtype))
         if tokens == 1 and self._prefill is None:
             if rows != self.execution_slot_ids.numel():
                 raise ValueError("decode rows do not match the execution slot ids")
@@ -152,7 +166,8 @@ class BatchedNQKVLlamaCache(Cache):
         expected = (self.execution_slot_ids.numel(), self.num_query_heads, 1, self.head_dim)
         if tuple(query_states.shape) != expected:
             raise ValueError("batched NQKV decode requires [rows, heads, 1, dim]")
-        query = hadamard(query_states.float()).to(self.dtype)[:, :, 0].contiguous()
+        query = (query_states if rotation_done(query_states) and query_states.dtype == self.dtype
+                 else hadamard(query_states.float()).to(self.dtype))[:, :, 0].contiguous()
         workspace = self._decode_workspace
         if query.shape[0] != workspace.batch_size:
             workspace = BatchedNQKVAttentionWorkspace.create(self.layer_caches[layer_idx], batch_size=query.shape[0],
@@ -162,13 +177,27 @@ class BatchedNQKVLlamaCache(Cache):
             active_mask=self.execution_active_mask, attention_scale=scale, workspace=workspace)
         return output.unsqueeze(1)
 
-    def prefill(self, layer_idx: int, query_states: torch.Tensor, *, scale: float) -> torch.Tensor:
-        """Whole-chunk causal attention over the pages just written: ``[rows, Hq, T, D]`` -> ``[rows, T, Hq, D]``."""
+    def prefill(self, layer_idx: int, query_states: torch.Tensor, *, scale: float,
+                key_states: torch.Tensor | None = None, value_states: torch.Tensor | None = None) -> torch.Tensor:
+        """Causal attention of a whole chunk: ``[rows, Hq, T, D]`` -> ``[rows, T, Hq, D]``.
+
+        A prefill from empty slots uses the chunk's BF16 keys (already rotated by ``update``) and values,
+        right-padded rows included (causality keeps valid queries away from the padding); any other
+        chunk reads the pages just written and the hot tail.
+        """
         self._validate_layer(layer_idx)
         if self._prefill is None:
             raise RuntimeError("prefill attention needs set_prefill_state(slot_ids, query_lengths)")
         slot_ids, query_lengths = self._prefill
-        query = hadamard(query_states.float()).to(self.dtype).permute(0, 2, 1, 3).contiguous()
+        if self._prefill_from_empty and key_states is not None and value_states is not None:
+            rotated_query = (query_states if rotation_done(query_states) and query_states.dtype == self.dtype
+                             else hadamard(query_states.float()).to(self.dtype))
+            out = torch.nn.functional.scaled_dot_product_attention(
+                rotated_query, key_states.to(self.dtype), value_states.to(self.dtype), attn_mask=None, dropout_p=0.0,
+                is_causal=True, scale=scale, enable_gqa=self.num_query_heads != self.num_kv_heads)
+            return out.transpose(1, 2)
+        query = (query_states if rotation_done(query_states) and query_states.dtype == self.dtype
+                 else hadamard(query_states.float()).to(self.dtype)).permute(0, 2, 1, 3).contiguous()
         rows, tokens = query.shape[0], query.shape[1]
         ws = self._prefill_workspace
         if ws is None or (ws.batch_size, ws.query_tokens) != (rows, tokens):
@@ -221,7 +250,7 @@ def _batched_nqkv_attention_interface(module, query: torch.Tensor, key: torch.Te
     scale = float(kwargs.get("scaling", module.scaling))
     if query.shape[2] == 1 and cache._prefill is None:
         return cache.attend(module.layer_idx, query, scale=scale), None
-    return cache.prefill(module.layer_idx, query, scale=scale), None
+    return cache.prefill(module.layer_idx, query, scale=scale, key_states=key, value_states=value), None
 
 
 def install_batched_nqkv_llama_backend(model: torch.nn.Module, cache: BatchedNQKVLlamaCache) -> str:

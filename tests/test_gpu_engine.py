@@ -67,6 +67,52 @@ def test_prefill_tracks_the_unquantised_model():
             assert cosine > 0.9, cosine
 
 
+def test_prefill_from_empty_slots_uses_the_chunks_own_kv_and_agrees_with_the_paged_path():
+    """Whole-prompt prefill (BF16 K/V of the chunk, as the reference) vs the same prompts through the quantised pages."""
+    model, cache, runner = _build(seed=7)
+    prompts = _prompts([37, 9, 64], seed=19)
+    width = max(p.numel() for p in prompts)
+    ids = torch.zeros((3, width), dtype=torch.long, device="cuda")
+    for row, prompt in enumerate(prompts):
+        ids[row, :prompt.numel()] = prompt.cuda()
+    slot_ids = torch.tensor([0, 1, 2], dtype=torch.int32, device="cuda")
+    q_lens = torch.tensor([p.numel() for p in prompts], dtype=torch.int32, device="cuda")
+    pos = torch.arange(width, device="cuda").unsqueeze(0).expand(3, width).contiguous()
+    logits, pages = [], []
+    for from_empty in (True, False):
+        for slot in range(3):
+            cache.register(f"probe-{from_empty}-{slot}", slot=slot)
+        cache.set_prefill_state(slot_ids=slot_ids, query_lengths=q_lens, from_empty=from_empty)
+        with torch.no_grad():
+            out = model(input_ids=ids, position_ids=pos, past_key_values=cache, use_cache=True).logits.float()
+        cache.set_decode_state()
+        logits.append(torch.stack([out[row, int(q_lens[row]) - 1] for row in range(3)]))
+        pages.append(cache.layer_caches[0].pool.key_codes[:8].clone())   # layer 0 sees identical inputs either way
+        cache.release_slots([0, 1, 2])
+    assert torch.equal(pages[0], pages[1])
+    cosine = torch.nn.functional.cosine_similarity(logits[0], logits[1], dim=-1)
+    assert float(cosine.min()) > 0.97, cosine
+
+
+def test_fused_rope_scope_changes_no_bit(monkeypatch):
+    """Rope + Q/K rotation from one launch per tensor vs the stock tensor ops: same tokens, same pages."""
+    import contextlib
+
+    import nestquant_aiinfra_b200.engine as engine
+
+    results = []
+    for fused in (True, False):
+        if not fused:
+            monkeypatch.setattr(engine, "fused_rope_scope", lambda: contextlib.nullcontext())
+        model, cache, runner = _build(seed=9)
+        first = runner.prefill_slots([0, 1, 3], _prompts([33, 4, 50], seed=23))
+        tokens = [first.clone()] + [runner.decode_eager().clone() for _ in range(3)]
+        results.append((tokens, cache.layer_caches[1].pool.key_codes.clone(), cache.layer_caches[1].hot_keys.clone()))
+    for a, b in zip(results[0][0], results[1][0]):
+        assert torch.equal(a, b)
+    assert torch.equal(results[0][1], results[1][1]) and torch.equal(results[0][2], results[1][2])
+
+
 def test_graph_decode_equals_eager_decode():
     prompts = _prompts([7, 16, 33, 50])
     outputs = []

@@ -133,3 +133,23 @@ def test_fuse_rmsnorm_replaces_llama_norms():
         assert isinstance(model.model.norm, FusedRMSNorm)
         after = model(ids).logits.float()
     assert rel_fro(after.cpu().numpy(), before.cpu().numpy()) < 2e-2
+
+
+@pytest.mark.parametrize("batch,heads,tokens,dim,dtype", [(5, 8, 1, 64, torch.bfloat16), (2, 4, 19, 128, torch.bfloat16),
+                                                          (3, 2, 7, 64, torch.float16), (1, 3, 5, 32, torch.float32)])
+def test_rope_and_rotation_in_one_launch_equal_the_tensor_ops(batch, heads, tokens, dim, dtype):
+    """nq_rope_hadamard == apply_rotary_pos_emb, and == hadamard(rope.float()).to(dtype) with the rotation, bit for bit."""
+    from transformers.models.llama.modeling_llama import rotate_half
+
+    from nestquant_aiinfra_b200.rope import rope_hadamard
+    from nestquant_aiinfra_b200.rotation import hadamard
+
+    # the layout of Llama's attention module: [B, T, H*D] viewed as [B, T, H, D] and transposed
+    x = torch.randn(batch, tokens, heads * dim, generator=rng(300 + dim)).to(dtype).cuda()
+    x = x.view(batch, tokens, heads, dim).transpose(1, 2)
+    angles = torch.rand(batch, tokens, dim, generator=rng(301)) * 6.28
+    cos, sin = angles.cos().to(dtype).cuda(), angles.sin().to(dtype).cuda()
+    stock = (x * cos.unsqueeze(1)) + (rotate_half(x) * sin.unsqueeze(1))
+    assert torch.equal(rope_hadamard(x, cos, sin, rotate=False), stock)
+    assert torch.equal(rope_hadamard(x, cos, sin), hadamard(stock.float()).to(dtype))
+    assert torch.equal(rope_hadamard(x[:1], cos[:1], sin[:1]), rope_hadamard(x, cos, sin)[:1])
