@@ -123,7 +123,8 @@ class BatchedNQKVLlamaRunner:
         slot_ids = torch.tensor(list(slots), dtype=torch.int32, device=self.device)
         q_lens = torch.tensor(lengths, dtype=torch.int32, device=self.device)
         positions = torch.arange(width, device=self.device).unsqueeze(0).expand(len(slots), width).contiguous()
-        self.cache.set_prefill_state(slot_ids=slot_ids, query_lengths=q_lens, from_empty=True)  # slots were just registered
+        self.cache.set_prefill_state(slot_ids=slot_ids, query_lengths=q_lens, from_empty=True,  # slots were just registered
+                                     host_slots=list(slots), host_lengths=lengths)
         try:
             with fused_rope_scope():
                 hidden = self.model.model(input_ids=ids, position_ids=positions, past_key_values=self.cache,

@@ -24,6 +24,7 @@ from transformers.cache_utils import Cache
 
 from .rope import rotation_done
 from .rotation import hadamard
+from .runtime.w4a4 import quantize_activation_cuda
 from .runtime.kv import (BatchedNQKVAttentionWorkspace, NQKVHotColdCache, NQKVPagePool,
                          _launch_append_hot_k1_graph_safe, _launch_append_hot_ragged_segment_graph_safe,
                          _launch_nqkv_decode_attention_batched_k1, launch_pack_full_hot_pages_graph_safe,
@@ -71,6 +72,8 @@ class BatchedNQKVLlamaCache(Cache):
             self.layer_caches[0], batch_size=capacity, query_heads=num_query_heads, output_dtype=dtype)
         self._prefill: tuple[torch.Tensor, torch.Tensor] | None = None  # (slot_ids, query_lengths)
         self._prefill_from_empty = False
+        self._bulk_host: tuple[list[int], list[int]] | None = None   # (slots, lengths) of a prefill from empty slots
+        self._bulk_plan = None
         self._prefill_workspace: BatchedNQKVAttentionWorkspace | None = None
         self._sequence_of_slot: dict[int, Hashable] = {}
 
@@ -107,19 +110,28 @@ class BatchedNQKVLlamaCache(Cache):
         self.execution_active_mask = self.active_mask if active_mask is None else active_mask
         self._prefill = None
 
-    def set_prefill_state(self, *, slot_ids: torch.Tensor, query_lengths: torch.Tensor,
-                          from_empty: bool = False) -> None:
+    def set_prefill_state(self, *, slot_ids: torch.Tensor, query_lengths: torch.Tensor, from_empty: bool = False,
+                          host_slots: Sequence[int] | None = None, host_lengths: Sequence[int] | None = None) -> None:
         """Rows of the next multi-token forward: row i appends ``query_lengths[i]`` tokens to ``slot_ids[i]``.
 
         ``from_empty`` states that every one of these slots holds no tokens yet (a whole-prompt
         prefill).  Attention then runs over the chunk's own BF16 keys and values, as the reference's
         ``prefill`` does (runtime/nqkv_batched_hf_backend.py:569-589); otherwise (a chunk that
-        continues a cached sequence) over the quantised pages plus the hot tail.
+        continues a cached sequence) over the quantised pages plus the hot tail.  When the caller
+        also passes the slots and lengths as host integers, the page writer encodes all full pages
+        of the chunk in one launch per tensor instead of walking the chunk page by page (same pages,
+        same metadata).
         """
         if slot_ids.dtype != torch.int32 or query_lengths.dtype != torch.int32 or slot_ids.shape != query_lengths.shape:
             raise ValueError("slot_ids and query_lengths must be int32 tensors of the same shape")
         self._prefill = (slot_ids, query_lengths)
         self._prefill_from_empty = bool(from_empty)
+        self._bulk_plan = None
+        self._bulk_host = None
+        if from_empty and host_slots is not None and host_lengths is not None:
+            if len(host_slots) != slot_ids.numel() or len(host_lengths) != slot_ids.numel():
+                raise ValueError("host_slots / host_lengths must match slot_ids")
+            self._bulk_host = ([int(v) for v in host_slots], [int(v) for v in host_lengths])
 
     # ------------------------------------------------------------------ Cache interface
     def _pack_full_pages(self, cache: NQKVHotColdCache) -> None:
@@ -149,6 +161,9 @@ class BatchedNQKVLlamaCache(Cache):
             raise ValueError("prefill rows do not match the prefill slot ids")
         key_nhd = rotated_key.permute(0, 2, 1, 3).contiguous()
         value_nhd = value_states.to(self.dtype).permute(0, 2, 1, 3).contiguous()
+        if self._bulk_host is not None:
+            self._write_chunk_from_empty(cache, key_nhd, value_nhd)
+            return rotated_key, value_states
         consumed = torch.zeros_like(query_lengths)
         index = slot_ids.long()
         for _ in range(math.ceil(tokens / self.page_size) + 1):
@@ -159,6 +174,63 @@ class BatchedNQKVLlamaCache(Cache):
             self._pack_full_pages(cache)
             consumed = consumed + counts
         return rotated_key, value_states
+
+    def _plan_chunk_from_empty(self, tokens: int):
+        """Index tensors of a whole-prompt chunk ``[rows, tokens]``: which tokens fill whole pages, which stay hot."""
+        slots, lengths = self._bulk_host
+        page, device = self.page_size, self.device
+        full_idx, page_ids, tail_src, tail_slot, tail_pos = [], [], [], [], []
+        table = torch.full((len(slots), self.max_pages), -1, dtype=torch.int32)
+        for row, (slot, length) in enumerate(zip(slots, lengths)):
+            if length > tokens or length // page > self.max_pages:
+                raise ValueError("prefill length exceeds the chunk or the cache length")
+            full, rest = length // page, length % page
+            full_idx.append(torch.arange(full * page) + row * tokens)
+            ids = torch.arange(full) + slot * self.max_pages
+            page_ids.append(ids)
+            table[row, :full] = ids.to(torch.int32)
+            tail_src.append(torch.arange(rest) + row * tokens + full * page)
+            tail_slot.append(torch.full((rest,), slot))
+            tail_pos.append(torch.arange(rest))
+        cat = lambda parts: torch.cat(parts).to(device) if parts else torch.zeros(0, dtype=torch.long, device=device)  # noqa: E731
+        lengths_t = torch.tensor(lengths, dtype=torch.int32)
+        return {"tokens": tokens, "full_idx": cat(full_idx), "page_ids": cat(page_ids), "tail_src": cat(tail_src),
+                "tail_slot": cat(tail_slot), "tail_pos": cat(tail_pos), "table": table.to(device),
+                "slots": torch.tensor(slots, dtype=torch.long, device=device),
+                "full": (lengths_t // page).to(device), "rest": (lengths_t % page).to(device),
+                "lengths": lengths_t.to(device)}
+
+    def _write_chunk_from_empty(self, cache: NQKVHotColdCache, key_nhd: torch.Tensor, value_nhd: torch.Tensor) -> None:
+        """All full pages of the chunk through one encoder launch per tensor, the remainder into the hot tail.
+
+        Leaves pool and metadata exactly as the page-by-page writer does (static page ids
+        ``slot * max_pages + page``).
+        """
+        rows, tokens = key_nhd.shape[0], key_nhd.shape[1]
+        plan = self._bulk_plan
+        if plan is None or plan["tokens"] != tokens:
+            plan = self._bulk_plan = self._plan_chunk_from_empty(tokens)
+        pool, dim = cache.pool, self.head_dim
+        for flat, codes, betas, norms, table, values, hot in (
+                (key_nhd.view(rows * tokens, -1), pool.key_codes, pool.key_betas, pool.key_norms, pool.beta_table,
+                 pool.betas, cache.hot_keys),
+                (value_nhd.view(rows * tokens, -1), pool.value_codes, pool.value_betas, pool.value_norms,
+                 pool.value_beta_table, pool.value_beta_values, cache.hot_values)):
+            pages = plan["page_ids"].numel()
+            if pages:
+                packed = quantize_activation_cuda(flat[plan["full_idx"]].view(-1, dim), q=14, betas=values,
+                                                  beta_table=table, keep_decoded=False)
+                codes[plan["page_ids"]] = packed.code_payload.view(pages, -1)
+                betas[plan["page_ids"]] = packed.beta_payload.view(pages, -1)
+                norms[plan["page_ids"]] = packed.row_norms.view(pages, -1)
+            if plan["tail_src"].numel():
+                hot[plan["tail_slot"], plan["tail_pos"]] = flat[plan["tail_src"]].view(-1, self.num_kv_heads, dim)
+        slots = plan["slots"]
+        cache.page_indices[slots] = plan["table"]
+        cache.page_counts[slots] = plan["full"]
+        cache.last_page_len[slots] = torch.where(plan["full"] > 0, self.page_size, 0).to(torch.int32)
+        cache.hot_lengths[slots] = plan["rest"]
+        cache.sequence_lengths[slots] = plan["lengths"]
 
     def attend(self, layer_idx: int, query_states: torch.Tensor, *, scale: float) -> torch.Tensor:
         """Decode: ``query_states [rows, Hq, 1, D]`` -> ``[rows, 1, Hq, D]``."""

@@ -94,6 +94,46 @@ def test_prefill_from_empty_slots_uses_the_chunks_own_kv_and_agrees_with_the_pag
     assert float(cosine.min()) > 0.97, cosine
 
 
+def test_bulk_page_writer_of_a_whole_prompt_equals_the_page_by_page_writer():
+    """One encoder launch per tensor for all full pages of a chunk vs the append / pack loop: same pool, same metadata."""
+    model, cache, runner = _build(capacity=4, max_cache_len=160, seed=13)
+    prompts = _prompts([47, 16, 3, 130], seed=29)
+    slots = [2, 0, 3, 1]
+    width = max(p.numel() for p in prompts)
+    ids = torch.zeros((4, width), dtype=torch.long, device="cuda")
+    for row, prompt in enumerate(prompts):
+        ids[row, :prompt.numel()] = prompt.cuda()
+    slot_ids = torch.tensor(slots, dtype=torch.int32, device="cuda")
+    lengths = [p.numel() for p in prompts]
+    q_lens = torch.tensor(lengths, dtype=torch.int32, device="cuda")
+    pos = torch.arange(width, device="cuda").unsqueeze(0).expand(4, width).contiguous()
+    snapshots = []
+    for bulk in (True, False):
+        for slot in slots:
+            cache.register(f"probe-{bulk}-{slot}", slot=slot)
+        extra = dict(host_slots=slots, host_lengths=lengths) if bulk else {}
+        cache.set_prefill_state(slot_ids=slot_ids, query_lengths=q_lens, from_empty=True, **extra)
+        with torch.no_grad():
+            model(input_ids=ids, position_ids=pos, past_key_values=cache, use_cache=True)
+        cache.set_decode_state()
+        state = []
+        for layer in cache.layer_caches:
+            pool = layer.pool
+            hot = [layer.hot_keys[s, :n % 16].clone() for s, n in zip(slots, lengths)]
+            hot += [layer.hot_values[s, :n % 16].clone() for s, n in zip(slots, lengths)]
+            used = torch.cat([torch.arange(n // 16) + s * cache.max_pages for s, n in zip(slots, lengths)]).cuda()
+            state.append([t[used].clone() for t in (pool.key_codes, pool.key_betas, pool.key_norms, pool.value_codes,
+                                                    pool.value_betas, pool.value_norms)] + hot +
+                         [layer.page_indices.clone(), layer.page_counts.clone(), layer.last_page_len.clone(),
+                          layer.hot_lengths.clone(), layer.sequence_lengths.clone()])
+        snapshots.append(state)
+        cache.release_slots(slots)
+    for a, b in zip(*snapshots):
+        for x, y in zip(a, b):
+            assert torch.equal(x, y)
+    assert snapshots[0][0][-4].tolist() == [1, 8, 2, 0]   # page counts by slot: 16, 130, 47 and 3 tokens
+
+
 def test_fused_rope_scope_changes_no_bit(monkeypatch):
     """Rope + Q/K rotation from one launch per tensor vs the stock tensor ops: same tokens, same pages."""
     import contextlib
