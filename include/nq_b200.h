@@ -127,6 +127,22 @@ int nq_w4a4_gemm(const uint8_t* act_codes, const uint8_t* act_beta_ids, const fl
                  int64_t w_block_offset, int64_t seed, void* out, int out_dtype,
                  void* workspace, size_t workspace_bytes, nq_stream_t stream);
 
+/* The same projection for a weight that stacks the rows of several tensors sharing one input
+ * (q/k/v, gate/up): one launch sequence instead of one per tensor.  The packed streams are the
+ * tensors' streams one after the other (rows of tensor i from seg_first_row[i] on; n = all rows);
+ * every tensor keeps its own dither counters (seg_block_offset[i], seg_seed[i]), so each output
+ * column has the operands nq_w4a4_gemm uses for its tensor alone (identical on the CUDA-core path;
+ * on the tensor-core path the split of K follows the tile count, i.e. the order of the sums may differ).  segments in [1, 4]; the three
+ * tables are host arrays read during the call.  The reference launches each projection on its own
+ * (runtime/cuda_w4a4_mma.py:230-484): no counterpart there. */
+int nq_w4a4_gemm_grouped(const uint8_t* act_codes, const uint8_t* act_beta_ids, const float* act_norms,
+                         const float* act_betas, const void* act_decoded,
+                         const uint8_t* w_codes, const uint8_t* w_beta_ids, const float* w_norms,
+                         const float* w_betas, int64_t m, int64_t n, int64_t k, int segments,
+                         const int64_t* seg_first_row, const int64_t* seg_block_offset,
+                         const int64_t* seg_seed, void* out, int out_dtype,
+                         void* workspace, size_t workspace_bytes, nq_stream_t stream);
+
 /* Small-M projection for callers that cannot allocate or pass a workspace (a plugin slot that
  * only receives inputs and outputs, a thread that must never reach cudaMalloc): same result as
  * nq_w4a4_gemm for m <= NQ_STATIC_MAX_M, but the scratch (decoded activation rows, split-K

@@ -172,14 +172,21 @@ __global__ void __launch_bounds__(kAttnThreads) nq_attn_paged_kernel(const AttnP
 #pragma unroll
                     for (int off = 1; off < BPR; off <<= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
                     if (valid) {
-                        const float mn = fmaxf(m[g], s);
-                        const float corr = exp2f(m[g] - mn);  // exp2(-inf) = 0 on the first token
-                        const float pr = exp2f(s - mn);
-                        l[g] = l[g] * corr + pr;
+                        // The reference point m[g] of the running softmax only moves when a score exceeds it
+                        // by more than 8 (a factor 256): until then the terms are added unscaled, which saves
+                        // the rescaling of the accumulator on almost every token and changes no sum mathematically.
+                        if (s > m[g] + 8.0f) {
+                            const float corr = exp2f(m[g] - s);  // exp2(-inf) = 0 on the first token
+                            l[g] *= corr;
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) acc[g][j] *= corr;
+                            m[g] = s;
+                        }
+                        const float pr = exp2f(s - m[g]);
+                        l[g] += pr;
                         const float pv = pr * vscale;
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) acc[g][j] = acc[g][j] * corr + pv * vvec[j];
-                        m[g] = mn;
+                        for (int j = 0; j < 8; ++j) acc[g][j] = fmaf(pv, vvec[j], acc[g][j]);
                     }
                 }
             }

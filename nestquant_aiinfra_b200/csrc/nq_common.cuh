@@ -38,6 +38,29 @@ static inline bool nq_aligned16(const void* p) { return (reinterpret_cast<uintpt
 // ---- device helpers --------------------------------------------------------
 #if defined(__CUDACC__)
 
+// Dither counters of a weight that stacks the rows of several tensors (q/k/v, gate/up): rows from
+// first_row[i] on belong to tensor i, whose block g (index in the stacked weight) has the counter
+// base[i] + 8 g.  A plain weight is one segment.
+#define NQ_MAX_SEGMENTS 4
+struct NqDitherSegments {
+    int count;
+    int first_row[NQ_MAX_SEGMENTS];
+    uint32_t base[NQ_MAX_SEGMENTS];
+};
+__host__ __device__ inline uint32_t nq_segment_base(const NqDitherSegments& seg, int row) {
+    uint32_t base = seg.base[0];
+#pragma unroll
+    for (int i = 1; i < NQ_MAX_SEGMENTS; ++i)
+        if (i < seg.count && row >= seg.first_row[i]) base = seg.base[i];
+    return base;
+}
+inline NqDitherSegments nq_one_segment(int64_t w_block_offset, int64_t seed) {
+    NqDitherSegments seg = {};
+    seg.count = 1;
+    seg.base[0] = (uint32_t)((uint64_t)w_block_offset * 8u + (uint64_t)seed);
+    return seg;
+}
+
 // Load the 8 consecutive elements of one E8 block (16-byte aligned) as float32.
 template <typename T>
 __device__ __forceinline__ void nq_load8(const T* p, float v[8]);

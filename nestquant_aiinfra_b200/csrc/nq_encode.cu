@@ -81,13 +81,13 @@ nq_a4_decode_kernel(const uint32_t* __restrict__ codes, const uint8_t* __restric
 __global__ void __launch_bounds__(256)
 nq_w4_decode_kernel(const uint32_t* __restrict__ codes, const uint8_t* __restrict__ beta_ids,
                     const float* __restrict__ norms, const float* __restrict__ beta_table,
-                    int64_t blocks, int bpr, float sqrt_k, uint32_t counter_base,
+                    int64_t blocks, int bpr, float sqrt_k, const NqDitherSegments seg,
                     uint4* __restrict__ out) {
     const int64_t g = (int64_t)blockIdx.x * 256 + threadIdx.x;
     if (g >= blocks) return;
     const int64_t row = g / bpr;
     float r[8];
-    nq_decode_weight_block(__ldg(codes + g), counter_base + (uint32_t)g * 8u, r);
+    nq_decode_weight_block(__ldg(codes + g), nq_segment_base(seg, (int)row) + (uint32_t)g * 8u, r);
     const float beta = __ldg(beta_table + nq_beta_id(beta_ids, g));
     const float ds = nq_div(__ldg(norms + row), sqrt_k);
 #pragma unroll
@@ -188,6 +188,19 @@ extern "C" int nq_a4_decode(const uint8_t* codes, const uint8_t* beta_ids, const
     return NQ_OK;
 }
 
+// Shared by the plain and the grouped entry: the dither counters come as segments.
+int nq_w4_decode_segments(const uint8_t* w_codes, const uint8_t* w_beta_ids, const float* w_norms,
+                          const float* w_betas, int64_t n, int64_t k, const NqDitherSegments& seg, void* out_bf16,
+                          cudaStream_t stream) {
+    const int64_t blocks = n * (k / 8);
+    const unsigned grid = (unsigned)((blocks + 255) / 256);
+    nq_w4_decode_kernel<<<grid, 256, 0, stream>>>(
+        reinterpret_cast<const uint32_t*>(w_codes), w_beta_ids, w_norms, w_betas, blocks, (int)(k / 8),
+        (float)sqrt((double)k), seg, reinterpret_cast<uint4*>(out_bf16));
+    NQ_CHECK_LAUNCH("nq_w4_decode");
+    return NQ_OK;
+}
+
 extern "C" int nq_w4_decode(const uint8_t* w_codes, const uint8_t* w_beta_ids, const float* w_norms,
                             const float* w_betas, int64_t n, int64_t k, int64_t w_block_offset,
                             int64_t seed, void* out_bf16, nq_stream_t stream) {
@@ -198,12 +211,6 @@ extern "C" int nq_w4_decode(const uint8_t* w_codes, const uint8_t* w_beta_ids, c
                "nq_w4_decode: block range exceeds the dither counter space");
     NQ_REQUIRE(nq_aligned16(out_bf16) && (reinterpret_cast<uintptr_t>(w_codes) & 3u) == 0, NQ_ERR_ALIGN,
                "nq_w4_decode: alignment");
-    const int64_t blocks = n * (k / 8);
-    const unsigned grid = (unsigned)((blocks + 255) / 256);
-    const uint32_t base = (uint32_t)((uint64_t)w_block_offset * 8u + (uint64_t)seed);
-    nq_w4_decode_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-        reinterpret_cast<const uint32_t*>(w_codes), w_beta_ids, w_norms, w_betas, blocks, (int)(k / 8),
-        (float)sqrt((double)k), base, reinterpret_cast<uint4*>(out_bf16));
-    NQ_CHECK_LAUNCH("nq_w4_decode");
-    return NQ_OK;
+    return nq_w4_decode_segments(w_codes, w_beta_ids, w_norms, w_betas, n, k, nq_one_segment(w_block_offset, seed),
+                                 out_bf16, reinterpret_cast<cudaStream_t>(stream));
 }

@@ -8,7 +8,10 @@ size_t nq_small_m_partial_bytes(int64_t m, int64_t n, int64_t k);
 int nq_launch_small_m(const void* a_dec, const uint8_t* w_codes, const uint8_t* w_beta_ids,
                       const float* w_norms, const float* w_betas, int64_t m, int64_t n, int64_t k,
                       int64_t w_block_offset, int64_t seed, void* out, int out_dtype,
-                      float* partial, unsigned* counters, cudaStream_t stream);
+                      float* partial, unsigned* counters, cudaStream_t stream, const NqDitherSegments* segments);
+int nq_w4_decode_segments(const uint8_t* w_codes, const uint8_t* w_beta_ids, const float* w_norms,
+                          const float* w_betas, int64_t n, int64_t k, const NqDitherSegments& seg, void* out_bf16,
+                          cudaStream_t stream);
 // tcgen05 path (nq_gemm_tc.cu)
 bool nq_tc_supported(int64_t m, int64_t n, int64_t k);
 size_t nq_tc_workspace_bytes(int64_t m, int64_t n, int64_t k);
@@ -49,12 +52,14 @@ extern "C" size_t nq_w4a4_workspace_bytes(int64_t m, int64_t n, int64_t k) {
     return carve(m, n, k).total;
 }
 
-extern "C" int nq_w4a4_gemm(const uint8_t* act_codes, const uint8_t* act_beta_ids, const float* act_norms,
-                            const float* act_betas, const void* act_decoded,
-                            const uint8_t* w_codes, const uint8_t* w_beta_ids, const float* w_norms,
-                            const float* w_betas, int64_t m, int64_t n, int64_t k,
-                            int64_t w_block_offset, int64_t seed, void* out, int out_dtype,
-                            void* workspace, size_t workspace_bytes, nq_stream_t stream) {
+namespace {
+
+// One projection; `seg` carries the dither counters of the (possibly stacked) weight.
+int w4a4_gemm_impl(const uint8_t* act_codes, const uint8_t* act_beta_ids, const float* act_norms,
+                   const float* act_betas, const void* act_decoded,
+                   const uint8_t* w_codes, const uint8_t* w_beta_ids, const float* w_norms,
+                   const float* w_betas, int64_t m, int64_t n, int64_t k, const NqDitherSegments& seg,
+                   void* out, int out_dtype, void* workspace, size_t workspace_bytes, nq_stream_t stream) {
     NQ_REQUIRE(w_codes && w_beta_ids && w_norms && w_betas && out, NQ_ERR_ARG, "nq_w4a4_gemm: null pointer");
     NQ_REQUIRE(act_decoded || (act_codes && act_beta_ids && act_norms && act_betas), NQ_ERR_ARG,
                "nq_w4a4_gemm: activation streams missing");
@@ -63,9 +68,6 @@ extern "C" int nq_w4a4_gemm(const uint8_t* act_codes, const uint8_t* act_beta_id
                (long long)m, (long long)n);
     NQ_REQUIRE(k >= 32 && k % 32 == 0, NQ_ERR_ARG, "nq_w4a4_gemm: k=%lld must be a multiple of 32", (long long)k);
     NQ_REQUIRE(out_dtype == NQ_F32 || out_dtype == NQ_BF16, NQ_ERR_ARG, "nq_w4a4_gemm: out_dtype must be f32 or bf16");
-    NQ_REQUIRE(seed >= 0 && seed < ((int64_t)1 << 31) && w_block_offset >= 0 &&
-                   w_block_offset + n * (k / 8) <= ((int64_t)1 << 28),
-               NQ_ERR_ARG, "nq_w4a4_gemm: dither seed / block range outside the 31-bit counter space");
     const Carve c = carve(m, n, k);
     NQ_REQUIRE(workspace && workspace_bytes >= c.total, NQ_ERR_WORKSPACE,
                "nq_w4a4_gemm: workspace of %zu bytes needed, %zu given", c.total, workspace_bytes);
@@ -84,7 +86,7 @@ extern "C" int nq_w4a4_gemm(const uint8_t* act_codes, const uint8_t* act_beta_id
     }
 
     if (m >= kTcMinM && nq_tc_supported(m, n, k)) {
-        int rc = nq_w4_decode(w_codes, w_beta_ids, w_norms, w_betas, n, k, w_block_offset, seed, ws + c.w_dec, stream);
+        int rc = nq_w4_decode_segments(w_codes, w_beta_ids, w_norms, w_betas, n, k, seg, ws + c.w_dec, s);
         if (rc) return rc;
         return nq_launch_tc_gemm(a_dec, ws + c.w_dec, m, n, k, out, out_dtype, ws + NQ_WS_STATUS_OFFSET, ws + c.tc,
                                  counters, s);
@@ -95,12 +97,57 @@ extern "C" int nq_w4a4_gemm(const uint8_t* act_codes, const uint8_t* act_beta_id
     for (int64_t m0 = 0; m0 < m; m0 += kSmallMMax) {
         const int64_t mc = (m - m0) < kSmallMMax ? (m - m0) : kSmallMMax;
         int rc = nq_launch_small_m(reinterpret_cast<const char*>(a_dec) + (size_t)m0 * k * 2, w_codes, w_beta_ids,
-                                   w_norms, w_betas, mc, n, k, w_block_offset, seed,
+                                   w_norms, w_betas, mc, n, k, 0, 0,
                                    reinterpret_cast<char*>(out) + (size_t)m0 * n * out_elem, out_dtype,
-                                   reinterpret_cast<float*>(ws + c.partial), counters, s);
+                                   reinterpret_cast<float*>(ws + c.partial), counters, s, &seg);
         if (rc) return rc;
     }
     return NQ_OK;
+}
+
+}  // namespace
+
+extern "C" int nq_w4a4_gemm(const uint8_t* act_codes, const uint8_t* act_beta_ids, const float* act_norms,
+                            const float* act_betas, const void* act_decoded,
+                            const uint8_t* w_codes, const uint8_t* w_beta_ids, const float* w_norms,
+                            const float* w_betas, int64_t m, int64_t n, int64_t k,
+                            int64_t w_block_offset, int64_t seed, void* out, int out_dtype,
+                            void* workspace, size_t workspace_bytes, nq_stream_t stream) {
+    NQ_REQUIRE(k >= 32 && k % 32 == 0 && n >= 8, NQ_ERR_ARG, "nq_w4a4_gemm: bad shape");
+    NQ_REQUIRE(seed >= 0 && seed < ((int64_t)1 << 31) && w_block_offset >= 0 &&
+                   w_block_offset + n * (k / 8) <= ((int64_t)1 << 28),
+               NQ_ERR_ARG, "nq_w4a4_gemm: dither seed / block range outside the 31-bit counter space");
+    return w4a4_gemm_impl(act_codes, act_beta_ids, act_norms, act_betas, act_decoded, w_codes, w_beta_ids, w_norms,
+                          w_betas, m, n, k, nq_one_segment(w_block_offset, seed), out, out_dtype, workspace,
+                          workspace_bytes, stream);
+}
+
+extern "C" int nq_w4a4_gemm_grouped(const uint8_t* act_codes, const uint8_t* act_beta_ids, const float* act_norms,
+                                    const float* act_betas, const void* act_decoded,
+                                    const uint8_t* w_codes, const uint8_t* w_beta_ids, const float* w_norms,
+                                    const float* w_betas, int64_t m, int64_t n, int64_t k, int segments,
+                                    const int64_t* seg_first_row, const int64_t* seg_block_offset,
+                                    const int64_t* seg_seed, void* out, int out_dtype,
+                                    void* workspace, size_t workspace_bytes, nq_stream_t stream) {
+    NQ_REQUIRE(segments >= 1 && segments <= NQ_MAX_SEGMENTS && seg_first_row && seg_block_offset && seg_seed,
+               NQ_ERR_ARG, "nq_w4a4_gemm_grouped: 1..%d segments with their tables", NQ_MAX_SEGMENTS);
+    NQ_REQUIRE(k >= 32 && k % 32 == 0 && n >= 8, NQ_ERR_ARG, "nq_w4a4_gemm_grouped: bad shape");
+    NqDitherSegments seg = {};
+    seg.count = segments;
+    const int64_t bpr = k / 8;
+    for (int i = 0; i < segments; ++i) {
+        const int64_t first = seg_first_row[i], end = i + 1 < segments ? seg_first_row[i + 1] : n;
+        NQ_REQUIRE((i == 0 ? first == 0 : first > seg_first_row[i - 1]) && first < end && end <= n, NQ_ERR_ARG,
+                   "nq_w4a4_gemm_grouped: segment rows must start at 0, increase and stay below n");
+        NQ_REQUIRE(seg_seed[i] >= 0 && seg_seed[i] < ((int64_t)1 << 31) && seg_block_offset[i] >= 0 &&
+                       seg_block_offset[i] + (end - first) * bpr <= ((int64_t)1 << 28),
+                   NQ_ERR_ARG, "nq_w4a4_gemm_grouped: dither seed / block range outside the 31-bit counter space");
+        seg.first_row[i] = (int)first;
+        // block g of the stacked weight is block g - first * bpr of tensor i
+        seg.base[i] = (uint32_t)((uint64_t)(seg_block_offset[i] - first * bpr) * 8u + (uint64_t)seg_seed[i]);
+    }
+    return w4a4_gemm_impl(act_codes, act_beta_ids, act_norms, act_betas, act_decoded, w_codes, w_beta_ids, w_norms,
+                          w_betas, m, n, k, seg, out, out_dtype, workspace, workspace_bytes, stream);
 }
 
 extern "C" int nq_w4a4_status(const void* workspace, uint32_t* status_host, nq_stream_t stream) {

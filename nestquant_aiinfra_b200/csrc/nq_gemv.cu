@@ -31,7 +31,7 @@ struct SmallMParams {
     int m, n, k;
     int slice_blocks;  // blocks per K slice (multiple of 32)
     int ksplit;
-    uint32_t counter_base;  // (8 * w_block_offset + seed) mod 2^32
+    NqDitherSegments seg;   // dither counters: base (8 * w_block_offset + seed) mod 2^32 per stacked tensor
     float sqrt_k;
     float* partial;      // [ksplit, m, n] when ksplit > 1
     unsigned* counters;  // [n / 8], zero on entry, zero on exit
@@ -62,6 +62,7 @@ __global__ void __launch_bounds__(kThreads) nq_w4a4_small_m_kernel(const SmallMP
 
     const int row = blockIdx.x * kRowsPerCta + warp;
     const float ds = nq_div(__ldg(p.w_norms + row), p.sqrt_k);
+    const uint32_t counter_base = nq_segment_base(p.seg, row);
 
     float acc[MT];
 #pragma unroll
@@ -70,7 +71,7 @@ __global__ void __launch_bounds__(kThreads) nq_w4a4_small_m_kernel(const SmallMP
     for (int b = lane; b < slice_n; b += 32) {
         const int64_t g = (int64_t)row * bpr + slice0 + b;
         float w[8];
-        nq_decode_weight_block(__ldg(p.w_codes + g), p.counter_base + (uint32_t)g * 8u, w);
+        nq_decode_weight_block(__ldg(p.w_codes + g), counter_base + (uint32_t)g * 8u, w);
         const float bt = __ldg(p.w_betas + nq_beta_id(p.w_beta_ids, g));
 #pragma unroll
         for (int j = 0; j < 8; ++j) w[j] = nq_bf16_round(nq_mul(nq_mul(w[j], bt), ds));
@@ -167,7 +168,7 @@ size_t nq_small_m_partial_bytes(int64_t m, int64_t n, int64_t k) {
 int nq_launch_small_m(const void* a_dec, const uint8_t* w_codes, const uint8_t* w_beta_ids,
                       const float* w_norms, const float* w_betas, int64_t m, int64_t n, int64_t k,
                       int64_t w_block_offset, int64_t seed, void* out, int out_dtype,
-                      float* partial, unsigned* counters, cudaStream_t stream) {
+                      float* partial, unsigned* counters, cudaStream_t stream, const NqDitherSegments* segments) {
     SmallMParams p;
     p.a_dec = reinterpret_cast<const __nv_bfloat16*>(a_dec);
     p.w_codes = reinterpret_cast<const uint32_t*>(w_codes);
@@ -176,7 +177,7 @@ int nq_launch_small_m(const void* a_dec, const uint8_t* w_codes, const uint8_t* 
     p.w_betas = w_betas;
     p.m = (int)m; p.n = (int)n; p.k = (int)k;
     small_m_split(k, &p.slice_blocks, &p.ksplit);
-    p.counter_base = (uint32_t)((uint64_t)w_block_offset * 8u + (uint64_t)seed);
+    p.seg = segments ? *segments : nq_one_segment(w_block_offset, seed);
     p.sqrt_k = (float)sqrt((double)k);
     p.partial = partial;
     p.counters = counters;

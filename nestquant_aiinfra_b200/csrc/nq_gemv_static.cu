@@ -32,7 +32,7 @@ size_t nq_small_m_partial_bytes(int64_t m, int64_t n, int64_t k);
 int nq_launch_small_m(const void* a_dec, const uint8_t* w_codes, const uint8_t* w_beta_ids,
                       const float* w_norms, const float* w_betas, int64_t m, int64_t n, int64_t k,
                       int64_t w_block_offset, int64_t seed, void* out, int out_dtype,
-                      float* partial, unsigned* counters, cudaStream_t stream);
+                      float* partial, unsigned* counters, cudaStream_t stream, const NqDitherSegments* segments);
 
 namespace {
 
@@ -113,5 +113,5 @@ extern "C" int nq_w4a4_gemv_static(const uint8_t* act_codes, const uint8_t* act_
     rc = nq_a4_decode(act_codes, act_beta_ids, act_norms, act_betas, m, k, decoded, NQ_BF16, stream);
     if (rc) return rc;
     return nq_launch_small_m(decoded, w_codes, w_beta_ids, w_norms, w_betas, m, n, k, w_block_offset, seed, out,
-                             out_dtype, partial, counters, s);
+                             out_dtype, partial, counters, s, nullptr);
 }

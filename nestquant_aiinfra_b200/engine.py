@@ -16,7 +16,8 @@ import torch
 from torch import nn
 
 from .formats import ACTIVATION_BETAS, KEY_BETAS, VALUE_BETAS, WEIGHT_BETAS, tensor_dither_seed
-from .fused_linear import FusedNQRTLinear, SharedHadamardCache, SharedPackedActivationCache
+from .fused_linear import (FusedNQRTLinear, SharedHadamardCache, SharedPackedActivationCache,
+                           SharedProjectionGroup)
 from .hf_backend import BatchedNQKVLlamaCache, install_batched_nqkv_llama_backend
 from .norm import fuse_rmsnorm_
 from .rope import fused_rope_scope
@@ -29,7 +30,8 @@ SHARE_GROUPS = (("self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj"), ("
 
 
 def quantize_llama_projections_(model: nn.Module, *, weight_betas: Sequence[float] = WEIGHT_BETAS,
-                                activation_betas: Sequence[float] = ACTIVATION_BETAS, project_seed: int = 58) -> int:
+                                activation_betas: Sequence[float] = ACTIVATION_BETAS, project_seed: int = 58,
+                                group_shared_inputs: bool = True) -> int:
     """Replace every decoder projection by a packed NQRT4 module, encoding W*H on the GPU.
 
     The input of each module is Hadamard-rotated, so the stored weight is ``hadamard(W)``
@@ -60,6 +62,10 @@ def quantize_llama_projections_(model: nn.Module, *, weight_betas: Sequence[floa
             setattr(parent, child_name, fused.to(linear.weight.device))
             del linear, rotated
             converted += 1
+        if group_shared_inputs:  # q/k/v and gate/up: one decode + GEMM launch sequence per group
+            for group in SHARE_GROUPS:
+                members = [getattr(getattr(layer, name.split(".")[0]), name.split(".")[1]) for name in group]
+                SharedProjectionGroup(members)
     torch.cuda.empty_cache()
     return converted
 
@@ -115,11 +121,13 @@ class BatchedNQKVLlamaRunner:
         width = max(int(p.numel()) for p in prompts)
         ids = torch.zeros((len(slots), width), dtype=torch.long, device=self.device)
         lengths = []
+        assignments = []
         for row, (slot, prompt) in enumerate(zip(slots, prompts)):
             self._generation[slot] += 1
-            self.cache.register(f"slot-{slot}-generation-{self._generation[slot]}", slot=slot)
+            assignments.append((f"slot-{slot}-generation-{self._generation[slot]}", slot))
             ids[row, :prompt.numel()] = prompt.to(self.device)
             lengths.append(int(prompt.numel()))
+        self.cache.register_batch(assignments)
         slot_ids = torch.tensor(list(slots), dtype=torch.int32, device=self.device)
         q_lens = torch.tensor(lengths, dtype=torch.int32, device=self.device)
         positions = torch.arange(width, device=self.device).unsqueeze(0).expand(len(slots), width).contiguous()

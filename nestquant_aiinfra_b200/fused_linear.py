@@ -17,7 +17,8 @@ from torch import nn
 
 from .rotation import hadamard
 from .runtime.w4a4 import (PreparedNQA4Activation, PreparedNQRTLinear, linear_packed_w4a4, prepare_fused_linear,
-                           quantize_activation_cuda, can_rotate_in_encoder, prefer_rotation_in_encoder)
+                           quantize_activation_cuda, can_rotate_in_encoder, prefer_rotation_in_encoder,
+                           group_prepared_linears)
 
 _BACKENDS = {"packed_w4a4_cuda_mma", "packed_w4a4_cuda_gemv_m1", "packed_w4a4"}
 
@@ -111,6 +112,50 @@ class SharedPackedActivationCache:
         self._remaining = 0
 
 
+class SharedProjectionGroup:
+    """One launch sequence for projections that share an input (q/k/v, gate/up).
+
+    The members' packed weights are stacked (``group_prepared_linears``); the first member called
+    with a packed activation runs the projection over all stacked rows, every member returns its
+    own column range of that result.  Members must receive the same packed activation object
+    (a shared ``SharedPackedActivationCache``); a member called with another one just triggers a
+    new projection.  The operands of every output column are the member's own (same decoded
+    weights, same activation); on the tensor-core path the split of K follows the tile count, so
+    sums may be taken in another order than in the member's own launch.
+    """
+
+    def __init__(self, members: "list[FusedNQRTLinear]", device: torch.device | str | None = None) -> None:
+        if any(member._prepared is None for member in members) and device is None:
+            raise ValueError("members without a prepared weight need the target device")
+        prepared = [member._prepared if device is None else member._prepared_for(torch.device(device))
+                    for member in members]
+        self.stacked, views = group_prepared_linears(prepared)
+        self.bounds = []
+        start = 0
+        for index, (member, view) in enumerate(zip(members, views)):
+            member._prepared = view          # the member keeps a view: no stream is held twice
+            member._group, member._group_index = self, index
+            self.bounds.append((start, start + view.rows))
+            start += view.rows
+        self._packed = None
+        self._output: torch.Tensor | None = None
+        self._remaining = 0
+        self.launches = 0
+
+    def project(self, packed: PreparedNQA4Activation, index: int) -> torch.Tensor:
+        if self._packed is not packed or self._output is None:
+            self._output = linear_packed_w4a4(packed, self.stacked)
+            self._packed = packed
+            self._remaining = len(self.bounds)
+            self.launches += 1
+        start, end = self.bounds[index]
+        output = self._output[..., start:end]
+        self._remaining -= 1
+        if self._remaining <= 0:
+            self._packed = self._output = None
+        return output
+
+
 class FusedNQRTLinear(nn.Module):
     """Apply one packed NQRT v4 weight without materialising a BF16 matrix in the module.
 
@@ -169,6 +214,9 @@ class FusedNQRTLinear(nn.Module):
         self.input_hadamard = input_hadamard
         # block-diagonal rotation of the input (tensor-parallel K shards); set by the owner, None = off
         self.input_rotation_block: int | None = None
+        # set by SharedProjectionGroup: this projection runs as a column range of a stacked weight
+        self._group: "SharedProjectionGroup | None" = None
+        self._group_index = 0
         self.input_transform_cache = input_transform_cache
         self.output_dtype = output_dtype
         self.compute_backend = compute_backend
@@ -258,7 +306,8 @@ class FusedNQRTLinear(nn.Module):
                 hadamard_block=block)
         self.a4_call_count += 1
         self.a4_encode_count += int(encoded)
-        outputs = linear_packed_w4a4(packed, prepared)
+        outputs = (linear_packed_w4a4(packed, prepared) if self._group is None
+                   else self._group.project(packed, self._group_index))
         self.w4a4_cuda_mma_dispatch_count += 1
         return outputs.to(self.output_dtype or original_dtype)
 

@@ -87,21 +87,36 @@ class BatchedNQKVLlamaCache(Cache):
         self._sequence_of_slot[slot] = sequence_id
 
     def register_batch(self, assignments: Sequence[tuple[Hashable, int]]) -> None:
+        """Register several sequences at once (one index upload instead of scalar writes per slot and layer)."""
+        slots = [int(slot) for _, slot in assignments]
+        if len(set(slots)) != len(slots) or any(slot in self._sequence_of_slot for slot in slots):
+            raise RuntimeError("a slot of the batch is already registered")
+        if any(not 0 <= slot < self.capacity for slot in slots):
+            raise ValueError("slot outside cache capacity")
+        if not slots:
+            return
+        index = torch.tensor(slots, dtype=torch.long, device=self.device)
+        for cache in self.layer_caches:
+            cache.register_many(index)
+        self.active_mask.index_fill_(0, index, True)
         for sequence_id, slot in assignments:
-            self.register(sequence_id, slot=slot)
+            self._sequence_of_slot[slot] = sequence_id
 
     def release_slots(self, slots: Sequence[int]) -> tuple[Hashable, ...]:
-        released = []
+        released, freed = [], []
         for slot in slots:
             if slot not in self._sequence_of_slot:
                 continue
             released.append(self._sequence_of_slot.pop(slot))
+            freed.append(int(slot))
+        if freed:
+            index = torch.tensor(freed, dtype=torch.long, device=self.device)
             for cache in self.layer_caches:
-                cache.active[slot] = False
-                cache.sequence_lengths[slot] = 0
-                cache.hot_lengths[slot] = 0
-                cache.page_counts[slot] = 0
-            self.active_mask[slot] = False
+                cache.active.index_fill_(0, index, False)
+                cache.sequence_lengths.index_fill_(0, index, 0)
+                cache.hot_lengths.index_fill_(0, index, 0)
+                cache.page_counts.index_fill_(0, index, 0)
+            self.active_mask.index_fill_(0, index, False)
         return tuple(released)
 
     def set_decode_state(self, *, slot_ids: torch.Tensor | None = None, active_mask: torch.Tensor | None = None) -> None:

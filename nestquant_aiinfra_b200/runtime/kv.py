@@ -141,6 +141,15 @@ class NQKVHotColdCache:
         self.page_indices[slot].fill_(-1)
         return slot
 
+    def register_many(self, index: torch.Tensor) -> None:
+        """``register`` for all slots of a device index tensor: six launches, no host-to-device scalar copies."""
+        self.active.index_fill_(0, index, True)
+        self.page_counts.index_fill_(0, index, 0)
+        self.last_page_len.index_fill_(0, index, 0)
+        self.hot_lengths.index_fill_(0, index, 0)
+        self.sequence_lengths.index_fill_(0, index, 0)
+        self.page_indices.index_fill_(0, index, -1)
+
     def reserve_targets(self, slots: Sequence[int]) -> list[int]:
         """Allocate one target page per slot for the next boundary pack (host control plane)."""
         ids = [self.pool.allocate() for _ in slots]

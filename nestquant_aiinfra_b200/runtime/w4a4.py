@@ -115,6 +115,9 @@ class PreparedNQRTLinear:
     # dither counter of the unsharded weight (the reference always passes 0, cuda_w4a4_mma.py:243).
     block_offset: int = 0
     out_features: int | None = None
+    # A weight that stacks the rows of several tensors sharing one input (q/k/v, gate/up):
+    # (first_row, block_offset, dither_seed) per tensor, see ``group_prepared_linears``.
+    segments: tuple[tuple[int, int, int], ...] | None = None
 
     @property
     def rows(self) -> int:
@@ -167,10 +170,12 @@ def can_rotate_in_encoder(feature_count: int, hadamard_block: int) -> bool:
 def prefer_rotation_in_encoder(rows: int, feature_count: int) -> bool:
     """Whether the fused launch beats ``hadamard`` + encoder for this shape.
 
-    A launch with few long rows splits every row over several CTAs and each of them would repeat
-    the transform of the whole row; there the two launches are faster.
+    Up to 4096 features the fused launch is the faster one at every row count; longer rows need so
+    much shared memory for the transform next to the encoder's own that occupancy drops, and a
+    launch with few rows would repeat the long transform in every CTA a row is split over: there
+    the two launches win (measured on 8192 features: 1.5 ms fused against 0.85 ms for 8644 rows).
     """
-    return feature_count <= 4096 or rows >= 148
+    return feature_count <= 4096
 
 
 def quantize_activation_cuda(
@@ -338,6 +343,17 @@ def _run(activation: PreparedNQA4Activation, weight: PreparedNQRTLinear, out_dty
     workspace = workspace_for(device, nbytes)
     out = torch.empty((m, n), dtype=out_dtype, device=device)
     decoded = activation.decoded if use_decoded else None
+    if weight.segments:
+        count = len(weight.segments)
+        table = lambda column: (ctypes.c_int64 * count)(*[int(entry[column]) for entry in weight.segments])  # noqa: E731
+        status = library.nq_w4a4_gemm_grouped(
+            _ptr(activation.code_payload), _ptr(activation.beta_payload), _ptr(activation.row_norms),
+            _ptr(activation.beta_table), _ptr(decoded),
+            _ptr(weight.code_payload), _ptr(weight.beta_payload), _ptr(weight.row_norms), _ptr(weight.beta_table),
+            _I64(m), _I64(n), _I64(k), ctypes.c_int(count), table(0), table(1), table(2),
+            _ptr(out), _DTYPE_TAG[out_dtype], _ptr(workspace), ctypes.c_size_t(workspace.numel()), _stream(device))
+        _lib.check(status, "linear_packed_w4a4")
+        return out
     status = library.nq_w4a4_gemm(
         _ptr(activation.code_payload), _ptr(activation.beta_payload), _ptr(activation.row_norms),
         _ptr(activation.beta_table), _ptr(decoded),
@@ -346,6 +362,46 @@ def _run(activation: PreparedNQA4Activation, weight: PreparedNQRTLinear, out_dty
         _ptr(out), _DTYPE_TAG[out_dtype], _ptr(workspace), ctypes.c_size_t(workspace.numel()), _stream(device))
     _lib.check(status, "linear_packed_w4a4")
     return out
+
+
+MAX_GROUP = 4  # NQ_MAX_SEGMENTS of the library
+
+
+def group_prepared_linears(weights: Sequence[PreparedNQRTLinear]) -> tuple[PreparedNQRTLinear, list[PreparedNQRTLinear]]:
+    """Stack packed weights that share an input into one launchable weight.
+
+    Returns the stacked weight (its streams are the members' streams one after the other, every
+    member keeping its own dither counters) and the members again as views into the stacked
+    buffers, so the originals can be dropped and no byte is held twice.  Each output column of a
+    projection with the stacked weight has the member's own operands (bit-equal result on the
+    CUDA-core path; same sums in possibly another order on the tensor-core path).
+    """
+    if not 2 <= len(weights) <= MAX_GROUP:
+        raise ValueError(f"a group holds 2..{MAX_GROUP} weights")
+    first = weights[0]
+    k = int(first.record.feature_count)
+    for w in weights:
+        if not isinstance(w, PreparedNQRTLinear) or w.segments:
+            raise TypeError("members must be plain PreparedNQRTLinear weights")
+        if int(w.record.feature_count) != k or w.code_payload.device != first.code_payload.device:
+            raise ValueError("members must share the feature count and the device")
+        if not torch.equal(w.beta_table, first.beta_table):
+            raise ValueError("members must share the beta table")
+    codes = torch.cat([w.code_payload[:w.rows * k // 2] for w in weights])
+    betas = torch.cat([w.beta_payload[:w.rows * k // 32] for w in weights])
+    norms = torch.cat([w.row_norms[:w.rows] for w in weights])
+    segments, views, row = [], [], 0
+    for w in weights:
+        segments.append((row, int(w.block_offset), int(w.record.dither_seed)))
+        views.append(PreparedNQRTLinear(
+            record=w.record, code_payload=codes[row * k // 2:(row + w.rows) * k // 2],
+            beta_payload=betas[row * k // 32:(row + w.rows) * k // 32], row_norms=norms[row:row + w.rows],
+            beta_table=first.beta_table, block_offset=w.block_offset, out_features=w.rows))
+        row += w.rows
+    stacked = PreparedNQRTLinear(record=first.record, code_payload=codes, beta_payload=betas, row_norms=norms,
+                                 beta_table=first.beta_table, block_offset=0, out_features=row,
+                                 segments=tuple(segments))
+    return stacked, views
 
 
 def read_status(device: torch.device | str = "cuda") -> int:

@@ -15,7 +15,8 @@ from torch import nn
 
 from .engine import BatchedNQKVLlamaRunner
 from .formats import ACTIVATION_BETAS, KEY_BETAS, VALUE_BETAS, WEIGHT_BETAS, tensor_dither_seed
-from .fused_linear import FusedNQRTLinear, SharedHadamardCache, SharedPackedActivationCache
+from .fused_linear import (FusedNQRTLinear, SharedHadamardCache, SharedPackedActivationCache,
+                           SharedProjectionGroup)
 from .hf_backend import BatchedNQKVLlamaCache, install_batched_nqkv_llama_backend
 from .norm import fuse_rmsnorm_
 from .rotation import hadamard
@@ -76,6 +77,8 @@ def build_llama_tp_shard(*, hidden_size: int, intermediate_size: int, num_layers
                                         activation_betas=ACTIVATION_BETAS, packed_activation_cache=acache)
             setattr(parent, child_name, fused.to(device))
             del linear
+        for group in GROUPS:  # q/k/v and gate/up shards: one decode + GEMM launch sequence per group
+            SharedProjectionGroup([getattr(getattr(layer, name.split(".")[0]), name.split(".")[1]) for name in group])
         torch.cuda.empty_cache()
     cache = BatchedNQKVLlamaCache(capacity=capacity, num_layers=num_layers, num_query_heads=num_heads // world,
                                   num_kv_heads=num_kv_heads // world, head_dim=head_dim, max_cache_len=max_cache_len,

@@ -4,7 +4,7 @@ import numpy as np
 import pytest
 import torch
 
-from helpers import ACT_BETAS, MAX_ABS_TOL, REL_FRO_TOL, make_weight_record, max_abs, rel_fro, rng
+from helpers import ACT_BETAS, MAX_ABS_TOL, REL_FRO_TOL, W_BETAS as W_BETAS_LOCAL, make_weight_record, max_abs, rel_fro, rng
 
 pytestmark = pytest.mark.gpu
 
@@ -153,3 +153,32 @@ def test_rope_and_rotation_in_one_launch_equal_the_tensor_ops(batch, heads, toke
     assert torch.equal(rope_hadamard(x, cos, sin, rotate=False), stock)
     assert torch.equal(rope_hadamard(x, cos, sin), hadamard(stock.float()).to(dtype))
     assert torch.equal(rope_hadamard(x[:1], cos[:1], sin[:1]), rope_hadamard(x, cos, sin)[:1])
+
+
+def test_stacked_projection_group_equals_the_members_own_projections(oracle):
+    """q/k/v-style group: one launch sequence over the stacked weight, column ranges equal to the members' own results."""
+    from nestquant_aiinfra_b200.fused_linear import (FusedNQRTLinear, SharedPackedActivationCache,
+                                                     SharedProjectionGroup)
+    from nestquant_aiinfra_b200.runtime import quantize_weight_cuda
+
+    k, sizes = 512, (256, 128, 128)
+    weights = [quantize_weight_cuda((0.02 * torch.randn(n, k, generator=rng(700 + n))).cuda(), betas=W_BETAS_LOCAL,
+                                    dither_seed=1000 + n) for n in sizes]
+    for m in (1, 5, 16, 40, 200):
+        x = torch.randn(m, k, generator=rng(710 + m)).bfloat16().cuda()
+        cache = SharedPackedActivationCache(len(sizes))
+        members = [FusedNQRTLinear(w, activation_betas=ACT_BETAS, packed_activation_cache=cache) for w in weights]
+        with torch.no_grad():
+            alone = [FusedNQRTLinear(w, activation_betas=ACT_BETAS)(x) for w in weights]
+            group = SharedProjectionGroup(members)
+            together = [member(x) for member in members]
+        assert group.launches == 1 and cache.misses == 1
+        for a, b in zip(alone, together):
+            assert b.shape == a.shape
+            if m < 8:   # CUDA-core path: the K split does not depend on N, so not a bit moves
+                assert torch.equal(a, b)
+            else:       # tensor-core path: the split-K layout follows the tile count; same operands, other summation order
+                assert rel_fro(b.float().cpu().numpy(), a.float().cpu().numpy()) < 2e-3
+        assert sum(member.packed_device_bytes for member in members) == \
+            sum(t.numel() * t.element_size() for t in (group.stacked.code_payload, group.stacked.beta_payload,
+                                                       group.stacked.row_norms)) + 3 * 16
