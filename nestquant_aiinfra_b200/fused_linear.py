@@ -150,6 +150,9 @@ class SharedProjectionGroup:
             self.launches += 1
         start, end = self.bounds[index]
         output = self._output[..., start:end]
+        if packed.token_count >= 512:
+            # many rows: tensor ops on a column slice fall off their vectorised kernels, a copy is cheaper
+            output = output.contiguous()
         self._remaining -= 1
         if self._remaining <= 0:
             self._packed = self._output = None
