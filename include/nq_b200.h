@@ -185,6 +185,20 @@ int nq_w4_decode(const uint8_t* w_codes, const uint8_t* w_beta_ids, const float*
                  const float* w_betas, int64_t n, int64_t k, int64_t w_block_offset,
                  int64_t seed, void* out_bf16, nq_stream_t stream);
 
+/* The projection on a weight that the caller keeps DECODED in device memory (w_decoded = the
+ * bf16 [n,k] output of nq_w4_decode, 4x the packed bytes): an opt-in trade of HBM capacity for
+ * time.  The operands are exactly the values nq_w4a4_gemm regenerates on every call, so the
+ * result agrees with it up to the order of the FP32 sums; m < 5 runs a streaming GEMV bound by
+ * HBM (one warp per output channel), larger m the tcgen05 GEMM without the per-call weight
+ * decode.  Activation arguments, out, out_dtype and the zero-initialised workspace (size from
+ * nq_w4a4_resident_workspace_bytes) as for nq_w4a4_gemm.  The reference never keeps a decoded
+ * weight (models/fused_linear.py:130-137 states that as the module's purpose): no counterpart. */
+size_t nq_w4a4_resident_workspace_bytes(int64_t m, int64_t n, int64_t k);
+int nq_w4a4_gemm_resident(const uint8_t* act_codes, const uint8_t* act_beta_ids, const float* act_norms,
+                          const float* act_betas, const void* act_decoded, const void* w_decoded,
+                          int64_t m, int64_t n, int64_t k, void* out, int out_dtype,
+                          void* workspace, size_t workspace_bytes, nq_stream_t stream);
+
 /* -------------------------------------------------------------------------
  * NQKV4 paged cache.  Device data model (unchanged from the reference):
  *   pool   key_codes/value_codes u8[capacity, P*H*D/2], key_betas/value_betas u8[capacity, P*H*D/32],

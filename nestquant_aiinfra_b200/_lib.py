@@ -17,7 +17,7 @@ _PKG = Path(__file__).resolve().parent
 CSRC = _PKG / "csrc"
 LIB_PATH = _PKG / "libnq_b200.so"
 HEADER = _PKG.parent / "include" / "nq_b200.h"
-SOURCES = ("nq_encode.cu", "nq_gemv.cu", "nq_gemv_static.cu", "nq_gemm.cu", "nq_gemm_tc.cu", "nq_kv.cu", "nq_attn.cu",
+SOURCES = ("nq_encode.cu", "nq_gemv.cu", "nq_gemv_bf16.cu", "nq_gemv_static.cu", "nq_gemm.cu", "nq_gemm_tc.cu", "nq_kv.cu", "nq_attn.cu",
            "nq_rotate.cu", "nq_encode_rotated.cu", "nq_norm.cu", "nq_rope.cu")
 
 NQ_F32, NQ_BF16, NQ_F16 = 0, 1, 2
@@ -74,7 +74,7 @@ def lib() -> ctypes.CDLL:
         handle.nq_last_error.restype = ctypes.c_char_p
         handle.nq_w4a4_workspace_bytes.restype = ctypes.c_size_t
         handle.nq_launch_count.restype = ctypes.c_ulonglong
-        for name in ("nq_kv_attention_workspace_bytes",):
+        for name in ("nq_kv_attention_workspace_bytes", "nq_w4a4_resident_workspace_bytes"):
             if hasattr(handle, name):
                 getattr(handle, name).restype = ctypes.c_size_t
         _LIB = handle

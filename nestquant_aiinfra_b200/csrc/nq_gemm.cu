@@ -18,6 +18,11 @@ size_t nq_tc_workspace_bytes(int64_t m, int64_t n, int64_t k);
 int nq_launch_tc_gemm(const void* a_dec, const void* w_dec, int64_t m, int64_t n, int64_t k, void* out,
                       int out_dtype, void* status_word, void* partial, unsigned* counters, cudaStream_t stream);
 
+// streaming GEMV on a resident BF16 weight (nq_gemv_bf16.cu)
+int nq_bf16_gemv_max_rows();
+int nq_launch_bf16_gemv(const void* a_dec, const void* w_dec, int64_t m, int64_t n, int64_t k, void* out,
+                        int out_dtype, cudaStream_t stream);
+
 namespace {
 
 constexpr int64_t kSmallMMax = 16;  // rows handled by one launch of the CUDA-core kernel
@@ -148,6 +153,78 @@ extern "C" int nq_w4a4_gemm_grouped(const uint8_t* act_codes, const uint8_t* act
     }
     return w4a4_gemm_impl(act_codes, act_beta_ids, act_norms, act_betas, act_decoded, w_codes, w_beta_ids, w_norms,
                           w_betas, m, n, k, seg, out, out_dtype, workspace, workspace_bytes, stream);
+}
+
+// ---- resident decoded weights ---------------------------------------------------------------
+namespace {
+
+// From this many rows on the tcgen05 GEMM is used on a resident weight; below, the streaming GEMV.
+constexpr int64_t kResidentTcMinM = 5;
+
+struct ResidentCarve {
+    size_t a_dec, tc, total;
+};
+
+ResidentCarve carve_resident(int64_t m, int64_t n, int64_t k) {
+    ResidentCarve c;
+    size_t off = NQ_WS_COUNTER_BYTES;
+    c.a_dec = off;
+    off += align256((size_t)m * k * 2);
+    c.tc = off;
+    if (m >= kResidentTcMinM && nq_tc_supported(m, n, k)) off += align256(nq_tc_workspace_bytes(m, n, k));
+    c.total = off;
+    return c;
+}
+
+}  // namespace
+
+extern "C" size_t nq_w4a4_resident_workspace_bytes(int64_t m, int64_t n, int64_t k) {
+    if (m < 1 || n < 1 || k < 8) return 0;
+    return carve_resident(m, n, k).total;
+}
+
+extern "C" int nq_w4a4_gemm_resident(const uint8_t* act_codes, const uint8_t* act_beta_ids, const float* act_norms,
+                                     const float* act_betas, const void* act_decoded, const void* w_decoded,
+                                     int64_t m, int64_t n, int64_t k, void* out, int out_dtype,
+                                     void* workspace, size_t workspace_bytes, nq_stream_t stream) {
+    NQ_REQUIRE(w_decoded && out, NQ_ERR_ARG, "nq_w4a4_gemm_resident: null pointer");
+    NQ_REQUIRE(act_decoded || (act_codes && act_beta_ids && act_norms && act_betas), NQ_ERR_ARG,
+               "nq_w4a4_gemm_resident: activation streams missing");
+    NQ_REQUIRE(m >= 1 && n >= 8 && n % 8 == 0 && n <= 131064, NQ_ERR_ARG,
+               "nq_w4a4_gemm_resident: m=%lld n=%lld unsupported (n must be a multiple of 8, <= 131064)",
+               (long long)m, (long long)n);
+    NQ_REQUIRE(k >= 32 && k % 32 == 0, NQ_ERR_ARG, "nq_w4a4_gemm_resident: k=%lld must be a multiple of 32",
+               (long long)k);
+    NQ_REQUIRE(out_dtype == NQ_F32 || out_dtype == NQ_BF16, NQ_ERR_ARG,
+               "nq_w4a4_gemm_resident: out_dtype must be f32 or bf16");
+    const ResidentCarve c = carve_resident(m, n, k);
+    NQ_REQUIRE(workspace && workspace_bytes >= c.total, NQ_ERR_WORKSPACE,
+               "nq_w4a4_gemm_resident: workspace of %zu bytes needed, %zu given", c.total, workspace_bytes);
+    NQ_REQUIRE(nq_aligned16(workspace) && nq_aligned16(out) && nq_aligned16(w_decoded) &&
+                   (!act_decoded || nq_aligned16(act_decoded)),
+               NQ_ERR_ALIGN, "nq_w4a4_gemm_resident: workspace, out, w_decoded and act_decoded must be 16-byte aligned");
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    char* ws = reinterpret_cast<char*>(workspace);
+
+    const void* a_dec = act_decoded;
+    if (!a_dec) {
+        int rc = nq_a4_decode(act_codes, act_beta_ids, act_norms, act_betas, m, k, ws + c.a_dec, NQ_BF16, stream);
+        if (rc) return rc;
+        a_dec = ws + c.a_dec;
+    }
+    if (m >= kResidentTcMinM && nq_tc_supported(m, n, k))
+        return nq_launch_tc_gemm(a_dec, w_decoded, m, n, k, out, out_dtype, ws + NQ_WS_STATUS_OFFSET, ws + c.tc,
+                                 reinterpret_cast<unsigned*>(ws), s);
+
+    const size_t out_elem = out_dtype == NQ_BF16 ? 2 : 4;
+    const int64_t step = nq_bf16_gemv_max_rows();
+    for (int64_t m0 = 0; m0 < m; m0 += step) {
+        const int64_t mc = (m - m0) < step ? (m - m0) : step;
+        int rc = nq_launch_bf16_gemv(reinterpret_cast<const char*>(a_dec) + (size_t)m0 * k * 2, w_decoded, mc, n, k,
+                                     reinterpret_cast<char*>(out) + (size_t)m0 * n * out_elem, out_dtype, s);
+        if (rc) return rc;
+    }
+    return NQ_OK;
 }
 
 extern "C" int nq_w4a4_status(const void* workspace, uint32_t* status_host, nq_stream_t stream) {

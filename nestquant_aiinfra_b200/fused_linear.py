@@ -18,7 +18,7 @@ from torch import nn
 from .rotation import hadamard
 from .runtime.w4a4 import (PreparedNQA4Activation, PreparedNQRTLinear, linear_packed_w4a4, prepare_fused_linear,
                            quantize_activation_cuda, can_rotate_in_encoder, prefer_rotation_in_encoder,
-                           group_prepared_linears)
+                           group_prepared_linears, keep_decoded_weight)
 
 _BACKENDS = {"packed_w4a4_cuda_mma", "packed_w4a4_cuda_gemv_m1", "packed_w4a4"}
 
@@ -130,6 +130,7 @@ class SharedProjectionGroup:
         prepared = [member._prepared if device is None else member._prepared_for(torch.device(device))
                     for member in members]
         self.stacked, views = group_prepared_linears(prepared)
+        self.views = views
         self.bounds = []
         start = 0
         for index, (member, view) in enumerate(zip(members, views)):
@@ -141,6 +142,12 @@ class SharedProjectionGroup:
         self._output: torch.Tensor | None = None
         self._remaining = 0
         self.launches = 0
+
+    def keep_decoded_weight(self) -> int:
+        """Keep the BF16 reconstruction of the stacked weight in device memory (opt-in, see
+        ``runtime.keep_decoded_weight``); returns the bytes this adds."""
+        self.stacked = keep_decoded_weight(self.stacked, self.views)
+        return self.stacked.decoded.numel() * 2
 
     def project(self, packed: PreparedNQA4Activation, index: int) -> torch.Tensor:
         if self._packed is not packed or self._output is None:
@@ -246,6 +253,21 @@ class FusedNQRTLinear(nn.Module):
             return 0
         return sum(t.numel() * t.element_size() for t in (p.code_payload, p.beta_payload, p.row_norms, p.beta_table))
 
+    def keep_decoded_weight(self, device: torch.device | str | None = None) -> int:
+        """Opt out of the module's default of never holding a BF16 matrix: keep the decoded weight
+        in device memory (``2 * out * in`` bytes more) so that later calls skip the weight decode.
+        A member of a ``SharedProjectionGroup`` converts the group's stacked weight.  Returns the
+        bytes added."""
+        if self._group is not None:
+            return 0 if self._group.stacked.decoded is not None else self._group.keep_decoded_weight()
+        prepared = self._prepared if device is None else self._prepared_for(torch.device(device))
+        if prepared is None:
+            raise ValueError("no prepared weight yet: pass the target device")
+        if prepared.decoded is not None:
+            return 0
+        self._prepared = keep_decoded_weight(prepared)
+        return self._prepared.decoded.numel() * 2
+
     def clear_prepared(self) -> None:
         if self.reader is not None or self._record is not None:
             self._prepared = None
@@ -313,6 +335,17 @@ class FusedNQRTLinear(nn.Module):
                    else self._group.project(packed, self._group_index))
         self.w4a4_cuda_mma_dispatch_count += 1
         return outputs.to(self.output_dtype or original_dtype)
+
+
+def keep_decoded_weights_(model: nn.Module, device: torch.device | str | None = None) -> int:
+    """Switch every ``FusedNQRTLinear`` of ``model`` to resident decoded weights; returns the bytes added.
+
+    An explicit trade for machines with HBM to spare: 4x the packed weight bytes stay resident and
+    no projection regenerates dither or searches E8 for its weight again.  The reference has no
+    such mode (its modules never hold a BF16 matrix).
+    """
+    return sum(module.keep_decoded_weight(device) for module in model.modules()
+               if isinstance(module, FusedNQRTLinear))
 
 
 def convert_linears_to_fused_nqrt_(model: nn.Module, reader: Any, names: Iterable[str], *,

@@ -7,7 +7,7 @@ from .w4a4 import (  # noqa: F401
     linear_packed_w4a4, linear_packed_w4a4_fp32, linear_packed_w4a4_gemv_m1,
     linear_packed_w4a4_gemv_m1_fp32_probe, linear_packed_w4a4_mma_small_m, linear_packed_w4a4_mma_m16,
     linear_packed_w4a4_mma_large_m_staged, linear_packed_w4a4_mma_chunked_staged,
-    decode_packed_a4, decode_packed_a4_m16, decode_packed_weight, workspace_for, read_status, gemm_bf16_tc, launch_count,
+    decode_packed_a4, decode_packed_a4_m16, decode_packed_weight, keep_decoded_weight, workspace_for, read_status, gemm_bf16_tc, launch_count,
 )
 from .kv import (  # noqa: F401,E402
     NQKVPagePool, NQKVHotColdCache, PreparedNQKVPage, quantize_nqkv_page_cuda,

@@ -14,6 +14,7 @@ dispatch and no CPU fallback.
 from __future__ import annotations
 
 import ctypes
+import dataclasses
 import math
 from dataclasses import dataclass
 from typing import Any, Sequence
@@ -118,6 +119,9 @@ class PreparedNQRTLinear:
     # A weight that stacks the rows of several tensors sharing one input (q/k/v, gate/up):
     # (first_row, block_offset, dither_seed) per tensor, see ``group_prepared_linears``.
     segments: tuple[tuple[int, int, int], ...] | None = None
+    # Opt-in: the BF16 ``[rows, K]`` reconstruction kept in device memory (``keep_decoded_weight``).
+    # With it the projection skips the per-call weight decode and reads 4x the packed bytes instead.
+    decoded: torch.Tensor | None = None
 
     @property
     def rows(self) -> int:
@@ -339,10 +343,20 @@ def _run(activation: PreparedNQA4Activation, weight: PreparedNQRTLinear, out_dty
     m, k, n = activation.token_count, activation.feature_count, weight.rows
     device = activation.code_payload.device
     library = _lib.lib()
+    decoded = activation.decoded if use_decoded else None
+    if weight.decoded is not None:
+        nbytes = library.nq_w4a4_resident_workspace_bytes(_I64(m), _I64(n), _I64(k))
+        workspace = workspace_for(device, nbytes)
+        out = torch.empty((m, n), dtype=out_dtype, device=device)
+        status = library.nq_w4a4_gemm_resident(
+            _ptr(activation.code_payload), _ptr(activation.beta_payload), _ptr(activation.row_norms),
+            _ptr(activation.beta_table), _ptr(decoded), _ptr(weight.decoded), _I64(m), _I64(n), _I64(k),
+            _ptr(out), _DTYPE_TAG[out_dtype], _ptr(workspace), ctypes.c_size_t(workspace.numel()), _stream(device))
+        _lib.check(status, "linear_packed_w4a4(resident)")
+        return out
     nbytes = library.nq_w4a4_workspace_bytes(_I64(m), _I64(n), _I64(k))
     workspace = workspace_for(device, nbytes)
     out = torch.empty((m, n), dtype=out_dtype, device=device)
-    decoded = activation.decoded if use_decoded else None
     if weight.segments:
         count = len(weight.segments)
         table = lambda column: (ctypes.c_int64 * count)(*[int(entry[column]) for entry in weight.segments])  # noqa: E731
@@ -497,19 +511,54 @@ def decode_packed_a4(activation: PreparedNQA4Activation, *, dtype: torch.dtype |
 decode_packed_a4_m16 = decode_packed_a4
 
 
-def decode_packed_weight(weight: PreparedNQRTLinear) -> torch.Tensor:
-    """BF16 ``[N, K]`` reconstruction of a packed weight (dither regenerated)."""
+def decode_packed_weight(weight: PreparedNQRTLinear, *, out: torch.Tensor | None = None) -> torch.Tensor:
+    """BF16 ``[N, K]`` reconstruction of a packed weight (dither regenerated); ``out`` may receive it."""
     if not isinstance(weight, PreparedNQRTLinear):
         raise TypeError("weight must be PreparedNQRTLinear")
+    if weight.segments:
+        raise ValueError("decode the members of a stacked weight one by one")
     record = weight.record
     n, k = weight.rows, int(record.feature_count)
     device = weight.code_payload.device
-    out = torch.empty((n, k), dtype=torch.bfloat16, device=device)
+    if out is None:
+        out = torch.empty((n, k), dtype=torch.bfloat16, device=device)
+    elif (out.dtype != torch.bfloat16 or tuple(out.shape) != (n, k) or not out.is_contiguous()
+          or out.device != device):
+        raise ValueError("out must be a contiguous bfloat16 [N, K] tensor on the weight's device")
     status = _lib.lib().nq_w4_decode(
         _ptr(weight.code_payload), _ptr(weight.beta_payload), _ptr(weight.row_norms), _ptr(weight.beta_table),
         _I64(n), _I64(k), _I64(int(weight.block_offset)), _I64(int(record.dither_seed)), _ptr(out), _stream(device))
     _lib.check(status, "decode_packed_weight")
     return out
+
+
+def keep_decoded_weight(weight: PreparedNQRTLinear,
+                        members: Sequence[PreparedNQRTLinear] | None = None) -> PreparedNQRTLinear:
+    """Return ``weight`` with its BF16 reconstruction kept in device memory (opt-in).
+
+    The packed streams stay as they are (they remain the record of truth); the decoded matrix
+    costs ``2 * N * K`` bytes more and lets every later projection skip the weight decode: the
+    small-token GEMV becomes a stream over BF16 bound by HBM, the tensor-core path loses its
+    decode launch.  The values are those the packed kernels regenerate per call, so results
+    agree with the packed path up to the order of the FP32 sums.  For a stacked weight pass the
+    member views of ``group_prepared_linears`` as ``members``.
+    """
+    if not isinstance(weight, PreparedNQRTLinear):
+        raise TypeError("weight must be PreparedNQRTLinear")
+    if weight.decoded is not None:
+        return weight
+    k = int(weight.record.feature_count)
+    if weight.segments:
+        if members is None or sum(member.rows for member in members) != weight.rows:
+            raise ValueError("a stacked weight needs its member views to be decoded")
+        decoded = torch.empty((weight.rows, k), dtype=torch.bfloat16, device=weight.code_payload.device)
+        row = 0
+        for member in members:
+            decode_packed_weight(member, out=decoded[row:row + member.rows])
+            row += member.rows
+    else:
+        decoded = decode_packed_weight(weight)
+    return dataclasses.replace(weight, decoded=decoded)
 
 
 def gemm_bf16_tc(a_dec: torch.Tensor, w_dec: torch.Tensor, *, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:

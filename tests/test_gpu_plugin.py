@@ -182,3 +182,36 @@ def test_stacked_projection_group_equals_the_members_own_projections(oracle):
         assert sum(member.packed_device_bytes for member in members) == \
             sum(t.numel() * t.element_size() for t in (group.stacked.code_payload, group.stacked.beta_payload,
                                                        group.stacked.row_norms)) + 3 * 16
+
+
+def test_keep_decoded_weights_switches_modules_and_groups(oracle):
+    """keep_decoded_weights_ turns every packed module (stand-alone or member of a stacked group) into the resident mode."""
+    from torch import nn
+
+    from nestquant_aiinfra_b200.fused_linear import (FusedNQRTLinear, SharedPackedActivationCache,
+                                                     SharedProjectionGroup, keep_decoded_weights_)
+    from nestquant_aiinfra_b200.runtime import quantize_weight_cuda
+
+    k, sizes = 512, (256, 128)
+    weights = [quantize_weight_cuda((0.02 * torch.randn(n, k, generator=rng(900 + n))).cuda(), betas=W_BETAS_LOCAL,
+                                    dither_seed=2000 + n) for n in sizes]
+    solo_weight = quantize_weight_cuda((0.02 * torch.randn(128, k, generator=rng(950))).cuda(), betas=W_BETAS_LOCAL,
+                                       dither_seed=77)
+    cache = SharedPackedActivationCache(len(sizes))
+    members = [FusedNQRTLinear(w, activation_betas=ACT_BETAS, packed_activation_cache=cache) for w in weights]
+    SharedProjectionGroup(members)
+    solo = FusedNQRTLinear(solo_weight, activation_betas=ACT_BETAS)
+    model = nn.ModuleList([*members, solo])
+    for m in (1, 3, 40):
+        x = torch.randn(m, k, generator=rng(960 + m)).bfloat16().cuda()
+        with torch.no_grad():
+            before = [module(x) for module in model]
+    added = keep_decoded_weights_(model)
+    assert added == 2 * k * (sum(sizes) + 128)
+    assert keep_decoded_weights_(model) == 0
+    assert members[0]._group.stacked.decoded is not None and solo._prepared.decoded is not None
+    with torch.no_grad():
+        after = [module(x) for module in model]
+    for a, b in zip(before, after):
+        assert a.shape == b.shape
+        assert rel_fro(b.float().cpu().numpy(), a.float().cpu().numpy()) < 2e-3  # bf16 outputs, other summation order

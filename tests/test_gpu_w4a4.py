@@ -212,3 +212,58 @@ def test_regime_entry_points_and_errors(rt, oracle):
         rt.linear_packed_w4a4(bad, weight)
     with pytest.raises(ValueError):
         rt.quantize_activation_cuda(torch.randn(1, 40).cuda(), q=14, betas=ACT_BETAS)
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 2048, 2048), (2, 512, 2048), (3, 256, 8192), (4, 96, 4096), (5, 256, 2048),
+                                   (7, 96, 4096), (9, 512, 2048), (64, 2048, 2048), (300, 512, 2048)])
+def test_resident_decoded_weight_projection(rt, oracle, m, n, k):
+    """Opt-in mode: the decoded BF16 weight stays in device memory; same operands, so the same parity gate."""
+    record, w_deq = make_weight_record(oracle, n, k, seed=1500 + n + k, dither_seed=321 + n)
+    packed = rt.prepare_fused_linear(record)
+    weight = rt.keep_decoded_weight(packed)
+    assert weight.decoded is not None and tuple(weight.decoded.shape) == (n, k)
+    assert torch.equal(weight.decoded.cpu(), torch.from_numpy(w_deq).bfloat16())
+    assert rt.keep_decoded_weight(weight) is weight
+    x = torch.randn(m, k, generator=rng(2500 + m)).bfloat16()
+    act = rt.quantize_activation_cuda(x.cuda(), q=14, betas=ACT_BETAS)
+    ac, ab, an = oracle.encode_packed(x.float().numpy(), ACT_BETAS)
+    a_deq = oracle.dequantize_rows(ac, ab, an, ACT_BETAS, m, k)
+    expected = oracle.gemm_bf16_operands(a_deq, w_deq)
+    actual = rt.linear_packed_w4a4_fp32(act, weight).cpu().numpy()
+    assert actual.shape == (m, n) and rt.read_status() == 0
+    assert max_abs(actual, expected) <= MAX_ABS_TOL, (max_abs(actual, expected), rel_fro(actual, expected))
+    assert rel_fro(actual, expected) <= REL_FRO_TOL, rel_fro(actual, expected)
+    # deterministic, and the packed path (which regenerates the same operands) agrees to summation order
+    assert np.array_equal(rt.linear_packed_w4a4_fp32(act, weight).cpu().numpy(), actual)
+    per_call = rt.linear_packed_w4a4_fp32(act, packed).cpu().numpy()
+    assert rel_fro(actual, per_call) <= 1e-5
+    # the kernel can decode the packed activation itself
+    from dataclasses import replace
+    again = rt.linear_packed_w4a4_fp32(replace(act, decoded=None), weight).cpu().numpy()
+    assert np.array_equal(again, actual)
+    out = rt.linear_packed_w4a4(act, weight)
+    assert out.dtype == torch.bfloat16 and torch.equal(out.cpu(), torch.from_numpy(actual).bfloat16())
+
+
+def test_resident_decoded_weight_argument_errors(rt, oracle):
+    import ctypes
+
+    from nestquant_aiinfra_b200 import _lib
+
+    library = _lib.lib()
+    assert library.nq_w4a4_resident_workspace_bytes(ctypes.c_int64(0), ctypes.c_int64(64), ctypes.c_int64(256)) == 0
+    buf = torch.zeros(1 << 20, dtype=torch.uint8, device="cuda")
+    null = ctypes.c_void_p(0)
+    args = [null, null, null, null, ctypes.c_void_p(buf.data_ptr()), null, ctypes.c_int64(1), ctypes.c_int64(64),
+            ctypes.c_int64(256), ctypes.c_void_p(buf.data_ptr()), ctypes.c_int(0), ctypes.c_void_p(buf.data_ptr()),
+            ctypes.c_size_t(buf.numel()), null]
+    assert library.nq_w4a4_gemm_resident(*args) < 0      # no decoded weight
+    args[5] = ctypes.c_void_p(buf.data_ptr())
+    args[8] = ctypes.c_int64(250)
+    assert library.nq_w4a4_gemm_resident(*args) < 0      # k not a multiple of 32
+    args[8] = ctypes.c_int64(256)
+    args[12] = ctypes.c_size_t(16)
+    assert library.nq_w4a4_gemm_resident(*args) < 0      # workspace too small
+    record, _ = make_weight_record(oracle, 64, 256, seed=3, dither_seed=4)
+    with pytest.raises(TypeError):
+        rt.keep_decoded_weight(record)
