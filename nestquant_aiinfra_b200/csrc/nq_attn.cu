@@ -80,8 +80,10 @@ __device__ __forceinline__ bool resolve_query(const AttnParams& p, int qi, int& 
     return active && limit > 0;
 }
 
+// Register budget: the exact E8 decode leaves issue slots idle at 12 warps per SM (168 registers), so the
+// kernel is built for 4 resident CTAs (128 registers; a few spilled words cost less than the lost warps).
 template <int G, int BPR>
-__global__ void __launch_bounds__(kAttnThreads) nq_attn_paged_kernel(const AttnParams p) {
+__global__ void __launch_bounds__(kAttnThreads, (G <= 4 ? 4 : 3)) nq_attn_paged_kernel(const AttnParams p) {
     constexpr int TPW = 32 / BPR;  // tokens per warp step
     constexpr int D = BPR * 8;
     __shared__ float s_merge[kAttnWarps][G][D + 2];
@@ -290,13 +292,31 @@ int launch_attn(const AttnParams& p, dim3 grid, cudaStream_t s) {
     return NQ_OK;
 }
 
-int choose_splits(int queries, int kv_heads, int max_pages) {
-    const int ctas = queries * kv_heads;
-    int splits = (4 * 148 + ctas - 1) / ctas;       // aim at >= 4 CTAs per SM
-    const int cap = (max_pages + 1 + 7) / 8;        // at least ~8 page slots per split
-    if (splits > cap) splits = cap;
-    if (splits > 64) splits = 64;
-    return splits < 1 ? 1 : splits;
+// Page-range splits per (query token, KV head).  The grid should fill whole waves of the CTAs that are
+// resident at once (148 SMs x 4, or x 3 for the widest GQA group): 256 CTAs x 3 splits used to run as 1.3
+// waves, i.e. the time of 2.  Among the split counts that leave every split >= 4 page slots and the grid
+// within 8 waves, take the smallest whose last wave is (nearly) full.
+int choose_splits(int queries, int kv_heads, int max_pages, int group) {
+    const long ctas = (long)queries * kv_heads;
+    const long resident = 148L * (group <= 4 ? 4 : 3);
+    int cap = (max_pages + 1 + 3) / 4;
+    if (cap > 64) cap = 64;
+    if (cap < 1) cap = 1;
+    double best = 0.0;
+    double score[65];
+    for (int s = 1; s <= cap; ++s) {
+        const long total = ctas * s;
+        if (s > 1 && total > 8 * resident) {
+            cap = s - 1;
+            break;
+        }
+        const long waves = (total + resident - 1) / resident;
+        score[s] = (double)total / (double)(waves * resident);
+        if (score[s] > best) best = score[s];
+    }
+    for (int s = 1; s <= cap; ++s)
+        if (score[s] >= best - 0.02) return s;
+    return 1;
 }
 
 }  // namespace
@@ -304,7 +324,7 @@ int choose_splits(int queries, int kv_heads, int max_pages) {
 extern "C" size_t nq_kv_attention_workspace_bytes(int batch, int q_tokens, int q_heads, int kv_heads, int dim,
                                                   int max_pages) {
     if (batch < 1 || q_tokens < 1 || q_heads < 1 || kv_heads < 1) return 0;
-    const int splits = choose_splits(batch * q_tokens, kv_heads, max_pages);
+    const int splits = choose_splits(batch * q_tokens, kv_heads, max_pages, q_heads / kv_heads);
     return (size_t)batch * q_tokens * q_heads * splits * (dim + 2) * sizeof(float) + 256;
 }
 
@@ -349,7 +369,7 @@ extern "C" int nq_kv_attention(const void* query, int q_dtype, int batch, int q_
     p.scale_log2e = scale * 1.4426950408889634f;
     p.sqrt_dim = (float)sqrt((double)dim);
     p.inv_sqrt_dim = 1.0f / p.sqrt_dim;
-    p.splits = choose_splits(batch * q_tokens, kv_heads, max_pages);
+    p.splits = choose_splits(batch * q_tokens, kv_heads, max_pages, group);
     p.out = out; p.out_dtype = out_dtype;
     p.partial = reinterpret_cast<float*>(workspace);
     if (p.splits > 1) {
