@@ -160,8 +160,8 @@ __global__ void __launch_bounds__(kAttnThreads, (G <= 4 ? 4 : 3)) nq_attn_paged_
                     const float vb = __ldg(p.value_beta_table + nq_beta_id(p.value_betas + page_id * beta_bytes, g));
                     const float kds = nq_div_by(__ldg(p.key_norms + (int64_t)page_id * rows + row), p.sqrt_dim, p.inv_sqrt_dim);
                     const float vds = nq_div_by(__ldg(p.value_norms + (int64_t)page_id * rows + row), p.sqrt_dim, p.inv_sqrt_dim);
-                    nq_decode_codeword_exact(kw, nullptr, kvec);
-                    nq_decode_codeword_exact(vw, nullptr, vvec);
+                    nq_decode_codeword_undithered(kw, kvec);
+                    nq_decode_codeword_undithered(vw, vvec);
                     kscale = kb * kds;
                     vscale = vb * vds;
                 }

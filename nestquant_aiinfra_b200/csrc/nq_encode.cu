@@ -62,7 +62,7 @@ nq_a4_decode_kernel(const uint32_t* __restrict__ codes, const uint8_t* __restric
     if (g >= blocks) return;
     const int64_t row = g / bpr;
     float r[8];
-    nq_decode_codeword_exact(__ldg(codes + g), nullptr, r);
+    nq_decode_codeword_undithered(__ldg(codes + g), r);
     const float beta = __ldg(beta_table + nq_beta_id(beta_ids, g));
     const float ds = nq_div(__ldg(norms + row), sqrt_k);
 #pragma unroll

@@ -104,4 +104,41 @@ void shim_encode_blocks_queued(const float* xs, long n, const float* beta, uint3
 void shim_cell_class(const float* lam, long n, int* out) {
     for (long i = 0; i < n; ++i) out[i] = nq_e8_cell_class(lam + 8 * i);
 }
+
+// Lean undithered decode against the exact one: every `stride`-th of the 14^8 codewords
+// (offset varied with the high digits so that no digit pattern is left out); also decodes a
+// caller-given list.  Returns the number of codewords whose eight values differ in any bit.
+long shim_undithered_mismatches(long stride) {
+    long bad = 0;
+    const long half = 14L * 14 * 14 * 14;
+    for (long hi = 0; hi < half; ++hi) {
+        int c[8];
+        long v = hi;
+        for (int j = 4; j < 8; ++j) { c[j] = (int)(v % 14); v /= 14; }
+        for (long lo = hi % stride; lo < half; lo += stride) {
+            long u = lo;
+            for (int j = 0; j < 4; ++j) { c[j] = (int)(u % 14); u /= 14; }
+            uint32_t w = 0;
+            for (int j = 0; j < 8; ++j) w |= (uint32_t)c[j] << (4 * j);
+            float a[8], b[8];
+            nq_decode_codeword_exact(w, nullptr, a);
+            nq_decode_codeword_undithered(w, b);
+            if (memcmp(a, b, sizeof a)) ++bad;
+        }
+    }
+    return bad;
+}
+
+void shim_decode_undithered(const uint32_t* words, long n, float* out) {
+    for (long i = 0; i < n; ++i) nq_decode_codeword_undithered(words[i], out + 8 * i);
+}
+
+// 1 when the short division equals IEEE division for every half-integer coset coordinate.
+int shim_div14_exact(void) {
+    for (int twice = -80; twice <= 160; ++twice) {
+        const float t = 0.5f * (float)twice;
+        if (nq_div14_coset(t) != t / 14.0f) return 0;
+    }
+    return 1;
+}
 }
