@@ -262,13 +262,38 @@ NQ_HD void nq_generator_apply(const int c[8], float t[8]) {
     t[7] = h;
 }
 
-// Same from a packed codeword (coordinate j in bits [4j, 4j+3]).
-NQ_HD void nq_codeword_coset(uint32_t word, float t[8]) {
-    int c[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) c[j] = (int)((word >> (4 * j)) & 15u);
-    nq_generator_apply(c, t);
+// Coset representative G*c of a packed codeword with few integer instructions: the nibbles are
+// split into even / odd bytes, the differences c_j - c_{j+1} are formed four at a time in one
+// 32-bit subtraction (every byte biased by 16, so no borrow crosses a byte), and each byte is
+// dropped into the mantissa of 1.5 * 2^23 to become a float without a conversion instruction.
+NQ_HD float nq_mantissa_byte(uint32_t bytes, int index) {
+#if defined(__CUDA_ARCH__)
+    return __uint_as_float(__byte_perm(bytes, 0x4B400000u, 0x7650u | (uint32_t)index));
+#else
+    return nq_bits_float(0x4B400000u | ((bytes >> (8 * index)) & 0xffu));
+#endif
 }
+NQ_HD void nq_codeword_coset_packed(uint32_t word, float t[8]) {
+    const uint32_t even = word & 0x0F0F0F0Fu;          // c0 c2 c4 c6
+    const uint32_t odd = (word >> 4) & 0x0F0F0F0Fu;    // c1 c3 c5 c7
+    const uint32_t odd3 = odd & 0x00FFFFFFu;           // c1 c3 c5 0
+    const uint32_t a = even + 0x10101010u - odd3;      // c0-c1, c2-c3, c4-c5, c6      (+16 each)
+    const uint32_t b = odd3 + 0x00101010u - (even >> 8);  // c1-c2, c3-c4, c5-c6, 0    (+16 each)
+    const float bias = NQ_MAGIC + 16.0f;
+    const float h = 0.5f * nq_sub(nq_mantissa_byte(odd, 3), NQ_MAGIC);
+    const float c0 = nq_sub(nq_mantissa_byte(even, 0), NQ_MAGIC);
+    t[0] = nq_add(nq_add(nq_sub(nq_mantissa_byte(a, 0), bias), c0), h);
+    t[1] = nq_add(nq_sub(nq_mantissa_byte(b, 0), bias), h);
+    t[2] = nq_add(nq_sub(nq_mantissa_byte(a, 1), bias), h);
+    t[3] = nq_add(nq_sub(nq_mantissa_byte(b, 1), bias), h);
+    t[4] = nq_add(nq_sub(nq_mantissa_byte(a, 2), bias), h);
+    t[5] = nq_add(nq_sub(nq_mantissa_byte(b, 2), bias), h);
+    t[6] = nq_add(nq_sub(nq_mantissa_byte(a, 3), bias), h);
+    t[7] = h;
+}
+
+// Same from a packed codeword (coordinate j in bits [4j, 4j+3]).
+NQ_HD void nq_codeword_coset(uint32_t word, float t[8]) { nq_codeword_coset_packed(word, t); }
 
 // Integer coordinates of a lattice point, reduced modulo q, as a codeword.
 // All intermediate values are exact small integers in float32.
@@ -317,36 +342,6 @@ NQ_HD void nq_decode_codeword_exact(uint32_t word, const float* dither, float r[
 NQ_HD float nq_div14_coset(float t) {
     const float q0 = nq_mul(t, NQ_RCP14);
     return nq_fma(nq_fma(-14.0f, q0, t), NQ_RCP14, q0);
-}
-
-// Coset representative G*c of a packed codeword with few integer instructions: the nibbles are
-// split into even / odd bytes, the differences c_j - c_{j+1} are formed four at a time in one
-// 32-bit subtraction (every byte biased by 16, so no borrow crosses a byte), and each byte is
-// dropped into the mantissa of 1.5 * 2^23 to become a float without a conversion instruction.
-NQ_HD float nq_mantissa_byte(uint32_t bytes, int index) {
-#if defined(__CUDA_ARCH__)
-    return __uint_as_float(__byte_perm(bytes, 0x4B400000u, 0x7650u | (uint32_t)index));
-#else
-    return nq_bits_float(0x4B400000u | ((bytes >> (8 * index)) & 0xffu));
-#endif
-}
-NQ_HD void nq_codeword_coset_packed(uint32_t word, float t[8]) {
-    const uint32_t even = word & 0x0F0F0F0Fu;          // c0 c2 c4 c6
-    const uint32_t odd = (word >> 4) & 0x0F0F0F0Fu;    // c1 c3 c5 c7
-    const uint32_t odd3 = odd & 0x00FFFFFFu;           // c1 c3 c5 0
-    const uint32_t a = even + 0x10101010u - odd3;      // c0-c1, c2-c3, c4-c5, c6      (+16 each)
-    const uint32_t b = odd3 + 0x00101010u - (even >> 8);  // c1-c2, c3-c4, c5-c6, 0    (+16 each)
-    const float bias = NQ_MAGIC + 16.0f;
-    const float h = 0.5f * nq_sub(nq_mantissa_byte(odd, 3), NQ_MAGIC);
-    const float c0 = nq_sub(nq_mantissa_byte(even, 0), NQ_MAGIC);
-    t[0] = nq_add(nq_add(nq_sub(nq_mantissa_byte(a, 0), bias), c0), h);
-    t[1] = nq_add(nq_sub(nq_mantissa_byte(b, 0), bias), h);
-    t[2] = nq_add(nq_sub(nq_mantissa_byte(a, 1), bias), h);
-    t[3] = nq_add(nq_sub(nq_mantissa_byte(b, 1), bias), h);
-    t[4] = nq_add(nq_sub(nq_mantissa_byte(a, 2), bias), h);
-    t[5] = nq_add(nq_sub(nq_mantissa_byte(b, 2), bias), h);
-    t[6] = nq_add(nq_sub(nq_mantissa_byte(a, 3), bias), h);
-    t[7] = h;
 }
 
 // Minimum-energy representative of an UNDITHERED codeword (activations, K/V pages): the same

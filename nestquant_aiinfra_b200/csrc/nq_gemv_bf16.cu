@@ -1,11 +1,14 @@
 // Small-token projection on a weight that is kept DECODED in HBM (BF16 [n, k],
-// the output of nq_w4_decode): a streaming GEMV.  One warp owns one output
-// channel; every lane issues up to eight 16-byte weight loads before it uses
-// the first, so a row of 2048 features is in flight as one burst of 4 KB per
-// warp.  The weights are read once with a streaming hint; the few activation
-// rows are re-read by every warp and stay in L1.  FP32 accumulation per lane
-// in feature order, then a shuffle tree: the result does not depend on
-// scheduling.
+// the output of nq_w4_decode): a streaming GEMV.  A warp owns one output
+// channel, or one of up to eight K ranges of it when the row is longer than
+// one burst; every lane issues up to eight 16-byte weight loads before it uses
+// the first, so 2048 features are in flight as one burst of 4 KB per warp and
+// a long row (8192, 28672 features) is spread over the warps of the CTA instead
+// of being walked burst after burst by one.  The K ranges of a row are added
+// in range order by one thread.  The weights are read once with a streaming
+// hint; the few activation rows are re-read by every warp and stay in L1.
+// FP32 accumulation per lane in feature order, then a shuffle tree: the result
+// does not depend on scheduling.
 //
 // This is the opt-in "resident decoded weights" mode: the operands are the very
 // BF16 values the packed kernels regenerate on every call (eight dither hashes
@@ -32,36 +35,43 @@ __device__ __forceinline__ uint4 nq_ld_stream(const uint4* p) {
 template <int MT>
 __global__ void __launch_bounds__(kGemvThreads) nq_bf16_gemv_kernel(const uint4* __restrict__ w,
                                                                     const uint4* __restrict__ a, int m, int n,
-                                                                    int bpr, void* out, int out_bf16) {
-    const int lane = threadIdx.x & 31;
-    const int row = blockIdx.x * kGemvWarps + (threadIdx.x >> 5);
-    if (row >= n) return;
-    const uint4* wr = w + (int64_t)row * bpr;
+                                                                    int bpr, int ksplit, int chunk, void* out,
+                                                                    int out_bf16) {
+    __shared__ float s_part[kGemvWarps][MT];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int rows_per_cta = kGemvWarps / ksplit;
+    const int part = warp % ksplit;
+    const int row = blockIdx.x * rows_per_cta + warp / ksplit;
+    const bool live = row < n;
+    const int b_begin = part * chunk, b_end = min(bpr, b_begin + chunk);
 
     float acc[MT];
 #pragma unroll
     for (int i = 0; i < MT; ++i) acc[i] = 0.0f;
 
-    for (int b0 = lane; b0 < bpr; b0 += 32 * kUnroll) {
-        uint4 wv[kUnroll];
+    if (live) {
+        const uint4* wr = w + (int64_t)row * bpr;
+        for (int b0 = b_begin + lane; b0 < b_end; b0 += 32 * kUnroll) {
+            uint4 wv[kUnroll];
 #pragma unroll
-        for (int u = 0; u < kUnroll; ++u) {
-            const int b = b0 + 32 * u;
-            wv[u] = b < bpr ? nq_ld_stream(wr + b) : make_uint4(0, 0, 0, 0);
-        }
+            for (int u = 0; u < kUnroll; ++u) {
+                const int b = b0 + 32 * u;
+                wv[u] = b < b_end ? nq_ld_stream(wr + b) : make_uint4(0, 0, 0, 0);
+            }
 #pragma unroll
-        for (int u = 0; u < kUnroll; ++u) {
-            const int b = b0 + 32 * u;
-            if (b >= bpr) break;
-            float wf[8];
-            nq_unpack_bf16x8(wv[u], wf);
+            for (int u = 0; u < kUnroll; ++u) {
+                const int b = b0 + 32 * u;
+                if (b >= b_end) break;
+                float wf[8];
+                nq_unpack_bf16x8(wv[u], wf);
 #pragma unroll
-            for (int i = 0; i < MT; ++i) {
-                if (i < m) {
-                    float af[8];
-                    nq_unpack_bf16x8(__ldg(a + (int64_t)i * bpr + b), af);
+                for (int i = 0; i < MT; ++i) {
+                    if (i < m) {
+                        float af[8];
+                        nq_unpack_bf16x8(__ldg(a + (int64_t)i * bpr + b), af);
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) acc[i] = fmaf(af[j], wf[j], acc[i]);
+                        for (int j = 0; j < 8; ++j) acc[i] = fmaf(af[j], wf[j], acc[i]);
+                    }
                 }
             }
         }
@@ -72,7 +82,21 @@ __global__ void __launch_bounds__(kGemvThreads) nq_bf16_gemv_kernel(const uint4*
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], off);
     }
-    if (lane == 0) {
+    if (ksplit > 1) {
+        if (lane == 0) {
+#pragma unroll
+            for (int i = 0; i < MT; ++i) s_part[warp][i] = acc[i];
+        }
+        __syncthreads();
+        if (part != 0) return;
+#pragma unroll
+        for (int i = 0; i < MT; ++i) {
+            float total = 0.0f;
+            for (int q = 0; q < ksplit; ++q) total += s_part[warp + q][i];
+            acc[i] = total;
+        }
+    }
+    if (lane == 0 && live) {
 #pragma unroll
         for (int i = 0; i < MT; ++i) {
             if (i < m) {
@@ -95,11 +119,19 @@ int nq_launch_bf16_gemv(const void* a_dec, const void* w_dec, int64_t m, int64_t
     const uint4* w = reinterpret_cast<const uint4*>(w_dec);
     const uint4* a = reinterpret_cast<const uint4*>(a_dec);
     const int bpr = (int)(k / 8);
-    const unsigned grid = (unsigned)((n + kGemvWarps - 1) / kGemvWarps);
+    // one burst = 32 lanes x 8 loads = 256 blocks; longer rows are shared by 2, 4 or 8 warps
+    int ksplit = 1;
+    while (ksplit < kGemvWarps && bpr > 256 * ksplit) ksplit *= 2;
+    const int chunk = ((bpr + ksplit - 1) / ksplit + 31) / 32 * 32;
+    const int rows_per_cta = kGemvWarps / ksplit;
+    const unsigned grid = (unsigned)((n + rows_per_cta - 1) / rows_per_cta);
     const int out_bf16 = out_dtype == NQ_BF16;
-    if (m == 1) nq_bf16_gemv_kernel<1><<<grid, kGemvThreads, 0, stream>>>(w, a, (int)m, (int)n, bpr, out, out_bf16);
-    else if (m == 2) nq_bf16_gemv_kernel<2><<<grid, kGemvThreads, 0, stream>>>(w, a, (int)m, (int)n, bpr, out, out_bf16);
-    else nq_bf16_gemv_kernel<4><<<grid, kGemvThreads, 0, stream>>>(w, a, (int)m, (int)n, bpr, out, out_bf16);
+    if (m == 1)
+        nq_bf16_gemv_kernel<1><<<grid, kGemvThreads, 0, stream>>>(w, a, (int)m, (int)n, bpr, ksplit, chunk, out, out_bf16);
+    else if (m == 2)
+        nq_bf16_gemv_kernel<2><<<grid, kGemvThreads, 0, stream>>>(w, a, (int)m, (int)n, bpr, ksplit, chunk, out, out_bf16);
+    else
+        nq_bf16_gemv_kernel<4><<<grid, kGemvThreads, 0, stream>>>(w, a, (int)m, (int)n, bpr, ksplit, chunk, out, out_bf16);
     NQ_CHECK_LAUNCH("nq_w4a4_gemm_resident(gemv)");
     return NQ_OK;
 }

@@ -120,10 +120,12 @@ long shim_undithered_mismatches(long stride) {
             for (int j = 0; j < 4; ++j) { c[j] = (int)(u % 14); u /= 14; }
             uint32_t w = 0;
             for (int j = 0; j < 8; ++j) w |= (uint32_t)c[j] << (4 * j);
-            float a[8], b[8];
+            float a[8], b[8], ta[8], tb[8];
             nq_decode_codeword_exact(w, nullptr, a);
             nq_decode_codeword_undithered(w, b);
-            if (memcmp(a, b, sizeof a)) ++bad;
+            nq_generator_apply(c, ta);          // the generator matrix applied coordinate by coordinate
+            nq_codeword_coset_packed(w, tb);    // the byte-parallel build the kernels use
+            if (memcmp(a, b, sizeof a) || memcmp(ta, tb, sizeof ta)) ++bad;
         }
     }
     return bad;
