@@ -458,7 +458,7 @@ def run_e2e(torch, rt, FusedNQRTLinear, weights, device, steps: int, distributed
     return {"ms": e0.elapsed_time(e1) / steps, "h2d": h2d, "d2h": d2h}
 
 
-def gemv_workload(torch, rt, device, pk) -> dict:
+def gemv_workload(torch, rt, device, pk, only: str | None = None) -> dict:
     """M = 1 projection of the four shapes: packed weight (decode in the kernel) and resident decoded weight.
 
     Each timed graph cycles over enough copies of the weight to exceed the 126 MB L2, so every launch streams
@@ -469,6 +469,8 @@ def gemv_workload(torch, rt, device, pk) -> dict:
     weights, inputs, beta_table = gpu_setup(torch, rt, device)
     rows = []
     for (name, n, k), w in zip(SHAPES, weights):
+        if only and name != only:
+            continue
         act = rt.quantize_activation_cuda(inputs[(k, 1)], q=14, betas=ACT_BETAS, beta_table=beta_table)
         resident = rt.keep_decoded_weight(w)
         copies = max(2, (160 << 20) // (n * k * 2) + 1)
@@ -658,7 +660,7 @@ def run_tp70b(args) -> None:
     model, cache = build_llama_tp_shard(hidden_size=8192, intermediate_size=28672, num_layers=args.tp_layers,
                                         num_heads=64, num_kv_heads=8, head_dim=128, vocab_size=128256, rank=rank,
                                         world=world, capacity=args.tp_batch,
-                                        max_cache_len=args.tp_context + steps + max(args.warmup, 3) + 32, device=device)
+                                        max_cache_len=args.tp_context + 2 * (steps + max(args.warmup, 3)) + 32, device=device)
     fill_cache_synthetic(cache, args.tp_context)
     runner = TensorParallelRunner(model, cache)
     runner.start_decode(args.tp_context)
@@ -692,6 +694,33 @@ def run_tp70b(args) -> None:
         dist.all_reduce(same, op=dist.ReduceOp.MIN)
     else:
         same = torch.tensor([1])
+    resident = None
+    if args.tp_resident:
+        # opt-in mode: every rank keeps the decoded BF16 weights of its shard; same graph-decode loop again
+        from nestquant_aiinfra_b200.fused_linear import keep_decoded_weights_
+
+        if isinstance(runner.graph, torch.cuda.CUDAGraph):
+            runner.graph.reset()
+            runner.graph = None
+        added = keep_decoded_weights_(model)
+        if graph is True:
+            runner.capture_decode_graph()
+        for _ in range(max(args.warmup, 3)):
+            runner.decode()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+        r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        r0.record()
+        for _ in range(steps):
+            runner.decode()
+        r1.record()
+        torch.cuda.synchronize(device)
+        rms = torch.tensor([r0.elapsed_time(r1) / steps], device=device)
+        if world > 1:
+            dist.all_reduce(rms, op=dist.ReduceOp.MAX)
+        resident = {"note": "opt-in: decoded BF16 weights of the shard kept in HBM", "extra_weight_bytes_per_rank": int(added),
+                    "ms_per_step": float(rms.item()), "tok_s": args.tp_batch / (float(rms.item()) * 1e-3)}
     if rank == 0:
         ms_step = float(ms.item())
         from nestquant_aiinfra_b200.fused_linear import FusedNQRTLinear
@@ -707,6 +736,7 @@ def run_tp70b(args) -> None:
                        "kv": "pages pre-filled by the page encoder with synthetic K/V"},
             "packed_weight_bytes_per_rank": int(packed), "build_s": round(build_s, 1),
             "ranks_agree_on_tokens": bool(same.item()),
+            **({"resident_decoded_weights": resident} if resident else {}),
         }), flush=True)
     if world > 1:
         # A live CUDA graph that captured NCCL kernels keeps the communicator busy: release it before
@@ -736,7 +766,7 @@ def run_single_extra(args) -> None:
     if args.workload == "kv":
         result = kv_workload(torch, rt, device, peaks())
     elif args.workload == "gemv":
-        result = gemv_workload(torch, rt, device, peaks())
+        result = gemv_workload(torch, rt, device, peaks(), args.shape)
     else:
         result = decode_workload(torch, device, kernel_mix=args.kernel_mix)
     print(json.dumps({"workload": args.workload, **result}), flush=True)
@@ -754,6 +784,10 @@ def main() -> None:
     parser.add_argument("--tp-layers", type=int, default=80, help="decoder layers of the tp70b workload")
     parser.add_argument("--tp-batch", type=int, default=128)
     parser.add_argument("--tp-context", type=int, default=4096)
+    parser.add_argument("--shape", choices=[name for name, _, _ in SHAPES], default=None,
+                        help="with --workload gemv: only this projection shape (short profiling runs)")
+    parser.add_argument("--tp-resident", action="store_true",
+                        help="tp70b: also time the opt-in mode that keeps the decoded BF16 weights of the shard in HBM")
     parser.add_argument("--kernel-mix", action="store_true",
                         help="with --workload decode: add the device time per kernel of a decode step (torch.profiler)")
     parser.add_argument("--skip-extras", action="store_true",

@@ -142,29 +142,8 @@ __global__ void __launch_bounds__(kAttnThreads, (G <= 4 ? 4 : 3)) nq_attn_paged_
                     }
                 }
             }
-            for (int t0 = 0; t0 < tlimit; t0 += TPW) {
-                const int t = t0 + tsub;
-                const bool valid = t < tlimit && base_token + t < limit;
-                float kvec[8], vvec[8];
-                float kscale = 1.0f, vscale = 1.0f;  // beta * norm / sqrt(D) of the row, applied after the dot product
-                if (is_hot) {
-                    const int64_t off = (((int64_t)slot * p.page_size + min(t, p.page_size - 1)) * p.kv_heads + h) * D + blk * 8;
-                    nq_load8<__nv_bfloat16>(reinterpret_cast<const __nv_bfloat16*>(p.hot_keys) + off, kvec);
-                    nq_load8<__nv_bfloat16>(reinterpret_cast<const __nv_bfloat16*>(p.hot_values) + off, vvec);
-                } else {
-                    const int row = min(t, p.page_size - 1) * p.kv_heads + h;
-                    const int64_t g = (int64_t)row * BPR + blk;
-                    const uint32_t kw = __ldg(reinterpret_cast<const uint32_t*>(p.key_codes + page_id * code_bytes) + g);
-                    const uint32_t vw = __ldg(reinterpret_cast<const uint32_t*>(p.value_codes + page_id * code_bytes) + g);
-                    const float kb = __ldg(p.key_beta_table + nq_beta_id(p.key_betas + page_id * beta_bytes, g));
-                    const float vb = __ldg(p.value_beta_table + nq_beta_id(p.value_betas + page_id * beta_bytes, g));
-                    const float kds = nq_div_by(__ldg(p.key_norms + (int64_t)page_id * rows + row), p.sqrt_dim, p.inv_sqrt_dim);
-                    const float vds = nq_div_by(__ldg(p.value_norms + (int64_t)page_id * rows + row), p.sqrt_dim, p.inv_sqrt_dim);
-                    nq_decode_codeword_undithered(kw, kvec);
-                    nq_decode_codeword_undithered(vw, vvec);
-                    kscale = kb * kds;
-                    vscale = vb * vds;
-                }
+            // scores of one token against the G query heads and the running-softmax update (lane = one E8 block)
+            auto update = [&](const float kvec[8], const float vvec[8], float kscale, float vscale, bool valid) {
 #pragma unroll
                 for (int g = 0; g < G; ++g) {
                     float s = 0.0f;
@@ -190,6 +169,53 @@ __global__ void __launch_bounds__(kAttnThreads, (G <= 4 ? 4 : 3)) nq_attn_paged_
 #pragma unroll
                         for (int j = 0; j < 8; ++j) acc[g][j] = fmaf(pv, vvec[j], acc[g][j]);
                     }
+                }
+            };
+            if (is_hot) {
+                for (int t0 = 0; t0 < tlimit; t0 += TPW) {
+                    const int t = t0 + tsub;
+                    const bool valid = t < tlimit && base_token + t < limit;
+                    float kvec[8], vvec[8];
+                    const int64_t off = (((int64_t)slot * p.page_size + min(t, p.page_size - 1)) * p.kv_heads + h) * D + blk * 8;
+                    nq_load8<__nv_bfloat16>(reinterpret_cast<const __nv_bfloat16*>(p.hot_keys) + off, kvec);
+                    nq_load8<__nv_bfloat16>(reinterpret_cast<const __nv_bfloat16*>(p.hot_values) + off, vvec);
+                    update(kvec, vvec, 1.0f, 1.0f, valid);
+                }
+            } else {
+                // The packed operands of the NEXT token step are fetched before this step is decoded: the
+                // decode is a few hundred instructions long, enough to cover the loads' latency.
+                const uint32_t* kcodes = reinterpret_cast<const uint32_t*>(p.key_codes + page_id * code_bytes);
+                const uint32_t* vcodes = reinterpret_cast<const uint32_t*>(p.value_codes + page_id * code_bytes);
+                const uint8_t* kbetas = p.key_betas + page_id * beta_bytes;
+                const uint8_t* vbetas = p.value_betas + page_id * beta_bytes;
+                const float* knorms = p.key_norms + (int64_t)page_id * rows;
+                const float* vnorms = p.value_norms + (int64_t)page_id * rows;
+                uint32_t kw, vw;
+                int kid, vid;
+                float kn, vn;
+                auto fetch = [&](int t) {
+                    const int row = min(t, p.page_size - 1) * p.kv_heads + h;
+                    const int64_t g = (int64_t)row * BPR + blk;
+                    kw = __ldg(kcodes + g);
+                    vw = __ldg(vcodes + g);
+                    kid = nq_beta_id(kbetas, g);
+                    vid = nq_beta_id(vbetas, g);
+                    kn = __ldg(knorms + row);
+                    vn = __ldg(vnorms + row);
+                };
+                fetch(tsub);
+                for (int t0 = 0; t0 < tlimit; t0 += TPW) {
+                    const int t = t0 + tsub;
+                    const bool valid = t < tlimit && base_token + t < limit;
+                    const uint32_t kw_now = kw, vw_now = vw;
+                    const float kb = __ldg(p.key_beta_table + kid), vb = __ldg(p.value_beta_table + vid);
+                    const float kds = nq_div_by(kn, p.sqrt_dim, p.inv_sqrt_dim);
+                    const float vds = nq_div_by(vn, p.sqrt_dim, p.inv_sqrt_dim);
+                    if (t0 + TPW < tlimit) fetch(t + TPW);
+                    float kvec[8], vvec[8];
+                    nq_decode_codeword_undithered(kw_now, kvec);
+                    nq_decode_codeword_undithered(vw_now, vvec);
+                    update(kvec, vvec, kb * kds, vb * vds, valid);
                 }
             }
         }
