@@ -553,11 +553,25 @@ def kv_workload(torch, rt, device, pk) -> dict:
 
     t_pack = _time_graph(torch, pack_once, device)
     pack_bytes = batch * (2 * page * heads * dim * 2 + pack_pool.page_payload_bytes)
+    # opt-in decoded shadow of the pool: same attention call, coordinates read instead of searched
+    before = ws.output.clone()
+    shadow_bytes = pool.enable_lattice_shadow()
+    t_shadow = _time_graph(torch, lambda: rt._launch_nqkv_decode_attention_batched_k1(
+        q, cache, slot_ids=slot_ids, active_mask=active, attention_scale=0.125, workspace=ws), device)
+    torch.cuda.synchronize(device)
+    identical = bool(torch.equal(before, ws.output))
+    lattice_read = batch * pages_per_seq * (2 * page * heads * dim + pool.page_payload_bytes - 2 * pool._code_bytes)
     return {
         "attention_decode": {"batch": batch, "ctx": ctx + 1, "q_heads": q_heads, "kv_heads": heads, "head_dim": dim,
                              "pages_per_seq": pages_per_seq, "us": round(t_attn, 2),
                              "gbs": round(attn_bytes / t_attn / 1e3, 1),
                              "frac_of_hbm": round(attn_bytes / t_attn / 1e3 / pk["hbm_gbs"], 4)},
+        "attention_decode_lattice_shadow": {
+            "note": "opt-in: int8 lattice coordinates kept beside the codes", "extra_bytes": int(shadow_bytes),
+            "us": round(t_shadow, 2), "bytes_read": int(lattice_read),
+            "gbs": round(lattice_read / t_shadow / 1e3, 1),
+            "frac_of_hbm": round(lattice_read / t_shadow / 1e3 / pk["hbm_gbs"], 4),
+            "output_identical_to_packed": identical},
         "page_pack_publish": {"pages": batch, "us": round(t_pack, 2), "us_per_page": round(t_pack / batch, 3),
                               "gbs": round(pack_bytes / t_pack / 1e3, 1), "note": "includes two small fill kernels"},
     }
@@ -569,7 +583,7 @@ def decode_workload(torch, device, *, requests: int = 64, new_tokens: int = 256,
 
     model, cache = build_llama_w4a4kv4(hidden_size=2048, intermediate_size=8192, num_layers=16, num_heads=32,
                                        num_kv_heads=8, head_dim=64, vocab_size=128256, capacity=requests,
-                                       max_cache_len=2048 + new_tokens + 16 + 72, device=device, seed=0)
+                                       max_cache_len=2048 + new_tokens + 16 + 144, device=device, seed=0)
     runner = BatchedNQKVLlamaRunner(model, cache)
     gen = torch.Generator().manual_seed(128)
     lengths = torch.randint(128, 2049, (requests,), generator=gen).tolist()
@@ -634,6 +648,25 @@ def decode_workload(torch, device, *, requests: int = 64, new_tokens: int = 256,
                 "extra_weight_bytes": int(added), "decode_steps": resident_steps,
                 "ms_per_step": round(resident_ms / resident_steps, 3),
                 "decode_tok_s": round(requests * resident_steps / (resident_ms * 1e-3), 1)}
+    # second opt-in on top: the decoded lattice coordinates of every KV page kept beside its codes (8 bits per
+    # entry), attention reads them instead of searching E8 per block; outputs are bit-identical
+    kv_added = cache.enable_lattice_shadow()
+    runner.capture_decode_graph()
+    for _ in range(3):
+        runner.decode()
+    torch.cuda.synchronize(device)
+    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s0.record()
+    for _ in range(resident_steps):
+        runner.decode()
+    s1.record()
+    torch.cuda.synchronize(device)
+    shadow_ms = s0.elapsed_time(s1)
+    resident["with_kv_lattice_shadow"] = {
+        "note": "also opt-in: decoded lattice coordinates of the KV pages kept beside the codes",
+        "extra_kv_bytes": int(kv_added), "decode_steps": resident_steps,
+        "ms_per_step": round(shadow_ms / resident_steps, 3),
+        "decode_tok_s": round(requests * resident_steps / (shadow_ms * 1e-3), 1)}
     return {**({"kernel_mix": mix} if mix else {}), "resident_decoded_weights": resident,
             "model": "llama-3.2-1b-arch random init, W4A4KV4, 112 NQRT4 projections", "requests": requests,
             "prompt_tokens": int(sum(lengths)), "decode_steps": steps, "ms_per_step": round(ms / steps, 3),
@@ -660,7 +693,7 @@ def run_tp70b(args) -> None:
     model, cache = build_llama_tp_shard(hidden_size=8192, intermediate_size=28672, num_layers=args.tp_layers,
                                         num_heads=64, num_kv_heads=8, head_dim=128, vocab_size=128256, rank=rank,
                                         world=world, capacity=args.tp_batch,
-                                        max_cache_len=args.tp_context + 2 * (steps + max(args.warmup, 3)) + 32, device=device)
+                                        max_cache_len=args.tp_context + 3 * (steps + max(args.warmup, 3)) + 32, device=device)
     fill_cache_synthetic(cache, args.tp_context)
     runner = TensorParallelRunner(model, cache)
     runner.start_decode(args.tp_context)
@@ -721,6 +754,29 @@ def run_tp70b(args) -> None:
             dist.all_reduce(rms, op=dist.ReduceOp.MAX)
         resident = {"note": "opt-in: decoded BF16 weights of the shard kept in HBM", "extra_weight_bytes_per_rank": int(added),
                     "ms_per_step": float(rms.item()), "tok_s": args.tp_batch / (float(rms.item()) * 1e-3)}
+        # on top: the decoded lattice shadow of the KV pages (attention reads coordinates instead of searching)
+        if isinstance(runner.graph, torch.cuda.CUDAGraph):
+            runner.graph.reset()
+            runner.graph = None
+        kv_added = cache.enable_lattice_shadow()
+        if graph is True:
+            runner.capture_decode_graph()
+        for _ in range(max(args.warmup, 3)):
+            runner.decode()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+        k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        k0.record()
+        for _ in range(steps):
+            runner.decode()
+        k1.record()
+        torch.cuda.synchronize(device)
+        kms = torch.tensor([k0.elapsed_time(k1) / steps], device=device)
+        if world > 1:
+            dist.all_reduce(kms, op=dist.ReduceOp.MAX)
+        resident["with_kv_lattice_shadow"] = {"extra_kv_bytes_per_rank": int(kv_added), "ms_per_step": float(kms.item()),
+                                              "tok_s": args.tp_batch / (float(kms.item()) * 1e-3)}
     if rank == 0:
         ms_step = float(ms.item())
         from nestquant_aiinfra_b200.fused_linear import FusedNQRTLinear

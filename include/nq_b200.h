@@ -267,6 +267,45 @@ int nq_kv_attention(const void* query, int q_dtype, int batch, int q_tokens, int
                     void* workspace, size_t workspace_bytes, void* out, int out_dtype,
                     nq_stream_t stream);
 
+/* Decoded shadow of the page pool ("lattice pages"), an opt-in trade of HBM for attention time.
+ * Decoding a K/V block (a nearest-point search in E8) is a pure function of its 32-bit codeword, and
+ * the paged attention above is bound by those searches, not by HBM.  A caller with memory to spare
+ * keeps, beside each code stream, key_lattice / value_lattice int8[capacity, P*H*D]: the eight
+ * minimum-energy coordinates of every block, doubled (half-integers in [-14, 14] -> [-28, 28]);
+ * 8 bits per entry beside the 4.25 of the page itself.  The NQKV4 streams stay the record (and what
+ * is compared with the reference); the shadow is derived from them on the device:
+ *   nq_kv_expand_pages         shadow of the listed pages of ONE code stream (page_ids[i] < 0 skipped),
+ *                              for eager writers and for converting a pool that is already filled;
+ *   nq_kv_pack_publish_lattice nq_kv_pack_publish that also writes the shadow of the pages it publishes;
+ *   nq_kv_attention_lattice    nq_kv_attention reading the shadow instead of searching: the same
+ *                              coordinates enter the same float32 arithmetic, so the output is
+ *                              bit-identical to nq_kv_attention.
+ * The reference always decodes in the attention kernel (runtime/nqkv_attention_k1.py:50-81): no counterpart. */
+int nq_kv_expand_pages(const uint8_t* codes, int8_t* lattice, const int32_t* page_ids, int64_t count,
+                       int pool_capacity, int page_size, int heads, int dim, nq_stream_t stream);
+int nq_kv_pack_publish_lattice(const void* hot_keys, const void* hot_values, int kv_dtype,
+                               int32_t* hot_lengths, const uint8_t* boundary_mask,
+                               const int32_t* target_page_ids, uint8_t* key_codes, uint8_t* key_betas,
+                               float* key_norms, uint8_t* value_codes, uint8_t* value_betas,
+                               float* value_norms, const float* key_beta_table,
+                               const float* value_beta_table, int32_t* page_indices, int32_t* page_counts,
+                               int32_t* last_page_lens, int max_sequences, int max_pages,
+                               int pool_capacity, int page_size, int heads, int dim, int8_t* key_lattice,
+                               int8_t* value_lattice, nq_stream_t stream);
+int nq_kv_attention_lattice(const void* query, int q_dtype, int batch, int q_tokens, int q_heads,
+                            const int32_t* slot_ids, const uint8_t* active_mask, const int32_t* q_lens,
+                            const uint8_t* cache_active, const int32_t* sequence_lengths,
+                            const int32_t* page_indices, const int32_t* page_counts,
+                            const int32_t* last_page_lens, const int32_t* hot_lengths,
+                            const uint8_t* key_codes, const uint8_t* key_betas, const float* key_norms,
+                            const uint8_t* value_codes, const uint8_t* value_betas,
+                            const float* value_norms, const float* key_beta_table,
+                            const float* value_beta_table, const void* hot_keys, const void* hot_values,
+                            int max_sequences, int max_pages, int pool_capacity, int page_size,
+                            int kv_heads, int dim, float scale, void* workspace, size_t workspace_bytes,
+                            void* out, int out_dtype, const int8_t* key_lattice,
+                            const int8_t* value_lattice, nq_stream_t stream);
+
 /* -------------------------------------------------------------------------
  * Normalised Sylvester Hadamard along the last axis of a contiguous [rows, n]
  * tensor, n a power of two in [8, 32768], computed in the tensor's dtype exactly as

@@ -37,6 +37,7 @@ struct AttnParams {
     const uint8_t *key_codes, *key_betas, *value_codes, *value_betas;
     const float *key_norms, *value_norms, *key_beta_table, *value_beta_table;
     const void *hot_keys, *hot_values;  // [S, P, H, D] bf16
+    const int8_t *key_lattice, *value_lattice;  // optional decoded shadow of the pool (doubled coordinates as int8)
     int max_sequences, max_pages, pool_capacity;
     float scale_log2e;  // attention scale * log2(e)
     float sqrt_dim, inv_sqrt_dim;
@@ -82,7 +83,19 @@ __device__ __forceinline__ bool resolve_query(const AttnParams& p, int qi, int& 
 
 // Register budget: the exact E8 decode leaves issue slots idle at 12 warps per SM (168 registers), so the
 // kernel is built for 4 resident CTAs (128 registers; a few spilled words cost less than the lost warps).
-template <int G, int BPR>
+// Eight doubled lattice coordinates (int8) -> the float coordinates the packed decode yields: each byte,
+// offset by 128, is dropped into the mantissa of 1.5 * 2^23 and one FMA removes the offsets and halves.
+__device__ __forceinline__ void nq_lattice_block(const uint2 raw, float v[8]) {
+    const uint32_t lo = raw.x ^ 0x80808080u, hi = raw.y ^ 0x80808080u;
+    const float bias = -0.5f * (NQ_MAGIC + 128.0f);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        v[j] = fmaf(__uint_as_float(__byte_perm(lo, 0x4B400000u, 0x7650u | (uint32_t)j)), 0.5f, bias);
+        v[j + 4] = fmaf(__uint_as_float(__byte_perm(hi, 0x4B400000u, 0x7650u | (uint32_t)j)), 0.5f, bias);
+    }
+}
+
+template <int G, int BPR, bool LAT>
 __global__ void __launch_bounds__(kAttnThreads, (G <= 4 ? 4 : 3)) nq_attn_paged_kernel(const AttnParams p) {
     constexpr int TPW = 32 / BPR;  // tokens per warp step
     constexpr int D = BPR * 8;
@@ -117,8 +130,105 @@ __global__ void __launch_bounds__(kAttnThreads, (G <= 4 ? 4 : 3)) nq_attn_paged_
         const int s_begin = split * per, s_end = min(total_slots, s_begin + per);
         const int rows = p.page_size * p.kv_heads;
         const int64_t code_bytes = (int64_t)rows * D / 2, beta_bytes = (int64_t)rows * D / 32;
+        // scores of one token against the G query heads and the running-softmax update (lane = one E8 block)
+        auto update = [&](const float kvec[8], const float vvec[8], float kscale, float vscale, bool valid) {
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                float s = 0.0f;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) s = fmaf(q[g][j], kvec[j], s);
+                s *= kscale;  // the beta of this lane's block, the norm of its row
+#pragma unroll
+                for (int off = 1; off < BPR; off <<= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+                if (valid) {
+                    // The reference point m[g] of the running softmax only moves when a score exceeds it
+                    // by more than 8 (a factor 256): until then the terms are added unscaled, which saves
+                    // the rescaling of the accumulator on almost every token and changes no sum mathematically.
+                    if (s > m[g] + 8.0f) {
+                        const float corr = exp2f(m[g] - s);  // exp2(-inf) = 0 on the first token
+                        l[g] *= corr;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) acc[g][j] *= corr;
+                        m[g] = s;
+                    }
+                    const float pr = exp2f(s - m[g]);
+                    l[g] += pr;
+                    const float pv = pr * vscale;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) acc[g][j] = fmaf(pv, vvec[j], acc[g][j]);
+                }
+            }
+        };
+        if constexpr (LAT) {
+            // Decoded shadow: a page costs a few hundred instructions per warp, so the loads are what has to be
+            // hidden.  The warp walks its cold pages as a stream of half-page items and fetches item i + 1
+            // (lattice coordinates, beta ids, norms) before it computes item i; token order is unchanged, so
+            // the sums are those of the packed kernel.
+            constexpr int CH = 2;                  // token steps per item
+            constexpr int kItemTokens = CH * TPW;
+            const int items_per_page = (p.page_size + kItemTokens - 1) / kItemTokens;
+            const int cold_end = min(s_end, page_count);
+            uint2 nk[CH], nv[CH];
+            int nid[CH];
+            float nkn[CH], nvn[CH];
+            // returns the page id of the item, -1 past the end of the warp's work, -2 for a page to skip
+            auto fetch_item = [&](int item) -> int {
+                const int ps = s_begin + warp + (item / items_per_page) * kAttnWarps;
+                if (ps >= cold_end || ps * p.page_size >= limit) return -1;
+                const int page_id = p.page_indices[(int64_t)slot * p.max_pages + ps];
+                if (page_id < 0 || page_id >= p.pool_capacity) return -2;
+                const int t_base = (item % items_per_page) * kItemTokens + tsub;
+#pragma unroll
+                for (int i = 0; i < CH; ++i) {
+                    const int row = min(t_base + i * TPW, p.page_size - 1) * p.kv_heads + h;
+                    const int64_t g = (int64_t)row * BPR + blk;
+                    const int64_t gl = (int64_t)page_id * rows * BPR + g;
+                    nk[i] = __ldg(reinterpret_cast<const uint2*>(p.key_lattice) + gl);
+                    nv[i] = __ldg(reinterpret_cast<const uint2*>(p.value_lattice) + gl);
+                    nid[i] = nq_beta_id(p.key_betas + page_id * beta_bytes, g) |
+                             (nq_beta_id(p.value_betas + page_id * beta_bytes, g) << 2);
+                    nkn[i] = __ldg(p.key_norms + (int64_t)page_id * rows + row);
+                    nvn[i] = __ldg(p.value_norms + (int64_t)page_id * rows + row);
+                }
+                return page_id;
+            };
+            int item = 0;
+            int next_page = fetch_item(0);
+            while (next_page != -1) {
+                uint2 ck[CH], cv[CH];
+                int cid[CH];
+                float ckn[CH], cvn[CH];
+#pragma unroll
+                for (int i = 0; i < CH; ++i) {
+                    ck[i] = nk[i]; cv[i] = nv[i]; cid[i] = nid[i]; ckn[i] = nkn[i]; cvn[i] = nvn[i];
+                }
+                const int this_page = next_page, this_item = item;
+                ++item;
+                next_page = fetch_item(item);
+                if (this_page < 0) continue;
+                const int ps = s_begin + warp + (this_item / items_per_page) * kAttnWarps;
+                const int tlimit = ps == page_count - 1 ? last_len : p.page_size;
+                const int base_token = ps * p.page_size;
+                const int t_first = (this_item % items_per_page) * kItemTokens;
+#pragma unroll
+                for (int i = 0; i < CH; ++i) {
+                    if (t_first + i * TPW >= tlimit) break;  // warp-uniform
+                    const int t = t_first + i * TPW + tsub;
+                    const bool valid = t < tlimit && base_token + t < limit;
+                    const float kb = __ldg(p.key_beta_table + (cid[i] & 3));
+                    const float vb = __ldg(p.value_beta_table + (cid[i] >> 2));
+                    const float kds = nq_div_by(ckn[i], p.sqrt_dim, p.inv_sqrt_dim);
+                    const float vds = nq_div_by(cvn[i], p.sqrt_dim, p.inv_sqrt_dim);
+                    float kvec[8], vvec[8];
+                    nq_lattice_block(ck[i], kvec);
+                    nq_lattice_block(cv[i], vvec);
+                    update(kvec, vvec, kb * kds, vb * vds, valid);
+                }
+            }
+        }
         for (int ps = s_begin + warp; ps < s_end; ps += kAttnWarps) {
             const bool is_hot = ps >= page_count;
+            if (LAT && !is_hot) continue;  // cold pages were streamed above
             const int base_token = is_hot ? cold : ps * p.page_size;
             if (base_token >= limit) break;  // warp-uniform: later slots are later tokens
             const int tlimit = is_hot ? hot_len : (ps == page_count - 1 ? last_len : p.page_size);
@@ -135,42 +245,20 @@ __global__ void __launch_bounds__(kAttnThreads, (G <= 4 ? 4 : 3)) nq_attn_paged_
                     const int next_id = p.page_indices[(int64_t)slot * p.max_pages + nps];
                     if (next_id >= 0 && next_id < p.pool_capacity) {
                         const int row = (lane & 15) * p.kv_heads + h;
-                        const uint8_t* src = (lane < 16 ? p.key_codes : p.value_codes) + next_id * code_bytes +
-                                             (int64_t)row * BPR * 4;
-                        asm volatile("prefetch.global.L1 [%0];" ::"l"(src));
-                        if (BPR * 4 > 128) asm volatile("prefetch.global.L1 [%0];" ::"l"(src + 128));
+                        if (LAT) {  // the row's decoded coordinates: D bytes
+                            const int8_t* src = (lane < 16 ? p.key_lattice : p.value_lattice) +
+                                                ((int64_t)next_id * rows + row) * D;
+                            asm volatile("prefetch.global.L1 [%0];" ::"l"(src));
+                            if (D > 128) asm volatile("prefetch.global.L1 [%0];" ::"l"(src + 128));
+                        } else {
+                            const uint8_t* src = (lane < 16 ? p.key_codes : p.value_codes) + next_id * code_bytes +
+                                                 (int64_t)row * BPR * 4;
+                            asm volatile("prefetch.global.L1 [%0];" ::"l"(src));
+                            if (BPR * 4 > 128) asm volatile("prefetch.global.L1 [%0];" ::"l"(src + 128));
+                        }
                     }
                 }
             }
-            // scores of one token against the G query heads and the running-softmax update (lane = one E8 block)
-            auto update = [&](const float kvec[8], const float vvec[8], float kscale, float vscale, bool valid) {
-#pragma unroll
-                for (int g = 0; g < G; ++g) {
-                    float s = 0.0f;
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) s = fmaf(q[g][j], kvec[j], s);
-                    s *= kscale;  // the beta of this lane's block, the norm of its row
-#pragma unroll
-                    for (int off = 1; off < BPR; off <<= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-                    if (valid) {
-                        // The reference point m[g] of the running softmax only moves when a score exceeds it
-                        // by more than 8 (a factor 256): until then the terms are added unscaled, which saves
-                        // the rescaling of the accumulator on almost every token and changes no sum mathematically.
-                        if (s > m[g] + 8.0f) {
-                            const float corr = exp2f(m[g] - s);  // exp2(-inf) = 0 on the first token
-                            l[g] *= corr;
-#pragma unroll
-                            for (int j = 0; j < 8; ++j) acc[g][j] *= corr;
-                            m[g] = s;
-                        }
-                        const float pr = exp2f(s - m[g]);
-                        l[g] += pr;
-                        const float pv = pr * vscale;
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) acc[g][j] = fmaf(pv, vvec[j], acc[g][j]);
-                    }
-                }
-            };
             if (is_hot) {
                 for (int t0 = 0; t0 < tlimit; t0 += TPW) {
                     const int t = t0 + tsub;
@@ -190,14 +278,21 @@ __global__ void __launch_bounds__(kAttnThreads, (G <= 4 ? 4 : 3)) nq_attn_paged_
                 const uint8_t* vbetas = p.value_betas + page_id * beta_bytes;
                 const float* knorms = p.key_norms + (int64_t)page_id * rows;
                 const float* vnorms = p.value_norms + (int64_t)page_id * rows;
-                uint32_t kw, vw;
+                uint32_t kw = 0, vw = 0;
+                uint2 klat = make_uint2(0, 0), vlat = make_uint2(0, 0);
                 int kid, vid;
                 float kn, vn;
                 auto fetch = [&](int t) {
                     const int row = min(t, p.page_size - 1) * p.kv_heads + h;
                     const int64_t g = (int64_t)row * BPR + blk;
-                    kw = __ldg(kcodes + g);
-                    vw = __ldg(vcodes + g);
+                    if (LAT) {
+                        const int64_t gl = (int64_t)page_id * rows * BPR + g;
+                        klat = __ldg(reinterpret_cast<const uint2*>(p.key_lattice) + gl);
+                        vlat = __ldg(reinterpret_cast<const uint2*>(p.value_lattice) + gl);
+                    } else {
+                        kw = __ldg(kcodes + g);
+                        vw = __ldg(vcodes + g);
+                    }
                     kid = nq_beta_id(kbetas, g);
                     vid = nq_beta_id(vbetas, g);
                     kn = __ldg(knorms + row);
@@ -208,13 +303,20 @@ __global__ void __launch_bounds__(kAttnThreads, (G <= 4 ? 4 : 3)) nq_attn_paged_
                     const int t = t0 + tsub;
                     const bool valid = t < tlimit && base_token + t < limit;
                     const uint32_t kw_now = kw, vw_now = vw;
+                    const uint2 klat_now = klat, vlat_now = vlat;
                     const float kb = __ldg(p.key_beta_table + kid), vb = __ldg(p.value_beta_table + vid);
                     const float kds = nq_div_by(kn, p.sqrt_dim, p.inv_sqrt_dim);
                     const float vds = nq_div_by(vn, p.sqrt_dim, p.inv_sqrt_dim);
                     if (t0 + TPW < tlimit) fetch(t + TPW);
                     float kvec[8], vvec[8];
-                    nq_decode_codeword_undithered(kw_now, kvec);
-                    nq_decode_codeword_undithered(vw_now, vvec);
+                    if (LAT) {
+                        // the pages' decoded shadow: same coordinates, read instead of searched
+                        nq_lattice_block(klat_now, kvec);
+                        nq_lattice_block(vlat_now, vvec);
+                    } else {
+                        nq_decode_codeword_undithered(kw_now, kvec);
+                        nq_decode_codeword_undithered(vw_now, vvec);
+                    }
                     update(kvec, vvec, kb * kds, vb * vds, valid);
                 }
             }
@@ -305,17 +407,22 @@ __global__ void __launch_bounds__(128) nq_attn_reduce_kernel(const AttnParams p)
     }
 }
 
-template <int G>
-int launch_attn(const AttnParams& p, dim3 grid, cudaStream_t s) {
-    if (p.dim == 64) nq_attn_paged_kernel<G, 8><<<grid, kAttnThreads, 0, s>>>(p);
-    else if (p.dim == 128) nq_attn_paged_kernel<G, 16><<<grid, kAttnThreads, 0, s>>>(p);
-    else if (p.dim == 32) nq_attn_paged_kernel<G, 4><<<grid, kAttnThreads, 0, s>>>(p);
-    else if (p.dim == 256) nq_attn_paged_kernel<G, 32><<<grid, kAttnThreads, 0, s>>>(p);
+template <int G, bool LAT>
+int launch_attn_dim(const AttnParams& p, dim3 grid, cudaStream_t s) {
+    if (p.dim == 64) nq_attn_paged_kernel<G, 8, LAT><<<grid, kAttnThreads, 0, s>>>(p);
+    else if (p.dim == 128) nq_attn_paged_kernel<G, 16, LAT><<<grid, kAttnThreads, 0, s>>>(p);
+    else if (p.dim == 32) nq_attn_paged_kernel<G, 4, LAT><<<grid, kAttnThreads, 0, s>>>(p);
+    else if (p.dim == 256) nq_attn_paged_kernel<G, 32, LAT><<<grid, kAttnThreads, 0, s>>>(p);
     else {
         nq_set_error("nq_kv_attention: head_dim must be 32, 64, 128 or 256");
         return NQ_ERR_ARG;
     }
     return NQ_OK;
+}
+
+template <int G>
+int launch_attn(const AttnParams& p, dim3 grid, cudaStream_t s) {
+    return p.key_lattice ? launch_attn_dim<G, true>(p, grid, s) : launch_attn_dim<G, false>(p, grid, s);
 }
 
 // Page-range splits per (query token, KV head).  The grid should fill whole waves of the CTAs that are
@@ -354,7 +461,7 @@ extern "C" size_t nq_kv_attention_workspace_bytes(int batch, int q_tokens, int q
     return (size_t)batch * q_tokens * q_heads * splits * (dim + 2) * sizeof(float) + 256;
 }
 
-extern "C" int nq_kv_attention(const void* query, int q_dtype, int batch, int q_tokens, int q_heads,
+static int kv_attention_impl(const void* query, int q_dtype, int batch, int q_tokens, int q_heads,
                                const int32_t* slot_ids, const uint8_t* active_mask, const int32_t* q_lens,
                                const uint8_t* cache_active, const int32_t* sequence_lengths,
                                const int32_t* page_indices, const int32_t* page_counts,
@@ -365,7 +472,7 @@ extern "C" int nq_kv_attention(const void* query, int q_dtype, int batch, int q_
                                const void* hot_keys, const void* hot_values, int max_sequences, int max_pages,
                                int pool_capacity, int page_size, int kv_heads, int dim, float scale,
                                void* workspace, size_t workspace_bytes, void* out, int out_dtype,
-                               nq_stream_t stream) {
+                               const int8_t* key_lattice, const int8_t* value_lattice, nq_stream_t stream) {
     NQ_REQUIRE(query && slot_ids && cache_active && sequence_lengths && page_indices && page_counts &&
                    last_page_lens && hot_lengths && key_codes && key_betas && key_norms && value_codes &&
                    value_betas && value_norms && key_beta_table && value_beta_table && hot_keys && hot_values && out,
@@ -391,11 +498,12 @@ extern "C" int nq_kv_attention(const void* query, int q_dtype, int batch, int q_
     p.key_norms = key_norms; p.value_norms = value_norms;
     p.key_beta_table = key_beta_table; p.value_beta_table = value_beta_table;
     p.hot_keys = hot_keys; p.hot_values = hot_values;
+    p.key_lattice = key_lattice; p.value_lattice = value_lattice;
     p.max_sequences = max_sequences; p.max_pages = max_pages; p.pool_capacity = pool_capacity;
     p.scale_log2e = scale * 1.4426950408889634f;
     p.sqrt_dim = (float)sqrt((double)dim);
     p.inv_sqrt_dim = 1.0f / p.sqrt_dim;
-    p.splits = choose_splits(batch * q_tokens, kv_heads, max_pages, group);
+    p.splits = choose_splits(batch * q_tokens, kv_heads, max_pages, group);  // same split with or without the shadow: same sums
     p.out = out; p.out_dtype = out_dtype;
     p.partial = reinterpret_cast<float*>(workspace);
     if (p.splits > 1) {
@@ -419,4 +527,47 @@ extern "C" int nq_kv_attention(const void* query, int q_dtype, int batch, int q_
         NQ_CHECK_LAUNCH("nq_kv_attention(reduce)");
     }
     return NQ_OK;
+}
+
+extern "C" int nq_kv_attention(const void* query, int q_dtype, int batch, int q_tokens, int q_heads,
+                               const int32_t* slot_ids, const uint8_t* active_mask, const int32_t* q_lens,
+                               const uint8_t* cache_active, const int32_t* sequence_lengths,
+                               const int32_t* page_indices, const int32_t* page_counts,
+                               const int32_t* last_page_lens, const int32_t* hot_lengths,
+                               const uint8_t* key_codes, const uint8_t* key_betas, const float* key_norms,
+                               const uint8_t* value_codes, const uint8_t* value_betas, const float* value_norms,
+                               const float* key_beta_table, const float* value_beta_table,
+                               const void* hot_keys, const void* hot_values, int max_sequences, int max_pages,
+                               int pool_capacity, int page_size, int kv_heads, int dim, float scale,
+                               void* workspace, size_t workspace_bytes, void* out, int out_dtype,
+                               nq_stream_t stream) {
+    return kv_attention_impl(query, q_dtype, batch, q_tokens, q_heads, slot_ids, active_mask, q_lens, cache_active,
+                             sequence_lengths, page_indices, page_counts, last_page_lens, hot_lengths, key_codes,
+                             key_betas, key_norms, value_codes, value_betas, value_norms, key_beta_table,
+                             value_beta_table, hot_keys, hot_values, max_sequences, max_pages, pool_capacity,
+                             page_size, kv_heads, dim, scale, workspace, workspace_bytes, out, out_dtype, nullptr,
+                             nullptr, stream);
+}
+
+extern "C" int nq_kv_attention_lattice(const void* query, int q_dtype, int batch, int q_tokens, int q_heads,
+                                       const int32_t* slot_ids, const uint8_t* active_mask, const int32_t* q_lens,
+                                       const uint8_t* cache_active, const int32_t* sequence_lengths,
+                                       const int32_t* page_indices, const int32_t* page_counts,
+                                       const int32_t* last_page_lens, const int32_t* hot_lengths,
+                                       const uint8_t* key_codes, const uint8_t* key_betas, const float* key_norms,
+                                       const uint8_t* value_codes, const uint8_t* value_betas,
+                                       const float* value_norms, const float* key_beta_table,
+                                       const float* value_beta_table, const void* hot_keys, const void* hot_values,
+                                       int max_sequences, int max_pages, int pool_capacity, int page_size,
+                                       int kv_heads, int dim, float scale, void* workspace, size_t workspace_bytes,
+                                       void* out, int out_dtype, const int8_t* key_lattice,
+                                       const int8_t* value_lattice, nq_stream_t stream) {
+    NQ_REQUIRE(key_lattice && value_lattice && nq_aligned16(key_lattice) && nq_aligned16(value_lattice), NQ_ERR_ARG,
+               "nq_kv_attention_lattice: 16-byte aligned lattice pages required");
+    return kv_attention_impl(query, q_dtype, batch, q_tokens, q_heads, slot_ids, active_mask, q_lens, cache_active,
+                             sequence_lengths, page_indices, page_counts, last_page_lens, hot_lengths, key_codes,
+                             key_betas, key_norms, value_codes, value_betas, value_norms, key_beta_table,
+                             value_beta_table, hot_keys, hot_values, max_sequences, max_pages, pool_capacity,
+                             page_size, kv_heads, dim, scale, workspace, workspace_bytes, out, out_dtype, key_lattice,
+                             value_lattice, stream);
 }

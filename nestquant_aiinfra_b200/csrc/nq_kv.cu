@@ -96,7 +96,49 @@ struct PackParams {
     int32_t* hot_lengths_rw;
     int max_sequences, max_pages, page_size, heads, dim, pool_capacity, ctas_per_stream;
     float sqrt_dim;
+    int8_t *key_lattice, *value_lattice;  // optional decoded shadow of the pool, [capacity, P*H*D]
 };
+
+// Decoded shadow of a page ("lattice page"): every E8 block of the code stream decoded once to its eight
+// minimum-energy coordinates, stored doubled as int8 (half-integers in [-14, 14] -> integers in [-28, 28]).
+// It is a pure function of the code stream, kept beside it by callers that trade HBM for attention time.
+__device__ __forceinline__ void nq_expand_block(const uint32_t* codes, int8_t* lattice, int64_t g) {
+    float r[8];
+    nq_decode_codeword_undithered(__ldg(codes + g), r);
+    uint32_t lo = 0, hi = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        lo |= ((uint32_t)(int)(2.0f * r[j]) & 0xffu) << (8 * j);
+        hi |= ((uint32_t)(int)(2.0f * r[j + 4]) & 0xffu) << (8 * j);
+    }
+    reinterpret_cast<uint2*>(lattice)[g] = make_uint2(lo, hi);
+}
+
+// Shadow of the pages that nq_kv_pack_pages_kernel has just written (same predicate, before the publish).
+__global__ void __launch_bounds__(256) nq_kv_expand_packed_kernel(const PackParams p) {
+    const int slot = blockIdx.x;
+    const bool full = p.boundary_mask[slot] != 0 && p.hot_lengths[slot] == p.page_size;
+    const int page_id = p.target_page_ids[slot];
+    if (!full || page_id < 0 || page_id >= p.pool_capacity) return;
+    const int blocks = p.page_size * p.heads * (p.dim >> 3);
+    const bool is_value = blockIdx.y != 0;
+    const uint32_t* codes = reinterpret_cast<const uint32_t*>(is_value ? p.value_codes : p.key_codes) +
+                            (int64_t)page_id * blocks;
+    int8_t* lattice = (is_value ? p.value_lattice : p.key_lattice) + (int64_t)page_id * blocks * 8;
+    for (int g = threadIdx.x; g < blocks; g += blockDim.x) nq_expand_block(codes, lattice, g);
+}
+
+// Shadow of an explicit list of pages (eager writers, conversion of an existing pool).
+__global__ void __launch_bounds__(256) nq_kv_expand_pages_kernel(const uint32_t* codes, int8_t* lattice,
+                                                                 const int32_t* page_ids, int blocks,
+                                                                 int pool_capacity) {
+    const int page_id = page_ids[blockIdx.x];
+    if (page_id < 0 || page_id >= pool_capacity) return;
+    const uint32_t* src = codes + (int64_t)page_id * blocks;
+    int8_t* dst = lattice + (int64_t)page_id * blocks * 8;
+    for (int g = blockIdx.y * blockDim.x + threadIdx.x; g < blocks; g += gridDim.y * blockDim.x)
+        nq_expand_block(src, dst, g);
+}
 
 template <typename T>
 __global__ void __launch_bounds__(NQ_ENC_THREADS, 5) nq_kv_pack_pages_kernel(const PackParams p) {
@@ -212,13 +254,14 @@ extern "C" int nq_kv_append(const void* key, const void* value, int kv_dtype, in
     return NQ_OK;
 }
 
-extern "C" int nq_kv_pack_publish(const void* hot_keys, const void* hot_values, int kv_dtype, int32_t* hot_lengths,
-                                  const uint8_t* boundary_mask, const int32_t* target_page_ids,
-                                  uint8_t* key_codes, uint8_t* key_betas, float* key_norms, uint8_t* value_codes,
-                                  uint8_t* value_betas, float* value_norms, const float* key_beta_table,
-                                  const float* value_beta_table, int32_t* page_indices, int32_t* page_counts,
-                                  int32_t* last_page_lens, int max_sequences, int max_pages, int pool_capacity,
-                                  int page_size, int heads, int dim, nq_stream_t stream) {
+static int kv_pack_publish_impl(const void* hot_keys, const void* hot_values, int kv_dtype, int32_t* hot_lengths,
+                                const uint8_t* boundary_mask, const int32_t* target_page_ids,
+                                uint8_t* key_codes, uint8_t* key_betas, float* key_norms, uint8_t* value_codes,
+                                uint8_t* value_betas, float* value_norms, const float* key_beta_table,
+                                const float* value_beta_table, int32_t* page_indices, int32_t* page_counts,
+                                int32_t* last_page_lens, int max_sequences, int max_pages, int pool_capacity,
+                                int page_size, int heads, int dim, int8_t* key_lattice, int8_t* value_lattice,
+                                nq_stream_t stream) {
     NQ_REQUIRE(hot_keys && hot_values && hot_lengths && boundary_mask && target_page_ids && key_codes && key_betas &&
                    key_norms && value_codes && value_betas && value_norms && key_beta_table && value_beta_table &&
                    page_indices && page_counts && last_page_lens,
@@ -237,6 +280,7 @@ extern "C" int nq_kv_pack_publish(const void* hot_keys, const void* hot_values, 
     p.page_indices = page_indices; p.page_counts = page_counts; p.last_page_lens = last_page_lens;
     p.max_sequences = max_sequences; p.max_pages = max_pages; p.page_size = page_size; p.heads = heads; p.dim = dim;
     p.pool_capacity = pool_capacity;
+    p.key_lattice = key_lattice; p.value_lattice = value_lattice;
     const int rpc = nq_encode_rows_per_cta(dim);
     p.ctas_per_stream = (page_size * heads + rpc - 1) / rpc;
     p.sqrt_dim = (float)sqrt((double)dim);
@@ -253,8 +297,57 @@ extern "C" int nq_kv_pack_publish(const void* hot_keys, const void* hot_values, 
         nq_kv_pack_pages_kernel<__half><<<grid, NQ_ENC_THREADS, smem, s>>>(p);
     }
     NQ_CHECK_LAUNCH("nq_kv_pack_publish(pack)");
+    if (key_lattice) {
+        nq_kv_expand_packed_kernel<<<dim3((unsigned)max_sequences, 2), 256, 0, s>>>(p);
+        NQ_CHECK_LAUNCH("nq_kv_pack_publish(lattice shadow)");
+    }
     nq_kv_publish_kernel<<<(max_sequences + 255) / 256, 256, 0, s>>>(p);
     NQ_CHECK_LAUNCH("nq_kv_pack_publish(publish)");
+    return NQ_OK;
+}
+
+extern "C" int nq_kv_pack_publish(const void* hot_keys, const void* hot_values, int kv_dtype, int32_t* hot_lengths,
+                                  const uint8_t* boundary_mask, const int32_t* target_page_ids,
+                                  uint8_t* key_codes, uint8_t* key_betas, float* key_norms, uint8_t* value_codes,
+                                  uint8_t* value_betas, float* value_norms, const float* key_beta_table,
+                                  const float* value_beta_table, int32_t* page_indices, int32_t* page_counts,
+                                  int32_t* last_page_lens, int max_sequences, int max_pages, int pool_capacity,
+                                  int page_size, int heads, int dim, nq_stream_t stream) {
+    return kv_pack_publish_impl(hot_keys, hot_values, kv_dtype, hot_lengths, boundary_mask, target_page_ids, key_codes,
+                                key_betas, key_norms, value_codes, value_betas, value_norms, key_beta_table,
+                                value_beta_table, page_indices, page_counts, last_page_lens, max_sequences, max_pages,
+                                pool_capacity, page_size, heads, dim, nullptr, nullptr, stream);
+}
+
+extern "C" int nq_kv_pack_publish_lattice(const void* hot_keys, const void* hot_values, int kv_dtype,
+                                          int32_t* hot_lengths, const uint8_t* boundary_mask,
+                                          const int32_t* target_page_ids, uint8_t* key_codes, uint8_t* key_betas,
+                                          float* key_norms, uint8_t* value_codes, uint8_t* value_betas,
+                                          float* value_norms, const float* key_beta_table,
+                                          const float* value_beta_table, int32_t* page_indices, int32_t* page_counts,
+                                          int32_t* last_page_lens, int max_sequences, int max_pages,
+                                          int pool_capacity, int page_size, int heads, int dim, int8_t* key_lattice,
+                                          int8_t* value_lattice, nq_stream_t stream) {
+    NQ_REQUIRE(key_lattice && value_lattice && nq_aligned16(key_lattice) && nq_aligned16(value_lattice), NQ_ERR_ARG,
+               "nq_kv_pack_publish_lattice: 16-byte aligned lattice pages required");
+    return kv_pack_publish_impl(hot_keys, hot_values, kv_dtype, hot_lengths, boundary_mask, target_page_ids, key_codes,
+                                key_betas, key_norms, value_codes, value_betas, value_norms, key_beta_table,
+                                value_beta_table, page_indices, page_counts, last_page_lens, max_sequences, max_pages,
+                                pool_capacity, page_size, heads, dim, key_lattice, value_lattice, stream);
+}
+
+extern "C" int nq_kv_expand_pages(const uint8_t* codes, int8_t* lattice, const int32_t* page_ids, int64_t count,
+                                  int pool_capacity, int page_size, int heads, int dim, nq_stream_t stream) {
+    NQ_REQUIRE(codes && lattice && page_ids, NQ_ERR_ARG, "nq_kv_expand_pages: null pointer");
+    NQ_REQUIRE(count >= 0 && count <= 0x7fffffff && pool_capacity >= 1 && dims_ok(page_size, heads, dim), NQ_ERR_ARG,
+               "nq_kv_expand_pages: bad geometry");
+    NQ_REQUIRE(nq_aligned16(codes) && nq_aligned16(lattice), NQ_ERR_ALIGN, "nq_kv_expand_pages: 16-byte alignment required");
+    if (count == 0) return NQ_OK;
+    const int blocks = page_size * heads * (dim >> 3);
+    const unsigned chunks = (unsigned)((blocks + 1023) / 1024);
+    nq_kv_expand_pages_kernel<<<dim3((unsigned)count, chunks), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const uint32_t*>(codes), lattice, page_ids, blocks, pool_capacity);
+    NQ_CHECK_LAUNCH("nq_kv_expand_pages");
     return NQ_OK;
 }
 

@@ -78,6 +78,17 @@ class BatchedNQKVLlamaCache(Cache):
         self._sequence_of_slot: dict[int, Hashable] = {}
 
     # ------------------------------------------------------------------ host control plane
+
+    def enable_lattice_shadow(self) -> int:
+        """Keep the decoded lattice coordinates of every layer's pages beside their codes (opt-in).
+
+        Trades HBM (8 bits per cached entry beside the page's 4.25) for attention time: the paged
+        attention then reads the coordinates instead of searching E8 for every block, with
+        bit-identical outputs.  Call it outside a graph capture and re-capture afterwards.  Returns
+        the bytes added.
+        """
+        return sum(cache.pool.enable_lattice_shadow() for cache in self.layer_caches)
+
     def register(self, sequence_id: Hashable, *, slot: int) -> None:
         if slot in self._sequence_of_slot:
             raise RuntimeError(f"slot {slot} is already registered")
@@ -240,6 +251,7 @@ class BatchedNQKVLlamaCache(Cache):
                 norms[plan["page_ids"]] = packed.row_norms.view(pages, -1)
             if plan["tail_src"].numel():
                 hot[plan["tail_slot"], plan["tail_pos"]] = flat[plan["tail_src"]].view(-1, self.num_kv_heads, dim)
+        pool.expand_pages(plan["page_ids"])  # keeps the opt-in decoded shadow current (no-op without one)
         slots = plan["slots"]
         cache.page_indices[slots] = plan["table"]
         cache.page_counts[slots] = plan["full"]

@@ -82,6 +82,37 @@ class NQKVPagePool:
         self.beta_table = torch.tensor(self.betas, device=target, dtype=torch.float32)
         self.value_beta_table = torch.tensor(self.value_beta_values, device=target, dtype=torch.float32)
         self._free = list(range(capacity - 1, -1, -1))
+        # opt-in decoded shadow of the code streams (``enable_lattice_shadow``): int8 [capacity, P*H*D]
+        self.key_lattice: torch.Tensor | None = None
+        self.value_lattice: torch.Tensor | None = None
+
+    def enable_lattice_shadow(self) -> int:
+        """Keep the decoded lattice coordinates of every page beside its codes (opt-in; returns the bytes added).
+
+        Decoding a block is a pure function of its codeword and is what bounds the paged attention;
+        with the shadow (8 bits per entry beside the page's 4.25) attention reads the coordinates
+        instead of searching for them and returns bit-identical outputs.  Pages already in the pool
+        are converted now; the page writers of this package keep the shadow current afterwards.
+        The NQKV4 streams stay the record and are unchanged.
+        """
+        if self.key_lattice is not None:
+            return 0
+        entries = self._row_count * self.head_dim
+        self.key_lattice = torch.zeros((self.capacity, entries), device=self.device, dtype=torch.int8)
+        self.value_lattice = torch.zeros_like(self.key_lattice)
+        self.expand_pages(torch.arange(self.capacity, dtype=torch.int32, device=self.device))
+        return 2 * self.capacity * entries
+
+    def expand_pages(self, page_ids: torch.Tensor) -> None:
+        """Refresh the decoded shadow of the listed pages (no-op without a shadow)."""
+        if self.key_lattice is None or page_ids.numel() == 0:
+            return
+        ids = page_ids.to(device=self.device, dtype=torch.int32).contiguous()
+        for codes, lattice in ((self.key_codes, self.key_lattice), (self.value_codes, self.value_lattice)):
+            status = _lib.lib().nq_kv_expand_pages(
+                _ptr(codes), _ptr(lattice), _ptr(ids), ctypes.c_int64(ids.numel()), _INT(self.capacity),
+                _INT(self.page_size), _INT(self.num_kv_heads), _INT(self.head_dim), _stream(self.device))
+            _lib.check(status, "expand_pages")
 
     @property
     def free_pages(self) -> int:
@@ -297,14 +328,18 @@ def launch_pack_full_hot_pages_graph_safe(cache: NQKVHotColdCache, *, boundary_m
         raise ValueError("boundary_mask must be bool with cache capacity shape")
     if boundary_mask.device != pool.device:
         raise ValueError("boundary_mask must be on the cache device")
-    status = _lib.lib().nq_kv_pack_publish(
+    args = [
         _ptr(cache.hot_keys), _ptr(cache.hot_values), _DTYPE_TAG[pool.output_dtype], _ptr(cache.hot_lengths),
         _ptr(boundary_mask), _ptr(cache.graph_target_page_ids), _ptr(pool.key_codes), _ptr(pool.key_betas),
         _ptr(pool.key_norms), _ptr(pool.value_codes), _ptr(pool.value_betas), _ptr(pool.value_norms),
         _ptr(pool.beta_table), _ptr(pool.value_beta_table), _ptr(cache.page_indices), _ptr(cache.page_counts),
         _ptr(cache.last_page_len), _INT(cache.max_sequences), _INT(cache.max_pages_per_sequence),
-        _INT(pool.capacity), _INT(pool.page_size), _INT(pool.num_kv_heads), _INT(pool.head_dim),
-        _stream(pool.device))
+        _INT(pool.capacity), _INT(pool.page_size), _INT(pool.num_kv_heads), _INT(pool.head_dim)]
+    if pool.key_lattice is not None:  # the decoded shadow of the published pages is written with them
+        status = _lib.lib().nq_kv_pack_publish_lattice(*args, _ptr(pool.key_lattice), _ptr(pool.value_lattice),
+                                                       _stream(pool.device))
+    else:
+        status = _lib.lib().nq_kv_pack_publish(*args, _stream(pool.device))
     _lib.check(status, "launch_pack_full_hot_pages_graph_safe")
 
 
@@ -342,7 +377,7 @@ def _attention(query4: torch.Tensor, cache: NQKVHotColdCache, slot_ids: torch.Te
     pool = cache.pool
     batch, tokens, heads, dim = query4.shape
     out_tag = _lib.NQ_BF16 if workspace.output.dtype == torch.bfloat16 else _lib.NQ_F32
-    status = _lib.lib().nq_kv_attention(
+    args = [
         _ptr(query4), _DTYPE_TAG[query4.dtype], _INT(batch), _INT(tokens), _INT(heads), _ptr(slot_ids),
         _ptr(active_mask), _ptr(q_lens), _ptr(cache.active), _ptr(cache.sequence_lengths), _ptr(cache.page_indices),
         _ptr(cache.page_counts), _ptr(cache.last_page_len), _ptr(cache.hot_lengths),
@@ -350,8 +385,12 @@ def _attention(query4: torch.Tensor, cache: NQKVHotColdCache, slot_ids: torch.Te
         _ptr(pool.value_betas), _ptr(pool.value_norms), _ptr(pool.beta_table), _ptr(pool.value_beta_table),
         _ptr(cache.hot_keys), _ptr(cache.hot_values), _INT(cache.max_sequences), _INT(cache.max_pages_per_sequence),
         _INT(pool.capacity), _INT(pool.page_size), _INT(pool.num_kv_heads), _INT(dim), ctypes.c_float(scale),
-        _ptr(workspace.partials), ctypes.c_size_t(workspace.partials.numel()), _ptr(workspace.output), _INT(out_tag),
-        _stream(pool.device))
+        _ptr(workspace.partials), ctypes.c_size_t(workspace.partials.numel()), _ptr(workspace.output), _INT(out_tag)]
+    if pool.key_lattice is not None:  # read the decoded shadow instead of searching E8 per block
+        status = _lib.lib().nq_kv_attention_lattice(*args, _ptr(pool.key_lattice), _ptr(pool.value_lattice),
+                                                    _stream(pool.device))
+    else:
+        status = _lib.lib().nq_kv_attention(*args, _stream(pool.device))
     _lib.check(status, what)
 
 

@@ -119,6 +119,7 @@ def fill_cache_synthetic(cache: BatchedNQKVLlamaCache, context: int, *, seed: in
                 norms[ids] = act.row_norms.view(capacity * full, -1)
                 del x, act
         if full:
+            pool.expand_pages(ids)  # keeps the opt-in decoded shadow current (no-op without one)
             layer.page_indices[:, :full] = ids.view(capacity, full).to(torch.int32)
         layer.page_counts.fill_(full)
         layer.last_page_len.fill_(page if full else 0)

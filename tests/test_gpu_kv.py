@@ -261,3 +261,58 @@ def test_written_pages_round_trip_through_attention(rt, oracle):
     out = rt.nqkv_decode_attention_batched_k1(q.cuda(), cache, slot_ids=slot_ids, active_mask=active, workspace=ws)
     expected = oracle.attn_decode(q.float().numpy(), [0, 1], [1, 1], rt.cache_arrays(cache), scale=0.125)
     _check_attention(out.cpu().numpy(), expected)
+
+
+def test_lattice_shadow_attention_is_bit_identical(oracle):
+    """Opt-in decoded shadow of the pool: attention reads coordinates instead of searching, same bits out.
+
+    Covers the three ways the shadow is written: conversion of a filled pool, the graph page writer
+    (pack + publish), and an explicit page list.
+    """
+    import nestquant_aiinfra_b200.runtime as rt
+
+    torch.manual_seed(11)
+    page, heads, dim, q_heads, seqs, max_pages = 16, 2, 64, 8, 3, 6
+    pool = rt.NQKVPagePool(capacity=seqs * max_pages, page_size=page, num_kv_heads=heads, head_dim=dim,
+                           key_betas=KEY_BETAS, value_betas=VALUE_BETAS)
+    cache = rt.NQKVHotColdCache(pool, max_sequences=seqs, max_pages_per_sequence=max_pages)
+    for slot in range(seqs):
+        cache.register(slot)
+    slot_ids = torch.arange(seqs, dtype=torch.int32, device="cuda")
+    everyone = torch.ones(seqs, dtype=torch.bool, device="cuda")
+
+    def grow(tokens: int) -> None:
+        for _ in range(tokens):
+            key = (torch.randn(seqs, heads, dim, device="cuda") * 1.3).bfloat16()
+            value = torch.randn(seqs, heads, dim, device="cuda").bfloat16()
+            rt._launch_append_hot_k1_graph_safe(key, value, cache, slot_ids=slot_ids, active_mask=everyone)
+            cache.graph_target_page_ids.copy_(slot_ids * max_pages + cache.page_counts)
+            rt.launch_pack_full_hot_pages_graph_safe(cache, boundary_mask=everyone)
+
+    def attend() -> torch.Tensor:
+        query = torch.randn(seqs, q_heads, dim, generator=torch.Generator().manual_seed(5)).bfloat16().cuda()
+        ws = rt.BatchedNQKVAttentionWorkspace.create(cache, batch_size=seqs, query_heads=q_heads,
+                                                     output_dtype=torch.float32)
+        return rt._launch_nqkv_decode_attention_batched_k1(query, cache, slot_ids=slot_ids, active_mask=everyone,
+                                                           attention_scale=0.125, workspace=ws).clone()
+
+    grow(2 * page + 5)                      # two published pages + a hot tail, no shadow yet
+    packed = attend()
+    added = pool.enable_lattice_shadow()    # converts the pages already in the pool
+    assert added == 2 * pool.capacity * page * heads * dim and pool.enable_lattice_shadow() == 0
+    assert torch.equal(attend(), packed)
+    grow(page + 3)                          # one more page through the graph writer, shadow written with it
+    with_shadow = attend()
+    key_lattice, value_lattice = pool.key_lattice, pool.value_lattice
+    pool.key_lattice = pool.value_lattice = None
+    assert torch.equal(attend(), with_shadow)   # the packed kernel on the same pool
+    pool.key_lattice, pool.value_lattice = key_lattice, value_lattice
+    # the shadow holds the doubled coordinates of the reference's decode
+    codes = pool.key_codes[0].cpu().numpy().view(np.uint32)
+    unpacked = np.stack([(codes >> (4 * j)) & 15 for j in range(8)], axis=1).astype(np.int64)
+    expect = (2.0 * oracle.decode_nested(unpacked)).astype(np.int8)
+    assert np.array_equal(pool.key_lattice[0].cpu().numpy().reshape(-1, 8), expect)
+    # explicit page list: wipe one page's shadow and restore it
+    pool.key_lattice[1].zero_()
+    pool.expand_pages(torch.tensor([1, -1], dtype=torch.int32))
+    assert torch.equal(attend(), with_shadow)
