@@ -105,3 +105,25 @@ def test_full_size_projection_tails_and_paths_agree(rt, oracle):
                       decoded=act.decoded[r:r + 1].contiguous())
         single = rt.linear_packed_w4a4_fp32(one, weight).cpu().numpy()[0]
         assert max_abs(single, full[r]) <= MAX_ABS_TOL and rel_fro(single, full[r]) <= REL_FRO_TOL
+
+
+@pytest.mark.parametrize("m", [1, 4, 64, 8192])
+def test_full_size_resident_weight_agrees_with_the_packed_call(rt, m):
+    """gate/up shape: the opt-in resident decoded weight is the per-call decode kept in memory, so the two
+    projections may differ only by the order of the FP32 sums."""
+    from nestquant_aiinfra_b200.rotation import hadamard
+
+    n, k = 8192, 2048
+    w = hadamard((0.02 * torch.randn(n, k, generator=rng(1000))).cuda())
+    packed = rt.quantize_weight_cuda(w, betas=W_BETAS, dither_seed=20261031, tensor_name="gate_up")
+    resident = rt.keep_decoded_weight(packed)
+    assert torch.equal(resident.decoded, rt.decode_packed_weight(packed))
+    x = hadamard(torch.randn(m, k, generator=rng(2000 + m)).bfloat16().cuda())
+    act = rt.quantize_activation_cuda(x, q=14, betas=ACT_BETAS)
+    a = rt.linear_packed_w4a4_fp32(act, packed).cpu().numpy()
+    b = rt.linear_packed_w4a4_fp32(act, resident).cpu().numpy()
+    assert rt.read_status() == 0
+    assert rel_fro(b, a) <= 1e-5 and max_abs(b, a) <= 1e-3, (rel_fro(b, a), max_abs(b, a))
+    # against a float32 product of the same BF16 operands
+    expected = (act.decoded.float() @ resident.decoded.float().T).cpu().numpy()
+    assert rel_fro(b, expected) <= REL_FRO_TOL and max_abs(b, expected) <= MAX_ABS_TOL
