@@ -308,6 +308,13 @@ def run_gpu(args) -> None:
                 dec["ms_per_step"] = round(float(t.item()), 3)
                 dec["decode_tok_s"] = round(world * dec["requests"] / (dec["ms_per_step"] * 1e-3), 1)
                 dec["replicas"] = world
+                resident = dec.get("resident_decoded_weights", {})
+                for leg in (resident, resident.get("with_kv_lattice_shadow", {})):  # the opt-in legs the same way
+                    if "ms_per_step" in leg:
+                        t = torch.tensor([leg["ms_per_step"]], device=device)
+                        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                        leg["ms_per_step"] = round(float(t.item()), 3)
+                        leg["decode_tok_s"] = round(world * dec["requests"] / (leg["ms_per_step"] * 1e-3), 1)
             extras["decode"] = dec
         except Exception as error:
             extras["decode"] = {"error": f"{type(error).__name__}: {error}"[:300]}
