@@ -636,10 +636,7 @@ def decode_workload(torch, device, *, requests: int = 64, new_tokens: int = 256,
         mix.append({"kernel": "all kernels", "us_per_step": round(whole, 1)})
     # opt-in mode: the decoded BF16 weights stay in HBM (4x the packed bytes), no per-call weight decode;
     # same graph-decode loop, 64 more steps on the contexts reached by then
-    from nestquant_aiinfra_b200.fused_linear import keep_decoded_weights_
-
-    added = keep_decoded_weights_(model)
-    runner.capture_decode_graph()
+    added = runner.keep_decoded_weights()  # captures the decode graph again
     for _ in range(3):
         runner.decode()
     torch.cuda.synchronize(device)
@@ -657,8 +654,7 @@ def decode_workload(torch, device, *, requests: int = 64, new_tokens: int = 256,
                 "decode_tok_s": round(requests * resident_steps / (resident_ms * 1e-3), 1)}
     # second opt-in on top: the decoded lattice coordinates of every KV page kept beside its codes (8 bits per
     # entry), attention reads them instead of searching E8 per block; outputs are bit-identical
-    kv_added = cache.enable_lattice_shadow()
-    runner.capture_decode_graph()
+    kv_added = runner.enable_lattice_shadow()  # captures the decode graph again
     for _ in range(3):
         runner.decode()
     torch.cuda.synchronize(device)

@@ -17,7 +17,7 @@ from torch import nn
 
 from .formats import ACTIVATION_BETAS, KEY_BETAS, VALUE_BETAS, WEIGHT_BETAS, tensor_dither_seed
 from .fused_linear import (FusedNQRTLinear, SharedHadamardCache, SharedPackedActivationCache,
-                           SharedProjectionGroup)
+                           SharedProjectionGroup, keep_decoded_weights_)
 from .hf_backend import BatchedNQKVLlamaCache, install_batched_nqkv_llama_backend
 from .norm import fuse_rmsnorm_
 from .rope import fused_rope_scope
@@ -185,6 +185,22 @@ class BatchedNQKVLlamaRunner:
             return self.decode_eager()
         self.graph.replay()
         return self.next_tokens
+
+    # Opt-in modes that spend spare HBM on decoded copies (off by default; the packed data stay the record).
+    # Both change which kernels a step launches, so a captured graph is captured again.
+    def keep_decoded_weights(self) -> int:
+        """Keep the decoded BF16 weights of every packed projection resident; returns the bytes added."""
+        added = keep_decoded_weights_(self.model)
+        if self.graph is not None:
+            self.capture_decode_graph()
+        return added
+
+    def enable_lattice_shadow(self) -> int:
+        """Keep the decoded lattice coordinates of the KV pages beside their codes; returns the bytes added."""
+        added = self.cache.enable_lattice_shadow()
+        if self.graph is not None:
+            self.capture_decode_graph()
+        return added
 
     # the warm-up and the capture run a real step; put the cache back afterwards
     def _snapshot(self):

@@ -175,6 +175,46 @@ def test_graph_decode_equals_eager_decode():
     assert eager_state[0][0].tolist() == [27, 36, 53, 70]
 
 
+def test_opt_in_decoded_copies_keep_the_generated_tokens():
+    """Lattice pages change no bit of a step; resident weights only the order of FP32 sums in the projections.
+
+    Both are switched on in the middle of a graph decode (the runner captures its graph again), across page
+    boundaries, and compared with an untouched run of the same model.
+    """
+    prompts = _prompts([7, 16, 33, 50])
+    runs = []
+    for mode in ("packed", "lattice", "resident"):
+        model, cache, runner = _build(seed=9)
+        first = runner.prefill_slots([0, 1, 2, 3], prompts)
+        runner.capture_decode_graph()
+        tokens = [first.clone()]
+        for step in range(24):
+            if step == 6 and mode == "lattice":
+                assert runner.enable_lattice_shadow() > 0
+            if step == 6 and mode == "resident":
+                assert runner.keep_decoded_weights() > 0
+            tokens.append(runner.decode().clone())
+        torch.cuda.synchronize()
+        pools = [(c.pool.key_codes.clone(), c.pool.value_codes.clone(), c.hot_keys.clone()) for c in cache.layer_caches]
+        runs.append((torch.stack(tokens), pools, cache))
+    (packed_tokens, packed_pools, _), (lattice_tokens, lattice_pools, lattice_cache), (resident_tokens, _, _) = runs
+    assert torch.equal(lattice_tokens, packed_tokens)
+    for a, b in zip(packed_pools, lattice_pools):
+        assert all(torch.equal(x, y) for x, y in zip(a, b))
+    # the shadow of every page written before and after the switch is the decode of its codes
+    for layer in lattice_cache.layer_caches:
+        pool = layer.pool
+        fresh = torch.zeros_like(pool.key_lattice)
+        saved, pool.key_lattice = pool.key_lattice, fresh
+        pool.expand_pages(torch.arange(pool.capacity, dtype=torch.int32))
+        assert torch.equal(fresh, saved)
+        pool.key_lattice = saved
+    # resident weights: same operands, sums in another order; greedy tokens of a random-init model may flip on
+    # near-ties, so compare the first steps after the switch only through agreement of most rows
+    agree = (resident_tokens == packed_tokens).float().mean().item()
+    assert agree > 0.9, agree
+
+
 def test_released_slot_is_reused_and_inactive_rows_do_not_move():
     model, cache, runner = _build(seed=1)
     runner.prefill_slots([1], _prompts([9]))
