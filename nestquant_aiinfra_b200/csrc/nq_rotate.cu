@@ -18,7 +18,7 @@ namespace {
 // The butterfly passes live in nq_rotate_core.cuh; the last pass here applies the 1/sqrt(n)
 // division and stores to global memory in the tensor dtype.
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 nq_hadamard_kernel(const T* __restrict__ x, T* __restrict__ out, int64_t rows, int n, int rows_per_cta,
                    float root, float inv_root) {
     extern __shared__ __align__(16) float buf[];
@@ -26,7 +26,7 @@ nq_hadamard_kernel(const T* __restrict__ x, T* __restrict__ out, int64_t rows, i
     const int nrows = (int)min((int64_t)rows_per_cta, rows - row0);
     const int total = nrows * n;           // elements of this CTA (rows are independent, n >= 8)
     nq_fwht_rows_to_smem<T>(x + row0 * n, buf, total, n);
-    for (int g = threadIdx.x; g < (total >> 3); g += 256) {
+    for (int g = threadIdx.x; g < (total >> 3); g += blockDim.x) {
         const float4 lo = reinterpret_cast<const float4*>(buf + g * 8)[0];
         const float4 hi = reinterpret_cast<const float4*>(buf + g * 8)[1];
         float v[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
@@ -50,7 +50,11 @@ int launch_hadamard(const void* x, void* out, int64_t rows, int64_t n, cudaStrea
     }
     const float root = (float)sqrt((double)n);
     const int64_t grid = (rows + rpc - 1) / rpc;
-    kernel<<<(unsigned)grid, 256, smem, stream>>>(reinterpret_cast<const T*>(x), reinterpret_cast<T*>(out), rows,
+    // one group of 8 elements per thread and pass for long rows (a row of 8192 is a chain of five passes:
+    // with 256 threads each pass took four rounds)
+    const int64_t groups = (int64_t)rpc * n / 8;
+    const unsigned threads = groups >= 1024 ? 1024u : (groups >= 512 ? 512u : 256u);
+    kernel<<<(unsigned)grid, threads, smem, stream>>>(reinterpret_cast<const T*>(x), reinterpret_cast<T*>(out), rows,
                                                   (int)n, rpc, root, 1.0f / root);
     NQ_CHECK_LAUNCH("nq_hadamard");
     return NQ_OK;
