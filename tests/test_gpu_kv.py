@@ -316,3 +316,35 @@ def test_lattice_shadow_attention_is_bit_identical(oracle):
     pool.key_lattice[1].zero_()
     pool.expand_pages(torch.tensor([1, -1], dtype=torch.int32))
     assert torch.equal(attend(), with_shadow)
+
+
+@pytest.mark.parametrize("heads,dim,q_heads", [(8, 64, 32), (2, 128, 16), (4, 32, 4), (1, 256, 2)])
+def test_lattice_shadow_prefill_and_decode_shapes(rt, heads, dim, q_heads):
+    """Every head_dim / GQA instantiation of the lattice-page kernel, causal chunk prefill and long decode:
+    bit-identical to the packed kernel on a pool filled by the eager page writer (random physical page ids)."""
+    lengths = [40, 16, 75, 5, 300]
+    cache = make_cache(rt, slots=5, max_pages=20, heads=heads, dim=dim)
+    fill_cache(rt, cache, lengths, seed=70 + dim)
+    slot_ids = torch.arange(5, dtype=torch.int32, device="cuda")
+    active = torch.ones(5, dtype=torch.bool, device="cuda")
+    q_lens = torch.tensor([9, 16, 64, 5, 33], dtype=torch.int32, device="cuda")
+    q_dec = torch.randn(5, q_heads, dim, generator=rng(71)).bfloat16().cuda()
+    q_pre = torch.randn(5, 64, q_heads, dim, generator=rng(72)).bfloat16().cuda()
+    scale = dim ** -0.5
+
+    def run():
+        ws1 = rt.BatchedNQKVAttentionWorkspace.create(cache, batch_size=5, query_heads=q_heads,
+                                                      output_dtype=torch.float32)
+        dec = rt.nqkv_decode_attention_batched_k1(q_dec, cache, slot_ids=slot_ids, active_mask=active,
+                                                  scale=scale, workspace=ws1).clone()
+        ws2 = rt.BatchedNQKVAttentionWorkspace.create(cache, batch_size=5, query_heads=q_heads,
+                                                      output_dtype=torch.float32, query_tokens=64)
+        pre = rt.nqkv_prefill_attention(q_pre, cache, slot_ids=slot_ids, query_lengths=q_lens,
+                                        scale=scale, workspace=ws2).clone()
+        return dec, pre
+
+    packed_dec, packed_pre = run()
+    assert cache.pool.enable_lattice_shadow() > 0
+    shadow_dec, shadow_pre = run()
+    assert torch.equal(shadow_dec, packed_dec) and torch.equal(shadow_pre, packed_pre)
+    assert bool(packed_dec.abs().sum() > 0) and bool(packed_pre.abs().sum() > 0)
