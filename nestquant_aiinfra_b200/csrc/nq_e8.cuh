@@ -406,7 +406,7 @@ NQ_HD void nq_decode_weight_block(uint32_t word, uint32_t counter_base, float r[
     }
     nq_e8_nearest_guarded(s, n);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) r[j] = nq_sub(t[j], nq_mul(14.0f, n[j]));
+    for (int j = 0; j < 8; ++j) r[j] = nq_fma(-14.0f, n[j], t[j]);  // 14*n is exact, so one rounding either way
 }
 
 // Position of a lattice point lam relative to the scaled Voronoi cell 14*V(E8):

@@ -53,6 +53,12 @@ nq_encode_rows_kernel(const T* __restrict__ x, int64_t rows, int k, int64_t row_
 // Decode of an undithered packed stream (activations / KV pages): one thread
 // per block, exact reference arithmetic.
 // ---------------------------------------------------------------------------
+// Row of flat block g: a 32-bit division whenever the stream has fewer than 2^31 blocks (every real
+// tensor), the 64-bit one costs several times as many instructions per thread.
+__device__ __forceinline__ int64_t nq_row_of_block(int64_t g, int64_t blocks, int bpr) {
+    return blocks <= 0x7fffffff ? (int64_t)((uint32_t)g / (uint32_t)bpr) : g / bpr;
+}
+
 template <bool OUT_BF16>
 __global__ void __launch_bounds__(256)
 nq_a4_decode_kernel(const uint32_t* __restrict__ codes, const uint8_t* __restrict__ beta_ids,
@@ -60,11 +66,11 @@ nq_a4_decode_kernel(const uint32_t* __restrict__ codes, const uint8_t* __restric
                     int64_t blocks, int bpr, float sqrt_k, void* __restrict__ out) {
     const int64_t g = (int64_t)blockIdx.x * 256 + threadIdx.x;
     if (g >= blocks) return;
-    const int64_t row = g / bpr;
+    const int64_t row = nq_row_of_block(g, blocks, bpr);
     float r[8];
     nq_decode_codeword_undithered(__ldg(codes + g), r);
     const float beta = __ldg(beta_table + nq_beta_id(beta_ids, g));
-    const float ds = nq_div(__ldg(norms + row), sqrt_k);
+    const float ds = nq_div_by(__ldg(norms + row), sqrt_k, nq_rcp(sqrt_k));  // = IEEE division, fewer instructions
 #pragma unroll
     for (int j = 0; j < 8; ++j) r[j] = nq_mul(nq_mul(r[j], beta), ds);
     if (OUT_BF16) {
@@ -85,11 +91,11 @@ nq_w4_decode_kernel(const uint32_t* __restrict__ codes, const uint8_t* __restric
                     uint4* __restrict__ out) {
     const int64_t g = (int64_t)blockIdx.x * 256 + threadIdx.x;
     if (g >= blocks) return;
-    const int64_t row = g / bpr;
+    const int64_t row = nq_row_of_block(g, blocks, bpr);
     float r[8];
     nq_decode_weight_block(__ldg(codes + g), nq_segment_base(seg, (int)row) + (uint32_t)g * 8u, r);
     const float beta = __ldg(beta_table + nq_beta_id(beta_ids, g));
-    const float ds = nq_div(__ldg(norms + row), sqrt_k);
+    const float ds = nq_div_by(__ldg(norms + row), sqrt_k, nq_rcp(sqrt_k));  // = IEEE division, fewer instructions
 #pragma unroll
     for (int j = 0; j < 8; ++j) r[j] = nq_mul(nq_mul(r[j], beta), ds);
     out[g] = nq_pack_bf16x8(r);
