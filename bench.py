@@ -247,16 +247,42 @@ def run_gpu(args) -> None:
     for _ in range(max(args.warmup, 3)):
         step(False)
     barrier()
+    # One sweep step is 112 launches, most of them a few microseconds long: issued call by call the host is the
+    # slower side on the small cells (and more so with eight ranks sharing one host), so the step is captured
+    # once as a CUDA graph and the timed region replays it, as the decode engine does with its step.
+    graph, per_step = None, None
+    try:
+        counted = rt.launch_count()
+        captured = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(captured):
+            step(False)
+        per_step = rt.launch_count() - counted
+        captured.replay()
+        torch.cuda.synchronize(device)
+        graph = captured
+    except Exception as error:  # keep measuring call by call if the capture is refused
+        print(f"bench: sweep step not captured ({type(error).__name__}: {error}); timing eager calls", file=sys.stderr)
+        torch.cuda.synchronize(device)
     launches0 = rt.launch_count()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     start.record(stream)
     for _ in range(args.steps):
-        step(True)
+        if graph is not None:
+            graph.replay()
+        else:
+            step(True)
     stop.record(stream)
     barrier()
-    launches = rt.launch_count() - launches0
+    launches = per_step * args.steps if graph is not None else rt.launch_count() - launches0
     clocks = sampler.stop()
+    if graph is not None:
+        # the encoder's own time: one more step, call by call, with events around every encode launch; the
+        # device first spins for ~10 ms so that the host queues the whole step ahead of it and the events
+        # bracket device time only, not the gaps between two calls of the host
+        torch.cuda._sleep(20_000_000)
+        step(True)
+        torch.cuda.synchronize(device)
     elapsed_ms = start.elapsed_time(stop)
     if rt.read_status(device) != 0:
         raise SystemExit("device status word is non-zero: a bounded wait in the GEMM gave up")
@@ -272,9 +298,10 @@ def run_gpu(args) -> None:
     enc_bytes = sum(m * k * 2 + m * (17 * k // 32 + 4) for m, k, _, _ in encode_events)
     enc_ms = sum(e0.elapsed_time(e1) for _, _, e0, e1 in encode_events)
     enc_gbs = enc_bytes / (enc_ms * 1e-3) / 1e9
+    enc_steps = 1 if graph is not None else args.steps  # steps the encode events cover
     roofline = {"kernel": "nq_encode_rows_kernel", "bound": "hbm", "achieved": enc_gbs, "peak": pk["hbm_gbs"],
                 "unit": "GB/s", "frac": enc_gbs / pk["hbm_gbs"], "peak_source": pk["source"],
-                "share_of_step": enc_ms / elapsed_ms, "launches": len(encode_events),
+                "share_of_step": (enc_ms / enc_steps) / ms_per_step, "launches": len(encode_events),
                 # DRAM bytes of the largest encode launch (8192 x 8192 BF16) from the ncu capture summarised in
                 # profiles/nq_encode_rows_kernel_8192x8192_bf16.md; its algorithmic bytes are 2MK + M(17K/32+4),
                 # the rest is the optional BF16 reconstruction the projection consumes.
@@ -330,7 +357,8 @@ def run_gpu(args) -> None:
             "config": {"workload": "w4a4_projection_sweep", "shapes": [list(s) for s in SHAPES],
                        "tokens": list(TOKENS), "q": 14, "betas": 4, "encode": "on the fly every call",
                        "l2": "one step touches > 1 GB of distinct operands, so inputs of a cell are evicted from the "
-                             "126 MB L2 before the cell repeats", "parallelism": f"replicas{world}"},
+                             "126 MB L2 before the cell repeats", "parallelism": f"replicas{world}",
+                       "launch": "CUDA graph of one step, replayed" if graph is not None else "call by call"},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],
                     "ms_per_step": e2e["ms"]},
