@@ -5,9 +5,12 @@
  *   - plain pointers and sizes, no framework types; every pointer is a DEVICE
  *     pointer unless its name ends in _host;
  *   - the caller owns every buffer, passes the CUDA stream explicitly and
- *     supplies workspaces; nothing here allocates device memory, synchronises
- *     the host, or keeps global state, so every call can be captured in a
- *     CUDA graph;
+ *     supplies workspaces; nothing here allocates device memory or synchronises
+ *     the host (nq_w4a4_status excepted).  Host-side state is limited to
+ *     per-device look-ups made on first use (SM count, the opt-in of a kernel
+ *     to large shared memory, the driver entry point that builds tensor maps)
+ *     and, for nq_w4a4_gemv_static only, the address of its built-in scratch;
+ *     launches go to the CURRENT device, which must be the stream's device;
  *   - return value 0 = success, negative = argument error (NQ_ERR_*), positive
  *     = cudaError_t of the failed launch; nq_last_error() describes the last
  *     failure of the calling thread;
@@ -149,8 +152,9 @@ int nq_w4a4_gemm_grouped(const uint8_t* act_codes, const uint8_t* act_beta_ids, 
  * partial sums, arrival counters) is a fixed array inside the library's device image, about
  * 8.6 MiB held by every GPU that loads the library until the process exits.  Shapes beyond
  * the limits below are rejected with NQ_ERR_ARG.  The first call on a device resolves the
- * array's address (do it during set-up, before any stream capture).  All calls share the one
- * array: calls that overlap on the GPU race on it.  Allocates nothing.
+ * array's address for the CURRENT device, which must be the device of `stream` (do it during
+ * set-up, before any stream capture).  All calls share the one array: calls that overlap on the
+ * GPU race on it.  Allocates nothing.
  * This entry point has no counterpart in the reference. */
 #define NQ_STATIC_MAX_M 16
 #define NQ_STATIC_MAX_N 8192
@@ -224,8 +228,10 @@ int nq_kv_append(const void* key, const void* value, int kv_dtype, int batch, in
 
 /* For every slot with boundary_mask[s] && hot_lengths[s] == P: encode its hot page, store the six
  * payload rows at pool[target_page_ids[s]], append the page id to the page table, set
- * last_page_lens = P and hot_lengths = 0 (publish only while page_counts < max_pages).  Only the
- * selected slots are encoded.  Payload bytes equal PackedNQKVPage.from_tensors
+ * last_page_lens = P and hot_lengths = 0.  A slot whose page table is full (page_counts ==
+ * max_pages) or whose target id lies outside [0, pool_capacity) is left untouched: nothing is
+ * written to the pool and nothing is published, its hot tail stays full.  Only the selected slots
+ * are encoded.  Payload bytes equal PackedNQKVPage.from_tensors
  * (core/kv_format.py:71-131).  Replaces launch_pack_full_hot_pages_graph_safe
  * (runtime/nqkv_graph_pack.py:76-135: encode of all slots + 6 copies + publish). */
 int nq_kv_pack_publish(const void* hot_keys, const void* hot_values, int kv_dtype, int32_t* hot_lengths,
@@ -252,6 +258,7 @@ int nq_kv_quantize_page(const void* key, const void* value, int kv_dtype, int va
  *          the first  total - q_lens[b] + i + 1  tokens (causal), reading pages directly
  *          (semantic of NQKVLlamaCache.prefill, runtime/nqkv_hf_backend.py:127-150).
  * K/V of cold pages are the float32 reconstruction; softmax and accumulation in float32.
+ * The hot tail (hot_keys / hot_values) is read as BF16 whatever dtype the pages were packed from.
  * workspace: nq_kv_attention_workspace_bytes(...) bytes (split partials). */
 size_t nq_kv_attention_workspace_bytes(int batch, int q_tokens, int q_heads, int kv_heads, int dim, int max_pages);
 int nq_kv_attention(const void* query, int q_dtype, int batch, int q_tokens, int q_heads,

@@ -22,6 +22,7 @@ SOURCES = ("nq_encode.cu", "nq_gemv.cu", "nq_gemv_bf16.cu", "nq_gemv_static.cu",
 
 NQ_F32, NQ_BF16, NQ_F16 = 0, 1, 2
 WS_COUNTER_BYTES = 65536
+WS_STATUS_OFFSET = 65532  # NQ_WS_STATUS_OFFSET of the header
 
 _LIB: ctypes.CDLL | None = None
 

@@ -35,6 +35,28 @@ void nq_count_launch();  // bumps the process-wide kernel-launch counter (nq_lau
 
 static inline bool nq_aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// Per-device facts, looked up once per device (a process may drive several GPUs): the current
+// device's index (or -1) and its SM count.  The tables only ever receive the same value for the same
+// slot, so unsynchronised writers are harmless.
+#define NQ_MAX_DEVICES 64
+inline int nq_current_device() {
+    int device = -1;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= NQ_MAX_DEVICES) return -1;
+    return device;
+}
+inline int nq_sm_count() {
+    static int counts[NQ_MAX_DEVICES] = {0};
+    const int device = nq_current_device();
+    if (device < 0) return 148;
+    if (counts[device] == 0) {
+        int count = 0;
+        if (cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || count <= 0)
+            count = 148;
+        counts[device] = count;
+    }
+    return counts[device];
+}
+
 // ---- device helpers --------------------------------------------------------
 #if defined(__CUDACC__)
 

@@ -58,7 +58,8 @@ struct NqEncodePlan {
 inline NqEncodePlan nq_encode_plan(int64_t rows, int k, bool dither) {
     NqEncodePlan plan;
     const int bpr = k / 8;
-    const int slots = 148 * 5;  // resident CTAs of the device this library is built for
+    const int sms = nq_sm_count();
+    const int slots = sms * 5;  // resident CTAs of the current device
     plan.rpc = nq_encode_rows_per_cta(k);
     plan.four_lanes = !dither && rows * bpr <= (int64_t)slots * (NQ_ENC_THREADS / 4);
     if (plan.four_lanes) {
@@ -76,8 +77,8 @@ inline NqEncodePlan nq_encode_plan(int64_t rows, int k, bool dither) {
     plan.splits = 1;
     if (splittable && plan.four_lanes) {
         plan.splits = bpr / 32;
-    } else if (splittable && bpr >= NQ_ENC_THREADS && grid < 148) {
-        plan.splits = (int)((2 * 148 + grid - 1) / grid);
+    } else if (splittable && bpr >= NQ_ENC_THREADS && grid < sms) {
+        plan.splits = (int)((2 * sms + grid - 1) / grid);
         if (plan.splits > bpr / 32) plan.splits = bpr / 32;
     }
     if (plan.splits < 1) plan.splits = 1;

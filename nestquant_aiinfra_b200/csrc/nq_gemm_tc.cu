@@ -281,16 +281,7 @@ int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t k, int bo
     return NQ_OK;
 }
 
-int sm_count() {
-    static int count = 0;
-    if (count == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, dev);
-        if (count <= 0) count = 148;
-    }
-    return count;
-}
+int sm_count() { return nq_sm_count(); }
 
 }  // namespace
 
@@ -340,15 +331,17 @@ int nq_launch_tc_gemm(const void* a_dec, const void* w_dec, int64_t m, int64_t n
     rc = make_map(&map_a, a_dec, m, k, p.tile_t);
     if (rc) return rc;
     const size_t smem = (size_t)stages * stage_bytes + sizeof(TcBarriers) + 1024;
-    static bool configured = false;
-    if (!configured) {
+    // the opt-in to more than 48 KB of dynamic shared memory is a per-device attribute of the kernel
+    static bool configured[NQ_MAX_DEVICES] = {false};
+    const int device = nq_current_device();
+    if (device < 0 || !configured[device]) {
         cudaError_t e = cudaFuncSetAttribute(nq_w4a4_tc_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              227 * 1024);
         if (e != cudaSuccess) {
             nq_set_error("nq_w4a4_gemm: cannot reserve shared memory: %s", cudaGetErrorString(e));
             return (int)e;
         }
-        configured = true;
+        if (device >= 0) configured[device] = true;
     }
     const int total = p.n_tiles * p.t_tiles * p.splits;
     const int grid = total < sm_count() ? total : sm_count();

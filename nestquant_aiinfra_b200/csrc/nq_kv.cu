@@ -99,6 +99,17 @@ struct PackParams {
     int8_t *key_lattice, *value_lattice;  // optional decoded shadow of the pool, [capacity, P*H*D]
 };
 
+// A slot's hot page is packed and published only when all of this holds: the slot is selected, its hot tail
+// is full, its page table has room, and the target id lies inside the pool.  The three kernels of a
+// pack-and-publish call use this one predicate, so a page is never written without being published
+// (a slot whose table is full must not touch the pool: with caller-computed ids its "next" id may
+// belong to another sequence) and never published without having been written.
+__device__ __forceinline__ bool nq_pack_selected(const PackParams& p, int slot) {
+    const int page_id = p.target_page_ids[slot];
+    return p.boundary_mask[slot] != 0 && p.hot_lengths[slot] == p.page_size && p.page_counts[slot] < p.max_pages &&
+           page_id >= 0 && page_id < p.pool_capacity;
+}
+
 // Decoded shadow of a page ("lattice page"): every E8 block of the code stream decoded once to its eight
 // minimum-energy coordinates, stored doubled as int8 (half-integers in [-14, 14] -> integers in [-28, 28]).
 // It is a pure function of the code stream, kept beside it by callers that trade HBM for attention time.
@@ -117,9 +128,8 @@ __device__ __forceinline__ void nq_expand_block(const uint32_t* codes, int8_t* l
 // Shadow of the pages that nq_kv_pack_pages_kernel has just written (same predicate, before the publish).
 __global__ void __launch_bounds__(256) nq_kv_expand_packed_kernel(const PackParams p) {
     const int slot = blockIdx.x;
-    const bool full = p.boundary_mask[slot] != 0 && p.hot_lengths[slot] == p.page_size;
+    if (!nq_pack_selected(p, slot)) return;
     const int page_id = p.target_page_ids[slot];
-    if (!full || page_id < 0 || page_id >= p.pool_capacity) return;
     const int blocks = p.page_size * p.heads * (p.dim >> 3);
     const bool is_value = blockIdx.y != 0;
     const uint32_t* codes = reinterpret_cast<const uint32_t*>(is_value ? p.value_codes : p.key_codes) +
@@ -144,9 +154,8 @@ template <typename T>
 __global__ void __launch_bounds__(NQ_ENC_THREADS, 5) nq_kv_pack_pages_kernel(const PackParams p) {
     extern __shared__ __align__(16) float smem[];
     const int slot = blockIdx.x;
-    const bool full = p.boundary_mask[slot] != 0 && p.hot_lengths[slot] == p.page_size;
+    if (!nq_pack_selected(p, slot)) return;  // CTA-uniform
     const int page_id = p.target_page_ids[slot];
-    if (!full || page_id < 0 || page_id >= p.pool_capacity) return;  // CTA-uniform
     const int is_value = blockIdx.y / p.ctas_per_stream;
     const int chunk = blockIdx.y - is_value * p.ctas_per_stream;
     const int rows = p.page_size * p.heads, rpc = nq_encode_rows_per_cta(p.dim), bpr = p.dim >> 3;
@@ -166,9 +175,8 @@ __global__ void __launch_bounds__(NQ_ENC_THREADS, 5) nq_kv_pack_pages_kernel(con
 __global__ void __launch_bounds__(256) nq_kv_publish_kernel(const PackParams p) {
     const int slot = blockIdx.x * blockDim.x + threadIdx.x;
     if (slot >= p.max_sequences) return;
+    if (!nq_pack_selected(p, slot)) return;
     const int count = p.page_counts[slot];
-    const bool full = p.boundary_mask[slot] != 0 && p.hot_lengths_rw[slot] == p.page_size && count < p.max_pages;
-    if (!full) return;
     p.page_indices[(int64_t)slot * p.max_pages + count] = p.target_page_ids[slot];
     p.page_counts[slot] = count + 1;
     p.last_page_lens[slot] = p.page_size;

@@ -101,7 +101,7 @@ class SharedPackedActivationCache:
                 self.clear()
             return packed, False
         packed = quantize_activation_cuda(inputs, q=q, betas=betas, beta_table=beta_table,
-                                          hadamard_block=hadamard_block)
+                                          hadamard_block=hadamard_block, keep_decoded=True)
         self._input, self._packed = inputs, packed
         self._remaining = self.uses_per_input - 1
         self.misses += 1
@@ -323,7 +323,7 @@ class FusedNQRTLinear(nn.Module):
             beta_table = beta_table.to(inputs.device)
         if self.packed_activation_cache is None:
             packed = quantize_activation_cuda(compute_inputs, q=self.activation_q, betas=self.activation_betas,
-                                              beta_table=beta_table, hadamard_block=block)
+                                              beta_table=beta_table, hadamard_block=block, keep_decoded=True)
             encoded = True
         else:
             packed, encoded = self.packed_activation_cache.encode(

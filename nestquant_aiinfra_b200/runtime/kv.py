@@ -360,6 +360,8 @@ class BatchedNQKVAttentionWorkspace:
     def create(cls, cache: NQKVHotColdCache, *, batch_size: int, query_heads: int,
                output_dtype: torch.dtype = torch.bfloat16, query_tokens: int = 1) -> "BatchedNQKVAttentionWorkspace":
         pool = cache.pool
+        if output_dtype not in (torch.bfloat16, torch.float32):
+            raise ValueError("output_dtype must be bfloat16 or float32")
         nbytes = _lib.lib().nq_kv_attention_workspace_bytes(
             _INT(batch_size), _INT(query_tokens), _INT(query_heads), _INT(pool.num_kv_heads), _INT(pool.head_dim),
             _INT(cache.max_pages_per_sequence))
@@ -376,6 +378,13 @@ def _attention(query4: torch.Tensor, cache: NQKVHotColdCache, slot_ids: torch.Te
                workspace: BatchedNQKVAttentionWorkspace, what: str) -> None:
     pool = cache.pool
     batch, tokens, heads, dim = query4.shape
+    if workspace.output.dtype not in (torch.bfloat16, torch.float32):
+        raise ValueError("the attention output buffer must be bfloat16 or float32")
+    if (workspace.batch_size, workspace.query_tokens, workspace.query_heads, workspace.head_dim,
+            workspace.max_pages) != (batch, tokens, heads, dim, cache.max_pages_per_sequence):
+        raise ValueError("attention workspace configuration does not match query and cache")
+    if workspace.output.numel() != batch * tokens * heads * dim or workspace.output.device != pool.device:
+        raise ValueError("attention output buffer does not match the query")
     out_tag = _lib.NQ_BF16 if workspace.output.dtype == torch.bfloat16 else _lib.NQ_F32
     args = [
         _ptr(query4), _DTYPE_TAG[query4.dtype], _INT(batch), _INT(tokens), _INT(heads), _ptr(slot_ids),
@@ -394,11 +403,18 @@ def _attention(query4: torch.Tensor, cache: NQKVHotColdCache, slot_ids: torch.Te
     _lib.check(status, what)
 
 
+def _default_output_dtype(query: torch.Tensor) -> torch.dtype:
+    """Output dtype of a workspace created on the fly: the kernel writes bfloat16 or float32 only."""
+    return torch.bfloat16 if query.dtype == torch.bfloat16 else torch.float32
+
+
 def _validate_query(query: torch.Tensor, cache: NQKVHotColdCache, slot_ids: torch.Tensor, ndim: int) -> None:
     pool = cache.pool
     if not isinstance(query, torch.Tensor) or query.ndim != ndim:
         raise ValueError("query must have shape [batch, query_heads, head_dim]" if ndim == 3 else
                          "query must have shape [batch, tokens, query_heads, head_dim]")
+    if query.dtype not in _DTYPE_TAG:
+        raise ValueError("query must be float16, bfloat16 or float32")
     if query.device != pool.device or query.shape[-1] != pool.head_dim:
         raise ValueError("query must match the cache CUDA device and head_dim")
     if query.shape[-2] < 1 or query.shape[-2] % pool.num_kv_heads:
@@ -438,7 +454,7 @@ def nqkv_decode_attention_batched_k1(query: torch.Tensor, cache: NQKVHotColdCach
     batch, heads, _ = query.shape
     if workspace is None:
         workspace = BatchedNQKVAttentionWorkspace.create(cache, batch_size=batch, query_heads=heads,
-                                                         output_dtype=query.dtype)
+                                                         output_dtype=_default_output_dtype(query))
     if (workspace.batch_size, workspace.query_tokens, workspace.query_heads, workspace.max_pages) != \
             (batch, 1, heads, cache.max_pages_per_sequence):
         raise ValueError("batched workspace configuration does not match query and cache")
@@ -461,7 +477,8 @@ def nqkv_prefill_attention(query: torch.Tensor, cache: NQKVHotColdCache, *, slot
     batch, tokens, heads, _ = query.shape
     if workspace is None:
         workspace = BatchedNQKVAttentionWorkspace.create(cache, batch_size=batch, query_heads=heads,
-                                                         output_dtype=query.dtype, query_tokens=tokens)
+                                                         output_dtype=_default_output_dtype(query),
+                                                         query_tokens=tokens)
     attention_scale = 1.0 / math.sqrt(cache.pool.head_dim) if scale is None else float(scale)
     _attention(query.contiguous(), cache, slot_ids, None, query_lengths, attention_scale, workspace,
                "nqkv_prefill_attention")
@@ -480,33 +497,3 @@ def cache_arrays(cache: NQKVHotColdCache) -> dict:
         "key_beta_table": pool.beta_table.cpu().numpy(), "value_beta_table": pool.value_beta_table.cpu().numpy(),
         "hot_keys": cache.hot_keys.float().cpu().numpy(), "hot_values": cache.hot_values.float().cpu().numpy(),
     }
-
-
-def smoke_check(oracle) -> None:
-    """Tiny KV round trip on cuda:0 against the CPU checker (called by the smoke entry point)."""
-    import numpy as np
-
-    from ..formats import KEY_BETAS, VALUE_BETAS
-
-    pool = NQKVPagePool(capacity=8, page_size=16, num_kv_heads=2, head_dim=64, key_betas=KEY_BETAS,
-                        value_betas=VALUE_BETAS, device="cuda:0")
-    cache = NQKVHotColdCache(pool, max_sequences=2, max_pages_per_sequence=4)
-    cache.register(0)
-    gen = torch.Generator().manual_seed(7)
-    slot_ids = torch.tensor([0], dtype=torch.int32, device=pool.device)
-    active = torch.tensor([True], device=pool.device)
-    for step in range(21):
-        k = torch.randn(1, 2, 64, generator=gen).bfloat16().to(pool.device)
-        v = torch.randn(1, 2, 64, generator=gen).bfloat16().to(pool.device)
-        _launch_append_hot_k1_graph_safe(k, v, cache, slot_ids=slot_ids, active_mask=active)
-        if step == 15:
-            cache.reserve_targets([0])
-            mask = torch.tensor([True, False], device=pool.device)
-            launch_pack_full_hot_pages_graph_safe(cache, boundary_mask=mask)
-    q = torch.randn(1, 4, 64, generator=gen).bfloat16().to(pool.device)
-    out = nqkv_decode_attention_batched_k1(q, cache, slot_ids=slot_ids, active_mask=active).float().cpu().numpy()
-    expected = oracle.attn_decode(q.float().cpu().numpy(), [0], [1], cache_arrays(cache), scale=0.125)
-    err = float(np.abs(out - expected).max())
-    assert int(cache.page_counts[0]) == 1 and int(cache.hot_lengths[0]) == 5, "page publish failed"
-    assert err <= 1e-2, f"paged attention differs from the checker: {err}"
-    print(f"smoke KV: 21 appends, 1 page packed, decode attention max_abs={err:.3e}")

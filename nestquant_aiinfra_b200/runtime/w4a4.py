@@ -184,7 +184,7 @@ def prefer_rotation_in_encoder(rows: int, feature_count: int) -> bool:
 
 def quantize_activation_cuda(
     inputs: torch.Tensor, *, q: int, betas: Sequence[float],
-    beta_table: torch.Tensor | None = None, keep_decoded: bool = True, hadamard_block: int | None = None,
+    beta_table: torch.Tensor | None = None, keep_decoded: bool = False, hadamard_block: int | None = None,
 ) -> PreparedNQA4Activation:
     """Encode floating activations into packed NQA4 payloads in one launch.
 
@@ -193,6 +193,10 @@ def quantize_activation_cuda(
     normalised Hadamard transform of that block size (the whole row when it equals the feature
     count) inside the same launch; the result equals ``quantize_activation_cuda(hadamard(inputs))``
     bit for bit (see ``can_rotate_in_encoder``).
+
+    ``keep_decoded=True`` also writes the BF16 reconstruction of the rows (``2 * M * K`` bytes) that a
+    projection called next would otherwise decode for itself; callers that only want the packed
+    streams (the KV page writers, a caller that stores the encoding) leave it off.
     """
     if not isinstance(inputs, torch.Tensor) or not inputs.is_floating_point():
         raise TypeError("inputs must be a floating-point tensor")
@@ -418,15 +422,29 @@ def group_prepared_linears(weights: Sequence[PreparedNQRTLinear]) -> tuple[Prepa
     return stacked, views
 
 
-def read_status(device: torch.device | str = "cuda") -> int:
-    """Device status word of the current stream's workspace (synchronises); 0 = ok."""
+def read_status(device: torch.device | str = "cuda", *, clear: bool = False) -> int:
+    """Device status of every projection workspace of ``device`` (synchronises the device); 0 = ok.
+
+    A bounded wait that gave up inside the tcgen05 kernel leaves its code in the status word of the
+    workspace that call used.  Eager calls and calls captured into CUDA graphs use different
+    workspaces (one per stream and mode), so the words of all of them are combined here: the first
+    non-zero code found is returned.  The words are sticky; ``clear=True`` zeroes them after reading.
+    """
     device = torch.device(device)
     if device.index is None:
         device = torch.device("cuda", torch.cuda.current_device())
-    workspace = workspace_for(device, 1)
-    value = ctypes.c_uint32(0)
-    _lib.check(_lib.lib().nq_w4a4_status(_ptr(workspace), ctypes.byref(value), _stream(device)), "read_status")
-    return int(value.value)
+    torch.cuda.synchronize(device)
+    found = 0
+    for (index, _stream_id, _capturing), workspace in list(_WORKSPACES.items()):
+        if index != device.index:
+            continue
+        value = ctypes.c_uint32(0)
+        _lib.check(_lib.lib().nq_w4a4_status(_ptr(workspace), ctypes.byref(value), _stream(device)), "read_status")
+        if value.value and not found:
+            found = int(value.value)
+        if clear and value.value:
+            workspace[_lib.WS_STATUS_OFFSET:_lib.WS_STATUS_OFFSET + 4].zero_()
+    return found
 
 
 def _check_types(activation, weight) -> None:
