@@ -14,8 +14,9 @@ FusedNQRTLinear plugin call with pinned host inputs and outputs (copies timed).
 With N > 1 GPUs (torchrun) every rank runs the same sweep on its own GPU: the
 projections are independent, so there is no data-path collective.
 
-`--impl reference` times the CPU checker (a C restatement of the reference's
-PyTorch-CPU path, all host threads) on a bounded sample of the same sweep.
+`--impl reference` times the reference's own PyTorch-CPU path (installed
+unmodified under oracle/_ref; the C restatement if it is not there) with all
+host threads on a bounded sample of every cell of the same sweep.
 """
 
 from __future__ import annotations
@@ -34,7 +35,6 @@ sys.path.insert(0, str(ROOT))
 
 SHAPES = (("q_o", 2048, 2048), ("k_v", 512, 2048), ("gate_up", 8192, 2048), ("down", 2048, 8192))
 TOKENS = (1, 8, 16, 64, 128, 512, 2048, 8192)
-CPU_SAMPLE_TOKENS = (1, 16, 128, 512)
 ACT_BETAS = tuple(v / 14 for v in (3.47, 4.74, 6.90, 18.11))
 W_BETAS = tuple(v / 14 for v in (4.0, 5.5, 7.0, 18.0))
 ENCODE_TRAFFIC_8192X8192 = 134_373_376 + 123_120_896  # dram__bytes_read.sum + dram__bytes_write.sum (ncu)
@@ -42,8 +42,8 @@ METRIC = "w4a4_e8_gemm_sweep_tflops"
 UNIT = "TFLOP/s"
 
 
-def sweep_flops(tokens=TOKENS) -> float:
-    return float(sum(2 * m * n * k for _, n, k in SHAPES for m in tokens))
+def sweep_flops() -> float:
+    return float(sum(2 * m * n * k for _, n, k in SHAPES for m in TOKENS))
 
 
 def peaks() -> dict:
@@ -114,67 +114,210 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-# --------------------------------------------------------------------------- CPU arm
-def cpu_sample_once(oracle, np, weights, activations) -> None:
-    """One pass of the bounded CPU sample: encode A, dequantise both operands, product."""
-    for (name, n, k), (wc, wb, wn, seed) in zip(SHAPES, weights):
-        w_deq = oracle.dequantize_rows(wc, wb, wn, W_BETAS, n, k, seed=seed)
-        for m in CPU_SAMPLE_TOKENS:
-            x = activations[(k, m)]
-            ac, ab, an = oracle.encode_packed(x, ACT_BETAS)
-            a_deq = oracle.dequantize_rows(ac, ab, an, ACT_BETAS, m, k)
-            oracle.gemm_f32(a_deq, w_deq)
+# --------------------------------------------------------------------------- CPU arms
+# Both CPU arms time every one of the sweep's 32 cells on a bounded sample and compose the time of the whole
+# sweep from it: the A4 encode and the dequantisation of its output cost the same per row, so they are
+# timed on the first CPU_ENCODE_ROWS rows of the cell and scaled to its M rows; the weight dequantisation is
+# timed on CPU_WEIGHT_ROWS rows and scaled to N; the float32 product runs at the cell's full size.
+CPU_ENCODE_ROWS = 32
+CPU_WEIGHT_ROWS = 256
 
 
-def cpu_setup():
-    import numpy as np
-
-    from oracle import nq_oracle as oracle
-
-    oracle.build()
-    rng = np.random.default_rng(1000)
-    weights, activations = [], {}
-    for i, (name, n, k) in enumerate(SHAPES):
-        w = oracle.hadamard((0.02 * rng.standard_normal((n, k))).astype(np.float32))
-        seed = 20261029 + i
-        wc, wb, wn = oracle.encode_packed(w, W_BETAS, seed=seed)
-        weights.append((wc, wb, wn, seed))
-        for m in CPU_SAMPLE_TOKENS:
-            if (k, m) not in activations:
-                x = oracle.round_bf16(rng.standard_normal((m, k)).astype(np.float32))
-                activations[(k, m)] = oracle.hadamard(x, round_bf16=True)
-    return oracle, np, weights, activations
+def sweep_config(world: int) -> dict:
+    """The workload description both arms print (identical objects, so the two lines can be compared)."""
+    return {"workload": "w4a4_projection_sweep", "shapes": [list(s) for s in SHAPES], "tokens": list(TOKENS),
+            "q": 14, "betas": 4, "encode": "on the fly every call", "parallelism": f"replicas{world}",
+            "l2": "one step touches > 1 GB of distinct operands, so inputs of a cell are evicted from the "
+                  "126 MB L2 before the cell repeats"}
 
 
-def cpu_baseline(repeats: int = 1, warmup: int = 0) -> dict:
-    oracle, np, weights, activations = cpu_setup()
+def host_threads() -> int:
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except (AttributeError, OSError):
+        return max(1, os.cpu_count() or 1)
+
+
+def _compose(per_shape_weight_s, per_cell_rows_s, per_cell_product_s) -> float:
+    """Seconds of the whole sweep from the sampled pieces (see the note above)."""
+    total = 0.0
+    for si, (_, n, k) in enumerate(SHAPES):
+        for m in TOKENS:
+            total += per_shape_weight_s[si] * (n / min(n, CPU_WEIGHT_ROWS))
+            total += per_cell_rows_s[(si, m)] * (m / min(m, CPU_ENCODE_ROWS))
+            total += per_cell_product_s[(si, m)]
+    return total
+
+
+class ReferenceCpuArm:
+    """The reference's own PyTorch-CPU path (nestquant.core, installed unmodified under oracle/_ref).
+
+    quantize_rows (core/quantizer.py:214) + pack_nestquant_indices (core/packing.py:137) of the activation,
+    QuantizedRows.dequantize (core/quantizer.py:39) of both operands, float32 product -- config 0's pipeline
+    on config 1's shapes.  The weight is encoded once outside the timed region (it is offline work).
+    """
+
+    kind = "reference"
+
+    def __init__(self, threads: int) -> None:
+        from oracle.build_ref import build as build_ref, ref_path
+
+        location = ref_path() or build_ref()
+        if location is None:
+            raise RuntimeError("oracle/_ref holds no installed reference and no reference source is present")
+        if str(location) not in sys.path:
+            sys.path.insert(0, str(location))
+        import torch
+        from nestquant.core.codec import generate_e8_dither_stateless
+        from nestquant.core.packing import pack_nestquant_indices
+        from nestquant.core.quantizer import quantize_rows
+        from nestquant.core.rotation import hadamard
+
+        torch.set_num_threads(threads)
+        self.torch, self.threads = torch, torch.get_num_threads()
+        self.quantize_rows, self.pack = quantize_rows, pack_nestquant_indices
+        gen = torch.Generator().manual_seed(1000)
+        self.weights, self.inputs, self.full = [], {}, {}
+        for i, (_, n, k) in enumerate(SHAPES):
+            rows = min(n, CPU_WEIGHT_ROWS)
+            w = hadamard(0.02 * torch.randn(rows, k, generator=gen))
+            dither = generate_e8_dither_stateless(rows * k // 8, seed=20261029 + i).reshape(rows, k // 8, 8)
+            self.weights.append(quantize_rows(w, 14, W_BETAS, dither=dither))
+            self.full[("w", i)] = torch.randn(n, k, generator=gen)
+        for k in sorted({k for _, _, k in SHAPES}):
+            for m in TOKENS:
+                x = torch.randn(m, k, generator=torch.Generator().manual_seed(2000 + m)).bfloat16()
+                self.inputs[(k, m)] = hadamard(x)[:min(m, CPU_ENCODE_ROWS)].float().contiguous()
+                self.full[("a", k, m)] = torch.randn(m, k, generator=gen)
+
+    def sample_step(self):
+        torch, clock = self.torch, time.perf_counter
+        weight_s, rows_s, product_s = {}, {}, {}
+        with torch.no_grad():
+            for si, (_, n, k) in enumerate(SHAPES):
+                t0 = clock()
+                self.weights[si].dequantize()
+                weight_s[si] = clock() - t0
+                for m in TOKENS:
+                    t0 = clock()
+                    qa = self.quantize_rows(self.inputs[(k, m)], 14, ACT_BETAS)
+                    self.pack(qa.codes, qa.beta_indices, q=qa.q, beta_count=len(qa.betas))
+                    qa.dequantize()
+                    rows_s[(si, m)] = clock() - t0
+                    t0 = clock()
+                    torch.matmul(self.full[("a", k, m)], self.full[("w", si)].T)
+                    product_s[(si, m)] = clock() - t0
+        return weight_s, rows_s, product_s
+
+    def describe(self) -> str:
+        return ("all 32 cells; nestquant.core quantize_rows + pack_nestquant_indices + dequantize of the activation on "
+                f"the first {CPU_ENCODE_ROWS} rows of each cell (scaled to M), QuantizedRows.dequantize of {CPU_WEIGHT_ROWS} "
+                "weight rows with the dither held in memory (scaled to N), torch float32 product at full size")
+
+
+class PortCpuArm:
+    """The C restatement of the same pipeline (oracle/nq_oracle.c, OpenMP), sampled the same way."""
+
+    kind = "port"
+
+    def __init__(self, threads: int) -> None:
+        import numpy as np
+
+        from oracle import nq_oracle as oracle
+
+        oracle.build()
+        oracle.set_threads(threads)
+        self.oracle, self.np, self.threads = oracle, np, oracle.thread_count()
+        rng = np.random.default_rng(1000)
+        self.weights, self.inputs, self.full = [], {}, {}
+        for i, (_, n, k) in enumerate(SHAPES):
+            rows = min(n, CPU_WEIGHT_ROWS)
+            w = oracle.hadamard((0.02 * rng.standard_normal((rows, k))).astype(np.float32))
+            seed = 20261029 + i
+            self.weights.append((*oracle.encode_packed(w, W_BETAS, seed=seed), seed, rows))
+            self.full[("w", i)] = rng.standard_normal((n, k)).astype(np.float32)
+        for k in sorted({k for _, _, k in SHAPES}):
+            for m in TOKENS:
+                rows = min(m, CPU_ENCODE_ROWS)
+                x = oracle.round_bf16(rng.standard_normal((rows, k)).astype(np.float32))
+                self.inputs[(k, m)] = oracle.hadamard(x, round_bf16=True)
+                self.full[("a", k, m)] = rng.standard_normal((m, k)).astype(np.float32)
+
+    def sample_step(self):
+        oracle, clock = self.oracle, time.perf_counter
+        weight_s, rows_s, product_s = {}, {}, {}
+        for si, (_, n, k) in enumerate(SHAPES):
+            wc, wb, wn, seed, rows = self.weights[si]
+            t0 = clock()
+            oracle.dequantize_rows(wc, wb, wn, W_BETAS, rows, k, seed=seed)
+            weight_s[si] = clock() - t0
+            for m in TOKENS:
+                x = self.inputs[(k, m)]
+                t0 = clock()
+                ac, ab, an = oracle.encode_packed(x, ACT_BETAS)
+                oracle.dequantize_rows(ac, ab, an, ACT_BETAS, x.shape[0], k)
+                rows_s[(si, m)] = clock() - t0
+                t0 = clock()
+                oracle.gemm_f32(self.full[("a", k, m)], self.full[("w", si)])
+                product_s[(si, m)] = clock() - t0
+        return weight_s, rows_s, product_s
+
+    def describe(self) -> str:
+        return ("all 32 cells; C restatement: encode + pack + dequantise of the activation on the first "
+                f"{CPU_ENCODE_ROWS} rows of each cell (scaled to M), dequantise of {CPU_WEIGHT_ROWS} weight rows with the "
+                "dither regenerated (scaled to N), float32 product at full size")
+
+
+def cpu_arm(prefer_reference: bool = True):
+    """The reference's own CPU path when it is installed under oracle/_ref, else the C restatement."""
+    threads = host_threads()
+    os.environ["OMP_NUM_THREADS"] = str(threads)  # a launcher may have exported 1 for its children
+    os.environ["MKL_NUM_THREADS"] = str(threads)
+    if prefer_reference:
+        try:
+            return ReferenceCpuArm(threads)
+        except Exception as error:  # not installed on this machine: fall back to the restatement, and say so
+            print(f"bench: reference CPU path unavailable ({type(error).__name__}: {error}); timing the C restatement",
+                  file=sys.stderr)
+    return PortCpuArm(threads)
+
+
+def cpu_baseline(arm, repeats: int = 1, warmup: int = 0) -> dict:
     for _ in range(warmup):
-        cpu_sample_once(oracle, np, weights, activations)
-    start = time.perf_counter()
+        arm.sample_step()
+    sample_seconds, composed = [], []
     for _ in range(repeats):
-        cpu_sample_once(oracle, np, weights, activations)
-    seconds = (time.perf_counter() - start) / repeats
-    flops = sweep_flops(CPU_SAMPLE_TOKENS)
-    return {"value": flops / seconds / 1e12, "unit": UNIT, "cores": oracle.thread_count(), "kind": "port",
-            "sample": f"cells M in {list(CPU_SAMPLE_TOKENS)} x 4 shapes: A4 encode + dequantise W and A + fp32 product "
-                      f"({seconds:.2f} s per pass)", "seconds_per_pass": seconds}
+        start = time.perf_counter()
+        pieces = arm.sample_step()
+        sample_seconds.append(time.perf_counter() - start)
+        composed.append(_compose(*pieces))
+    composed.sort()
+    sweep_seconds = composed[len(composed) // 2]
+    return {"value": sweep_flops() / sweep_seconds / 1e12, "unit": UNIT, "cores": arm.threads, "kind": arm.kind,
+            "sample": f"{arm.describe()}; {sum(sample_seconds) / len(sample_seconds):.2f} s of CPU work per step, "
+                      f"{sweep_seconds:.1f} s for the whole sweep when composed",
+            "seconds_per_sample_step": sum(sample_seconds) / len(sample_seconds),
+            "sweep_seconds_composed": sweep_seconds}
 
 
 def run_reference(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    base = cpu_baseline(repeats=max(1, args.steps), warmup=min(args.warmup, 1))
-    seconds = base.pop("seconds_per_pass")
+    world = int(os.environ.get("WORLD_SIZE", str(args.gpus)))
+    arm = cpu_arm()
+    base = cpu_baseline(arm, repeats=max(1, args.steps), warmup=args.warmup)
+    seconds = base.pop("seconds_per_sample_step")
     line = {
-        "impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus,
+        "impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": seconds * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "w4a4_projection_sweep", "shapes": [list(s) for s in SHAPES],
-                   "tokens": list(CPU_SAMPLE_TOKENS), "note": "bounded CPU sample of the GPU arm's sweep"},
+        "config": sweep_config(world),
         "cpu_baseline": base,
         "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
+        "note": "ms_per_step is the wall time of one bounded sample step; value is the sweep's flops over the time "
+                "of the whole sweep composed from the sampled pieces",
     }
     print(json.dumps(line), flush=True)
 
@@ -214,6 +357,7 @@ def run_gpu(args) -> None:
 
         # NCCL's banner / debug lines must not land on stdout next to the JSON line
         os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")  # plain peer paths: the all-reduces are ~2 % of a TP step
         dist.init_process_group("nccl", device_id=device)
     import nestquant_aiinfra_b200.runtime as rt
     from nestquant_aiinfra_b200.fused_linear import FusedNQRTLinear
@@ -231,7 +375,7 @@ def run_gpu(args) -> None:
             if record:
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record(stream)
-            act = rt.quantize_activation_cuda(x, q=14, betas=ACT_BETAS, beta_table=beta_table)
+            act = rt.quantize_activation_cuda(x, q=14, betas=ACT_BETAS, beta_table=beta_table, keep_decoded=True)
             if record:
                 e1.record(stream)
                 encode_events.append((m, k, e0, e1))
@@ -346,19 +490,27 @@ def run_gpu(args) -> None:
         except Exception as error:
             extras["decode"] = {"error": f"{type(error).__name__}: {error}"[:300]}
         torch.cuda.empty_cache()
+        if distributed:
+            # config 4: the tensor-parallel decode step over these ranks (the only workload here with a collective)
+            try:
+                extras["tp"] = tp_decode(torch, dist, device, rank, world, layers=args.tp_layers, batch=args.tp_batch,
+                                         context=args.tp_context, steps=3, warmup=3)
+            except Exception as error:
+                extras["tp"] = {"error": f"{type(error).__name__}: {error}"[:300]}
+            torch.cuda.empty_cache()
     if rank == 0:
-        base = cpu_baseline(repeats=2) if world == 1 and not args.skip_extras else None
-        if base:
-            base.pop("seconds_per_pass", None)
+        base = port = None
+        if world == 1 and not args.skip_extras:
+            arm = cpu_arm()
+            base = cpu_baseline(arm, repeats=2, warmup=1)
+            if arm.kind == "reference":  # the C restatement beside it, as a second figure
+                port = cpu_baseline(PortCpuArm(host_threads()), repeats=2, warmup=1)
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "w4a4_projection_sweep", "shapes": [list(s) for s in SHAPES],
-                       "tokens": list(TOKENS), "q": 14, "betas": 4, "encode": "on the fly every call",
-                       "l2": "one step touches > 1 GB of distinct operands, so inputs of a cell are evicted from the "
-                             "126 MB L2 before the cell repeats", "parallelism": f"replicas{world}",
-                       "launch": "CUDA graph of one step, replayed" if graph is not None else "call by call"},
+            "config": sweep_config(world),
+            "launch": "CUDA graph of one step, replayed" if graph is not None else "call by call",
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],
                     "ms_per_step": e2e["ms"]},
@@ -366,13 +518,13 @@ def run_gpu(args) -> None:
             "roofline": roofline,
             "roofline_gemm": gemm,
             "cpu_baseline": base,
+            "cpu_baseline_port": port,
             "cells": table,
         }
         line.update(extras)
         print(json.dumps(line), flush=True)
     if distributed:
-        dist.barrier()
-        dist.destroy_process_group()
+        _teardown(torch, dist, device)
 
 
 def _time_graph(torch, fn, device, reps: int = 5) -> float:
@@ -414,8 +566,9 @@ def cell_table(torch, rt, weights, inputs, beta_table, device, pk):
         w_bytes = n * k * 17 // 32 + 4 * n + 32
         for m in TOKENS:
             x = inputs[(k, m)]
-            act = rt.quantize_activation_cuda(x, q=14, betas=ACT_BETAS, beta_table=beta_table)
-            t_enc = _time_graph(torch, lambda: rt.quantize_activation_cuda(x, q=14, betas=ACT_BETAS, beta_table=beta_table), device)
+            act = rt.quantize_activation_cuda(x, q=14, betas=ACT_BETAS, beta_table=beta_table, keep_decoded=True)
+            t_enc = _time_graph(torch, lambda: rt.quantize_activation_cuda(x, q=14, betas=ACT_BETAS, beta_table=beta_table,
+                                                                           keep_decoded=True), device)
             t_proj = _time_graph(torch, lambda: rt.linear_packed_w4a4(act, w), device)
             row = {"shape": name, "M": m, "encode_us": round(t_enc, 2), "proj_us": round(t_proj, 2),
                    "w_gbs": round((w_bytes + m * k * 2 + m * n * 2) / t_proj / 1e3, 1),
@@ -506,7 +659,7 @@ def gemv_workload(torch, rt, device, pk, only: str | None = None) -> dict:
     for (name, n, k), w in zip(SHAPES, weights):
         if only and name != only:
             continue
-        act = rt.quantize_activation_cuda(inputs[(k, 1)], q=14, betas=ACT_BETAS, beta_table=beta_table)
+        act = rt.quantize_activation_cuda(inputs[(k, 1)], q=14, betas=ACT_BETAS, beta_table=beta_table, keep_decoded=True)
         resident = rt.keep_decoded_weight(w)
         copies = max(2, (160 << 20) // (n * k * 2) + 1)
         clones = [dataclasses.replace(resident, decoded=resident.decoded.clone()) for _ in range(copies)]
@@ -581,13 +734,42 @@ def kv_workload(torch, rt, device, pk) -> dict:
     pack_cache.hot_values.copy_(torch.randn(pack_cache.hot_values.shape, generator=gen).bfloat16())
     pack_cache.graph_target_page_ids.copy_(torch.arange(batch, dtype=torch.int32))
 
-    def pack_once():
+    def rearm():  # the publish step empties the hot tails and advances the page tables: put both back
         pack_cache.hot_lengths.fill_(page)
         pack_cache.page_counts.zero_()
+
+    def pack_once():
+        rearm()
         rt.launch_pack_full_hot_pages_graph_safe(pack_cache, boundary_mask=active)
 
-    t_pack = _time_graph(torch, pack_once, device)
+    t_rearm = _time_graph(torch, rearm, device, reps=48)
+    t_pack = max(_time_graph(torch, pack_once, device, reps=48) - t_rearm, 0.0)  # the pack + publish launches alone
     pack_bytes = batch * (2 * page * heads * dim * 2 + pack_pool.page_payload_bytes)
+    # ragged prefill over the same pool: every sequence continues a cached context of U[0, 4032] tokens with a
+    # chunk of U[1, 64] new tokens whose K/V are already appended (cold pages + hot tail); causal, pages read directly
+    starts = torch.randint(0, 4033, (batch,), generator=gen)
+    chunks = torch.randint(1, 65, (batch,), generator=gen)
+    totals = starts + chunks
+    pre_cache = rt.NQKVHotColdCache(pool, max_sequences=batch, max_pages_per_sequence=pages_per_seq + 1)
+    for slot in range(batch):
+        pre_cache.register(slot)
+    pre_cache.page_indices[:, :pages_per_seq] = perm.view(batch, pages_per_seq).to(torch.int32)
+    pre_cache.page_counts.copy_((totals // page).to(torch.int32))
+    pre_cache.last_page_len.copy_(torch.where(totals >= page, page, 0).to(torch.int32))
+    pre_cache.hot_lengths.copy_((totals % page).to(torch.int32))
+    pre_cache.sequence_lengths.copy_(totals.to(torch.int32))
+    pre_cache.hot_keys.copy_(torch.randn(pre_cache.hot_keys.shape, generator=gen).bfloat16())
+    pre_cache.hot_values.copy_(torch.randn(pre_cache.hot_values.shape, generator=gen).bfloat16())
+    t_max = int(chunks.max())
+    pq = hadamard(torch.randn(batch, t_max, q_heads, dim, generator=gen).to(device)).bfloat16()
+    q_lens = chunks.to(torch.int32).to(device)
+    pws = rt.BatchedNQKVAttentionWorkspace.create(pre_cache, batch_size=batch, query_heads=q_heads, query_tokens=t_max)
+    t_prefill = _time_graph(torch, lambda: rt.nqkv_prefill_attention(
+        pq, pre_cache, slot_ids=slot_ids, query_lengths=q_lens, scale=0.125, workspace=pws), device)
+    new_tokens = int(chunks.sum())
+    # algorithmic bytes: every sequence's pages and hot tail once, its queries in and its outputs out
+    prefill_bytes = int(((totals // page) * pool.page_payload_bytes + (totals % page) * 2 * heads * dim * 2).sum()) \
+        + 2 * new_tokens * q_heads * dim * 2
     # opt-in decoded shadow of the pool: same attention call, coordinates read instead of searched
     before = ws.output.clone()
     shadow_bytes = pool.enable_lattice_shadow()
@@ -608,7 +790,17 @@ def kv_workload(torch, rt, device, pk) -> dict:
             "frac_of_hbm": round(lattice_read / t_shadow / 1e3 / pk["hbm_gbs"], 4),
             "output_identical_to_packed": identical},
         "page_pack_publish": {"pages": batch, "us": round(t_pack, 2), "us_per_page": round(t_pack / batch, 3),
-                              "gbs": round(pack_bytes / t_pack / 1e3, 1), "note": "includes two small fill kernels"},
+                              "gbs": round(pack_bytes / t_pack / 1e3, 1),
+                              "frac_of_hbm": round(pack_bytes / t_pack / 1e3 / pk["hbm_gbs"], 4),
+                              "note": "pack + publish launches alone (the two fills that re-arm the cache, "
+                                      f"{t_rearm:.2f} us, are timed separately and subtracted)"},
+        "attention_prefill_ragged": {
+            "batch": batch, "start_contexts": "U[0, 4032]", "chunk_lengths": "U[1, 64]", "new_tokens": new_tokens,
+            "cached_tokens": int(totals.sum()), "q_heads": q_heads, "kv_heads": heads, "head_dim": dim,
+            "us": round(t_prefill, 2), "new_tok_per_s": round(new_tokens / t_prefill * 1e6, 1),
+            "gbs": round(prefill_bytes / t_prefill / 1e3, 1),
+            "frac_of_hbm": round(prefill_bytes / t_prefill / 1e3 / pk["hbm_gbs"], 4),
+            "bytes": "pages + hot tail of every sequence once, queries in, outputs out"},
     }
 
 
@@ -705,29 +897,41 @@ def decode_workload(torch, device, *, requests: int = 64, new_tokens: int = 256,
             "prefill_tok_s": round(sum(lengths) / prefill_s, 1), "cuda_graph": True}
 
 
-def run_tp70b(args) -> None:
-    """Config 4: Llama-3-70B architecture, random init, W4A4KV4, tensor parallel over the ranks of torchrun."""
-    import torch
-    import torch.distributed as dist
+def tp_decode(torch, dist, device, rank: int, world: int, *, layers: int, batch: int, context: int, steps: int,
+              warmup: int, resident: bool = False) -> dict:
+    """Config 4: Llama-3-70B architecture (one seeded model sharded over the ranks), W4A4KV4, graph decode.
 
+    Returns the measurements (identical on every rank; the times are the maximum over the ranks).  The
+    all-reduce share comes from one more step issued call by call with CUDA events around every collective.
+    """
+    from nestquant_aiinfra_b200.fused_linear import FusedNQRTLinear
+    from nestquant_aiinfra_b200.tensor_parallel import RowParallelNQRTLinear
     from nestquant_aiinfra_b200.tp_engine import TensorParallelRunner, build_llama_tp_shard, fill_cache_synthetic
 
-    rank, local_rank = int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    torch.cuda.set_device(local_rank)
-    device = torch.device("cuda", local_rank)
-    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
-    if world > 1:
-        dist.init_process_group("nccl", device_id=device)
-    steps = max(args.steps, 1)
+    def timed(runner) -> float:
+        for _ in range(warmup):
+            runner.decode()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            runner.decode()
+        e1.record()
+        torch.cuda.synchronize(device)
+        ms = torch.tensor([e0.elapsed_time(e1) / steps], device=device)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
     t0 = time.perf_counter()
-    model, cache = build_llama_tp_shard(hidden_size=8192, intermediate_size=28672, num_layers=args.tp_layers,
-                                        num_heads=64, num_kv_heads=8, head_dim=128, vocab_size=128256, rank=rank,
-                                        world=world, capacity=args.tp_batch,
-                                        max_cache_len=args.tp_context + 3 * (steps + max(args.warmup, 3)) + 32, device=device)
-    fill_cache_synthetic(cache, args.tp_context)
+    model, cache = build_llama_tp_shard(hidden_size=8192, intermediate_size=28672, num_layers=layers, num_heads=64,
+                                        num_kv_heads=8, head_dim=128, vocab_size=128256, rank=rank, world=world,
+                                        capacity=batch, max_cache_len=context + 4 * (steps + warmup) + 48, device=device)
+    fill_cache_synthetic(cache, context)
     runner = TensorParallelRunner(model, cache)
-    runner.start_decode(args.tp_context)
+    runner.start_decode(context)
     torch.cuda.synchronize(device)
     build_s = time.perf_counter() - t0
     graph = True
@@ -737,109 +941,122 @@ def run_tp70b(args) -> None:
         graph = f"eager ({type(error).__name__})"
         runner.graph = None
         runner.cache.set_decode_state()
-    for _ in range(max(args.warmup, 3)):
-        runner.decode()
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize(device)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(steps):
-        runner.decode()
-    e1.record()
-    torch.cuda.synchronize(device)
-    ms = torch.tensor([e0.elapsed_time(e1) / steps], device=device)
+    ms_step = timed(runner)
     tokens = runner.next_tokens.clone()
+    same = torch.tensor([1], device=device)
     if world > 1:
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        reference = tokens.clone()
-        dist.broadcast(reference, src=0)
-        same = torch.tensor([int(torch.equal(reference, tokens))], device=device)
+        first = tokens.clone()
+        dist.broadcast(first, src=0)
+        same = torch.tensor([int(torch.equal(first, tokens))], device=device)
         dist.all_reduce(same, op=dist.ReduceOp.MIN)
-    else:
-        same = torch.tensor([1])
-    resident = None
-    if args.tp_resident:
+    # all-reduce share: one eager step with events around every collective (2 per layer)
+    collective_ms, collectives = 0.0, 0
+    if world > 1:
+        rows = [m for m in model.modules() if isinstance(m, RowParallelNQRTLinear)]
+        events: list = []
+        for module in rows:
+            module.collective_events = events
+        runner.decode_eager()
+        torch.cuda.synchronize(device)
+        for module in rows:
+            module.collective_events = None
+        t = torch.tensor([sum(a.elapsed_time(b) for a, b in events)], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        collective_ms, collectives = float(t.item()), len(events)
+    packed = sum(m.packed_device_bytes for m in model.modules() if isinstance(m, (FusedNQRTLinear, RowParallelNQRTLinear)))
+    result = {
+        "workload": "llama-3-70b-arch W4A4KV4 tensor-parallel decode (one seeded model sharded over the ranks)",
+        "parallelism": f"tp{world}", "layers": layers, "batch": batch, "context": context, "steps": steps,
+        "warmup": warmup, "ms_per_step": ms_step, "tok_s": batch / (ms_step * 1e-3),
+        "ms_per_layer": ms_step / layers,
+        "all_reduce": {"collective": "NCCL all_reduce(sum) of [batch, 8192] BF16 after o_proj and down_proj",
+                       "per_step": collectives, "ms_per_step_eager": round(collective_ms, 3),
+                       "share_of_step": round(collective_ms / ms_step, 4) if ms_step else None},
+        "cuda_graph": graph, "kv": "pages pre-filled by the page encoder with synthetic K/V",
+        "packed_weight_bytes_per_rank": int(packed), "build_s": round(build_s, 1),
+        "ranks_agree_on_tokens": bool(same.item()),
+    }
+    if layers != 80:
+        result["ms_per_step_80_layers_extrapolated"] = ms_step / layers * 80
+    if resident:
         # opt-in mode: every rank keeps the decoded BF16 weights of its shard; same graph-decode loop again
         from nestquant_aiinfra_b200.fused_linear import keep_decoded_weights_
+
+        def recapture() -> None:
+            if isinstance(runner.graph, torch.cuda.CUDAGraph):
+                runner.graph.reset()
+                runner.graph = None
+            if graph is True:
+                runner.capture_decode_graph()
 
         if isinstance(runner.graph, torch.cuda.CUDAGraph):
             runner.graph.reset()
             runner.graph = None
         added = keep_decoded_weights_(model)
-        if graph is True:
-            runner.capture_decode_graph()
-        for _ in range(max(args.warmup, 3)):
-            runner.decode()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize(device)
-        r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        r0.record()
-        for _ in range(steps):
-            runner.decode()
-        r1.record()
-        torch.cuda.synchronize(device)
-        rms = torch.tensor([r0.elapsed_time(r1) / steps], device=device)
-        if world > 1:
-            dist.all_reduce(rms, op=dist.ReduceOp.MAX)
-        resident = {"note": "opt-in: decoded BF16 weights of the shard kept in HBM", "extra_weight_bytes_per_rank": int(added),
-                    "ms_per_step": float(rms.item()), "tok_s": args.tp_batch / (float(rms.item()) * 1e-3)}
-        # on top: the decoded lattice shadow of the KV pages (attention reads coordinates instead of searching)
+        recapture()
+        rms = timed(runner)
+        result["resident_decoded_weights"] = {"note": "opt-in: decoded BF16 weights of the shard kept in HBM",
+                                              "extra_weight_bytes_per_rank": int(added), "ms_per_step": rms,
+                                              "tok_s": batch / (rms * 1e-3)}
         if isinstance(runner.graph, torch.cuda.CUDAGraph):
             runner.graph.reset()
             runner.graph = None
         kv_added = cache.enable_lattice_shadow()
-        if graph is True:
-            runner.capture_decode_graph()
-        for _ in range(max(args.warmup, 3)):
-            runner.decode()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize(device)
-        k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        k0.record()
-        for _ in range(steps):
-            runner.decode()
-        k1.record()
-        torch.cuda.synchronize(device)
-        kms = torch.tensor([k0.elapsed_time(k1) / steps], device=device)
-        if world > 1:
-            dist.all_reduce(kms, op=dist.ReduceOp.MAX)
-        resident["with_kv_lattice_shadow"] = {"extra_kv_bytes_per_rank": int(kv_added), "ms_per_step": float(kms.item()),
-                                              "tok_s": args.tp_batch / (float(kms.item()) * 1e-3)}
-    if rank == 0:
-        ms_step = float(ms.item())
-        from nestquant_aiinfra_b200.fused_linear import FusedNQRTLinear
+        recapture()
+        kms = timed(runner)
+        result["resident_decoded_weights"]["with_kv_lattice_shadow"] = {
+            "extra_kv_bytes_per_rank": int(kv_added), "ms_per_step": kms, "tok_s": batch / (kms * 1e-3)}
+    # A live CUDA graph that captured NCCL kernels keeps the communicator busy: release it before any teardown.
+    if isinstance(runner.graph, torch.cuda.CUDAGraph):
+        runner.graph.reset()
+    runner.graph = None
+    del runner, model, cache
+    torch.cuda.synchronize(device)
+    torch.cuda.empty_cache()
+    return result
 
-        packed = sum(m.packed_device_bytes for m in model.modules() if isinstance(m, FusedNQRTLinear))
+
+def _teardown(torch, dist, device) -> None:
+    """Leave the process group; bounded, so that a stuck finalize cannot hold the GPUs."""
+    torch.cuda.synchronize(device)
+    dist.barrier()
+    torch.cuda.synchronize(device)
+    sys.stdout.flush()
+    watchdog = threading.Timer(45.0, lambda: os._exit(0))
+    watchdog.daemon = True
+    watchdog.start()
+    dist.destroy_process_group()
+    watchdog.cancel()
+
+
+def run_tp70b(args) -> None:
+    """Config 4 alone (run under torchrun, one process per GPU)."""
+    import torch
+    import torch.distributed as dist
+
+    rank, local_rank = int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    result = tp_decode(torch, dist, device, rank, world, layers=args.tp_layers, batch=args.tp_batch,
+                       context=args.tp_context, steps=max(args.steps, 1), warmup=max(args.warmup, 3),
+                       resident=args.tp_resident)
+    if rank == 0:
         print(json.dumps({
-            "metric": "w4a4kv4_tp_decode_tok_s", "value": args.tp_batch / (ms_step * 1e-3), "unit": "tok/s",
-            "n_gpus": world, "steps": steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
+            "metric": "w4a4kv4_tp_decode_tok_s", "value": result["tok_s"], "unit": "tok/s", "n_gpus": world,
+            "steps": result["steps"], "warmup": result["warmup"], "ms_per_step": result["ms_per_step"],
             "higher_is_better": True, "scaling": "strong", "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "llama-3-70b-arch W4A4KV4 tensor-parallel decode", "layers": args.tp_layers,
-                       "batch": args.tp_batch, "context": args.tp_context, "parallelism": f"tp{world}",
-                       "all_reduce": "NCCL after o_proj and down_proj", "cuda_graph": graph,
-                       "kv": "pages pre-filled by the page encoder with synthetic K/V"},
-            "packed_weight_bytes_per_rank": int(packed), "build_s": round(build_s, 1),
-            "ranks_agree_on_tokens": bool(same.item()),
-            **({"resident_decoded_weights": resident} if resident else {}),
+            "config": {"workload": result["workload"], "layers": result["layers"], "batch": result["batch"],
+                       "context": result["context"], "parallelism": result["parallelism"]},
+            **{k: v for k, v in result.items() if k not in ("workload", "layers", "batch", "context", "parallelism",
+                                                            "steps", "warmup", "ms_per_step")},
         }), flush=True)
     if world > 1:
-        # A live CUDA graph that captured NCCL kernels keeps the communicator busy: release it before
-        # the teardown, and bound the teardown so that a stuck finalize cannot hold the GPUs.
-        if isinstance(runner.graph, torch.cuda.CUDAGraph):
-            runner.graph.reset()
-        runner.graph = None
-        torch.cuda.synchronize(device)
-        dist.barrier()
-        torch.cuda.synchronize(device)
-        sys.stdout.flush()
-        watchdog = threading.Timer(45.0, lambda: os._exit(0))
-        watchdog.daemon = True
-        watchdog.start()
-        dist.destroy_process_group()
-        watchdog.cancel()
+        _teardown(torch, dist, device)
 
 
 def run_single_extra(args) -> None:

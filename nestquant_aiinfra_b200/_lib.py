@@ -40,15 +40,20 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
     deps = sources + list(CSRC.glob("*.cuh")) + [HEADER]
     if not force and LIB_PATH.exists() and all(LIB_PATH.stat().st_mtime >= d.stat().st_mtime for d in deps):
         return LIB_PATH
+    # link beside the target and rename: several ranks may find the library stale at the same time
+    scratch = LIB_PATH.with_name(f".{LIB_PATH.name}.{os.getpid()}.tmp")
     command = [
-        _nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-        "-shared", "-Xcompiler", "-fPIC", "-o", str(LIB_PATH), *map(str, sources),
+        _nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--threads", "0",
+        "-shared", "-Xcompiler", "-fPIC", "-o", str(scratch), *map(str, sources),
     ]
     if verbose:
         command.insert(1, "-Xptxas=-v")
     result = subprocess.run(command, capture_output=True, text=True)
     if result.returncode != 0:
+        if scratch.exists():
+            scratch.unlink()
         raise RuntimeError(f"nvcc failed:\n{result.stdout}\n{result.stderr}")
+    os.replace(scratch, LIB_PATH)
     if verbose:
         print(result.stderr)
     return LIB_PATH

@@ -16,7 +16,8 @@ import torch
 from torch import nn
 
 from .rotation import hadamard
-from .runtime.w4a4 import (PreparedNQA4Activation, PreparedNQRTLinear, linear_packed_w4a4, prepare_fused_linear,
+from .runtime.w4a4 import (PreparedNQA4Activation, PreparedNQRTLinear, linear_packed_w4a4, linear_packed_w4a4_fp32,
+                           prepare_fused_linear,
                            quantize_activation_cuda, can_rotate_in_encoder, prefer_rotation_in_encoder,
                            group_prepared_linears, keep_decoded_weight)
 
@@ -331,8 +332,12 @@ class FusedNQRTLinear(nn.Module):
                 hadamard_block=block)
         self.a4_call_count += 1
         self.a4_encode_count += int(encoded)
-        outputs = (linear_packed_w4a4(packed, prepared) if self._group is None
-                   else self._group.project(packed, self._group_index))
+        if self._group is not None:
+            outputs = self._group.project(packed, self._group_index)
+        elif self.output_dtype == torch.float32:
+            outputs = linear_packed_w4a4_fp32(packed, prepared)  # the accumulator itself, not rounded to the input dtype first
+        else:
+            outputs = linear_packed_w4a4(packed, prepared)
         self.w4a4_cuda_mma_dispatch_count += 1
         return outputs.to(self.output_dtype or original_dtype)
 

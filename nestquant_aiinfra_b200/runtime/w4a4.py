@@ -250,8 +250,13 @@ def quantize_activation_cuda(
 
 
 def quantize_weight_cuda(weight: torch.Tensor, *, betas: Sequence[float], dither_seed: int,
-                         tensor_name: str = "weight", q: int = 14) -> PreparedNQRTLinear:
+                         tensor_name: str = "weight", q: int = 14, block_offset: int = 0) -> PreparedNQRTLinear:
     """Encode a ``[N, K]`` weight on the GPU into NQRT4 streams (stateless dither).
+
+    ``block_offset`` is the global index of the weight's first E8 block inside its record: a row
+    range ``[lo, hi)`` of a larger tensor encoded with ``block_offset = lo * K / 8`` and the tensor's
+    seed yields exactly the bytes of that row range of the whole tensor's streams, so
+    tensor-parallel ranks can encode their own output rows.
 
     Bit-exact with the reference's CPU encode
     (``quantize_rows(W, 14, betas, dither=generate_e8_dither_stateless(N*K/8, seed))``
@@ -277,15 +282,16 @@ def quantize_weight_cuda(weight: torch.Tensor, *, betas: Sequence[float], dither
     beta_ids = torch.empty(n * k // 32, dtype=torch.uint8, device=device)
     norms = torch.empty(n, dtype=torch.float32, device=device)
     status = _lib.lib().nq_w4_encode(_ptr(w), _DTYPE_TAG[w.dtype], _I64(n), _I64(k), _I64(k), _ptr(beta_table),
-                                     _I64(int(dither_seed)), _I64(0), _ptr(codes), _ptr(beta_ids), _ptr(norms),
-                                     _stream(device))
+                                     _I64(int(dither_seed)), _I64(int(block_offset)), _ptr(codes), _ptr(beta_ids),
+                                     _ptr(norms), _stream(device))
     _lib.check(status, "quantize_weight_cuda")
     record = PackedNestQuantTensor(
         tensor_name=tensor_name,
         indices=PackedNestQuantIndices((n, k // 8, 8), 14, 4, b"", b""),
         row_norms=norms, betas=tuple(float(b) for b in betas), feature_count=k, dither_seed=int(dither_seed))
     return PreparedNQRTLinear(record=record, code_payload=codes, beta_payload=beta_ids, row_norms=norms,
-                              beta_table=beta_table)
+                              beta_table=beta_table, block_offset=int(block_offset),
+                              out_features=n if block_offset else None)
 
 
 # ---------------------------------------------------------------------------

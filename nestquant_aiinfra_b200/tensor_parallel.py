@@ -95,7 +95,8 @@ class RowParallelNQRTLinear(nn.Module):
 
     def __init__(self, weight_slice: torch.Tensor, rank: int, world: int, *, dither_seed: int,
                  weight_betas: Sequence[float] = WEIGHT_BETAS, activation_betas: Sequence[float] = ACTIVATION_BETAS,
-                 process_group=None, project: Callable[[torch.Tensor], torch.Tensor] | None = None) -> None:
+                 process_group=None, project: Callable[[torch.Tensor], torch.Tensor] | None = None,
+                 reduce_dtype: torch.dtype | None = None) -> None:
         super().__init__()
         self.rank, self.world, self.process_group = rank, world, process_group
         self.out_features, self.in_features = int(weight_slice.shape[0]), int(weight_slice.shape[1])
@@ -104,13 +105,17 @@ class RowParallelNQRTLinear(nn.Module):
             raise ValueError("the K shard must be divisible by 32")
         self._project = project
         self.inner = None
+        # measurement hook: a list here receives one (start, end) CUDA-event pair per all-reduce
+        self.collective_events: list | None = None
         if project is None:
             from .fused_linear import FusedNQRTLinear
             from .runtime.w4a4 import quantize_weight_cuda
 
             rotated = block_hadamard(weight_slice.float(), self.hadamard_block)
             prepared = quantize_weight_cuda(rotated, betas=weight_betas, dither_seed=dither_seed)
-            self.inner = FusedNQRTLinear(prepared, input_hadamard=False, activation_betas=tuple(activation_betas))
+            # reduce_dtype = float32 sums the ranks' FP32 accumulators (parity checks); None sums in the input dtype
+            self.inner = FusedNQRTLinear(prepared, input_hadamard=False, activation_betas=tuple(activation_betas),
+                                         output_dtype=reduce_dtype)
             self.inner.input_rotation_block = self.hadamard_block  # rotated inside the encoder launch when it fits
 
     @property
@@ -127,5 +132,13 @@ class RowParallelNQRTLinear(nn.Module):
         if self.world > 1:
             import torch.distributed as dist
 
-            dist.all_reduce(partial, op=dist.ReduceOp.SUM, group=self.process_group)
+            events = self.collective_events
+            if events is not None and partial.is_cuda:
+                start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                start.record()
+                dist.all_reduce(partial, op=dist.ReduceOp.SUM, group=self.process_group)
+                end.record()
+                events.append((start, end))
+            else:
+                dist.all_reduce(partial, op=dist.ReduceOp.SUM, group=self.process_group)
         return partial

@@ -28,10 +28,28 @@ ROW = ("self_attn.o_proj", "mlp.down_proj")
 GROUPS = (("self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj"), ("mlp.gate_proj", "mlp.up_proj"))
 
 
+def full_projection_weight(layer: int, name: str, rows: int, cols: int, *, seed: int, device: torch.device,
+                           std: float = 0.02) -> torch.Tensor:
+    """The unsharded ``[rows, cols]`` float32 weight of one projection of the synthetic model.
+
+    A pure function of (seed, layer, name): every rank regenerates the same full tensor and cuts its
+    own slice out of it, so the ranks together hold ONE model (not ``world`` copies of a shard).
+    """
+    gen = torch.Generator(device=device).manual_seed(tensor_dither_seed(seed + 1000003, f"{layer}.{name}"))
+    return torch.randn(rows, cols, generator=gen, device=device, dtype=torch.float32) * std
+
+
 def build_llama_tp_shard(*, hidden_size: int, intermediate_size: int, num_layers: int, num_heads: int,
                          num_kv_heads: int, head_dim: int, vocab_size: int, rank: int, world: int, capacity: int,
                          max_cache_len: int, device: torch.device | str, seed: int = 0, process_group=None):
-    """Random-init shard ``rank`` of ``world`` of a Llama architecture, converted to W4A4KV4."""
+    """Shard ``rank`` of ``world`` of ONE random-init Llama architecture, converted to W4A4KV4.
+
+    Column-parallel projections (q, k, v, gate, up) take the rank's output rows of the full
+    weight and encode them with the full tensor's dither seed and ``block_offset = first_row * K / 8``:
+    the streams are byte for byte the rank's row range of the unsharded record.  Row-parallel
+    projections (o, down) take the rank's input features of the full weight as a self-contained
+    shard (``RowParallelNQRTLinear``).  Embeddings, norms and lm_head are replicated.
+    """
     from transformers import LlamaConfig, LlamaForCausalLM
 
     if num_heads % world or num_kv_heads % world or intermediate_size % world:
@@ -53,6 +71,12 @@ def build_llama_tp_shard(*, hidden_size: int, intermediate_size: int, num_layers
     finally:
         torch.set_default_dtype(previous)
     model.eval()
+    full_shapes = {"self_attn.q_proj": (num_heads * head_dim, hidden_size),
+                   "self_attn.k_proj": (num_kv_heads * head_dim, hidden_size),
+                   "self_attn.v_proj": (num_kv_heads * head_dim, hidden_size),
+                   "self_attn.o_proj": (hidden_size, num_heads * head_dim),
+                   "mlp.gate_proj": (intermediate_size, hidden_size), "mlp.up_proj": (intermediate_size, hidden_size),
+                   "mlp.down_proj": (hidden_size, intermediate_size)}
     for index, layer in enumerate(model.model.layers):
         caches = {}
         for group in GROUPS:
@@ -63,20 +87,29 @@ def build_llama_tp_shard(*, hidden_size: int, intermediate_size: int, num_layers
             parent_name, child_name = name.split(".")
             parent = getattr(layer, parent_name)
             linear = getattr(parent, child_name)
-            full_name = f"model.layers.{index}.{name}.weight.tp{rank}of{world}"
-            dither = tensor_dither_seed(58, full_name)
+            full_name = f"model.layers.{index}.{name}.weight"
+            rows, cols = full_shapes[name]
+            full = full_projection_weight(index, name, rows, cols, seed=seed, device=device)
             if name in ROW:
-                fused = RowParallelNQRTLinear(linear.weight.detach(), rank, world, dither_seed=dither,
+                lo, hi = cols // world * rank, cols // world * (rank + 1)
+                if tuple(linear.weight.shape) != (rows, hi - lo):
+                    raise RuntimeError(f"{name}: shard shape {tuple(linear.weight.shape)} is not a K slice of {(rows, cols)}")
+                fused = RowParallelNQRTLinear(full[:, lo:hi].contiguous(), rank, world,
+                                              dither_seed=tensor_dither_seed(58, f"{full_name}.tp{rank}of{world}"),
                                               weight_betas=WEIGHT_BETAS, activation_betas=ACTIVATION_BETAS,
                                               process_group=process_group)
             else:
-                prepared = quantize_weight_cuda(hadamard(linear.weight.detach().float()), betas=WEIGHT_BETAS,
-                                                dither_seed=dither, tensor_name=full_name)
+                lo, hi = rows // world * rank, rows // world * (rank + 1)
+                if tuple(linear.weight.shape) != (hi - lo, cols):
+                    raise RuntimeError(f"{name}: shard shape {tuple(linear.weight.shape)} is not a row range of {(rows, cols)}")
+                prepared = quantize_weight_cuda(hadamard(full[lo:hi].contiguous()), betas=WEIGHT_BETAS,
+                                                dither_seed=tensor_dither_seed(58, full_name), tensor_name=full_name,
+                                                block_offset=lo * (cols // 8))
                 hcache, acache = caches[name]
                 fused = FusedNQRTLinear(prepared, full_name, input_hadamard=True, input_transform_cache=hcache,
                                         activation_betas=ACTIVATION_BETAS, packed_activation_cache=acache)
             setattr(parent, child_name, fused.to(device))
-            del linear
+            del linear, full
         for group in GROUPS:  # q/k/v and gate/up shards: one decode + GEMM launch sequence per group
             SharedProjectionGroup([getattr(getattr(layer, name.split(".")[0]), name.split(".")[1]) for name in group])
         torch.cuda.empty_cache()

@@ -34,17 +34,22 @@ def build(force: bool = False) -> Path:
     source = _HERE / "nq_oracle.c"
     if not force and _LIB_PATH.exists() and _LIB_PATH.stat().st_mtime >= source.stat().st_mtime:
         return _LIB_PATH
+    # compile beside the target and rename: several processes (test ranks) may build at the same time
+    scratch = _LIB_PATH.with_name(f".{_LIB_PATH.name}.{os.getpid()}.tmp")
     base = ["-O2", "-fPIC", "-shared", "-ffp-contract=off", "-fno-fast-math", "-std=c11",
-            "-o", str(_LIB_PATH), str(source), "-lm"]
+            "-o", str(scratch), str(source), "-lm"]
     compilers = [c for c in ("/usr/bin/gcc", "gcc", "cc") if c]
     last = None
     for compiler in compilers:
         for extra in (["-fopenmp"], []):
             try:
                 subprocess.run([compiler, *extra, *base], check=True, capture_output=True)
+                os.replace(scratch, _LIB_PATH)
                 return _LIB_PATH
             except (OSError, subprocess.CalledProcessError) as error:  # try next variant
                 last = error
+    if scratch.exists():
+        scratch.unlink()
     raise RuntimeError(f"could not build the CPU checker: {last}")
 
 
@@ -242,6 +247,11 @@ def attn_prefill(query, slot_ids, q_lens, cache: dict, *, scale: float) -> np.nd
     return out
 
 
+def set_threads(threads: int) -> None:
+    """Threads of the checker's parallel loops from now on (overrides OMP_NUM_THREADS)."""
+    lib().nqo_set_threads(_INT(int(threads)))
+
+
 def thread_count() -> int:
-    """Threads the C checker will use (OpenMP default = all host cores)."""
-    return int(os.environ.get("OMP_NUM_THREADS", os.cpu_count() or 1))
+    """Threads the C checker uses for its parallel loops right now."""
+    return int(lib().nqo_max_threads())

@@ -27,7 +27,7 @@ def test_full_size_encode_streams(rt, oracle, m, k):
     from nestquant_aiinfra_b200.rotation import hadamard
 
     x = hadamard(torch.randn(m, k, generator=rng(2000 + m)).bfloat16().cuda())
-    act = rt.quantize_activation_cuda(x, q=14, betas=ACT_BETAS)
+    act = rt.quantize_activation_cuda(x, q=14, betas=ACT_BETAS, keep_decoded=True)
     # (1) the BF16 reconstruction written by the encoder == decode kernel applied to the emitted streams
     assert torch.equal(act.decoded, rt.decode_packed_a4(act, dtype=torch.bfloat16))
     # (2) every code is a valid residue (< 14) and norms are finite and positive
@@ -95,7 +95,7 @@ def test_full_size_projection_tails_and_paths_agree(rt, oracle):
     record, _ = make_weight_record(oracle, n, k, seed=31, dither_seed=32)
     weight = rt.prepare_fused_linear(record)
     x = torch.randn(m, k, generator=rng(33)).bfloat16().cuda()
-    act = rt.quantize_activation_cuda(x, q=14, betas=ACT_BETAS)
+    act = rt.quantize_activation_cuda(x, q=14, betas=ACT_BETAS, keep_decoded=True)
     full = rt.linear_packed_w4a4_fp32(act, weight).cpu().numpy()
     rows = [0, 255, 256, 511, 512, 519]
     for r in rows:
@@ -119,7 +119,7 @@ def test_full_size_resident_weight_agrees_with_the_packed_call(rt, m):
     resident = rt.keep_decoded_weight(packed)
     assert torch.equal(resident.decoded, rt.decode_packed_weight(packed))
     x = hadamard(torch.randn(m, k, generator=rng(2000 + m)).bfloat16().cuda())
-    act = rt.quantize_activation_cuda(x, q=14, betas=ACT_BETAS)
+    act = rt.quantize_activation_cuda(x, q=14, betas=ACT_BETAS, keep_decoded=True)
     a = rt.linear_packed_w4a4_fp32(act, packed).cpu().numpy()
     b = rt.linear_packed_w4a4_fp32(act, resident).cpu().numpy()
     assert rt.read_status() == 0
@@ -127,3 +127,95 @@ def test_full_size_resident_weight_agrees_with_the_packed_call(rt, m):
     # against a float32 product of the same BF16 operands
     expected = (act.decoded.float() @ resident.decoded.float().T).cpu().numpy()
     assert rel_fro(b, expected) <= REL_FRO_TOL and max_abs(b, expected) <= MAX_ABS_TOL
+
+
+
+# ---------------------------------------------------------------------------------------------------------
+# Config 2 at its own size: 32 sequences x 256 cold pages (context 4096) + hot tail, 8 KV heads, head_dim 64,
+# 1 % outlier channels (x8), keys Hadamard-rotated per head, random physical page permutation.
+def _config2_cache(rt, *, totals, seed=4096):
+    from helpers import KEY_BETAS, VALUE_BETAS
+    from nestquant_aiinfra_b200.rotation import hadamard
+
+    batch, heads, dim, page, ctx = 32, 8, 64, 16, 4096
+    pages_per_seq = ctx // page
+    capacity = batch * pages_per_seq
+    pool = rt.NQKVPagePool(capacity=capacity, page_size=page, num_kv_heads=heads, head_dim=dim, key_betas=KEY_BETAS,
+                           value_betas=VALUE_BETAS)
+    cache = rt.NQKVHotColdCache(pool, max_sequences=batch, max_pages_per_sequence=pages_per_seq + 1)
+    gen = rng(seed)
+    perm = torch.randperm(capacity, generator=gen).cuda()
+    rows = capacity * page * heads
+    for which, (codes, betas, norms, table, values) in enumerate((
+            (pool.key_codes, pool.key_betas, pool.key_norms, pool.beta_table, KEY_BETAS),
+            (pool.value_codes, pool.value_betas, pool.value_norms, pool.value_beta_table, VALUE_BETAS))):
+        x = torch.randn(batch, ctx, heads, dim, generator=gen)
+        outliers = torch.randperm(heads * dim, generator=gen)[:6]     # ceil(0.01 * 8 * 64) (head, channel) pairs
+        x.view(batch, ctx, heads * dim)[:, :, outliers] *= 8.0
+        x = x.cuda()
+        x = hadamard(x) if which == 0 else x
+        act = rt.quantize_activation_cuda(x.bfloat16().reshape(rows, dim), q=14, betas=values, beta_table=table)
+        codes[perm] = act.code_payload.view(capacity, -1)
+        betas[perm] = act.beta_payload.view(capacity, -1)
+        norms[perm] = act.row_norms.view(capacity, -1)
+        del x, act
+    for slot in range(batch):
+        cache.register(slot)
+    totals = torch.as_tensor(totals)
+    cache.page_indices[:, :pages_per_seq] = perm.view(batch, pages_per_seq).to(torch.int32)
+    cache.page_counts.copy_((totals // page).to(torch.int32))
+    cache.last_page_len.copy_(torch.where(totals >= page, page, 0).to(torch.int32))
+    cache.hot_lengths.copy_((totals % page).to(torch.int32))
+    cache.sequence_lengths.copy_(totals.to(torch.int32))
+    cache.hot_keys.copy_(torch.randn(cache.hot_keys.shape, generator=gen).bfloat16())
+    cache.hot_values.copy_(torch.randn(cache.hot_values.shape, generator=gen).bfloat16())
+    return cache, gen
+
+
+def test_config2_decode_attention_at_full_size(rt, oracle):
+    """Batch 32 x (256 pages + 1 hot token), 32 query heads: the FP32 output against the CPU checker."""
+    from nestquant_aiinfra_b200.rotation import hadamard
+
+    batch, q_heads, dim = 32, 32, 64
+    cache, gen = _config2_cache(rt, totals=[4097] * batch)
+    q = hadamard(torch.randn(batch, q_heads, dim, generator=gen).cuda()).bfloat16()
+    slot_ids = torch.arange(batch, dtype=torch.int32, device="cuda")
+    active = torch.ones(batch, dtype=torch.bool, device="cuda")
+    ws = rt.BatchedNQKVAttentionWorkspace.create(cache, batch_size=batch, query_heads=q_heads, output_dtype=torch.float32)
+    out = rt.nqkv_decode_attention_batched_k1(q, cache, slot_ids=slot_ids, active_mask=active, workspace=ws)
+    actual = out.cpu().numpy()
+    expected = oracle.attn_decode(q.float().cpu().numpy(), list(range(batch)), [1] * batch, rt.cache_arrays(cache),
+                                  scale=0.125)
+    assert np.isfinite(actual).all()
+    assert max_abs(actual, expected) <= MAX_ABS_TOL and rel_fro(actual, expected) <= REL_FRO_TOL, \
+        (max_abs(actual, expected), rel_fro(actual, expected))
+
+
+def test_config2_ragged_prefill_at_full_size(rt, oracle):
+    """Start contexts U[0, 4032], chunk lengths U[1, 64] whose K/V are appended already: sub-page, exact-fill,
+    one-boundary and multi-page chunks over cold pages plus hot tail, against the CPU checker."""
+    from nestquant_aiinfra_b200.rotation import hadamard
+
+    batch, q_heads, dim = 32, 32, 64
+    draw = rng(77)
+    starts = torch.randint(0, 4033, (batch,), generator=draw)
+    chunks = torch.randint(1, 65, (batch,), generator=draw)
+    starts[0], chunks[0] = 0, 5          # everything still hot
+    starts[1], chunks[1] = 16, 16        # exact page fill
+    starts[2], chunks[2] = 4032, 64      # the longest context, a multi-page chunk
+    starts[3], chunks[3] = 30, 3         # one boundary crossed
+    cache, gen = _config2_cache(rt, totals=(starts + chunks).tolist())
+    t_max = int(chunks.max())
+    q = hadamard(torch.randn(batch, t_max, q_heads, dim, generator=gen).cuda()).bfloat16()
+    slot_ids = torch.arange(batch, dtype=torch.int32, device="cuda")
+    q_lens = chunks.to(torch.int32).cuda()
+    ws = rt.BatchedNQKVAttentionWorkspace.create(cache, batch_size=batch, query_heads=q_heads, output_dtype=torch.float32,
+                                                 query_tokens=t_max)
+    out = rt.nqkv_prefill_attention(q, cache, slot_ids=slot_ids, query_lengths=q_lens, scale=0.125, workspace=ws)
+    actual = out.cpu().numpy()
+    expected = oracle.attn_prefill(q.float().cpu().numpy(), list(range(batch)), chunks.tolist(), rt.cache_arrays(cache),
+                                   scale=0.125)
+    for b in range(batch):
+        assert not actual[b, int(chunks[b]):].any()      # rows beyond the chunk stay zero
+    assert max_abs(actual, expected) <= MAX_ABS_TOL and rel_fro(actual, expected) <= REL_FRO_TOL, \
+        (max_abs(actual, expected), rel_fro(actual, expected))

@@ -25,7 +25,7 @@ def rt():
 
 
 def _encode(rt, x: torch.Tensor, betas):
-    act = rt.quantize_activation_cuda(x.cuda(), q=14, betas=betas)
+    act = rt.quantize_activation_cuda(x.cuda(), q=14, betas=betas, keep_decoded=True)
     torch.cuda.synchronize()
     return act
 
@@ -79,8 +79,8 @@ def test_rotation_inside_the_encoder_equals_two_launches(rt, rows, k, block, dty
 
     x = torch.randn(rows, k, generator=rng(600 + rows)).to(dtype).cuda()
     rotated = hadamard(x.reshape(rows, k // block, block)).reshape(rows, k)
-    two = rt.quantize_activation_cuda(rotated, q=14, betas=ACT_BETAS)
-    one = rt.quantize_activation_cuda(x, q=14, betas=ACT_BETAS, hadamard_block=block)
+    two = rt.quantize_activation_cuda(rotated, q=14, betas=ACT_BETAS, keep_decoded=True)
+    one = rt.quantize_activation_cuda(x, q=14, betas=ACT_BETAS, hadamard_block=block, keep_decoded=True)
     torch.cuda.synchronize()
     assert torch.equal(one.code_payload, two.code_payload) and torch.equal(one.beta_payload, two.beta_payload)
     assert torch.equal(one.row_norms, two.row_norms) and torch.equal(one.decoded, two.decoded)
