@@ -258,14 +258,14 @@ class PortCpuArm:
                 oracle.dequantize_rows(ac, ab, an, ACT_BETAS, x.shape[0], k)
                 rows_s[(si, m)] = clock() - t0
                 t0 = clock()
-                oracle.gemm_f32(self.full[("a", k, m)], self.full[("w", si)])
+                self.np.matmul(self.full[("a", k, m)], self.full[("w", si)].T)  # the host's BLAS, as torch uses one
                 product_s[(si, m)] = clock() - t0
         return weight_s, rows_s, product_s
 
     def describe(self) -> str:
         return ("all 32 cells; C restatement: encode + pack + dequantise of the activation on the first "
                 f"{CPU_ENCODE_ROWS} rows of each cell (scaled to M), dequantise of {CPU_WEIGHT_ROWS} weight rows with the "
-                "dither regenerated (scaled to N), float32 product at full size")
+                "dither regenerated (scaled to N), float32 product at full size through numpy's BLAS")
 
 
 def cpu_arm(prefer_reference: bool = True):
@@ -366,19 +366,10 @@ def run_gpu(args) -> None:
     cells = [(si, m) for si in range(len(SHAPES)) for m in TOKENS]
     stream = torch.cuda.current_stream(device)
 
-    encode_events: list = []
-
-    def step(record: bool) -> None:
+    def step() -> None:
         for si, m in cells:
-            _, n, k = SHAPES[si]
-            x = inputs[(k, m)]
-            if record:
-                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                e0.record(stream)
+            x = inputs[(SHAPES[si][2], m)]
             act = rt.quantize_activation_cuda(x, q=14, betas=ACT_BETAS, beta_table=beta_table, keep_decoded=True)
-            if record:
-                e1.record(stream)
-                encode_events.append((m, k, e0, e1))
             rt.linear_packed_w4a4(act, weights[si])
 
     def barrier() -> None:
@@ -389,7 +380,7 @@ def run_gpu(args) -> None:
     sampler = ClockSampler(local_rank)  # samples from the warm-up on, so the timed region is always covered
     sampler.start()
     for _ in range(max(args.warmup, 3)):
-        step(False)
+        step()
     barrier()
     # One sweep step is 112 launches, most of them a few microseconds long: issued call by call the host is the
     # slower side on the small cells (and more so with eight ranks sharing one host), so the step is captured
@@ -399,7 +390,7 @@ def run_gpu(args) -> None:
         counted = rt.launch_count()
         captured = torch.cuda.CUDAGraph()
         with torch.cuda.graph(captured):
-            step(False)
+            step()
         per_step = rt.launch_count() - counted
         captured.replay()
         torch.cuda.synchronize(device)
@@ -415,18 +406,30 @@ def run_gpu(args) -> None:
         if graph is not None:
             graph.replay()
         else:
-            step(True)
+            step()
     stop.record(stream)
     barrier()
     launches = per_step * args.steps if graph is not None else rt.launch_count() - launches0
+    # The encoder's own time inside a step: the 32 encode launches of one step alone, as a CUDA graph on the same
+    # stream (events around three replays; each replay re-reads 0.4 GB of inputs, more than the L2 holds).
+    def encodes_only() -> None:
+        for si, m in cells:
+            x = inputs[(SHAPES[si][2], m)]
+            rt.quantize_activation_cuda(x, q=14, betas=ACT_BETAS, beta_table=beta_table, keep_decoded=True)
+
+    enc_graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(enc_graph):
+        encodes_only()
+    enc_graph.replay()
+    torch.cuda.synchronize(device)
+    enc0, enc1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    enc0.record(stream)
+    for _ in range(3):
+        enc_graph.replay()
+    enc1.record(stream)
+    torch.cuda.synchronize(device)
     clocks = sampler.stop()
-    if graph is not None:
-        # the encoder's own time: one more step, call by call, with events around every encode launch; the
-        # device first spins for ~10 ms so that the host queues the whole step ahead of it and the events
-        # bracket device time only, not the gaps between two calls of the host
-        torch.cuda._sleep(20_000_000)
-        step(True)
-        torch.cuda.synchronize(device)
+    enc_ms_per_step = enc0.elapsed_time(enc1) / 3
     elapsed_ms = start.elapsed_time(stop)
     if rt.read_status(device) != 0:
         raise SystemExit("device status word is non-zero: a bounded wait in the GEMM gave up")
@@ -439,13 +442,12 @@ def run_gpu(args) -> None:
 
     # dominant kernel (by device time): the A4 encoder, HBM-bound by bytes
     pk = peaks()
-    enc_bytes = sum(m * k * 2 + m * (17 * k // 32 + 4) for m, k, _, _ in encode_events)
-    enc_ms = sum(e0.elapsed_time(e1) for _, _, e0, e1 in encode_events)
-    enc_gbs = enc_bytes / (enc_ms * 1e-3) / 1e9
-    enc_steps = 1 if graph is not None else args.steps  # steps the encode events cover
+    enc_bytes = sum(m * SHAPES[si][2] * 2 + m * (17 * SHAPES[si][2] // 32 + 4) for si, m in cells)
+    enc_gbs = enc_bytes / (enc_ms_per_step * 1e-3) / 1e9
     roofline = {"kernel": "nq_encode_rows_kernel", "bound": "hbm", "achieved": enc_gbs, "peak": pk["hbm_gbs"],
                 "unit": "GB/s", "frac": enc_gbs / pk["hbm_gbs"], "peak_source": pk["source"],
-                "share_of_step": (enc_ms / enc_steps) / ms_per_step, "launches": len(encode_events),
+                "share_of_step": enc_ms_per_step / ms_per_step, "launches": len(cells),
+                "us_per_step": round(enc_ms_per_step * 1e3, 1),
                 # DRAM bytes of the largest encode launch (8192 x 8192 BF16) from the ncu capture summarised in
                 # profiles/nq_encode_rows_kernel_8192x8192_bf16.md; its algorithmic bytes are 2MK + M(17K/32+4),
                 # the rest is the optional BF16 reconstruction the projection consumes.
@@ -456,7 +458,7 @@ def run_gpu(args) -> None:
     table, gemm = ([], None) if args.skip_extras else cell_table(torch, rt, weights, inputs, beta_table, device, pk)
 
     e2e = ({"ms": None, "h2d": 0, "d2h": 0} if args.skip_extras else
-           run_e2e(torch, rt, FusedNQRTLinear, weights, device, min(args.steps, 3), distributed))
+           run_e2e(torch, rt, FusedNQRTLinear, weights, device, max(3, min(args.steps, 10)), distributed))
     if distributed and e2e["ms"] is not None:
         t = torch.tensor([e2e["ms"]], device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -513,7 +515,8 @@ def run_gpu(args) -> None:
             "launch": "CUDA graph of one step, replayed" if graph is not None else "call by call",
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],
-                    "ms_per_step": e2e["ms"]},
+                    "ms_per_step": e2e["ms"], "launch": e2e.get("launch"), "numa": e2e.get("numa"),
+                    "result_on_host": e2e.get("nonzero_result")},
             "gpu_launches": int(launches),
             "roofline": roofline,
             "roofline_gemm": gemm,
@@ -591,59 +594,117 @@ def cell_table(torch, rt, weights, inputs, beta_table, device, pk):
     return table, best
 
 
-def run_e2e(torch, rt, FusedNQRTLinear, weights, device, steps: int, distributed: bool) -> dict:
-    """The sweep through the plugin call with pinned host inputs and outputs."""
-    layers = [FusedNQRTLinear(w, input_hadamard=True, activation_betas=ACT_BETAS).to(device) for w in weights]
-    host_in, host_out = {}, {}
-    for _, _, k in SHAPES:
-        for m in TOKENS:
-            if (k, m) not in host_in:
-                host_in[(k, m)] = torch.randn(m, k, generator=torch.Generator().manual_seed(3000 + m)).bfloat16().pin_memory()
-    for si, (_, n, _) in enumerate(SHAPES):
-        for m in TOKENS:
-            host_out[(si, m)] = torch.empty(m, n, dtype=torch.bfloat16).pin_memory()
-    h2d = sum(host_in[(k, m)].numel() * 2 for _, _, k in SHAPES for m in TOKENS)
-    d2h = sum(t.numel() * 2 for t in host_out.values())
-    # Three streams: host->device copies, compute (the plugin calls) and device->host copies overlap, as a
-    # serving loop would issue them; every cell's input still crosses PCIe inside the timed region and every
-    # output is back in pinned host memory before the stop event.
-    compute = torch.cuda.current_stream(device)
-    copy_in, copy_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
-    cells = [(si, m) for si in range(len(SHAPES)) for m in TOKENS]
+def bind_to_gpu_numa_node(torch, device) -> dict:
+    """Best effort: run this process (and first-touch its pinned buffers) on the CPUs of the GPU's NUMA node.
 
-    def step() -> None:
+    Eight ranks on one host otherwise all sit on node 0 and push their copies through one memory controller.
+    Only this process's CPU affinity changes; nothing on the GPU or the host outlives the process.
+    """
+    info: dict = {"bound": False}
+    try:
+        props = torch.cuda.get_device_properties(device)
+        bdf = f"{props.pci_domain_id:04x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
+        node = int(Path(f"/sys/bus/pci/devices/{bdf}/numa_node").read_text().strip())
+        info.update({"pci": bdf, "node": node})
+        if node < 0:
+            return info
+        cpus: set[int] = set()
+        for part in Path(f"/sys/devices/system/node/node{node}/cpulist").read_text().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = cpus & set(os.sched_getaffinity(0))
+        if allowed:
+            os.sched_setaffinity(0, allowed)
+            info.update({"bound": True, "cpus": len(allowed)})
+    except Exception as error:  # no sysfs entry, no permission, old torch: leave the affinity as it is
+        info["note"] = f"{type(error).__name__}: {error}"[:120]
+    return info
+
+
+def run_e2e(torch, rt, FusedNQRTLinear, weights, device, steps: int, distributed: bool) -> dict:
+    """The sweep through the plugin call (FusedNQRTLinear.forward) with pinned host inputs and outputs.
+
+    One pinned slab holds the inputs of all 32 cells and one the outputs.  A step copies every cell's input to the
+    device, calls the module, and copies the result back; the three kinds of work run on three streams so that
+    copies in both directions overlap the kernels.  The whole step -- 32 host-to-device copies, 32 module calls,
+    32 device-to-host copies -- is captured once as a CUDA graph and the timed region replays it: every input
+    still crosses PCIe inside the timed region and every output is back in pinned host memory before the stop
+    event, but the host issues one launch per step instead of several hundred calls.
+    """
+    numa = bind_to_gpu_numa_node(torch, device)
+    layers = [FusedNQRTLinear(w, input_hadamard=True, activation_betas=ACT_BETAS).to(device) for w in weights]
+    # large cells first: their copies overlap the rest of the step, the small ones form the tail
+    cells = sorted(((si, m) for si in range(len(SHAPES)) for m in TOKENS),
+                   key=lambda c: -c[1] * (SHAPES[c[0]][1] + SHAPES[c[0]][2]))
+    in_elems = [m * SHAPES[si][2] for si, m in cells]
+    out_elems = [m * SHAPES[si][1] for si, m in cells]
+    host_in = torch.empty(sum(in_elems), dtype=torch.bfloat16).pin_memory()
+    host_out = torch.empty(sum(out_elems), dtype=torch.bfloat16).pin_memory()
+    dev_in = torch.empty(sum(in_elems), dtype=torch.bfloat16, device=device)
+    gen = torch.Generator().manual_seed(3000)
+    host_in.copy_(torch.randn(host_in.numel(), generator=gen).bfloat16())
+    in_off = [0]
+    for n in in_elems:
+        in_off.append(in_off[-1] + n)
+    out_off = [0]
+    for n in out_elems:
+        out_off.append(out_off[-1] + n)
+    h2d, d2h = host_in.numel() * 2, host_out.numel() * 2
+    compute = torch.cuda.Stream(device)
+    copy_in, copy_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
+
+    keep: list = []  # results stay allocated while another stream still reads them (for the graph: for its lifetime)
+
+    def step() -> None:  # issued on `compute`; the side streams fork from it and join it again
+        keep.clear()
         with torch.no_grad():
-            staged = []
-            for si, m in cells:
-                k = SHAPES[si][2]
-                with torch.cuda.stream(copy_in):
-                    x = host_in[(k, m)].to(device, non_blocking=True)
-                    ready = torch.cuda.Event()
-                    ready.record(copy_in)
-                staged.append((x, ready))
-            for (si, m), (x, ready) in zip(cells, staged):
-                compute.wait_event(ready)
-                y = layers[si](x)
-                x.record_stream(compute)
+            copy_in.wait_stream(compute)
+            copy_out.wait_stream(compute)
+            ready = []
+            with torch.cuda.stream(copy_in):
+                for i in range(len(cells)):
+                    dev_in[in_off[i]:in_off[i + 1]].copy_(host_in[in_off[i]:in_off[i + 1]], non_blocking=True)
+                    event = torch.cuda.Event()
+                    event.record(copy_in)
+                    ready.append(event)
+            for i, (si, m) in enumerate(cells):
+                compute.wait_event(ready[i])
+                y = layers[si](dev_in[in_off[i]:in_off[i + 1]].view(m, SHAPES[si][2]))
+                keep.append(y)
                 done = torch.cuda.Event()
                 done.record(compute)
                 with torch.cuda.stream(copy_out):
                     copy_out.wait_event(done)
-                    host_out[(si, m)].copy_(y, non_blocking=True)
-                    y.record_stream(copy_out)
+                    host_out[out_off[i]:out_off[i + 1]].view(m, SHAPES[si][1]).copy_(y, non_blocking=True)
+            compute.wait_stream(copy_in)
             compute.wait_stream(copy_out)
 
-    step()
-    torch.cuda.synchronize(device)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    copy_in.wait_stream(compute)
-    e0.record(compute)
-    copy_in.wait_event(e0)
-    for _ in range(steps):
-        step()
-    e1.record(compute)
-    torch.cuda.synchronize(device)
-    return {"ms": e0.elapsed_time(e1) / steps, "h2d": h2d, "d2h": d2h}
+    graph = None
+    with torch.cuda.stream(compute):
+        step()  # warm-up, call by call
+        torch.cuda.synchronize(device)
+        try:
+            captured = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(captured, stream=compute):
+                step()
+            captured.replay()
+            torch.cuda.synchronize(device)
+            graph = captured
+        except Exception as error:  # keep the call-by-call step if the capture is refused
+            print(f"bench: end-to-end step not captured ({type(error).__name__}: {error})", file=sys.stderr)
+            torch.cuda.synchronize(device)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(compute)
+        for _ in range(steps):
+            if graph is not None:
+                graph.replay()
+            else:
+                step()
+        e1.record(compute)
+        torch.cuda.synchronize(device)
+    checksum = float(host_out[:out_elems[0]].float().abs().sum())  # the largest cell's result really is on the host
+    return {"ms": e0.elapsed_time(e1) / steps, "h2d": h2d, "d2h": d2h, "numa": numa, "nonzero_result": checksum > 0,
+            "launch": "CUDA graph of one step (copies and module calls), replayed" if graph is not None else "call by call"}
 
 
 def gemv_workload(torch, rt, device, pk, only: str | None = None) -> dict:

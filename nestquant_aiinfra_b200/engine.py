@@ -1,11 +1,20 @@
 """W4A4KV4 Llama runner: GPU weight conversion, ragged prefill and CUDA-graph decode.
 
 Counterpart of the reference's ``BatchedNQKVLlamaRunner`` (runtime/nqkv_batched_runner.py:
-eager prefill :190-225, graph decode :302-361) reduced to what drives the hot path: the
-model is a stock Hugging Face ``LlamaForCausalLM`` whose 7 projections per layer are
-``FusedNQRTLinear`` modules and whose attention goes through ``BatchedNQKVLlamaCache``.
-Because page ids are assigned on the device, one captured graph serves every decode step
-(the reference needs a second "boundary" graph and a host read of the hot lengths).
+eager prefill :190-225, graph decode :302-361): the model is a stock Hugging Face
+``LlamaForCausalLM`` whose 7 projections per layer are ``FusedNQRTLinear`` modules and whose
+attention goes through ``BatchedNQKVLlamaCache``.  Because page ids are assigned on the device,
+one captured graph serves every decode step (the reference needs a second "boundary" graph and a
+host read of the hot lengths).
+
+The runner can be driven in two ways:
+
+* as the ``RaggedDecodeBackend`` of the reference's continuous-batching engine
+  (runtime/inference_engine.py:14-32): ``prefill(input_ids)``, ``prefill_slots(input_ids,
+  positions=, write_mask=, valid_lengths=)``, ``capture(...)``, ``decode(token, positions=,
+  active_mask=, valid_lengths=)`` returning logits, ``clear_slots(slot_mask)``;
+* with sampling kept on the device: ``prefill_slots(slots, prompts)`` and ``decode()`` returning
+  the greedy tokens of all rows (what the throughput benchmark uses).
 """
 
 from __future__ import annotations
@@ -103,19 +112,224 @@ def build_llama_w4a4kv4(*, hidden_size: int, intermediate_size: int, num_layers:
 class BatchedNQKVLlamaRunner:
     """Greedy ragged prefill + fixed-width graph decode over a ``BatchedNQKVLlamaCache``."""
 
-    def __init__(self, model: nn.Module, cache: BatchedNQKVLlamaCache) -> None:
+    def __init__(self, model: nn.Module, cache: BatchedNQKVLlamaCache, *, execution_policy: str = "full",
+                 prefill_logits: str = "last") -> None:
+        if not isinstance(model, nn.Module):
+            raise TypeError("model must be a torch module")
+        if not isinstance(cache, BatchedNQKVLlamaCache):
+            raise TypeError("cache must be a BatchedNQKVLlamaCache")
+        if execution_policy not in {"fixed", "decode", "full"}:
+            raise ValueError("execution_policy must be fixed, decode, or full")
+        if prefill_logits not in {"last", "all"}:
+            raise ValueError("prefill_logits must be last or all")
         self.model, self.cache = model, cache
         self.device = cache.device
+        self.execution_policy = execution_policy
+        # "last": prefill_slots evaluates the lm_head at the last prompt token of every row only and returns a
+        # [capacity, width, vocab] VIEW whose columns all alias that row's logits (no memory), which is what a
+        # sampler reads; "all" materialises the logits of every position as the reference does.
+        self.prefill_logits = prefill_logits
         c = cache.capacity
+        self.batch_size = c
+        self.max_cache_len = cache.max_cache_len
         self.tokens = torch.zeros((c, 1), dtype=torch.long, device=self.device)
         self.positions = torch.zeros((c, 1), dtype=torch.long, device=self.device)
         self.next_tokens = torch.zeros(c, dtype=torch.long, device=self.device)
         self.graph: torch.cuda.CUDAGraph | None = None
         self._generation = [0] * c
+        # state of the engine protocol
+        self.logits: torch.Tensor | None = None            # [capacity, 1, vocab], written by the captured step
+        self.logits_graph: torch.cuda.CUDAGraph | None = None
+        self._prepared = False
+        self.compact_prefill_calls = 0
+        self.compact_prefill_rows = 0
+        self.graph_replay_count = 0
 
+    # ------------------------------------------------------------------ reference engine protocol
+    @property
+    def graph_captured(self) -> bool:
+        return self.logits_graph is not None
+
+    def _validate_common(self, input_ids, positions, write_mask, valid_lengths) -> None:
+        if input_ids.dtype != torch.long or input_ids.ndim != 2:
+            raise ValueError("input_ids must be rank-2 torch.long")
+        if input_ids.shape[0] != self.batch_size:
+            raise ValueError("input batch must equal fixed runner capacity")
+        if positions.dtype != torch.long or positions.shape != input_ids.shape:
+            raise ValueError("positions must be torch.long and match input_ids")
+        if write_mask.dtype != torch.bool or write_mask.shape != input_ids.shape:
+            raise ValueError("write_mask must be bool and match input_ids")
+        if valid_lengths.dtype != torch.long or tuple(valid_lengths.shape) != (self.batch_size,):
+            raise ValueError("valid_lengths must have shape [batch_size]")
+        if any(t.device != self.device for t in (input_ids, positions, write_mask, valid_lengths)):
+            raise ValueError("runner inputs must be on the model CUDA device")
+        if bool(write_mask.any().item()):
+            written = positions[write_mask]
+            if int(written.min().item()) < 0:
+                raise ValueError("written positions must be non-negative")
+            if int(written.max().item()) >= self.max_cache_len:
+                raise ValueError("written positions exceed the NQKV cache")
+
+    def _register_new_rows(self, row_mask: torch.Tensor) -> None:
+        assignments = []
+        for slot in row_mask.nonzero(as_tuple=False).flatten().cpu().tolist():
+            try:
+                self.cache.manager.sequence_id(slot)
+            except KeyError:
+                self._generation[slot] += 1
+                assignments.append((f"slot-{slot}-generation-{self._generation[slot]}", slot))
+        if assignments:
+            self.cache.register_batch(assignments)
+
+    def _hidden(self, input_ids: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
+        """Decoder stack only; ends the cache's prefill transaction (releasing the rows after a failure)."""
+        try:
+            with fused_rope_scope():
+                hidden = self.model.model(input_ids=input_ids, position_ids=positions, past_key_values=self.cache,
+                                          use_cache=True).last_hidden_state
+        except Exception:
+            self.cache.finish_prefill_page_transaction(success=False)
+            raise
+        self.cache.finish_prefill_page_transaction(success=True)
+        return hidden
+
+    def _prefill_logits(self, hidden: torch.Tensor, write_mask: torch.Tensor) -> torch.Tensor:
+        """``[rows, width, vocab]`` logits of a prefill, per the ``prefill_logits`` policy."""
+        if self.prefill_logits == "all" or hidden.shape[1] == 1:
+            return self.model.lm_head(hidden)
+        rows, width = write_mask.shape
+        last = (write_mask.sum(dim=1) - 1).clamp_min(0)
+        picked = self.model.lm_head(hidden[torch.arange(rows, device=self.device), last])
+        return picked[:, None, :].expand(rows, width, picked.shape[-1])
+
+    def _engine_prefill(self, input_ids: torch.Tensor) -> torch.Tensor:
+        """Warm all fixed rows with ``input_ids [capacity, width]``; the engine clears them right afterwards."""
+        if input_ids.dtype != torch.long or input_ids.ndim != 2:
+            raise ValueError("input_ids must be rank-2 torch.long")
+        if input_ids.shape[0] != self.batch_size or input_ids.device != self.device:
+            raise ValueError("input_ids batch or device does not match the runner")
+        width = input_ids.shape[1]
+        if width < 1 or width > self.max_cache_len:
+            raise ValueError("prefill width is outside the NQKV cache")
+        positions = torch.arange(width, device=self.device).expand(self.batch_size, -1).contiguous()
+        write_mask = torch.ones_like(input_ids, dtype=torch.bool)
+        self._register_new_rows(write_mask.any(dim=1))
+        self.cache.disable_graph_decode()
+        self.cache.set_batch_state(active_mask=write_mask.any(dim=1), write_mask=write_mask)
+        logits = self._prefill_logits(self._hidden(input_ids, positions), write_mask)
+        self._prepared = True
+        return logits
+
+    @torch.inference_mode()
+    def prefill(self, input_ids: torch.Tensor) -> torch.Tensor:
+        return self._engine_prefill(input_ids)
+
+    def _engine_prefill_slots(self, input_ids, positions, write_mask, valid_lengths) -> torch.Tensor:
+        if not self._prepared:
+            raise RuntimeError("initial prefill must prepare the runner")
+        self._validate_common(input_ids, positions, write_mask, valid_lengths)
+        row_active = write_mask.any(dim=1)
+        self._register_new_rows(row_active)
+        self.cache.disable_graph_decode()
+        active_count = int(row_active.sum().item())
+        if self.execution_policy != "full" or active_count in (0, self.batch_size):
+            self.cache.set_batch_state(active_mask=row_active, write_mask=write_mask)
+            return self._prefill_logits(self._hidden(input_ids, positions), write_mask)
+        # only the rows that write take part in the forward
+        self.compact_prefill_calls += 1
+        self.compact_prefill_rows += active_count
+        compact_mask = write_mask[row_active]
+        self.cache.set_prefill_execution_state(slot_ids=self.cache.slot_ids[row_active], write_mask=compact_mask)
+        compact = self._prefill_logits(self._hidden(input_ids[row_active], positions[row_active]), compact_mask)
+        if self.prefill_logits == "last" and compact.shape[1] > 1:
+            picked = torch.zeros((self.batch_size, compact.shape[-1]), device=self.device, dtype=compact.dtype)
+            picked[row_active] = compact[:, 0]
+            return picked[:, None, :].expand(self.batch_size, input_ids.shape[1], picked.shape[-1])
+        logits = torch.zeros((self.batch_size, compact.shape[1], compact.shape[2]), device=self.device, dtype=compact.dtype)
+        logits[row_active] = compact
+        return logits
+
+    def _logits_step(self) -> None:
+        with fused_rope_scope():
+            out = self.model(input_ids=self.tokens, position_ids=self.positions, past_key_values=self.cache,
+                             use_cache=True).logits
+        self.logits.copy_(out)
+
+    @torch.inference_mode()
+    def capture(self, sample_token: torch.Tensor, *, positions: torch.Tensor, active_mask: torch.Tensor,
+                valid_lengths: torch.Tensor) -> None:
+        """Capture ONE fixed-width decode step that returns logits (inactive rows are masked on the device;
+        full hot pages are detected and packed inside the same graph, so no boundary graph is needed)."""
+        if not self._prepared:
+            raise RuntimeError("prefill must prepare the runner before warmup")
+        if self.logits_graph is not None:
+            return
+        self._validate_common(sample_token, positions, active_mask, valid_lengths)
+        if sample_token.shape[1] != 1:
+            raise ValueError("decode capture takes one token per row")
+        self.tokens.copy_(sample_token)
+        self.positions.copy_(positions)
+        self.cache.active_mask.copy_(active_mask[:, 0])
+        self.cache.set_decode_state()
+        vocab = self.model.config.vocab_size
+        dtype = next(self.model.parameters()).dtype
+        self.logits = torch.zeros((self.batch_size, 1, vocab), device=self.device, dtype=dtype)
+        state = self._snapshot()
+        side = torch.cuda.Stream(self.device)
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(side):
+            self._logits_step()  # warm-up: loads kernels, sizes workspaces
+        torch.cuda.current_stream(self.device).wait_stream(side)
+        torch.cuda.synchronize(self.device)
+        self._restore(state)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self._logits_step()
+        torch.cuda.synchronize(self.device)
+        self._restore(state)
+        self.logits_graph = graph
+
+    def _engine_decode(self, token, positions, active_mask, valid_lengths) -> torch.Tensor:
+        if self.logits_graph is None or self.logits is None:
+            raise RuntimeError("capture must warm the runner before decode")
+        self._validate_common(token, positions, active_mask, valid_lengths)
+        if token.shape[1] != 1:
+            raise ValueError("decode takes one token per row")
+        self.tokens.copy_(token)
+        self.positions.copy_(positions)
+        self.cache.active_mask.copy_(active_mask[:, 0])
+        self.cache.set_decode_state()
+        self.logits_graph.replay()
+        self.graph_replay_count += 1
+        return torch.where(active_mask[:, :, None], self.logits, torch.zeros((), device=self.device, dtype=self.logits.dtype))
+
+    def clear_slots(self, slot_mask: torch.Tensor) -> None:
+        if slot_mask.dtype != torch.bool or tuple(slot_mask.shape) != (self.batch_size,):
+            raise ValueError("slot_mask must be bool with shape [batch_size]")
+        if slot_mask.device != self.device:
+            raise ValueError("slot_mask must be on the model device")
+        self.cache.release_slots(slot_mask.nonzero(as_tuple=False).flatten().cpu().tolist())
+
+    # ------------------------------------------------------------------ device-side sampling
     @torch.no_grad()
-    def prefill_slots(self, slots: Sequence[int], prompts: Sequence[torch.Tensor]) -> torch.Tensor:
-        """Whole-prompt prefill of ``prompts[i]`` into ``slots[i]``; returns the greedy next token per row."""
+    def prefill_slots(self, slots, prompts=None, *, positions: torch.Tensor | None = None,
+                      write_mask: torch.Tensor | None = None, valid_lengths: torch.Tensor | None = None) -> torch.Tensor:
+        """Two call forms.
+
+        ``prefill_slots(input_ids, positions=, write_mask=, valid_lengths=)`` is the engine protocol
+        (runtime/nqkv_batched_runner.py:190-225): ``input_ids [capacity, width]``, rows that write are
+        new requests; returns logits ``[capacity, width, vocab]`` (see ``prefill_logits``).
+
+        ``prefill_slots(slots, prompts)`` is whole-prompt prefill of ``prompts[i]`` into ``slots[i]``
+        with the sampling on the device; returns the greedy next token per row.
+        """
+        if positions is not None or write_mask is not None or valid_lengths is not None:
+            if prompts is not None or positions is None or write_mask is None or valid_lengths is None:
+                raise TypeError("the engine form takes input_ids, positions=, write_mask= and valid_lengths=")
+            with torch.inference_mode():
+                return self._engine_prefill_slots(slots, positions, write_mask, valid_lengths)
+        if prompts is None:
+            raise TypeError("prefill_slots(slots, prompts) needs the prompts")
         if len(slots) != len(prompts) or not slots:
             raise ValueError("slots and prompts must be non-empty and of equal length")
         width = max(int(p.numel()) for p in prompts)
@@ -180,7 +394,19 @@ class BatchedNQKVLlamaRunner:
         self._restore(state)
         self.graph = graph
 
-    def decode(self) -> torch.Tensor:
+    def decode(self, token: torch.Tensor | None = None, *, positions: torch.Tensor | None = None,
+               active_mask: torch.Tensor | None = None, valid_lengths: torch.Tensor | None = None) -> torch.Tensor:
+        """``decode()``: one step for every active slot, greedy tokens ``[capacity]`` sampled on the device.
+
+        ``decode(token, positions=, active_mask=, valid_lengths=)``: the engine protocol
+        (runtime/nqkv_batched_runner.py:302-361), one graph replay, returns logits ``[capacity, 1, vocab]``
+        with the rows that are not active zeroed.
+        """
+        if token is not None:
+            if positions is None or active_mask is None or valid_lengths is None:
+                raise TypeError("the engine form takes token, positions=, active_mask= and valid_lengths=")
+            with torch.inference_mode():
+                return self._engine_decode(token, positions, active_mask, valid_lengths)
         if self.graph is None:
             return self.decode_eager()
         self.graph.replay()

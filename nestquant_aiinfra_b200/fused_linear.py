@@ -10,7 +10,8 @@ input tensor object), one packed projection call, cast to the output dtype.
 
 from __future__ import annotations
 
-from typing import Any, Iterable
+from dataclasses import dataclass
+from typing import Any
 
 import torch
 from torch import nn
@@ -24,8 +25,15 @@ from .runtime.w4a4 import (PreparedNQA4Activation, PreparedNQRTLinear, linear_pa
 _BACKENDS = {"packed_w4a4_cuda_mma", "packed_w4a4_cuda_gemv_m1", "packed_w4a4"}
 
 
-class SharedHadamardCache:
-    """Reuse one inference-only Hadamard result for modules sharing an input."""
+class _SharedByIdentity:
+    """One value computed from an input tensor, handed to ``uses_per_input`` consumers of that same object.
+
+    Projections that read the same hidden state (q/k/v, gate/up) are called one after the other with
+    the very same tensor object; the first call computes, the following ones fetch, and the entry is
+    dropped when the last consumer has been served.  Inference only: a cached value carries no graph.
+    """
+
+    _what = "shared input"
 
     def __init__(self, uses_per_input: int) -> None:
         if isinstance(uses_per_input, bool) or not isinstance(uses_per_input, int):
@@ -33,84 +41,75 @@ class SharedHadamardCache:
         if uses_per_input < 2:
             raise ValueError("uses_per_input must be at least two")
         self.uses_per_input = uses_per_input
-        self._input = None
-        self._output = None
-        self._remaining = 0
-        self.hits = 0
-        self.misses = 0
+        self.hits = self.misses = 0
+        self._key: torch.Tensor | None = None
+        self._value: Any = None
+        self._left = 0
+
+    def _require_inference(self) -> None:
+        if torch.is_grad_enabled():
+            raise RuntimeError(f"{self._what} caching requires inference or no-grad mode")
+
+    def _fetch(self, inputs: torch.Tensor):
+        """The stored value if ``inputs`` is the object it was computed from (and counts the use), else None."""
+        if self._key is not inputs or self._left <= 0:
+            return None
+        value = self._value
+        self.hits += 1
+        self._left -= 1
+        if self._left == 0:
+            self.clear()
+        return value
+
+    def _store(self, inputs: torch.Tensor, value) -> None:
+        self._key, self._value, self._left = inputs, value, self.uses_per_input - 1
+        self.misses += 1
+
+    def clear(self) -> None:
+        self._key = self._value = None
+        self._left = 0
+
+
+class SharedHadamardCache(_SharedByIdentity):
+    """Reuse one Hadamard result for modules sharing an input (models/fused_linear.py:49-84)."""
+
+    _what = "shared Hadamard"
+    _IN_ENCODER = object()  # marker: the rotation runs inside the encoder launch, there is no tensor to hand out
 
     def transform(self, inputs: torch.Tensor) -> torch.Tensor:
-        if torch.is_grad_enabled():
-            raise RuntimeError("shared Hadamard caching requires inference or no-grad mode")
-        if self._input is inputs and self._output is not None:
-            self.hits += 1
-            output = self._output
-            self._remaining -= 1
-            if self._remaining == 0:
-                self.clear()
-            return output
+        self._require_inference()
+        cached = self._fetch(inputs)
+        if cached is not None and cached is not self._IN_ENCODER:
+            return cached
         output = hadamard(inputs)
-        self._input, self._output = inputs, output
-        self._remaining = self.uses_per_input - 1
-        self.misses += 1
+        if cached is None:
+            self._store(inputs, output)
         return output
 
     def note_rotation_in_encoder(self, inputs: torch.Tensor) -> None:
         """Same hit / miss accounting as ``transform`` when the encoder launch does the rotation itself."""
-        if torch.is_grad_enabled():
-            raise RuntimeError("shared Hadamard caching requires inference or no-grad mode")
-        if self._input is inputs and self._remaining > 0:
-            self.hits += 1
-            self._remaining -= 1
-            if self._remaining == 0:
-                self.clear()
-            return
-        self._input, self._output = inputs, None
-        self._remaining = self.uses_per_input - 1
-        self.misses += 1
-
-    def clear(self) -> None:
-        self._input = self._output = None
-        self._remaining = 0
+        self._require_inference()
+        if self._fetch(inputs) is None:
+            self._store(inputs, self._IN_ENCODER)
 
 
-class SharedPackedActivationCache:
-    """Reuse one packed A4 encoding for projections sharing an input tensor (by identity)."""
+class SharedPackedActivationCache(_SharedByIdentity):
+    """Reuse one packed A4 encoding for projections sharing an input tensor (models/fused_linear.py:87-127)."""
 
-    def __init__(self, uses_per_input: int) -> None:
-        if isinstance(uses_per_input, bool) or not isinstance(uses_per_input, int):
-            raise TypeError("uses_per_input must be an integer")
-        if uses_per_input < 2:
-            raise ValueError("uses_per_input must be at least two")
-        self.uses_per_input = uses_per_input
-        self._input = None
-        self._packed: PreparedNQA4Activation | None = None
-        self._remaining = 0
-        self.hits = 0
-        self.misses = 0
+    _what = "shared A4"
 
     def encode(self, inputs: torch.Tensor, *, q: int, betas: tuple[float, ...],
                beta_table: torch.Tensor | None = None,
                hadamard_block: int | None = None) -> tuple[PreparedNQA4Activation, bool]:
-        if torch.is_grad_enabled():
-            raise RuntimeError("shared A4 caching requires inference or no-grad mode")
-        if self._input is inputs and self._packed is not None:
-            self.hits += 1
-            packed = self._packed
-            self._remaining -= 1
-            if self._remaining == 0:
-                self.clear()
+        """``(packed, encoded_now)``: the second item tells the caller whether this call ran the encoder."""
+        self._require_inference()
+        packed = self._fetch(inputs)
+        if packed is not None:
             return packed, False
         packed = quantize_activation_cuda(inputs, q=q, betas=betas, beta_table=beta_table,
                                           hadamard_block=hadamard_block, keep_decoded=True)
-        self._input, self._packed = inputs, packed
-        self._remaining = self.uses_per_input - 1
-        self.misses += 1
+        self._store(inputs, packed)
         return packed, True
-
-    def clear(self) -> None:
-        self._input = self._packed = None
-        self._remaining = 0
 
 
 class SharedProjectionGroup:
@@ -353,41 +352,156 @@ def keep_decoded_weights_(model: nn.Module, device: torch.device | str | None = 
                if isinstance(module, FusedNQRTLinear))
 
 
-def convert_linears_to_fused_nqrt_(model: nn.Module, reader: Any, names: Iterable[str], *,
+HADAMARD_METADATA_FORMAT = "local_hadamard_linear_v1"  # models/rotated_linear.py:18
+_SERVED_BACKENDS = ("packed_w4a4", "packed_w4a4_cuda_mma", "packed_w4a4_cuda_gemv_m1")
+
+
+@dataclass(frozen=True)
+class FusedNQRTConversionReport:
+    """What a conversion replaced (same fields as the reference's report, models/fused_linear.py:533-540)."""
+
+    replaced_linear_names: tuple[str, ...]
+    input_hadamard_names: tuple[str, ...]
+    shared_hadamard_groups: tuple[tuple[str, ...], ...]
+    grouped_qkv_groups: tuple[tuple[str, str, str], ...]
+    w4a4_tiled_fallback_names: tuple[str, ...] = ()
+    m1_down_splitk_fallback_names: tuple[str, ...] = ()
+
+
+def _rotated_module_names(metadata) -> set[str]:
+    """Modules whose stored weight is Hadamard-rotated, from the checkpoint metadata (models/fused_linear.py:720-732)."""
+    entry = (metadata or {}).get("hadamard_rotation")
+    if entry is None:
+        return set()
+    if not isinstance(entry, dict) or entry.get("format") != HADAMARD_METADATA_FORMAT:
+        raise ValueError("unsupported or malformed Hadamard checkpoint metadata")
+    names = entry.get("converted_linear_names")
+    if not isinstance(names, list) or any(not isinstance(n, str) or not n for n in names):
+        raise ValueError("Hadamard converted module names must be nonempty strings")
+    return set(names)
+
+
+def _input_sharing_groups(names: set[str]) -> tuple[tuple[str, ...], ...]:
+    """q/k/v of one attention block and gate/up of one MLP receive the same input tensor."""
+    buckets: dict[tuple[str, str], list[str]] = {}
+    for name in sorted(names):
+        parent, _, leaf = name.rpartition(".")
+        kind = "qkv" if leaf in ("q_proj", "k_proj", "v_proj") else "gate_up" if leaf in ("gate_proj", "up_proj") else None
+        if kind is not None:
+            buckets.setdefault((parent, kind), []).append(name)
+    return tuple(tuple(group) for group in buckets.values() if len(group) > 1)
+
+
+def _name_collection(value, what: str) -> tuple[str, ...]:
+    if isinstance(value, (str, bytes)):
+        raise TypeError(f"{what} must be a collection of module names")
+    names = tuple(value)
+    if any(not isinstance(name, str) or not name for name in names):
+        raise ValueError(f"{what} must contain nonempty module names")
+    return names
+
+
+def convert_linears_to_fused_nqrt_(model: nn.Module, reader: Any, include_names, *,
+                                   output_dtype: torch.dtype | None = None, group_qkv: bool = False,
                                    compute_backend: str = "packed_w4a4_cuda_mma", activation_q: int = 14,
                                    activation_betas: tuple[float, ...] | None = None,
-                                   input_hadamard_names: Iterable[str] | None = None,
-                                   share_groups: Iterable[Iterable[str]] = (),
-                                   enable_m1_down_splitk: bool = False, **_ignored) -> dict[str, int]:
-    """Replace ``nn.Linear`` children named in ``names`` (``...proj.weight``) by packed modules.
+                                   w4a4_tiled_fallback_names=(), enable_m1_down_splitk: bool = False,
+                                   m1_down_splitk_fallback_names=()) -> FusedNQRTConversionReport:
+    """Replace the selected ``nn.Linear`` modules of ``model`` by packed NQRT modules, all or nothing.
 
-    ``share_groups`` lists module names that receive the same input tensor (q/k/v, gate/up):
-    they share one Hadamard and one A4 encode per forward, as the reference does
-    (models/fused_linear.py:616-627).
+    Signature and behaviour of the reference's converter (models/fused_linear.py:543-695):
+    ``include_names`` are MODULE names; ``reader`` is the checkpoint reader (``get_entry(name)`` with
+    ``.kind`` / ``.shape``, ``read_named_record(name)``, ``model_metadata``), e.g. the reference's
+    ``NQMCFileReader``.  Which modules rotate their input comes from the checkpoint metadata;
+    q/k/v and gate/up of one block are found by name and share one rotation and one A4 encode per
+    forward.  Everything is validated before the first module is replaced.
+
+    Differences, all forced by there being one backend here: ``compute_backend`` must be one of the
+    packed W4A4 CUDA names; ``group_qkv`` stacks q/k/v into one weight decoded and multiplied by one
+    launch sequence (the reference runs one grouped Triton kernel) and needs the modules on a CUDA
+    device at conversion time; modules listed in ``w4a4_tiled_fallback_names`` /
+    ``m1_down_splitk_fallback_names`` are accepted, reported, and run on the same kernels as the rest.
     """
-    wanted = {name[:-len(".weight")] if name.endswith(".weight") else name for name in names}
-    hadamard_names = wanted if input_hadamard_names is None else {
-        n[:-len(".weight")] if n.endswith(".weight") else n for n in input_hadamard_names}
-    caches: dict[str, tuple[SharedHadamardCache, SharedPackedActivationCache]] = {}
+    if not isinstance(model, nn.Module):
+        raise TypeError("model must be a torch.nn.Module")
+    for attribute in ("get_entry", "read_named_record"):
+        if not callable(getattr(reader, attribute, None)):
+            raise TypeError("reader must be a checkpoint reader (get_entry, read_named_record, model_metadata)")
+    requested = _name_collection(include_names, "include_names")
+    if not requested:
+        raise ValueError("include_names must contain nonempty module names")
+    if len(set(requested)) != len(requested):
+        raise ValueError("include_names must be unique")
+    if not isinstance(group_qkv, bool):
+        raise TypeError("group_qkv must be a bool")
+    if not isinstance(enable_m1_down_splitk, bool):
+        raise TypeError("enable_m1_down_splitk must be a bool")
+    tiled_names = frozenset(_name_collection(w4a4_tiled_fallback_names, "w4a4_tiled_fallback_names"))
+    splitk_names = frozenset(_name_collection(m1_down_splitk_fallback_names, "m1_down_splitk_fallback_names"))
+    wanted = set(requested)
+    if not tiled_names <= wanted:
+        raise ValueError("w4a4_tiled_fallback_names must be included in include_names")
+    if not splitk_names <= wanted:
+        raise ValueError("m1_down_splitk_fallback_names must be included in include_names")
+    if splitk_names and not enable_m1_down_splitk:
+        raise ValueError("m1_down_splitk_fallback_names requires enable_m1_down_splitk=True")
+    if compute_backend not in _SERVED_BACKENDS:
+        raise ValueError(f"unsupported fused NQRT compute_backend (this build serves {', '.join(_SERVED_BACKENDS)})")
+    if not activation_betas:
+        raise ValueError("packed_w4a4 requires activation_betas")
+
+    modules = dict(model.named_modules())
+    rotated = _rotated_module_names(getattr(reader, "model_metadata", None)) & wanted
+    share_groups = _input_sharing_groups(rotated)
+    qkv_groups: tuple[tuple[str, str, str], ...] = ()
+    if group_qkv:
+        parents = sorted({name.rpartition(".")[0] for name in rotated})
+        complete = [tuple(f"{parent}.{leaf}_proj" for leaf in ("q", "k", "v")) for parent in parents]
+        qkv_groups = tuple(group for group in complete if all(name in rotated for name in group))
+        if tiled_names & {name for group in qkv_groups for name in group}:
+            raise ValueError("w4a4_tiled_fallback_names cannot use grouped QKV replacement")
+
+    staged = []
+    for name in requested:  # validate everything first: a failure must leave the model untouched
+        module = modules.get(name)
+        if not isinstance(module, nn.Linear):
+            raise ValueError(f"module is not a Linear: {name}")
+        if module.bias is not None:
+            raise ValueError(f"the packed W4A4 CUDA path requires bias=None: {name}")
+        entry = reader.get_entry(f"{name}.weight")
+        if getattr(entry, "kind", "nestquant") != "nestquant":
+            raise ValueError(f"module weight is not packed: {name}")
+        if tuple(module.weight.shape) != tuple(entry.shape):
+            raise ValueError(f"quantized weight shape mismatch: {name}.weight")
+        staged.append((name, module))
+
+    caches = {}
     for group in share_groups:
-        members = [m for m in group if m in wanted]
-        if len(members) >= 2:
-            pair = (SharedHadamardCache(len(members)), SharedPackedActivationCache(len(members)))
-            for member in members:
-                caches[member] = pair
-    converted = 0
-    for module_name, module in list(model.named_modules()):
-        for child_name, child in list(module.named_children()):
-            full = f"{module_name}.{child_name}" if module_name else child_name
-            if full not in wanted or not isinstance(child, nn.Linear):
-                continue
-            had = full in hadamard_names
-            hcache, acache = caches.get(full, (None, None))
-            fused = FusedNQRTLinear(reader, full + ".weight", None, input_hadamard=had,
-                                    input_transform_cache=hcache if had else None,
-                                    compute_backend=compute_backend, activation_q=activation_q,
-                                    activation_betas=activation_betas, packed_activation_cache=acache,
-                                    enable_m1_down_splitk=enable_m1_down_splitk)
-            setattr(module, child_name, fused)
-            converted += 1
-    return {"converted": converted, "requested": len(wanted)}
+        pair = (SharedHadamardCache(len(group)), SharedPackedActivationCache(len(group)))
+        for name in group:
+            caches[name] = pair
+    built: dict[str, FusedNQRTLinear] = {}
+    for name, module in staged:
+        hcache, acache = caches.get(name, (None, None))
+        fused = FusedNQRTLinear(
+            reader, f"{name}.weight", None, input_hadamard=name in rotated, input_transform_cache=hcache,
+            output_dtype=module.weight.dtype if output_dtype is None else output_dtype,
+            compute_backend=compute_backend, activation_q=activation_q, activation_betas=tuple(activation_betas),
+            packed_activation_cache=acache,
+            enable_m1_down_splitk=enable_m1_down_splitk and name not in splitk_names)
+        fused.to(device=module.weight.device)
+        fused.train(module.training)
+        built[name] = fused
+    for group in qkv_groups:
+        device = modules[group[0]].weight.device
+        if device.type != "cuda":
+            raise ValueError("group_qkv stacks the packed weights on the device: move the model to CUDA first")
+        SharedProjectionGroup([built[name] for name in group], device=device)
+    for name, _ in staged:
+        parent_name, _, child_name = name.rpartition(".")
+        setattr(model if not parent_name else modules[parent_name], child_name, built[name])
+    return FusedNQRTConversionReport(
+        replaced_linear_names=tuple(sorted(requested)), input_hadamard_names=tuple(sorted(rotated)),
+        shared_hadamard_groups=share_groups, grouped_qkv_groups=qkv_groups,
+        w4a4_tiled_fallback_names=tuple(sorted(tiled_names)),
+        m1_down_splitk_fallback_names=tuple(sorted(splitk_names)))

@@ -12,6 +12,16 @@ captured graph serves boundary and non-boundary steps; a prefill chunk that cont
 sequence reads the pages it has just written plus the hot tail (the reference only prefills from
 empty slots, with SDPA over the chunk's BF16 K/V -- which is what a prefill from empty slots does
 here too).
+
+Two ways to drive the cache:
+
+* the reference's runner protocol (runtime/nqkv_batched_hf_backend.py:147-354, 493-531):
+  ``set_batch_state`` / ``set_decode_execution_state`` / ``set_prefill_execution_state`` /
+  ``enable_graph_decode`` / ``disable_graph_decode`` / ``finish_prefill_page_transaction`` and the
+  ``manager`` object its runner reaches into.  The reference's ``BatchedNQKVLlamaRunner`` and
+  ``ContinuousBatchInferenceEngine`` can drive this class unchanged;
+* ``set_decode_state`` / ``set_prefill_state`` of this package's own runner, which additionally
+  allows a chunk to continue a cached sequence and one graph for every decode step.
 """
 
 from __future__ import annotations
@@ -31,6 +41,54 @@ from .runtime.kv import (BatchedNQKVAttentionWorkspace, NQKVHotColdCache, NQKVPa
                          nqkv_prefill_attention)
 
 BATCHED_NQKV_ATTENTION_NAME = "nestquant_batched_nqkv_k1"
+
+
+class StaticPageManager:
+    """What the reference's runner expects behind ``cache.manager`` (runtime/nqkv_batch_manager.py).
+
+    The reference reserves the target page of every slot that is about to fill its hot tail on the
+    host, commits the reservation after the forward and cancels it when the forward failed
+    (runtime/nqkv_batched_runner.py:344-359).  Here the page a slot publishes next is a pure function
+    of the device-side page table (``slot * max_pages + page_counts[slot]``, computed inside the same
+    launch sequence as the pack), so there is nothing to reserve, commit or cancel: the three calls
+    are kept for the runner and do nothing.
+    """
+
+    def __init__(self, owner: "BatchedNQKVLlamaCache") -> None:
+        self._owner = owner
+
+    @property
+    def layer_caches(self) -> list[NQKVHotColdCache]:
+        return self._owner.layer_caches
+
+    @property
+    def request_ids(self) -> tuple[Hashable, ...]:
+        return tuple(self._owner._sequence_of_slot.values())
+
+    @property
+    def active_requests(self) -> int:
+        return len(self._owner._sequence_of_slot)
+
+    def sequence_id(self, slot: int) -> Hashable:
+        return self._owner._sequence_of_slot[slot]  # KeyError for a free slot, as the runner expects
+
+    def register(self, sequence_id: Hashable, *, slot: int) -> None:
+        self._owner.register(sequence_id, slot=slot)
+
+    def register_batch(self, assignments: Sequence[tuple[Hashable, int]]) -> None:
+        self._owner.register_batch(assignments)
+
+    def release_slots(self, slots: Sequence[int]) -> tuple[Hashable, ...]:
+        return self._owner.release_slots(slots)
+
+    def reserve_graph_transition_pages(self, slots: Sequence[int]) -> tuple[int, ...]:
+        return ()
+
+    def commit_graph_transition_pages(self, slots: Sequence[int]) -> None:
+        return None
+
+    def cancel_graph_transition_pages(self, slots: Sequence[int]) -> None:
+        return None
 
 
 class BatchedNQKVLlamaCache(Cache):
@@ -57,7 +115,9 @@ class BatchedNQKVLlamaCache(Cache):
             pool = NQKVPagePool(capacity=capacity * max_pages, page_size=page_size, num_kv_heads=num_kv_heads,
                                 head_dim=head_dim, q=q, key_betas=key_betas, value_betas=value_betas,
                                 output_dtype=dtype, device=target)
-            self.layer_caches.append(NQKVHotColdCache(pool, max_sequences=capacity, max_pages_per_sequence=max_pages))
+            layer = NQKVHotColdCache(pool, max_sequences=capacity, max_pages_per_sequence=max_pages)
+            pool.page_accounting = (lambda c=layer: c.page_counts.sum().item())  # ids are assigned on the device
+            self.layer_caches.append(layer)
         self.capacity, self.num_layers = capacity, num_layers
         self.num_query_heads, self.num_kv_heads, self.head_dim = num_query_heads, num_kv_heads, head_dim
         self._max_cache_len, self.page_size, self.max_pages = max_cache_len, page_size, max_pages
@@ -76,6 +136,21 @@ class BatchedNQKVLlamaCache(Cache):
         self._bulk_plan = None
         self._prefill_workspace: BatchedNQKVAttentionWorkspace | None = None
         self._sequence_of_slot: dict[int, Hashable] = {}
+        # state of the reference's runner protocol
+        self.manager = StaticPageManager(self)
+        self.boundary_mask = torch.zeros(capacity, device=target, dtype=torch.bool)
+        self._write_mask: torch.Tensor | None = None
+        self._k1_mask: torch.Tensor | None = None          # active rows of an eager one-token forward
+        self._graph_decode_enabled = False
+        self._graph_boundary_pack_enabled = False
+        self._fresh_slots: set[int] = set()                # registered, nothing written yet
+        self._transaction_slots: tuple[int, ...] = ()      # slots the running prefill writes to
+        # switches the reference's runner sets; every ragged layout goes through the same writer here
+        self.ragged_subpage_enabled = True
+        self.ragged_full_page_pack_enabled = True
+        self.ragged_cross_page_enabled = True
+        self.ragged_multi_page_enabled = True
+        self.multi_page_batched_pack_enabled = True
 
     # ------------------------------------------------------------------ host control plane
 
@@ -93,9 +168,10 @@ class BatchedNQKVLlamaCache(Cache):
         if slot in self._sequence_of_slot:
             raise RuntimeError(f"slot {slot} is already registered")
         for cache in self.layer_caches:
-            cache.register(slot)
+            cache.register(slot, sequence_id)
         self.active_mask[slot] = True
         self._sequence_of_slot[slot] = sequence_id
+        self._fresh_slots.add(int(slot))
 
     def register_batch(self, assignments: Sequence[tuple[Hashable, int]]) -> None:
         """Register several sequences at once (one index upload instead of scalar writes per slot and layer)."""
@@ -112,6 +188,9 @@ class BatchedNQKVLlamaCache(Cache):
         self.active_mask.index_fill_(0, index, True)
         for sequence_id, slot in assignments:
             self._sequence_of_slot[slot] = sequence_id
+            self._fresh_slots.add(int(slot))
+            for cache in self.layer_caches:
+                cache._slot_of_sequence[sequence_id] = slot
 
     def release_slots(self, slots: Sequence[int]) -> tuple[Hashable, ...]:
         released, freed = [], []
@@ -119,7 +198,10 @@ class BatchedNQKVLlamaCache(Cache):
             if slot not in self._sequence_of_slot:
                 continue
             released.append(self._sequence_of_slot.pop(slot))
+            for cache in self.layer_caches:
+                cache._slot_of_sequence.pop(released[-1], None)
             freed.append(int(slot))
+            self._fresh_slots.discard(int(slot))
         if freed:
             index = torch.tensor(freed, dtype=torch.long, device=self.device)
             for cache in self.layer_caches:
@@ -135,6 +217,10 @@ class BatchedNQKVLlamaCache(Cache):
         self.execution_slot_ids = self.slot_ids if slot_ids is None else slot_ids
         self.execution_active_mask = self.active_mask if active_mask is None else active_mask
         self._prefill = None
+        self._k1_mask = None
+        self._write_mask = None
+        self._graph_decode_enabled = False
+        self._fresh_slots.clear()  # rows of a decode step are written to on the device; none counts as empty any more
 
     def set_prefill_state(self, *, slot_ids: torch.Tensor, query_lengths: torch.Tensor, from_empty: bool = False,
                           host_slots: Sequence[int] | None = None, host_lengths: Sequence[int] | None = None) -> None:
@@ -154,15 +240,129 @@ class BatchedNQKVLlamaCache(Cache):
         self._prefill_from_empty = bool(from_empty)
         self._bulk_plan = None
         self._bulk_host = None
+        self._k1_mask = None
+        self._graph_decode_enabled = False
         if from_empty and host_slots is not None and host_lengths is not None:
             if len(host_slots) != slot_ids.numel() or len(host_lengths) != slot_ids.numel():
                 raise ValueError("host_slots / host_lengths must match slot_ids")
             self._bulk_host = ([int(v) for v in host_slots], [int(v) for v in host_lengths])
+            self._fresh_slots.difference_update(self._bulk_host[0])
+
+    # ------------------------------------------------------------------ the reference's runner protocol
+    @property
+    def max_cache_len(self) -> int:
+        return self._max_cache_len
+
+    @property
+    def graph_decode_enabled(self) -> bool:
+        return self._graph_decode_enabled
+
+    def _enter_rows(self, slot_ids: torch.Tensor, write_mask: torch.Tensor) -> None:
+        """Common part of the two prefill-capable states: row ``i`` writes ``write_mask[i].sum()`` tokens to ``slot_ids[i]``."""
+        host_mask = write_mask.detach().cpu()
+        counts = host_mask.sum(dim=1).tolist()
+        width = write_mask.shape[1]
+        for row, count in enumerate(counts):  # the writers take prefix masks (right-padded prompts)
+            if count and not bool(host_mask[row, :count].all()):
+                raise ValueError("write_mask rows must be prefixes (valid tokens first, padding after)")
+        slots = slot_ids.tolist()
+        written = [(slot, count) for slot, count in zip(slots, counts) if count]
+        self._write_mask = write_mask
+        self._transaction_slots = tuple(slot for slot, _ in written)
+        self._graph_decode_enabled = False
+        self._bulk_plan = None
+        self._bulk_host = None
+        if width == 1:
+            # one token per row: the decode writer and the paged decode kernel, as the reference does for T = 1
+            self._prefill = None
+            self._k1_mask = write_mask[:, 0].contiguous()
+        else:
+            self._k1_mask = None
+            self._prefill = (slot_ids, write_mask.sum(dim=1).to(torch.int32))
+            self._prefill_from_empty = True  # the reference's prefill semantic: SDPA over the chunk's own K/V
+            if written and all(slot in self._fresh_slots for slot, _ in written):
+                self._bulk_host = (slots, [int(c) for c in counts])  # rows with 0 tokens are skipped by the plan
+        self._fresh_slots.difference_update(slot for slot, _ in written)
+
+    def set_batch_state(self, *, active_mask: torch.Tensor, write_mask: torch.Tensor) -> None:
+        """Rows of the next forward are the ``capacity`` logical slots (runtime/nqkv_batched_hf_backend.py:147-280)."""
+        if active_mask.dtype != torch.bool or tuple(active_mask.shape) != (self.capacity,):
+            raise ValueError("active_mask must be bool with shape [capacity]")
+        if write_mask.dtype != torch.bool or write_mask.ndim != 2:
+            raise ValueError("write_mask must be bool with shape [capacity, tokens]")
+        if write_mask.shape[0] != self.capacity:
+            raise ValueError("write_mask batch must equal cache capacity")
+        if active_mask.device != self.device or write_mask.device != self.device:
+            raise ValueError("batch state tensors must be on the cache device")
+        if bool((write_mask.any(dim=1) & ~active_mask).any().item()):
+            raise ValueError("inactive rows cannot request KV writes")
+        self.active_mask.copy_(active_mask)
+        self.execution_slot_ids = self.slot_ids
+        self.execution_active_mask = self.active_mask
+        self._enter_rows(self.slot_ids, write_mask)
+
+    def set_decode_execution_state(self, *, slot_ids: torch.Tensor, active_mask: torch.Tensor) -> None:
+        """Map compact one-token rows to logical slots (runtime/nqkv_batched_hf_backend.py:282-317)."""
+        if slot_ids.dtype != torch.int32 or slot_ids.ndim != 1:
+            raise ValueError("execution slot_ids must be rank-1 torch.int32")
+        if active_mask.dtype != torch.bool or active_mask.shape != slot_ids.shape:
+            raise ValueError("execution active_mask must be bool and match slot_ids")
+        if slot_ids.device != self.device or active_mask.device != self.device:
+            raise ValueError("execution state tensors must be on the cache device")
+        if not 1 <= slot_ids.numel() <= self.capacity:
+            raise ValueError("execution row count must be within cache capacity")
+        if bool(((slot_ids < 0) | (slot_ids >= self.capacity)).any().item()):
+            raise ValueError("execution slot_ids are outside logical capacity")
+        selected = slot_ids[active_mask]
+        if selected.numel() != torch.unique(selected).numel():
+            raise ValueError("active execution rows must map to unique logical slots")
+        self.execution_slot_ids = slot_ids
+        self.execution_active_mask = active_mask
+        self._write_mask = active_mask[:, None]
+        self._prefill = None
+        self._k1_mask = None
+        self._bulk_host = None
+        self._transaction_slots = ()
+
+    def set_prefill_execution_state(self, *, slot_ids: torch.Tensor, write_mask: torch.Tensor) -> None:
+        """Compact prefill rows: row ``i`` writes to logical slot ``slot_ids[i]`` (:319-333)."""
+        if write_mask.dtype != torch.bool or write_mask.ndim != 2:
+            raise ValueError("execution write_mask must be rank-2 bool")
+        self.set_decode_execution_state(slot_ids=slot_ids, active_mask=write_mask.any(dim=1))
+        self._enter_rows(slot_ids, write_mask)
+
+    def enable_graph_decode(self, *, boundary_pack: bool = False) -> None:
+        """One-token updates go through the host-free writer; full hot pages are packed only when
+        ``boundary_pack`` is set, for the rows of ``boundary_mask`` (:335-349)."""
+        self._graph_decode_enabled = True
+        self._graph_boundary_pack_enabled = bool(boundary_pack)
+        self._write_mask = self.execution_active_mask[:, None]
+        self._prefill = None
+        self._k1_mask = None
+        self._bulk_host = None
+        self._transaction_slots = ()
+        self._fresh_slots.clear()
+
+    def disable_graph_decode(self) -> None:
+        self._graph_decode_enabled = False
+        self._graph_boundary_pack_enabled = False
+
+    def finish_prefill_page_transaction(self, *, success: bool) -> None:
+        """End of one eager prefill forward (:493-531).  Pages have static ids, so there is nothing to
+        commit; after a failed forward the slots it wrote to are released, as the reference does,
+        so that no half-written sequence stays registered."""
+        slots = self._transaction_slots
+        self._transaction_slots = ()
+        self._bulk_host = None
+        self._bulk_plan = None
+        self.boundary_mask.zero_()
+        if not success and slots:
+            self.release_slots(slots)
 
     # ------------------------------------------------------------------ Cache interface
-    def _pack_full_pages(self, cache: NQKVHotColdCache) -> None:
+    def _pack_full_pages(self, cache: NQKVHotColdCache, mask: torch.Tensor | None = None) -> None:
         torch.add(self._page_base, cache.page_counts, out=cache.graph_target_page_ids)
-        launch_pack_full_hot_pages_graph_safe(cache, boundary_mask=self._all_slots)
+        launch_pack_full_hot_pages_graph_safe(cache, boundary_mask=self._all_slots if mask is None else mask)
 
     def update(self, key_states: torch.Tensor, value_states: torch.Tensor, layer_idx: int, cache_kwargs=None):
         self._validate_layer(layer_idx)
@@ -176,9 +376,13 @@ class BatchedNQKVLlamaCache(Cache):
         if tokens == 1 and self._prefill is None:
             if rows != self.execution_slot_ids.numel():
                 raise ValueError("decode rows do not match the execution slot ids")
+            mask = self.execution_active_mask if self._k1_mask is None else self._k1_mask
             _launch_append_hot_k1_graph_safe(rotated_key[:, :, 0], value_states[:, :, 0].to(self.dtype), cache,
-                                             slot_ids=self.execution_slot_ids, active_mask=self.execution_active_mask)
-            self._pack_full_pages(cache)
+                                             slot_ids=self.execution_slot_ids, active_mask=mask)
+            if not self._graph_decode_enabled:
+                self._pack_full_pages(cache)
+            elif self._graph_boundary_pack_enabled:  # the reference's boundary graph: only the rows the runner marked
+                self._pack_full_pages(cache, self.boundary_mask)
             return rotated_key, value_states
         if self._prefill is None:
             raise RuntimeError("multi-token update needs set_prefill_state(slot_ids, query_lengths)")
@@ -206,15 +410,17 @@ class BatchedNQKVLlamaCache(Cache):
         slots, lengths = self._bulk_host
         page, device = self.page_size, self.device
         full_idx, page_ids, tail_src, tail_slot, tail_pos = [], [], [], [], []
-        table = torch.full((len(slots), self.max_pages), -1, dtype=torch.int32)
-        for row, (slot, length) in enumerate(zip(slots, lengths)):
+        rows = [(row, slot, length) for row, (slot, length) in enumerate(zip(slots, lengths)) if length > 0]
+        slots, lengths = [slot for _, slot, _ in rows], [length for _, _, length in rows]
+        table = torch.full((len(rows), self.max_pages), -1, dtype=torch.int32)
+        for index, (row, slot, length) in enumerate(rows):
             if length > tokens or length // page > self.max_pages:
                 raise ValueError("prefill length exceeds the chunk or the cache length")
             full, rest = length // page, length % page
             full_idx.append(torch.arange(full * page) + row * tokens)
             ids = torch.arange(full) + slot * self.max_pages
             page_ids.append(ids)
-            table[row, :full] = ids.to(torch.int32)
+            table[index, :full] = ids.to(torch.int32)
             tail_src.append(torch.arange(rest) + row * tokens + full * page)
             tail_slot.append(torch.full((rest,), slot))
             tail_pos.append(torch.arange(rest))
@@ -276,14 +482,33 @@ class BatchedNQKVLlamaCache(Cache):
             active_mask=self.execution_active_mask, attention_scale=scale, workspace=workspace)
         return output.unsqueeze(1)
 
-    def prefill(self, layer_idx: int, query_states: torch.Tensor, *, scale: float,
-                key_states: torch.Tensor | None = None, value_states: torch.Tensor | None = None) -> torch.Tensor:
+    def prefill(self, *args, scale: float, key_states: torch.Tensor | None = None,
+                value_states: torch.Tensor | None = None) -> torch.Tensor:
         """Causal attention of a whole chunk: ``[rows, Hq, T, D]`` -> ``[rows, T, Hq, D]``.
+
+        Called as ``prefill(layer_idx, query_states, scale=..., key_states=..., value_states=...)`` by this
+        package's attention interface, or in the reference's form ``prefill(query, key, value,
+        attention_mask, scale=...)`` (runtime/nqkv_batched_hf_backend.py:569-589), which has no layer index
+        and always means the chunk's own K/V.
 
         A prefill from empty slots uses the chunk's BF16 keys (already rotated by ``update``) and values,
         right-padded rows included (causality keeps valid queries away from the padding); any other
         chunk reads the pages just written and the hot tail.
         """
+        if args and isinstance(args[0], torch.Tensor):  # the reference's call form
+            if len(args) != 4:
+                raise TypeError("prefill(query, key, value, attention_mask, *, scale) takes four tensors")
+            query_states, key_states, value_states, attention_mask = args
+            rotated_query = (query_states if rotation_done(query_states) and query_states.dtype == self.dtype
+                             else hadamard(query_states.float()).to(self.dtype))
+            out = torch.nn.functional.scaled_dot_product_attention(
+                rotated_query, key_states.to(self.dtype), value_states.to(self.dtype), attn_mask=attention_mask,
+                dropout_p=0.0, is_causal=attention_mask is None, scale=scale,
+                enable_gqa=self.num_query_heads != self.num_kv_heads)
+            return out.transpose(1, 2)
+        if len(args) != 2:
+            raise TypeError("prefill(layer_idx, query_states, *, scale, key_states, value_states)")
+        layer_idx, query_states = args
         self._validate_layer(layer_idx)
         if self._prefill is None:
             raise RuntimeError("prefill attention needs set_prefill_state(slot_ids, query_lengths)")

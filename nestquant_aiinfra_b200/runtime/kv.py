@@ -82,6 +82,7 @@ class NQKVPagePool:
         self.beta_table = torch.tensor(self.betas, device=target, dtype=torch.float32)
         self.value_beta_table = torch.tensor(self.value_beta_values, device=target, dtype=torch.float32)
         self._free = list(range(capacity - 1, -1, -1))
+        self.page_accounting = None  # optional callable returning the pages in use (see ``allocated_pages``)
         # opt-in decoded shadow of the code streams (``enable_lattice_shadow``): int8 [capacity, P*H*D]
         self.key_lattice: torch.Tensor | None = None
         self.value_lattice: torch.Tensor | None = None
@@ -119,6 +120,14 @@ class NQKVPagePool:
         return len(self._free)
 
     @property
+    def allocated_pages(self) -> int:
+        """Pages in use: handed out by ``allocate``, or -- for an owner that assigns page ids on the device --
+        the pages its page tables hold (``page_accounting``; reads the device)."""
+        if self.page_accounting is not None:
+            return int(self.page_accounting())
+        return self.capacity - len(self._free)
+
+    @property
     def page_payload_bytes(self) -> int:
         return 2 * (self._code_bytes + self._beta_bytes + 4 * self._row_count)
 
@@ -151,6 +160,7 @@ class NQKVHotColdCache:
         self.hot_keys = torch.zeros(shape, device=dev, dtype=pool.output_dtype)
         self.hot_values = torch.zeros_like(self.hot_keys)
         self.graph_target_page_ids = torch.zeros(s, dtype=torch.int32, device=dev)
+        self._slot_of_sequence: dict = {}
 
     # the reference reaches these through ``cache.cold_cache``; keep both spellings
     @property
@@ -161,9 +171,15 @@ class NQKVHotColdCache:
     def last_page_lens(self) -> torch.Tensor:
         return self.last_page_len
 
-    def register(self, slot: int) -> int:
+    def total_tokens(self, sequence_id) -> int:
+        """Tokens held for a sequence registered under ``sequence_id`` (reads the device)."""
+        return int(self.sequence_lengths[self._slot_of_sequence[sequence_id]].item())
+
+    def register(self, slot: int, sequence_id=None) -> int:
         if not 0 <= slot < self.max_sequences:
             raise ValueError("slot outside cache capacity")
+        if sequence_id is not None:
+            self._slot_of_sequence[sequence_id] = slot
         self.active[slot] = True
         self.page_counts[slot] = 0
         self.last_page_len[slot] = 0

@@ -252,3 +252,31 @@ def test_tp_shard_runs_single_rank():
     graph = [runner.decode().clone() for _ in range(3)]
     assert all(torch.equal(a, b) for a, b in zip(eager, graph))
     assert cache.layer_caches[0].sequence_lengths.tolist() == [40, 40, 40]
+
+
+
+def test_a_slot_at_its_cache_limit_cannot_touch_its_neighbour():
+    """Static page ids are ``slot * max_pages + page``: a slot whose page table is full must stop packing, or its next
+    id would be the first page of the following slot.  Slot 0 decodes far past the cache length; slot 1's pages, hot
+    tail and attention output must not change."""
+    from nestquant_aiinfra_b200.engine import BatchedNQKVLlamaRunner, build_llama_w4a4kv4
+
+    model, cache = build_llama_w4a4kv4(hidden_size=256, intermediate_size=512, num_layers=1, num_heads=4, num_kv_heads=2,
+                                       head_dim=64, vocab_size=128, capacity=2, max_cache_len=32, seed=5)
+    assert cache.max_pages == 2
+    runner = BatchedNQKVLlamaRunner(model, cache)
+    runner.prefill_slots([0, 1], _prompts([30, 20], seed=9))
+    layer = cache.layer_caches[0]
+    pool = layer.pool
+    before = [t.clone() for t in (pool.key_codes[2:4], pool.value_codes[2:4], pool.key_norms[2:4],
+                                  layer.hot_keys[1], layer.hot_values[1], layer.page_indices[1])]
+    cache.active_mask[1] = False          # only slot 0 decodes
+    for _ in range(40):                   # 30 + 40 tokens: well past 2 pages + a full hot tail
+        runner.decode_eager()
+    torch.cuda.synchronize()
+    assert int(layer.page_counts[0]) == 2 and int(layer.hot_lengths[0]) == 16   # saturated, nothing published beyond the table
+    assert int(layer.sequence_lengths[0]) == 48 and int(layer.sequence_lengths[1]) == 20
+    after = (pool.key_codes[2:4], pool.value_codes[2:4], pool.key_norms[2:4], layer.hot_keys[1], layer.hot_values[1],
+             layer.page_indices[1])
+    for a, b in zip(after, before):
+        assert torch.equal(a, b)
