@@ -18,6 +18,20 @@
 // Every mbarrier wait is bounded; on a time-out the role records a code in
 // the status word, raises the CTA abort flag, in-flight copies are drained and
 // TMEM is released before the CTA returns.
+//
+// FUSED variant (one launch for the whole projection): sixteen more warps per CTA
+// decode the packed NQRT4 weight -- codeword, regenerated dither, two E8 searches,
+// beta and row scale -- on the ALU pipes while the tensor pipe of the same SM runs
+// the MMAs.  Decode work is cut into units of 128 channels x 64 features that the
+// CTAs take round-robin in channel-tile order; a unit's BF16 values go to the W^
+// scratch (L2-resident for the shapes of interest), every warp bumps the channel
+// tile's arrival counter when its share of a unit is written, and a TMA producer
+// waits (bounded) until the counter of ITS channel tile says all features are
+// there before it starts loading that tile.  Output tiles are ordered channel-tile
+// major, so the first tiles become ready after 1/n_tiles of the decode and the MMAs
+// trail the decode instead of waiting for all of it.  Decode warps never wait for
+// anything, so no CTA can block another one: the kernel needs no co-residency.
+// The weight is still decoded exactly once per call.
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <math.h>
@@ -34,6 +48,9 @@ constexpr int kTileK = 64;       // K elements per stage (one 128-byte swizzle r
 constexpr int kThreadsTc = 192;  // 6 warps
 constexpr int kAccCols = 256;    // TMEM columns per accumulator buffer
 constexpr int kMaxStages = 8;
+constexpr int kDecodeWarps = 16;                              // FUSED: warps 6..21 decode the weight
+constexpr int kThreadsFused = kThreadsTc + kDecodeWarps * 32;  // 704
+constexpr int kUnitBlocks = kTileN * (kTileK / 8);            // E8 blocks per decode unit (128 channels x 64 features)
 
 struct TcParams {
     int m, n, k;        // tokens, channels, features
@@ -43,9 +60,24 @@ struct TcParams {
     void* out;          // [m, n]
     int out_bf16;
     unsigned* status;   // 0 = ok
+    int group_n;        // output tiles are visited in bands of group_n channel tiles: within a band token-tile major
+                        // (group_n = n_tiles: plain token-tile-major order)
     int splits;         // K splits per output tile (1 = none); work item = tile * splits + split
     float* partial;     // [splits, m, n] float32 partial sums when splits > 1
     unsigned* counters; // unused
+};
+
+// Operands of the decode warps (FUSED only).
+struct FusedParams {
+    const uint32_t* codes;   // packed NQRT4 streams of the weight
+    const uint8_t* beta_ids;
+    const float* norms;
+    const float* betas;
+    NqDitherSegments seg;
+    float sqrt_k;
+    uint4* w_dec;            // [n, k] BF16 scratch: written by the decode warps, read by the TMA loads of map_w
+    unsigned* ready;         // [n_tiles] warp arrivals per channel tile; zero on entry, zero again on exit
+    unsigned* exit_count;    // CTAs that have finished; the last one clears `ready`
 };
 
 struct __align__(8) TcBarriers {
@@ -58,14 +90,25 @@ struct __align__(8) TcBarriers {
     unsigned ticket;
 };
 
+// Channel and token offset of output tile `tile` (see TcParams::group_n).
+__device__ __forceinline__ void tc_tile_origin(const TcParams& p, int tile, int& n0, int& t0) {
+    const int per_band = p.group_n * p.t_tiles;
+    const int band = tile / per_band, r = tile - band * per_band;
+    const int width = min(p.group_n, p.n_tiles - band * p.group_n);
+    const int t_tile = r / width;
+    n0 = (band * p.group_n + (r - t_tile * width)) * kTileN;
+    t0 = t_tile * p.tile_t;
+}
+
 __device__ __forceinline__ void tc_fail(const TcParams& p, TcBarriers* bars, unsigned code) {
     atomicCAS(p.status, 0u, code);
     *reinterpret_cast<volatile int*>(&bars->abort_flag) = 1;
 }
 
-__global__ void __launch_bounds__(kThreadsTc, 1)
+template <bool FUSED>
+__global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsTc, 1)
 nq_w4a4_tc_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
-                       const TcParams p) {
+                       const TcParams p, const FusedParams f) {
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment required by the 128-byte swizzle
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -109,9 +152,28 @@ nq_w4a4_tc_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
             bool ok = true;
             for (int item = blockIdx.x; item < total_tiles && ok; item += gridDim.x) {
                 const int tile = item / p.splits, split = item - tile * p.splits;
-                const int n0 = (tile % p.n_tiles) * kTileN;
-                const int t0 = (tile / p.n_tiles) * p.tile_t;
+                int n0, t0;
+                tc_tile_origin(p, tile, n0, t0);
                 const int ks0 = split * k_steps_all / p.splits, ks1 = (split + 1) * k_steps_all / p.splits;
+                if (FUSED) {
+                    // every decode warp adds one arrival per unit of this channel tile
+                    const uint32_t target = (uint32_t)k_steps_all * kDecodeWarps;
+                    const uint32_t* flag = f.ready + n0 / kTileN;
+                    bool there = false;
+                    for (uint32_t poll = 0; poll < (1u << 19) && !there; ++poll) {
+                        there = ld_acquire_gpu(flag) >= target;
+                        if (!there) {
+                            if (*abort_flag) break;
+                            __nanosleep(200);
+                        }
+                    }
+                    if (!there) {
+                        tc_fail(p, bars, 5);
+                        ok = false;
+                        break;
+                    }
+                    fence_proxy_async_all();  // the decoded values were written with plain stores
+                }
                 for (int ks = ks0; ks < ks1; ++ks, ++fill) {
                     const int s = fill % p.stages;
                     const uint32_t use = fill / p.stages;
@@ -172,6 +234,32 @@ nq_w4a4_tc_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
                 if (ok) umma_commit(&bars->acc_full[buf]);
             }
         }
+    } else if (FUSED && warp >= kThreadsTc / 32) {
+        // ------------------------------------------------------------ weight decode (ALU pipes)
+        const int dt = (int)threadIdx.x - kThreadsTc;
+        const int bpr = p.k >> 3;
+        const int units = p.n_tiles * k_steps_all;
+        const float rcp_sqrt_k = nq_rcp(f.sqrt_k);
+        for (int u = blockIdx.x; u < units; u += gridDim.x) {
+            const int n_tile = u / k_steps_all, kc = u - n_tile * k_steps_all;
+#pragma unroll 1
+            for (int i = dt; i < kUnitBlocks; i += kDecodeWarps * 32) {
+                // eight consecutive threads write the 128 contiguous bytes of one channel's 64 features
+                const int row = n_tile * kTileN + (i >> 3);
+                const int64_t g = (int64_t)row * bpr + kc * (kTileK / 8) + (i & 7);
+                float r[8];
+                nq_decode_weight_block(__ldg(f.codes + g), nq_segment_base(f.seg, row) + (uint32_t)g * 8u, r);
+                const float beta = __ldg(f.betas + nq_beta_id(f.beta_ids, g));
+                const float ds = nq_div_by(__ldg(f.norms + row), f.sqrt_k, rcp_sqrt_k);  // = IEEE division
+#pragma unroll
+                for (int j = 0; j < 8; ++j) r[j] = nq_mul(nq_mul(r[j], beta), ds);
+                f.w_dec[g] = nq_pack_bf16x8(r);
+            }
+            fence_proxy_async_all();
+            __threadfence();  // every lane's stores are visible device-wide before lane 0 counts the warp in
+            __syncwarp();
+            if (lane == 0) atomicAdd(f.ready + n_tile, 1u);
+        }
     } else {
         // ------------------------------------------------------------ epilogue
         const int quarter = warp & 3;  // TMEM lane quarter this warp may read
@@ -179,8 +267,8 @@ nq_w4a4_tc_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
         for (int item = blockIdx.x; item < total_tiles; item += gridDim.x, ++local_tile) {
             const uint32_t buf = local_tile & 1, use = local_tile >> 1;
             const int tile = item / p.splits, split = item - tile * p.splits;
-            const int n0 = (tile % p.n_tiles) * kTileN;
-            const int t0 = (tile / p.n_tiles) * p.tile_t;
+            int n0, t0;
+            tc_tile_origin(p, tile, n0, t0);
             const bool ready = mbar_wait_bounded(&bars->acc_full[buf], use & 1, abort_flag);
             if (!ready) {
                 if (lane == 0) tc_fail(p, bars, 4);
@@ -223,6 +311,18 @@ nq_w4a4_tc_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
         __syncwarp();
         tc_fence_after();
         tmem_dealloc(tmem_base, 2 * kAccCols);
+    }
+    if (FUSED) {
+        // the last CTA to finish puts the arrival counters back to zero for the next call
+        if (threadIdx.x == 0) {
+            __threadfence();
+            bars->ticket = atomicAdd(f.exit_count, 1u);
+        }
+        __syncthreads();
+        if (bars->ticket == gridDim.x - 1) {
+            for (int i = threadIdx.x; i < p.n_tiles; i += blockDim.x) f.ready[i] = 0u;
+            if (threadIdx.x == 0) *f.exit_count = 0u;
+        }
     }
 }
 
@@ -308,9 +408,18 @@ size_t nq_tc_workspace_bytes(int64_t m, int64_t n, int64_t k) {
     return splits > 1 ? (size_t)splits * m * n * sizeof(float) : 256;
 }
 
-int nq_launch_tc_gemm(const void* a_dec, const void* w_dec, int64_t m, int64_t n, int64_t k, void* out,
-                      int out_dtype, void* status_word, void* partial, unsigned* counters, cudaStream_t stream) {
+namespace {
+
+struct TcPlan {
     TcParams p;
+    CUtensorMap map_w, map_a;
+    size_t smem;
+    int total;  // output work items (tiles x splits)
+};
+
+int tc_plan(TcPlan& plan, const void* a_dec, const void* w_dec, int64_t m, int64_t n, int64_t k, void* out,
+            int out_dtype, void* status_word, void* partial, unsigned* counters) {
+    TcParams& p = plan.p;
     p.splits = partial ? tc_splits(m, n, k) : 1;
     p.partial = reinterpret_cast<float*>(partial);
     p.counters = counters;
@@ -318,6 +427,7 @@ int nq_launch_tc_gemm(const void* a_dec, const void* w_dec, int64_t m, int64_t n
     p.tile_t = m > 128 ? 256 : (m > 64 ? 128 : (m > 32 ? 64 : 32));
     p.n_tiles = (int)(n / kTileN);
     p.t_tiles = (int)((m + p.tile_t - 1) / p.tile_t);
+    p.group_n = p.n_tiles;
     const size_t stage_bytes = (size_t)(kTileN + p.tile_t) * kTileK * 2;
     int stages = (int)((200 * 1024) / stage_bytes);
     if (stages > kMaxStages) stages = kMaxStages;
@@ -325,17 +435,22 @@ int nq_launch_tc_gemm(const void* a_dec, const void* w_dec, int64_t m, int64_t n
     p.out = out;
     p.out_bf16 = out_dtype == NQ_BF16;
     p.status = reinterpret_cast<unsigned*>(status_word);
-    CUtensorMap map_w, map_a;
-    int rc = make_map(&map_w, w_dec, n, k, kTileN);
+    int rc = make_map(&plan.map_w, w_dec, n, k, kTileN);
     if (rc) return rc;
-    rc = make_map(&map_a, a_dec, m, k, p.tile_t);
+    rc = make_map(&plan.map_a, a_dec, m, k, p.tile_t);
     if (rc) return rc;
-    const size_t smem = (size_t)stages * stage_bytes + sizeof(TcBarriers) + 1024;
-    // the opt-in to more than 48 KB of dynamic shared memory is a per-device attribute of the kernel
+    plan.smem = (size_t)stages * stage_bytes + sizeof(TcBarriers) + 1024;
+    plan.total = p.n_tiles * p.t_tiles * p.splits;
+    return NQ_OK;
+}
+
+// the opt-in to more than 48 KB of dynamic shared memory is a per-device attribute of each kernel
+template <bool FUSED>
+int tc_configure() {
     static bool configured[NQ_MAX_DEVICES] = {false};
     const int device = nq_current_device();
     if (device < 0 || !configured[device]) {
-        cudaError_t e = cudaFuncSetAttribute(nq_w4a4_tc_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(nq_w4a4_tc_gemm_kernel<FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              227 * 1024);
         if (e != cudaSuccess) {
             nq_set_error("nq_w4a4_gemm: cannot reserve shared memory: %s", cudaGetErrorString(e));
@@ -343,10 +458,10 @@ int nq_launch_tc_gemm(const void* a_dec, const void* w_dec, int64_t m, int64_t n
         }
         if (device >= 0) configured[device] = true;
     }
-    const int total = p.n_tiles * p.t_tiles * p.splits;
-    const int grid = total < sm_count() ? total : sm_count();
-    nq_w4a4_tc_gemm_kernel<<<grid, kThreadsTc, smem, stream>>>(map_w, map_a, p);
-    NQ_CHECK_LAUNCH("nq_w4a4_gemm(tcgen05)");
+    return NQ_OK;
+}
+
+int tc_reduce(const TcParams& p, int64_t m, int64_t n, void* out, cudaStream_t stream) {
     if (p.splits > 1) {
         const int64_t quads = m * n / 4;  // n % 128 == 0
         nq_tc_splitk_reduce_kernel<<<(unsigned)((quads + 255) / 256), 256, 0, stream>>>(
@@ -354,4 +469,54 @@ int nq_launch_tc_gemm(const void* a_dec, const void* w_dec, int64_t m, int64_t n
         NQ_CHECK_LAUNCH("nq_w4a4_gemm(split-K reduce)");
     }
     return NQ_OK;
+}
+
+}  // namespace
+
+int nq_launch_tc_gemm(const void* a_dec, const void* w_dec, int64_t m, int64_t n, int64_t k, void* out,
+                      int out_dtype, void* status_word, void* partial, unsigned* counters, cudaStream_t stream) {
+    TcPlan plan;
+    int rc = tc_plan(plan, a_dec, w_dec, m, n, k, out, out_dtype, status_word, partial, counters);
+    if (rc) return rc;
+    if ((rc = tc_configure<false>())) return rc;
+    const int grid = plan.total < sm_count() ? plan.total : sm_count();
+    nq_w4a4_tc_gemm_kernel<false><<<grid, kThreadsTc, plan.smem, stream>>>(plan.map_w, plan.map_a, plan.p, FusedParams{});
+    NQ_CHECK_LAUNCH("nq_w4a4_gemm(tcgen05)");
+    return tc_reduce(plan.p, m, n, out, stream);
+}
+
+// The whole projection in one launch: the packed weight is decoded into w_scratch by the decode warps
+// of the same kernel that multiplies it (see the header of this file).  counters: at least
+// n / 128 + 1 zeroed words, left zero.
+int nq_launch_fused_gemm(const void* a_dec, const uint8_t* w_codes, const uint8_t* w_beta_ids, const float* w_norms,
+                         const float* w_betas, const NqDitherSegments& seg, void* w_scratch, int64_t m, int64_t n,
+                         int64_t k, void* out, int out_dtype, void* status_word, void* partial, unsigned* counters,
+                         cudaStream_t stream) {
+    TcPlan plan;
+    int rc = tc_plan(plan, a_dec, w_scratch, m, n, k, out, out_dtype, status_word, partial, counters);
+    if (rc) return rc;
+    if ((rc = tc_configure<true>())) return rc;
+    // Tile order: narrow bands of channel tiles, so that the first tiles only need the first band of the weight
+    // (the MMAs then trail the decode) -- but every band streams the whole activation matrix once more, so when
+    // that matrix is larger than about half of the L2 the bands are widened to keep it to four passes over HBM.
+    const size_t a_bytes = (size_t)m * k * 2;
+    plan.p.group_n = a_bytes <= ((size_t)64 << 20) ? 2 : (plan.p.n_tiles + 3) / 4;
+    if (plan.p.group_n < 2) plan.p.group_n = 2;
+    if (plan.p.group_n > plan.p.n_tiles) plan.p.group_n = plan.p.n_tiles;
+    FusedParams f;
+    f.codes = reinterpret_cast<const uint32_t*>(w_codes);
+    f.beta_ids = w_beta_ids;
+    f.norms = w_norms;
+    f.betas = w_betas;
+    f.seg = seg;
+    f.sqrt_k = (float)sqrt((double)k);
+    f.w_dec = reinterpret_cast<uint4*>(w_scratch);
+    f.ready = counters;
+    f.exit_count = counters + plan.p.n_tiles;
+    const int units = plan.p.n_tiles * (int)(k / kTileK);
+    const int work = plan.total > units ? plan.total : units;
+    const int grid = work < sm_count() ? work : sm_count();
+    nq_w4a4_tc_gemm_kernel<true><<<grid, kThreadsFused, plan.smem, stream>>>(plan.map_w, plan.map_a, plan.p, f);
+    NQ_CHECK_LAUNCH("nq_w4a4_gemm(fused decode + tcgen05)");
+    return tc_reduce(plan.p, m, n, out, stream);
 }

@@ -348,7 +348,7 @@ def can_use_w4a4_mma_chunked_staged(activation, weight) -> bool:
 # the projection
 # ---------------------------------------------------------------------------
 def _run(activation: PreparedNQA4Activation, weight: PreparedNQRTLinear, out_dtype: torch.dtype,
-         *, use_decoded: bool = True) -> torch.Tensor:
+         *, use_decoded: bool = True, two_pass: bool = False) -> torch.Tensor:
     record = weight.record
     m, k, n = activation.token_count, activation.feature_count, weight.rows
     device = activation.code_payload.device
@@ -378,7 +378,8 @@ def _run(activation: PreparedNQA4Activation, weight: PreparedNQRTLinear, out_dty
             _ptr(out), _DTYPE_TAG[out_dtype], _ptr(workspace), ctypes.c_size_t(workspace.numel()), _stream(device))
         _lib.check(status, "linear_packed_w4a4")
         return out
-    status = library.nq_w4a4_gemm(
+    entry = library.nq_w4a4_gemm_two_pass if two_pass else library.nq_w4a4_gemm
+    status = entry(
         _ptr(activation.code_payload), _ptr(activation.beta_payload), _ptr(activation.row_norms),
         _ptr(activation.beta_table), _ptr(decoded),
         _ptr(weight.code_payload), _ptr(weight.beta_payload), _ptr(weight.row_norms), _ptr(weight.beta_table),
@@ -481,6 +482,16 @@ def linear_packed_w4a4_fp32(activation: PreparedNQA4Activation, weight: Prepared
         raise ValueError("activation or packed weight is unsupported by the W4A4 kernels")
     n = weight.rows
     return _run(activation, weight, torch.float32).reshape(*activation.original_shape[:-1], n)
+
+
+def linear_packed_w4a4_two_pass_fp32(activation: PreparedNQA4Activation, weight: PreparedNQRTLinear) -> torch.Tensor:
+    """The projection as two launches (whole-weight decode, then the tcgen05 GEMM) instead of the fused
+    kernel: a building block for measurement and the cross-check of the fused kernel (identical result)."""
+    _check_types(activation, weight)
+    if not can_use_w4a4(activation, weight) or weight.segments or weight.decoded is not None:
+        raise ValueError("the two-pass entry takes a plain packed weight")
+    n = weight.rows
+    return _run(activation, weight, torch.float32, two_pass=True).reshape(*activation.original_shape[:-1], n)
 
 
 def _regime(name: str, predicate):

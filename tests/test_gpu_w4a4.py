@@ -267,3 +267,25 @@ def test_resident_decoded_weight_argument_errors(rt, oracle):
     record, _ = make_weight_record(oracle, 64, 256, seed=3, dither_seed=4)
     with pytest.raises(TypeError):
         rt.keep_decoded_weight(record)
+
+
+
+@pytest.mark.parametrize("m,n,k", [(8, 128, 64), (40, 512, 2048), (200, 256, 1024), (520, 2048, 2048), (1300, 1024, 512)])
+def test_fused_decode_gemm_equals_the_two_launch_path(rt, oracle, m, n, k):
+    """The kernel that decodes the weight beside its own MMAs and the decode-then-GEMM pair run the same MMAs on
+    the same decoded values: results must be identical bit for bit, the status word clean, and a second call on
+    the same workspace (arrival counters back at zero) must reproduce the first."""
+    record, w_deq = make_weight_record(oracle, n, k, seed=900 + m, dither_seed=1234 + m)
+    weight = rt.prepare_fused_linear(record)
+    x = torch.randn(m, k, generator=rng(77 + m)).bfloat16().cuda()
+    act = rt.quantize_activation_cuda(x, q=14, betas=ACT_BETAS, keep_decoded=True)
+    fused = rt.linear_packed_w4a4_fp32(act, weight)
+    again = rt.linear_packed_w4a4_fp32(act, weight)
+    two_pass = rt.linear_packed_w4a4_two_pass_fp32(act, weight)
+    assert rt.read_status() == 0
+    assert torch.equal(fused, again)
+    assert torch.equal(fused, two_pass)
+    codes, beta_ids, norms = (t.cpu().numpy() for t in (act.code_payload, act.beta_payload, act.row_norms))
+    expected = oracle.gemm_bf16_operands(oracle.dequantize_rows(codes, beta_ids, norms, ACT_BETAS, m, k), w_deq)
+    actual = fused.cpu().numpy()
+    assert max_abs(actual, expected) <= MAX_ABS_TOL and rel_fro(actual, expected) <= REL_FRO_TOL
