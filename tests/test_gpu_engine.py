@@ -265,7 +265,8 @@ def test_a_slot_at_its_cache_limit_cannot_touch_its_neighbour():
                                        head_dim=64, vocab_size=128, capacity=2, max_cache_len=32, seed=5)
     assert cache.max_pages == 2
     runner = BatchedNQKVLlamaRunner(model, cache)
-    runner.prefill_slots([0, 1], _prompts([30, 20], seed=9))
+    gen = torch.Generator().manual_seed(9)
+    runner.prefill_slots([0, 1], [torch.randint(0, 128, (n,), generator=gen) for n in (30, 20)])  # ids inside this model's vocabulary
     layer = cache.layer_caches[0]
     pool = layer.pool
     before = [t.clone() for t in (pool.key_codes[2:4], pool.value_codes[2:4], pool.key_norms[2:4],
