@@ -120,9 +120,7 @@ int nq_a4_decode(const uint8_t* codes, const uint8_t* beta_ids, const float* nor
  *              left zero by every call.
  * Requirements: k % 32 == 0, n % 8 == 0, n <= 131064.  The tcgen05 path is taken for
  * m >= 8 when n % 128 == 0 and k % 64 == 0 (split-K with a deterministic reduction when few tiles):
- * ONE kernel whose decode warps turn the packed weight into BF16 tiles (dither regenerated, two E8
- * searches per block) while its tensor pipe multiplies the tiles that are already there; a bounded
- * wait of a tile for its weights that gives up leaves code 5 in the status word. */
+ * the weight is decoded once per call into the BF16 scratch of the workspace, then multiplied. */
 #define NQ_WS_COUNTER_BYTES 65536
 #define NQ_WS_STATUS_OFFSET 65532 /* last word of the counter area: device status, 0 = ok */
 size_t nq_w4a4_workspace_bytes(int64_t m, int64_t n, int64_t k);
@@ -133,17 +131,19 @@ int nq_w4a4_gemm(const uint8_t* act_codes, const uint8_t* act_beta_ids, const fl
                  int64_t w_block_offset, int64_t seed, void* out, int out_dtype,
                  void* workspace, size_t workspace_bytes, nq_stream_t stream);
 
-/* nq_w4a4_gemm with the weight decode and the tcgen05 GEMM as two launches (decode of the whole weight to
- * the BF16 scratch, then the GEMM) instead of the fused kernel that decodes beside its MMAs.  Same arguments,
- * same result bit for bit; kept as a building block for measurement and as the cross-check of the fused
- * kernel.  The reference has no counterpart (its large-M kernel decodes inside its MMA loop,
- * runtime/nqrt4_w4a4_mma.cu:606-723, once per 128-row chunk). */
-int nq_w4a4_gemm_two_pass(const uint8_t* act_codes, const uint8_t* act_beta_ids, const float* act_norms,
-                          const float* act_betas, const void* act_decoded,
-                          const uint8_t* w_codes, const uint8_t* w_beta_ids, const float* w_norms,
-                          const float* w_betas, int64_t m, int64_t n, int64_t k,
-                          int64_t w_block_offset, int64_t seed, void* out, int out_dtype,
-                          void* workspace, size_t workspace_bytes, nq_stream_t stream);
+/* nq_w4a4_gemm as ONE launch for m >= 8 (n % 128 == 0, k % 64 == 0; other shapes take nq_w4a4_gemm's path): the
+ * kernel's decode warps turn the packed weight into BF16 tiles on the ALU pipes (dither regenerated, two E8
+ * searches per block) while the tensor pipe of the same SM multiplies the tiles that are already there; a TMA
+ * producer waits (bounded; status code 5 when it gives up) for the arrival counter of its channel tile.  This is the
+ * shape of the reference's large-M kernel, which decodes inside its MMA loop (runtime/nqrt4_w4a4_mma.cu:606-723),
+ * with the weight still decoded once per call.  Same arguments and workspace as nq_w4a4_gemm, same result bit for
+ * bit.  On B200 it does not beat nq_w4a4_gemm's two launches yet, so it is a separate entry, not the default. */
+int nq_w4a4_gemm_fused(const uint8_t* act_codes, const uint8_t* act_beta_ids, const float* act_norms,
+                       const float* act_betas, const void* act_decoded,
+                       const uint8_t* w_codes, const uint8_t* w_beta_ids, const float* w_norms,
+                       const float* w_betas, int64_t m, int64_t n, int64_t k,
+                       int64_t w_block_offset, int64_t seed, void* out, int out_dtype,
+                       void* workspace, size_t workspace_bytes, nq_stream_t stream);
 
 /* The same projection for a weight that stacks the rows of several tensors sharing one input
  * (q/k/v, gate/up): one launch sequence instead of one per tensor.  The packed streams are the
@@ -192,8 +192,8 @@ int nq_bf16_gemm_tc(const void* a_bf16, const void* w_bf16, int64_t m, int64_t n
  * stream (the only entry point that synchronises).  Non-zero means a bounded
  * wait inside the tcgen05 kernel gave up: 1 = producer waiting for a free
  * stage, 2 = MMA waiting for a free accumulator, 3 = MMA waiting for a TMA
- * stage, 4 = epilogue waiting for the accumulator, 5 = producer waiting for the
- * decode warps to finish a channel tile of the weight.  No counterpart in the
+ * stage, 4 = epilogue waiting for the accumulator, 5 = (nq_w4a4_gemm_fused) producer
+ * waiting for the decode warps to finish a channel tile of the weight.  No counterpart in the
  * reference (its kernels have no device-side waits). */
 int nq_w4a4_status(const void* workspace, uint32_t* status_host, nq_stream_t stream);
 

@@ -70,7 +70,7 @@ int w4a4_gemm_impl(const uint8_t* act_codes, const uint8_t* act_beta_ids, const 
                    const uint8_t* w_codes, const uint8_t* w_beta_ids, const float* w_norms,
                    const float* w_betas, int64_t m, int64_t n, int64_t k, const NqDitherSegments& seg,
                    void* out, int out_dtype, void* workspace, size_t workspace_bytes, nq_stream_t stream,
-                   bool two_pass = false) {
+                   bool fused = false) {
     NQ_REQUIRE(w_codes && w_beta_ids && w_norms && w_betas && out, NQ_ERR_ARG, "nq_w4a4_gemm: null pointer");
     NQ_REQUIRE(act_decoded || (act_codes && act_beta_ids && act_norms && act_betas), NQ_ERR_ARG,
                "nq_w4a4_gemm: activation streams missing");
@@ -97,7 +97,7 @@ int w4a4_gemm_impl(const uint8_t* act_codes, const uint8_t* act_beta_ids, const 
     }
 
     if (m >= kTcMinM && nq_tc_supported(m, n, k)) {
-        if (!two_pass)  // one launch: the weight decode runs beside the MMAs of the same kernel
+        if (fused)  // one launch: the weight decode runs beside the MMAs of the same kernel
             return nq_launch_fused_gemm(a_dec, w_codes, w_beta_ids, w_norms, w_betas, seg, ws + c.w_dec, m, n, k, out,
                                         out_dtype, ws + NQ_WS_STATUS_OFFSET, ws + c.tc, counters, s);
         int rc = nq_w4_decode_segments(w_codes, w_beta_ids, w_norms, w_betas, n, k, seg, ws + c.w_dec, s);
@@ -136,20 +136,21 @@ extern "C" int nq_w4a4_gemm(const uint8_t* act_codes, const uint8_t* act_beta_id
                           workspace_bytes, stream);
 }
 
-// The same projection with the weight decode and the tcgen05 GEMM as two launches back to back (decode of the
-// whole weight to the BF16 scratch, then the GEMM): what nq_w4a4_gemm did before its fused kernel, kept as a
-// building block for measurement and as the cross-check of the fused kernel (both run the same MMAs on the same
-// decoded values, so their results are identical).
-extern "C" int nq_w4a4_gemm_two_pass(const uint8_t* act_codes, const uint8_t* act_beta_ids, const float* act_norms,
-                                     const float* act_betas, const void* act_decoded,
-                                     const uint8_t* w_codes, const uint8_t* w_beta_ids, const float* w_norms,
-                                     const float* w_betas, int64_t m, int64_t n, int64_t k,
-                                     int64_t w_block_offset, int64_t seed, void* out, int out_dtype,
-                                     void* workspace, size_t workspace_bytes, nq_stream_t stream) {
-    NQ_REQUIRE(k >= 32 && k % 32 == 0 && n >= 8, NQ_ERR_ARG, "nq_w4a4_gemm_two_pass: bad shape");
+// The same projection as ONE launch: the kernel's decode warps turn the packed weight into BF16 tiles (written to
+// the scratch, counted per channel tile) while its tensor pipe multiplies the tiles that are already there.  It runs
+// the same MMAs on the same decoded values as nq_w4a4_gemm, so the results are identical bit for bit.  Measured on
+// B200 it does not beat the two launches of nq_w4a4_gemm yet (the decode runs slower inside the persistent kernel
+// than alone, and the MMAs slow down while it runs), which is why it is a separate entry and not the default.
+extern "C" int nq_w4a4_gemm_fused(const uint8_t* act_codes, const uint8_t* act_beta_ids, const float* act_norms,
+                                  const float* act_betas, const void* act_decoded,
+                                  const uint8_t* w_codes, const uint8_t* w_beta_ids, const float* w_norms,
+                                  const float* w_betas, int64_t m, int64_t n, int64_t k,
+                                  int64_t w_block_offset, int64_t seed, void* out, int out_dtype,
+                                  void* workspace, size_t workspace_bytes, nq_stream_t stream) {
+    NQ_REQUIRE(k >= 32 && k % 32 == 0 && n >= 8, NQ_ERR_ARG, "nq_w4a4_gemm_fused: bad shape");
     NQ_REQUIRE(seed >= 0 && seed < ((int64_t)1 << 31) && w_block_offset >= 0 &&
                    w_block_offset + n * (k / 8) <= ((int64_t)1 << 28),
-               NQ_ERR_ARG, "nq_w4a4_gemm_two_pass: dither seed / block range outside the 31-bit counter space");
+               NQ_ERR_ARG, "nq_w4a4_gemm_fused: dither seed / block range outside the 31-bit counter space");
     return w4a4_gemm_impl(act_codes, act_beta_ids, act_norms, act_betas, act_decoded, w_codes, w_beta_ids, w_norms,
                           w_betas, m, n, k, nq_one_segment(w_block_offset, seed), out, out_dtype, workspace,
                           workspace_bytes, stream, true);

@@ -348,7 +348,7 @@ def can_use_w4a4_mma_chunked_staged(activation, weight) -> bool:
 # the projection
 # ---------------------------------------------------------------------------
 def _run(activation: PreparedNQA4Activation, weight: PreparedNQRTLinear, out_dtype: torch.dtype,
-         *, use_decoded: bool = True, two_pass: bool = False) -> torch.Tensor:
+         *, use_decoded: bool = True, fused: bool = False) -> torch.Tensor:
     record = weight.record
     m, k, n = activation.token_count, activation.feature_count, weight.rows
     device = activation.code_payload.device
@@ -378,7 +378,7 @@ def _run(activation: PreparedNQA4Activation, weight: PreparedNQRTLinear, out_dty
             _ptr(out), _DTYPE_TAG[out_dtype], _ptr(workspace), ctypes.c_size_t(workspace.numel()), _stream(device))
         _lib.check(status, "linear_packed_w4a4")
         return out
-    entry = library.nq_w4a4_gemm_two_pass if two_pass else library.nq_w4a4_gemm
+    entry = library.nq_w4a4_gemm_fused if fused else library.nq_w4a4_gemm
     status = entry(
         _ptr(activation.code_payload), _ptr(activation.beta_payload), _ptr(activation.row_norms),
         _ptr(activation.beta_table), _ptr(decoded),
@@ -484,14 +484,14 @@ def linear_packed_w4a4_fp32(activation: PreparedNQA4Activation, weight: Prepared
     return _run(activation, weight, torch.float32).reshape(*activation.original_shape[:-1], n)
 
 
-def linear_packed_w4a4_two_pass_fp32(activation: PreparedNQA4Activation, weight: PreparedNQRTLinear) -> torch.Tensor:
-    """The projection as two launches (whole-weight decode, then the tcgen05 GEMM) instead of the fused
-    kernel: a building block for measurement and the cross-check of the fused kernel (identical result)."""
+def linear_packed_w4a4_fused_fp32(activation: PreparedNQA4Activation, weight: PreparedNQRTLinear) -> torch.Tensor:
+    """The projection as ONE launch (the kernel decodes the weight beside its own MMAs) instead of the default
+    decode launch followed by the GEMM launch; identical result.  Not the default: it is not faster yet."""
     _check_types(activation, weight)
     if not can_use_w4a4(activation, weight) or weight.segments or weight.decoded is not None:
-        raise ValueError("the two-pass entry takes a plain packed weight")
+        raise ValueError("the fused entry takes a plain packed weight")
     n = weight.rows
-    return _run(activation, weight, torch.float32, two_pass=True).reshape(*activation.original_shape[:-1], n)
+    return _run(activation, weight, torch.float32, fused=True).reshape(*activation.original_shape[:-1], n)
 
 
 def _regime(name: str, predicate):

@@ -272,16 +272,16 @@ def test_resident_decoded_weight_argument_errors(rt, oracle):
 
 @pytest.mark.parametrize("m,n,k", [(8, 128, 64), (40, 512, 2048), (200, 256, 1024), (520, 2048, 2048), (1300, 1024, 512)])
 def test_fused_decode_gemm_equals_the_two_launch_path(rt, oracle, m, n, k):
-    """The kernel that decodes the weight beside its own MMAs and the decode-then-GEMM pair run the same MMAs on
-    the same decoded values: results must be identical bit for bit, the status word clean, and a second call on
-    the same workspace (arrival counters back at zero) must reproduce the first."""
+    """The kernel that decodes the weight beside its own MMAs (nq_w4a4_gemm_fused) and the default decode-then-GEMM
+    pair run the same MMAs on the same decoded values: results must be identical bit for bit, the status word
+    clean, and a second call on the same workspace (arrival counters back at zero) must reproduce the first."""
     record, w_deq = make_weight_record(oracle, n, k, seed=900 + m, dither_seed=1234 + m)
     weight = rt.prepare_fused_linear(record)
     x = torch.randn(m, k, generator=rng(77 + m)).bfloat16().cuda()
     act = rt.quantize_activation_cuda(x, q=14, betas=ACT_BETAS, keep_decoded=True)
-    fused = rt.linear_packed_w4a4_fp32(act, weight)
-    again = rt.linear_packed_w4a4_fp32(act, weight)
-    two_pass = rt.linear_packed_w4a4_two_pass_fp32(act, weight)
+    fused = rt.linear_packed_w4a4_fused_fp32(act, weight)
+    again = rt.linear_packed_w4a4_fused_fp32(act, weight)
+    two_pass = rt.linear_packed_w4a4_fp32(act, weight)
     assert rt.read_status() == 0
     assert torch.equal(fused, again)
     assert torch.equal(fused, two_pass)
