@@ -481,6 +481,13 @@ def run_gpu(args) -> None:
                 dec["ms_per_step"] = round(float(t.item()), 3)
                 dec["decode_tok_s"] = round(world * dec["requests"] / (dec["ms_per_step"] * 1e-3), 1)
                 dec["replicas"] = world
+                cont = dec.get("continuous_batch", {})
+                if "decode_tok_s" in cont:  # replicas: every rank runs the same request stream; N x the slowest rank
+                    t = torch.tensor([cont["decode_tok_s"], cont["tok_s_including_prefill"]], device=device)
+                    dist.all_reduce(t, op=dist.ReduceOp.MIN)
+                    cont["decode_tok_s"] = round(world * float(t[0].item()), 1)
+                    cont["tok_s_including_prefill"] = round(world * float(t[1].item()), 1)
+                    cont["replicas"] = world
                 resident = dec.get("resident_decoded_weights", {})
                 for leg in (resident, resident.get("with_kv_lattice_shadow", {})):  # the opt-in legs the same way
                     if "ms_per_step" in leg:
@@ -870,6 +877,75 @@ def kv_workload(torch, rt, device, pk) -> dict:
     }
 
 
+def continuous_batch(torch, runner, cache, device, *, total_requests: int = 96, new_tokens: int = 256,
+                     prefill_group: int = 8, seed: int = 129) -> dict:
+    """Config 3 as a continuous batch: more requests than slots, prompts U[128, 2048], `new_tokens` greedy tokens each.
+
+    Requests are admitted `prefill_group` at a time into free slots (whole-prompt prefill, eager), every admitted
+    request decodes one token per step of the ONE captured graph, a request that has its tokens releases its slot
+    and the next waiting requests join.  Sampling stays on the device; the host only counts.
+    """
+    from collections import deque
+
+    capacity = cache.capacity
+    cache.release_slots(list(range(capacity)))
+    gen = torch.Generator().manual_seed(seed)
+    lengths = torch.randint(128, 2049, (total_requests,), generator=gen).tolist()
+    prompts = [torch.randint(0, 128256, (n,), generator=gen) for n in lengths]
+    waiting = deque(range(total_requests))
+    owner = [None] * capacity   # request of a slot
+    left = [0] * capacity       # decode tokens the slot's request still needs
+    generated = prefilled = steps = active_rows = 0
+    decode_events, prefill_s = [], 0.0
+    torch.cuda.synchronize(device)
+    wall0 = time.perf_counter()
+    while waiting or any(left):
+        free = [s for s in range(capacity) if owner[s] is None]
+        running = capacity - len(free)
+        if waiting and free and (len(free) >= prefill_group or running == 0 or len(waiting) <= len(free)):
+            group = [waiting.popleft() for _ in range(min(prefill_group, len(free), len(waiting)))]
+            slots = free[:len(group)]
+            t0 = time.perf_counter()
+            runner.prefill_slots(slots, [prompts[i] for i in group])   # also samples each request's first token
+            torch.cuda.synchronize(device)
+            prefill_s += time.perf_counter() - t0
+            for slot, request in zip(slots, group):
+                owner[slot], left[slot] = request, new_tokens - 1
+                prefilled += lengths[request]
+                generated += 1
+            if runner.graph is None:
+                runner.capture_decode_graph()
+        if any(left):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            runner.decode()
+            e1.record()
+            decode_events.append((e0, e1))
+            steps += 1
+            done = []
+            for slot in range(capacity):
+                if left[slot]:
+                    left[slot] -= 1
+                    generated += 1
+                    active_rows += 1
+                    if left[slot] == 0:
+                        done.append(slot)
+            if done:
+                cache.release_slots(done)
+                for slot in done:
+                    owner[slot] = None
+    torch.cuda.synchronize(device)
+    wall = time.perf_counter() - wall0
+    decode_ms = sum(a.elapsed_time(b) for a, b in decode_events)
+    return {"requests": total_requests, "slots": capacity, "new_tokens_each": new_tokens, "prompt_tokens": int(prefilled),
+            "generated_tokens": generated, "decode_steps": steps, "mean_active_rows": round(active_rows / max(steps, 1), 1),
+            "decode_ms_per_step": round(decode_ms / max(steps, 1), 3),
+            "decode_tok_s": round(active_rows / (decode_ms * 1e-3), 1),
+            "prefill_s": round(prefill_s, 2), "wall_s": round(wall, 2),
+            "tok_s_including_prefill": round(generated / wall, 1), "cuda_graph": True,
+            "note": "requests finish, release their slot and new ones join between replays of one decode graph"}
+
+
 def decode_workload(torch, device, *, requests: int = 64, new_tokens: int = 256, kernel_mix: bool = False) -> dict:
     """Llama-3.2-1B architecture, random init, W4A4KV4: ragged prefill then graph decode of `requests` rows."""
     from nestquant_aiinfra_b200.engine import BatchedNQKVLlamaRunner, build_llama_w4a4kv4
@@ -920,6 +996,16 @@ def decode_workload(torch, device, *, requests: int = 64, new_tokens: int = 256,
         mix = [{"kernel": key[:80], "us_per_step": round(us, 1), "launches_per_step": round(count, 1),
                 "share": round(us / whole, 4)} for us, count, key in rows[:16]]
         mix.append({"kernel": "all kernels", "us_per_step": round(whole, 1)})
+    # config 3 proper: a continuous batch on the same model (96 requests over the 64 slots)
+    try:
+        continuous = continuous_batch(torch, runner, cache, device)
+    except Exception as error:
+        continuous = {"error": f"{type(error).__name__}: {error}"[:300]}
+    # back to a full static batch for the opt-in legs below
+    cache.release_slots(list(range(requests)))
+    for start in range(0, requests, 8):
+        group = order[start:start + 8]
+        runner.prefill_slots(group, [prompts[i] for i in group])
     # opt-in mode: the decoded BF16 weights stay in HBM (4x the packed bytes), no per-call weight decode;
     # same graph-decode loop, 64 more steps on the contexts reached by then
     added = runner.keep_decoded_weights()  # captures the decode graph again
@@ -956,8 +1042,9 @@ def decode_workload(torch, device, *, requests: int = 64, new_tokens: int = 256,
         "extra_kv_bytes": int(kv_added), "decode_steps": resident_steps,
         "ms_per_step": round(shadow_ms / resident_steps, 3),
         "decode_tok_s": round(requests * resident_steps / (shadow_ms * 1e-3), 1)}
-    return {**({"kernel_mix": mix} if mix else {}), "resident_decoded_weights": resident,
+    return {**({"kernel_mix": mix} if mix else {}), "continuous_batch": continuous, "resident_decoded_weights": resident,
             "model": "llama-3.2-1b-arch random init, W4A4KV4, 112 NQRT4 projections", "requests": requests,
+            "static_batch_note": "the top-level figures are a static batch: all requests prefilled, then lock-step decode",
             "prompt_tokens": int(sum(lengths)), "decode_steps": steps, "ms_per_step": round(ms / steps, 3),
             "decode_tok_s": round(requests * steps / (ms * 1e-3), 1), "prefill_s": round(prefill_s, 2),
             "prefill_tok_s": round(sum(lengths) / prefill_s, 1), "cuda_graph": True}
