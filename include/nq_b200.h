@@ -258,6 +258,27 @@ int nq_kv_pack_publish(const void* hot_keys, const void* hot_values, int kv_dtyp
                        int32_t* last_page_lens, int max_sequences, int max_pages, int pool_capacity,
                        int page_size, int heads, int dim, nq_stream_t stream);
 
+/* Device-side page allocation.  The free pages of a pool are a stack in device memory, free_ids[0 .. *free_count),
+ * that kernels pop and push in stream order, so a decode step needs no host read of the hot lengths and no host
+ * reservation, and the pool need not be a fixed partition of max_pages per slot.  The reference allocates on the
+ * host and reads hot_lengths every step (runtime/nqkv_batched_runner.py:344-359); its notes sketch a device-side
+ * scheme without building it (docs/nqkv_gpu_page_ring_research.md:148-186): no counterpart.
+ *   nq_kv_alloc_targets  before nq_kv_pack_publish: writes target_page_ids[s] = a popped page for every slot that
+ *                        will pack (boundary_mask[s], hot_lengths[s] == P, page_counts[s] < max_pages), -1 for the
+ *                        others and when the stack is empty (such a slot is then not packed);
+ *   nq_kv_alloc_pages    pops `count` pages into out_ids (bulk writers; -1 where the stack ran dry);
+ *   nq_kv_release_pages  pushes the pages of the slots selected by slot_mask back, sets their page-table rows to -1
+ *                        and their page_counts / last_page_lens / hot_lengths / sequence_lengths to 0.
+ * The host's admission control must keep the sum of the admitted requests' maximum page counts within the pool. */
+int nq_kv_alloc_targets(const int32_t* hot_lengths, const uint8_t* boundary_mask, const int32_t* page_counts,
+                        const int32_t* free_ids, int32_t* free_count, int32_t* target_page_ids,
+                        int max_sequences, int max_pages, int page_size, nq_stream_t stream);
+int nq_kv_alloc_pages(int count, const int32_t* free_ids, int32_t* free_count, int32_t* out_ids, nq_stream_t stream);
+int nq_kv_release_pages(const uint8_t* slot_mask, int32_t* page_indices, int32_t* page_counts,
+                        int32_t* last_page_lens, int32_t* hot_lengths, int32_t* sequence_lengths,
+                        int32_t* free_ids, int32_t* free_count, int max_sequences, int max_pages,
+                        int pool_capacity, nq_stream_t stream);
+
 /* Quantise and bit-pack one NHD page prefix key/value [valid_tokens, H, D] (rows after the prefix
  * are zero) into six caller-provided payload buffers of one page.  Replaces
  * quantize_nqkv_page_cuda (runtime/nqkv_page.py:241-329). */

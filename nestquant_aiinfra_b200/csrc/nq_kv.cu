@@ -183,6 +183,72 @@ __global__ void __launch_bounds__(256) nq_kv_publish_kernel(const PackParams p) 
     p.hot_lengths_rw[slot] = 0;
 }
 
+// ------------------------------------------------------ device-side page allocator --
+// The free pages of a pool are a stack in device memory: free_ids[0 .. *free_count).  Kernels of one stream pop
+// and push it without the host: no per-step read of the hot lengths, no host reservation, and the pool need not be
+// a fixed partition of max_pages per slot.  Admission control (the host never admits more requests than the pool
+// can hold at their maximum lengths) is what guarantees that a pop finds a page; a pop from an empty stack
+// yields -1, which the pack kernels treat as "do not pack" (the slot's hot tail stays full).
+
+// One target page for every slot that is about to pack: same predicate as nq_pack_selected, minus the id.
+__global__ void __launch_bounds__(256) nq_kv_alloc_targets_kernel(const int32_t* hot_lengths, const uint8_t* boundary_mask,
+                                                                  const int32_t* page_counts, const int32_t* free_ids,
+                                                                  int32_t* free_count, int32_t* target_page_ids,
+                                                                  int max_sequences, int max_pages, int page_size) {
+    const int slot = blockIdx.x * blockDim.x + threadIdx.x;
+    if (slot >= max_sequences) return;
+    int id = -1;
+    if (boundary_mask[slot] != 0 && hot_lengths[slot] == page_size && page_counts[slot] < max_pages) {
+        const int old = atomicSub(free_count, 1);
+        if (old > 0) id = free_ids[old - 1];
+        else atomicAdd(free_count, 1);  // empty: put the count back
+    }
+    target_page_ids[slot] = id;
+}
+
+// `count` pages at once (bulk writers): out_ids[i] for i < count, -1 where the stack ran dry.
+__global__ void __launch_bounds__(256) nq_kv_alloc_pages_kernel(int count, const int32_t* free_ids, int32_t* free_count,
+                                                                int32_t* out_ids) {
+    __shared__ int s_old;
+    if (threadIdx.x == 0) {
+        const int old = atomicSub(free_count, count);
+        if (old < count) atomicAdd(free_count, count - max(old, 0));  // only max(old, 0) pages were there
+        s_old = old;
+    }
+    __syncthreads();
+    const int old = s_old;
+    for (int i = threadIdx.x; i < count; i += blockDim.x) out_ids[i] = i < old ? free_ids[old - 1 - i] : -1;
+}
+
+// Give the pages of the selected slots back and empty those slots (one CTA per slot).
+__global__ void __launch_bounds__(128) nq_kv_release_pages_kernel(const uint8_t* slot_mask, int32_t* page_indices,
+                                                                  int32_t* page_counts, int32_t* last_page_lens,
+                                                                  int32_t* hot_lengths, int32_t* sequence_lengths,
+                                                                  int32_t* free_ids, int32_t* free_count, int max_pages,
+                                                                  int pool_capacity) {
+    __shared__ int s_base;
+    const int slot = blockIdx.x;
+    if (slot_mask[slot] == 0) return;
+    const int count = min(max(page_counts[slot], 0), max_pages);
+    if (threadIdx.x == 0) s_base = count > 0 ? atomicAdd(free_count, count) : 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < max_pages; i += blockDim.x) {
+        int32_t* entry = page_indices + (int64_t)slot * max_pages + i;
+        if (i < count) {
+            const int id = *entry;
+            // a table entry is always a page this allocator handed out; the range check guards the stack anyway
+            if (s_base + i < pool_capacity) free_ids[s_base + i] = (id >= 0 && id < pool_capacity) ? id : 0;
+        }
+        *entry = -1;
+    }
+    if (threadIdx.x == 0) {
+        page_counts[slot] = 0;
+        last_page_lens[slot] = 0;
+        hot_lengths[slot] = 0;
+        sequence_lengths[slot] = 0;
+    }
+}
+
 // ------------------------------------------------------------- eager one page --
 struct PageParams {
     const void *key, *value;  // [valid, H, D]
@@ -342,6 +408,44 @@ extern "C" int nq_kv_pack_publish_lattice(const void* hot_keys, const void* hot_
                                 key_betas, key_norms, value_codes, value_betas, value_norms, key_beta_table,
                                 value_beta_table, page_indices, page_counts, last_page_lens, max_sequences, max_pages,
                                 pool_capacity, page_size, heads, dim, key_lattice, value_lattice, stream);
+}
+
+extern "C" int nq_kv_alloc_targets(const int32_t* hot_lengths, const uint8_t* boundary_mask, const int32_t* page_counts,
+                                   const int32_t* free_ids, int32_t* free_count, int32_t* target_page_ids,
+                                   int max_sequences, int max_pages, int page_size, nq_stream_t stream) {
+    NQ_REQUIRE(hot_lengths && boundary_mask && page_counts && free_ids && free_count && target_page_ids, NQ_ERR_ARG,
+               "nq_kv_alloc_targets: null pointer");
+    NQ_REQUIRE(max_sequences >= 1 && max_pages >= 1 && page_size >= 1, NQ_ERR_ARG, "nq_kv_alloc_targets: bad geometry");
+    nq_kv_alloc_targets_kernel<<<(max_sequences + 255) / 256, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        hot_lengths, boundary_mask, page_counts, free_ids, free_count, target_page_ids, max_sequences, max_pages,
+        page_size);
+    NQ_CHECK_LAUNCH("nq_kv_alloc_targets");
+    return NQ_OK;
+}
+
+extern "C" int nq_kv_alloc_pages(int count, const int32_t* free_ids, int32_t* free_count, int32_t* out_ids,
+                                 nq_stream_t stream) {
+    NQ_REQUIRE(free_ids && free_count && (out_ids || count == 0), NQ_ERR_ARG, "nq_kv_alloc_pages: null pointer");
+    NQ_REQUIRE(count >= 0, NQ_ERR_ARG, "nq_kv_alloc_pages: negative count");
+    if (count == 0) return NQ_OK;
+    nq_kv_alloc_pages_kernel<<<1, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(count, free_ids, free_count, out_ids);
+    NQ_CHECK_LAUNCH("nq_kv_alloc_pages");
+    return NQ_OK;
+}
+
+extern "C" int nq_kv_release_pages(const uint8_t* slot_mask, int32_t* page_indices, int32_t* page_counts,
+                                   int32_t* last_page_lens, int32_t* hot_lengths, int32_t* sequence_lengths,
+                                   int32_t* free_ids, int32_t* free_count, int max_sequences, int max_pages,
+                                   int pool_capacity, nq_stream_t stream) {
+    NQ_REQUIRE(slot_mask && page_indices && page_counts && last_page_lens && hot_lengths && sequence_lengths &&
+                   free_ids && free_count,
+               NQ_ERR_ARG, "nq_kv_release_pages: null pointer");
+    NQ_REQUIRE(max_sequences >= 1 && max_pages >= 1 && pool_capacity >= 1, NQ_ERR_ARG, "nq_kv_release_pages: bad geometry");
+    nq_kv_release_pages_kernel<<<max_sequences, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        slot_mask, page_indices, page_counts, last_page_lens, hot_lengths, sequence_lengths, free_ids, free_count,
+        max_pages, pool_capacity);
+    NQ_CHECK_LAUNCH("nq_kv_release_pages");
+    return NQ_OK;
 }
 
 extern "C" int nq_kv_expand_pages(const uint8_t* codes, int8_t* lattice, const int32_t* page_ids, int64_t count,

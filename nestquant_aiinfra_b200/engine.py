@@ -81,7 +81,8 @@ def quantize_llama_projections_(model: nn.Module, *, weight_betas: Sequence[floa
 
 def build_llama_w4a4kv4(*, hidden_size: int, intermediate_size: int, num_layers: int, num_heads: int,
                         num_kv_heads: int, head_dim: int, vocab_size: int, capacity: int, max_cache_len: int,
-                        device: torch.device | str = "cuda", seed: int = 0, page_size: int = 16):
+                        device: torch.device | str = "cuda", seed: int = 0, page_size: int = 16,
+                        page_allocation: str = "static", pool_pages: int | None = None):
     """Random-init Llama architecture converted to W4A4KV4: returns ``(model, cache)``."""
     from transformers import LlamaConfig, LlamaForCausalLM
 
@@ -103,7 +104,8 @@ def build_llama_w4a4kv4(*, hidden_size: int, intermediate_size: int, num_layers:
     cache = BatchedNQKVLlamaCache(capacity=capacity, num_layers=num_layers, num_query_heads=num_heads,
                                   num_kv_heads=num_kv_heads, head_dim=head_dim, max_cache_len=max_cache_len,
                                   page_size=page_size, key_betas=KEY_BETAS, value_betas=VALUE_BETAS,
-                                  dtype=torch.bfloat16, device=device)
+                                  dtype=torch.bfloat16, device=device, page_allocation=page_allocation,
+                                  pool_pages=pool_pages)
     install_batched_nqkv_llama_backend(model, cache)
     fuse_rmsnorm_(model)  # one launch per normalisation instead of six tensor kernels
     return model, cache
@@ -313,7 +315,8 @@ class BatchedNQKVLlamaRunner:
     # ------------------------------------------------------------------ device-side sampling
     @torch.no_grad()
     def prefill_slots(self, slots, prompts=None, *, positions: torch.Tensor | None = None,
-                      write_mask: torch.Tensor | None = None, valid_lengths: torch.Tensor | None = None) -> torch.Tensor:
+                      write_mask: torch.Tensor | None = None, valid_lengths: torch.Tensor | None = None,
+                      max_tokens: int | None = None) -> torch.Tensor:
         """Two call forms.
 
         ``prefill_slots(input_ids, positions=, write_mask=, valid_lengths=)`` is the engine protocol
@@ -321,7 +324,9 @@ class BatchedNQKVLlamaRunner:
         new requests; returns logits ``[capacity, width, vocab]`` (see ``prefill_logits``).
 
         ``prefill_slots(slots, prompts)`` is whole-prompt prefill of ``prompts[i]`` into ``slots[i]``
-        with the sampling on the device; returns the greedy next token per row.
+        with the sampling on the device; returns the greedy next token per row.  ``max_tokens`` (prompt plus
+        the tokens the request may still generate) is the admission budget of a cache with device-side page
+        allocation; it defaults to the cache length.
         """
         if positions is not None or write_mask is not None or valid_lengths is not None:
             if prompts is not None or positions is None or write_mask is None or valid_lengths is None:
@@ -341,7 +346,7 @@ class BatchedNQKVLlamaRunner:
             assignments.append((f"slot-{slot}-generation-{self._generation[slot]}", slot))
             ids[row, :prompt.numel()] = prompt.to(self.device)
             lengths.append(int(prompt.numel()))
-        self.cache.register_batch(assignments)
+        self.cache.register_batch(assignments, max_tokens=max_tokens)
         slot_ids = torch.tensor(list(slots), dtype=torch.int32, device=self.device)
         q_lens = torch.tensor(lengths, dtype=torch.int32, device=self.device)
         positions = torch.arange(width, device=self.device).unsqueeze(0).expand(len(slots), width).contiguous()
@@ -432,16 +437,21 @@ class BatchedNQKVLlamaRunner:
     def _snapshot(self):
         per_layer = []
         for cache in self.cache.layer_caches:
-            per_layer.append(tuple(t.clone() for t in (cache.page_indices, cache.page_counts, cache.last_page_len,
-                                                       cache.hot_lengths, cache.sequence_lengths, cache.hot_keys,
-                                                       cache.hot_values)))
+            per_layer.append(tuple(t.clone() for t in self._state_tensors(cache)))
         return per_layer, self.tokens.clone(), self.positions.clone()
+
+    @staticmethod
+    def _state_tensors(cache):
+        tensors = [cache.page_indices, cache.page_counts, cache.last_page_len, cache.hot_lengths,
+                   cache.sequence_lengths, cache.hot_keys, cache.hot_values]
+        if cache.pool.free_ids is not None:  # device-side allocator: a warm-up step may pop pages
+            tensors += [cache.pool.free_ids, cache.pool.free_count]
+        return tensors
 
     def _restore(self, state) -> None:
         per_layer, tokens, positions = state
         for cache, saved in zip(self.cache.layer_caches, per_layer):
-            for dst, src in zip((cache.page_indices, cache.page_counts, cache.last_page_len, cache.hot_lengths,
-                                 cache.sequence_lengths, cache.hot_keys, cache.hot_values), saved):
+            for dst, src in zip(self._state_tensors(cache), saved):
                 dst.copy_(src)
         self.tokens.copy_(tokens)
         self.positions.copy_(positions)

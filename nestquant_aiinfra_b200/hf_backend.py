@@ -97,7 +97,8 @@ class BatchedNQKVLlamaCache(Cache):
     def __init__(self, *, capacity: int, num_layers: int, num_query_heads: int, num_kv_heads: int, head_dim: int,
                  max_cache_len: int, page_size: int = 16, q: int = 14, key_betas: Sequence[float],
                  value_betas: Sequence[float], dtype: torch.dtype = torch.bfloat16,
-                 device: torch.device | str = "cuda") -> None:
+                 device: torch.device | str = "cuda", page_allocation: str = "static",
+                 pool_pages: int | None = None) -> None:
         super().__init__(layers=[])
         for name, value in (("capacity", capacity), ("num_layers", num_layers), ("num_query_heads", num_query_heads),
                             ("num_kv_heads", num_kv_heads), ("head_dim", head_dim), ("max_cache_len", max_cache_len),
@@ -110,13 +111,28 @@ class BatchedNQKVLlamaCache(Cache):
         if target.type == "cuda" and target.index is None:
             target = torch.device("cuda", torch.cuda.current_device())
         max_pages = math.ceil(max_cache_len / page_size)
+        # "static": page ids are slot * max_pages + page (the pool is a fixed partition, as the reference sizes it);
+        # "device": the pool is a device-side free stack of `pool_pages` pages shared by all slots, popped by the
+        # page writers and pushed back on release; the host only keeps an admission budget (see `register`).
+        if page_allocation not in {"static", "device"}:
+            raise ValueError("page_allocation must be static or device")
+        if pool_pages is None:
+            pool_pages = capacity * max_pages
+        if isinstance(pool_pages, bool) or not isinstance(pool_pages, int) or pool_pages < 1:
+            raise ValueError("pool_pages must be a positive integer")
+        if page_allocation == "static" and pool_pages != capacity * max_pages:
+            raise ValueError("static page ids need a pool of capacity * ceil(max_cache_len / page_size) pages")
+        self.page_allocation, self.pool_pages = page_allocation, pool_pages
+        self._page_budget: dict[int, int] = {}   # slot -> pages its request may need at most (device allocation)
         self.layer_caches: list[NQKVHotColdCache] = []
         for _ in range(num_layers):
-            pool = NQKVPagePool(capacity=capacity * max_pages, page_size=page_size, num_kv_heads=num_kv_heads,
+            pool = NQKVPagePool(capacity=pool_pages, page_size=page_size, num_kv_heads=num_kv_heads,
                                 head_dim=head_dim, q=q, key_betas=key_betas, value_betas=value_betas,
                                 output_dtype=dtype, device=target)
             layer = NQKVHotColdCache(pool, max_sequences=capacity, max_pages_per_sequence=max_pages)
             pool.page_accounting = (lambda c=layer: c.page_counts.sum().item())  # ids are assigned on the device
+            if page_allocation == "device":
+                pool.enable_device_allocator()
             self.layer_caches.append(layer)
         self.capacity, self.num_layers = capacity, num_layers
         self.num_query_heads, self.num_kv_heads, self.head_dim = num_query_heads, num_kv_heads, head_dim
@@ -164,16 +180,31 @@ class BatchedNQKVLlamaCache(Cache):
         """
         return sum(cache.pool.enable_lattice_shadow() for cache in self.layer_caches)
 
-    def register(self, sequence_id: Hashable, *, slot: int) -> None:
+    def _admit(self, slots: Sequence[int], max_tokens: int | None) -> None:
+        """Admission budget of the device-side allocator: the pages every admitted request may need at its longest
+        must fit the pool, so that a pop on the device always finds a page."""
+        if self.page_allocation != "device":
+            return
+        tokens = self._max_cache_len if max_tokens is None else int(max_tokens)
+        if not 1 <= tokens <= self._max_cache_len:
+            raise ValueError("max_tokens must be in [1, max_cache_len]")
+        pages = math.ceil(tokens / self.page_size)
+        if sum(self._page_budget.values()) + pages * len(slots) > self.pool_pages:
+            raise RuntimeError("NQKV page pool exhausted")
+        for slot in slots:
+            self._page_budget[int(slot)] = pages
+
+    def register(self, sequence_id: Hashable, *, slot: int, max_tokens: int | None = None) -> None:
         if slot in self._sequence_of_slot:
             raise RuntimeError(f"slot {slot} is already registered")
+        self._admit([slot], max_tokens)
         for cache in self.layer_caches:
             cache.register(slot, sequence_id)
         self.active_mask[slot] = True
         self._sequence_of_slot[slot] = sequence_id
         self._fresh_slots.add(int(slot))
 
-    def register_batch(self, assignments: Sequence[tuple[Hashable, int]]) -> None:
+    def register_batch(self, assignments: Sequence[tuple[Hashable, int]], *, max_tokens: int | None = None) -> None:
         """Register several sequences at once (one index upload instead of scalar writes per slot and layer)."""
         slots = [int(slot) for _, slot in assignments]
         if len(set(slots)) != len(slots) or any(slot in self._sequence_of_slot for slot in slots):
@@ -182,6 +213,7 @@ class BatchedNQKVLlamaCache(Cache):
             raise ValueError("slot outside cache capacity")
         if not slots:
             return
+        self._admit(slots, max_tokens)
         index = torch.tensor(slots, dtype=torch.long, device=self.device)
         for cache in self.layer_caches:
             cache.register_many(index)
@@ -204,8 +236,15 @@ class BatchedNQKVLlamaCache(Cache):
             self._fresh_slots.discard(int(slot))
         if freed:
             index = torch.tensor(freed, dtype=torch.long, device=self.device)
+            if self.page_allocation == "device":
+                mask = torch.zeros(self.capacity, dtype=torch.bool, device=self.device).index_fill_(0, index, True)
+                for slot in freed:
+                    self._page_budget.pop(slot, None)
             for cache in self.layer_caches:
                 cache.active.index_fill_(0, index, False)
+                if self.page_allocation == "device":
+                    cache.device_release_slots(mask)  # pages back to the stack, tables and lengths cleared
+                    continue
                 cache.sequence_lengths.index_fill_(0, index, 0)
                 cache.hot_lengths.index_fill_(0, index, 0)
                 cache.page_counts.index_fill_(0, index, 0)
@@ -361,8 +400,12 @@ class BatchedNQKVLlamaCache(Cache):
 
     # ------------------------------------------------------------------ Cache interface
     def _pack_full_pages(self, cache: NQKVHotColdCache, mask: torch.Tensor | None = None) -> None:
-        torch.add(self._page_base, cache.page_counts, out=cache.graph_target_page_ids)
-        launch_pack_full_hot_pages_graph_safe(cache, boundary_mask=self._all_slots if mask is None else mask)
+        mask = self._all_slots if mask is None else mask
+        if self.page_allocation == "device":
+            cache.device_alloc_targets(mask)   # pops a page for every slot that is about to pack
+        else:
+            torch.add(self._page_base, cache.page_counts, out=cache.graph_target_page_ids)
+        launch_pack_full_hot_pages_graph_safe(cache, boundary_mask=mask)
 
     def update(self, key_states: torch.Tensor, value_states: torch.Tensor, layer_idx: int, cache_kwargs=None):
         self._validate_layer(layer_idx)
@@ -409,7 +452,7 @@ class BatchedNQKVLlamaCache(Cache):
         """Index tensors of a whole-prompt chunk ``[rows, tokens]``: which tokens fill whole pages, which stay hot."""
         slots, lengths = self._bulk_host
         page, device = self.page_size, self.device
-        full_idx, page_ids, tail_src, tail_slot, tail_pos = [], [], [], [], []
+        full_idx, page_ids, tail_src, tail_slot, tail_pos, table_rows, table_cols = [], [], [], [], [], [], []
         rows = [(row, slot, length) for row, (slot, length) in enumerate(zip(slots, lengths)) if length > 0]
         slots, lengths = [slot for _, slot, _ in rows], [length for _, _, length in rows]
         table = torch.full((len(rows), self.max_pages), -1, dtype=torch.int32)
@@ -421,6 +464,8 @@ class BatchedNQKVLlamaCache(Cache):
             ids = torch.arange(full) + slot * self.max_pages
             page_ids.append(ids)
             table[index, :full] = ids.to(torch.int32)
+            table_rows.append(torch.full((full,), index))
+            table_cols.append(torch.arange(full))
             tail_src.append(torch.arange(rest) + row * tokens + full * page)
             tail_slot.append(torch.full((rest,), slot))
             tail_pos.append(torch.arange(rest))
@@ -428,6 +473,7 @@ class BatchedNQKVLlamaCache(Cache):
         lengths_t = torch.tensor(lengths, dtype=torch.int32)
         return {"tokens": tokens, "full_idx": cat(full_idx), "page_ids": cat(page_ids), "tail_src": cat(tail_src),
                 "tail_slot": cat(tail_slot), "tail_pos": cat(tail_pos), "table": table.to(device),
+                "table_rows": cat(table_rows), "table_cols": cat(table_cols),
                 "slots": torch.tensor(slots, dtype=torch.long, device=device),
                 "full": (lengths_t // page).to(device), "rest": (lengths_t % page).to(device),
                 "lengths": lengths_t.to(device)}
@@ -443,23 +489,30 @@ class BatchedNQKVLlamaCache(Cache):
         if plan is None or plan["tokens"] != tokens:
             plan = self._bulk_plan = self._plan_chunk_from_empty(tokens)
         pool, dim = cache.pool, self.head_dim
+        page_ids, page_table = plan["page_ids"], plan["table"]
+        if self.page_allocation == "device" and page_ids.numel():
+            # the pages come off this layer's device-side stack instead of the static partition
+            popped = pool.device_alloc_pages(page_ids.numel())
+            page_ids = popped.long()
+            page_table = torch.full_like(plan["table"], -1)
+            page_table[plan["table_rows"], plan["table_cols"]] = popped
         for flat, codes, betas, norms, table, values, hot in (
                 (key_nhd.view(rows * tokens, -1), pool.key_codes, pool.key_betas, pool.key_norms, pool.beta_table,
                  pool.betas, cache.hot_keys),
                 (value_nhd.view(rows * tokens, -1), pool.value_codes, pool.value_betas, pool.value_norms,
                  pool.value_beta_table, pool.value_beta_values, cache.hot_values)):
-            pages = plan["page_ids"].numel()
+            pages = page_ids.numel()
             if pages:
                 packed = quantize_activation_cuda(flat[plan["full_idx"]].view(-1, dim), q=14, betas=values,
                                                   beta_table=table, keep_decoded=False)
-                codes[plan["page_ids"]] = packed.code_payload.view(pages, -1)
-                betas[plan["page_ids"]] = packed.beta_payload.view(pages, -1)
-                norms[plan["page_ids"]] = packed.row_norms.view(pages, -1)
+                codes[page_ids] = packed.code_payload.view(pages, -1)
+                betas[page_ids] = packed.beta_payload.view(pages, -1)
+                norms[page_ids] = packed.row_norms.view(pages, -1)
             if plan["tail_src"].numel():
                 hot[plan["tail_slot"], plan["tail_pos"]] = flat[plan["tail_src"]].view(-1, self.num_kv_heads, dim)
-        pool.expand_pages(plan["page_ids"])  # keeps the opt-in decoded shadow current (no-op without one)
+        pool.expand_pages(page_ids)  # keeps the opt-in decoded shadow current (no-op without one)
         slots = plan["slots"]
-        cache.page_indices[slots] = plan["table"]
+        cache.page_indices[slots] = page_table
         cache.page_counts[slots] = plan["full"]
         cache.last_page_len[slots] = torch.where(plan["full"] > 0, self.page_size, 0).to(torch.int32)
         cache.hot_lengths[slots] = plan["rest"]

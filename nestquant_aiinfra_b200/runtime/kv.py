@@ -83,9 +83,38 @@ class NQKVPagePool:
         self.value_beta_table = torch.tensor(self.value_beta_values, device=target, dtype=torch.float32)
         self._free = list(range(capacity - 1, -1, -1))
         self.page_accounting = None  # optional callable returning the pages in use (see ``allocated_pages``)
+        # device-side free stack (``enable_device_allocator``)
+        self.free_ids: torch.Tensor | None = None
+        self.free_count: torch.Tensor | None = None
         # opt-in decoded shadow of the code streams (``enable_lattice_shadow``): int8 [capacity, P*H*D]
         self.key_lattice: torch.Tensor | None = None
         self.value_lattice: torch.Tensor | None = None
+
+    def enable_device_allocator(self) -> None:
+        """Hand the pool's free pages to a device-side stack (``free_ids[0 .. free_count)``).
+
+        Afterwards the page writers pop their target pages on the device (``device_alloc_targets``,
+        ``device_alloc_pages``) and ``device_release_slots`` pushes them back; ``allocate`` / ``release``
+        of the host list must not be used any more.
+        """
+        if self.free_ids is not None:
+            return
+        self.free_ids = torch.tensor(self._free, dtype=torch.int32, device=self.device)
+        if self.free_ids.numel() < self.capacity:  # pages the host list had already handed out stay out
+            self.free_ids = torch.cat([self.free_ids, torch.zeros(self.capacity - self.free_ids.numel(),
+                                                                  dtype=torch.int32, device=self.device)])
+        self.free_count = torch.tensor([len(self._free)], dtype=torch.int32, device=self.device)
+        self._free = []
+
+    def device_alloc_pages(self, count: int) -> torch.Tensor:
+        """Pop ``count`` page ids on the device (no host sync): int32 ``[count]``."""
+        if self.free_ids is None:
+            raise RuntimeError("the pool has no device-side allocator")
+        out = torch.empty(count, dtype=torch.int32, device=self.device)
+        status = _lib.lib().nq_kv_alloc_pages(_INT(count), _ptr(self.free_ids), _ptr(self.free_count), _ptr(out),
+                                              _stream(self.device))
+        _lib.check(status, "device_alloc_pages")
+        return out
 
     def enable_lattice_shadow(self) -> int:
         """Keep the decoded lattice coordinates of every page beside its codes (opt-in; returns the bytes added).
@@ -123,6 +152,8 @@ class NQKVPagePool:
     def allocated_pages(self) -> int:
         """Pages in use: handed out by ``allocate``, or -- for an owner that assigns page ids on the device --
         the pages its page tables hold (``page_accounting``; reads the device)."""
+        if self.free_count is not None:
+            return self.capacity - int(self.free_count.item())
         if self.page_accounting is not None:
             return int(self.page_accounting())
         return self.capacity - len(self._free)
@@ -196,6 +227,30 @@ class NQKVHotColdCache:
         self.hot_lengths.index_fill_(0, index, 0)
         self.sequence_lengths.index_fill_(0, index, 0)
         self.page_indices.index_fill_(0, index, -1)
+
+    def device_alloc_targets(self, boundary_mask: torch.Tensor) -> None:
+        """Pop one target page on the device for every slot that is about to pack (graph safe, no host reads)."""
+        pool = self.pool
+        if pool.free_ids is None:
+            raise RuntimeError("the pool has no device-side allocator")
+        status = _lib.lib().nq_kv_alloc_targets(
+            _ptr(self.hot_lengths), _ptr(boundary_mask), _ptr(self.page_counts), _ptr(pool.free_ids),
+            _ptr(pool.free_count), _ptr(self.graph_target_page_ids), _INT(self.max_sequences),
+            _INT(self.max_pages_per_sequence), _INT(pool.page_size), _stream(pool.device))
+        _lib.check(status, "device_alloc_targets")
+
+    def device_release_slots(self, slot_mask: torch.Tensor) -> None:
+        """Push the pages of the selected slots back to the device-side stack and empty those slots."""
+        pool = self.pool
+        if pool.free_ids is None:
+            raise RuntimeError("the pool has no device-side allocator")
+        if slot_mask.dtype != torch.bool or tuple(slot_mask.shape) != (self.max_sequences,):
+            raise ValueError("slot_mask must be bool with cache capacity shape")
+        status = _lib.lib().nq_kv_release_pages(
+            _ptr(slot_mask), _ptr(self.page_indices), _ptr(self.page_counts), _ptr(self.last_page_len),
+            _ptr(self.hot_lengths), _ptr(self.sequence_lengths), _ptr(pool.free_ids), _ptr(pool.free_count),
+            _INT(self.max_sequences), _INT(self.max_pages_per_sequence), _INT(pool.capacity), _stream(pool.device))
+        _lib.check(status, "device_release_slots")
 
     def reserve_targets(self, slots: Sequence[int]) -> list[int]:
         """Allocate one target page per slot for the next boundary pack (host control plane)."""

@@ -281,3 +281,55 @@ def test_a_slot_at_its_cache_limit_cannot_touch_its_neighbour():
              layer.page_indices[1])
     for a, b in zip(after, before):
         assert torch.equal(a, b)
+
+
+def test_device_side_page_allocation_matches_static_ids_with_a_smaller_pool():
+    """Pages popped from the device-side free stack instead of ``slot * max_pages + page``: same tokens and page
+    contents as the static partition from a pool a third of its size; a released slot gives its pages back; the
+    admission budget refuses what the pool could not hold.  Eager steps and replays of a captured graph."""
+    import pytest
+
+    from nestquant_aiinfra_b200.engine import BatchedNQKVLlamaRunner, build_llama_w4a4kv4
+
+    common = dict(hidden_size=256, intermediate_size=512, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=64,
+                  vocab_size=128, capacity=4, max_cache_len=256, seed=7)        # static pool: 4 x 16 = 64 pages
+    gen = torch.Generator().manual_seed(21)
+    prompts = [torch.randint(0, 128, (n,), generator=gen) for n in (45, 9, 70)]
+    slots = [0, 2, 3]
+    tokens, caches = {}, {}
+    for mode, extra in (("static", {}), ("device", dict(page_allocation="device", pool_pages=20))):
+        model, cache = build_llama_w4a4kv4(**common, **extra)
+        runner = BatchedNQKVLlamaRunner(model, cache)
+        seen = [runner.prefill_slots(slots, prompts, max_tokens=112).clone()]   # 7 pages each at most: 21 > 20 ...
+        seen += [runner.decode_eager().clone() for _ in range(12)]              # eager steps across page boundaries
+        runner.capture_decode_graph()
+        seen += [runner.decode().clone() for _ in range(14)]                    # graph replays across more of them
+        tokens[mode], caches[mode] = seen, cache
+        if mode == "static":
+            continue
+    for a, b in zip(tokens["static"], tokens["device"]):
+        assert torch.equal(a, b)
+    static, device = caches["static"], caches["device"]
+    for ls, ld in zip(static.layer_caches, device.layer_caches):
+        assert torch.equal(ls.page_counts, ld.page_counts) and torch.equal(ls.hot_lengths, ld.hot_lengths)
+        in_use = int(ld.page_counts.sum())
+        assert ld.pool.allocated_pages == in_use and int(ld.pool.free_count) == 20 - in_use
+        for slot in slots:
+            for position in range(int(ld.page_counts[slot])):
+                sid, did = int(ls.page_indices[slot, position]), int(ld.page_indices[slot, position])
+                assert sid == slot * 16 + position and 0 <= did < 20
+                assert torch.equal(ls.pool.key_codes[sid], ld.pool.key_codes[did])
+                assert torch.equal(ls.pool.value_norms[sid], ld.pool.value_norms[did])
+        ids = ld.page_indices[ld.page_indices >= 0].tolist()
+        assert len(set(ids)) == len(ids) == in_use                                # no page handed out twice
+    held = int(device.layer_caches[0].page_counts[3])
+    device.release_slots([3])
+    for layer in device.layer_caches:
+        assert layer.page_indices[3].tolist() == [-1] * 16 and int(layer.sequence_lengths[3]) == 0
+        assert layer.pool.allocated_pages == int(layer.page_counts.sum())
+        free = layer.pool.free_ids[:int(layer.pool.free_count)].tolist()
+        assert len(set(free)) == len(free) and not set(free) & set(layer.page_indices[layer.page_indices >= 0].tolist())
+    assert held > 0
+    device.register("late", slot=3, max_tokens=96)          # 7 + 7 + 6 = 20 pages of budget: fits
+    with pytest.raises(RuntimeError, match="exhausted"):
+        device.register("too much", slot=1, max_tokens=16)   # one more page does not
