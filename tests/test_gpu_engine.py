@@ -297,10 +297,10 @@ def test_device_side_page_allocation_matches_static_ids_with_a_smaller_pool():
     prompts = [torch.randint(0, 128, (n,), generator=gen) for n in (45, 9, 70)]
     slots = [0, 2, 3]
     tokens, caches = {}, {}
-    for mode, extra in (("static", {}), ("device", dict(page_allocation="device", pool_pages=20))):
+    for mode, extra in (("static", {}), ("device", dict(page_allocation="device", pool_pages=24))):
         model, cache = build_llama_w4a4kv4(**common, **extra)
         runner = BatchedNQKVLlamaRunner(model, cache)
-        seen = [runner.prefill_slots(slots, prompts, max_tokens=112).clone()]   # 7 pages each at most: 21 > 20 ...
+        seen = [runner.prefill_slots(slots, prompts, max_tokens=112).clone()]   # budget: 7 pages each, 21 of the 24
         seen += [runner.decode_eager().clone() for _ in range(12)]              # eager steps across page boundaries
         runner.capture_decode_graph()
         seen += [runner.decode().clone() for _ in range(14)]                    # graph replays across more of them
@@ -313,11 +313,11 @@ def test_device_side_page_allocation_matches_static_ids_with_a_smaller_pool():
     for ls, ld in zip(static.layer_caches, device.layer_caches):
         assert torch.equal(ls.page_counts, ld.page_counts) and torch.equal(ls.hot_lengths, ld.hot_lengths)
         in_use = int(ld.page_counts.sum())
-        assert ld.pool.allocated_pages == in_use and int(ld.pool.free_count) == 20 - in_use
+        assert ld.pool.allocated_pages == in_use and int(ld.pool.free_count) == 24 - in_use
         for slot in slots:
             for position in range(int(ld.page_counts[slot])):
                 sid, did = int(ls.page_indices[slot, position]), int(ld.page_indices[slot, position])
-                assert sid == slot * 16 + position and 0 <= did < 20
+                assert sid == slot * 16 + position and 0 <= did < 24
                 assert torch.equal(ls.pool.key_codes[sid], ld.pool.key_codes[did])
                 assert torch.equal(ls.pool.value_norms[sid], ld.pool.value_norms[did])
         ids = ld.page_indices[ld.page_indices >= 0].tolist()
@@ -330,6 +330,6 @@ def test_device_side_page_allocation_matches_static_ids_with_a_smaller_pool():
         free = layer.pool.free_ids[:int(layer.pool.free_count)].tolist()
         assert len(set(free)) == len(free) and not set(free) & set(layer.page_indices[layer.page_indices >= 0].tolist())
     assert held > 0
-    device.register("late", slot=3, max_tokens=96)          # 7 + 7 + 6 = 20 pages of budget: fits
+    device.register("late", slot=3, max_tokens=96)          # 7 + 7 + 6 = 20 pages of budget: fits the 24
     with pytest.raises(RuntimeError, match="exhausted"):
-        device.register("too much", slot=1, max_tokens=16)   # one more page does not
+        device.register("too much", slot=1, max_tokens=80)   # 5 more pages do not
