@@ -80,6 +80,25 @@ int nq_a4_encode_rotated(const void* x, int x_dtype, int64_t rows, int64_t k, in
                          const float* beta_table, uint8_t* out_codes, uint8_t* out_beta_ids,
                          float* out_norms, void* out_decoded, nq_stream_t stream);
 
+/* Module-level fusion at the plugin boundary: the elementwise producer of a projection's input, the rotation and
+ * the A4 encode in ONE launch.  Outputs are bit-identical to the separate launches.
+ *   nq_a4_encode_rmsnorm_rotated   rows = weight * dtype(x * rsqrt(mean(x^2) + eps)), i.e. nq_rmsnorm (same fixed
+ *                                  reduction order), in front of q/k/v and gate/up (models/fused_linear.py:287-306
+ *                                  receives the normalised hidden state from the model's LlamaRMSNorm)
+ *   nq_a4_encode_silu_mul_rotated  rows = dtype(dtype(silu(gate)) * up), the tensor ops of the Llama MLP in front of
+ *                                  down_proj
+ * x / gate / up are [rows, k] with row stride `row_stride` elements (gate and up may be column ranges of one
+ * stacked projection output); weight is [k].  Other arguments as nq_a4_encode_rotated.  The reference leaves both
+ * producers to the model's tensor ops: no counterpart. */
+int nq_a4_encode_rmsnorm_rotated(const void* x, const void* weight, float eps, int dtype, int64_t rows, int64_t k,
+                                 int64_t row_stride, int64_t hadamard_block, const float* beta_table,
+                                 uint8_t* out_codes, uint8_t* out_beta_ids, float* out_norms, void* out_decoded,
+                                 nq_stream_t stream);
+int nq_a4_encode_silu_mul_rotated(const void* gate, const void* up, int dtype, int64_t rows, int64_t k,
+                                  int64_t row_stride, int64_t hadamard_block, const float* beta_table,
+                                  uint8_t* out_codes, uint8_t* out_beta_ids, float* out_norms, void* out_decoded,
+                                  nq_stream_t stream);
+
 /* Weight encoder: the same search with the stateless subtractive dither of
  * global block  w_block_offset + row*k/8 + block  ("lcg31_mix_v1",
  * core/codec.py:176-224).  Bit-exact with quantize_rows(W, 14, betas,

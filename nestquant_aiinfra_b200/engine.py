@@ -28,7 +28,7 @@ from .formats import ACTIVATION_BETAS, KEY_BETAS, VALUE_BETAS, WEIGHT_BETAS, ten
 from .fused_linear import (FusedNQRTLinear, SharedHadamardCache, SharedPackedActivationCache,
                            SharedProjectionGroup, keep_decoded_weights_)
 from .hf_backend import BatchedNQKVLlamaCache, install_batched_nqkv_llama_backend
-from .norm import fuse_rmsnorm_
+from .norm import fuse_rmsnorm_, fuse_silu_mlp_
 from .rope import fused_rope_scope
 from .rotation import hadamard
 from .runtime.w4a4 import quantize_weight_cuda
@@ -82,8 +82,13 @@ def quantize_llama_projections_(model: nn.Module, *, weight_betas: Sequence[floa
 def build_llama_w4a4kv4(*, hidden_size: int, intermediate_size: int, num_layers: int, num_heads: int,
                         num_kv_heads: int, head_dim: int, vocab_size: int, capacity: int, max_cache_len: int,
                         device: torch.device | str = "cuda", seed: int = 0, page_size: int = 16,
-                        page_allocation: str = "static", pool_pages: int | None = None):
-    """Random-init Llama architecture converted to W4A4KV4: returns ``(model, cache)``."""
+                        page_allocation: str = "static", pool_pages: int | None = None,
+                        fuse_producers: bool = True):
+    """Random-init Llama architecture converted to W4A4KV4: returns ``(model, cache)``.
+
+    ``fuse_producers`` moves the decoder layers' RMS norms and the MLP's SiLU * up into the encoder launch of the
+    projections they feed (same bits, fewer launches per step).
+    """
     from transformers import LlamaConfig, LlamaForCausalLM
 
     config = LlamaConfig(hidden_size=hidden_size, intermediate_size=intermediate_size, num_hidden_layers=num_layers,
@@ -107,7 +112,9 @@ def build_llama_w4a4kv4(*, hidden_size: int, intermediate_size: int, num_layers:
                                   dtype=torch.bfloat16, device=device, page_allocation=page_allocation,
                                   pool_pages=pool_pages)
     install_batched_nqkv_llama_backend(model, cache)
-    fuse_rmsnorm_(model)  # one launch per normalisation instead of six tensor kernels
+    fuse_rmsnorm_(model, defer_into_projections=fuse_producers)  # one launch per normalisation, or none at all
+    if fuse_producers:
+        fuse_silu_mlp_(model)
     return model, cache
 
 

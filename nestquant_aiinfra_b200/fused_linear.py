@@ -18,7 +18,7 @@ from torch import nn
 
 from .rotation import hadamard
 from .runtime.w4a4 import (PreparedNQA4Activation, PreparedNQRTLinear, linear_packed_w4a4, linear_packed_w4a4_fp32,
-                           prepare_fused_linear,
+                           prepare_fused_linear, prefer_producer_in_encoder,
                            quantize_activation_cuda, can_rotate_in_encoder, prefer_rotation_in_encoder,
                            group_prepared_linears, keep_decoded_weight)
 
@@ -99,15 +99,15 @@ class SharedPackedActivationCache(_SharedByIdentity):
     _what = "shared A4"
 
     def encode(self, inputs: torch.Tensor, *, q: int, betas: tuple[float, ...],
-               beta_table: torch.Tensor | None = None,
-               hadamard_block: int | None = None) -> tuple[PreparedNQA4Activation, bool]:
+               beta_table: torch.Tensor | None = None, hadamard_block: int | None = None,
+               rmsnorm: tuple[torch.Tensor, float] | None = None) -> tuple[PreparedNQA4Activation, bool]:
         """``(packed, encoded_now)``: the second item tells the caller whether this call ran the encoder."""
         self._require_inference()
         packed = self._fetch(inputs)
         if packed is not None:
             return packed, False
         packed = quantize_activation_cuda(inputs, q=q, betas=betas, beta_table=beta_table,
-                                          hadamard_block=hadamard_block, keep_decoded=True)
+                                          hadamard_block=hadamard_block, keep_decoded=True, rmsnorm=rmsnorm)
         self._store(inputs, packed)
         return packed, True
 
@@ -286,7 +286,7 @@ class FusedNQRTLinear(nn.Module):
         self._prepared = prepared
         return prepared
 
-    def forward(self, inputs: torch.Tensor) -> torch.Tensor:
+    def _check_inputs(self, inputs: torch.Tensor) -> None:
         if not isinstance(inputs, torch.Tensor) or not inputs.is_floating_point():
             raise TypeError("inputs must be a floating-point tensor")
         if inputs.ndim == 0 or inputs.shape[-1] != self.in_features:
@@ -294,6 +294,42 @@ class FusedNQRTLinear(nn.Module):
             raise ValueError(f"input feature dimension {actual} does not match {self.in_features}")
         if inputs.device.type != "cuda":
             raise ValueError("FusedNQRTLinear requires CUDA inputs")
+
+    def _finish(self, packed: PreparedNQA4Activation, encoded: bool, prepared: PreparedNQRTLinear,
+                original_dtype: torch.dtype) -> torch.Tensor:
+        self.a4_call_count += 1
+        self.a4_encode_count += int(encoded)
+        if self._group is not None:
+            outputs = self._group.project(packed, self._group_index)
+        elif self.output_dtype == torch.float32:
+            outputs = linear_packed_w4a4_fp32(packed, prepared)  # the accumulator itself, not rounded to the input dtype first
+        else:
+            outputs = linear_packed_w4a4(packed, prepared)
+        self.w4a4_cuda_mma_dispatch_count += 1
+        return outputs.to(self.output_dtype or original_dtype)
+
+    def forward_silu_mul(self, gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+        """``self(silu(gate) * up)`` -- the Llama MLP's input of ``down_proj``.  When the shape allows it, SiLU, the
+        product, the rotation and the A4 encode run as ONE launch (same bits as the tensor ops followed by the
+        rotate-and-encode); otherwise this is literally ``self(silu(gate) * up)``."""
+        self._check_inputs(gate)
+        if up.shape != gate.shape or up.dtype != gate.dtype or up.device != gate.device:
+            raise ValueError("gate and up must share shape, dtype and device")
+        block = self.in_features if self.input_hadamard else self.input_rotation_block
+        rows = gate.numel() // self.in_features
+        if (block is None or torch.is_grad_enabled() or not can_rotate_in_encoder(self.in_features, block)
+                or not prefer_producer_in_encoder(rows, self.in_features)):
+            return self.forward(torch.nn.functional.silu(gate) * up)
+        prepared = self._prepared_for(gate.device)
+        beta_table = self.activation_beta_table
+        if beta_table.device != gate.device:
+            beta_table = beta_table.to(gate.device)
+        packed = quantize_activation_cuda(gate, q=self.activation_q, betas=self.activation_betas, beta_table=beta_table,
+                                          hadamard_block=block, keep_decoded=True, silu_mul_with=up)
+        return self._finish(packed, True, prepared, gate.dtype)
+
+    def forward(self, inputs: torch.Tensor) -> torch.Tensor:
+        self._check_inputs(inputs)
         original_dtype = inputs.dtype
         # The rotation of the input runs inside the encoder launch when the sizes allow it
         # (bit-identical to hadamard() followed by the encoder); otherwise as its own launch.
@@ -302,6 +338,17 @@ class FusedNQRTLinear(nn.Module):
                              and inputs.dtype in (torch.bfloat16, torch.float16, torch.float32)
                              and can_rotate_in_encoder(self.in_features, wanted_block)
                              and prefer_rotation_in_encoder(inputs.numel() // self.in_features, self.in_features))
+        # A normalisation that its module left pending (norm.FusedRMSNorm(defer=True)) is done inside the same
+        # launch when the rotation is; otherwise it is materialised once for all consumers of this input.
+        pending_norm = getattr(inputs, "_nq_pending_norm", None)
+        if pending_norm is not None and not rotate_in_encoder:
+            materialised = getattr(inputs, "_nq_materialised", None)
+            if materialised is None:
+                from .norm import rms_norm
+
+                materialised = rms_norm(inputs, *pending_norm)
+                inputs._nq_materialised = materialised
+            inputs, pending_norm = materialised, None
         if rotate_in_encoder:
             if self.input_transform_cache is not None:
                 self.input_transform_cache.note_rotation_in_encoder(inputs)
@@ -323,22 +370,14 @@ class FusedNQRTLinear(nn.Module):
             beta_table = beta_table.to(inputs.device)
         if self.packed_activation_cache is None:
             packed = quantize_activation_cuda(compute_inputs, q=self.activation_q, betas=self.activation_betas,
-                                              beta_table=beta_table, hadamard_block=block, keep_decoded=True)
+                                              beta_table=beta_table, hadamard_block=block, keep_decoded=True,
+                                              rmsnorm=pending_norm)
             encoded = True
         else:
             packed, encoded = self.packed_activation_cache.encode(
                 compute_inputs, q=self.activation_q, betas=self.activation_betas, beta_table=beta_table,
-                hadamard_block=block)
-        self.a4_call_count += 1
-        self.a4_encode_count += int(encoded)
-        if self._group is not None:
-            outputs = self._group.project(packed, self._group_index)
-        elif self.output_dtype == torch.float32:
-            outputs = linear_packed_w4a4_fp32(packed, prepared)  # the accumulator itself, not rounded to the input dtype first
-        else:
-            outputs = linear_packed_w4a4(packed, prepared)
-        self.w4a4_cuda_mma_dispatch_count += 1
-        return outputs.to(self.output_dtype or original_dtype)
+                hadamard_block=block, rmsnorm=pending_norm)
+        return self._finish(packed, encoded, prepared, original_dtype)
 
 
 def keep_decoded_weights_(model: nn.Module, device: torch.device | str | None = None) -> int:

@@ -42,22 +42,49 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
 
 
 class FusedRMSNorm(nn.Module):
-    """Drop-in for ``LlamaRMSNorm``: same parameter, same formula, one launch."""
+    """Drop-in for ``LlamaRMSNorm``: same parameter, same formula, one launch.
 
-    def __init__(self, weight: torch.Tensor, eps: float) -> None:
+    ``defer=True`` is for a norm whose ONLY consumers are ``FusedNQRTLinear`` modules (Llama's
+    ``input_layernorm`` in front of q/k/v and ``post_attention_layernorm`` in front of gate/up): the
+    module then launches nothing and returns a view of its input that carries the pending
+    normalisation; the first projection that receives it normalises, rotates and encodes in one
+    launch (bit-identical to this module's kernel followed by the rotate-and-encode), the others reuse
+    that encoding.  A consumer that cannot fuse materialises the normalised tensor once.
+    """
+
+    def __init__(self, weight: torch.Tensor, eps: float, *, defer: bool = False) -> None:
         super().__init__()
         self.weight = nn.Parameter(weight.detach(), requires_grad=False)
         self.variance_epsilon = float(eps)
+        self.defer = bool(defer)
 
     def forward(self, hidden_states: torch.Tensor) -> torch.Tensor:
+        if self.defer and not torch.is_grad_enabled() and hidden_states.is_cuda:
+            pending = hidden_states.view(hidden_states.shape)  # a new tensor object on the same storage, no launch
+            pending._nq_pending_norm = (self.weight, self.variance_epsilon)
+            return pending
         return rms_norm(hidden_states, self.weight, self.variance_epsilon)
 
     def extra_repr(self) -> str:
         return f"{tuple(self.weight.shape)}, eps={self.variance_epsilon}"
 
 
-def fuse_rmsnorm_(model: nn.Module) -> int:
-    """Replace every RMS-norm child that has a ``weight`` and a ``variance_epsilon`` by ``FusedRMSNorm``."""
+def _feeds_only_packed_projections(layer: nn.Module, norm_name: str) -> bool:
+    """Llama decoder layer: ``input_layernorm`` feeds q/k/v, ``post_attention_layernorm`` feeds gate/up."""
+    from .fused_linear import FusedNQRTLinear
+
+    owner, leaves = {"input_layernorm": ("self_attn", ("q_proj", "k_proj", "v_proj")),
+                     "post_attention_layernorm": ("mlp", ("gate_proj", "up_proj"))}.get(norm_name, (None, ()))
+    block = getattr(layer, owner, None) if owner else None
+    return block is not None and all(isinstance(getattr(block, leaf, None), FusedNQRTLinear) for leaf in leaves)
+
+
+def fuse_rmsnorm_(model: nn.Module, *, defer_into_projections: bool = False) -> int:
+    """Replace every RMS-norm child that has a ``weight`` and a ``variance_epsilon`` by ``FusedRMSNorm``.
+
+    ``defer_into_projections`` lets the two norms of a Llama decoder layer whose consumers are all packed
+    projections hand their work to the projections' encoder launch (see ``FusedRMSNorm``).
+    """
     replaced = 0
     for module in list(model.modules()):
         for name, child in list(module.named_children()):
@@ -65,6 +92,42 @@ def fuse_rmsnorm_(model: nn.Module) -> int:
                 continue
             if not hasattr(child, "variance_epsilon") or not isinstance(getattr(child, "weight", None), torch.Tensor):
                 continue
-            setattr(module, name, FusedRMSNorm(child.weight, child.variance_epsilon))
+            defer = defer_into_projections and _feeds_only_packed_projections(module, name)
+            setattr(module, name, FusedRMSNorm(child.weight, child.variance_epsilon, defer=defer))
+            replaced += 1
+    return replaced
+
+
+class FusedSiluMLP(nn.Module):
+    """Llama's gated MLP ``down(silu(gate(x)) * up(x))`` with the elementwise part inside down_proj's encoder launch.
+
+    Keeps the three projection modules of the MLP it replaces (same attribute names).  The reference leaves SiLU
+    and the product to the model's tensor ops (two launches) in front of ``FusedNQRTLinear``'s own Hadamard and
+    encode (models/fused_linear.py:287-306); no counterpart there.
+    """
+
+    def __init__(self, gate_proj: nn.Module, up_proj: nn.Module, down_proj: nn.Module) -> None:
+        super().__init__()
+        self.gate_proj, self.up_proj, self.down_proj = gate_proj, up_proj, down_proj
+
+    def forward(self, hidden_states: torch.Tensor) -> torch.Tensor:
+        return self.down_proj.forward_silu_mul(self.gate_proj(hidden_states), self.up_proj(hidden_states))
+
+
+def fuse_silu_mlp_(model: nn.Module) -> int:
+    """Replace every Llama-style MLP (``act_fn`` = SiLU, three bias-free packed projections) by ``FusedSiluMLP``."""
+    from .fused_linear import FusedNQRTLinear
+
+    replaced = 0
+    for module in list(model.modules()):
+        for name, child in list(module.named_children()):
+            if isinstance(child, FusedSiluMLP) or not all(hasattr(child, a) for a in ("gate_proj", "up_proj", "down_proj", "act_fn")):
+                continue
+            if not isinstance(child.act_fn, nn.SiLU) and getattr(child.act_fn, "__name__", "") != "silu" \
+                    and type(child.act_fn).__name__ not in {"SiLUActivation", "SiLU"}:
+                continue
+            if not isinstance(child.down_proj, FusedNQRTLinear):
+                continue
+            setattr(module, name, FusedSiluMLP(child.gate_proj, child.up_proj, child.down_proj))
             replaced += 1
     return replaced

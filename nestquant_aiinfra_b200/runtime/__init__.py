@@ -1,7 +1,7 @@
 """Operator layer: the reference's ``nestquant.runtime`` names for the W4A4KV4 path."""
 
 from .w4a4 import (  # noqa: F401
-    PreparedNQA4Activation, PreparedNQRTLinear, prepare_fused_linear, quantize_activation_cuda, quantize_weight_cuda, can_rotate_in_encoder, prefer_rotation_in_encoder, group_prepared_linears,
+    PreparedNQA4Activation, PreparedNQRTLinear, prepare_fused_linear, quantize_activation_cuda, quantize_weight_cuda, can_rotate_in_encoder, prefer_rotation_in_encoder, prefer_producer_in_encoder, group_prepared_linears,
     can_use_w4a4, can_use_w4a4_gemv_m1, can_use_w4a4_mma_small_m, can_use_w4a4_mma_m16,
     can_use_w4a4_mma_large_m_staged, can_use_w4a4_mma_chunked_staged,
     linear_packed_w4a4, linear_packed_w4a4_fp32, linear_packed_w4a4_fused_fp32, linear_packed_w4a4_gemv_m1,

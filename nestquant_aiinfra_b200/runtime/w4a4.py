@@ -182,9 +182,21 @@ def prefer_rotation_in_encoder(rows: int, feature_count: int) -> bool:
     return feature_count <= 4096
 
 
+def prefer_producer_in_encoder(rows: int, feature_count: int) -> bool:
+    """Whether the elementwise producer of a projection input (RMS norm; SiLU(gate) * up), the rotation and the
+    encode should run as ONE launch for this shape.
+
+    Up to 4096 features the rotation is done inside the encoder anyway.  Longer rows (the 8192-wide input of
+    down_proj) are split over several CTAs that each repeat the transform: worth it while the launch is small
+    (decode-time batches, where four launches become one), not for thousands of rows.
+    """
+    return feature_count <= 4096 or rows <= 256
+
+
 def quantize_activation_cuda(
     inputs: torch.Tensor, *, q: int, betas: Sequence[float],
     beta_table: torch.Tensor | None = None, keep_decoded: bool = False, hadamard_block: int | None = None,
+    rmsnorm: tuple[torch.Tensor, float] | None = None, silu_mul_with: torch.Tensor | None = None,
 ) -> PreparedNQA4Activation:
     """Encode floating activations into packed NQA4 payloads in one launch.
 
@@ -193,6 +205,10 @@ def quantize_activation_cuda(
     normalised Hadamard transform of that block size (the whole row when it equals the feature
     count) inside the same launch; the result equals ``quantize_activation_cuda(hadamard(inputs))``
     bit for bit (see ``can_rotate_in_encoder``).
+
+    ``rmsnorm=(weight, eps)`` encodes ``rms_norm(inputs, weight, eps)`` and ``silu_mul_with=up`` encodes
+    ``silu(inputs) * up`` instead of ``inputs`` -- the producer, the rotation (``hadamard_block`` is required) and
+    the encode in one launch, bit-identical to the separate launches.
 
     ``keep_decoded=True`` also writes the BF16 reconstruction of the rows (``2 * M * K`` bytes) that a
     projection called next would otherwise decode for itself; callers that only want the packed
@@ -216,13 +232,37 @@ def quantize_activation_cuda(
     if inputs.dtype not in _DTYPE_TAG:
         raise ValueError("inputs must use float16, bfloat16, or float32")
     k = inputs.shape[-1]
+    producer = None
+    if rmsnorm is not None or silu_mul_with is not None:
+        if rmsnorm is not None and silu_mul_with is not None:
+            raise ValueError("pass rmsnorm or silu_mul_with, not both")
+        if hadamard_block is None:
+            raise ValueError("a producer is fused into the rotate-and-encode launch: hadamard_block is required")
+        if rmsnorm is not None:
+            weight, eps = rmsnorm
+            if (not isinstance(weight, torch.Tensor) or tuple(weight.shape) != (k,) or weight.dtype != inputs.dtype
+                    or weight.device != inputs.device):
+                raise ValueError("the norm weight must be a vector of the feature size with the input's dtype and device")
+            producer = ("rmsnorm", weight.contiguous(), float(eps))
+        else:
+            up = silu_mul_with
+            if (not isinstance(up, torch.Tensor) or up.shape != inputs.shape or up.dtype != inputs.dtype
+                    or up.device != inputs.device):
+                raise ValueError("silu_mul_with must match the input's shape, dtype and device")
+            producer = ("silu_mul", up, 0.0)
     rows = inputs.reshape(-1, k)
     if hadamard_block is not None:
         if not can_rotate_in_encoder(k, hadamard_block):
             raise ValueError("hadamard_block must be a power of two >= 8 dividing a feature count <= 16384")
-        rows = rows.contiguous()
+        if producer is None:
+            rows = rows.contiguous()
     if rows.stride(-1) != 1 or (rows.stride(0) * rows.element_size()) % 16 or rows.data_ptr() % 16:
         rows = rows.contiguous()
+    second = None
+    if producer is not None and producer[0] == "silu_mul":
+        second = producer[1].reshape(-1, k)
+        if (second.stride(-1) != 1 or second.stride(0) != rows.stride(0) or second.data_ptr() % 16):
+            rows, second = rows.contiguous(), second.contiguous()   # the kernel takes one row stride for both
     device = inputs.device
     if beta_table is None:
         beta_table = torch.tensor(beta_values, device=device, dtype=torch.float32)
@@ -234,7 +274,17 @@ def quantize_activation_cuda(
     beta_ids = torch.empty(m * k // 32, dtype=torch.uint8, device=device)
     norms = torch.empty(m, dtype=torch.float32, device=device)
     decoded = torch.empty((m, k), dtype=torch.bfloat16, device=device) if keep_decoded else None
-    if hadamard_block is None:
+    if producer is not None and producer[0] == "rmsnorm":
+        status = _lib.lib().nq_a4_encode_rmsnorm_rotated(
+            _ptr(rows), _ptr(producer[1]), ctypes.c_float(producer[2]), _DTYPE_TAG[inputs.dtype], _I64(m), _I64(k),
+            _I64(rows.stride(0)), _I64(hadamard_block), _ptr(beta_table), _ptr(codes), _ptr(beta_ids), _ptr(norms),
+            _ptr(decoded), _stream(device))
+    elif producer is not None:
+        status = _lib.lib().nq_a4_encode_silu_mul_rotated(
+            _ptr(rows), _ptr(second), _DTYPE_TAG[inputs.dtype], _I64(m), _I64(k), _I64(rows.stride(0)),
+            _I64(hadamard_block), _ptr(beta_table), _ptr(codes), _ptr(beta_ids), _ptr(norms), _ptr(decoded),
+            _stream(device))
+    elif hadamard_block is None:
         status = _lib.lib().nq_a4_encode(
             _ptr(rows), _DTYPE_TAG[inputs.dtype], _I64(m), _I64(k), _I64(rows.stride(0)), _ptr(beta_table),
             _ptr(codes), _ptr(beta_ids), _ptr(norms), _ptr(decoded), _stream(device))

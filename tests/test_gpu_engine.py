@@ -333,3 +333,35 @@ def test_device_side_page_allocation_matches_static_ids_with_a_smaller_pool():
     device.register("late", slot=3, max_tokens=96)          # 7 + 7 + 6 = 20 pages of budget: fits the 24
     with pytest.raises(RuntimeError, match="exhausted"):
         device.register("too much", slot=1, max_tokens=80)   # 5 more pages do not
+
+
+def test_producers_fused_into_the_projections_change_no_token():
+    """Norms deferred into the q/k/v and gate/up encoder launch, SiLU * up inside down_proj's: same greedy tokens
+    through a ragged prefill and eager + graph decode as with the separate launches, and fewer launches per step."""
+    from nestquant_aiinfra_b200.engine import BatchedNQKVLlamaRunner, build_llama_w4a4kv4
+    from nestquant_aiinfra_b200.norm import FusedRMSNorm, FusedSiluMLP
+    from nestquant_aiinfra_b200.runtime import launch_count
+
+    common = dict(hidden_size=256, intermediate_size=512, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=64,
+                  vocab_size=128, capacity=4, max_cache_len=128, seed=11)
+    gen = torch.Generator().manual_seed(31)
+    prompts = [torch.randint(0, 128, (n,), generator=gen) for n in (17, 40, 5)]
+    tokens, launches = {}, {}
+    for fused in (False, True):
+        model, cache = build_llama_w4a4kv4(**common, fuse_producers=fused)
+        layer = model.model.layers[0]
+        assert isinstance(layer.mlp, FusedSiluMLP) == fused
+        assert isinstance(layer.input_layernorm, FusedRMSNorm) and layer.input_layernorm.defer == fused
+        assert not model.model.norm.defer                       # the final norm feeds the dense lm_head
+        runner = BatchedNQKVLlamaRunner(model, cache)
+        seen = [runner.prefill_slots([0, 1, 3], prompts).clone()]
+        before = launch_count()
+        seen.append(runner.decode_eager().clone())
+        launches[fused] = launch_count() - before
+        seen += [runner.decode_eager().clone() for _ in range(3)]
+        runner.capture_decode_graph()
+        seen += [runner.decode().clone() for _ in range(4)]
+        tokens[fused] = seen
+    for a, b in zip(tokens[False], tokens[True]):
+        assert torch.equal(a, b)
+    assert launches[True] < launches[False]

@@ -289,3 +289,33 @@ def test_fused_decode_gemm_equals_the_two_launch_path(rt, oracle, m, n, k):
     expected = oracle.gemm_bf16_operands(oracle.dequantize_rows(codes, beta_ids, norms, ACT_BETAS, m, k), w_deq)
     actual = fused.cpu().numpy()
     assert max_abs(actual, expected) <= MAX_ABS_TOL and rel_fro(actual, expected) <= REL_FRO_TOL
+
+
+@pytest.mark.parametrize("rows,k,dtype", [(5, 2048, torch.bfloat16), (64, 2048, torch.bfloat16), (1, 4096, torch.bfloat16),
+                                          (3, 8192, torch.bfloat16), (70, 8192, torch.bfloat16), (9, 1024, torch.float16),
+                                          (4, 512, torch.float32)])
+def test_producers_inside_the_encoder_equal_the_separate_launches(rt, rows, k, dtype):
+    """RMS norm -> rotate -> encode and SiLU(gate) * up -> rotate -> encode as ONE launch each: the same streams,
+    norms and reconstruction as the producer's own launch(es) followed by the rotate-and-encode launch."""
+    from nestquant_aiinfra_b200.norm import rms_norm
+
+    def same(one, two):
+        assert torch.equal(one.code_payload, two.code_payload) and torch.equal(one.beta_payload, two.beta_payload)
+        assert torch.equal(one.row_norms, two.row_norms) and torch.equal(one.decoded, two.decoded)
+
+    x = (3.0 * torch.randn(rows, k, generator=rng(900 + rows))).to(dtype).cuda()
+    weight = (1.0 + 0.1 * torch.randn(k, generator=rng(901))).to(dtype).cuda()
+    one = rt.quantize_activation_cuda(x, q=14, betas=ACT_BETAS, hadamard_block=k, keep_decoded=True, rmsnorm=(weight, 1e-5))
+    two = rt.quantize_activation_cuda(rms_norm(x, weight, 1e-5), q=14, betas=ACT_BETAS, hadamard_block=k, keep_decoded=True)
+    same(one, two)
+    # gate and up as the two column ranges of one stacked projection output (row stride 2k)
+    stacked = torch.randn(rows, 2 * k, generator=rng(902 + rows)).to(dtype).cuda()
+    gate, up = stacked[:, :k], stacked[:, k:]
+    one = rt.quantize_activation_cuda(gate, q=14, betas=ACT_BETAS, hadamard_block=k, keep_decoded=True, silu_mul_with=up)
+    two = rt.quantize_activation_cuda(torch.nn.functional.silu(gate) * up, q=14, betas=ACT_BETAS, hadamard_block=k,
+                                      keep_decoded=True)
+    same(one, two)
+    with pytest.raises(ValueError):
+        rt.quantize_activation_cuda(gate, q=14, betas=ACT_BETAS, silu_mul_with=up)             # needs hadamard_block
+    with pytest.raises(ValueError):
+        rt.quantize_activation_cuda(x, q=14, betas=ACT_BETAS, hadamard_block=k, rmsnorm=(weight[:8], 1e-5))
