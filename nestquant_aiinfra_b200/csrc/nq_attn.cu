@@ -15,6 +15,7 @@
 #include <math.h>
 
 #include "nq_common.cuh"
+#include "nq_lut.cuh"
 
 namespace {
 
@@ -42,6 +43,7 @@ struct AttnParams {
     float scale_log2e;  // attention scale * log2(e)
     float sqrt_dim, inv_sqrt_dim;
     int splits;
+    int per_slots;  // page slots (cold pages + hot tail) per split
     float* partial;  // [B*Tq, Hq, splits, D + 2]
     void* out;       // [B, Tq, Hq, D]
     int out_dtype;
@@ -95,259 +97,398 @@ __device__ __forceinline__ void nq_lattice_block(const uint2 raw, float v[8]) {
     }
 }
 
+// Sum of v[0..N) over the 32 lanes by recursive halving: in every round a lane keeps one half of its values and
+// hands the other half to the partner lane^M.  With N >= 32 a lane ends up owning the totals of the N / 32
+// values [lane * N/32, (lane + 1) * N/32) in v[0..N/32); with N < 32 value lane / (32 / N) in v[0] (the lanes of
+// one group all hold it).
+template <int N, int M>
+__device__ __forceinline__ void reduce_scatter(float* v, int lane) {
+    if constexpr (M >= 1) {
+        if constexpr (N >= 2) {
+            const bool up = (lane & M) != 0;
+#pragma unroll
+            for (int i = 0; i < N / 2; ++i) {
+                const float send = up ? v[i] : v[i + N / 2];
+                const float keep = up ? v[i + N / 2] : v[i];
+                v[i] = keep + __shfl_xor_sync(0xffffffffu, send, M);
+            }
+            reduce_scatter<N / 2, M / 2>(v, lane);
+        } else {
+            v[0] += __shfl_xor_sync(0xffffffffu, v[0], M);
+            reduce_scatter<1, M / 2>(v, lane);
+        }
+    }
+}
+
+// a[c] of a small register array with a run-time index (a chain of selects: the array stays in registers)
+template <typename T, int N>
+__device__ __forceinline__ T pick_step(const T (&a)[N], int c) {
+    T v = a[0];
+#pragma unroll
+    for (int i = 1; i < N; ++i) v = (c == i) ? a[i] : v;
+    return v;
+}
+
+// 2-bit beta ids of the BPR blocks of one row (block b in bits 2b, 2b+1).
+template <int BPR>
+struct RowIds {
+    using type = uint32_t;
+};
+template <>
+struct RowIds<32> {
+    using type = uint64_t;
+};
+template <int BPR>
+__device__ __forceinline__ typename RowIds<BPR>::type load_row_ids(const uint8_t* ids, int64_t row) {
+    const uint8_t* src = ids + row * (BPR / 4);
+    if constexpr (BPR == 4) return __ldg(src);
+    else if constexpr (BPR == 8) return __ldg(reinterpret_cast<const uint16_t*>(src));
+    else if constexpr (BPR == 16) return __ldg(reinterpret_cast<const uint32_t*>(src));
+    else return __ldg(reinterpret_cast<const unsigned long long*>(src));
+}
+
+// One CTA = one (query token, KV head, page-range split); its four warps take turns on steps of 32 consecutive
+// token positions of the range, ONE TOKEN PER LANE.  A warp works in chunks of CH of its steps:
+//   pass 1  every lane decodes the K blocks of its token one after the other and accumulates the scores of the
+//           G query heads (query in shared memory, read as broadcasts): no cross-lane traffic at all;
+//   softmax chunk maximum per head over the warp (the reference point only moves when it is exceeded by more
+//           than 8, i.e. a factor 256), one exp2 per (token, head);
+//   pass 2  block by block of V: every lane decodes the block of its CH tokens and accumulates the G x 8
+//           products p * v; ONE recursive-halving reduction per block and chunk then leaves each lane with the
+//           chunk's total of one output feature, which it adds to its running output.
+// K/V blocks are decoded once for all query heads of the GQA group.
 template <int G, int BPR, bool LAT>
 __global__ void __launch_bounds__(kAttnThreads, (G <= 4 ? 4 : 3)) nq_attn_paged_kernel(const AttnParams p) {
-    constexpr int TPW = 32 / BPR;  // tokens per warp step
     constexpr int D = BPR * 8;
-    __shared__ float s_merge[kAttnWarps][G][D + 2];
+    constexpr int NV = G * 8;                      // products of one V block
+    constexpr int NVL = NV >= 32 ? NV / 32 : 1;    // totals a lane owns after the reduction
+    constexpr int CH = G <= 4 ? 4 : 2;             // steps per chunk (bounded by the registers of p[CH][G])
+    using Ids = typename RowIds<BPR>::type;
+    // Shared memory: [decode table of the packed pages | scaled query | scores / probabilities]; the merge
+    // buffer of the epilogue reuses the same storage once every warp has left the page loop.
+    constexpr size_t kMergeBytes = sizeof(float) * kAttnWarps * G * (D + 2);
+    constexpr size_t kTableBytes = LAT ? 0 : sizeof(NqLutShared);
+    constexpr size_t kQueryBytes = sizeof(float) * G * D;
+    constexpr size_t kProbBytes = sizeof(float) * CH * kAttnThreads * G;
+    constexpr size_t kLoopBytes = kTableBytes + kQueryBytes + kProbBytes;
+    constexpr size_t kSharedBytes = kMergeBytes > kLoopBytes ? kMergeBytes : kLoopBytes;
+    static_assert(kTableBytes % 16 == 0 && kQueryBytes % 16 == 0, "shared-memory regions must stay 16-byte aligned");
+    __shared__ __align__(16) unsigned char s_raw[kSharedBytes];
+    float (*s_merge)[G][D + 2] = reinterpret_cast<float (*)[G][D + 2]>(s_raw);
+    const NqLutShared* lut = reinterpret_cast<const NqLutShared*>(s_raw);
+    float* s_q = reinterpret_cast<float*>(s_raw + kTableBytes);
+    // scores, then probabilities, of my token of each step
+    float (*s_prob)[kAttnThreads][G] = reinterpret_cast<float (*)[kAttnThreads][G]>(s_raw + kTableBytes + kQueryBytes);
 
     const int qi = blockIdx.x / p.kv_heads, h = blockIdx.x - qi * p.kv_heads;
     const int split = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int blk = lane % BPR, tsub = lane / BPR;
 
     int slot, limit, total_slots, page_count, last_len, hot_len;
     const bool active = resolve_query(p, qi, slot, limit, total_slots, page_count, last_len, hot_len);
     const int cold = page_count > 0 ? (page_count - 1) * p.page_size + last_len : 0;
 
-    float m[G], l[G], acc[G][8], q[G][8];
+    // A split that starts past the sequence's end (or past the causal limit) has nothing to add: it leaves the
+    // neutral partial and returns before the table is loaded.
+    if (p.splits > 1 && !(active && split * p.per_slots < total_slots && split * p.per_slots * p.page_size < limit)) {
+        for (int item = threadIdx.x; item < G * (D + 2); item += kAttnThreads) {
+            const int g = item / (D + 2), f = item - g * (D + 2);
+            p.partial[(((int64_t)qi * p.q_heads + h * G + g) * p.splits + split) * (D + 2) + f] = f == D ? -INFINITY : 0.0f;
+        }
+        return;
+    }
+
+    // the G query heads of this KV head are contiguous: [qi][h * G .. h * G + G)[D], pre-multiplied by scale * log2(e)
+    for (int i = threadIdx.x; i < G * D / 8; i += kAttnThreads) {
+        const int64_t qoff = ((int64_t)qi * p.q_heads + h * G) * D + i * 8;
+        float v[8];
+        if (p.q_dtype == NQ_BF16) nq_load8<__nv_bfloat16>(reinterpret_cast<const __nv_bfloat16*>(p.query) + qoff, v);
+        else if (p.q_dtype == NQ_F16) nq_load8<__half>(reinterpret_cast<const __half*>(p.query) + qoff, v);
+        else nq_load8<float>(reinterpret_cast<const float*>(p.query) + qoff, v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s_q[i * 8 + j] = v[j] * p.scale_log2e;
+    }
+    if constexpr (!LAT) nq_lut_load(reinterpret_cast<NqLutShared*>(s_raw));  // ends with a barrier
+    else __syncthreads();
+
+    float m[G], l[G], out[BPR][NVL];
 #pragma unroll
     for (int g = 0; g < G; ++g) {
         m[g] = -INFINITY;
         l[g] = 0.0f;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) acc[g][j] = 0.0f;
-        const int64_t qoff = ((int64_t)qi * p.q_heads + h * G + g) * D + blk * 8;
-        if (p.q_dtype == NQ_BF16) nq_load8<__nv_bfloat16>(reinterpret_cast<const __nv_bfloat16*>(p.query) + qoff, q[g]);
-        else if (p.q_dtype == NQ_F16) nq_load8<__half>(reinterpret_cast<const __half*>(p.query) + qoff, q[g]);
-        else nq_load8<float>(reinterpret_cast<const float*>(p.query) + qoff, q[g]);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) q[g][j] *= p.scale_log2e;
     }
+#pragma unroll
+    for (int b = 0; b < BPR; ++b)
+#pragma unroll
+        for (int i = 0; i < NVL; ++i) out[b][i] = 0.0f;
+    // the head whose totals this lane owns after a reduction
+    const int my_head = (NV >= 32 ? lane * NVL : lane / (32 / (NV < 32 ? NV : 32))) >> 3;
 
     if (active) {
-        const int per = (total_slots + p.splits - 1) / p.splits;
-        const int s_begin = split * per, s_end = min(total_slots, s_begin + per);
-        const int rows = p.page_size * p.kv_heads;
-        const int64_t code_bytes = (int64_t)rows * D / 2, beta_bytes = (int64_t)rows * D / 32;
-        // scores of one token against the G query heads and the running-softmax update (lane = one E8 block)
-        auto update = [&](const float kvec[8], const float vvec[8], float kscale, float vscale, bool valid) {
+        const int P = p.page_size;
+        const int s_begin = split * p.per_slots, s_end = min(total_slots, s_begin + p.per_slots);
+        const int tok_begin = s_begin * P, tok_end = s_end * P;
+        const int steps = tok_end > tok_begin ? (tok_end - tok_begin + 31) >> 5 : 0;
+        const int rows = P * p.kv_heads;
+        const uint32_t* kcodes = reinterpret_cast<const uint32_t*>(p.key_codes);
+        const uint32_t* vcodes = reinterpret_cast<const uint32_t*>(p.value_codes);
+
+        float kbeta[4], vbeta[4];
 #pragma unroll
-            for (int g = 0; g < G; ++g) {
-                float s = 0.0f;
-#pragma unroll
-                for (int j = 0; j < 8; ++j) s = fmaf(q[g][j], kvec[j], s);
-                s *= kscale;  // the beta of this lane's block, the norm of its row
-#pragma unroll
-                for (int off = 1; off < BPR; off <<= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-                if (valid) {
-                    // The reference point m[g] of the running softmax only moves when a score exceeds it
-                    // by more than 8 (a factor 256): until then the terms are added unscaled, which saves
-                    // the rescaling of the accumulator on almost every token and changes no sum mathematically.
-                    if (s > m[g] + 8.0f) {
-                        const float corr = exp2f(m[g] - s);  // exp2(-inf) = 0 on the first token
-                        l[g] *= corr;
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) acc[g][j] *= corr;
-                        m[g] = s;
-                    }
-                    const float pr = exp2f(s - m[g]);
-                    l[g] += pr;
-                    const float pv = pr * vscale;
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) acc[g][j] = fmaf(pv, vvec[j], acc[g][j]);
-                }
-            }
-        };
-        if constexpr (LAT) {
-            // Decoded shadow: a page costs a few hundred instructions per warp, so the loads are what has to be
-            // hidden.  The warp walks its cold pages as a stream of half-page items and fetches item i + 1
-            // (lattice coordinates, beta ids, norms) before it computes item i; token order is unchanged, so
-            // the sums are those of the packed kernel.
-            constexpr int CH = 2;                  // token steps per item
-            constexpr int kItemTokens = CH * TPW;
-            const int items_per_page = (p.page_size + kItemTokens - 1) / kItemTokens;
-            const int cold_end = min(s_end, page_count);
-            uint2 nk[CH], nv[CH];
-            int nid[CH];
-            float nkn[CH], nvn[CH];
-            // returns the page id of the item, -1 past the end of the warp's work, -2 for a page to skip
-            auto fetch_item = [&](int item) -> int {
-                const int ps = s_begin + warp + (item / items_per_page) * kAttnWarps;
-                if (ps >= cold_end || ps * p.page_size >= limit) return -1;
-                const int page_id = p.page_indices[(int64_t)slot * p.max_pages + ps];
-                if (page_id < 0 || page_id >= p.pool_capacity) return -2;
-                const int t_base = (item % items_per_page) * kItemTokens + tsub;
-#pragma unroll
-                for (int i = 0; i < CH; ++i) {
-                    const int row = min(t_base + i * TPW, p.page_size - 1) * p.kv_heads + h;
-                    const int64_t g = (int64_t)row * BPR + blk;
-                    const int64_t gl = (int64_t)page_id * rows * BPR + g;
-                    nk[i] = __ldg(reinterpret_cast<const uint2*>(p.key_lattice) + gl);
-                    nv[i] = __ldg(reinterpret_cast<const uint2*>(p.value_lattice) + gl);
-                    nid[i] = nq_beta_id(p.key_betas + page_id * beta_bytes, g) |
-                             (nq_beta_id(p.value_betas + page_id * beta_bytes, g) << 2);
-                    nkn[i] = __ldg(p.key_norms + (int64_t)page_id * rows + row);
-                    nvn[i] = __ldg(p.value_norms + (int64_t)page_id * rows + row);
-                }
-                return page_id;
-            };
-            int item = 0;
-            int next_page = fetch_item(0);
-            while (next_page != -1) {
-                uint2 ck[CH], cv[CH];
-                int cid[CH];
-                float ckn[CH], cvn[CH];
-#pragma unroll
-                for (int i = 0; i < CH; ++i) {
-                    ck[i] = nk[i]; cv[i] = nv[i]; cid[i] = nid[i]; ckn[i] = nkn[i]; cvn[i] = nvn[i];
-                }
-                const int this_page = next_page, this_item = item;
-                ++item;
-                next_page = fetch_item(item);
-                if (this_page < 0) continue;
-                const int ps = s_begin + warp + (this_item / items_per_page) * kAttnWarps;
-                const int tlimit = ps == page_count - 1 ? last_len : p.page_size;
-                const int base_token = ps * p.page_size;
-                const int t_first = (this_item % items_per_page) * kItemTokens;
-#pragma unroll
-                for (int i = 0; i < CH; ++i) {
-                    if (t_first + i * TPW >= tlimit) break;  // warp-uniform
-                    const int t = t_first + i * TPW + tsub;
-                    const bool valid = t < tlimit && base_token + t < limit;
-                    const float kb = __ldg(p.key_beta_table + (cid[i] & 3));
-                    const float vb = __ldg(p.value_beta_table + (cid[i] >> 2));
-                    const float kds = nq_div_by(ckn[i], p.sqrt_dim, p.inv_sqrt_dim);
-                    const float vds = nq_div_by(cvn[i], p.sqrt_dim, p.inv_sqrt_dim);
-                    float kvec[8], vvec[8];
-                    nq_lattice_block(ck[i], kvec);
-                    nq_lattice_block(cv[i], vvec);
-                    update(kvec, vvec, kb * kds, vb * vds, valid);
-                }
-            }
+        for (int i = 0; i < 4; ++i) {
+            kbeta[i] = __ldg(p.key_beta_table + i);
+            vbeta[i] = __ldg(p.value_beta_table + i);
         }
-        for (int ps = s_begin + warp; ps < s_end; ps += kAttnWarps) {
-            const bool is_hot = ps >= page_count;
-            if (LAT && !is_hot) continue;  // cold pages were streamed above
-            const int base_token = is_hot ? cold : ps * p.page_size;
-            if (base_token >= limit) break;  // warp-uniform: later slots are later tokens
-            const int tlimit = is_hot ? hot_len : (ps == page_count - 1 ? last_len : p.page_size);
-            int page_id = 0;
-            if (!is_hot) {
-                page_id = p.page_indices[(int64_t)slot * p.max_pages + ps];
-                if (page_id < 0 || page_id >= p.pool_capacity) continue;  // defensive: never read outside the pool
-            }
-            // pull the codes of this warp's NEXT page towards L1 while this one is decoded: lane l asks for
-            // the code row of token l & 15 (keys on lanes 0..15, values on lanes 16..31)
-            {
-                const int nps = ps + kAttnWarps;
-                if (nps < s_end && nps < page_count && (lane & 15) < p.page_size) {
-                    const int next_id = p.page_indices[(int64_t)slot * p.max_pages + nps];
-                    if (next_id >= 0 && next_id < p.pool_capacity) {
-                        const int row = (lane & 15) * p.kv_heads + h;
-                        if (LAT) {  // the row's decoded coordinates: D bytes
-                            const int8_t* src = (lane < 16 ? p.key_lattice : p.value_lattice) +
-                                                ((int64_t)next_id * rows + row) * D;
-                            asm volatile("prefetch.global.L1 [%0];" ::"l"(src));
-                            if (D > 128) asm volatile("prefetch.global.L1 [%0];" ::"l"(src + 128));
-                        } else {
-                            const uint8_t* src = (lane < 16 ? p.key_codes : p.value_codes) + next_id * code_bytes +
-                                                 (int64_t)row * BPR * 4;
-                            asm volatile("prefetch.global.L1 [%0];" ::"l"(src));
-                            if (BPR * 4 > 128) asm volatile("prefetch.global.L1 [%0];" ::"l"(src + 128));
+        for (int st0 = warp; st0 < steps; st0 += kAttnWarps * CH) {
+            // ---- where is my token of each step?  (all loads of the chunk's bookkeeping go out together) ----
+            int64_t row[CH];       // row of the pool (cold) or of the hot tail
+            unsigned hot_mask = 0, valid_mask = 0, any_mask = 0;   // bit c: this lane's token of step c
+            Ids kid[CH], vid[CH];
+            float kds[CH], vds[CH];
+#pragma unroll
+            for (int c = 0; c < CH; ++c) {
+                const int st = st0 + c * kAttnWarps;
+                row[c] = 0;
+                kid[c] = 0;
+                vid[c] = 0;
+                kds[c] = 0.0f;
+                vds[c] = 0.0f;
+                bool valid = false, hot = false;
+                if (st < steps) {
+                    const int tau = tok_begin + st * 32 + lane;
+                    const int ps = tau / P, t = tau - ps * P;
+                    if (tau < tok_end) {
+                        hot = ps >= page_count;
+                        const int tlimit = hot ? hot_len : (ps == page_count - 1 ? last_len : P);
+                        const int base_token = hot ? cold : ps * P;
+                        valid = t < tlimit && base_token + t < limit;
+                        if (valid && !hot) {
+                            const int page_id = p.page_indices[(int64_t)slot * p.max_pages + ps];
+                            valid = page_id >= 0 && page_id < p.pool_capacity;  // defensive: never read outside the pool
+                            if (valid) {
+                                row[c] = (int64_t)page_id * rows + t * p.kv_heads + h;
+                                kid[c] = load_row_ids<BPR>(p.key_betas, row[c]);
+                                vid[c] = load_row_ids<BPR>(p.value_betas, row[c]);
+                                kds[c] = __ldg(p.key_norms + row[c]);
+                                vds[c] = __ldg(p.value_norms + row[c]);
+                                // pull the code rows towards L1: the first use is a few hundred instructions away
+                                if constexpr (LAT) {
+                                    asm volatile("prefetch.global.L1 [%0];" ::"l"(p.key_lattice + row[c] * D));
+                                    asm volatile("prefetch.global.L1 [%0];" ::"l"(p.value_lattice + row[c] * D));
+                                } else {
+                                    asm volatile("prefetch.global.L1 [%0];" ::"l"(kcodes + row[c] * BPR));
+                                    asm volatile("prefetch.global.L1 [%0];" ::"l"(vcodes + row[c] * BPR));
+                                }
+                            }
+                        } else if (valid) {
+                            row[c] = ((int64_t)slot * P + t) * p.kv_heads + h;
                         }
                     }
                 }
+                const bool any = __any_sync(0xffffffffu, valid);
+                valid_mask |= (valid ? 1u : 0u) << c;
+                hot_mask |= (hot ? 1u : 0u) << c;
+                any_mask |= (any ? 1u : 0u) << c;
             }
-            if (is_hot) {
-                for (int t0 = 0; t0 < tlimit; t0 += TPW) {
-                    const int t = t0 + tsub;
-                    const bool valid = t < tlimit && base_token + t < limit;
-                    float kvec[8], vvec[8];
-                    const int64_t off = (((int64_t)slot * p.page_size + min(t, p.page_size - 1)) * p.kv_heads + h) * D + blk * 8;
-                    nq_load8<__nv_bfloat16>(reinterpret_cast<const __nv_bfloat16*>(p.hot_keys) + off, kvec);
-                    nq_load8<__nv_bfloat16>(reinterpret_cast<const __nv_bfloat16*>(p.hot_values) + off, vvec);
-                    update(kvec, vvec, 1.0f, 1.0f, valid);
+#pragma unroll
+            for (int c = 0; c < CH; ++c) {
+                kds[c] = nq_div_by(kds[c], p.sqrt_dim, p.inv_sqrt_dim);
+                vds[c] = nq_div_by(vds[c], p.sqrt_dim, p.inv_sqrt_dim);
+            }
+            // The step loops below stay rolled (ONE copy of the block decode per pass: laid out once per
+            // step the kernel text no longer fits the instruction cache), so the per-step values are
+            // picked out of their registers by index.
+            // ---- pass 1: scores of my token against the G heads, two blocks at a time ----
+#pragma unroll 1
+            for (int c = 0; c < CH; ++c) {
+                const bool valid = (valid_mask >> c) & 1u, hot = (hot_mask >> c) & 1u;
+                const bool cold_row = valid && !hot;
+                const int64_t my_row = pick_step(row, c);
+                const Ids my_ids = pick_step(kid, c);
+                const float my_ds = pick_step(kds, c);
+                float sc[G];
+#pragma unroll
+                for (int g = 0; g < G; ++g) sc[g] = 0.0f;
+                if ((any_mask >> c) & 1u) {
+                    // the operands of the NEXT pair of blocks are fetched before this pair is decoded
+                    uint2 next_words = make_uint2(0, 0);
+                    uint4 next_lat = make_uint4(0, 0, 0, 0);
+                    if (cold_row) {
+                        if constexpr (LAT) next_lat = __ldg(reinterpret_cast<const uint4*>(p.key_lattice) + my_row * (BPR / 2));
+                        else next_words = __ldg(reinterpret_cast<const uint2*>(kcodes + my_row * BPR));
+                    }
+#pragma unroll 1
+                    for (int b = 0; b < BPR; b += 2) {
+                        float kv0[8], kv1[8], ksc0 = 0.0f, ksc1 = 0.0f;
+                        const uint2 words = next_words;
+                        const uint4 lat = next_lat;
+                        if (cold_row && b + 2 < BPR) {
+                            if constexpr (LAT) next_lat = __ldg(reinterpret_cast<const uint4*>(p.key_lattice) + my_row * (BPR / 2) + (b >> 1) + 1);
+                            else next_words = __ldg(reinterpret_cast<const uint2*>(kcodes + my_row * BPR + b + 2));
+                        }
+                        if constexpr (LAT) {
+                            nq_lattice_block(make_uint2(lat.x, lat.y), kv0);  // zero words (inactive lane) decode to finite values
+                            nq_lattice_block(make_uint2(lat.z, lat.w), kv1);
+                        } else {
+                            NqLutBlock b0, b1;
+                            nq_lut_begin_shared(words.x, lut, lane, b0);
+                            nq_lut_begin_shared(words.y, lut, lane, b1);
+                            bool ic0 = b0.delta < 0, ic1 = b1.delta < 0;
+                            if (b0.delta == 0) ic0 = nq_lut_resolve_tie_shared(b0, lut);
+                            if (b1.delta == 0) ic1 = nq_lut_resolve_tie_shared(b1, lut);
+                            nq_lut_finish(b0, ic0, kv0);
+                            nq_lut_finish(b1, ic1, kv1);
+                        }
+                        if (cold_row) {
+                            ksc0 = pick_step(kbeta, (int)((my_ids >> (2 * b)) & 3)) * my_ds;
+                            ksc1 = pick_step(kbeta, (int)((my_ids >> (2 * b + 2)) & 3)) * my_ds;
+                        } else if (valid) {  // hot tail: BF16 rows
+                            const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(p.hot_keys) + my_row * D + b * 8;
+                            nq_load8<__nv_bfloat16>(src, kv0);
+                            nq_load8<__nv_bfloat16>(src + 8, kv1);
+                            ksc0 = ksc1 = 1.0f;
+                        }
+                        const float4* qrow = reinterpret_cast<const float4*>(s_q + b * 8);
+#pragma unroll
+                        for (int g = 0; g < G; ++g) {
+                            const float4 q0 = qrow[g * (D / 4)], q1 = qrow[g * (D / 4) + 1];
+                            const float4 q2 = qrow[g * (D / 4) + 2], q3 = qrow[g * (D / 4) + 3];
+                            float d0 = q0.x * kv0[0], d1 = q2.x * kv1[0];
+                            d0 = fmaf(q0.y, kv0[1], d0); d1 = fmaf(q2.y, kv1[1], d1);
+                            d0 = fmaf(q0.z, kv0[2], d0); d1 = fmaf(q2.z, kv1[2], d1);
+                            d0 = fmaf(q0.w, kv0[3], d0); d1 = fmaf(q2.w, kv1[3], d1);
+                            d0 = fmaf(q1.x, kv0[4], d0); d1 = fmaf(q3.x, kv1[4], d1);
+                            d0 = fmaf(q1.y, kv0[5], d0); d1 = fmaf(q3.y, kv1[5], d1);
+                            d0 = fmaf(q1.z, kv0[6], d0); d1 = fmaf(q3.z, kv1[6], d1);
+                            d0 = fmaf(q1.w, kv0[7], d0); d1 = fmaf(q3.w, kv1[7], d1);
+                            sc[g] = fmaf(ksc0, d0, sc[g]);
+                            sc[g] = fmaf(ksc1, d1, sc[g]);
+                        }
+                    }
                 }
-            } else {
-                // The packed operands of the NEXT token step are fetched before this step is decoded: the
-                // decode is a few hundred instructions long, enough to cover the loads' latency.
-                const uint32_t* kcodes = reinterpret_cast<const uint32_t*>(p.key_codes + page_id * code_bytes);
-                const uint32_t* vcodes = reinterpret_cast<const uint32_t*>(p.value_codes + page_id * code_bytes);
-                const uint8_t* kbetas = p.key_betas + page_id * beta_bytes;
-                const uint8_t* vbetas = p.value_betas + page_id * beta_bytes;
-                const float* knorms = p.key_norms + (int64_t)page_id * rows;
-                const float* vnorms = p.value_norms + (int64_t)page_id * rows;
-                uint32_t kw = 0, vw = 0;
-                uint2 klat = make_uint2(0, 0), vlat = make_uint2(0, 0);
-                int kid, vid;
-                float kn, vn;
-                auto fetch = [&](int t) {
-                    const int row = min(t, p.page_size - 1) * p.kv_heads + h;
-                    const int64_t g = (int64_t)row * BPR + blk;
-                    if (LAT) {
-                        const int64_t gl = (int64_t)page_id * rows * BPR + g;
-                        klat = __ldg(reinterpret_cast<const uint2*>(p.key_lattice) + gl);
-                        vlat = __ldg(reinterpret_cast<const uint2*>(p.value_lattice) + gl);
+#pragma unroll
+                for (int g = 0; g < G; ++g) s_prob[c][threadIdx.x][g] = valid ? sc[g] : -INFINITY;
+            }
+
+            // ---- softmax of the chunk (every thread only touches its own column of s_prob) ----
+            bool rescale = false;
+            float my_corr = 1.0f;
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                float sv[CH];
+#pragma unroll
+                for (int c = 0; c < CH; ++c) sv[c] = s_prob[c][threadIdx.x][g];
+                float cm = sv[0];
+#pragma unroll
+                for (int c = 1; c < CH; ++c) cm = fmaxf(cm, sv[c]);
+#pragma unroll
+                for (int off = 16; off >= 1; off >>= 1) cm = fmaxf(cm, __shfl_xor_sync(0xffffffffu, cm, off));
+                // The reference point m[g] of the running softmax only moves when a score exceeds it by more
+                // than 8 (a factor 256): until then the terms are added unscaled, which saves rescaling the
+                // running output on almost every chunk and changes no sum mathematically.
+                if (cm > m[g] + 8.0f) {
+                    const float corr = exp2f(m[g] - cm);  // exp2(-inf) = 0 on the first chunk
+                    l[g] *= corr;
+                    if (g == my_head) my_corr = corr;
+                    m[g] = cm;
+                    rescale = true;
+                }
+#pragma unroll
+                for (int c = 0; c < CH; ++c) {
+                    const float pr = ((valid_mask >> c) & 1u) ? exp2f(sv[c] - m[g]) : 0.0f;
+                    s_prob[c][threadIdx.x][g] = pr;
+                    l[g] += pr;
+                }
+            }
+            if (rescale) {
+#pragma unroll
+                for (int b = 0; b < BPR; ++b)
+#pragma unroll
+                    for (int i = 0; i < NVL; ++i) out[b][i] *= my_corr;
+            }
+
+            // ---- pass 2: p * V, one block of features at a time, two steps at a time ----
+#pragma unroll 1
+            for (int b = 0; b < BPR; ++b) {
+                float acc[NV];
+#pragma unroll
+                for (int i = 0; i < NV; ++i) acc[i] = 0.0f;
+#pragma unroll 1
+                for (int c = 0; c < CH; c += 2) {
+                    if (!((any_mask >> c) & 3u)) continue;  // warp-uniform: neither step has a token
+                    const bool valid0 = (valid_mask >> c) & 1u, valid1 = (valid_mask >> (c + 1)) & 1u;
+                    const bool cold0 = valid0 && !((hot_mask >> c) & 1u), cold1 = valid1 && !((hot_mask >> (c + 1)) & 1u);
+                    const int64_t row0 = pick_step(row, c), row1 = pick_step(row, c + 1);
+                    float vv0[8], vv1[8], vsc0 = 0.0f, vsc1 = 0.0f;
+                    if constexpr (LAT) {
+                        const uint2 z = make_uint2(0, 0);
+                        nq_lattice_block(cold0 ? __ldg(reinterpret_cast<const uint2*>(p.value_lattice) + row0 * BPR + b) : z, vv0);
+                        nq_lattice_block(cold1 ? __ldg(reinterpret_cast<const uint2*>(p.value_lattice) + row1 * BPR + b) : z, vv1);
                     } else {
-                        kw = __ldg(kcodes + g);
-                        vw = __ldg(vcodes + g);
+                        const uint32_t w0 = cold0 ? __ldg(vcodes + row0 * BPR + b) : 0u;
+                        const uint32_t w1 = cold1 ? __ldg(vcodes + row1 * BPR + b) : 0u;
+                        NqLutBlock b0, b1;
+                        nq_lut_begin_shared(w0, lut, lane, b0);
+                        nq_lut_begin_shared(w1, lut, lane, b1);
+                        bool ic0 = b0.delta < 0, ic1 = b1.delta < 0;
+                        if (b0.delta == 0) ic0 = nq_lut_resolve_tie_shared(b0, lut);
+                        if (b1.delta == 0) ic1 = nq_lut_resolve_tie_shared(b1, lut);
+                        nq_lut_finish(b0, ic0, vv0);
+                        nq_lut_finish(b1, ic1, vv1);
                     }
-                    kid = nq_beta_id(kbetas, g);
-                    vid = nq_beta_id(vbetas, g);
-                    kn = __ldg(knorms + row);
-                    vn = __ldg(vnorms + row);
-                };
-                fetch(tsub);
-                for (int t0 = 0; t0 < tlimit; t0 += TPW) {
-                    const int t = t0 + tsub;
-                    const bool valid = t < tlimit && base_token + t < limit;
-                    const uint32_t kw_now = kw, vw_now = vw;
-                    const uint2 klat_now = klat, vlat_now = vlat;
-                    const float kb = __ldg(p.key_beta_table + kid), vb = __ldg(p.value_beta_table + vid);
-                    const float kds = nq_div_by(kn, p.sqrt_dim, p.inv_sqrt_dim);
-                    const float vds = nq_div_by(vn, p.sqrt_dim, p.inv_sqrt_dim);
-                    if (t0 + TPW < tlimit) fetch(t + TPW);
-                    float kvec[8], vvec[8];
-                    if (LAT) {
-                        // the pages' decoded shadow: same coordinates, read instead of searched
-                        nq_lattice_block(klat_now, kvec);
-                        nq_lattice_block(vlat_now, vvec);
-                    } else {
-                        nq_decode_codeword_undithered(kw_now, kvec);
-                        nq_decode_codeword_undithered(vw_now, vvec);
+                    if (cold0) vsc0 = pick_step(vbeta, (int)((pick_step(vid, c) >> (2 * b)) & 3)) * pick_step(vds, c);
+                    else if (valid0) {
+                        nq_load8<__nv_bfloat16>(reinterpret_cast<const __nv_bfloat16*>(p.hot_values) + row0 * D + b * 8, vv0);
+                        vsc0 = 1.0f;
                     }
-                    update(kvec, vvec, kb * kds, vb * vds, valid);
+                    if (cold1) vsc1 = pick_step(vbeta, (int)((pick_step(vid, c + 1) >> (2 * b)) & 3)) * pick_step(vds, c + 1);
+                    else if (valid1) {
+                        nq_load8<__nv_bfloat16>(reinterpret_cast<const __nv_bfloat16*>(p.hot_values) + row1 * D + b * 8, vv1);
+                        vsc1 = 1.0f;
+                    }
+#pragma unroll
+                    for (int g = 0; g < G; ++g) {
+                        // an inactive lane has probability 0 and scale 0 against finite decoded values
+                        const float pv0 = s_prob[c][threadIdx.x][g] * vsc0, pv1 = s_prob[c + 1][threadIdx.x][g] * vsc1;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) acc[g * 8 + j] = fmaf(pv1, vv1[j], fmaf(pv0, vv0[j], acc[g * 8 + j]));
+                    }
+                }
+                reduce_scatter<NV, 16>(acc, lane);
+                // out[b] is indexed with the loop variable of a rolled loop: keep it in registers with a switch
+#pragma unroll
+                for (int bb = 0; bb < BPR; ++bb) {
+                    if (bb == b) {
+#pragma unroll
+                        for (int i = 0; i < NVL; ++i) out[bb][i] += acc[i];
+                    }
                 }
             }
         }
     }
 
-    // merge the token sub-groups of the warp (same block index, different tokens)
+    // the lanes' partial denominators
 #pragma unroll
     for (int g = 0; g < G; ++g) {
 #pragma unroll
-        for (int off = BPR; off < 32; off <<= 1) {
-            const float mo = __shfl_xor_sync(0xffffffffu, m[g], off);
-            const float lo = __shfl_xor_sync(0xffffffffu, l[g], off);
-            const float mn = fmaxf(m[g], mo);
-            const float c0 = mn == -INFINITY ? 0.0f : exp2f(m[g] - mn);
-            const float c1 = mn == -INFINITY ? 0.0f : exp2f(mo - mn);
-            l[g] = l[g] * c0 + lo * c1;
+        for (int off = 16; off >= 1; off >>= 1) l[g] += __shfl_xor_sync(0xffffffffu, l[g], off);
+    }
+    __syncthreads();  // the loop's storage becomes the merge buffer
+    if (lane == 0) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const float ao = __shfl_xor_sync(0xffffffffu, acc[g][j], off);
-                acc[g][j] = acc[g][j] * c0 + ao * c1;
-            }
-            m[g] = mn;
+        for (int g = 0; g < G; ++g) {
+            s_merge[warp][g][D] = m[g];
+            s_merge[warp][g][D + 1] = l[g];
         }
-        if (tsub == 0) {
-            if (blk == 0) {
-                s_merge[warp][g][D] = m[g];
-                s_merge[warp][g][D + 1] = l[g];
-            }
+    }
+    {
+        constexpr int kGroup = NV >= 32 ? 1 : 32 / NV;  // lanes holding the same total
+        if (lane % kGroup == 0) {
+            const int first = NV >= 32 ? lane * NVL : lane / kGroup;  // index g * 8 + j of the lane's first total
 #pragma unroll
-            for (int j = 0; j < 8; ++j) s_merge[warp][g][blk * 8 + j] = acc[g][j];
+            for (int b = 0; b < BPR; ++b)
+#pragma unroll
+                for (int i = 0; i < NVL; ++i) s_merge[warp][(first + i) >> 3][b * 8 + ((first + i) & 7)] = out[b][i];
         }
     }
     __syncthreads();
@@ -425,31 +566,41 @@ int launch_attn(const AttnParams& p, dim3 grid, cudaStream_t s) {
     return p.key_lattice ? launch_attn_dim<G, true>(p, grid, s) : launch_attn_dim<G, false>(p, grid, s);
 }
 
-// Page-range splits per (query token, KV head).  The grid should fill whole waves of the CTAs that are
-// resident at once (148 SMs x 4, or x 3 for the widest GQA group): 256 CTAs x 3 splits used to run as 1.3
-// waves, i.e. the time of 2.  Among the split counts that leave every split >= 4 page slots and the grid
-// within 8 waves, take the smallest whose last wave is (nearly) full.
-int choose_splits(int queries, int kv_heads, int max_pages, int group) {
-    const long ctas = (long)queries * kv_heads;
+// Page-range splits per (query token, KV head).  Every CTA of a launch owns the SAME number of page slots
+// (`per_slots`, from the cache's maximum length), so a short sequence occupies few CTAs instead of being cut
+// into slivers, and the CTAs past a sequence's end return at once.  A warp works best on chunks of
+// CH x 32 tokens, a CTA therefore on kAttnWarps x CH x 32: that is the range, as long as it still yields
+// about two resident sets of CTAs; small batches take shorter ranges (down to one step per warp) to fill the
+// machine, very large grids longer ones (at most ~8 resident sets).  The plan only depends on what
+// nq_kv_attention_workspace_bytes is told; pages count as 16 tokens in it (any page size is correct).
+struct SplitPlan {
+    int splits, per_slots;
+};
+SplitPlan plan_splits(int queries, int kv_heads, int max_pages, int group) {
+    const long base = (long)queries * kv_heads;
     const long resident = 148L * (group <= 4 ? 4 : 3);
-    int cap = (max_pages + 1 + 3) / 4;
-    if (cap > 64) cap = 64;
-    if (cap < 1) cap = 1;
-    double best = 0.0;
-    double score[65];
-    for (int s = 1; s <= cap; ++s) {
-        const long total = ctas * s;
-        if (s > 1 && total > 8 * resident) {
-            cap = s - 1;
-            break;
+    const int max_slots = max_pages + 1;  // cold pages + the hot tail
+    const int steps_per_chunk = group <= 4 ? 4 : 2;
+    const int slots_full = kAttnWarps * steps_per_chunk * 32 / 16;
+    const int slots_min = kAttnWarps * 32 / 16;
+    const int splits_fill = (int)((2 * resident + base - 1) / base);
+    int per = slots_full;
+    int splits = (max_slots + per - 1) / per;
+    if (splits >= splits_fill) {
+        while (splits > 1 && base * splits > 8 * resident) {
+            per += slots_full;
+            splits = (max_slots + per - 1) / per;
         }
-        const long waves = (total + resident - 1) / resident;
-        score[s] = (double)total / (double)(waves * resident);
-        if (score[s] > best) best = score[s];
+    } else {
+        const int finest = (max_slots + slots_min - 1) / slots_min;
+        splits = splits_fill < finest ? splits_fill : finest;
     }
-    for (int s = 1; s <= cap; ++s)
-        if (score[s] >= best - 0.02) return s;
-    return 1;
+    if (splits > 64) splits = 64;
+    if (splits < 1) splits = 1;
+    SplitPlan plan;
+    plan.per_slots = (max_slots + splits - 1) / splits;
+    plan.splits = (max_slots + plan.per_slots - 1) / plan.per_slots;
+    return plan;
 }
 
 }  // namespace
@@ -457,7 +608,7 @@ int choose_splits(int queries, int kv_heads, int max_pages, int group) {
 extern "C" size_t nq_kv_attention_workspace_bytes(int batch, int q_tokens, int q_heads, int kv_heads, int dim,
                                                   int max_pages) {
     if (batch < 1 || q_tokens < 1 || q_heads < 1 || kv_heads < 1) return 0;
-    const int splits = choose_splits(batch * q_tokens, kv_heads, max_pages, q_heads / kv_heads);
+    const int splits = plan_splits(batch * q_tokens, kv_heads, max_pages, q_heads / kv_heads).splits;
     return (size_t)batch * q_tokens * q_heads * splits * (dim + 2) * sizeof(float) + 256;
 }
 
@@ -503,7 +654,9 @@ static int kv_attention_impl(const void* query, int q_dtype, int batch, int q_to
     p.scale_log2e = scale * 1.4426950408889634f;
     p.sqrt_dim = (float)sqrt((double)dim);
     p.inv_sqrt_dim = 1.0f / p.sqrt_dim;
-    p.splits = choose_splits(batch * q_tokens, kv_heads, max_pages, group);  // same split with or without the shadow: same sums
+    const SplitPlan plan = plan_splits(batch * q_tokens, kv_heads, max_pages, group);  // same with or without the shadow: same sums
+    p.splits = plan.splits;
+    p.per_slots = plan.per_slots;
     p.out = out; p.out_dtype = out_dtype;
     p.partial = reinterpret_cast<float*>(workspace);
     if (p.splits > 1) {
@@ -512,6 +665,10 @@ static int kv_attention_impl(const void* query, int q_dtype, int batch, int q_to
                    "nq_kv_attention: workspace of %zu bytes needed, %zu given", need, workspace_bytes);
     }
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    if (!key_lattice) {
+        const cudaError_t err = nq_lut_ensure(s);
+        NQ_REQUIRE(err == cudaSuccess, (int)err, "nq_kv_attention: decode table: %s", cudaGetErrorString(err));
+    }
     dim3 grid((unsigned)(batch * q_tokens * kv_heads), (unsigned)p.splits);
     int rc;
     switch (group) {

@@ -361,6 +361,202 @@ NQ_HD void nq_decode_codeword_undithered(uint32_t word, float r[8]) {
     for (int j = 0; j < 8; ++j) r[j] = nq_fma(-14.0f, n[j], t[j]);
 }
 
+// ------------------------------------------------- table-driven decode ------
+//
+// The decode of an UNDITHERED codeword only ever sees 92 different coordinate values: the
+// doubled coset coordinates T = 2t are integers in [-26, 65].  Everything the search derives
+// from one coordinate -- the two roundings, their residuals, the rounding parities -- is a
+// function of T alone, so it is tabulated once and a block becomes eight table reads plus a
+// few integer operations on packed fields:
+//
+//   R0 = T - 28*round(t/14), R1 = T - 14 - 28*round(t/14 - 1/2)   residuals in units of 1/28
+//                                                                  (|R1| = 14 - |R0| always)
+//   integer-coset distance minus half-coset distance, in units of 28/784:
+//       delta = sum|R0| - 56 + odd0*(28 - 2*max|R0|) - odd1*(28 - 2*max|R1|)
+//   delta != 0 decides the coset (the float32 sums of the reference differ by >= 0.0357 then);
+//   delta == 0 is a true tie of the two cosets, which the reference resolves through the
+//   rounding of its sequential float32 sums: those sums are reproduced from tabulated squares.
+//
+// The parity repair moves the FIRST coordinate with the largest |residual| in float32.  For
+// different |R| that order is the order of |R|; coordinates with equal |R| but different T
+// differ by rounding noise, so the table carries the rank of the float32 value among the
+// entries of equal |R| ("sub").  Ordering key of coordinate j: |R| : sub : (7 - j).
+//
+// Entry (two 32-bit words):
+//   k: [31:28] |R0|  [27:25] sub0  [24:22] 0 (7-j goes here)  [18] parity1  [17] parity0  [16] e0<0
+//      [15:12] |R1|  [11: 9] sub1  [ 8: 6] 0 (7-j)            [0] e1<0
+//   o: bf16(R0/2) << 16 | bf16(R1/2)        the decoded coordinate for either coset (exact)
+// Tie entry: squares of (s - p) for {integer, integer repaired, half, half repaired}.
+// The table spans T in [-30, 75], the range of ANY 32-bit word (nibbles up to 15), so that a
+// stray word can never index outside it; codewords proper only reach [-26, 65].
+#define NQ_LUT_ENTRIES 106
+#define NQ_LUT_BIAS 30
+
+struct NqLutCoord {
+    float e0, e1;      // residuals of the two roundings as the reference computes them
+    int r0_twice14;    // R0, R1
+    int r1_twice14;
+    int par0, par1;    // parity of the rounded values
+    float q[4];        // squared distances: integer coset, repaired; half coset, repaired
+};
+
+NQ_HD void nq_lut_coordinate(int twice_t, NqLutCoord& c) {
+    const float t = 0.5f * nq_small_int_to_float(twice_t);
+    const float s = nq_div14_coset(t);
+    const float t0 = nq_add(s, NQ_MAGIC);
+    const float r0 = nq_sub(t0, NQ_MAGIC);
+    c.par0 = nq_float_bits(t0) & 1;
+    c.e0 = nq_sub(s, r0);
+    const float y = nq_sub(s, 0.5f);
+    const float t1 = nq_add(y, NQ_MAGIC);
+    const float r1 = nq_sub(t1, NQ_MAGIC);
+    c.par1 = nq_float_bits(t1) & 1;
+    c.e1 = nq_sub(y, r1);
+    const int ir0 = (nq_float_bits(t0) & 0x7fffff) - 0x400000, ir1 = (nq_float_bits(t1) & 0x7fffff) - 0x400000;
+    c.r0_twice14 = twice_t - 28 * ir0;
+    c.r1_twice14 = twice_t - 14 - 28 * ir1;
+    const float d0 = nq_sub(s, r0);
+    const float d0f = nq_sub(s, nq_add(r0, c.e0 >= 0.0f ? 1.0f : -1.0f));
+    const float d1 = nq_sub(s, nq_add(r1, 0.5f));
+    const float d1f = nq_sub(s, nq_add(nq_add(r1, c.e1 >= 0.0f ? 1.0f : -1.0f), 0.5f));
+    c.q[0] = nq_mul(d0, d0);
+    c.q[1] = nq_mul(d0f, d0f);
+    c.q[2] = nq_mul(d1, d1);
+    c.q[3] = nq_mul(d1f, d1f);
+}
+
+// Packs entry `index` from the coordinates of all entries (`all`, NQ_LUT_ENTRIES of them).
+NQ_HD void nq_lut_pack(const NqLutCoord* all, int index, uint32_t& k, uint32_t& o) {
+    const NqLutCoord& c = all[index];
+    const int a0 = c.r0_twice14 < 0 ? -c.r0_twice14 : c.r0_twice14;
+    const int a1 = c.r1_twice14 < 0 ? -c.r1_twice14 : c.r1_twice14;
+    int sub0 = 0, sub1 = 0;
+    for (int i = 0; i < NQ_LUT_ENTRIES; ++i) {
+        const int b0 = all[i].r0_twice14 < 0 ? -all[i].r0_twice14 : all[i].r0_twice14;
+        const int b1 = all[i].r1_twice14 < 0 ? -all[i].r1_twice14 : all[i].r1_twice14;
+        sub0 += (b0 == a0 && fabsf(all[i].e0) < fabsf(c.e0)) ? 1 : 0;
+        sub1 += (b1 == a1 && fabsf(all[i].e1) < fabsf(c.e1)) ? 1 : 0;
+    }
+    k = ((uint32_t)a0 << 28) | ((uint32_t)(sub0 & 7) << 25) | ((uint32_t)c.par1 << 18) | ((uint32_t)c.par0 << 17) |
+        ((c.e0 < 0.0f ? 1u : 0u) << 16) | ((uint32_t)a1 << 12) | ((uint32_t)(sub1 & 7) << 9) | (c.e1 < 0.0f ? 1u : 0u);
+    o = (nq_bf16_bits(0.5f * nq_small_int_to_float(c.r0_twice14)) << 16) |
+        nq_bf16_bits(0.5f * nq_small_int_to_float(c.r1_twice14));
+}
+
+// Table indices (T + NQ_LUT_BIAS) of the eight coordinates of a codeword, four per word: `ia` holds
+// coordinates 0, 2, 4, 6 and `ib` coordinates 1, 3, 5, 7 (byte i = coordinate 2i / 2i + 1).
+NQ_HD void nq_lut_indices(uint32_t word, uint32_t& ia, uint32_t& ib) {
+    const uint32_t even = word & 0x0F0F0F0Fu;              // c0 c2 c4 c6
+    const uint32_t odd3 = (word >> 4) & 0x000F0F0Fu;       // c1 c3 c5 0
+    const uint32_t a = even + 0x10101010u - odd3;          // c0-c1, c2-c3, c4-c5, c6     (+16 each)
+    const uint32_t b = odd3 + 0x10101010u - (even >> 8);   // c1-c2, c3-c4, c5-c6, 0      (+16 each)
+    const uint32_t x = (word >> 28) * 0x01010101u - 0x02020202u;  // c7 - 32 + 30 in every byte (no byte of a sum underflows)
+    ia = 2u * a + x + 2u * (word & 0xFu);
+    ib = 2u * b + x;
+}
+
+NQ_HD uint32_t nq_max_u16x2(uint32_t a, uint32_t b) {
+#if defined(__CUDA_ARCH__)
+    return __vmaxu2(a, b);
+#else
+    const uint32_t lo = (a & 0xffffu) > (b & 0xffffu) ? (a & 0xffffu) : (b & 0xffffu);
+    const uint32_t hi = (a >> 16) > (b >> 16) ? (a >> 16) : (b >> 16);
+    return (hi << 16) | lo;
+#endif
+}
+NQ_HD uint32_t nq_max3_u16x2(uint32_t a, uint32_t b, uint32_t c) {
+#if defined(__CUDA_ARCH__) && __CUDA_ARCH__ >= 900
+    return __vimax3_u16x2(a, b, c);
+#else
+    return nq_max_u16x2(nq_max_u16x2(a, b), c);
+#endif
+}
+
+// Decode of an undithered codeword from the table, in three phases so that a caller can interleave
+// the straight-line parts of several blocks around the (rare, divergent) tie resolution:
+//   nq_lut_begin        eight table reads, the integer decision;  blk.delta < 0: integer coset,
+//                       > 0: half coset, == 0: the two cosets are equally far
+//   nq_lut_resolve_tie  only for delta == 0: the reference's sequential float32 sums decide
+//   nq_lut_finish       the eight decoded coordinates of the chosen coset, parity repair applied
+// fetch(packed, i, k, o) reads the entry whose index is byte i of `packed`; tie(packed, i, q) reads
+// the four squares of that entry.
+struct NqLutBlock {
+    uint32_t o[8];       // bf16 pair (integer coset, half coset) of every coordinate
+    uint32_t m;          // largest ordering key of the integer coset (upper half) and of the half coset (lower half)
+    uint32_t ia, ib;     // table indices, kept for the tie path
+    int delta;
+    uint32_t odd;        // bit 0: the integer coset needs the parity repair, bit 1: the half coset does
+};
+
+template <class Fetch>
+NQ_HD void nq_lut_begin(uint32_t word, Fetch&& fetch, NqLutBlock& blk) {
+    uint32_t k[8];
+    nq_lut_indices(word, blk.ia, blk.ib);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) fetch((j & 1) ? blk.ib : blk.ia, j >> 1, k[j], blk.o[j]);
+    uint32_t asum = 0, x = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+#if defined(__CUDA_ARCH__)
+        asum = __umulhi(k[j], 16u) + asum;
+#else
+        asum += k[j] >> 28;
+#endif
+        x ^= k[j];
+    }
+    blk.odd = (x >> 17) & 3u;
+    blk.m = nq_max3_u16x2(
+        nq_max3_u16x2(k[0] | 0x01C001C0u, k[1] | 0x01800180u, k[2] | 0x01400140u),
+        nq_max3_u16x2(k[3] | 0x01000100u, k[4] | 0x00C000C0u, k[5] | 0x00800080u),
+        nq_max_u16x2(k[6] | 0x00400040u, k[7]));
+    const int rmax0 = (int)(blk.m >> 28), rmax1 = (int)((blk.m >> 12) & 15u);
+    blk.delta = (int)asum - 56 + ((blk.odd & 1u) ? 28 - 2 * rmax0 : 0) - ((blk.odd & 2u) ? 28 - 2 * rmax1 : 0);
+}
+
+template <class Tie>
+NQ_HD bool nq_lut_resolve_tie(const NqLutBlock& blk, Tie&& tie) {
+    const int fix0 = (blk.odd & 1u) ? 7 - (int)((blk.m >> 22) & 7u) : -1;
+    const int fix1 = (blk.odd & 2u) ? 7 - (int)((blk.m >> 6) & 7u) : -1;
+    float s0 = 0.0f, s1 = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        float q[4];
+        tie((j & 1) ? blk.ib : blk.ia, j >> 1, q);
+        s0 = nq_add(s0, j == fix0 ? q[1] : q[0]);
+        s1 = nq_add(s1, j == fix1 ? q[3] : q[2]);
+    }
+    return s0 < s1;
+}
+
+NQ_HD void nq_lut_finish(const NqLutBlock& blk, bool integer_coset, float r[8]) {
+    const uint32_t key = integer_coset ? (blk.m >> 16) : (blk.m & 0xffffu);
+    const bool odd = ((integer_coset ? blk.odd : (blk.odd >> 1)) & 1u) != 0;
+#if defined(__CUDA_ARCH__)
+    const uint32_t pick = integer_coset ? 0x3244u : 0x1044u;  // byte selector: the chosen bf16 into the upper half
+#pragma unroll
+    for (int j = 0; j < 8; ++j) r[j] = __uint_as_float(__byte_perm(blk.o[j], 0u, pick));
+#else
+#pragma unroll
+    for (int j = 0; j < 8; ++j) r[j] = nq_bits_float(integer_coset ? (blk.o[j] & 0xffff0000u) : (blk.o[j] << 16));
+#endif
+    // parity repair; residual e < 0: the rounded value moves down by one, the decoded coordinate up by 14
+    const int fix = odd ? 7 - (int)((key >> 6) & 7u) : -1;
+    const float by = (key & 1u) ? 14.0f : -14.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) r[j] = (j == fix) ? nq_add(r[j], by) : r[j];
+}
+
+// The three phases in one call: the same eight values as nq_decode_codeword_exact(word, nullptr, r)
+// for every one of the 14^8 codewords (checked on the host).
+template <class Fetch, class Tie>
+NQ_HD void nq_decode_codeword_lut(uint32_t word, Fetch&& fetch, Tie&& tie, float r[8]) {
+    NqLutBlock blk;
+    nq_lut_begin(word, fetch, blk);
+    bool integer_coset = blk.delta < 0;
+    if (blk.delta == 0) integer_coset = nq_lut_resolve_tie(blk, tie);
+    nq_lut_finish(blk, integer_coset, r);
+}
+
 // ------------------------------------------------------------ dither ------
 
 // "lcg31_mix_v1" (codec.py:204-221): every stage reduced modulo 2^31.

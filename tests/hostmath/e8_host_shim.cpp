@@ -144,3 +144,81 @@ int shim_div14_exact(void) {
     return 1;
 }
 }
+
+// Table-driven undithered decode (nq_decode_codeword_lut) against the exact decode.
+namespace {
+struct HostLut {
+    uint32_t k[NQ_LUT_ENTRIES], o[NQ_LUT_ENTRIES];
+    float q[NQ_LUT_ENTRIES][4];
+    int bad_sub;
+    HostLut() : bad_sub(0) {
+        NqLutCoord all[NQ_LUT_ENTRIES];
+        for (int i = 0; i < NQ_LUT_ENTRIES; ++i) nq_lut_coordinate(i - NQ_LUT_BIAS, all[i]);
+        for (int i = 0; i < NQ_LUT_ENTRIES; ++i) {
+            nq_lut_pack(all, i, k[i], o[i]);
+            for (int c = 0; c < 4; ++c) q[i][c] = all[i].q[c];
+            // the rank among entries of equal |R| must fit its three bits
+            int sub0 = 0, sub1 = 0;
+            for (int j = 0; j < NQ_LUT_ENTRIES; ++j) {
+                sub0 += abs(all[j].r0_twice14) == abs(all[i].r0_twice14) && fabsf(all[j].e0) < fabsf(all[i].e0);
+                sub1 += abs(all[j].r1_twice14) == abs(all[i].r1_twice14) && fabsf(all[j].e1) < fabsf(all[i].e1);
+            }
+            if (sub0 > 7 || sub1 > 7 || abs(all[i].r0_twice14) > 14 || abs(all[i].r1_twice14) > 14 ||
+                abs(all[i].r0_twice14) + abs(all[i].r1_twice14) != 14)
+                ++bad_sub;
+        }
+    }
+};
+const HostLut& host_lut() {
+    static HostLut lut;
+    return lut;
+}
+inline void decode_lut(uint32_t w, float* r) {
+    const HostLut& lut = host_lut();
+    nq_decode_codeword_lut(
+        w,
+        [&](uint32_t packed, int i, uint32_t& k, uint32_t& o) {
+            const int idx = (packed >> (8 * i)) & 0xff;
+            k = lut.k[idx];
+            o = lut.o[idx];
+        },
+        [&](uint32_t packed, int i, float q[4]) {
+            const int idx = (packed >> (8 * i)) & 0xff;
+            for (int c = 0; c < 4; ++c) q[c] = lut.q[idx][c];
+        },
+        r);
+}
+}  // namespace
+
+extern "C" {
+// 0 when every table entry keeps its fields inside their bit widths.
+int shim_lut_field_overflows(void) { return host_lut().bad_sub; }
+
+// Codewords (every `stride`-th of the 14^8, upper half of the digits in [hi_begin, hi_end)) whose
+// table-driven decode differs in any bit from the exact decode.
+long shim_lut_mismatches(long stride, long hi_begin, long hi_end) {
+    long bad = 0;
+    const long half = 14L * 14 * 14 * 14;
+    if (hi_end > half) hi_end = half;
+    for (long hi = hi_begin; hi < hi_end; ++hi) {
+        int c[8];
+        long v = hi;
+        for (int j = 4; j < 8; ++j) { c[j] = (int)(v % 14); v /= 14; }
+        for (long lo = hi % stride; lo < half; lo += stride) {
+            long u = lo;
+            for (int j = 0; j < 4; ++j) { c[j] = (int)(u % 14); u /= 14; }
+            uint32_t w = 0;
+            for (int j = 0; j < 8; ++j) w |= (uint32_t)c[j] << (4 * j);
+            float a[8], b[8];
+            nq_decode_codeword_exact(w, nullptr, a);
+            decode_lut(w, b);
+            if (memcmp(a, b, sizeof a)) ++bad;
+        }
+    }
+    return bad;
+}
+
+void shim_decode_lut(const uint32_t* words, long n, float* out) {
+    for (long i = 0; i < n; ++i) decode_lut(words[i], out + 8 * i);
+}
+}
