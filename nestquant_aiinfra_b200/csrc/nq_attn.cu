@@ -592,8 +592,11 @@ SplitPlan plan_splits(int queries, int kv_heads, int max_pages, int group) {
             splits = (max_slots + per - 1) / per;
         }
     } else {
+        // not enough sequences to fill the machine with full ranges: one resident set of shorter ones
+        const int one_set = (int)((resident + base - 1) / base);
         const int finest = (max_slots + slots_min - 1) / slots_min;
-        splits = splits_fill < finest ? splits_fill : finest;
+        splits = one_set < finest ? one_set : finest;
+        if (splits < (max_slots + slots_full - 1) / slots_full) splits = (max_slots + slots_full - 1) / slots_full;
     }
     if (splits > 64) splits = 64;
     if (splits < 1) splits = 1;

@@ -559,15 +559,18 @@ NQ_HD void nq_decode_codeword_lut(uint32_t word, Fetch&& fetch, Tie&& tie, float
 
 // ------------------------------------------------------------ dither ------
 
-// "lcg31_mix_v1" (codec.py:204-221): every stage reduced modulo 2^31.
+// "lcg31_mix_v1" (codec.py:204-221): every stage reduced modulo 2^31.  Bit 31 of the intermediate
+// values is left as garbage instead of being masked after every stage: a product's low 31 bits only
+// depend on the low 31 bits of its factor, and the shifted copies are masked where they are folded
+// in (one three-input logic operation), so bits 0..30 are those of the reference at every stage.
 NQ_HD uint32_t nq_lcg31_mix(uint32_t counter_plus_seed) {
-    uint32_t v = counter_plus_seed & 0x7fffffffu;
-    v ^= v >> 16;
-    v = (v * 1103515245u + 12345u) & 0x7fffffffu;
-    v ^= v >> 13;
-    v = (v * 134775813u + 1u) & 0x7fffffffu;
-    v ^= v >> 16;
-    return v;
+    uint32_t v = counter_plus_seed;
+    v ^= (v >> 16) & 0x7fffu;
+    v = v * 1103515245u + 12345u;
+    v ^= (v >> 13) & 0x3ffffu;
+    v = v * 134775813u + 1u;
+    v ^= (v >> 16) & 0x7fffu;
+    return v & 0x7fffffffu;
 }
 
 // Subtractive dither of one global block: u - Q(u), u uniform in [0,2)^8.
