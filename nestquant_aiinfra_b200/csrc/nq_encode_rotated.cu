@@ -110,7 +110,25 @@ template <typename T, int MODE = kPlain>
 int launch_encode_rotated(const void* x, int64_t rows, int64_t k, int64_t hadamard_block, const float* beta_table,
                           uint8_t* out_codes, uint8_t* out_beta_ids, float* out_norms, void* out_decoded,
                           cudaStream_t stream, const void* x2 = nullptr, int64_t stride = 0, float eps = 0.0f) {
-    const NqEncodePlan plan = nq_encode_plan(rows, (int)k, false);
+    NqEncodePlan plan = nq_encode_plan(rows, (int)k, false);
+    {
+        // Every CTA a row is split over repeats the load, the producer and the transform of the whole row, so
+        // (unlike the plain encoder) more CTAs than SMs only add work: long rows are split just far enough to
+        // give every SM one CTA, and the four-lanes-per-block latency mode is kept for CTAs with at most 64 blocks
+        // (measured on 8 / 64 / 256 rows of 2048 and 8192 features).
+        const int bpr = (int)k / 8;
+        if (nq_encode_rows_per_cta((int)k) == 1) {
+            const int sms = nq_sm_count();
+            int splits = rows < sms ? (int)(sms / rows) : 1;
+            if (splits > bpr / 32) splits = bpr / 32;
+            if (splits < 1) splits = 1;
+            plan.rpc = 1;
+            plan.blocks_per_split = ((bpr + splits - 1) / splits + 31) / 32 * 32;
+            plan.splits = (bpr + plan.blocks_per_split - 1) / plan.blocks_per_split;
+            plan.four_lanes = plan.blocks_per_split <= 64;
+            if (plan.splits == 1) plan.blocks_per_split = 0x40000000;
+        }
+    }
     const int rpc = plan.rpc, splits = plan.splits, blocks_per_split = plan.blocks_per_split;
     const size_t smem = ((size_t)rpc * k + nq_encode_smem_floats((int)k, rpc)) * sizeof(float);
     auto kernel = nq_encode_rotated_kernel<T, MODE>;
