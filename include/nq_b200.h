@@ -6,9 +6,11 @@
  *     pointer unless its name ends in _host;
  *   - the caller owns every buffer, passes the CUDA stream explicitly and
  *     supplies workspaces; nothing here allocates device memory or synchronises
- *     the host (nq_w4a4_status excepted).  Host-side state is limited to
+ *     the host (nq_w4a4_status and the first nq_kv_attention call per device
+ *     excepted).  Host-side state is limited to
  *     per-device look-ups made on first use (SM count, the opt-in of a kernel
- *     to large shared memory, the driver entry point that builds tensor maps)
+ *     to large shared memory, the driver entry point that builds tensor maps,
+ *     whether the page-decode table of nq_kv_attention has been filled)
  *     and, for nq_w4a4_gemv_static only, the address of its built-in scratch;
  *     launches go to the CURRENT device, which must be the stream's device;
  *   - return value 0 = success, negative = argument error (NQ_ERR_*), positive
@@ -315,7 +317,11 @@ int nq_kv_quantize_page(const void* key, const void* value, int kv_dtype, int va
  *          (semantic of NQKVLlamaCache.prefill, runtime/nqkv_hf_backend.py:127-150).
  * K/V of cold pages are the float32 reconstruction; softmax and accumulation in float32.
  * The hot tail (hot_keys / hot_values) is read as BF16 whatever dtype the pages were packed from.
- * workspace: nq_kv_attention_workspace_bytes(...) bytes (split partials). */
+ * workspace: nq_kv_attention_workspace_bytes(...) bytes (split partials).
+ * The pages are decoded through a 106-entry table that the library keeps in a fixed array of
+ * its own image (no allocation): the FIRST call on a device fills it with a one-CTA kernel on
+ * `stream` and waits for that kernel once; while `stream` is being captured the fill is
+ * recorded into the graph instead. */
 size_t nq_kv_attention_workspace_bytes(int batch, int q_tokens, int q_heads, int kv_heads, int dim, int max_pages);
 int nq_kv_attention(const void* query, int q_dtype, int batch, int q_tokens, int q_heads,
                     const int32_t* slot_ids, const uint8_t* active_mask, const int32_t* q_lens,

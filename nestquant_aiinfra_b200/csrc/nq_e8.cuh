@@ -188,25 +188,28 @@ NQ_HD void nq_e8_nearest_exact(const float x[8], float out[8]) {
 // nq_e8_nearest_exact.
 NQ_HD void nq_e8_nearest_guarded(const float x[8], float out[8]) {
     float r0[8], e0[8], r1[8], e1[8];
-    int par0 = 0, par1 = 0;
+    // The parities of the two roundings come from the (exact) float sums of the rounded values rather than
+    // from eight XORs of their bit patterns: adds go to the FMA pipe, the logic pipe is the busy one.
+    float sum0 = 0.0f, sum1 = 0.0f;
     float s0 = 0.0f, s1 = 0.0f, m0 = 0.0f, m1 = 0.0f;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
         const float t0 = nq_add(x[j], NQ_MAGIC);
         r0[j] = nq_sub(t0, NQ_MAGIC);
-        par0 ^= nq_float_bits(t0);
+        sum0 = nq_add(sum0, r0[j]);
         e0[j] = nq_sub(x[j], r0[j]);
         s0 = nq_fma(e0[j], e0[j], s0);
         m0 = fmaxf(m0, fabsf(e0[j]));
         const float y = nq_sub(x[j], 0.5f);
         const float t1 = nq_add(y, NQ_MAGIC);
         r1[j] = nq_sub(t1, NQ_MAGIC);
-        par1 ^= nq_float_bits(t1);
+        sum1 = nq_add(sum1, r1[j]);
         e1[j] = nq_sub(y, r1[j]);
         s1 = nq_fma(e1[j], e1[j], s1);
         m1 = fmaxf(m1, fabsf(e1[j]));
     }
-    const bool odd0 = (par0 & 1) != 0, odd1 = (par1 & 1) != 0;
+    const bool odd0 = (nq_float_bits(nq_add(sum0, NQ_MAGIC)) & 1) != 0;
+    const bool odd1 = (nq_float_bits(nq_add(sum1, NQ_MAGIC)) & 1) != 0;
     if (odd0) s0 += 1.0f - 2.0f * m0;
     if (odd1) s1 += 1.0f - 2.0f * m1;
     const float diff = s0 - s1;
@@ -233,16 +236,17 @@ NQ_HD void nq_e8_nearest_guarded(const float x[8], float out[8]) {
     }
     const bool odd = integer_coset ? odd0 : odd1;
     const float m = integer_coset ? m0 : m1;
-    const float half = integer_coset ? 0.0f : 0.5f;
+    const float half_coset = integer_coset ? 0.0f : 1.0f;
     bool pending = odd;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
         const float e = integer_coset ? e0[j] : e1[j];
-        float r = integer_coset ? r0[j] : r1[j];
+        // r0 or r1 + 1/2 without a select: (r1 + 1/2) - r0 is +-1/2 exactly, so the FMA is exact
+        float r = nq_fma(half_coset, nq_sub(nq_add(r1[j], 0.5f), r0[j]), r0[j]);
         const bool hit = pending && fabsf(e) == m;  // first coordinate reaching the maximum
         r += hit ? (e >= 0.0f ? 1.0f : -1.0f) : 0.0f;
         pending = pending && !hit;
-        out[j] = r + half;
+        out[j] = r;
     }
 }
 

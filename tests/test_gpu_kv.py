@@ -177,7 +177,7 @@ def _check_attention(actual, expected):
     assert rel_fro(actual, expected) <= REL_FRO_TOL, rel_fro(actual, expected)
 
 
-@pytest.mark.parametrize("heads,dim,q_heads", [(8, 64, 32), (2, 128, 16), (2, 64, 2)])
+@pytest.mark.parametrize("heads,dim,q_heads", [(8, 64, 32), (2, 128, 16), (2, 64, 2), (4, 32, 8), (1, 256, 2)])
 def test_decode_attention_matches_checker(rt, oracle, heads, dim, q_heads):
     lengths = [1, 16, 17, 250, None, 0, 96]
     cache = make_cache(rt, slots=len(lengths), max_pages=16, heads=heads, dim=dim)
