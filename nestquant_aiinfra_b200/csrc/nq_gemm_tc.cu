@@ -48,6 +48,7 @@ constexpr int kTileK = 64;       // K elements per stage (one 128-byte swizzle r
 constexpr int kThreadsTc = 192;  // 6 warps
 constexpr int kAccCols = 256;    // TMEM columns per accumulator buffer
 constexpr int kMaxStages = 8;
+constexpr int kPairMinK = 4096;   // paired channel tiles pay once the main loop dwarfs the exposed epilogue (measured)
 constexpr int kDecodeWarps = 16;                              // FUSED: warps 6..21 decode the weight
 constexpr int kThreadsFused = kThreadsTc + kDecodeWarps * 32;  // 704 threads at 80 registers
 constexpr int kUnitBlocks = kTileN * (kTileK / 8);            // E8 blocks per decode unit (128 channels x 64 features)
@@ -62,6 +63,8 @@ struct TcParams {
     unsigned* status;   // 0 = ok
     int group_n;        // output tiles are visited in bands of group_n channel tiles: within a band token-tile major
                         // (group_n = n_tiles: plain token-tile-major order)
+    int pair;           // 1: a work item covers TWO adjacent channel tiles (256 channels) that share the token tile in
+                        // shared memory; both 256-column accumulators belong to the item, n_tiles counts pairs
     int splits;         // K splits per output tile (1 = none); work item = tile * splits + split
     float* partial;     // [splits, m, n] float32 partial sums when splits > 1
     unsigned* counters; // unused
@@ -91,12 +94,13 @@ struct __align__(8) TcBarriers {
 };
 
 // Channel and token offset of output tile `tile` (see TcParams::group_n).
+template <bool PAIR = false>
 __device__ __forceinline__ void tc_tile_origin(const TcParams& p, int tile, int& n0, int& t0) {
     const int per_band = p.group_n * p.t_tiles;
     const int band = tile / per_band, r = tile - band * per_band;
     const int width = min(p.group_n, p.n_tiles - band * p.group_n);
     const int t_tile = r / width;
-    n0 = (band * p.group_n + (r - t_tile * width)) * kTileN;
+    n0 = (band * p.group_n + (r - t_tile * width)) * (PAIR ? 2 * kTileN : kTileN);
     t0 = t_tile * p.tile_t;
 }
 
@@ -105,14 +109,15 @@ __device__ __forceinline__ void tc_fail(const TcParams& p, TcBarriers* bars, uns
     *reinterpret_cast<volatile int*>(&bars->abort_flag) = 1;
 }
 
-template <bool FUSED>
+template <bool FUSED, bool PAIR = false>
 __global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreadsTc, 1)
 nq_w4a4_tc_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
                        const TcParams p, const FusedParams f) {
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment required by the 128-byte swizzle
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    const uint32_t w_bytes = kTileN * kTileK * 2;
+    const uint32_t w_tile_bytes = kTileN * kTileK * 2;
+    const uint32_t w_bytes = PAIR ? 2 * w_tile_bytes : w_tile_bytes;
     const uint32_t a_bytes = (uint32_t)p.tile_t * kTileK * 2;
     const uint32_t stage_bytes = w_bytes + a_bytes;
     TcBarriers* bars = reinterpret_cast<TcBarriers*>(smem + (size_t)p.stages * stage_bytes);
@@ -153,7 +158,7 @@ nq_w4a4_tc_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
             for (int item = blockIdx.x; item < total_tiles && ok; item += gridDim.x) {
                 const int tile = item / p.splits, split = item - tile * p.splits;
                 int n0, t0;
-                tc_tile_origin(p, tile, n0, t0);
+                tc_tile_origin<PAIR>(p, tile, n0, t0);
                 const int ks0 = split * k_steps_all / p.splits, ks1 = (split + 1) * k_steps_all / p.splits;
                 if (FUSED) {
                     // every decode warp adds one arrival per unit of this channel tile
@@ -185,6 +190,7 @@ nq_w4a4_tc_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
                     uint8_t* dst = smem + (size_t)s * stage_bytes;
                     mbar_arrive_expect_tx(&bars->full[s], stage_bytes);
                     tma_load_2d(dst, &map_w, ks * kTileK, n0, &bars->full[s]);
+                    if (PAIR) tma_load_2d(dst + w_tile_bytes, &map_w, ks * kTileK, n0 + kTileN, &bars->full[s]);
                     tma_load_2d(dst + w_bytes, &map_a, ks * kTileK, t0, &bars->full[s]);
                 }
             }
@@ -203,7 +209,8 @@ nq_w4a4_tc_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
             uint32_t fill = 0, local_tile = 0;
             bool ok = true;
             for (int item = blockIdx.x; item < total_tiles && ok; item += gridDim.x, ++local_tile) {
-                const uint32_t buf = local_tile & 1, use = local_tile >> 1;
+                // paired items own both accumulator buffers: nothing to alternate, the epilogue has to drain first
+                const uint32_t buf = PAIR ? 0u : (local_tile & 1), use = PAIR ? local_tile : (local_tile >> 1);
                 if (use > 0 && !mbar_wait_bounded(&bars->acc_empty[buf], (use - 1) & 1, abort_flag)) {
                     tc_fail(p, bars, 2);
                     break;
@@ -222,12 +229,16 @@ nq_w4a4_tc_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
                     tc_fence_after();
                     const uint32_t base = smem_u32(smem + (size_t)s * stage_bytes);
                     const uint64_t desc_w = umma_desc_sw128(base);
+                    const uint64_t desc_w1 = umma_desc_sw128(base + w_tile_bytes);
                     const uint64_t desc_a = umma_desc_sw128(base + w_bytes);
 #pragma unroll
                     for (int kk = 0; kk < kTileK / 16; ++kk) {
                         // +32 bytes per K16 step inside the 128-byte swizzle row (16-byte units)
                         umma_bf16(acc, desc_w + (uint64_t)(kk * 2), desc_a + (uint64_t)(kk * 2), idesc,
                                   (ks > ks0 || kk > 0) ? 1u : 0u);
+                        if (PAIR)
+                            umma_bf16(acc + kAccCols, desc_w1 + (uint64_t)(kk * 2), desc_a + (uint64_t)(kk * 2), idesc,
+                                      (ks > ks0 || kk > 0) ? 1u : 0u);
                     }
                     umma_commit(&bars->empty[s]);
                 }
@@ -269,18 +280,19 @@ nq_w4a4_tc_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
         const int quarter = warp & 3;  // TMEM lane quarter this warp may read
         uint32_t local_tile = 0;
         for (int item = blockIdx.x; item < total_tiles; item += gridDim.x, ++local_tile) {
-            const uint32_t buf = local_tile & 1, use = local_tile >> 1;
+            const uint32_t buf = PAIR ? 0u : (local_tile & 1), use = PAIR ? local_tile : (local_tile >> 1);
             const int tile = item / p.splits, split = item - tile * p.splits;
             int n0, t0;
-            tc_tile_origin(p, tile, n0, t0);
+            tc_tile_origin<PAIR>(p, tile, n0, t0);
             const bool ready = mbar_wait_bounded(&bars->acc_full[buf], use & 1, abort_flag);
             if (!ready) {
                 if (lane == 0) tc_fail(p, bars, 4);
                 break;
             }
             tc_fence_after();
-            const int channel = n0 + quarter * 32 + lane;
-            const uint32_t taddr = tmem_base + buf * kAccCols + ((uint32_t)(quarter * 32) << 16);
+            for (int half = 0; half < (PAIR ? 2 : 1); ++half) {
+            const int channel = n0 + half * kTileN + quarter * 32 + lane;
+            const uint32_t taddr = tmem_base + (buf + half) * kAccCols + ((uint32_t)(quarter * 32) << 16);
             for (int c = 0; c < p.tile_t; c += 32) {
                 if (t0 + c >= p.m) break;  // warp-uniform
                 uint32_t r[32];
@@ -302,6 +314,7 @@ nq_w4a4_tc_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
                     for (int j = 0; j < 32; ++j)
                         if (t0 + c + j < p.m) o[(int64_t)j * p.n] = __uint_as_float(r[j]);
                 }
+            }
             }
             tc_fence_before();
             __syncwarp();
@@ -422,7 +435,7 @@ struct TcPlan {
 };
 
 int tc_plan(TcPlan& plan, const void* a_dec, const void* w_dec, int64_t m, int64_t n, int64_t k, void* out,
-            int out_dtype, void* status_word, void* partial, unsigned* counters) {
+            int out_dtype, void* status_word, void* partial, unsigned* counters, bool allow_pair = false) {
     TcParams& p = plan.p;
     p.splits = partial ? tc_splits(m, n, k) : 1;
     p.partial = reinterpret_cast<float*>(partial);
@@ -431,8 +444,16 @@ int tc_plan(TcPlan& plan, const void* a_dec, const void* w_dec, int64_t m, int64
     p.tile_t = m > 128 ? 256 : (m > 64 ? 128 : (m > 32 ? 64 : 32));
     p.n_tiles = (int)(n / kTileN);
     p.t_tiles = (int)((m + p.tile_t - 1) / p.tile_t);
+    // Two channel tiles per work item when that still gives every SM an item: the token tile is loaded once for 256
+    // channels (64 KB instead of 96 KB of shared-memory fill for the same MMAs), at the price of an epilogue that
+    // the next item's MMAs cannot overlap (both accumulator buffers belong to the item).  Measured on M = 8192:
+    // K = 8192 (down_proj) 224 -> 208 us, K = 2048 (gate/up) 4 % slower, hence the bound on k.  The pairing is a
+    // template parameter: as a run-time flag it slowed the unpaired kernel by 20 %.
+    p.pair = (allow_pair && p.tile_t == 256 && p.splits == 1 && n % (2 * kTileN) == 0 && k >= kPairMinK &&
+              (n / (2 * kTileN)) * p.t_tiles >= sm_count()) ? 1 : 0;
+    if (p.pair) p.n_tiles /= 2;
     p.group_n = p.n_tiles;
-    const size_t stage_bytes = (size_t)(kTileN + p.tile_t) * kTileK * 2;
+    const size_t stage_bytes = (size_t)(kTileN * (p.pair ? 2 : 1) + p.tile_t) * kTileK * 2;
     int stages = (int)((200 * 1024) / stage_bytes);
     if (stages > kMaxStages) stages = kMaxStages;
     p.stages = stages;
@@ -449,12 +470,12 @@ int tc_plan(TcPlan& plan, const void* a_dec, const void* w_dec, int64_t m, int64
 }
 
 // the opt-in to more than 48 KB of dynamic shared memory is a per-device attribute of each kernel
-template <bool FUSED>
+template <bool FUSED, bool PAIR = false>
 int tc_configure() {
     static bool configured[NQ_MAX_DEVICES] = {false};
     const int device = nq_current_device();
     if (device < 0 || !configured[device]) {
-        cudaError_t e = cudaFuncSetAttribute(nq_w4a4_tc_gemm_kernel<FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(nq_w4a4_tc_gemm_kernel<FUSED, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              227 * 1024);
         if (e != cudaSuccess) {
             nq_set_error("nq_w4a4_gemm: cannot reserve shared memory: %s", cudaGetErrorString(e));
@@ -480,11 +501,16 @@ int tc_reduce(const TcParams& p, int64_t m, int64_t n, void* out, cudaStream_t s
 int nq_launch_tc_gemm(const void* a_dec, const void* w_dec, int64_t m, int64_t n, int64_t k, void* out,
                       int out_dtype, void* status_word, void* partial, unsigned* counters, cudaStream_t stream) {
     TcPlan plan;
-    int rc = tc_plan(plan, a_dec, w_dec, m, n, k, out, out_dtype, status_word, partial, counters);
+    int rc = tc_plan(plan, a_dec, w_dec, m, n, k, out, out_dtype, status_word, partial, counters, true);
     if (rc) return rc;
-    if ((rc = tc_configure<false>())) return rc;
     const int grid = plan.total < sm_count() ? plan.total : sm_count();
-    nq_w4a4_tc_gemm_kernel<false><<<grid, kThreadsTc, plan.smem, stream>>>(plan.map_w, plan.map_a, plan.p, FusedParams{});
+    if (plan.p.pair) {
+        if ((rc = tc_configure<false, true>())) return rc;
+        nq_w4a4_tc_gemm_kernel<false, true><<<grid, kThreadsTc, plan.smem, stream>>>(plan.map_w, plan.map_a, plan.p, FusedParams{});
+    } else {
+        if ((rc = tc_configure<false>())) return rc;
+        nq_w4a4_tc_gemm_kernel<false><<<grid, kThreadsTc, plan.smem, stream>>>(plan.map_w, plan.map_a, plan.p, FusedParams{});
+    }
     NQ_CHECK_LAUNCH("nq_w4a4_gemm(tcgen05)");
     return tc_reduce(plan.p, m, n, out, stream);
 }

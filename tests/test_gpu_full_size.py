@@ -67,7 +67,7 @@ def test_full_size_weight_encode_is_idempotent(rt, oracle):
     assert 0.01 < rel < 0.2, rel  # 4.25-bit reconstruction error of a Gaussian matrix
 
 
-@pytest.mark.parametrize("m,n,k", [(8192, 8192, 2048), (8192, 2048, 8192), (2048, 512, 2048)])
+@pytest.mark.parametrize("m,n,k", [(8192, 8192, 2048), (8192, 2048, 8192), (5000, 2048, 4096), (2048, 512, 2048)])
 def test_full_size_tensor_core_gemm_matches_float32_product(rt, m, n, k):
     a = (torch.randn(m, k, generator=rng(m + 1)) * 0.7).bfloat16().cuda()
     w = (torch.randn(n, k, generator=rng(n + 2)) * 0.02).bfloat16().cuda()
