@@ -39,6 +39,9 @@ extern "C" {
 void shim_nearest_e8_guarded(const float* x, float* out, long n) {
     for (long i = 0; i < n; ++i) nq_e8_nearest_guarded(x + 8 * i, out + 8 * i);
 }
+void shim_nearest_e8_guarded_lean(const float* x, float* out, long n) {
+    for (long i = 0; i < n; ++i) nq_e8_nearest_guarded<true>(x + 8 * i, out + 8 * i);
+}
 
 // Weight-path decode of packed codewords: r = t - d - 14 Q((t - d)/14).
 void shim_decode_weight(const uint32_t* words, long n, long first_block, long seed, float* out) {

@@ -67,14 +67,16 @@ def test_bf16_rounding(shim, oracle):
     assert np.array_equal(got, oracle.round_bf16(values))
 
 
-def test_guarded_nearest_equals_exact(shim, oracle, golden):
+@pytest.mark.parametrize("entry", ["shim_nearest_e8_guarded", "shim_nearest_e8_guarded_lean"])
+def test_guarded_nearest_equals_exact(shim, oracle, golden, entry):
+    search = getattr(shim, entry)  # the lean form is the one the encoder's searches use
     x = golden["e8_in"]
     out = np.empty_like(x)
-    shim.shim_nearest_e8_guarded(_p(x), _p(out), ctypes.c_long(len(x)))
+    search(_p(x), _p(out), ctypes.c_long(len(x)))
     assert np.array_equal(out, golden["e8_out"])
     x = (np.random.default_rng(1).standard_normal((500000, 8)) * 2).astype(np.float32)
     out = np.empty_like(x)
-    shim.shim_nearest_e8_guarded(_p(x), _p(out), ctypes.c_long(len(x)))
+    search(_p(x), _p(out), ctypes.c_long(len(x)))
     assert np.array_equal(out, oracle.nearest_e8(x))
 
 
