@@ -503,7 +503,7 @@ def run_gpu(args) -> None:
             # config 4: the tensor-parallel decode step over these ranks (the only workload here with a collective)
             try:
                 extras["tp"] = tp_decode(torch, dist, device, rank, world, layers=args.tp_layers, batch=args.tp_batch,
-                                         context=args.tp_context, steps=3, warmup=3)
+                                         context=args.tp_context, steps=3, warmup=3, collective=args.tp_collective)
             except Exception as error:
                 extras["tp"] = {"error": f"{type(error).__name__}: {error}"[:300]}
             torch.cuda.empty_cache()
@@ -1051,7 +1051,7 @@ def decode_workload(torch, device, *, requests: int = 64, new_tokens: int = 256,
 
 
 def tp_decode(torch, dist, device, rank: int, world: int, *, layers: int, batch: int, context: int, steps: int,
-              warmup: int, resident: bool = False) -> dict:
+              warmup: int, resident: bool = False, collective: str = "nccl") -> dict:
     """Config 4: Llama-3-70B architecture (one seeded model sharded over the ranks), W4A4KV4, graph decode.
 
     Returns the measurements (identical on every rank; the times are the maximum over the ranks).  The
@@ -1087,13 +1087,38 @@ def tp_decode(torch, dist, device, rank: int, world: int, *, layers: int, batch:
     runner.start_decode(context)
     torch.cuda.synchronize(device)
     build_s = time.perf_counter() - t0
-    graph = True
-    try:
-        runner.capture_decode_graph()
-    except Exception as error:  # collectives inside a capture are not available everywhere
-        graph = f"eager ({type(error).__name__})"
+    row_modules = [m for m in model.modules() if isinstance(m, RowParallelNQRTLinear)]
+
+    def capture() -> object:
+        if isinstance(runner.graph, torch.cuda.CUDAGraph):
+            runner.graph.reset()
         runner.graph = None
-        runner.cache.set_decode_state()
+        try:
+            runner.capture_decode_graph()
+            return True
+        except Exception as error:  # collectives inside a capture are not available everywhere
+            runner.graph = None
+            runner.cache.set_decode_state()
+            return f"eager ({type(error).__name__})"
+
+    # The partial sums after o_proj / down_proj: NCCL, or this repository's own kernel over peer memory (one node).
+    collective_note = "NCCL all_reduce(sum) of [batch, 8192] BF16 after o_proj and down_proj"
+    reducer = None
+    if world > 1 and collective == "peer":
+        try:
+            from nestquant_aiinfra_b200.tensor_parallel import PeerAllReduce
+
+            reducer = PeerAllReduce(batch * 8192, device)
+            for module in row_modules:
+                module.peer_all_reduce = reducer
+            collective_note = ("nq_tp_allreduce_bf16 (peer-memory loads over NVLink, float32 sum in rank order) of "
+                               "[batch, 8192] BF16 after o_proj and down_proj")
+        except Exception as error:
+            reducer = None
+            for module in row_modules:
+                module.peer_all_reduce = None
+            collective_note += f"; peer-memory collective unavailable ({type(error).__name__}: {error})"[:200]
+    graph = capture()
     ms_step = timed(runner)
     tokens = runner.next_tokens.clone()
     same = torch.tensor([1], device=device)
@@ -1105,26 +1130,52 @@ def tp_decode(torch, dist, device, rank: int, world: int, *, layers: int, batch:
     # all-reduce share: one eager step with events around every collective (2 per layer)
     collective_ms, collectives = 0.0, 0
     if world > 1:
-        rows = [m for m in model.modules() if isinstance(m, RowParallelNQRTLinear)]
         events: list = []
-        for module in rows:
+        for module in row_modules:
             module.collective_events = events
         runner.decode_eager()
         torch.cuda.synchronize(device)
-        for module in rows:
+        for module in row_modules:
             module.collective_events = None
         t = torch.tensor([sum(a.elapsed_time(b) for a, b in events)], device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         collective_ms, collectives = float(t.item()), len(events)
+    # the same step with the OTHER collective, for comparison (never the headline; any failure only drops the key)
+    other = None
+    if world > 1:
+        try:
+            if reducer is None:
+                from nestquant_aiinfra_b200.tensor_parallel import PeerAllReduce
+
+                trial = PeerAllReduce(batch * 8192, device)
+                for module in row_modules:
+                    module.peer_all_reduce = trial
+                graph_other = capture()
+                other_ms = timed(runner)
+                broken = torch.tensor([trial.status()], device=device)
+                dist.all_reduce(broken, op=dist.ReduceOp.MAX)
+                other = {"collective": "nq_tp_allreduce_bf16 (this repository's kernel: peer-memory loads over NVLink)",
+                         "ms_per_step": other_ms, "cuda_graph": graph_other, "status": int(broken.item())}
+            else:
+                for module in row_modules:
+                    module.peer_all_reduce = None
+                graph_other = capture()
+                other = {"collective": "NCCL all_reduce", "ms_per_step": timed(runner), "cuda_graph": graph_other}
+        except Exception as error:
+            other = {"error": f"{type(error).__name__}: {error}"[:200]}
+        for module in row_modules:
+            module.peer_all_reduce = reducer
+        graph = capture()  # back to the measured configuration for the opt-in legs below
     packed = sum(m.packed_device_bytes for m in model.modules() if isinstance(m, (FusedNQRTLinear, RowParallelNQRTLinear)))
     result = {
         "workload": "llama-3-70b-arch W4A4KV4 tensor-parallel decode (one seeded model sharded over the ranks)",
         "parallelism": f"tp{world}", "layers": layers, "batch": batch, "context": context, "steps": steps,
         "warmup": warmup, "ms_per_step": ms_step, "tok_s": batch / (ms_step * 1e-3),
         "ms_per_layer": ms_step / layers,
-        "all_reduce": {"collective": "NCCL all_reduce(sum) of [batch, 8192] BF16 after o_proj and down_proj",
+        "all_reduce": {"collective": collective_note,
                        "per_step": collectives, "ms_per_step_eager": round(collective_ms, 3),
-                       "share_of_step": round(collective_ms / ms_step, 4) if ms_step else None},
+                       "share_of_step": round(collective_ms / ms_step, 4) if ms_step else None,
+                       "other_collective": other},
         "cuda_graph": graph, "kv": "pages pre-filled by the page encoder with synthetic K/V",
         "packed_weight_bytes_per_rank": int(packed), "build_s": round(build_s, 1),
         "ranks_agree_on_tokens": bool(same.item()),
@@ -1197,7 +1248,7 @@ def run_tp70b(args) -> None:
         dist.init_process_group("nccl", device_id=device)
     result = tp_decode(torch, dist, device, rank, world, layers=args.tp_layers, batch=args.tp_batch,
                        context=args.tp_context, steps=max(args.steps, 1), warmup=max(args.warmup, 3),
-                       resident=args.tp_resident)
+                       resident=args.tp_resident, collective=args.tp_collective)
     if rank == 0:
         print(json.dumps({
             "metric": "w4a4kv4_tp_decode_tok_s", "value": result["tok_s"], "unit": "tok/s", "n_gpus": world,
@@ -1243,6 +1294,10 @@ def main() -> None:
     parser.add_argument("--tp-context", type=int, default=4096)
     parser.add_argument("--shape", choices=[name for name, _, _ in SHAPES], default=None,
                         help="with --workload gemv: only this projection shape (short profiling runs)")
+    parser.add_argument("--tp-collective", choices=("peer", "nccl"), default="nccl",
+                        help="tensor-parallel sum after o_proj / down_proj: NCCL, or this repository's peer-memory "
+                             "kernel (falls back to NCCL when symmetric memory is unavailable); the other one is "
+                             "timed too and reported under all_reduce.other_collective")
     parser.add_argument("--tp-resident", action="store_true",
                         help="tp70b: also time the opt-in mode that keeps the decoded BF16 weights of the shard in HBM")
     parser.add_argument("--kernel-mix", action="store_true",

@@ -405,6 +405,26 @@ int nq_rope_hadamard(const void* x, int dtype, int64_t batch, int64_t heads, int
 int nq_rmsnorm(const void* x, const void* weight, int dtype, int64_t rows, int64_t n, float eps, void* out,
                nq_stream_t stream);
 
+/* -------------------------------------------------------------------------
+ * Tensor-parallel sum of the ranks' partial projection outputs over peer memory (one node).
+ * No counterpart in the reference (single GPU); replaces the NCCL all-reduce after o_proj /
+ * down_proj of a tensor-parallel shard (one launch per rank, partials read over NVLink with
+ * plain 16-byte loads, summed in rank order in float32 on every rank: identical results).
+ *   partials_host  HOST array of `world` device pointers: every rank's BF16 partial [count]
+ *                  as mapped in THIS process (symmetric / IPC memory); entry `rank` is local
+ *   pads_host      HOST array of `world` device pointers: every rank's flag pad of
+ *                  NQ_TP_PAD_BYTES bytes, mapped the same way, zeroed once before the first
+ *                  call of the group (words 0..15 are written by the peers, 16..18 are local:
+ *                  calls completed, CTA ticket, status: non-zero = a bounded wait gave up)
+ *   out_bf16       local result [count]; count % 8 == 0
+ * All ranks must issue the same sequence of calls with the same count; a rank's partial must
+ * not be rewritten before ITS call has completed (stream order on the rank is enough: the
+ * call returns only after every rank has finished reading).  world <= NQ_TP_MAX_RANKS. */
+#define NQ_TP_MAX_RANKS 8
+#define NQ_TP_PAD_BYTES 128
+int nq_tp_allreduce_bf16(const void* const* partials_host, void* const* pads_host, int rank, int world,
+                         void* out_bf16, int64_t count, nq_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

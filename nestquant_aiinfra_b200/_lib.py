@@ -18,7 +18,7 @@ CSRC = _PKG / "csrc"
 LIB_PATH = _PKG / "libnq_b200.so"
 HEADER = _PKG.parent / "include" / "nq_b200.h"
 SOURCES = ("nq_encode.cu", "nq_gemv.cu", "nq_gemv_bf16.cu", "nq_gemv_static.cu", "nq_gemm.cu", "nq_gemm_tc.cu", "nq_kv.cu", "nq_attn.cu",
-           "nq_rotate.cu", "nq_encode_rotated.cu", "nq_norm.cu", "nq_rope.cu")
+           "nq_rotate.cu", "nq_encode_rotated.cu", "nq_norm.cu", "nq_rope.cu", "nq_allreduce.cu")
 
 NQ_F32, NQ_BF16, NQ_F16 = 0, 1, 2
 WS_COUNTER_BYTES = 65536

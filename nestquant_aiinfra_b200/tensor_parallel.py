@@ -85,6 +85,72 @@ class ColumnParallelNQRTLinear(nn.Module):
         return self.inner(x)
 
 
+class PeerAllReduce:
+    """Sum of the ranks' BF16 partial outputs read straight out of peer memory (``nq_tp_allreduce_bf16``).
+
+    One instance serves every row-parallel projection of a rank: it owns a buffer in symmetric memory
+    (``torch.distributed._symmetric_memory``: the same allocation mapped into every process of the group) that
+    holds this rank's partial and its flag pad, and the peers' addresses of both.  ``reduce(partial)`` copies the
+    partial into the buffer and launches the kernel; the result is a fresh local tensor.  All ranks must call it
+    in the same order with the same shapes (they do: the model code is the same on every rank).  Works under
+    CUDA-graph capture (the call number lives in device memory).  One node only; NCCL remains the fallback.
+    """
+
+    PAD_BYTES = 128
+
+    def __init__(self, max_elements: int, device: torch.device, process_group=None) -> None:
+        import ctypes
+
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+
+        from . import _lib
+
+        group = process_group if process_group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        if self.world > 8:
+            raise ValueError("PeerAllReduce serves at most 8 ranks")
+        if max_elements < 8 or max_elements % 8:
+            raise ValueError("max_elements must be a positive multiple of 8")
+        self.max_elements = int(max_elements)
+        self.device = torch.device(device)
+        nbytes = self.PAD_BYTES + 2 * self.max_elements
+        self._buffer = symm.empty(nbytes, dtype=torch.uint8, device=self.device)
+        self._buffer.zero_()
+        self._handle = symm.rendezvous(self._buffer, group)
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group)  # every pad is zero before anybody's first call
+        bases = [int(ptr) for ptr in self._handle.buffer_ptrs]
+        pointer_array = ctypes.c_void_p * self.world
+        self._pads = pointer_array(*bases)
+        self._partials = pointer_array(*[base + self.PAD_BYTES for base in bases])
+        self._local_partial = self._buffer[self.PAD_BYTES:].view(torch.bfloat16)
+        self._lib = _lib
+        self.calls = 0
+
+    def status(self) -> int:
+        """Non-zero when a bounded wait of an earlier call gave up (1: partials, 2: end of reading)."""
+        torch.cuda.synchronize(self.device)
+        return int(self._buffer[:self.PAD_BYTES].view(torch.int32)[18].item())
+
+    def reduce(self, partial: torch.Tensor) -> torch.Tensor:
+        import ctypes
+
+        if partial.dtype != torch.bfloat16 or partial.device != self.device:
+            raise ValueError("PeerAllReduce sums bfloat16 tensors of its own device")
+        count = partial.numel()
+        if count > self.max_elements or count % 8:
+            raise ValueError("partial must have a multiple of 8 elements, at most max_elements")
+        self._local_partial[:count].copy_(partial.reshape(-1))
+        out = torch.empty_like(partial, memory_format=torch.contiguous_format)
+        status = self._lib.lib().nq_tp_allreduce_bf16(
+            self._partials, self._pads, self.rank, self.world, ctypes.c_void_p(out.data_ptr()),
+            ctypes.c_int64(count), ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream))
+        self._lib.check(status, "nq_tp_allreduce_bf16")
+        self.calls += 1
+        return out
+
+
 class RowParallelNQRTLinear(nn.Module):
     """``y = all_reduce_sum( Q(x[:, shard] H_blk) . W[:, shard]^T )`` with a self-contained shard.
 
@@ -107,6 +173,8 @@ class RowParallelNQRTLinear(nn.Module):
         self.inner = None
         # measurement hook: a list here receives one (start, end) CUDA-event pair per all-reduce
         self.collective_events: list | None = None
+        # a PeerAllReduce here replaces the NCCL all-reduce (BF16 partials, one node)
+        self.peer_all_reduce: PeerAllReduce | None = None
         if project is None:
             from .fused_linear import FusedNQRTLinear
             from .runtime.w4a4 import quantize_weight_cuda
@@ -132,13 +200,21 @@ class RowParallelNQRTLinear(nn.Module):
         if self.world > 1:
             import torch.distributed as dist
 
+            peer = self.peer_all_reduce if partial.dtype == torch.bfloat16 and partial.is_cuda else None
+
+            def collective(tensor: torch.Tensor) -> torch.Tensor:
+                if peer is not None:
+                    return peer.reduce(tensor)
+                dist.all_reduce(tensor, op=dist.ReduceOp.SUM, group=self.process_group)
+                return tensor
+
             events = self.collective_events
             if events is not None and partial.is_cuda:
                 start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 start.record()
-                dist.all_reduce(partial, op=dist.ReduceOp.SUM, group=self.process_group)
+                partial = collective(partial)
                 end.record()
                 events.append((start, end))
             else:
-                dist.all_reduce(partial, op=dist.ReduceOp.SUM, group=self.process_group)
+                partial = collective(partial)
         return partial

@@ -134,3 +134,73 @@ def test_row_parallel_all_reduce_two_nccl_ranks(tmp_path):
     mp.spawn(_nccl_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
     a, b = np.load(tmp_path / "rank0.npy"), np.load(tmp_path / "rank1.npy")
     assert np.array_equal(a, b)
+
+
+def _peer_worker(rank: int, world: int, port: int, out_dir: str) -> None:
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    device = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+    try:
+        from nestquant_aiinfra_b200.tensor_parallel import PeerAllReduce, RowParallelNQRTLinear, shard_range
+
+        reducer = PeerAllReduce(128 * 1024, device)
+        # plain tensors, several calls in a row, sizes that change: every call sums what the ranks hold
+        results = []
+        for call, count in enumerate((64, 4096, 128 * 1024, 4096)):
+            mine = torch.randn(count, generator=rng(100 * call + rank)).bfloat16().to(device)
+            total = sum(torch.randn(count, generator=rng(100 * call + r)).bfloat16().float() for r in range(world))
+            out = reducer.reduce(mine)
+            assert torch.equal(out.cpu(), total.bfloat16())  # float32 sum in rank order, one rounding
+            results.append(out)
+        # the same calls replayed from a CUDA graph: the call number lives in device memory
+        static = torch.randn(4096, generator=rng(900 + rank)).bfloat16().to(device)
+        expected = sum(torch.randn(4096, generator=rng(900 + r)).bfloat16().float() for r in range(world)).bfloat16()
+        side = torch.cuda.Stream(device)
+        with torch.cuda.stream(side):
+            reducer.reduce(static)
+            torch.cuda.synchronize(device)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                first = reducer.reduce(static)
+                second = reducer.reduce(first)  # two dependent collectives inside one graph
+            for _ in range(3):
+                graph.replay()
+            torch.cuda.synchronize(device)
+        assert torch.equal(first.cpu(), expected)
+        assert torch.equal(second.cpu(), (expected.float() * world).bfloat16())
+        assert reducer.status() == 0
+        # the row-parallel projection with the peer collective: same gate as with NCCL
+        n, k, m = 256, 2048, 8
+        weight = 0.02 * torch.randn(n, k, generator=rng(5))
+        x = torch.randn(m, k, generator=rng(6)).bfloat16()
+        lo, hi = shard_range(k, world, rank, multiple=32)
+        layer = RowParallelNQRTLinear(weight[:, lo:hi].contiguous().cuda(), rank, world, dither_seed=300 + rank).cuda()
+        layer.peer_all_reduce = reducer
+        with torch.no_grad():
+            out = layer(x[:, lo:hi].contiguous().cuda())
+        torch.cuda.synchronize()
+        assert out.dtype == torch.bfloat16 and reducer.status() == 0
+        np.save(os.path.join(out_dir, f"peer{rank}.npy"), out.float().cpu().numpy())
+        from oracle import nq_oracle as oracle
+
+        expected = sum(shard_product(oracle, weight, x, *shard_range(k, world, r, multiple=32), 300 + r)
+                       for r in range(world))
+        actual = out.float().cpu().numpy()
+        # BF16 partials and a BF16 result: the stated gates plus the rounding of the output dtype
+        assert max_abs(actual, expected) <= MAX_ABS_TOL + 2.0 ** -8 * np.abs(expected).max()
+        assert rel_fro(actual, expected) <= 4e-3
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_peer_memory_all_reduce_two_ranks(tmp_path):
+    """nq_tp_allreduce_bf16 over symmetric memory: exact sums, graph replay, and the projection end to end."""
+    import torch.multiprocessing as mp
+
+    mp.spawn(_peer_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    a, b = np.load(tmp_path / "peer0.npy"), np.load(tmp_path / "peer1.npy")
+    assert np.array_equal(a, b)
