@@ -13,6 +13,8 @@
  *     whether the page-decode table of nq_kv_attention has been filled)
  *     and, for nq_w4a4_gemv_static only, the address of its built-in scratch;
  *     launches go to the CURRENT device, which must be the stream's device;
+ *   - every entry point opens an NVTX range of its own name around its launches
+ *     (visible to profiling tools, otherwise a no-op);
  *   - return value 0 = success, negative = argument error (NQ_ERR_*), positive
  *     = cudaError_t of the failed launch; nq_last_error() describes the last
  *     failure of the calling thread;

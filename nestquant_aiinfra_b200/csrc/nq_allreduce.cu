@@ -117,6 +117,7 @@ __global__ void __launch_bounds__(kArThreads) nq_tp_allreduce_kernel(const ArPar
 
 extern "C" int nq_tp_allreduce_bf16(const void* const* partials_host, void* const* pads_host, int rank, int world,
                                     void* out_bf16, int64_t count, nq_stream_t stream) {
+    NQ_RANGE("nq_tp_allreduce_bf16");
     NQ_REQUIRE(partials_host && pads_host && out_bf16, NQ_ERR_ARG, "nq_tp_allreduce_bf16: null pointer");
     NQ_REQUIRE(world >= 1 && world <= kMaxRanks && rank >= 0 && rank < world, NQ_ERR_ARG,
                "nq_tp_allreduce_bf16: 1 <= world <= %d and 0 <= rank < world required", kMaxRanks);

@@ -701,6 +701,7 @@ extern "C" int nq_kv_attention(const void* query, int q_dtype, int batch, int q_
                                int pool_capacity, int page_size, int kv_heads, int dim, float scale,
                                void* workspace, size_t workspace_bytes, void* out, int out_dtype,
                                nq_stream_t stream) {
+    NQ_RANGE("nq_kv_attention");
     return kv_attention_impl(query, q_dtype, batch, q_tokens, q_heads, slot_ids, active_mask, q_lens, cache_active,
                              sequence_lengths, page_indices, page_counts, last_page_lens, hot_lengths, key_codes,
                              key_betas, key_norms, value_codes, value_betas, value_norms, key_beta_table,
@@ -722,6 +723,7 @@ extern "C" int nq_kv_attention_lattice(const void* query, int q_dtype, int batch
                                        int kv_heads, int dim, float scale, void* workspace, size_t workspace_bytes,
                                        void* out, int out_dtype, const int8_t* key_lattice,
                                        const int8_t* value_lattice, nq_stream_t stream) {
+    NQ_RANGE("nq_kv_attention_lattice");
     NQ_REQUIRE(key_lattice && value_lattice && nq_aligned16(key_lattice) && nq_aligned16(value_lattice), NQ_ERR_ARG,
                "nq_kv_attention_lattice: 16-byte aligned lattice pages required");
     return kv_attention_impl(query, q_dtype, batch, q_tokens, q_heads, slot_ids, active_mask, q_lens, cache_active,

@@ -35,6 +35,16 @@ void nq_count_launch();  // bumps the process-wide kernel-launch counter (nq_lau
 
 static inline bool nq_aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// NVTX range around every C-ABI entry (host side only; a no-op call when no profiling tool is attached).
+#include <nvtx3/nvToolsExt.h>
+struct NqRange {
+    explicit NqRange(const char* name) { nvtxRangePushA(name); }
+    ~NqRange() { nvtxRangePop(); }
+    NqRange(const NqRange&) = delete;
+    NqRange& operator=(const NqRange&) = delete;
+};
+#define NQ_RANGE(name) NqRange nq_range_guard_(name)
+
 // Per-device facts, looked up once per device (a process may drive several GPUs): the current
 // device's index (or -1) and its SM count.  The tables only ever receive the same value for the same
 // slot, so unsynchronised writers are harmless.

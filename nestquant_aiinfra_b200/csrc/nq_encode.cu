@@ -132,6 +132,7 @@ static int launch_encode(const void* x, int64_t rows, int64_t k, int64_t row_str
 extern "C" int nq_a4_encode(const void* x, int x_dtype, int64_t rows, int64_t k, int64_t row_stride,
                             const float* beta_table, uint8_t* out_codes, uint8_t* out_beta_ids,
                             float* out_norms, void* out_decoded, nq_stream_t stream) {
+    NQ_RANGE("nq_a4_encode");
     NQ_REQUIRE(x && beta_table && out_codes && out_beta_ids && out_norms, NQ_ERR_ARG,
                "nq_a4_encode: null pointer");
     NQ_REQUIRE(rows >= 1 && rows <= (int64_t)1 << 31, NQ_ERR_ARG, "nq_a4_encode: rows=%lld out of range", (long long)rows);
@@ -155,6 +156,7 @@ extern "C" int nq_a4_encode(const void* x, int x_dtype, int64_t rows, int64_t k,
 extern "C" int nq_w4_encode(const void* w, int w_dtype, int64_t rows, int64_t k, int64_t row_stride,
                             const float* beta_table, int64_t seed, int64_t w_block_offset,
                             uint8_t* out_codes, uint8_t* out_beta_ids, float* out_norms, nq_stream_t stream) {
+    NQ_RANGE("nq_w4_encode");
     NQ_REQUIRE(w && beta_table && out_codes && out_beta_ids && out_norms, NQ_ERR_ARG, "nq_w4_encode: null pointer");
     NQ_REQUIRE(rows >= 1 && k >= 32 && k <= 32768 && k % 32 == 0 && row_stride >= k, NQ_ERR_ARG,
                "nq_w4_encode: bad shape rows=%lld k=%lld", (long long)rows, (long long)k);
@@ -177,6 +179,7 @@ extern "C" int nq_w4_encode(const void* w, int w_dtype, int64_t rows, int64_t k,
 extern "C" int nq_a4_decode(const uint8_t* codes, const uint8_t* beta_ids, const float* norms,
                             const float* beta_table, int64_t rows, int64_t k, void* out, int out_dtype,
                             nq_stream_t stream) {
+    NQ_RANGE("nq_a4_decode");
     NQ_REQUIRE(codes && beta_ids && norms && beta_table && out, NQ_ERR_ARG, "nq_a4_decode: null pointer");
     NQ_REQUIRE(rows >= 1 && k >= 8 && k % 8 == 0, NQ_ERR_ARG, "nq_a4_decode: bad shape");
     NQ_REQUIRE(out_dtype == NQ_F32 || out_dtype == NQ_BF16, NQ_ERR_ARG, "nq_a4_decode: out_dtype must be f32 or bf16");
@@ -210,6 +213,7 @@ int nq_w4_decode_segments(const uint8_t* w_codes, const uint8_t* w_beta_ids, con
 extern "C" int nq_w4_decode(const uint8_t* w_codes, const uint8_t* w_beta_ids, const float* w_norms,
                             const float* w_betas, int64_t n, int64_t k, int64_t w_block_offset,
                             int64_t seed, void* out_bf16, nq_stream_t stream) {
+    NQ_RANGE("nq_w4_decode");
     NQ_REQUIRE(w_codes && w_beta_ids && w_norms && w_betas && out_bf16, NQ_ERR_ARG, "nq_w4_decode: null pointer");
     NQ_REQUIRE(n >= 1 && k >= 8 && k % 8 == 0, NQ_ERR_ARG, "nq_w4_decode: bad shape");
     NQ_REQUIRE(seed >= 0 && seed < ((int64_t)1 << 31) && w_block_offset >= 0, NQ_ERR_ARG, "nq_w4_decode: bad seed/offset");

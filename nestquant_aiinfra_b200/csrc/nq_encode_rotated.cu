@@ -156,6 +156,7 @@ int launch_encode_rotated(const void* x, int64_t rows, int64_t k, int64_t hadama
 extern "C" int nq_a4_encode_rotated(const void* x, int x_dtype, int64_t rows, int64_t k, int64_t hadamard_block,
                                     const float* beta_table, uint8_t* out_codes, uint8_t* out_beta_ids,
                                     float* out_norms, void* out_decoded, nq_stream_t stream) {
+    NQ_RANGE("nq_a4_encode_rotated");
     NQ_REQUIRE(x && beta_table && out_codes && out_beta_ids && out_norms, NQ_ERR_ARG,
                "nq_a4_encode_rotated: null pointer");
     NQ_REQUIRE(rows >= 1 && k % 32 == 0 && k >= 32 && k <= NQ_ROTATED_MAX_K, NQ_ERR_ARG,
@@ -199,6 +200,7 @@ extern "C" int nq_a4_encode_rmsnorm_rotated(const void* x, const void* weight, f
                                             int64_t k, int64_t row_stride, int64_t hadamard_block,
                                             const float* beta_table, uint8_t* out_codes, uint8_t* out_beta_ids,
                                             float* out_norms, void* out_decoded, nq_stream_t stream) {
+    NQ_RANGE("nq_a4_encode_rmsnorm_rotated");
     int rc = check_fused_args("nq_a4_encode_rmsnorm_rotated", x, weight, beta_table, out_codes, out_beta_ids, out_norms,
                               out_decoded, dtype, rows, k, row_stride, hadamard_block);
     if (rc) return rc;
@@ -214,6 +216,7 @@ extern "C" int nq_a4_encode_silu_mul_rotated(const void* gate, const void* up, i
                                              int64_t row_stride, int64_t hadamard_block, const float* beta_table,
                                              uint8_t* out_codes, uint8_t* out_beta_ids, float* out_norms,
                                              void* out_decoded, nq_stream_t stream) {
+    NQ_RANGE("nq_a4_encode_silu_mul_rotated");
     int rc = check_fused_args("nq_a4_encode_silu_mul_rotated", gate, up, beta_table, out_codes, out_beta_ids, out_norms,
                               out_decoded, dtype, rows, k, row_stride, hadamard_block);
     if (rc) return rc;

@@ -127,6 +127,7 @@ extern "C" int nq_w4a4_gemm(const uint8_t* act_codes, const uint8_t* act_beta_id
                             const float* w_betas, int64_t m, int64_t n, int64_t k,
                             int64_t w_block_offset, int64_t seed, void* out, int out_dtype,
                             void* workspace, size_t workspace_bytes, nq_stream_t stream) {
+    NQ_RANGE("nq_w4a4_gemm");
     NQ_REQUIRE(k >= 32 && k % 32 == 0 && n >= 8, NQ_ERR_ARG, "nq_w4a4_gemm: bad shape");
     NQ_REQUIRE(seed >= 0 && seed < ((int64_t)1 << 31) && w_block_offset >= 0 &&
                    w_block_offset + n * (k / 8) <= ((int64_t)1 << 28),
@@ -147,6 +148,7 @@ extern "C" int nq_w4a4_gemm_fused(const uint8_t* act_codes, const uint8_t* act_b
                                   const float* w_betas, int64_t m, int64_t n, int64_t k,
                                   int64_t w_block_offset, int64_t seed, void* out, int out_dtype,
                                   void* workspace, size_t workspace_bytes, nq_stream_t stream) {
+    NQ_RANGE("nq_w4a4_gemm_fused");
     NQ_REQUIRE(k >= 32 && k % 32 == 0 && n >= 8, NQ_ERR_ARG, "nq_w4a4_gemm_fused: bad shape");
     NQ_REQUIRE(seed >= 0 && seed < ((int64_t)1 << 31) && w_block_offset >= 0 &&
                    w_block_offset + n * (k / 8) <= ((int64_t)1 << 28),
@@ -163,6 +165,7 @@ extern "C" int nq_w4a4_gemm_grouped(const uint8_t* act_codes, const uint8_t* act
                                     const int64_t* seg_first_row, const int64_t* seg_block_offset,
                                     const int64_t* seg_seed, void* out, int out_dtype,
                                     void* workspace, size_t workspace_bytes, nq_stream_t stream) {
+    NQ_RANGE("nq_w4a4_gemm_grouped");
     NQ_REQUIRE(segments >= 1 && segments <= NQ_MAX_SEGMENTS && seg_first_row && seg_block_offset && seg_seed,
                NQ_ERR_ARG, "nq_w4a4_gemm_grouped: 1..%d segments with their tables", NQ_MAX_SEGMENTS);
     NQ_REQUIRE(k >= 32 && k % 32 == 0 && n >= 8, NQ_ERR_ARG, "nq_w4a4_gemm_grouped: bad shape");
@@ -216,6 +219,7 @@ extern "C" int nq_w4a4_gemm_resident(const uint8_t* act_codes, const uint8_t* ac
                                      const float* act_betas, const void* act_decoded, const void* w_decoded,
                                      int64_t m, int64_t n, int64_t k, void* out, int out_dtype,
                                      void* workspace, size_t workspace_bytes, nq_stream_t stream) {
+    NQ_RANGE("nq_w4a4_gemm_resident");
     NQ_REQUIRE(w_decoded && out, NQ_ERR_ARG, "nq_w4a4_gemm_resident: null pointer");
     NQ_REQUIRE(act_decoded || (act_codes && act_beta_ids && act_norms && act_betas), NQ_ERR_ARG,
                "nq_w4a4_gemm_resident: activation streams missing");
@@ -257,6 +261,7 @@ extern "C" int nq_w4a4_gemm_resident(const uint8_t* act_codes, const uint8_t* ac
 }
 
 extern "C" int nq_w4a4_status(const void* workspace, uint32_t* status_host, nq_stream_t stream) {
+    NQ_RANGE("nq_w4a4_status");
     NQ_REQUIRE(workspace && status_host, NQ_ERR_ARG, "nq_w4a4_status: null pointer");
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     cudaError_t e = cudaMemcpyAsync(status_host, reinterpret_cast<const char*>(workspace) + NQ_WS_STATUS_OFFSET,
@@ -274,6 +279,7 @@ extern "C" int nq_w4a4_status(const void* workspace, uint32_t* status_host, nq_s
 extern "C" int nq_bf16_gemm_tc(const void* a_bf16, const void* w_bf16, int64_t m, int64_t n, int64_t k,
                                void* out, int out_dtype, void* workspace, size_t workspace_bytes,
                                nq_stream_t stream) {
+    NQ_RANGE("nq_bf16_gemm_tc");
     NQ_REQUIRE(a_bf16 && w_bf16 && out && workspace, NQ_ERR_ARG, "nq_bf16_gemm_tc: null pointer");
     NQ_REQUIRE(nq_tc_supported(m, n, k), NQ_ERR_ARG, "nq_bf16_gemm_tc: needs n %% 128 == 0 and k %% 64 == 0");
     NQ_REQUIRE(out_dtype == NQ_F32 || out_dtype == NQ_BF16, NQ_ERR_ARG, "nq_bf16_gemm_tc: out_dtype");

@@ -80,6 +80,7 @@ extern "C" int nq_w4a4_gemv_static(const uint8_t* act_codes, const uint8_t* act_
                                    const float* w_norms, const float* w_betas, int64_t m, int64_t n, int64_t k,
                                    int64_t w_block_offset, int64_t seed, void* out, int out_dtype,
                                    nq_stream_t stream) {
+    NQ_RANGE("nq_w4a4_gemv_static");
     NQ_REQUIRE(act_codes && act_beta_ids && act_norms && act_betas && w_codes && w_beta_ids && w_norms && w_betas && out,
                NQ_ERR_ARG, "nq_w4a4_gemv_static: null pointer");
     NQ_REQUIRE(m >= 1 && m <= kStaticMaxM && n >= 8 && n % 8 == 0 && n <= kStaticMaxN && k >= 32 && k % 32 == 0 &&

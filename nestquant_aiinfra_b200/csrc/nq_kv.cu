@@ -301,6 +301,7 @@ extern "C" int nq_kv_append(const void* key, const void* value, int kv_dtype, in
                             const int32_t* segment_counts, const uint8_t* cache_active, void* hot_keys,
                             void* hot_values, int32_t* hot_lengths, int32_t* sequence_lengths, int max_sequences,
                             int page_size, int heads, int dim, nq_stream_t stream) {
+    NQ_RANGE("nq_kv_append");
     NQ_REQUIRE(key && value && slot_ids && cache_active && hot_keys && hot_values && hot_lengths && sequence_lengths,
                NQ_ERR_ARG, "nq_kv_append: null pointer");
     NQ_REQUIRE(mode >= 0 && mode <= 2, NQ_ERR_ARG, "nq_kv_append: mode must be 0 (K1), 1 (write mask) or 2 (segment)");
@@ -387,6 +388,7 @@ extern "C" int nq_kv_pack_publish(const void* hot_keys, const void* hot_values, 
                                   const float* value_beta_table, int32_t* page_indices, int32_t* page_counts,
                                   int32_t* last_page_lens, int max_sequences, int max_pages, int pool_capacity,
                                   int page_size, int heads, int dim, nq_stream_t stream) {
+    NQ_RANGE("nq_kv_pack_publish");
     return kv_pack_publish_impl(hot_keys, hot_values, kv_dtype, hot_lengths, boundary_mask, target_page_ids, key_codes,
                                 key_betas, key_norms, value_codes, value_betas, value_norms, key_beta_table,
                                 value_beta_table, page_indices, page_counts, last_page_lens, max_sequences, max_pages,
@@ -402,6 +404,7 @@ extern "C" int nq_kv_pack_publish_lattice(const void* hot_keys, const void* hot_
                                           int32_t* last_page_lens, int max_sequences, int max_pages,
                                           int pool_capacity, int page_size, int heads, int dim, int8_t* key_lattice,
                                           int8_t* value_lattice, nq_stream_t stream) {
+    NQ_RANGE("nq_kv_pack_publish_lattice");
     NQ_REQUIRE(key_lattice && value_lattice && nq_aligned16(key_lattice) && nq_aligned16(value_lattice), NQ_ERR_ARG,
                "nq_kv_pack_publish_lattice: 16-byte aligned lattice pages required");
     return kv_pack_publish_impl(hot_keys, hot_values, kv_dtype, hot_lengths, boundary_mask, target_page_ids, key_codes,
@@ -413,6 +416,7 @@ extern "C" int nq_kv_pack_publish_lattice(const void* hot_keys, const void* hot_
 extern "C" int nq_kv_alloc_targets(const int32_t* hot_lengths, const uint8_t* boundary_mask, const int32_t* page_counts,
                                    const int32_t* free_ids, int32_t* free_count, int32_t* target_page_ids,
                                    int max_sequences, int max_pages, int page_size, nq_stream_t stream) {
+    NQ_RANGE("nq_kv_alloc_targets");
     NQ_REQUIRE(hot_lengths && boundary_mask && page_counts && free_ids && free_count && target_page_ids, NQ_ERR_ARG,
                "nq_kv_alloc_targets: null pointer");
     NQ_REQUIRE(max_sequences >= 1 && max_pages >= 1 && page_size >= 1, NQ_ERR_ARG, "nq_kv_alloc_targets: bad geometry");
@@ -425,6 +429,7 @@ extern "C" int nq_kv_alloc_targets(const int32_t* hot_lengths, const uint8_t* bo
 
 extern "C" int nq_kv_alloc_pages(int count, const int32_t* free_ids, int32_t* free_count, int32_t* out_ids,
                                  nq_stream_t stream) {
+    NQ_RANGE("nq_kv_alloc_pages");
     NQ_REQUIRE(free_ids && free_count && (out_ids || count == 0), NQ_ERR_ARG, "nq_kv_alloc_pages: null pointer");
     NQ_REQUIRE(count >= 0, NQ_ERR_ARG, "nq_kv_alloc_pages: negative count");
     if (count == 0) return NQ_OK;
@@ -437,6 +442,7 @@ extern "C" int nq_kv_release_pages(const uint8_t* slot_mask, int32_t* page_indic
                                    int32_t* last_page_lens, int32_t* hot_lengths, int32_t* sequence_lengths,
                                    int32_t* free_ids, int32_t* free_count, int max_sequences, int max_pages,
                                    int pool_capacity, nq_stream_t stream) {
+    NQ_RANGE("nq_kv_release_pages");
     NQ_REQUIRE(slot_mask && page_indices && page_counts && last_page_lens && hot_lengths && sequence_lengths &&
                    free_ids && free_count,
                NQ_ERR_ARG, "nq_kv_release_pages: null pointer");
@@ -450,6 +456,7 @@ extern "C" int nq_kv_release_pages(const uint8_t* slot_mask, int32_t* page_indic
 
 extern "C" int nq_kv_expand_pages(const uint8_t* codes, int8_t* lattice, const int32_t* page_ids, int64_t count,
                                   int pool_capacity, int page_size, int heads, int dim, nq_stream_t stream) {
+    NQ_RANGE("nq_kv_expand_pages");
     NQ_REQUIRE(codes && lattice && page_ids, NQ_ERR_ARG, "nq_kv_expand_pages: null pointer");
     NQ_REQUIRE(count >= 0 && count <= 0x7fffffff && pool_capacity >= 1 && dims_ok(page_size, heads, dim), NQ_ERR_ARG,
                "nq_kv_expand_pages: bad geometry");
@@ -467,6 +474,7 @@ extern "C" int nq_kv_quantize_page(const void* key, const void* value, int kv_dt
                                    int heads, int dim, const float* key_beta_table, const float* value_beta_table,
                                    uint8_t* key_codes, uint8_t* key_betas, float* key_norms, uint8_t* value_codes,
                                    uint8_t* value_betas, float* value_norms, nq_stream_t stream) {
+    NQ_RANGE("nq_kv_quantize_page");
     NQ_REQUIRE(key && value && key_beta_table && value_beta_table && key_codes && key_betas && key_norms &&
                    value_codes && value_betas && value_norms,
                NQ_ERR_ARG, "nq_kv_quantize_page: null pointer");

@@ -61,6 +61,7 @@ int launch_rmsnorm(const void* x, const void* weight, int64_t rows, int64_t n, f
 
 extern "C" int nq_rmsnorm(const void* x, const void* weight, int dtype, int64_t rows, int64_t n, float eps, void* out,
                           nq_stream_t stream) {
+    NQ_RANGE("nq_rmsnorm");
     NQ_REQUIRE(x && weight && out, NQ_ERR_ARG, "nq_rmsnorm: null pointer");
     NQ_REQUIRE(rows >= 1 && rows <= 0x7fffffff && n >= 8 && n % 8 == 0 && n <= (1 << 20), NQ_ERR_ARG,
                "nq_rmsnorm: rows=%lld n=%lld (n must be a multiple of 8)", (long long)rows, (long long)n);

@@ -97,6 +97,7 @@ int launch_rope(const RopeParams& p, cudaStream_t s) {
 extern "C" int nq_rope_hadamard(const void* x, int dtype, int64_t batch, int64_t heads, int64_t tokens, int64_t dim,
                                 int64_t stride_b, int64_t stride_h, int64_t stride_t, const void* cos,
                                 const void* sin, int apply_hadamard, void* out, nq_stream_t stream) {
+    NQ_RANGE("nq_rope_hadamard");
     NQ_REQUIRE(x && cos && sin && out, NQ_ERR_ARG, "nq_rope_hadamard: null pointer");
     NQ_REQUIRE(batch >= 1 && heads >= 1 && tokens >= 1, NQ_ERR_ARG, "nq_rope_hadamard: empty tensor");
     NQ_REQUIRE(dim >= 16 && dim <= 1024 && (dim & (dim - 1)) == 0, NQ_ERR_ARG,

@@ -63,6 +63,7 @@ int launch_hadamard(const void* x, void* out, int64_t rows, int64_t n, cudaStrea
 }  // namespace
 
 extern "C" int nq_hadamard(const void* x, void* out, int dtype, int64_t rows, int64_t n, nq_stream_t stream) {
+    NQ_RANGE("nq_hadamard");
     NQ_REQUIRE(x && out, NQ_ERR_ARG, "nq_hadamard: null pointer");
     NQ_REQUIRE(rows >= 1 && n >= 8 && n <= 32768 && (n & (n - 1)) == 0, NQ_ERR_ARG,
                "nq_hadamard: n=%lld must be a power of two in [8, 32768]", (long long)n);
