@@ -48,7 +48,7 @@ constexpr int kTileK = 64;       // K elements per stage (one 128-byte swizzle r
 constexpr int kThreadsTc = 192;  // 6 warps
 constexpr int kAccCols = 256;    // TMEM columns per accumulator buffer
 constexpr int kMaxStages = 8;
-constexpr int kPairMinK = 4096;   // paired channel tiles pay once the main loop dwarfs the exposed epilogue (measured)
+constexpr int kPairMinK = 2048;   // paired channel tiles: measured from 32 k-steps per item upwards
 constexpr int kDecodeWarps = 16;                              // FUSED: warps 6..21 decode the weight
 constexpr int kThreadsFused = kThreadsTc + kDecodeWarps * 32;  // 704 threads at 80 registers
 constexpr int kUnitBlocks = kTileN * (kTileK / 8);            // E8 blocks per decode unit (128 channels x 64 features)
@@ -121,6 +121,9 @@ nq_w4a4_tc_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
     const uint32_t a_bytes = (uint32_t)p.tile_t * kTileK * 2;
     const uint32_t stage_bytes = w_bytes + a_bytes;
     TcBarriers* bars = reinterpret_cast<TcBarriers*>(smem + (size_t)p.stages * stage_bytes);
+    // PAIR: four private 32 x 32 BF16 tiles behind the barriers, one per epilogue warp
+    uint8_t* epilogue_stage = reinterpret_cast<uint8_t*>(bars) + ((sizeof(TcBarriers) + 15) & ~(size_t)15);
+    (void)epilogue_stage;
     volatile int* abort_flag = &bars->abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -298,6 +301,27 @@ nq_w4a4_tc_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
                 uint32_t r[32];
                 tmem_ld_32x32(taddr + (uint32_t)c, r);
                 tmem_ld_wait();
+                if constexpr (PAIR) {
+                    if (p.out_bf16) {
+                        // The pair's epilogue is not hidden behind the next item's MMAs, so it is worth doing
+                        // properly: the warp's 32 tokens x 32 channels go through a private 2 KB tile of shared
+                        // memory and leave as 16-byte stores (four per lane instead of 32 two-byte ones).
+                        __nv_bfloat16* tile = reinterpret_cast<__nv_bfloat16*>(epilogue_stage) + (warp - 2) * (32 * 32);
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) tile[j * 32 + lane] = __float2bfloat16_rn(__uint_as_float(r[j]));
+                        __syncwarp();
+                        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + (int64_t)(t0 + c) * p.n + n0 +
+                                           half * kTileN + quarter * 32;
+#pragma unroll
+                        for (int round = 0; round < 4; ++round) {
+                            const int row = round * 8 + (lane >> 2), piece = lane & 3;
+                            const uint4 v = *reinterpret_cast<const uint4*>(tile + row * 32 + piece * 8);
+                            if (t0 + c + row < p.m) *reinterpret_cast<uint4*>(o + (int64_t)row * p.n + piece * 8) = v;
+                        }
+                        __syncwarp();
+                        continue;
+                    }
+                }
                 if (p.splits > 1) {
                     float* o = p.partial + ((int64_t)split * p.m + t0 + c) * p.n + channel;
 #pragma unroll
@@ -446,9 +470,10 @@ int tc_plan(TcPlan& plan, const void* a_dec, const void* w_dec, int64_t m, int64
     p.t_tiles = (int)((m + p.tile_t - 1) / p.tile_t);
     // Two channel tiles per work item when that still gives every SM an item: the token tile is loaded once for 256
     // channels (64 KB instead of 96 KB of shared-memory fill for the same MMAs), at the price of an epilogue that
-    // the next item's MMAs cannot overlap (both accumulator buffers belong to the item).  Measured on M = 8192:
-    // K = 8192 (down_proj) 224 -> 208 us, K = 2048 (gate/up) 4 % slower, hence the bound on k.  The pairing is a
-    // template parameter: as a run-time flag it slowed the unpaired kernel by 20 %.
+    // the next item's MMAs cannot overlap (both accumulator buffers belong to the item) -- which is why the paired
+    // epilogue leaves through shared memory as 16-byte stores.  Measured on M = 8192 (GEMM alone): down_proj
+    // (K = 8192) 224 -> 178 us, gate/up (K = 2048) 207 -> 180 us, q/o 55 -> 41 us.  The pairing is a template
+    // parameter: as a run-time flag it slowed the unpaired kernel by 20 %.
     p.pair = (allow_pair && p.tile_t == 256 && p.splits == 1 && n % (2 * kTileN) == 0 && k >= kPairMinK &&
               (n / (2 * kTileN)) * p.t_tiles >= sm_count()) ? 1 : 0;
     if (p.pair) p.n_tiles /= 2;
@@ -464,7 +489,7 @@ int tc_plan(TcPlan& plan, const void* a_dec, const void* w_dec, int64_t m, int64
     if (rc) return rc;
     rc = make_map(&plan.map_a, a_dec, m, k, p.tile_t);
     if (rc) return rc;
-    plan.smem = (size_t)stages * stage_bytes + sizeof(TcBarriers) + 1024;
+    plan.smem = (size_t)stages * stage_bytes + sizeof(TcBarriers) + 1024 + (p.pair ? 16 + 4 * 32 * 32 * 2 : 0);
     plan.total = p.n_tiles * p.t_tiles * p.splits;
     return NQ_OK;
 }
