@@ -82,6 +82,10 @@ def test_full_size_tensor_core_gemm_matches_float32_product(rt, m, n, k):
     err = float((out - expected).abs().max())
     fro = float((out - expected).norm() / expected.norm())
     assert err <= MAX_ABS_TOL and fro <= REL_FRO_TOL, (err, fro)
+    # the BF16 output (paired tiles store it through shared memory) is the rounded accumulator, element for element
+    rounded = rt.gemm_bf16_tc(a, w, out_dtype=torch.bfloat16)
+    assert rt.read_status() == 0
+    assert torch.equal(rounded, out.bfloat16())
 
 
 def test_full_size_projection_tails_and_paths_agree(rt, oracle):
