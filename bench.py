@@ -1051,7 +1051,7 @@ def decode_workload(torch, device, *, requests: int = 64, new_tokens: int = 256,
 
 
 def tp_decode(torch, dist, device, rank: int, world: int, *, layers: int, batch: int, context: int, steps: int,
-              warmup: int, resident: bool = False, collective: str = "nccl") -> dict:
+              warmup: int, resident: bool = False, collective: str = "peer") -> dict:
     """Config 4: Llama-3-70B architecture (one seeded model sharded over the ranks), W4A4KV4, graph decode.
 
     Returns the measurements (identical on every rank; the times are the maximum over the ranks).  The
@@ -1106,11 +1106,9 @@ def tp_decode(torch, dist, device, rank: int, world: int, *, layers: int, batch:
     reducer = None
     if world > 1 and collective == "peer":
         try:
-            from nestquant_aiinfra_b200.tensor_parallel import PeerAllReduce
+            from nestquant_aiinfra_b200.tp_engine import attach_peer_all_reduce
 
-            reducer = PeerAllReduce(batch * 8192, device)
-            for module in row_modules:
-                module.peer_all_reduce = reducer
+            reducer = attach_peer_all_reduce(model, batch, device)
             collective_note = ("nq_tp_allreduce_bf16 (peer-memory loads over NVLink, float32 sum in rank order) of "
                                "[batch, 8192] BF16 after o_proj and down_proj")
         except Exception as error:
@@ -1120,6 +1118,18 @@ def tp_decode(torch, dist, device, rank: int, world: int, *, layers: int, batch:
             collective_note += f"; peer-memory collective unavailable ({type(error).__name__}: {error})"[:200]
     graph = capture()
     ms_step = timed(runner)
+    if reducer is not None:
+        # a bounded wait of the peer-memory collective that gave up on any rank voids the run: NCCL takes over
+        broken = torch.tensor([reducer.status()], device=device)
+        dist.all_reduce(broken, op=dist.ReduceOp.MAX)
+        if int(broken.item()) != 0:
+            collective_note = (f"NCCL all_reduce(sum) of [batch, 8192] BF16 (the peer-memory collective reported "
+                               f"status {int(broken.item())} and was dropped)")
+            reducer = None
+            for module in row_modules:
+                module.peer_all_reduce = None
+            graph = capture()
+            ms_step = timed(runner)
     tokens = runner.next_tokens.clone()
     same = torch.tensor([1], device=device)
     if world > 1:
@@ -1294,10 +1304,10 @@ def main() -> None:
     parser.add_argument("--tp-context", type=int, default=4096)
     parser.add_argument("--shape", choices=[name for name, _, _ in SHAPES], default=None,
                         help="with --workload gemv: only this projection shape (short profiling runs)")
-    parser.add_argument("--tp-collective", choices=("peer", "nccl"), default="nccl",
-                        help="tensor-parallel sum after o_proj / down_proj: NCCL, or this repository's peer-memory "
-                             "kernel (falls back to NCCL when symmetric memory is unavailable); the other one is "
-                             "timed too and reported under all_reduce.other_collective")
+    parser.add_argument("--tp-collective", choices=("peer", "nccl"), default="peer",
+                        help="tensor-parallel sum after o_proj / down_proj: this repository's peer-memory kernel "
+                             "(falls back to NCCL when symmetric memory is unavailable or a wait gives up) or NCCL; "
+                             "the other one is timed too and reported under all_reduce.other_collective")
     parser.add_argument("--tp-resident", action="store_true",
                         help="tp70b: also time the opt-in mode that keeps the decoded BF16 weights of the shard in HBM")
     parser.add_argument("--kernel-mix", action="store_true",

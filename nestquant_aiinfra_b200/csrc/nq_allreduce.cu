@@ -113,6 +113,85 @@ __global__ void __launch_bounds__(kArThreads) nq_tp_allreduce_kernel(const ArPar
     }
 }
 
+// Two-shot form for four ranks and more: a rank first sums ITS slice (1 / world of the values) of all partials
+// and writes the rounded result back into its own partial buffer (nobody else reads that slice in this phase),
+// then every rank copies the other ranks' finished slices.  Per rank 2 * (world - 1) / world of the buffer
+// crosses NVLink instead of world - 1 buffers; the price is a third flag round between the two phases, for
+// which every CTA of the launch has to be resident (the grid is at most one CTA per SM, and a CTA only ever
+// waits for flags that CTAs which have already started will set).  Flag words 20..27: "rank r has reduced its
+// slice of call e"; word 19: CTA ticket of the first phase.  Same sums in the same order as the one-shot form.
+__global__ void __launch_bounds__(kArThreads) nq_tp_allreduce_two_shot_kernel(const ArParams p) {
+    uint32_t* mine = p.pad[p.rank];
+    __shared__ int s_last;
+    const uint32_t e = *reinterpret_cast<volatile uint32_t*>(mine + 16) + 1u;
+    const bool broken = *reinterpret_cast<volatile uint32_t*>(mine + 18) != 0u;
+    if (blockIdx.x == 0 && threadIdx.x < p.world) {
+        __threadfence_system();
+        st_release_sys(p.pad[threadIdx.x] + p.rank, e);
+    }
+    if (threadIdx.x == 0 && !broken && !wait_all(mine, p.world, e)) atomicCAS(mine + 18, 0u, 1u);
+    __syncthreads();
+
+    // phase 1: my slice of every partial -> reduced, into my own buffer (peers fetch it in phase 2) and into out
+    const int64_t slice = p.vecs / p.world, begin = slice * p.rank;
+    uint4* my_partial = const_cast<uint4*>(p.partial[p.rank]);
+    for (int64_t i = (int64_t)blockIdx.x * kArThreads + threadIdx.x; i < slice; i += (int64_t)gridDim.x * kArThreads) {
+        uint4 v[kMaxRanks];
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; ++r)
+            if (r < p.world) v[r] = ld_volatile_16(p.partial[r] + begin + i);
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; ++r) {
+            if (r < p.world) {
+                float f[8];
+                nq_unpack_bf16x8(v[r], f);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[j] += f[j];
+            }
+        }
+        const uint4 packed = nq_pack_bf16x8(acc);
+        my_partial[begin + i] = packed;
+        p.out[begin + i] = packed;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence_system();  // the reduced slice before the flag
+        s_last = atomicAdd(mine + 19, 1u) == gridDim.x - 1 ? 1 : 0;
+    }
+    __syncthreads();
+    if (s_last && threadIdx.x < p.world) st_release_sys(p.pad[threadIdx.x] + 20 + p.rank, e);
+    if (s_last && threadIdx.x == 0) mine[19] = 0u;
+    if (threadIdx.x == 0 && !broken && !wait_all(mine + 20, p.world, e)) atomicCAS(mine + 18, 0u, 3u);
+    __syncthreads();
+
+    // phase 2: the other ranks' reduced slices
+    const int64_t others = slice * (p.world - 1);
+    for (int64_t i = (int64_t)blockIdx.x * kArThreads + threadIdx.x; i < others; i += (int64_t)gridDim.x * kArThreads) {
+        const int hop = (int)(i / slice);                      // 0 .. world - 2
+        const int src = (p.rank + 1 + hop) % p.world;          // every rank starts with another peer
+        const int64_t at = slice * src + (i - (int64_t)hop * slice);
+        p.out[at] = ld_volatile_16(p.partial[src] + at);
+    }
+
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        s_last = atomicAdd(mine + 17, 1u) == gridDim.x - 1 ? 1 : 0;
+    }
+    __syncthreads();
+    if (s_last) {
+        if (threadIdx.x < p.world) st_release_sys(p.pad[threadIdx.x] + 8 + p.rank, e);
+        if (threadIdx.x == 0) {
+            if (!broken && !wait_all(mine + 8, p.world, e)) atomicCAS(mine + 18, 0u, 2u);
+            mine[17] = 0u;
+            *reinterpret_cast<volatile uint32_t*>(mine + 16) = e;
+        }
+    }
+}
+
 }  // namespace
 
 extern "C" int nq_tp_allreduce_bf16(const void* const* partials_host, void* const* pads_host, int rank, int world,
@@ -141,7 +220,14 @@ extern "C" int nq_tp_allreduce_bf16(const void* const* partials_host, void* cons
     const int64_t wanted = (p.vecs + kArThreads - 1) / kArThreads;
     const int sms = nq_sm_count();
     const unsigned grid = (unsigned)(wanted < sms ? wanted : sms);
-    nq_tp_allreduce_kernel<<<grid, kArThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);
+    if (world >= 4 && p.vecs % world == 0) {
+        // the two-shot kernel waits between its phases: never more CTAs than can be resident at once
+        const int64_t per_phase = (p.vecs / world * (world - 1) + kArThreads - 1) / kArThreads;
+        const unsigned two_shot_grid = (unsigned)(per_phase < sms ? per_phase : sms);
+        nq_tp_allreduce_two_shot_kernel<<<two_shot_grid, kArThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);
+    } else {
+        nq_tp_allreduce_kernel<<<grid, kArThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);
+    }
     NQ_CHECK_LAUNCH("nq_tp_allreduce_bf16");
     return NQ_OK;
 }

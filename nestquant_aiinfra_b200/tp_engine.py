@@ -122,6 +122,23 @@ def build_llama_tp_shard(*, hidden_size: int, intermediate_size: int, num_layers
 
 
 @torch.no_grad()
+def attach_peer_all_reduce(model: torch.nn.Module, max_rows: int, device: torch.device | str, process_group=None):
+    """Give every row-parallel projection of ``model`` the peer-memory sum (``tensor_parallel.PeerAllReduce``) in place
+    of the NCCL all-reduce; ``max_rows`` is the largest number of token rows a call will carry.  Returns the reducer
+    (its ``status()`` is non-zero when a bounded wait gave up); raises when symmetric memory cannot be set up, in
+    which case the modules keep NCCL."""
+    from .tensor_parallel import PeerAllReduce
+
+    rows = [m for m in model.modules() if isinstance(m, RowParallelNQRTLinear)]
+    if not rows:
+        raise ValueError("model has no row-parallel projections")
+    width = max(m.out_features for m in rows)
+    reducer = PeerAllReduce(int(max_rows) * width, torch.device(device), process_group)
+    for module in rows:
+        module.peer_all_reduce = reducer
+    return reducer
+
+
 def fill_cache_synthetic(cache: BatchedNQKVLlamaCache, context: int, *, seed: int = 4096) -> None:
     """Fill every slot with ``context`` tokens of seeded synthetic K/V through the page encoder.
 

@@ -196,11 +196,14 @@ def _peer_worker(rank: int, world: int, port: int, out_dir: str) -> None:
         dist.destroy_process_group()
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_peer_memory_all_reduce_two_ranks(tmp_path):
-    """nq_tp_allreduce_bf16 over symmetric memory: exact sums, graph replay, and the projection end to end."""
+@pytest.mark.parametrize("world", [2, 4])
+def test_peer_memory_all_reduce(tmp_path, world):
+    """nq_tp_allreduce_bf16 over symmetric memory: exact sums, graph replay, and the projection end to end
+    (two ranks: the one-shot kernel; four ranks: the two-shot kernel)."""
     import torch.multiprocessing as mp
 
-    mp.spawn(_peer_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
-    a, b = np.load(tmp_path / "peer0.npy"), np.load(tmp_path / "peer1.npy")
-    assert np.array_equal(a, b)
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    mp.spawn(_peer_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    outputs = [np.load(tmp_path / f"peer{r}.npy") for r in range(world)]
+    assert all(np.array_equal(outputs[0], other) for other in outputs[1:])
