@@ -170,7 +170,13 @@ __global__ void __launch_bounds__(kAttnThreads, (G <= 4 ? 4 : 3)) nq_attn_paged_
     constexpr size_t kTableBytes = LAT ? 0 : sizeof(NqLutShared);
     constexpr size_t kQueryBytes = sizeof(float) * G * D;
     constexpr size_t kProbBytes = sizeof(float) * CH * kAttnThreads * G;
-    constexpr size_t kLoopBytes = kTableBytes + kQueryBytes + kProbBytes;
+    // per-step values that pass 2 reads once per (block, step pair): in shared memory when it fits (indexed by a
+    // run-time step there, a chain of selects on the busiest pipe otherwise), every thread its own column
+    constexpr size_t kStateBytes = (size_t)CH * kAttnThreads * (sizeof(int64_t) + sizeof(Ids) + sizeof(float)) + 32;
+    // (measured: pays for four steps per chunk on packed pages, 268 -> 258 us; with two steps per chunk or on the
+    // cheap lattice pages the extra shared-memory reads cost more than the selects)
+    constexpr bool kStateInShared = !LAT && CH == 4 && kTableBytes + kQueryBytes + kProbBytes + kStateBytes <= 48 * 1024;
+    constexpr size_t kLoopBytes = kTableBytes + kQueryBytes + kProbBytes + (kStateInShared ? kStateBytes : 0);
     constexpr size_t kSharedBytes = kMergeBytes > kLoopBytes ? kMergeBytes : kLoopBytes;
     static_assert(kTableBytes % 16 == 0 && kQueryBytes % 16 == 0, "shared-memory regions must stay 16-byte aligned");
     __shared__ __align__(16) unsigned char s_raw[kSharedBytes];
@@ -179,6 +185,13 @@ __global__ void __launch_bounds__(kAttnThreads, (G <= 4 ? 4 : 3)) nq_attn_paged_
     float* s_q = reinterpret_cast<float*>(s_raw + kTableBytes);
     // scores, then probabilities, of my token of each step
     float (*s_prob)[kAttnThreads][G] = reinterpret_cast<float (*)[kAttnThreads][G]>(s_raw + kTableBytes + kQueryBytes);
+    unsigned char* s_state = s_raw + kTableBytes + kQueryBytes + kProbBytes;
+    int64_t (*s_row)[kAttnThreads] = reinterpret_cast<int64_t (*)[kAttnThreads]>(s_state);
+    Ids (*s_vid)[kAttnThreads] = reinterpret_cast<Ids (*)[kAttnThreads]>(s_state + (size_t)CH * kAttnThreads * sizeof(int64_t));
+    float (*s_vds)[kAttnThreads] = reinterpret_cast<float (*)[kAttnThreads]>(
+        s_state + (size_t)CH * kAttnThreads * (sizeof(int64_t) + sizeof(Ids)));
+    float* s_vbeta = reinterpret_cast<float*>(s_state + (size_t)CH * kAttnThreads * (sizeof(int64_t) + sizeof(Ids) + sizeof(float)));
+    (void)s_row; (void)s_vid; (void)s_vds; (void)s_vbeta;
 
     const int qi = blockIdx.x / p.kv_heads, h = blockIdx.x - qi * p.kv_heads;
     const int split = blockIdx.y;
@@ -239,6 +252,11 @@ __global__ void __launch_bounds__(kAttnThreads, (G <= 4 ? 4 : 3)) nq_attn_paged_
             kbeta[i] = __ldg(p.key_beta_table + i);
             vbeta[i] = __ldg(p.value_beta_table + i);
         }
+        if constexpr (kStateInShared) {
+            // every thread writes the same four values: no ordering needed beyond the warp's own
+            if (lane < 4) s_vbeta[lane] = __ldg(p.value_beta_table + lane);
+            __syncwarp();
+        }
         for (int st0 = warp; st0 < steps; st0 += kAttnWarps * CH) {
             // ---- where is my token of each step?  (all loads of the chunk's bookkeeping go out together) ----
             int64_t row[CH];       // row of the pool (cold) or of the hot tail
@@ -294,6 +312,11 @@ __global__ void __launch_bounds__(kAttnThreads, (G <= 4 ? 4 : 3)) nq_attn_paged_
             for (int c = 0; c < CH; ++c) {
                 kds[c] = nq_div_by(kds[c], p.sqrt_dim, p.inv_sqrt_dim);
                 vds[c] = nq_div_by(vds[c], p.sqrt_dim, p.inv_sqrt_dim);
+                if constexpr (kStateInShared) {
+                    s_row[c][threadIdx.x] = row[c];
+                    s_vid[c][threadIdx.x] = vid[c];
+                    s_vds[c][threadIdx.x] = vds[c];
+                }
             }
             // The step loops below stay rolled (ONE copy of the block decode per pass: laid out once per
             // step the kernel text no longer fits the instruction cache), so the per-step values are
@@ -418,7 +441,14 @@ __global__ void __launch_bounds__(kAttnThreads, (G <= 4 ? 4 : 3)) nq_attn_paged_
                     if (!((any_mask >> c) & 3u)) continue;  // warp-uniform: neither step has a token
                     const bool valid0 = (valid_mask >> c) & 1u, valid1 = (valid_mask >> (c + 1)) & 1u;
                     const bool cold0 = valid0 && !((hot_mask >> c) & 1u), cold1 = valid1 && !((hot_mask >> (c + 1)) & 1u);
-                    const int64_t row0 = pick_step(row, c), row1 = pick_step(row, c + 1);
+                    int64_t row0, row1;
+                    if constexpr (kStateInShared) {
+                        row0 = s_row[c][threadIdx.x];
+                        row1 = s_row[c + 1][threadIdx.x];
+                    } else {
+                        row0 = pick_step(row, c);
+                        row1 = pick_step(row, c + 1);
+                    }
                     float vv0[8], vv1[8], vsc0 = 0.0f, vsc1 = 0.0f;
                     if constexpr (LAT) {
                         const uint2 z = make_uint2(0, 0);
@@ -436,12 +466,18 @@ __global__ void __launch_bounds__(kAttnThreads, (G <= 4 ? 4 : 3)) nq_attn_paged_
                         nq_lut_finish(b0, ic0, vv0);
                         nq_lut_finish(b1, ic1, vv1);
                     }
-                    if (cold0) vsc0 = pick_step(vbeta, (int)((pick_step(vid, c) >> (2 * b)) & 3)) * pick_step(vds, c);
+                    if (cold0) {
+                        if constexpr (kStateInShared) vsc0 = s_vbeta[(int)((s_vid[c][threadIdx.x] >> (2 * b)) & 3)] * s_vds[c][threadIdx.x];
+                        else vsc0 = pick_step(vbeta, (int)((pick_step(vid, c) >> (2 * b)) & 3)) * pick_step(vds, c);
+                    }
                     else if (valid0) {
                         nq_load8<__nv_bfloat16>(reinterpret_cast<const __nv_bfloat16*>(p.hot_values) + row0 * D + b * 8, vv0);
                         vsc0 = 1.0f;
                     }
-                    if (cold1) vsc1 = pick_step(vbeta, (int)((pick_step(vid, c + 1) >> (2 * b)) & 3)) * pick_step(vds, c + 1);
+                    if (cold1) {
+                        if constexpr (kStateInShared) vsc1 = s_vbeta[(int)((s_vid[c + 1][threadIdx.x] >> (2 * b)) & 3)] * s_vds[c + 1][threadIdx.x];
+                        else vsc1 = pick_step(vbeta, (int)((pick_step(vid, c + 1) >> (2 * b)) & 3)) * pick_step(vds, c + 1);
+                    }
                     else if (valid1) {
                         nq_load8<__nv_bfloat16>(reinterpret_cast<const __nv_bfloat16*>(p.hot_values) + row1 * D + b * 8, vv1);
                         vsc1 = 1.0f;
