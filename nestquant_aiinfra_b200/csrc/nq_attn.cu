@@ -157,29 +157,43 @@ __device__ __forceinline__ typename RowIds<BPR>::type load_row_ids(const uint8_t
 //           products p * v; ONE recursive-halving reduction per block and chunk then leaves each lane with the
 //           chunk's total of one output feature, which it adds to its running output.
 // K/V blocks are decoded once for all query heads of the GQA group.
+// Compile-time layout of one instantiation: steps per chunk and the shared-memory regions
+// [decode table of the packed pages | scaled query | scores / probabilities | per-step values]; the merge buffer of
+// the epilogue reuses the same storage once every warp has left the page loop.
+template <int G, int BPR, bool LAT>
+struct AttnLayout {
+    using Ids = typename RowIds<BPR>::type;
+    static constexpr int D = BPR * 8;
+    // steps per chunk; four for the widest GQA group too were measured no faster (651 against 656 us on the 70B
+    // shard shape, slower with one KV head per rank)
+    static constexpr int CH = G <= 4 ? 4 : 2;
+    static constexpr size_t kMergeBytes = sizeof(float) * kAttnWarps * G * (D + 2);
+    static constexpr size_t kTableBytes = LAT ? 0 : sizeof(NqLutShared);
+    static constexpr size_t kQueryBytes = sizeof(float) * G * D;
+    static constexpr size_t kProbBytes = sizeof(float) * CH * kAttnThreads * G;
+    // per-step values that pass 2 reads once per (block, step pair): in shared memory (indexed by a run-time step
+    // there, a chain of selects on the busiest pipe otherwise), every thread its own column.  Measured: pays for
+    // four steps per chunk on packed pages (268 -> 258 us); with two steps per chunk or on the cheap lattice pages
+    // the extra shared-memory reads cost more than the selects.
+    static constexpr size_t kStateBytes = (size_t)CH * kAttnThreads * (sizeof(int64_t) + sizeof(Ids) + sizeof(float)) + 32;
+    static constexpr bool kStateInShared = !LAT && CH == 4;
+    static constexpr size_t kLoopBytes = kTableBytes + kQueryBytes + kProbBytes + (kStateInShared ? kStateBytes : 0);
+    static constexpr size_t kSharedBytes = kMergeBytes > kLoopBytes ? kMergeBytes : kLoopBytes;
+    static_assert(kTableBytes % 16 == 0 && kQueryBytes % 16 == 0 && kProbBytes % 16 == 0,
+                  "shared-memory regions must stay 16-byte aligned");
+};
+
 template <int G, int BPR, bool LAT>
 __global__ void __launch_bounds__(kAttnThreads, (G <= 4 ? 4 : 3)) nq_attn_paged_kernel(const AttnParams p) {
+    using Layout = AttnLayout<G, BPR, LAT>;
+    using Ids = typename Layout::Ids;
     constexpr int D = BPR * 8;
     constexpr int NV = G * 8;                      // products of one V block
     constexpr int NVL = NV >= 32 ? NV / 32 : 1;    // totals a lane owns after the reduction
-    constexpr int CH = G <= 4 ? 4 : 2;             // steps per chunk (bounded by the registers of p[CH][G])
-    using Ids = typename RowIds<BPR>::type;
-    // Shared memory: [decode table of the packed pages | scaled query | scores / probabilities]; the merge
-    // buffer of the epilogue reuses the same storage once every warp has left the page loop.
-    constexpr size_t kMergeBytes = sizeof(float) * kAttnWarps * G * (D + 2);
-    constexpr size_t kTableBytes = LAT ? 0 : sizeof(NqLutShared);
-    constexpr size_t kQueryBytes = sizeof(float) * G * D;
-    constexpr size_t kProbBytes = sizeof(float) * CH * kAttnThreads * G;
-    // per-step values that pass 2 reads once per (block, step pair): in shared memory when it fits (indexed by a
-    // run-time step there, a chain of selects on the busiest pipe otherwise), every thread its own column
-    constexpr size_t kStateBytes = (size_t)CH * kAttnThreads * (sizeof(int64_t) + sizeof(Ids) + sizeof(float)) + 32;
-    // (measured: pays for four steps per chunk on packed pages, 268 -> 258 us; with two steps per chunk or on the
-    // cheap lattice pages the extra shared-memory reads cost more than the selects)
-    constexpr bool kStateInShared = !LAT && CH == 4 && kTableBytes + kQueryBytes + kProbBytes + kStateBytes <= 48 * 1024;
-    constexpr size_t kLoopBytes = kTableBytes + kQueryBytes + kProbBytes + (kStateInShared ? kStateBytes : 0);
-    constexpr size_t kSharedBytes = kMergeBytes > kLoopBytes ? kMergeBytes : kLoopBytes;
-    static_assert(kTableBytes % 16 == 0 && kQueryBytes % 16 == 0, "shared-memory regions must stay 16-byte aligned");
-    __shared__ __align__(16) unsigned char s_raw[kSharedBytes];
+    constexpr int CH = Layout::CH;
+    constexpr size_t kTableBytes = Layout::kTableBytes, kQueryBytes = Layout::kQueryBytes, kProbBytes = Layout::kProbBytes;
+    constexpr bool kStateInShared = Layout::kStateInShared;
+    extern __shared__ __align__(16) unsigned char s_raw[];  // Layout::kSharedBytes
     float (*s_merge)[G][D + 2] = reinterpret_cast<float (*)[G][D + 2]>(s_raw);
     const NqLutShared* lut = reinterpret_cast<const NqLutShared*>(s_raw);
     float* s_q = reinterpret_cast<float*>(s_raw + kTableBytes);
@@ -584,17 +598,35 @@ __global__ void __launch_bounds__(128) nq_attn_reduce_kernel(const AttnParams p)
     }
 }
 
+// One instantiation: the opt-in to more than 48 KB of dynamic shared memory is a per-device attribute of the kernel.
+template <int G, int BPR, bool LAT>
+int launch_attn_one(const AttnParams& p, dim3 grid, cudaStream_t s) {
+    constexpr size_t bytes = AttnLayout<G, BPR, LAT>::kSharedBytes;
+    if (bytes > 48 * 1024) {
+        static bool configured[NQ_MAX_DEVICES] = {false};
+        const int device = nq_current_device();
+        if (device < 0 || !configured[device]) {
+            const cudaError_t e = cudaFuncSetAttribute(nq_attn_paged_kernel<G, BPR, LAT>,
+                                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+            if (e != cudaSuccess) {
+                nq_set_error("nq_kv_attention: cannot reserve %zu bytes of shared memory: %s", bytes, cudaGetErrorString(e));
+                return (int)e;
+            }
+            if (device >= 0) configured[device] = true;
+        }
+    }
+    nq_attn_paged_kernel<G, BPR, LAT><<<grid, kAttnThreads, bytes, s>>>(p);
+    return NQ_OK;
+}
+
 template <int G, bool LAT>
 int launch_attn_dim(const AttnParams& p, dim3 grid, cudaStream_t s) {
-    if (p.dim == 64) nq_attn_paged_kernel<G, 8, LAT><<<grid, kAttnThreads, 0, s>>>(p);
-    else if (p.dim == 128) nq_attn_paged_kernel<G, 16, LAT><<<grid, kAttnThreads, 0, s>>>(p);
-    else if (p.dim == 32) nq_attn_paged_kernel<G, 4, LAT><<<grid, kAttnThreads, 0, s>>>(p);
-    else if (p.dim == 256) nq_attn_paged_kernel<G, 32, LAT><<<grid, kAttnThreads, 0, s>>>(p);
-    else {
-        nq_set_error("nq_kv_attention: head_dim must be 32, 64, 128 or 256");
-        return NQ_ERR_ARG;
-    }
-    return NQ_OK;
+    if (p.dim == 64) return launch_attn_one<G, 8, LAT>(p, grid, s);
+    if (p.dim == 128) return launch_attn_one<G, 16, LAT>(p, grid, s);
+    if (p.dim == 32) return launch_attn_one<G, 4, LAT>(p, grid, s);
+    if (p.dim == 256) return launch_attn_one<G, 32, LAT>(p, grid, s);
+    nq_set_error("nq_kv_attention: head_dim must be 32, 64, 128 or 256");
+    return NQ_ERR_ARG;
 }
 
 template <int G>
