@@ -522,7 +522,8 @@ def run_gpu(args) -> None:
             "launch": "CUDA graph of one step, replayed" if graph is not None else "call by call",
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],
-                    "ms_per_step": e2e["ms"], "launch": e2e.get("launch"), "numa": e2e.get("numa"),
+                    "ms_per_step": e2e["ms"], "launch": e2e.get("launch"), "cell_order": e2e.get("cell_order"),
+                    "numa": e2e.get("numa"),
                     "result_on_host": e2e.get("nonzero_result")},
             "gpu_launches": int(launches),
             "roofline": roofline,
@@ -633,10 +634,47 @@ def bind_to_gpu_numa_node(torch, device) -> dict:
     return info
 
 
+def e2e_cell_order(torch, layers, device) -> list[tuple[int, int]]:
+    """Order of the 32 cells inside one end-to-end step.
+
+    A step is a three-stage flow shop -- copy in, module call, copy out, each stage serial on its own stream -- and
+    the copy in is the longest stage, so the order decides how long the other two trail behind it.  Every cell is
+    run once by itself (after a warm-up call) with CUDA events around its three stages; Johnson's rule on
+    (copy in, module call + copy out) then puts the cells that take longer to drain than to feed first, by
+    increasing copy-in time, and the others last, by decreasing drain time.  Nothing is skipped or merged: the
+    timed step still copies every input in and every output out.
+    """
+    stream = torch.cuda.current_stream(device)
+    measured = []
+    for si, (_name, n, k) in enumerate(SHAPES):
+        for m in TOKENS:
+            host_x = torch.randn(m, k).bfloat16().pin_memory()
+            host_y = torch.empty(m, n, dtype=torch.bfloat16).pin_memory()
+            dev_x = torch.empty(m, k, dtype=torch.bfloat16, device=device)
+            marks = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+            with torch.no_grad():
+                for attempt in range(2):  # the first pass loads kernels and sizes workspaces
+                    marks[0].record(stream)
+                    dev_x.copy_(host_x, non_blocking=True)
+                    marks[1].record(stream)
+                    y = layers[si](dev_x)
+                    marks[2].record(stream)
+                    host_y.copy_(y, non_blocking=True)
+                    marks[3].record(stream)
+                    torch.cuda.synchronize(device)
+            feed = marks[0].elapsed_time(marks[1])
+            drain = marks[1].elapsed_time(marks[3])
+            measured.append(((si, m), feed, drain))
+    first = sorted((c for c in measured if c[1] < c[2]), key=lambda c: c[1])
+    last = sorted((c for c in measured if c[1] >= c[2]), key=lambda c: -c[2])
+    return [c[0] for c in first + last]
+
+
 def run_e2e(torch, rt, FusedNQRTLinear, weights, device, steps: int, distributed: bool) -> dict:
     """The sweep through the plugin call (FusedNQRTLinear.forward) with pinned host inputs and outputs.
 
-    One pinned slab holds the inputs of all 32 cells and one the outputs.  A step copies every cell's input to the
+    One pinned slab holds the inputs of all 32 cells and one the outputs (in the order ``e2e_cell_order`` derives
+    from per-cell measurements).  A step copies every cell's input to the
     device, calls the module, and copies the result back; the three kinds of work run on three streams so that
     copies in both directions overlap the kernels.  The whole step -- 32 host-to-device copies, 32 module calls,
     32 device-to-host copies -- is captured once as a CUDA graph and the timed region replays it: every input
@@ -645,9 +683,7 @@ def run_e2e(torch, rt, FusedNQRTLinear, weights, device, steps: int, distributed
     """
     numa = bind_to_gpu_numa_node(torch, device)
     layers = [FusedNQRTLinear(w, input_hadamard=True, activation_betas=ACT_BETAS).to(device) for w in weights]
-    # large cells first: their copies overlap the rest of the step, the small ones form the tail
-    cells = sorted(((si, m) for si in range(len(SHAPES)) for m in TOKENS),
-                   key=lambda c: -c[1] * (SHAPES[c[0]][1] + SHAPES[c[0]][2]))
+    cells = e2e_cell_order(torch, layers, device)
     in_elems = [m * SHAPES[si][2] for si, m in cells]
     out_elems = [m * SHAPES[si][1] for si, m in cells]
     host_in = torch.empty(sum(in_elems), dtype=torch.bfloat16).pin_memory()
@@ -716,7 +752,9 @@ def run_e2e(torch, rt, FusedNQRTLinear, weights, device, steps: int, distributed
         torch.cuda.synchronize(device)
     checksum = float(host_out[:out_elems[0]].float().abs().sum())  # the largest cell's result really is on the host
     return {"ms": e0.elapsed_time(e1) / steps, "h2d": h2d, "d2h": d2h, "numa": numa, "nonzero_result": checksum > 0,
-            "launch": "CUDA graph of one step (copies and module calls), replayed" if graph is not None else "call by call"}
+            "launch": "CUDA graph of one step (copies and module calls), replayed" if graph is not None else "call by call",
+            "cell_order": "Johnson's rule on the measured (copy in, call + copy out) of every cell; first "
+                          + f"{SHAPES[cells[0][0]][0]} M={cells[0][1]}, last {SHAPES[cells[-1][0]][0]} M={cells[-1][1]}"}
 
 
 def gemv_workload(torch, rt, device, pk, only: str | None = None) -> dict:
