@@ -44,6 +44,7 @@ struct AttnParams {
     float sqrt_dim, inv_sqrt_dim;
     int splits;
     int per_slots;  // page slots (cold pages + hot tail) per split
+    int q_tiles;    // query tiles per batch row (a CTA of the tiled instantiations owns QT consecutive query tokens)
     float* partial;  // [B*Tq, Hq, splits, D + 2]
     void* out;       // [B, Tq, Hq, D]
     int out_dtype;
@@ -81,6 +82,37 @@ __device__ __forceinline__ bool resolve_query(const AttnParams& p, int qi, int& 
     }
     total_slots = page_count + (hot_len > 0 ? 1 : 0);
     return active && limit > 0;
+}
+
+// The same for a tile of QT consecutive query tokens of batch row b, first token i0.  `limit0` is the causal
+// limit of the first token (token i0 + r sees the first limit0 + r positions), `nrows` the number of tokens of
+// the tile that are queries at all, `limit` the limit of the last of them.  Returns false when no token of the
+// tile sees anything.
+template <int QT>
+__device__ __forceinline__ bool resolve_tile(const AttnParams& p, int b, int i0, int& slot, int& limit0, int& nrows,
+                                             int& limit, int& total_slots, int& page_count, int& last_len,
+                                             int& hot_len) {
+    const int requested = p.slot_ids[b];
+    const bool in_range = requested >= 0 && requested < p.max_sequences;
+    slot = min(max(requested, 0), p.max_sequences - 1);
+    bool active = in_range && p.cache_active[slot] != 0 && p.sequence_lengths[slot] > 0;
+    if (p.active_mask) active = active && p.active_mask[b] != 0;
+    page_count = min(max(p.page_counts[slot], 0), p.max_pages);
+    last_len = p.last_page_lens[slot];
+    hot_len = min(max(p.hot_lengths[slot], 0), p.page_size);
+    const int cold = page_count > 0 ? (page_count - 1) * p.page_size + last_len : 0;
+    const int total = cold + hot_len;
+    nrows = min(QT, p.q_tokens - i0);
+    limit0 = total;
+    if (p.q_lens) {
+        const int ql = p.q_lens[b];
+        nrows = min(nrows, ql - i0);
+        limit0 = total - ql + i0 + 1;
+    }
+    // without query lengths every token sees the whole context: one limit for all rows
+    limit = p.q_lens ? limit0 + nrows - 1 : total;
+    total_slots = page_count + (hot_len > 0 ? 1 : 0);
+    return active && nrows > 0 && limit > 0;
 }
 
 // Register budget: the exact E8 decode leaves issue slots idle at 12 warps per SM (168 registers), so the
@@ -183,8 +215,14 @@ struct AttnLayout {
                   "shared-memory regions must stay 16-byte aligned");
 };
 
-template <int G, int BPR, bool LAT>
+//
+// QT > 1 (chunk prefill): the G rows of the CTA are QT consecutive query tokens x G / QT query heads, row
+// r = token * (G / QT) + head.  A K/V block is then decoded once for all of them; query token r of the tile sees
+// the first limit0 + r positions, which is a per-row mask on the scores.
+template <int G, int BPR, bool LAT, int QT = 1>
 __global__ void __launch_bounds__(kAttnThreads, (G <= 4 ? 4 : 3)) nq_attn_paged_kernel(const AttnParams p) {
+    static_assert(G % QT == 0, "rows = query tokens x heads of the GQA group");
+    constexpr int GH = G / QT;  // query heads per KV head
     using Layout = AttnLayout<G, BPR, LAT>;
     using Ids = typename Layout::Ids;
     constexpr int D = BPR * 8;
@@ -207,29 +245,48 @@ __global__ void __launch_bounds__(kAttnThreads, (G <= 4 ? 4 : 3)) nq_attn_paged_
     float* s_vbeta = reinterpret_cast<float*>(s_state + (size_t)CH * kAttnThreads * (sizeof(int64_t) + sizeof(Ids) + sizeof(float)));
     (void)s_row; (void)s_vid; (void)s_vds; (void)s_vbeta;
 
-    const int qi = blockIdx.x / p.kv_heads, h = blockIdx.x - qi * p.kv_heads;
+    // qi: the (first) query token of this CTA, as an index into [B * Tq]
+    const int tile = blockIdx.x / p.kv_heads, h = blockIdx.x - tile * p.kv_heads;
     const int split = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-    int slot, limit, total_slots, page_count, last_len, hot_len;
-    const bool active = resolve_query(p, qi, slot, limit, total_slots, page_count, last_len, hot_len);
+    int qi, slot, limit, total_slots, page_count, last_len, hot_len;
+    int limit0 = 0, nrows = 1, rows_in_tensor = 1;  // of the tile
+    bool active;
+    if constexpr (QT == 1) {
+        qi = tile;
+        active = resolve_query(p, qi, slot, limit, total_slots, page_count, last_len, hot_len);
+    } else {
+        const int b = tile / p.q_tiles, i0 = (tile - b * p.q_tiles) * QT;
+        qi = b * p.q_tokens + i0;
+        rows_in_tensor = min(QT, p.q_tokens - i0);
+        active = resolve_tile<QT>(p, b, i0, slot, limit0, nrows, limit, total_slots, page_count, last_len, hot_len);
+    }
+    (void)limit0; (void)nrows; (void)rows_in_tensor;
     const int cold = page_count > 0 ? (page_count - 1) * p.page_size + last_len : 0;
+    // row r of the CTA -> row of the [B * Tq, Hq] output (only rows with r / GH < rows_in_tensor exist)
+    auto out_row = [&](int r) { return (int64_t)(qi + r / GH) * p.q_heads + h * GH + (r % GH); };
 
     // A split that starts past the sequence's end (or past the causal limit) has nothing to add: it leaves the
     // neutral partial and returns before the table is loaded.
     if (p.splits > 1 && !(active && split * p.per_slots < total_slots && split * p.per_slots * p.page_size < limit)) {
         for (int item = threadIdx.x; item < G * (D + 2); item += kAttnThreads) {
             const int g = item / (D + 2), f = item - g * (D + 2);
-            p.partial[(((int64_t)qi * p.q_heads + h * G + g) * p.splits + split) * (D + 2) + f] = f == D ? -INFINITY : 0.0f;
+            if (g / GH < rows_in_tensor) p.partial[(out_row(g) * p.splits + split) * (D + 2) + f] = f == D ? -INFINITY : 0.0f;
         }
         return;
     }
 
-    // the G query heads of this KV head are contiguous: [qi][h * G .. h * G + G)[D], pre-multiplied by scale * log2(e)
+    // the query heads of this KV head are contiguous per token: [qi + token][h * GH .. h * GH + GH)[D]; they are
+    // pre-multiplied by scale * log2(e)
     for (int i = threadIdx.x; i < G * D / 8; i += kAttnThreads) {
-        const int64_t qoff = ((int64_t)qi * p.q_heads + h * G) * D + i * 8;
+        const int r = (i * 8) / D;
+        const int64_t qoff = out_row(r) * D + (i * 8 - r * D);
         float v[8];
-        if (p.q_dtype == NQ_BF16) nq_load8<__nv_bfloat16>(reinterpret_cast<const __nv_bfloat16*>(p.query) + qoff, v);
+        if (r / GH >= rows_in_tensor) {  // a tile that reaches past the last query token
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = 0.0f;
+        } else if (p.q_dtype == NQ_BF16) nq_load8<__nv_bfloat16>(reinterpret_cast<const __nv_bfloat16*>(p.query) + qoff, v);
         else if (p.q_dtype == NQ_F16) nq_load8<__half>(reinterpret_cast<const __half*>(p.query) + qoff, v);
         else nq_load8<float>(reinterpret_cast<const float*>(p.query) + qoff, v);
 #pragma unroll
@@ -275,6 +332,7 @@ __global__ void __launch_bounds__(kAttnThreads, (G <= 4 ? 4 : 3)) nq_attn_paged_
             // ---- where is my token of each step?  (all loads of the chunk's bookkeeping go out together) ----
             int64_t row[CH];       // row of the pool (cold) or of the hot tail
             unsigned hot_mask = 0, valid_mask = 0, any_mask = 0;   // bit c: this lane's token of step c
+            unsigned first_rows = 0;  // QT > 1, four bits per step: the first query token of the tile that sees my token
             Ids kid[CH], vid[CH];
             float kds[CH], vds[CH];
 #pragma unroll
@@ -294,6 +352,7 @@ __global__ void __launch_bounds__(kAttnThreads, (G <= 4 ? 4 : 3)) nq_attn_paged_
                         const int tlimit = hot ? hot_len : (ps == page_count - 1 ? last_len : P);
                         const int base_token = hot ? cold : ps * P;
                         valid = t < tlimit && base_token + t < limit;
+                        if constexpr (QT > 1) first_rows |= (unsigned)min(max(base_token + t - limit0 + 1, 0), QT) << (4 * c);
                         if (valid && !hot) {
                             const int page_id = p.page_indices[(int64_t)slot * p.max_pages + ps];
                             valid = page_id >= 0 && page_id < p.pool_capacity;  // defensive: never read outside the pool
@@ -415,6 +474,13 @@ __global__ void __launch_bounds__(kAttnThreads, (G <= 4 ? 4 : 3)) nq_attn_paged_
                 float sv[CH];
 #pragma unroll
                 for (int c = 0; c < CH; ++c) sv[c] = s_prob[c][threadIdx.x][g];
+                if constexpr (QT > 1) {  // causal mask of this row's query token (rows past the chunk see nothing)
+#pragma unroll
+                    for (int c = 0; c < CH; ++c) {
+                        const int first = (int)((first_rows >> (4 * c)) & 15u);
+                        if (g / GH < first || g / GH >= nrows) sv[c] = -INFINITY;
+                    }
+                }
                 float cm = sv[0];
 #pragma unroll
                 for (int c = 1; c < CH; ++c) cm = fmaxf(cm, sv[c]);
@@ -432,7 +498,7 @@ __global__ void __launch_bounds__(kAttnThreads, (G <= 4 ? 4 : 3)) nq_attn_paged_
                 }
 #pragma unroll
                 for (int c = 0; c < CH; ++c) {
-                    const float pr = ((valid_mask >> c) & 1u) ? exp2f(sv[c] - m[g]) : 0.0f;
+                    const float pr = (((valid_mask >> c) & 1u) && (QT == 1 || sv[c] != -INFINITY)) ? exp2f(sv[c] - m[g]) : 0.0f;
                     s_prob[c][threadIdx.x][g] = pr;
                     l[g] += pr;
                 }
@@ -557,14 +623,14 @@ __global__ void __launch_bounds__(kAttnThreads, (G <= 4 ? 4 : 3)) nq_attn_paged_
 #pragma unroll
             for (int j = 0; j < 8; ++j) a[j] += s_merge[w][g][b8 * 8 + j] * c;
         }
-        const int head = h * G + g;
+        if (g / GH >= rows_in_tensor) continue;  // a tile that reaches past the last query token
         if (p.splits == 1) {
             const float inv = (active && ll > 0.0f) ? 1.0f / ll : 0.0f;
 #pragma unroll
             for (int j = 0; j < 8; ++j) a[j] *= inv;
-            store_out(p.out, p.out_dtype, ((int64_t)qi * p.q_heads + head) * BPR + b8, a);
+            store_out(p.out, p.out_dtype, out_row(g) * BPR + b8, a);
         } else {
-            float* dst = p.partial + (((int64_t)qi * p.q_heads + head) * p.splits + split) * (D + 2);
+            float* dst = p.partial + (out_row(g) * p.splits + split) * (D + 2);
 #pragma unroll
             for (int j = 0; j < 8; ++j) dst[b8 * 8 + j] = a[j];
             if (b8 == 0) {
@@ -599,14 +665,14 @@ __global__ void __launch_bounds__(128) nq_attn_reduce_kernel(const AttnParams p)
 }
 
 // One instantiation: the opt-in to more than 48 KB of dynamic shared memory is a per-device attribute of the kernel.
-template <int G, int BPR, bool LAT>
+template <int G, int BPR, bool LAT, int QT = 1>
 int launch_attn_one(const AttnParams& p, dim3 grid, cudaStream_t s) {
     constexpr size_t bytes = AttnLayout<G, BPR, LAT>::kSharedBytes;
     if (bytes > 48 * 1024) {
         static bool configured[NQ_MAX_DEVICES] = {false};
         const int device = nq_current_device();
         if (device < 0 || !configured[device]) {
-            const cudaError_t e = cudaFuncSetAttribute(nq_attn_paged_kernel<G, BPR, LAT>,
+            const cudaError_t e = cudaFuncSetAttribute(nq_attn_paged_kernel<G, BPR, LAT, QT>,
                                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
             if (e != cudaSuccess) {
                 nq_set_error("nq_kv_attention: cannot reserve %zu bytes of shared memory: %s", bytes, cudaGetErrorString(e));
@@ -615,7 +681,7 @@ int launch_attn_one(const AttnParams& p, dim3 grid, cudaStream_t s) {
             if (device >= 0) configured[device] = true;
         }
     }
-    nq_attn_paged_kernel<G, BPR, LAT><<<grid, kAttnThreads, bytes, s>>>(p);
+    nq_attn_paged_kernel<G, BPR, LAT, QT><<<grid, kAttnThreads, bytes, s>>>(p);
     return NQ_OK;
 }
 
@@ -632,6 +698,27 @@ int launch_attn_dim(const AttnParams& p, dim3 grid, cudaStream_t s) {
 template <int G>
 int launch_attn(const AttnParams& p, dim3 grid, cudaStream_t s) {
     return p.key_lattice ? launch_attn_dim<G, true>(p, grid, s) : launch_attn_dim<G, false>(p, grid, s);
+}
+
+// Chunk prefill: a CTA takes `tile` consecutive query tokens so that its eight rows (tile x heads of the GQA
+// group) share every decoded K/V block.  Built for the two common head sizes; everything else (and a group of
+// eight, which fills the rows by itself) runs one query token per CTA.
+constexpr int kTileRows = 8;
+int query_tile(int q_tokens, int group, int dim) {
+    return (q_tokens > 1 && group < kTileRows && (dim == 64 || dim == 128)) ? kTileRows / group : 1;
+}
+
+template <int BPR, bool LAT>
+int launch_attn_tiled_dim(const AttnParams& p, dim3 grid, cudaStream_t s, int tile) {
+    if (tile == 2) return launch_attn_one<kTileRows, BPR, LAT, 2>(p, grid, s);
+    if (tile == 4) return launch_attn_one<kTileRows, BPR, LAT, 4>(p, grid, s);
+    return launch_attn_one<kTileRows, BPR, LAT, 8>(p, grid, s);
+}
+
+int launch_attn_tiled(const AttnParams& p, dim3 grid, cudaStream_t s, int tile) {
+    if (p.dim == 64)
+        return p.key_lattice ? launch_attn_tiled_dim<8, true>(p, grid, s, tile) : launch_attn_tiled_dim<8, false>(p, grid, s, tile);
+    return p.key_lattice ? launch_attn_tiled_dim<16, true>(p, grid, s, tile) : launch_attn_tiled_dim<16, false>(p, grid, s, tile);
 }
 
 // Page-range splits per (query token, KV head).  Every CTA of a launch owns the SAME number of page slots
@@ -679,7 +766,10 @@ SplitPlan plan_splits(int queries, int kv_heads, int max_pages, int group) {
 extern "C" size_t nq_kv_attention_workspace_bytes(int batch, int q_tokens, int q_heads, int kv_heads, int dim,
                                                   int max_pages) {
     if (batch < 1 || q_tokens < 1 || q_heads < 1 || kv_heads < 1) return 0;
-    const int splits = plan_splits(batch * q_tokens, kv_heads, max_pages, q_heads / kv_heads).splits;
+    const int group = q_heads / kv_heads;
+    const int tile = query_tile(q_tokens, group, dim);
+    const int splits = plan_splits(batch * ((q_tokens + tile - 1) / tile), kv_heads, max_pages,
+                                   tile > 1 ? kTileRows : group).splits;
     return (size_t)batch * q_tokens * q_heads * splits * (dim + 2) * sizeof(float) + 256;
 }
 
@@ -725,7 +815,10 @@ static int kv_attention_impl(const void* query, int q_dtype, int batch, int q_to
     p.scale_log2e = scale * 1.4426950408889634f;
     p.sqrt_dim = (float)sqrt((double)dim);
     p.inv_sqrt_dim = 1.0f / p.sqrt_dim;
-    const SplitPlan plan = plan_splits(batch * q_tokens, kv_heads, max_pages, group);  // same with or without the shadow: same sums
+    const int tile = query_tile(q_tokens, group, dim);
+    p.q_tiles = (q_tokens + tile - 1) / tile;
+    // same with or without the shadow: same sums
+    const SplitPlan plan = plan_splits(batch * p.q_tiles, kv_heads, max_pages, tile > 1 ? kTileRows : group);
     p.splits = plan.splits;
     p.per_slots = plan.per_slots;
     p.out = out; p.out_dtype = out_dtype;
@@ -740,9 +833,10 @@ static int kv_attention_impl(const void* query, int q_dtype, int batch, int q_to
         const cudaError_t err = nq_lut_ensure(s);
         NQ_REQUIRE(err == cudaSuccess, (int)err, "nq_kv_attention: decode table: %s", cudaGetErrorString(err));
     }
-    dim3 grid((unsigned)(batch * q_tokens * kv_heads), (unsigned)p.splits);
+    dim3 grid((unsigned)(batch * p.q_tiles * kv_heads), (unsigned)p.splits);
     int rc;
-    switch (group) {
+    if (tile > 1) rc = launch_attn_tiled(p, grid, s, tile);
+    else switch (group) {
         case 1: rc = launch_attn<1>(p, grid, s); break;
         case 2: rc = launch_attn<2>(p, grid, s); break;
         case 4: rc = launch_attn<4>(p, grid, s); break;

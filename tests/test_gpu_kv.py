@@ -240,6 +240,28 @@ def test_prefill_attention_ragged_chunks_cross_pages(rt, oracle):
     _check_attention(actual, expected)
 
 
+@pytest.mark.parametrize("heads,dim,q_heads,q_tokens", [(2, 64, 8, 13), (2, 64, 4, 13), (2, 64, 2, 21),
+                                                        (2, 128, 8, 13), (1, 128, 2, 10), (1, 128, 1, 19)])
+def test_prefill_attention_query_tiles(rt, oracle, heads, dim, q_heads, q_tokens):
+    """Chunk prefill with several query tokens per CTA (2, 4 or 8 by GQA group, both tiled head sizes): chunks
+    that end inside a tile, a chunk of one token, an inactive row, query counts that are no multiple of the tile."""
+    lengths = [40, 16, 75, 5, 300]
+    cache = make_cache(rt, slots=5, max_pages=20, heads=heads, dim=dim)
+    fill_cache(rt, cache, lengths, seed=90 + dim + q_heads)
+    q_lens = torch.tensor([9, 1, q_tokens, 5, 0], dtype=torch.int32, device="cuda")
+    slot_ids = torch.arange(5, dtype=torch.int32, device="cuda")
+    q = torch.randn(5, q_tokens, q_heads, dim, generator=rng(91)).bfloat16()
+    scale = dim ** -0.5
+    ws = rt.BatchedNQKVAttentionWorkspace.create(cache, batch_size=5, query_heads=q_heads, output_dtype=torch.float32,
+                                                 query_tokens=q_tokens)
+    out = rt.nqkv_prefill_attention(q.cuda(), cache, slot_ids=slot_ids, query_lengths=q_lens, scale=scale, workspace=ws)
+    expected = oracle.attn_prefill(q.float().numpy(), [0, 1, 2, 3, 4], q_lens.cpu().numpy(), rt.cache_arrays(cache),
+                                   scale=scale)
+    actual = out.cpu().numpy()
+    assert not actual[0, 9:].any() and not actual[1, 1:].any() and not actual[4].any()
+    _check_attention(actual, expected)
+
+
 def test_written_pages_round_trip_through_attention(rt, oracle):
     """append -> pack/publish -> attention: the whole write path feeds the read path."""
     cache = make_cache(rt, slots=2, max_pages=4, heads=2)
