@@ -26,7 +26,7 @@ from torch import nn
 
 from .formats import ACTIVATION_BETAS, KEY_BETAS, VALUE_BETAS, WEIGHT_BETAS, tensor_dither_seed
 from .fused_linear import (FusedNQRTLinear, SharedHadamardCache, SharedPackedActivationCache,
-                           SharedProjectionGroup, keep_decoded_weights_)
+                           SharedProjectionGroup, WeightDecodeAhead, keep_decoded_weights_)
 from .hf_backend import BatchedNQKVLlamaCache, install_batched_nqkv_llama_backend
 from .norm import fuse_rmsnorm_, fuse_silu_mlp_
 from .rope import fused_rope_scope
@@ -122,7 +122,7 @@ class BatchedNQKVLlamaRunner:
     """Greedy ragged prefill + fixed-width graph decode over a ``BatchedNQKVLlamaCache``."""
 
     def __init__(self, model: nn.Module, cache: BatchedNQKVLlamaCache, *, execution_policy: str = "full",
-                 prefill_logits: str = "last") -> None:
+                 prefill_logits: str = "last", weight_decode_ahead: bool = True) -> None:
         if not isinstance(model, nn.Module):
             raise TypeError("model must be a torch module")
         if not isinstance(cache, BatchedNQKVLlamaCache):
@@ -134,6 +134,10 @@ class BatchedNQKVLlamaRunner:
         self.model, self.cache = model, cache
         self.device = cache.device
         self.execution_policy = execution_policy
+        # Captured decode steps of at least eight rows decode the weights a layer needs after its attention on a
+        # second stream while the attention runs (``enable_weight_decode_ahead``; bit-identical results, one
+        # layer's decoded weights of scratch).  False keeps every step on one stream.
+        self.weight_decode_ahead = bool(weight_decode_ahead)
         # "last": prefill_slots evaluates the lm_head at the last prompt token of every row only and returns a
         # [capacity, width, vocab] VIEW whose columns all alias that row's logits (no memory), which is what a
         # sampler reads; "all" materialises the logits of every position as the reference does.
@@ -280,6 +284,7 @@ class BatchedNQKVLlamaRunner:
         self.positions.copy_(positions)
         self.cache.active_mask.copy_(active_mask[:, 0])
         self.cache.set_decode_state()
+        self._ensure_decode_ahead()
         vocab = self.model.config.vocab_size
         dtype = next(self.model.parameters()).dtype
         self.logits = torch.zeros((self.batch_size, 1, vocab), device=self.device, dtype=dtype)
@@ -391,6 +396,7 @@ class BatchedNQKVLlamaRunner:
     def capture_decode_graph(self) -> None:
         """Capture one fixed-width decode step (all ``capacity`` rows, inactive rows masked on the device)."""
         self.cache.set_decode_state()
+        self._ensure_decode_ahead()
         state = self._snapshot()
         side = torch.cuda.Stream(self.device)
         side.wait_stream(torch.cuda.current_stream(self.device))
@@ -424,10 +430,48 @@ class BatchedNQKVLlamaRunner:
         self.graph.replay()
         return self.next_tokens
 
+    def enable_weight_decode_ahead(self) -> int:
+        """Decode the weights of ``o_proj``, gate / up and ``down_proj`` of a layer on a second stream while the
+        layer's paged attention runs (``fused_linear.WeightDecodeAhead``): same kernels, same results, the idle
+        tail of the attention filled.  Costs one layer's decoded weights of scratch (returned, in bytes) and takes
+        effect for decode steps of at least eight rows; a captured decode graph is captured again."""
+        self.weight_decode_ahead = True
+        if self.cache.decode_ahead is not None:
+            return 0
+        self._ensure_decode_ahead()
+        self._recapture()
+        return 0 if self.cache.decode_ahead is None else self.cache.decode_ahead.scratch_bytes
+
+    def disable_weight_decode_ahead(self) -> None:
+        self.weight_decode_ahead = False
+        if self.cache.decode_ahead is None:
+            return
+        self.cache.decode_ahead.detach()
+        self.cache.decode_ahead = None
+        self._recapture()
+
+    def _ensure_decode_ahead(self) -> None:
+        if not self.weight_decode_ahead or self.cache.decode_ahead is not None:
+            return
+        if self.batch_size < WeightDecodeAhead.MIN_ROWS:
+            return
+        ahead = WeightDecodeAhead(self.model.model.layers, self.device)
+        if any(ahead.layers):
+            self.cache.decode_ahead = ahead
+
+    def _recapture(self) -> None:
+        # (a logits graph of the engine protocol keeps replaying the mode it was captured in)
+        if self.graph is not None:
+            self.capture_decode_graph()
+
     # Opt-in modes that spend spare HBM on decoded copies (off by default; the packed data stay the record).
     # Both change which kernels a step launches, so a captured graph is captured again.
     def keep_decoded_weights(self) -> int:
         """Keep the decoded BF16 weights of every packed projection resident; returns the bytes added."""
+        ahead = self.cache.decode_ahead is not None
+        if ahead:  # nothing is left to decode ahead: the units would point at weights that are replaced now
+            self.cache.decode_ahead.detach()
+            self.cache.decode_ahead = None
         added = keep_decoded_weights_(self.model)
         if self.graph is not None:
             self.capture_decode_graph()

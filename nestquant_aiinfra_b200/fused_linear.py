@@ -10,6 +10,7 @@ input tensor object), one packed projection call, cast to the output dtype.
 
 from __future__ import annotations
 
+import dataclasses
 from dataclasses import dataclass
 from typing import Any
 
@@ -20,7 +21,7 @@ from .rotation import hadamard
 from .runtime.w4a4 import (PreparedNQA4Activation, PreparedNQRTLinear, linear_packed_w4a4, linear_packed_w4a4_fp32,
                            prepare_fused_linear, prefer_producer_in_encoder,
                            quantize_activation_cuda, can_rotate_in_encoder, prefer_rotation_in_encoder,
-                           group_prepared_linears, keep_decoded_weight)
+                           group_prepared_linears, keep_decoded_weight, decode_packed_weight)
 
 _BACKENDS = {"packed_w4a4_cuda_mma", "packed_w4a4_cuda_gemv_m1", "packed_w4a4"}
 
@@ -142,6 +143,7 @@ class SharedProjectionGroup:
         self._output: torch.Tensor | None = None
         self._remaining = 0
         self.launches = 0
+        self._ahead: "_AheadUnit | None" = None  # set by WeightDecodeAhead
 
     def keep_decoded_weight(self) -> int:
         """Keep the BF16 reconstruction of the stacked weight in device memory (opt-in, see
@@ -151,7 +153,10 @@ class SharedProjectionGroup:
 
     def project(self, packed: PreparedNQA4Activation, index: int) -> torch.Tensor:
         if self._packed is not packed or self._output is None:
-            self._output = linear_packed_w4a4(packed, self.stacked)
+            stacked = self.stacked
+            if self._ahead is not None and self._ahead.armed:
+                stacked = self._ahead.take(packed.token_count)
+            self._output = linear_packed_w4a4(packed, stacked)
             self._packed = packed
             self._remaining = len(self.bounds)
             self.launches += 1
@@ -227,6 +232,7 @@ class FusedNQRTLinear(nn.Module):
         # set by SharedProjectionGroup: this projection runs as a column range of a stacked weight
         self._group: "SharedProjectionGroup | None" = None
         self._group_index = 0
+        self._ahead: "_AheadUnit | None" = None  # set by WeightDecodeAhead
         self.input_transform_cache = input_transform_cache
         self.output_dtype = output_dtype
         self.compute_backend = compute_backend
@@ -299,6 +305,8 @@ class FusedNQRTLinear(nn.Module):
                 original_dtype: torch.dtype) -> torch.Tensor:
         self.a4_call_count += 1
         self.a4_encode_count += int(encoded)
+        if self._group is None and self._ahead is not None and self._ahead.armed:
+            prepared = self._ahead.take(packed.token_count)
         if self._group is not None:
             outputs = self._group.project(packed, self._group_index)
         elif self.output_dtype == torch.float32:
@@ -378,6 +386,117 @@ class FusedNQRTLinear(nn.Module):
                 compute_inputs, q=self.activation_q, betas=self.activation_betas, beta_table=beta_table,
                 hadamard_block=block, rmsnorm=pending_norm)
         return self._finish(packed, encoded, prepared, original_dtype)
+
+
+class _AheadUnit:
+    """One packed weight (a module's own or a group's stacked one) whose BF16 form another stream prepares."""
+
+    def __init__(self, owner, packed: PreparedNQRTLinear, members: "list[PreparedNQRTLinear] | None") -> None:
+        self.owner = owner
+        self.packed = packed
+        self.members = members                      # member views of a stacked weight, else None
+        self.resident: PreparedNQRTLinear | None = None  # `packed` with the scratch as its decoded matrix
+        self.event: torch.cuda.Event | None = None
+        self.armed = False
+
+    def bind(self, scratch: torch.Tensor) -> None:
+        rows, k = self.packed.rows, int(self.packed.record.feature_count)
+        self.resident = dataclasses.replace(self.packed, decoded=scratch[:rows * k].view(rows, k))
+
+    def decode(self) -> None:
+        """Queue the decode on the current stream and remember where it ends."""
+        out = self.resident.decoded
+        if self.members is None:
+            decode_packed_weight(self.packed, out=out)
+        else:
+            row = 0
+            for member in self.members:
+                decode_packed_weight(member, out=out[row:row + member.rows])
+                row += member.rows
+        self.event = torch.cuda.Event()
+        self.event.record(torch.cuda.current_stream(out.device))
+        self.armed = True
+
+    def take(self, token_count: int) -> PreparedNQRTLinear:
+        """The weight to project with; the caller's stream waits for the decode (which joins the two streams)."""
+        self.armed = False
+        torch.cuda.current_stream(self.resident.decoded.device).wait_event(self.event)
+        # below eight rows the packed path runs the CUDA-core kernel, not decode + tcgen05: keep its sums
+        return self.resident if token_count >= WeightDecodeAhead.MIN_ROWS else self.packed
+
+
+class WeightDecodeAhead:
+    """Decode the packed weights a decoder layer needs AFTER its attention WHILE the attention runs.
+
+    The paged attention of a decode step leaves SMs idle towards its end (sequences of different lengths);
+    the weight decodes of ``o_proj``, gate / up and ``down_proj`` of the same layer do not depend on it.
+    ``launch(layer)`` -- called right before the layer's attention is queued -- forks a second stream
+    from the current one, queues those decodes there into scratch matrices shared by all layers, and
+    the projections then wait for "their" decode and run the tensor-core GEMM on the scratch (the
+    resident entry of the library).  Same kernels on the same operands as the plain sequence, so the
+    results are bit-identical; inside a CUDA graph capture the second stream becomes a parallel branch
+    of the graph.  Every armed unit must be consumed before the step ends (the projections of the layer
+    do that), otherwise a capture would end with an unjoined stream.
+    """
+
+    MIN_ROWS = 8
+    _BEFORE_ATTENTION = ("q_proj", "k_proj", "v_proj")
+
+    def __init__(self, layers, device: torch.device | str) -> None:
+        self.device = torch.device(device)
+        self.stream = torch.cuda.Stream(self.device)
+        self.layers: list[list[_AheadUnit]] = []
+        sizes: list[int] = []
+        for layer in layers:
+            units: list[_AheadUnit] = []
+            seen: set[int] = set()
+            for name, module in layer.named_modules():
+                if not isinstance(module, FusedNQRTLinear) or any(part in self._BEFORE_ATTENTION for part in name.split(".")):
+                    continue
+                group = module._group
+                if group is not None:
+                    if id(group) in seen or group.stacked.decoded is not None:
+                        continue
+                    seen.add(id(group))
+                    units.append(_AheadUnit(group, group.stacked, list(group.views)))
+                else:
+                    prepared = module._prepared_for(self.device)
+                    if prepared.decoded is None:
+                        units.append(_AheadUnit(module, prepared, None))
+            for index, unit in enumerate(units):
+                elements = unit.packed.rows * int(unit.packed.record.feature_count)
+                if index == len(sizes):
+                    sizes.append(elements)
+                sizes[index] = max(sizes[index], elements)
+            self.layers.append(units)
+        self.scratch = [torch.empty(n, dtype=torch.bfloat16, device=self.device) for n in sizes]
+        for units in self.layers:
+            for index, unit in enumerate(units):
+                unit.bind(self.scratch[index])
+                unit.owner._ahead = unit
+        self.launches = 0
+
+    @property
+    def scratch_bytes(self) -> int:
+        return sum(t.numel() * 2 for t in self.scratch)
+
+    def launch(self, layer_index: int, rows: int) -> None:
+        if rows < self.MIN_ROWS or not 0 <= layer_index < len(self.layers) or not self.layers[layer_index]:
+            return
+        main = torch.cuda.current_stream(self.device)
+        fork = torch.cuda.Event()
+        fork.record(main)
+        self.stream.wait_event(fork)
+        with torch.cuda.stream(self.stream):
+            for unit in self.layers[layer_index]:
+                unit.decode()
+        self.launches += 1
+
+    def detach(self) -> None:
+        for units in self.layers:
+            for unit in units:
+                unit.owner._ahead = None
+                unit.armed = False
 
 
 def keep_decoded_weights_(model: nn.Module, device: torch.device | str | None = None) -> int:

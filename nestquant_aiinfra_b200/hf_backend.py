@@ -146,6 +146,8 @@ class BatchedNQKVLlamaCache(Cache):
         self._page_base = torch.arange(capacity, device=target, dtype=torch.int32) * max_pages
         self._decode_workspace = BatchedNQKVAttentionWorkspace.create(
             self.layer_caches[0], batch_size=capacity, query_heads=num_query_heads, output_dtype=dtype)
+        # optional fused_linear.WeightDecodeAhead of the model this cache serves (the runner installs it)
+        self.decode_ahead = None
         self._prefill: tuple[torch.Tensor, torch.Tensor] | None = None  # (slot_ids, query_lengths)
         self._prefill_from_empty = False
         self._bulk_host: tuple[list[int], list[int]] | None = None   # (slots, lengths) of a prefill from empty slots
@@ -526,6 +528,9 @@ class BatchedNQKVLlamaCache(Cache):
             raise ValueError("batched NQKV decode requires [rows, heads, 1, dim]")
         query = (query_states if rotation_done(query_states) and query_states.dtype == self.dtype
                  else hadamard(query_states.float()).to(self.dtype))[:, :, 0].contiguous()
+        if self.decode_ahead is not None:
+            # the weights the layer needs after its attention are decoded on a second stream meanwhile
+            self.decode_ahead.launch(layer_idx, query.shape[0])
         workspace = self._decode_workspace
         if query.shape[0] != workspace.batch_size:
             workspace = BatchedNQKVAttentionWorkspace.create(self.layer_caches[layer_idx], batch_size=query.shape[0],

@@ -183,6 +183,10 @@ def fill_cache_synthetic(cache: BatchedNQKVLlamaCache, context: int, *, seed: in
 class TensorParallelRunner(BatchedNQKVLlamaRunner):
     """Decode runner of one shard: same step, collectives happen inside the row-parallel modules."""
 
+    def __init__(self, model, cache, *, weight_decode_ahead: bool = False, **options) -> None:
+        # one stream per shard unless asked: the second stream's decodes would share the SMs with the collective
+        super().__init__(model, cache, weight_decode_ahead=weight_decode_ahead, **options)
+
     def start_decode(self, context: int, *, seed: int = 1) -> None:
         gen = torch.Generator().manual_seed(seed)  # identical tokens on every rank
         vocab = self.model.config.vocab_size

@@ -175,6 +175,39 @@ def test_graph_decode_equals_eager_decode():
     assert eager_state[0][0].tolist() == [27, 36, 53, 70]
 
 
+def test_weight_decode_ahead_changes_no_bit_of_a_step():
+    """Captured decode steps of eight rows or more decode the weights of o / gate-up / down on a second stream
+    during the layer's attention: same kernels on the same operands, so tokens, pages and hot tails are equal."""
+    from nestquant_aiinfra_b200.engine import BatchedNQKVLlamaRunner, build_llama_w4a4kv4
+
+    prompts = _prompts([7, 16, 33, 50, 12, 3, 28, 41])
+    runs = []
+    for ahead in (False, True, True):
+        model, cache = build_llama_w4a4kv4(**TINY, capacity=8, max_cache_len=128, seed=9)
+        runner = BatchedNQKVLlamaRunner(model, cache, weight_decode_ahead=ahead)
+        first = runner.prefill_slots(list(range(8)), prompts)
+        runner.capture_decode_graph()
+        assert (cache.decode_ahead is not None) == ahead
+        tokens = [first.clone()]
+        for step in range(24):
+            if step == 8 and ahead and len(runs) == 2:   # switched off and on again in the middle of a run
+                runner.disable_weight_decode_ahead()
+                assert cache.decode_ahead is None
+            if step == 16 and ahead and len(runs) == 2:
+                assert runner.enable_weight_decode_ahead() > 0
+            tokens.append(runner.decode().clone())
+        torch.cuda.synchronize()
+        if ahead and cache.decode_ahead is not None:
+            assert cache.decode_ahead.launches >= 2 * TINY["num_layers"]
+            assert len(cache.decode_ahead.layers[0]) == 3       # o_proj, gate/up (stacked), down_proj
+        pools = [(c.pool.key_codes.clone(), c.pool.value_codes.clone(), c.hot_keys.clone()) for c in cache.layer_caches]
+        runs.append((torch.stack(tokens), pools))
+    for tokens, pools in runs[1:]:
+        assert torch.equal(tokens, runs[0][0])
+        for a, b in zip(runs[0][1], pools):
+            assert all(torch.equal(x, y) for x, y in zip(a, b))
+
+
 def test_opt_in_decoded_copies_keep_the_generated_tokens():
     """Lattice pages change no bit of a step; resident weights only the order of FP32 sums in the projections.
 
