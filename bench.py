@@ -503,7 +503,8 @@ def run_gpu(args) -> None:
             # config 4: the tensor-parallel decode step over these ranks (the only workload here with a collective)
             try:
                 extras["tp"] = tp_decode(torch, dist, device, rank, world, layers=args.tp_layers, batch=args.tp_batch,
-                                         context=args.tp_context, steps=3, warmup=3, collective=args.tp_collective)
+                                         context=args.tp_context, steps=3, warmup=3, collective=args.tp_collective,
+                                         decode_ahead=args.tp_decode_ahead == "on")
             except Exception as error:
                 extras["tp"] = {"error": f"{type(error).__name__}: {error}"[:300]}
             torch.cuda.empty_cache()
@@ -1089,7 +1090,7 @@ def decode_workload(torch, device, *, requests: int = 64, new_tokens: int = 256,
 
 
 def tp_decode(torch, dist, device, rank: int, world: int, *, layers: int, batch: int, context: int, steps: int,
-              warmup: int, resident: bool = False, collective: str = "peer") -> dict:
+              warmup: int, resident: bool = False, collective: str = "peer", decode_ahead: bool = False) -> dict:
     """Config 4: Llama-3-70B architecture (one seeded model sharded over the ranks), W4A4KV4, graph decode.
 
     Returns the measurements (identical on every rank; the times are the maximum over the ranks).  The
@@ -1121,7 +1122,7 @@ def tp_decode(torch, dist, device, rank: int, world: int, *, layers: int, batch:
                                         num_kv_heads=8, head_dim=128, vocab_size=128256, rank=rank, world=world,
                                         capacity=batch, max_cache_len=context + 4 * (steps + warmup) + 48, device=device)
     fill_cache_synthetic(cache, context)
-    runner = TensorParallelRunner(model, cache)
+    runner = TensorParallelRunner(model, cache, weight_decode_ahead=decode_ahead)
     runner.start_decode(context)
     torch.cuda.synchronize(device)
     build_s = time.perf_counter() - t0
@@ -1220,6 +1221,7 @@ def tp_decode(torch, dist, device, rank: int, world: int, *, layers: int, batch:
         "parallelism": f"tp{world}", "layers": layers, "batch": batch, "context": context, "steps": steps,
         "warmup": warmup, "ms_per_step": ms_step, "tok_s": batch / (ms_step * 1e-3),
         "ms_per_layer": ms_step / layers,
+        "weight_decode_ahead": runner.cache.decode_ahead is not None,
         "all_reduce": {"collective": collective_note,
                        "per_step": collectives, "ms_per_step_eager": round(collective_ms, 3),
                        "share_of_step": round(collective_ms / ms_step, 4) if ms_step else None,
@@ -1296,7 +1298,8 @@ def run_tp70b(args) -> None:
         dist.init_process_group("nccl", device_id=device)
     result = tp_decode(torch, dist, device, rank, world, layers=args.tp_layers, batch=args.tp_batch,
                        context=args.tp_context, steps=max(args.steps, 1), warmup=max(args.warmup, 3),
-                       resident=args.tp_resident, collective=args.tp_collective)
+                       resident=args.tp_resident, collective=args.tp_collective,
+                       decode_ahead=args.tp_decode_ahead == "on")
     if rank == 0:
         print(json.dumps({
             "metric": "w4a4kv4_tp_decode_tok_s", "value": result["tok_s"], "unit": "tok/s", "n_gpus": world,
@@ -1346,6 +1349,9 @@ def main() -> None:
                         help="tensor-parallel sum after o_proj / down_proj: this repository's peer-memory kernel "
                              "(falls back to NCCL when symmetric memory is unavailable or a wait gives up) or NCCL; "
                              "the other one is timed too and reported under all_reduce.other_collective")
+    parser.add_argument("--tp-decode-ahead", choices=("on", "off"), default="off",
+                        help="tensor-parallel decode: decode the shard's o / gate-up / down weights of a layer on a "
+                             "second stream during the layer's attention (as the single-GPU runner does by default)")
     parser.add_argument("--tp-resident", action="store_true",
                         help="tp70b: also time the opt-in mode that keeps the decoded BF16 weights of the shard in HBM")
     parser.add_argument("--kernel-mix", action="store_true",
