@@ -366,11 +366,38 @@ def run_gpu(args) -> None:
     cells = [(si, m) for si in range(len(SHAPES)) for m in TOKENS]
     stream = torch.cuda.current_stream(device)
 
-    def step() -> None:
+    def run_cell(si: int, m: int):
+        x = inputs[(SHAPES[si][2], m)]
+        act = rt.quantize_activation_cuda(x, q=14, betas=ACT_BETAS, beta_table=beta_table, keep_decoded=True)
+        return rt.linear_packed_w4a4(act, weights[si])
+
+    def step_one_stream() -> None:
         for si, m in cells:
-            x = inputs[(SHAPES[si][2], m)]
-            act = rt.quantize_activation_cuda(x, q=14, betas=ACT_BETAS, beta_table=beta_table, keep_decoded=True)
-            rt.linear_packed_w4a4(act, weights[si])
+            run_cell(si, m)
+
+    # The 32 cells are independent calls.  A step issues them on `--streams` streams that fork from the timing
+    # stream and join it again (parallel branches of the captured graph): most launches of the small cells and the
+    # tails of the large ones leave SMs idle that another cell's kernels can use.  Cells are dealt longest first
+    # to the least loaded stream, from one measurement of every cell alone during the warm-up.
+    lanes: list[list[tuple[int, int]]] = [list(cells)]
+    side_streams = [torch.cuda.Stream(device) for _ in range(max(args.streams, 1))]
+
+    def step() -> None:
+        if len(lanes) == 1:
+            step_one_stream()
+            return
+        origin = torch.cuda.current_stream(device)  # the timing stream, or the capturing one
+        fork = torch.cuda.Event()
+        fork.record(origin)
+        results = []  # outputs stay allocated until every stream has joined
+        for lane, todo in zip(side_streams, lanes):
+            lane.wait_event(fork)
+            with torch.cuda.stream(lane):
+                for si, m in todo:
+                    results.append(run_cell(si, m))
+                done = torch.cuda.Event()
+                done.record(lane)
+            origin.wait_event(done)
 
     def barrier() -> None:
         if distributed:
@@ -379,6 +406,22 @@ def run_gpu(args) -> None:
 
     sampler = ClockSampler(local_rank)  # samples from the warm-up on, so the timed region is always covered
     sampler.start()
+    step()  # loads the kernels
+    if args.streams > 1:
+        alone = {}
+        for si, m in cells:
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record(stream)
+            run_cell(si, m)
+            t1.record(stream)
+            torch.cuda.synchronize(device)
+            alone[(si, m)] = t0.elapsed_time(t1)
+        lanes = [[] for _ in range(args.streams)]
+        load = [0.0] * args.streams
+        for cell in sorted(cells, key=lambda c: -alone[c]):
+            lightest = load.index(min(load))
+            lanes[lightest].append(cell)
+            load[lightest] += alone[cell]
     for _ in range(max(args.warmup, 3)):
         step()
     barrier()
@@ -428,15 +471,31 @@ def run_gpu(args) -> None:
         enc_graph.replay()
     enc1.record(stream)
     torch.cuda.synchronize(device)
+    # the same step with the cells one after the other on one stream, for reference
+    serial_ms = None
+    if len(lanes) > 1:
+        serial_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(serial_graph):
+            step_one_stream()
+        serial_graph.replay()
+        torch.cuda.synchronize(device)
+        ser0, ser1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ser0.record(stream)
+        for _ in range(3):
+            serial_graph.replay()
+        ser1.record(stream)
+        torch.cuda.synchronize(device)
+        serial_ms = ser0.elapsed_time(ser1) / 3
     clocks = sampler.stop()
     enc_ms_per_step = enc0.elapsed_time(enc1) / 3
     elapsed_ms = start.elapsed_time(stop)
     if rt.read_status(device) != 0:
         raise SystemExit("device status word is non-zero: a bounded wait in the GEMM gave up")
     if distributed:
-        t = torch.tensor([elapsed_ms], device=device)
+        t = torch.tensor([elapsed_ms, serial_ms or 0.0], device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        elapsed_ms = float(t.item())
+        elapsed_ms = float(t[0].item())
+        serial_ms = float(t[1].item()) or None
     ms_per_step = elapsed_ms / args.steps
     value = world * sweep_flops() / (ms_per_step * 1e-3) / 1e12
 
@@ -446,7 +505,8 @@ def run_gpu(args) -> None:
     enc_gbs = enc_bytes / (enc_ms_per_step * 1e-3) / 1e9
     roofline = {"kernel": "nq_encode_rows_kernel", "bound": "hbm", "achieved": enc_gbs, "peak": pk["hbm_gbs"],
                 "unit": "GB/s", "frac": enc_gbs / pk["hbm_gbs"], "peak_source": pk["source"],
-                "share_of_step": enc_ms_per_step / ms_per_step, "launches": len(cells),
+                # share of the device work of a step: against the step with its cells one after the other
+                "share_of_step": enc_ms_per_step / (serial_ms or ms_per_step), "launches": len(cells),
                 "us_per_step": round(enc_ms_per_step * 1e3, 1),
                 # DRAM bytes of the largest encode launch (8192 x 8192 BF16) from the ncu capture summarised in
                 # profiles/nq_encode_rows_kernel_8192x8192_bf16.md; its algorithmic bytes are 2MK + M(17K/32+4),
@@ -520,7 +580,11 @@ def run_gpu(args) -> None:
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": sweep_config(world),
-            "launch": "CUDA graph of one step, replayed" if graph is not None else "call by call",
+            "launch": (("CUDA graph of one step, replayed" if graph is not None else "call by call")
+                       + (f"; the 32 cells on {len(lanes)} streams, dealt longest first" if len(lanes) > 1 else "")),
+            "one_stream": None if serial_ms is None else {
+                "ms_per_step": serial_ms, "value": world * sweep_flops() / (serial_ms * 1e-3) / 1e12,
+                "note": "the same step with its 32 cells one after the other on one stream (CUDA graph, 3 replays)"},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],
                     "ms_per_step": e2e["ms"], "launch": e2e.get("launch"), "cell_order": e2e.get("cell_order"),
@@ -1336,6 +1400,9 @@ def main() -> None:
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=5)
     parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--streams", type=int, default=4,
+                        help="streams the cells of one sweep step are issued on (1 = one after the other; the "
+                             "one-stream time is measured and reported either way)")
     parser.add_argument("--impl", choices=("native", "reference"), default="native")
     parser.add_argument("--workload", choices=("all", "kv", "decode", "gemv", "tp70b"), default="all",
                         help="all = sweep (+ extras); kv / decode / gemv = only that extra workload, for profiling; "
