@@ -125,6 +125,8 @@ class SharedProjectionGroup:
     sums may be taken in another order than in the member's own launch.
     """
 
+    SEPARATE_FROM = 512  # rows from which every member runs its own projection
+
     def __init__(self, members: "list[FusedNQRTLinear]", device: torch.device | str | None = None) -> None:
         if any(member._prepared is None for member in members) and device is None:
             raise ValueError("members without a prepared weight need the target device")
@@ -152,6 +154,15 @@ class SharedProjectionGroup:
         return self.stacked.decoded.numel() * 2
 
     def project(self, packed: PreparedNQA4Activation, index: int) -> torch.Tensor:
+        if packed.token_count >= self.SEPARATE_FROM and not (self._ahead is not None and self._ahead.armed):
+            # many rows: the launches saved by stacking no longer matter, while every member would have to copy
+            # its column range out of the stacked result (tensor ops on a column slice fall off their vectorised
+            # kernels): the member's own projection writes a contiguous result at the same decode + GEMM work
+            view = self.views[index]
+            if self.stacked.decoded is not None:  # resident decoded weights: the member's rows of the stacked matrix
+                start, end = self.bounds[index]
+                view = dataclasses.replace(view, decoded=self.stacked.decoded[start:end])
+            return linear_packed_w4a4(packed, view)
         if self._packed is not packed or self._output is None:
             stacked = self.stacked
             if self._ahead is not None and self._ahead.armed:
@@ -162,9 +173,6 @@ class SharedProjectionGroup:
             self.launches += 1
         start, end = self.bounds[index]
         output = self._output[..., start:end]
-        if packed.token_count >= 512:
-            # many rows: tensor ops on a column slice fall off their vectorised kernels, a copy is cheaper
-            output = output.contiguous()
         self._remaining -= 1
         if self._remaining <= 0:
             self._packed = self._output = None
