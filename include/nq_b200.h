@@ -384,6 +384,14 @@ int nq_kv_attention_lattice(const void* query, int q_dtype, int batch, int q_tok
  * the dtype, final IEEE division by float32(sqrt(n)).  x may equal out. */
 int nq_hadamard(const void* x, void* out, int dtype, int64_t rows, int64_t n, nq_stream_t stream);
 
+/* hadamard(silu(gate) * up) in one launch: the rotated input of a Llama down_proj
+ * (models/fused_linear.py:287-290 applied to the MLP's `act_fn(gate_proj(x)) * up_proj(x)`) for rows too long
+ * for nq_a4_encode_silu_mul_rotated.  gate, up and out are contiguous [rows, n] tensors of `dtype`; the
+ * product is formed with the tensor ops' arithmetic (x / (1 + exp(-x)) in float32 rounded to the dtype, then
+ * the product rounded to the dtype), so the result equals nq_hadamard of that product bit for bit. */
+int nq_hadamard_silu_mul(const void* gate, const void* up, void* out, int dtype, int64_t rows, int64_t n,
+                         nq_stream_t stream);
+
 /* Rotary position embedding of query or key heads and, with apply_hadamard != 0, the float32
  * Hadamard rotation the KV backend applies to them afterwards, in one launch:
  *   rope     (x * cos) + (rotate_half(x) * sin), every product and the sum rounded to `dtype`

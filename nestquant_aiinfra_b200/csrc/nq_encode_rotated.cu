@@ -86,12 +86,7 @@ nq_encode_rotated_kernel(const T* __restrict__ x, const T* __restrict__ x2, int6
                 float u[8];
                 nq_load8<T>(x + (row0 + r) * stride + col, v);
                 nq_load8<T>(x2 + (row0 + r) * stride + col, u);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    // silu on a tensor of dtype T: x / (1 + exp(-x)) in float32, rounded to T; then the product, rounded
-                    const float s = nq_round_to<T>(nq_div(v[j], nq_add(1.0f, expf(-v[j]))));
-                    v[j] = nq_round_to<T>(nq_mul(s, u[j]));
-                }
+                nq_silu_mul8<T>(v, u);
             },
             rotated, total, hadamard_block);
     }

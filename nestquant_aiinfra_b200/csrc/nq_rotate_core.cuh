@@ -104,3 +104,166 @@ template <typename T>
 __device__ __forceinline__ void nq_fwht_rows_to_smem(const T* __restrict__ x, float* buf, int total, int n) {
     nq_fwht_groups_to_smem<T>([&](int g, float v[8]) { nq_load8<T>(x + (int64_t)g * 8, v); }, buf, total, n);
 }
+
+// ---- 16-bit tensor dtypes: two values per register ------------------------------------------
+//
+// A float32 add of two BF16 (FP16) values followed by rounding to BF16 (FP16) equals ONE correctly
+// rounded BF16 (FP16) add: the float32 sum is exact unless the exponents differ by more than 16 (13),
+// and then the small operand is so far below half an ulp of the result that no rounding boundary is
+// near.  So a butterfly of the reference is add.rn / sub.rn on the packed pair type, two butterflies
+// per instruction, and the row lives in shared memory in its own dtype (half the bytes).
+//
+// A thread always works on TWO radix-8 groups at once, value j of both groups in one register, so
+// that all three stages of a pass combine different registers: in pass 0 the two groups are
+// neighbours (16 consecutive elements), in the later passes neighbouring columns, whose values are
+// already adjacent in memory (one 32-bit word).  Word addresses are XOR-swizzled (bits 2..4 with
+// bits 5..7) so that the pass with eight-element spacing is free of bank conflicts as well.
+template <typename T> struct NqPacked;
+template <> struct NqPacked<__nv_bfloat16> {
+    using pair = __nv_bfloat162;
+    static __device__ __forceinline__ void to_floats(uint32_t w, float& lo, float& hi) {
+        lo = __uint_as_float(w << 16);
+        hi = __uint_as_float(w & 0xffff0000u);
+    }
+};
+template <> struct NqPacked<__half> {
+    using pair = __half2;
+    static __device__ __forceinline__ void to_floats(uint32_t w, float& lo, float& hi) {
+        const __half2 h = *reinterpret_cast<const __half2*>(&w);
+        lo = __low2float(h);
+        hi = __high2float(h);
+    }
+};
+
+template <typename T>
+__device__ __forceinline__ void nq_butterfly_packed(uint32_t& l, uint32_t& r) {
+    using P = typename NqPacked<T>::pair;
+    const P a = *reinterpret_cast<const P*>(&l), b = *reinterpret_cast<const P*>(&r);
+    const P sum = __hadd2(a, b), diff = __hsub2(a, b);
+    l = *reinterpret_cast<const uint32_t*>(&sum);
+    r = *reinterpret_cast<const uint32_t*>(&diff);
+}
+
+template <typename T, int STAGES>
+__device__ __forceinline__ void nq_butterflies_packed(uint32_t v[8]) {
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) {
+        const int h = 1 << s;
+#pragma unroll
+        for (int j = 0; j < (1 << STAGES); ++j)
+            if ((j & h) == 0) nq_butterfly_packed<T>(v[j], v[j | h]);
+    }
+}
+
+__device__ __forceinline__ int nq_fwht_swizzle(int word) { return word ^ (((word >> 5) & 7) << 2); }
+
+// All butterfly stages of total / n rows of n elements (n a power of two >= 16, total a multiple of 16)
+// read from x; the result stays in `words` (total / 2 packed words at swizzled addresses, element
+// 2i in the low half of word i), NOT yet divided by sqrt(n).  Ends with a barrier.
+// load(g) supplies the 8 consecutive elements of group g as four packed words.
+template <typename T, class Load>
+__device__ __forceinline__ void nq_fwht_groups_packed(Load&& load, uint32_t* words, int total, int n) {
+    static_assert(sizeof(T) == 2, "packed path of the 16-bit dtypes");
+    const int nthreads = blockDim.x;
+    int log_n = 0;
+    while ((1 << log_n) < n) ++log_n;
+
+    // pass 0: widths 1, 2, 4 inside two neighbouring groups of 8 consecutive elements
+    for (int pg = threadIdx.x; pg < (total >> 4); pg += nthreads) {
+        const uint4 a = load(2 * pg);
+        const uint4 b = load(2 * pg + 1);
+        const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+        uint32_t v[8];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            v[2 * i] = __byte_perm(aw[i], bw[i], 0x5410);      // (a[2i], b[2i])
+            v[2 * i + 1] = __byte_perm(aw[i], bw[i], 0x7632);  // (a[2i+1], b[2i+1])
+        }
+        nq_butterflies_packed<T, 3>(v);
+        uint4 oa, ob;
+        oa.x = __byte_perm(v[0], v[1], 0x5410); ob.x = __byte_perm(v[0], v[1], 0x7632);
+        oa.y = __byte_perm(v[2], v[3], 0x5410); ob.y = __byte_perm(v[2], v[3], 0x7632);
+        oa.z = __byte_perm(v[4], v[5], 0x5410); ob.z = __byte_perm(v[4], v[5], 0x7632);
+        oa.w = __byte_perm(v[6], v[7], 0x5410); ob.w = __byte_perm(v[6], v[7], 0x7632);
+        *reinterpret_cast<uint4*>(words + nq_fwht_swizzle(8 * pg)) = oa;
+        *reinterpret_cast<uint4*>(words + nq_fwht_swizzle(8 * pg + 4)) = ob;
+    }
+    __syncthreads();
+    int done = 3;
+    while (done < log_n) {
+        const int stages = min(3, log_n - done);
+        const int wp = 1 << (done - 1);        // words between the values a thread combines (w / 2)
+        const int spanw = wp << stages;        // words covered by one family of column pairs
+        const int work = (total >> 1) >> stages;
+        for (int t = threadIdx.x; t < work; t += nthreads) {
+            const int base = (t / wp) * spanw + (t % wp);
+            uint32_t v[8];
+            if (stages == 3) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = words[nq_fwht_swizzle(base + j * wp)];
+                nq_butterflies_packed<T, 3>(v);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) words[nq_fwht_swizzle(base + j * wp)] = v[j];
+            } else if (stages == 2) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) v[j] = words[nq_fwht_swizzle(base + j * wp)];
+                nq_butterflies_packed<T, 2>(v);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) words[nq_fwht_swizzle(base + j * wp)] = v[j];
+            } else {
+                v[0] = words[nq_fwht_swizzle(base)];
+                v[1] = words[nq_fwht_swizzle(base + wp)];
+                nq_butterflies_packed<T, 1>(v);
+                words[nq_fwht_swizzle(base)] = v[0];
+                words[nq_fwht_swizzle(base + wp)] = v[1];
+            }
+        }
+        __syncthreads();
+        done += stages;
+    }
+}
+
+// Same with the rows read from global memory (contiguous in `x`).
+template <typename T>
+__device__ __forceinline__ void nq_fwht_rows_packed(const T* __restrict__ x, uint32_t* words, int total, int n) {
+    nq_fwht_groups_packed<T>([&](int g) { return __ldg(reinterpret_cast<const uint4*>(x) + g); }, words, total, n);
+}
+
+// 8 float32 values of dtype T (already rounded to it) as four packed words.
+template <typename T> __device__ __forceinline__ uint4 nq_pack_exact8(const float v[8]);
+template <> __device__ __forceinline__ uint4 nq_pack_exact8<__nv_bfloat16>(const float v[8]) {
+    return make_uint4(__byte_perm(__float_as_uint(v[0]), __float_as_uint(v[1]), 0x7632),
+                      __byte_perm(__float_as_uint(v[2]), __float_as_uint(v[3]), 0x7632),
+                      __byte_perm(__float_as_uint(v[4]), __float_as_uint(v[5]), 0x7632),
+                      __byte_perm(__float_as_uint(v[6]), __float_as_uint(v[7]), 0x7632));
+}
+template <> __device__ __forceinline__ uint4 nq_pack_exact8<__half>(const float v[8]) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+        w[i] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// SiLU(gate) * up on tensors of dtype T as the tensor ops compute it: x / (1 + exp(-x)) in float32 rounded to
+// T, then the product rounded to T.
+template <typename T>
+__device__ __forceinline__ void nq_silu_mul8(float gate[8], const float up[8]) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const float s = nq_round_to<T>(nq_div(gate[j], nq_add(1.0f, expf(-gate[j]))));
+        gate[j] = nq_round_to<T>(nq_mul(s, up[j]));
+    }
+}
+
+// The 8 consecutive elements of group g (elements 8g .. 8g+7) of a packed row buffer, as float32.
+template <typename T>
+__device__ __forceinline__ void nq_fwht_packed_group(const uint32_t* words, int g, float v[8]) {
+    const uint4 w = *reinterpret_cast<const uint4*>(words + nq_fwht_swizzle(4 * g));
+    NqPacked<T>::to_floats(w.x, v[0], v[1]);
+    NqPacked<T>::to_floats(w.y, v[2], v[3]);
+    NqPacked<T>::to_floats(w.z, v[4], v[5]);
+    NqPacked<T>::to_floats(w.w, v[6], v[7]);
+}

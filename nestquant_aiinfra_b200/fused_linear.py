@@ -17,7 +17,7 @@ from typing import Any
 import torch
 from torch import nn
 
-from .rotation import hadamard
+from .rotation import hadamard, hadamard_silu_mul
 from .runtime.w4a4 import (PreparedNQA4Activation, PreparedNQRTLinear, linear_packed_w4a4, linear_packed_w4a4_fp32,
                            prepare_fused_linear, prefer_producer_in_encoder,
                            quantize_activation_cuda, can_rotate_in_encoder, prefer_rotation_in_encoder,
@@ -333,9 +333,17 @@ class FusedNQRTLinear(nn.Module):
             raise ValueError("gate and up must share shape, dtype and device")
         block = self.in_features if self.input_hadamard else self.input_rotation_block
         rows = gate.numel() // self.in_features
-        if (block is None or torch.is_grad_enabled() or not can_rotate_in_encoder(self.in_features, block)
-                or not prefer_producer_in_encoder(rows, self.in_features)):
+        if block is None or torch.is_grad_enabled() or gate.dtype not in (torch.bfloat16, torch.float16, torch.float32):
             return self.forward(torch.nn.functional.silu(gate) * up)
+        if not can_rotate_in_encoder(self.in_features, block) or not prefer_producer_in_encoder(rows, self.in_features):
+            # long rows: product and rotation as one launch in front of the plain encoder
+            if self.input_transform_cache is not None:
+                return self.forward(torch.nn.functional.silu(gate) * up)
+            shape = gate.shape
+            if block != self.in_features:
+                blocked = (*shape[:-1], self.in_features // block, block)
+                gate, up = gate.reshape(blocked), up.reshape(blocked)
+            return self._encode_and_project(hadamard_silu_mul(gate, up).reshape(shape), None, None, gate.dtype)
         prepared = self._prepared_for(gate.device)
         beta_table = self.activation_beta_table
         if beta_table.device != gate.device:
@@ -380,10 +388,15 @@ class FusedNQRTLinear(nn.Module):
                 compute_inputs = hadamard(inputs.reshape(*inputs.shape[:-1], self.in_features // b, b)).reshape(inputs.shape)
             else:
                 compute_inputs = inputs
-        prepared = self._prepared_for(inputs.device)
+        return self._encode_and_project(compute_inputs, block, pending_norm, original_dtype)
+
+    def _encode_and_project(self, compute_inputs: torch.Tensor, block: int | None, pending_norm,
+                            original_dtype: torch.dtype) -> torch.Tensor:
+        """A4 encode (rotating by ``block`` and applying ``pending_norm`` inside the launch when given) + projection."""
+        prepared = self._prepared_for(compute_inputs.device)
         beta_table = self.activation_beta_table
-        if beta_table.device != inputs.device:
-            beta_table = beta_table.to(inputs.device)
+        if beta_table.device != compute_inputs.device:
+            beta_table = beta_table.to(compute_inputs.device)
         if self.packed_activation_cache is None:
             packed = quantize_activation_cuda(compute_inputs, q=self.activation_q, betas=self.activation_betas,
                                               beta_table=beta_table, hadamard_block=block, keep_decoded=True,

@@ -48,3 +48,21 @@ def hadamard(x: torch.Tensor) -> torch.Tensor:
             _lib.check(status, "hadamard")
             return out
     return hadamard_butterflies(x)
+
+
+def hadamard_silu_mul(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """``hadamard(silu(gate) * up)`` as one launch on CUDA tensors (same bits as the three tensor steps)."""
+    if gate.shape != up.shape or gate.dtype != up.dtype or gate.device != up.device:
+        raise ValueError("gate and up must share shape, dtype and device")
+    n = gate.shape[-1] if gate.ndim else 0
+    if (gate.device.type != "cuda" or gate.dtype not in _DTYPE_TAG or n < 8 or n > 32768 or n & (n - 1)
+            or gate.numel() == 0):
+        return hadamard(torch.nn.functional.silu(gate) * up)
+    a, b = gate.contiguous(), up.contiguous()
+    out = torch.empty_like(a)
+    status = _lib.lib().nq_hadamard_silu_mul(
+        ctypes.c_void_p(a.data_ptr()), ctypes.c_void_p(b.data_ptr()), ctypes.c_void_p(out.data_ptr()),
+        _DTYPE_TAG[gate.dtype], ctypes.c_int64(a.numel() // n), ctypes.c_int64(n),
+        ctypes.c_void_p(torch.cuda.current_stream(gate.device).cuda_stream))
+    _lib.check(status, "hadamard_silu_mul")
+    return out

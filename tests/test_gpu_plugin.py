@@ -11,7 +11,9 @@ pytestmark = pytest.mark.gpu
 
 @pytest.mark.parametrize("rows,n,dtype", [(3, 2048, torch.float32), (3, 2048, torch.bfloat16), (5, 64, torch.float32),
                                           (257, 64, torch.bfloat16), (4, 8192, torch.bfloat16), (7, 128, torch.float16),
-                                          (2, 16384, torch.float32), (9, 8, torch.float32)])
+                                          (2, 16384, torch.float32), (9, 8, torch.float32), (5, 8, torch.bfloat16),
+                                          (131, 16, torch.bfloat16), (33, 32, torch.float16), (3, 512, torch.bfloat16),
+                                          (2, 1024, torch.float16), (3, 4096, torch.bfloat16), (2, 32768, torch.bfloat16)])
 def test_hadamard_bit_exact(oracle, golden, rows, n, dtype):
     from nestquant_aiinfra_b200.rotation import hadamard, hadamard_butterflies
 
@@ -26,6 +28,21 @@ def test_hadamard_bit_exact(oracle, golden, rows, n, dtype):
         expected = hadamard_butterflies(x)  # the reference's own op sequence, on the CPU
     got = hadamard(x.cuda()).cpu()
     assert got.dtype == dtype and torch.equal(got, expected)
+
+
+@pytest.mark.parametrize("rows,n,dtype", [(64, 8192, torch.bfloat16), (5, 8192, torch.float16), (3, 2048, torch.float32),
+                                          (130, 16, torch.bfloat16), (7, 8, torch.bfloat16), (1, 32768, torch.bfloat16)])
+def test_hadamard_of_the_silu_product_in_one_launch(rows, n, dtype):
+    """hadamard(silu(gate) * up) as one launch == the two tensor ops followed by the rotation kernel, bit for bit."""
+    from nestquant_aiinfra_b200.rotation import hadamard, hadamard_silu_mul
+
+    gate = (3.0 * torch.randn(rows, n, generator=rng(5 * n + rows))).to(dtype).cuda()
+    up = torch.randn(rows, n, generator=rng(7 * n + rows)).to(dtype).cuda()
+    expected = hadamard(torch.nn.functional.silu(gate) * up)
+    got = hadamard_silu_mul(gate, up)
+    assert got.dtype == dtype and torch.equal(got, expected)
+    blocked = hadamard_silu_mul(gate.view(rows, -1, 8), up.view(rows, -1, 8))   # block-diagonal: rows of 8
+    assert torch.equal(blocked, hadamard((torch.nn.functional.silu(gate) * up).view(rows, -1, 8)))
 
 
 def test_hadamard_rejects_non_power_of_two():
