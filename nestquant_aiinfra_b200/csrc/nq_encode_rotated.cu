@@ -39,8 +39,15 @@ nq_encode_rotated_kernel(const T* __restrict__ x, const T* __restrict__ x2, int6
     const int64_t row0 = (int64_t)blockIdx.x * rpc;
     const int nrows = (int)min((int64_t)rpc, rows - row0);
     const int total = nrows * k;
+    // 16-bit dtypes: packed butterflies on the rows in their own dtype, held in the upper half of `rotated`
+    // until they are handed to the encoder as float32 (nq_fwht_packed_to_floats)
+    const bool packed = sizeof(T) == 2 && hadamard_block >= 16;
+    uint32_t* words = reinterpret_cast<uint32_t*>(rotated + (total >> 1));
     if (MODE == kPlain) {
-        nq_fwht_rows_to_smem<T>(x + row0 * k, rotated, total, hadamard_block);
+        if constexpr (sizeof(T) == 2) {
+            if (packed) nq_fwht_rows_packed<T>(x + row0 * k, words, total, hadamard_block);
+        }
+        if (!packed) nq_fwht_rows_to_smem<T>(x + row0 * k, rotated, total, hadamard_block);
     } else if (MODE == kRmsNorm) {
         // 1 / rms of every row of this CTA, with nq_rmsnorm's reduction order: 128 threads take the row's groups
         // of 8 in strides, FMA chains, butterfly over the warp, the four warps in order
@@ -68,31 +75,44 @@ nq_encode_rotated_kernel(const T* __restrict__ x, const T* __restrict__ x2, int6
             }
             __syncthreads();
         }
-        nq_fwht_groups_to_smem<T>(
-            [&](int g, float v[8]) {
-                const int r = (g * 8) / k, col = g * 8 - r * k;
-                float w[8];
-                nq_load8<T>(x + (row0 + r) * stride + col, v);
-                nq_load8<T>(x2 + col, w);
-                const float scale = row_scale[r];
+        auto normalised = [&](int g, float v[8]) {
+            const int r = (g * 8) / k, col = g * 8 - r * k;
+            float w[8];
+            nq_load8<T>(x + (row0 + r) * stride + col, v);
+            nq_load8<T>(x2 + col, w);
+            const float scale = row_scale[r];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) v[j] = nq_round_to<T>(nq_mul(w[j], nq_round_to<T>(nq_mul(v[j], scale))));
-            },
-            rotated, total, hadamard_block);
+            for (int j = 0; j < 8; ++j) v[j] = nq_round_to<T>(nq_mul(w[j], nq_round_to<T>(nq_mul(v[j], scale))));
+        };
+        if constexpr (sizeof(T) == 2) {
+            if (packed)
+                nq_fwht_groups_packed<T>([&](int g) { float v[8]; normalised(g, v); return nq_pack_exact8<T>(v); },
+                                         words, total, hadamard_block);
+        }
+        if (!packed) nq_fwht_groups_to_smem<T>(normalised, rotated, total, hadamard_block);
     } else {
-        nq_fwht_groups_to_smem<T>(
-            [&](int g, float v[8]) {
-                const int r = (g * 8) / k, col = g * 8 - r * k;
-                float u[8];
-                nq_load8<T>(x + (row0 + r) * stride + col, v);
-                nq_load8<T>(x2 + (row0 + r) * stride + col, u);
-                nq_silu_mul8<T>(v, u);
-            },
-            rotated, total, hadamard_block);
+        auto product = [&](int g, float v[8]) {
+            const int r = (g * 8) / k, col = g * 8 - r * k;
+            float u[8];
+            nq_load8<T>(x + (row0 + r) * stride + col, v);
+            nq_load8<T>(x2 + (row0 + r) * stride + col, u);
+            nq_silu_mul8<T>(v, u);
+        };
+        if constexpr (sizeof(T) == 2) {
+            if (packed)
+                nq_fwht_groups_packed<T>([&](int g) { float v[8]; product(g, v); return nq_pack_exact8<T>(v); },
+                                         words, total, hadamard_block);
+        }
+        if (!packed) nq_fwht_groups_to_smem<T>(product, rotated, total, hadamard_block);
     }
-    for (int i = threadIdx.x; i < total; i += NQ_ENC_THREADS)
-        rotated[i] = nq_round_to<T>(nq_div_by(rotated[i], root, inv_root));
-    __syncthreads();
+    if constexpr (sizeof(T) == 2) {
+        if (packed) nq_fwht_packed_to_floats<T>(rotated, total, root, inv_root);
+    }
+    if (!packed) {
+        for (int i = threadIdx.x; i < total; i += NQ_ENC_THREADS)
+            rotated[i] = nq_round_to<T>(nq_div_by(rotated[i], root, inv_root));
+        __syncthreads();
+    }
     const int64_t g0 = row0 * bpr;
     const int blk_begin = (int)blockIdx.y * blocks_per_split;
     nq_encode_rows_cta<float, false, false>(rotated, k, nrows, nrows, k, beta_table, sqrt_k, codes + g0,

@@ -267,3 +267,43 @@ __device__ __forceinline__ void nq_fwht_packed_group(const uint32_t* words, int 
     NqPacked<T>::to_floats(w.z, v[4], v[5]);
     NqPacked<T>::to_floats(w.w, v[6], v[7]);
 }
+
+// In-place hand-over of a packed transform to a consumer that reads float32: `floats` is a region of `total`
+// floats whose UPPER half holds the packed words of nq_fwht_groups_packed (words = floats + total / 2 as
+// 32-bit words).  Every value is divided by `root` (IEEE), rounded to T and written as float32 at its element
+// index.  Chunks of 8 groups per thread go front to back; inside a chunk all words are read before the first
+// float is written (one barrier), and the floats of a chunk never reach words of a later chunk: chunk c ends
+// at byte 4 (c+1) C of the region, the words not yet read start at byte 2 total + 2 (c+1) C >= that.
+// Called by all `nthreads` threads of the CTA; ends with a barrier.
+template <typename T>
+__device__ __forceinline__ void nq_fwht_packed_to_floats(float* floats, int total, float root, float inv_root) {
+    const uint32_t* words = reinterpret_cast<const uint32_t*>(floats + (total >> 1));
+    const int groups = total >> 3;
+    const int nthreads = blockDim.x;
+    for (int g0 = 0; g0 < groups; g0 += nthreads * 8) {
+        uint4 w[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int g = g0 + i * nthreads + threadIdx.x;
+            w[i] = g < groups ? *reinterpret_cast<const uint4*>(words + nq_fwht_swizzle(4 * g)) : make_uint4(0, 0, 0, 0);
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int g = g0 + i * nthreads + threadIdx.x;
+            if (g < groups) {
+                float v[8];
+                NqPacked<T>::to_floats(w[i].x, v[0], v[1]);
+                NqPacked<T>::to_floats(w[i].y, v[2], v[3]);
+                NqPacked<T>::to_floats(w[i].z, v[4], v[5]);
+                NqPacked<T>::to_floats(w[i].w, v[6], v[7]);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = nq_round_to<T>(nq_div_by(v[j], root, inv_root));
+                float4* dst = reinterpret_cast<float4*>(floats + g * 8);
+                dst[0] = make_float4(v[0], v[1], v[2], v[3]);
+                dst[1] = make_float4(v[4], v[5], v[6], v[7]);
+            }
+        }
+    }
+    __syncthreads();
+}
