@@ -386,11 +386,12 @@ int nq_hadamard(const void* x, void* out, int dtype, int64_t rows, int64_t n, nq
 
 /* hadamard(silu(gate) * up) in one launch: the rotated input of a Llama down_proj
  * (models/fused_linear.py:287-290 applied to the MLP's `act_fn(gate_proj(x)) * up_proj(x)`) for rows too long
- * for nq_a4_encode_silu_mul_rotated.  gate, up and out are contiguous [rows, n] tensors of `dtype`; the
+ * for nq_a4_encode_silu_mul_rotated.  gate and up are [rows, n] tensors of `dtype` whose rows lie row_stride
+ * elements apart (column ranges of one stacked gate/up result need no copy), out is contiguous [rows, n]; the
  * product is formed with the tensor ops' arithmetic (x / (1 + exp(-x)) in float32 rounded to the dtype, then
  * the product rounded to the dtype), so the result equals nq_hadamard of that product bit for bit. */
-int nq_hadamard_silu_mul(const void* gate, const void* up, void* out, int dtype, int64_t rows, int64_t n,
-                         nq_stream_t stream);
+int nq_hadamard_silu_mul(const void* gate, const void* up, int64_t row_stride, void* out, int dtype, int64_t rows,
+                         int64_t n, nq_stream_t stream);
 
 /* Rotary position embedding of query or key heads and, with apply_hadamard != 0, the float32
  * Hadamard rotation the KV backend applies to them afterwards, in one launch:

@@ -21,8 +21,8 @@ namespace {
 // input of a Llama down_proj, produced while the rows are loaded.
 template <typename T, bool SILU_MUL>
 __global__ void __launch_bounds__(1024)
-nq_hadamard_kernel(const T* __restrict__ x, const T* __restrict__ x2, T* __restrict__ out, int64_t rows, int n,
-                   int rows_per_cta, float root, float inv_root) {
+nq_hadamard_kernel(const T* __restrict__ x, const T* __restrict__ x2, int64_t in_stride, T* __restrict__ out,
+                   int64_t rows, int n, int rows_per_cta, float root, float inv_root) {
     extern __shared__ __align__(16) float buf[];
     const int64_t row0 = (int64_t)blockIdx.x * rows_per_cta;
     const int nrows = (int)min((int64_t)rows_per_cta, rows - row0);
@@ -34,8 +34,10 @@ nq_hadamard_kernel(const T* __restrict__ x, const T* __restrict__ x2, T* __restr
                 nq_fwht_groups_packed<T>(
                     [&](int g) {
                         float v[8], u[8];
-                        nq_load8<T>(x + row0 * n + (int64_t)g * 8, v);
-                        nq_load8<T>(x2 + row0 * n + (int64_t)g * 8, u);
+                        const int r = (g * 8) / n;
+                        const int64_t at = (row0 + r) * in_stride + (g * 8 - r * n);
+                        nq_load8<T>(x + at, v);
+                        nq_load8<T>(x2 + at, u);
                         nq_silu_mul8<T>(v, u);
                         return nq_pack_exact8<T>(v);
                     },
@@ -57,8 +59,10 @@ nq_hadamard_kernel(const T* __restrict__ x, const T* __restrict__ x2, T* __restr
         nq_fwht_groups_to_smem<T>(
             [&](int g, float v[8]) {
                 float u[8];
-                nq_load8<T>(x + row0 * n + (int64_t)g * 8, v);
-                nq_load8<T>(x2 + row0 * n + (int64_t)g * 8, u);
+                const int r = (g * 8) / n;
+                const int64_t at = (row0 + r) * in_stride + (g * 8 - r * n);
+                nq_load8<T>(x + at, v);
+                nq_load8<T>(x2 + at, u);
                 nq_silu_mul8<T>(v, u);
             },
             buf, total, n);
@@ -76,7 +80,8 @@ nq_hadamard_kernel(const T* __restrict__ x, const T* __restrict__ x2, T* __restr
 }
 
 template <typename T, bool SILU_MUL = false>
-int launch_hadamard(const void* x, void* out, int64_t rows, int64_t n, cudaStream_t stream, const void* x2 = nullptr) {
+int launch_hadamard(const void* x, void* out, int64_t rows, int64_t n, cudaStream_t stream, const void* x2 = nullptr,
+                    int64_t in_stride = 0) {
     int rpc = (int)(n >= 2048 ? 1 : 2048 / n);
     // rows are held as float32, or (16-bit dtypes, packed path) in their own dtype
     const size_t smem = (size_t)rpc * n * ((sizeof(T) == 2 && n >= 16) ? sizeof(T) : sizeof(float));
@@ -101,7 +106,8 @@ int launch_hadamard(const void* x, void* out, int64_t rows, int64_t n, cudaStrea
         if (grid >= 8 * (int64_t)nq_sm_count()) threads = 128u;
     }
     kernel<<<(unsigned)grid, threads, smem, stream>>>(reinterpret_cast<const T*>(x), reinterpret_cast<const T*>(x2),
-                                                  reinterpret_cast<T*>(out), rows, (int)n, rpc, root, 1.0f / root);
+                                                  in_stride, reinterpret_cast<T*>(out), rows, (int)n, rpc, root,
+                                                  1.0f / root);
     NQ_CHECK_LAUNCH("nq_hadamard");
     return NQ_OK;
 }
@@ -125,19 +131,21 @@ extern "C" int nq_hadamard(const void* x, void* out, int dtype, int64_t rows, in
 
 // hadamard(silu(gate) * up) in one launch: the input of a Llama down_proj whose rows are too long for the
 // rotation inside the encoder.  Same bits as the two tensor ops followed by nq_hadamard.
-extern "C" int nq_hadamard_silu_mul(const void* gate, const void* up, void* out, int dtype, int64_t rows, int64_t n,
-                                    nq_stream_t stream) {
+extern "C" int nq_hadamard_silu_mul(const void* gate, const void* up, int64_t row_stride, void* out, int dtype,
+                                    int64_t rows, int64_t n, nq_stream_t stream) {
     NQ_RANGE("nq_hadamard_silu_mul");
     NQ_REQUIRE(gate && up && out, NQ_ERR_ARG, "nq_hadamard_silu_mul: null pointer");
     NQ_REQUIRE(rows >= 1 && n >= 8 && n <= 32768 && (n & (n - 1)) == 0, NQ_ERR_ARG,
                "nq_hadamard_silu_mul: n=%lld must be a power of two in [8, 32768]", (long long)n);
-    NQ_REQUIRE(nq_aligned16(gate) && nq_aligned16(up) && nq_aligned16(out), NQ_ERR_ALIGN,
-               "nq_hadamard_silu_mul: 16-byte alignment required");
+    const int64_t esize = dtype == NQ_F32 ? 4 : 2;
+    NQ_REQUIRE(row_stride >= n, NQ_ERR_ARG, "nq_hadamard_silu_mul: row_stride < n");
+    NQ_REQUIRE(nq_aligned16(gate) && nq_aligned16(up) && nq_aligned16(out) && (row_stride * esize) % 16 == 0, NQ_ERR_ALIGN,
+               "nq_hadamard_silu_mul: 16-byte alignment required (pointers and row stride)");
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     switch (dtype) {
-        case NQ_F32: return launch_hadamard<float, true>(gate, out, rows, n, s, up);
-        case NQ_BF16: return launch_hadamard<__nv_bfloat16, true>(gate, out, rows, n, s, up);
-        case NQ_F16: return launch_hadamard<__half, true>(gate, out, rows, n, s, up);
+        case NQ_F32: return launch_hadamard<float, true>(gate, out, rows, n, s, up, row_stride);
+        case NQ_BF16: return launch_hadamard<__nv_bfloat16, true>(gate, out, rows, n, s, up, row_stride);
+        case NQ_F16: return launch_hadamard<__half, true>(gate, out, rows, n, s, up, row_stride);
         default: nq_set_error("nq_hadamard_silu_mul: unknown dtype %d", dtype); return NQ_ERR_ARG;
     }
 }

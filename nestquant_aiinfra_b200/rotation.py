@@ -58,11 +58,21 @@ def hadamard_silu_mul(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     if (gate.device.type != "cuda" or gate.dtype not in _DTYPE_TAG or n < 8 or n > 32768 or n & (n - 1)
             or gate.numel() == 0):
         return hadamard(torch.nn.functional.silu(gate) * up)
-    a, b = gate.contiguous(), up.contiguous()
-    out = torch.empty_like(a)
+    # rows a fixed distance apart (column ranges of one stacked gate/up result) are read in place
+    esize = gate.element_size()
+    try:
+        a, b = gate.view(-1, n), up.view(-1, n)
+        strided = (a.stride(1) == 1 and b.stride() == a.stride() and (a.shape[0] == 1 or a.stride(0) >= n)
+                   and (a.stride(0) * esize) % 16 == 0 and a.data_ptr() % 16 == 0 and b.data_ptr() % 16 == 0)
+    except RuntimeError:  # the leading axes do not collapse into rows of one stride
+        strided = False
+    if not strided:
+        a, b = gate.contiguous().view(-1, n), up.contiguous().view(-1, n)
+    row_stride = max(int(a.stride(0)), n) if a.shape[0] > 1 else n
+    out = torch.empty(gate.shape, dtype=gate.dtype, device=gate.device)
     status = _lib.lib().nq_hadamard_silu_mul(
-        ctypes.c_void_p(a.data_ptr()), ctypes.c_void_p(b.data_ptr()), ctypes.c_void_p(out.data_ptr()),
-        _DTYPE_TAG[gate.dtype], ctypes.c_int64(a.numel() // n), ctypes.c_int64(n),
+        ctypes.c_void_p(a.data_ptr()), ctypes.c_void_p(b.data_ptr()), ctypes.c_int64(row_stride),
+        ctypes.c_void_p(out.data_ptr()), _DTYPE_TAG[gate.dtype], ctypes.c_int64(gate.numel() // n), ctypes.c_int64(n),
         ctypes.c_void_p(torch.cuda.current_stream(gate.device).cuda_stream))
     _lib.check(status, "hadamard_silu_mul")
     return out

@@ -41,6 +41,8 @@ def test_hadamard_of_the_silu_product_in_one_launch(rows, n, dtype):
     expected = hadamard(torch.nn.functional.silu(gate) * up)
     got = hadamard_silu_mul(gate, up)
     assert got.dtype == dtype and torch.equal(got, expected)
+    stacked = torch.cat([gate, up], dim=-1).unsqueeze(1)                           # column ranges of one result: read in place
+    assert torch.equal(hadamard_silu_mul(stacked[..., :n], stacked[..., n:]), expected.unsqueeze(1))
     blocked = hadamard_silu_mul(gate.view(rows, -1, 8), up.view(rows, -1, 8))   # block-diagonal: rows of 8
     assert torch.equal(blocked, hadamard((torch.nn.functional.silu(gate) * up).view(rows, -1, 8)))
 
