@@ -84,6 +84,31 @@ def test_reference_engine_drives_this_runner_through_a_continuous_batch(referenc
     assert read_status() == 0
 
 
+def test_reference_engine_gets_the_same_tokens_with_the_weight_decode_ahead(reference):
+    """Eight slots, so that the logits graph of the engine protocol decodes weights on the second stream: the
+    reference's engine generates exactly the tokens it generates with every step on one stream."""
+    from nestquant.runtime.inference_engine import ContinuousBatchInferenceEngine
+
+    from nestquant_aiinfra_b200.engine import BatchedNQKVLlamaRunner
+
+    spec = [(3, 20), (40, 4), (17, 33), (5, 2), (31, 18), (9, 9), (16, 17), (22, 25), (7, 30), (12, 6), (28, 11)]
+    generated = []
+    for ahead in (False, True):
+        model, cache = _tiny(capacity=8)
+        runner = BatchedNQKVLlamaRunner(model, cache, weight_decode_ahead=ahead)
+        engine = ContinuousBatchInferenceEngine(runner, pad_token_id=0)
+        requests = _requests(reference, spec)
+        _run(engine, requests)
+        assert runner.graph_captured and (cache.decode_ahead is not None) == ahead
+        if ahead:
+            assert cache.decode_ahead.launches > 0
+        generated.append([tuple(r.generated_token_ids) for r in requests])
+    assert generated[0] == generated[1]
+    from nestquant_aiinfra_b200.runtime import read_status
+
+    assert read_status() == 0
+
+
 def test_engine_protocol_prefill_equals_the_device_sampling_path(reference):
     """Same rows, same widths, same kernels: the protocol's logits give the tokens the device-side path samples,
     and both leave the same pages and hot tails behind."""
