@@ -138,6 +138,9 @@ class BatchedNQKVLlamaRunner:
         # second stream while the attention runs (``enable_weight_decode_ahead``; bit-identical results, one
         # layer's decoded weights of scratch).  False keeps every step on one stream.
         self.weight_decode_ahead = bool(weight_decode_ahead)
+        # scratch of a switched-off decode-ahead: a graph captured earlier may still write to it when replayed
+        self._retired_decode_ahead: list = []
+        self._idle_decode_ahead = None  # switched off by the user: attached again when switched back on
         # "last": prefill_slots evaluates the lm_head at the last prompt token of every row only and returns a
         # [capacity, width, vocab] VIEW whose columns all alias that row's logits (no memory), which is what a
         # sampler reads; "all" materialises the logits of every position as the reference does.
@@ -444,18 +447,31 @@ class BatchedNQKVLlamaRunner:
 
     def disable_weight_decode_ahead(self) -> None:
         self.weight_decode_ahead = False
-        if self.cache.decode_ahead is None:
-            return
-        self.cache.decode_ahead.detach()
-        self.cache.decode_ahead = None
+        self._retire_decode_ahead(reusable=True)
         self._recapture()
+
+    def _retire_decode_ahead(self, reusable: bool = False) -> None:
+        ahead = self.cache.decode_ahead or (None if reusable else self._idle_decode_ahead)
+        if ahead is None:
+            return
+        ahead.detach()
+        self.cache.decode_ahead = None
+        if reusable:
+            self._idle_decode_ahead = ahead
+        else:
+            self._idle_decode_ahead = None
+            self._retired_decode_ahead.append(ahead)
 
     def _ensure_decode_ahead(self) -> None:
         if not self.weight_decode_ahead or self.cache.decode_ahead is not None:
             return
         if self.batch_size < WeightDecodeAhead.MIN_ROWS:
             return
-        ahead = WeightDecodeAhead(self.model.model.layers, self.device)
+        if self._idle_decode_ahead is not None:
+            ahead, self._idle_decode_ahead = self._idle_decode_ahead, None
+            ahead.attach()
+        else:
+            ahead = WeightDecodeAhead(self.model.model.layers, self.device)
         if any(ahead.layers):
             self.cache.decode_ahead = ahead
 
@@ -468,10 +484,7 @@ class BatchedNQKVLlamaRunner:
     # Both change which kernels a step launches, so a captured graph is captured again.
     def keep_decoded_weights(self) -> int:
         """Keep the decoded BF16 weights of every packed projection resident; returns the bytes added."""
-        ahead = self.cache.decode_ahead is not None
-        if ahead:  # nothing is left to decode ahead: the units would point at weights that are replaced now
-            self.cache.decode_ahead.detach()
-            self.cache.decode_ahead = None
+        self._retire_decode_ahead()  # nothing is left to decode ahead, and the units point at weights replaced now
         added = keep_decoded_weights_(self.model)
         if self.graph is not None:
             self.capture_decode_graph()

@@ -519,6 +519,11 @@ class WeightDecodeAhead:
                 unit.owner._ahead = None
                 unit.armed = False
 
+    def attach(self) -> None:
+        for units in self.layers:
+            for unit in units:
+                unit.owner._ahead = unit
+
 
 def keep_decoded_weights_(model: nn.Module, device: torch.device | str | None = None) -> int:
     """Switch every ``FusedNQRTLinear`` of ``model`` to resident decoded weights; returns the bytes added.
