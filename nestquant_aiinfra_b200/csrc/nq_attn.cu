@@ -1,13 +1,15 @@
 // Paged GQA attention that reads NQKV4 pages directly (decode and chunked
-// causal prefill).  One CTA owns one (query token, KV head, page-range split):
-// every K/V vector is decoded ONCE for all query heads of its GQA group, with
-// the exact codec arithmetic (undithered streams have real Voronoi ties), FP32
-// online softmax, and a BF16 hot tail as the last "page".  No page-count cap.
+// causal prefill).  One CTA owns one (query token or tile of query tokens, KV
+// head, page-range split): every K/V vector is decoded ONCE for all query rows
+// of the CTA -- the heads of its GQA group, times the tokens of a prefill
+// tile -- with the exact codec arithmetic (undithered streams have real Voronoi
+// ties, see the table-driven decode in nq_e8.cuh), FP32 online softmax, and a
+// BF16 hot tail as the last "page".  No page-count cap.
 //
-// Lane mapping: a warp covers 32 / (D/8) tokens per step; lane = (token, E8
-// block of the head vector).  Score = shuffle-reduced dot over the D/8 lanes of
-// a token.  Split partials (m, l, acc[D]) are merged by a second small kernel
-// (skipped when there is a single split).
+// Lane mapping: one cached token per lane (a warp covers 32 consecutive token
+// positions per step); the kernel's own comment below describes the passes.
+// Split partials (m, l, acc[D]) are merged by a second small kernel (skipped
+// when there is a single split).
 //
 // Replaces runtime/nqkv_attention_k1.py:243-471 (page / hot / reduce Triton
 // kernels, 127-page cap at :807-809) and adds the page-reading prefill the
