@@ -258,12 +258,16 @@ int nq_w4a4_gemm_resident(const uint8_t* act_codes, const uint8_t* act_beta_ids,
  *           (_launch_append_hot_k1_graph_safe, runtime/nqkv_graph_writer.py:291-332)
  *   mode 1  key/value [B, T, H, D], mask = prefix write_mask[B, T]  (:373-419)
  *   mode 2  key/value [B, T, H, D], per-row (source_starts, segment_counts)  (:422-473)
- * Active slot ids must be unique (the reference's control plane guarantees it). */
+ * Active slot ids must be unique (the reference's control plane guarantees it).
+ * key_row_stride / value_row_stride: elements between the batch rows b and b + 1 of key / value, 0 = dense
+ * (T * H * D); a row itself is contiguous.  With a stride the V rows of a stacked q/k/v projection result are
+ * read where they are. */
 int nq_kv_append(const void* key, const void* value, int kv_dtype, int batch, int tokens, int mode,
                  const int32_t* slot_ids, const uint8_t* mask, const int32_t* source_starts,
                  const int32_t* segment_counts, const uint8_t* cache_active, void* hot_keys,
                  void* hot_values, int32_t* hot_lengths, int32_t* sequence_lengths, int max_sequences,
-                 int page_size, int heads, int dim, nq_stream_t stream);
+                 int page_size, int heads, int dim, int64_t key_row_stride, int64_t value_row_stride,
+                 nq_stream_t stream);
 
 /* For every slot with boundary_mask[s] && hot_lengths[s] == P: encode its hot page, store the six
  * payload rows at pool[target_page_ids[s]], append the page id to the page table, set

@@ -29,6 +29,7 @@ struct AppendParams {
     int32_t* hot_lengths;
     int32_t* sequence_lengths;
     int max_sequences, page_size, vec_per_token;  // vec_per_token = H * D * elem / 16
+    int64_t key_row_vecs, value_row_vecs;         // 16-byte vectors between the rows b and b + 1 of key / value
 };
 
 __global__ void __launch_bounds__(256) nq_kv_append_kernel(const AppendParams p) {
@@ -69,10 +70,10 @@ __global__ void __launch_bounds__(256) nq_kv_append_kernel(const AppendParams p)
         }
         const int dst = hot_len + local;
         if (!ok || dst >= p.page_size) continue;
-        const int64_t s_off = ((int64_t)b * p.tokens + src) * p.vec_per_token + v;
+        const int64_t in_row = (int64_t)src * p.vec_per_token + v;
         const int64_t d_off = ((int64_t)slot * p.page_size + dst) * p.vec_per_token + v;
-        p.hot_keys[d_off] = __ldg(p.key + s_off);
-        p.hot_values[d_off] = __ldg(p.value + s_off);
+        p.hot_keys[d_off] = __ldg(p.key + b * p.key_row_vecs + in_row);
+        p.hot_values[d_off] = __ldg(p.value + b * p.value_row_vecs + in_row);
     }
     if (threadIdx.x == 0 && commit) {
         p.hot_lengths[slot] = hot_len + count;
@@ -300,7 +301,8 @@ extern "C" int nq_kv_append(const void* key, const void* value, int kv_dtype, in
                             const int32_t* slot_ids, const uint8_t* mask, const int32_t* source_starts,
                             const int32_t* segment_counts, const uint8_t* cache_active, void* hot_keys,
                             void* hot_values, int32_t* hot_lengths, int32_t* sequence_lengths, int max_sequences,
-                            int page_size, int heads, int dim, nq_stream_t stream) {
+                            int page_size, int heads, int dim, int64_t key_row_stride, int64_t value_row_stride,
+                            nq_stream_t stream) {
     NQ_RANGE("nq_kv_append");
     NQ_REQUIRE(key && value && slot_ids && cache_active && hot_keys && hot_values && hot_lengths && sequence_lengths,
                NQ_ERR_ARG, "nq_kv_append: null pointer");
@@ -324,6 +326,13 @@ extern "C" int nq_kv_append(const void* key, const void* value, int kv_dtype, in
     p.hot_lengths = hot_lengths; p.sequence_lengths = sequence_lengths;
     p.max_sequences = max_sequences; p.page_size = page_size;
     p.vec_per_token = heads * dim * esize / 16;
+    const int64_t dense = (int64_t)tokens * heads * dim;  // elements of one row [T, H, D]
+    NQ_REQUIRE((key_row_stride == 0 || key_row_stride >= dense) && (value_row_stride == 0 || value_row_stride >= dense),
+               NQ_ERR_ARG, "nq_kv_append: a row stride is smaller than a row");
+    NQ_REQUIRE((key_row_stride * esize) % 16 == 0 && (value_row_stride * esize) % 16 == 0, NQ_ERR_ALIGN,
+               "nq_kv_append: row strides must be multiples of 16 bytes");
+    p.key_row_vecs = (key_row_stride ? key_row_stride : dense) * esize / 16;
+    p.value_row_vecs = (value_row_stride ? value_row_stride : dense) * esize / 16;
     nq_kv_append_kernel<<<batch, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);
     NQ_CHECK_LAUNCH("nq_kv_append");
     return NQ_OK;

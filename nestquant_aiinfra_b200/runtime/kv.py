@@ -27,6 +27,7 @@ from .. import _lib
 from .w4a4 import _DTYPE_TAG, _ptr, _stream
 
 _INT = ctypes.c_int
+_I64 = ctypes.c_int64
 
 
 def _betas(values: Sequence[float]) -> tuple[float, ...]:
@@ -337,6 +338,23 @@ def quantize_nqkv_page_cuda(key: torch.Tensor, value: torch.Tensor, *, page_size
 
 
 # --------------------------------------------------------------------------- writers
+def _rows_in_place(tensor: torch.Tensor) -> tuple[torch.Tensor, int]:
+    """``(tensor, row_stride)`` for the append kernel: rows (the first axis) that are contiguous inside but lie a
+    fixed distance apart -- the K or V columns of a stacked projection result -- are read where they are
+    (stride in elements); anything else is made dense first (stride 0)."""
+    if tensor.is_contiguous():
+        return tensor, 0
+    inner = 1
+    for size, stride in zip(reversed(tensor.shape[1:]), reversed(tensor.stride()[1:])):
+        if size != 1 and stride != inner:
+            return tensor.contiguous(), 0
+        inner *= size
+    row = tensor.stride(0)
+    if tensor.shape[0] > 1 and (row < inner or (row * tensor.element_size()) % 16 or tensor.data_ptr() % 16):
+        return tensor.contiguous(), 0
+    return tensor, int(row) if tensor.shape[0] > 1 else 0
+
+
 def _append(cache: NQKVHotColdCache, key: torch.Tensor, value: torch.Tensor, mode: int, slot_ids: torch.Tensor,
             mask: torch.Tensor | None, source_starts: torch.Tensor | None, segment_counts: torch.Tensor | None,
             what: str) -> None:
@@ -353,12 +371,14 @@ def _append(cache: NQKVHotColdCache, key: torch.Tensor, value: torch.Tensor, mod
         (batch, tokens, pool.num_kv_heads, pool.head_dim)
     if tuple(key.shape) != expected:
         raise ValueError(f"key and value must have shape {expected}")
-    key, value = key.contiguous(), value.contiguous()
+    key, key_stride = _rows_in_place(key)
+    value, value_stride = _rows_in_place(value)
     status = _lib.lib().nq_kv_append(
         _ptr(key), _ptr(value), _DTYPE_TAG[key.dtype], _INT(batch), _INT(tokens), _INT(mode), _ptr(slot_ids),
         _ptr(mask), _ptr(source_starts), _ptr(segment_counts), _ptr(cache.active), _ptr(cache.hot_keys),
         _ptr(cache.hot_values), _ptr(cache.hot_lengths), _ptr(cache.sequence_lengths), _INT(cache.max_sequences),
-        _INT(pool.page_size), _INT(pool.num_kv_heads), _INT(pool.head_dim), _stream(pool.device))
+        _INT(pool.page_size), _INT(pool.num_kv_heads), _INT(pool.head_dim), _I64(key_stride), _I64(value_stride),
+        _stream(pool.device))
     _lib.check(status, what)
 
 

@@ -223,6 +223,29 @@ def test_decode_attention_argument_errors(rt):
         rt.nqkv_decode_attention_batched_k1(q, cache, slot_ids=ids.long(), active_mask=on)
 
 
+def test_append_reads_rows_of_a_stacked_projection_in_place(rt):
+    """K1 append with K and V as column ranges of one [B, q + k + v] result (row stride, no copy) writes the
+    same hot tails as with dense tensors."""
+    tails = []
+    for strided in (False, True):
+        cache = make_cache(rt, slots=4, max_pages=2, heads=2)
+        for s in range(4):
+            cache.register(s)
+        slot_ids = torch.tensor([2, 0, 3, 1], dtype=torch.int32, device="cuda")
+        active = torch.tensor([True, True, False, True], device="cuda")
+        for step in range(3):
+            stacked = torch.randn(4, 256 + 128 + 128, generator=rng(300 + step)).bfloat16().cuda()
+            k = stacked[:, 256:384].view(4, 2, 64)
+            v = stacked[:, 384:].view(4, 2, 64)
+            assert not v.is_contiguous()
+            if not strided:
+                k, v = k.contiguous(), v.contiguous()
+            rt.append_hot_k1_graph_safe(k, v, cache, slot_ids=slot_ids, active_mask=active)
+        tails.append((cache.hot_keys.clone(), cache.hot_values.clone(), cache.hot_lengths.clone()))
+    assert tails[0][2].tolist() == [3, 3, 3, 0]
+    assert all(torch.equal(a, b) for a, b in zip(*tails))
+
+
 def test_prefill_attention_ragged_chunks_cross_pages(rt, oracle):
     lengths = [40, 16, 75, 5]
     cache = make_cache(rt, slots=4, max_pages=8)
