@@ -411,6 +411,14 @@ int nq_rope_hadamard(const void* x, int dtype, int64_t batch, int64_t heads, int
                      int64_t stride_b, int64_t stride_h, int64_t stride_t, const void* cos, const void* sin,
                      int apply_hadamard, void* out, nq_stream_t stream);
 
+/* The same for the query heads and the key heads of one attention layer in ONE launch: q [B, Hq, T, D] and
+ * k [B, Hk, T, D] of one dtype with their own element strides ({batch, head, token}, 16-byte multiples) and
+ * their own contiguous outputs; cos / sin [B, T, D] are shared. */
+int nq_rope_hadamard_pair(const void* q, const void* k, int dtype, int64_t batch, int64_t q_heads, int64_t k_heads,
+                          int64_t tokens, int64_t dim, const int64_t* q_strides, const int64_t* k_strides,
+                          const void* cos, const void* sin, int apply_hadamard, void* q_out, void* k_out,
+                          nq_stream_t stream);
+
 /* RMS normalisation of rows as Hugging Face's LlamaRMSNorm computes it, in one launch:
  *   out = weight * dtype(x * rsqrt(mean(x^2) + eps))      (mean and product in float32)
  * It precedes every rotate-then-encode launch of a decoder layer; the reference leaves it to

@@ -29,12 +29,16 @@ struct RopeParams {
     float root, inv_root;
 };
 
+// blockIdx.y selects the tensor: a launch takes the query heads and the key heads of a layer together
+// (second.vectors = 0 for a launch with one tensor).
 template <typename T>
-__global__ void __launch_bounds__(kRopeThreads) nq_rope_kernel(const RopeParams p) {
+__global__ void __launch_bounds__(kRopeThreads) nq_rope_kernel(const RopeParams first, const RopeParams second) {
     extern __shared__ __align__(16) float buf[];
+    const RopeParams& p = blockIdx.y ? second : first;
     const int bpr = p.dim >> 3;                        // groups of 8 features per vector
     const int vectors_per_cta = kRopeThreads / bpr;
     const int64_t v0 = (int64_t)blockIdx.x * vectors_per_cta;
+    if (v0 >= p.vectors) return;  // the grid is sized for the larger tensor
     const int nvec = (int)min((int64_t)vectors_per_cta, p.vectors - v0);
     const int total = nvec * p.dim;
     const T* x = reinterpret_cast<const T*>(p.x);
@@ -83,13 +87,45 @@ __global__ void __launch_bounds__(kRopeThreads) nq_rope_kernel(const RopeParams 
 }
 
 template <typename T>
-int launch_rope(const RopeParams& p, cudaStream_t s) {
+int launch_rope(const RopeParams& p, const RopeParams& second, cudaStream_t s) {
     const int vectors_per_cta = kRopeThreads / (p.dim >> 3);
-    const int64_t grid = (p.vectors + vectors_per_cta - 1) / vectors_per_cta;
+    const int64_t most = p.vectors > second.vectors ? p.vectors : second.vectors;
+    const int64_t grid = (most + vectors_per_cta - 1) / vectors_per_cta;
     const size_t smem = (size_t)vectors_per_cta * p.dim * sizeof(float);
-    nq_rope_kernel<T><<<(unsigned)grid, kRopeThreads, smem, s>>>(p);
+    nq_rope_kernel<T><<<dim3((unsigned)grid, second.vectors > 0 ? 2u : 1u), kRopeThreads, smem, s>>>(p, second);
     NQ_CHECK_LAUNCH("nq_rope_hadamard");
     return NQ_OK;
+}
+
+int rope_params(RopeParams& p, const char* what, const void* x, int dtype, int64_t batch, int64_t heads, int64_t tokens,
+                int64_t dim, int64_t stride_b, int64_t stride_h, int64_t stride_t, const void* cos, const void* sin,
+                int apply_hadamard, void* out) {
+    NQ_REQUIRE(x && cos && sin && out, NQ_ERR_ARG, "%s: null pointer", what);
+    NQ_REQUIRE(batch >= 1 && heads >= 1 && tokens >= 1, NQ_ERR_ARG, "%s: empty tensor", what);
+    NQ_REQUIRE(dim >= 16 && dim <= 1024 && (dim & (dim - 1)) == 0, NQ_ERR_ARG,
+               "%s: dim=%lld must be a power of two in [16, 1024]", what, (long long)dim);
+    NQ_REQUIRE(batch * heads * tokens <= ((int64_t)1 << 40), NQ_ERR_ARG, "%s: tensor too large", what);
+    const int64_t esize = dtype == NQ_F32 ? 4 : 2;
+    NQ_REQUIRE(nq_aligned16(x) && nq_aligned16(cos) && nq_aligned16(sin) && nq_aligned16(out) &&
+                   (stride_b * esize) % 16 == 0 && (stride_h * esize) % 16 == 0 && (stride_t * esize) % 16 == 0,
+               NQ_ERR_ALIGN, "%s: pointers and strides must be 16-byte aligned", what);
+    p.x = x; p.cos = cos; p.sin = sin; p.out = out;
+    p.vectors = batch * heads * tokens;
+    p.heads = (int)heads; p.tokens = (int)tokens; p.dim = (int)dim;
+    p.stride_b = stride_b; p.stride_h = stride_h; p.stride_t = stride_t;
+    p.apply_hadamard = apply_hadamard;
+    p.root = (float)sqrt((double)dim);
+    p.inv_root = 1.0f / p.root;
+    return NQ_OK;
+}
+
+int launch_rope_dtype(int dtype, const RopeParams& p, const RopeParams& second, cudaStream_t s) {
+    switch (dtype) {
+        case NQ_F32: return launch_rope<float>(p, second, s);
+        case NQ_BF16: return launch_rope<__nv_bfloat16>(p, second, s);
+        case NQ_F16: return launch_rope<__half>(p, second, s);
+        default: nq_set_error("nq_rope_hadamard: unknown dtype %d", dtype); return NQ_ERR_ARG;
+    }
 }
 
 }  // namespace
@@ -98,28 +134,27 @@ extern "C" int nq_rope_hadamard(const void* x, int dtype, int64_t batch, int64_t
                                 int64_t stride_b, int64_t stride_h, int64_t stride_t, const void* cos,
                                 const void* sin, int apply_hadamard, void* out, nq_stream_t stream) {
     NQ_RANGE("nq_rope_hadamard");
-    NQ_REQUIRE(x && cos && sin && out, NQ_ERR_ARG, "nq_rope_hadamard: null pointer");
-    NQ_REQUIRE(batch >= 1 && heads >= 1 && tokens >= 1, NQ_ERR_ARG, "nq_rope_hadamard: empty tensor");
-    NQ_REQUIRE(dim >= 16 && dim <= 1024 && (dim & (dim - 1)) == 0, NQ_ERR_ARG,
-               "nq_rope_hadamard: dim=%lld must be a power of two in [16, 1024]", (long long)dim);
-    NQ_REQUIRE(batch * heads * tokens <= ((int64_t)1 << 40), NQ_ERR_ARG, "nq_rope_hadamard: tensor too large");
-    const int64_t esize = dtype == NQ_F32 ? 4 : 2;
-    NQ_REQUIRE(nq_aligned16(x) && nq_aligned16(cos) && nq_aligned16(sin) && nq_aligned16(out) &&
-                   (stride_b * esize) % 16 == 0 && (stride_h * esize) % 16 == 0 && (stride_t * esize) % 16 == 0,
-               NQ_ERR_ALIGN, "nq_rope_hadamard: pointers and strides must be 16-byte aligned");
-    RopeParams p;
-    p.x = x; p.cos = cos; p.sin = sin; p.out = out;
-    p.vectors = batch * heads * tokens;
-    p.heads = (int)heads; p.tokens = (int)tokens; p.dim = (int)dim;
-    p.stride_b = stride_b; p.stride_h = stride_h; p.stride_t = stride_t;
-    p.apply_hadamard = apply_hadamard;
-    p.root = (float)sqrt((double)dim);
-    p.inv_root = 1.0f / p.root;
-    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-    switch (dtype) {
-        case NQ_F32: return launch_rope<float>(p, s);
-        case NQ_BF16: return launch_rope<__nv_bfloat16>(p, s);
-        case NQ_F16: return launch_rope<__half>(p, s);
-        default: nq_set_error("nq_rope_hadamard: unknown dtype %d", dtype); return NQ_ERR_ARG;
-    }
+    RopeParams p, none = {};
+    const int rc = rope_params(p, "nq_rope_hadamard", x, dtype, batch, heads, tokens, dim, stride_b, stride_h, stride_t,
+                               cos, sin, apply_hadamard, out);
+    if (rc) return rc;
+    return launch_rope_dtype(dtype, p, none, reinterpret_cast<cudaStream_t>(stream));
+}
+
+// The query heads and the key heads of one attention layer in ONE launch (same cos / sin, same dtype, same
+// batch, tokens and dim; each tensor with its own head count, strides and output).
+extern "C" int nq_rope_hadamard_pair(const void* q, const void* k, int dtype, int64_t batch, int64_t q_heads,
+                                     int64_t k_heads, int64_t tokens, int64_t dim, const int64_t* q_strides,
+                                     const int64_t* k_strides, const void* cos, const void* sin, int apply_hadamard,
+                                     void* q_out, void* k_out, nq_stream_t stream) {
+    NQ_RANGE("nq_rope_hadamard_pair");
+    NQ_REQUIRE(q_strides && k_strides, NQ_ERR_ARG, "nq_rope_hadamard_pair: null strides");
+    RopeParams pq, pk;
+    int rc = rope_params(pq, "nq_rope_hadamard_pair(q)", q, dtype, batch, q_heads, tokens, dim, q_strides[0], q_strides[1],
+                         q_strides[2], cos, sin, apply_hadamard, q_out);
+    if (rc) return rc;
+    rc = rope_params(pk, "nq_rope_hadamard_pair(k)", k, dtype, batch, k_heads, tokens, dim, k_strides[0], k_strides[1],
+                     k_strides[2], cos, sin, apply_hadamard, k_out);
+    if (rc) return rc;
+    return launch_rope_dtype(dtype, pq, pk, reinterpret_cast<cudaStream_t>(stream));
 }

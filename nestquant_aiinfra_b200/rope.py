@@ -60,11 +60,36 @@ def rope_hadamard(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, *, rota
     return out
 
 
+def rope_hadamard_pair(q: torch.Tensor, k: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, *,
+                       rotate: bool = True) -> tuple[torch.Tensor, torch.Tensor]:
+    """``rope_hadamard`` of the query heads and the key heads of one layer as ONE launch."""
+    if not (_usable(q, cos, sin) and _usable(k, cos, sin)) or q.dtype != k.dtype or q.shape[0] != k.shape[0] \
+            or q.shape[2:] != k.shape[2:] or q.device != k.device:
+        raise ValueError("rope_hadamard_pair needs q and k [B, H, T, D] of one dtype, batch, length and head size")
+    batch, q_heads, tokens, dim = q.shape
+    cos = cos.expand(batch, tokens, dim).contiguous()
+    sin = sin.expand(batch, tokens, dim).contiguous()
+    q_out = torch.empty((batch, q_heads, tokens, dim), dtype=q.dtype, device=q.device)
+    k_out = torch.empty((batch, k.shape[1], tokens, dim), dtype=k.dtype, device=k.device)
+    strides = lambda t: (ctypes.c_int64 * 3)(t.stride(0), t.stride(1), t.stride(2))  # noqa: E731
+    status = _lib.lib().nq_rope_hadamard_pair(
+        ctypes.c_void_p(q.data_ptr()), ctypes.c_void_p(k.data_ptr()), _DTYPE_TAG[q.dtype], ctypes.c_int64(batch),
+        ctypes.c_int64(q_heads), ctypes.c_int64(k.shape[1]), ctypes.c_int64(tokens), ctypes.c_int64(dim), strides(q),
+        strides(k), ctypes.c_void_p(cos.data_ptr()), ctypes.c_void_p(sin.data_ptr()), ctypes.c_int(1 if rotate else 0),
+        ctypes.c_void_p(q_out.data_ptr()), ctypes.c_void_p(k_out.data_ptr()),
+        ctypes.c_void_p(torch.cuda.current_stream(q.device).cuda_stream))
+    _lib.check(status, "rope_hadamard_pair")
+    return q_out, k_out
+
+
 def _apply_rotary_pos_emb(q, k, cos, sin, unsqueeze_dim=1):
     if (getattr(_state, "depth", 0) > 0 and unsqueeze_dim == 1 and isinstance(q, torch.Tensor)
             and not torch.is_grad_enabled() and _usable(q, cos, sin) and _usable(k, cos, sin)):
-        q_out = rope_hadamard(q, cos, sin)
-        k_out = rope_hadamard(k, cos, sin)
+        if q.dtype == k.dtype and q.shape[0] == k.shape[0] and q.shape[2:] == k.shape[2:]:
+            q_out, k_out = rope_hadamard_pair(q, k, cos, sin)
+        else:
+            q_out = rope_hadamard(q, cos, sin)
+            k_out = rope_hadamard(k, cos, sin)
         setattr(q_out, _MARK, True)
         setattr(k_out, _MARK, True)
         return q_out, k_out

@@ -172,6 +172,16 @@ def test_rope_and_rotation_in_one_launch_equal_the_tensor_ops(batch, heads, toke
     assert torch.equal(rope_hadamard(x, cos, sin, rotate=False), stock)
     assert torch.equal(rope_hadamard(x, cos, sin), hadamard(stock.float()).to(dtype))
     assert torch.equal(rope_hadamard(x[:1], cos[:1], sin[:1]), rope_hadamard(x, cos, sin)[:1])
+    # query and key heads of a layer in one launch: column ranges of one stacked [B, T, (Hq + Hk) * D] result
+    from nestquant_aiinfra_b200.rope import rope_hadamard_pair
+
+    both = torch.randn(batch, tokens, 3 * heads * dim, generator=rng(302 + dim)).to(dtype).cuda()
+    q = both[..., :2 * heads * dim].view(batch, tokens, 2 * heads, dim).transpose(1, 2)
+    k = both[..., 2 * heads * dim:].view(batch, tokens, heads, dim).transpose(1, 2)
+    for rotate in (False, True):
+        q_out, k_out = rope_hadamard_pair(q, k, cos, sin, rotate=rotate)
+        assert torch.equal(q_out, rope_hadamard(q, cos, sin, rotate=rotate))
+        assert torch.equal(k_out, rope_hadamard(k, cos, sin, rotate=rotate))
 
 
 def test_stacked_projection_group_equals_the_members_own_projections(oracle):
