@@ -471,7 +471,10 @@ class BatchedNQKVLlamaRunner:
             ahead, self._idle_decode_ahead = self._idle_decode_ahead, None
             ahead.attach()
         else:
-            ahead = WeightDecodeAhead(self.model.model.layers, self.device)
+            layers = getattr(getattr(self.model, "model", None), "layers", None)
+            if layers is None:  # not a decoder stack this runner knows how to walk: every step stays on one stream
+                return
+            ahead = WeightDecodeAhead(layers, self.device)
         if any(ahead.layers):
             self.cache.decode_ahead = ahead
 
