@@ -274,7 +274,9 @@ int nq_kv_append(const void* key, const void* value, int kv_dtype, int batch, in
  * last_page_lens = P and hot_lengths = 0.  A slot whose page table is full (page_counts ==
  * max_pages) or whose target id lies outside [0, pool_capacity) is left untouched: nothing is
  * written to the pool and nothing is published, its hot tail stays full.  Only the selected slots
- * are encoded.  Payload bytes equal PackedNQKVPage.from_tensors
+ * are encoded.  target_page_ids may be null for a pool that is a fixed partition of max_pages pages
+ * per slot: slot s then packs into page s * max_pages + page_counts[s] (no id array to refresh per
+ * step).  Payload bytes equal PackedNQKVPage.from_tensors
  * (core/kv_format.py:71-131).  Replaces launch_pack_full_hot_pages_graph_safe
  * (runtime/nqkv_graph_pack.py:76-135: encode of all slots + 6 copies + publish). */
 int nq_kv_pack_publish(const void* hot_keys, const void* hot_values, int kv_dtype, int32_t* hot_lengths,

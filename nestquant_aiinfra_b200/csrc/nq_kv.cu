@@ -87,7 +87,7 @@ struct PackParams {
     const void* hot_values;
     const int32_t* hot_lengths;
     const uint8_t* boundary_mask;    // [S]
-    const int32_t* target_page_ids;  // [S]
+    const int32_t* target_page_ids;  // [S], or null: static ids slot * max_pages + page_counts[slot]
     uint8_t *key_codes, *key_betas, *value_codes, *value_betas;  // pool streams [capacity, bytes per page]
     float *key_norms, *value_norms;                                // [capacity, P*H]
     const float *key_beta_table, *value_beta_table;
@@ -105,8 +105,14 @@ struct PackParams {
 // pack-and-publish call use this one predicate, so a page is never written without being published
 // (a slot whose table is full must not touch the pool: with caller-computed ids its "next" id may
 // belong to another sequence) and never published without having been written.
+// The page a slot packs into: the caller's id, or (no id array) the slot's own next page of a pool that is a fixed
+// partition of max_pages per slot.  page_counts only changes in the publish kernel, after every reader.
+__device__ __forceinline__ int nq_pack_target(const PackParams& p, int slot) {
+    return p.target_page_ids ? p.target_page_ids[slot] : slot * p.max_pages + p.page_counts[slot];
+}
+
 __device__ __forceinline__ bool nq_pack_selected(const PackParams& p, int slot) {
-    const int page_id = p.target_page_ids[slot];
+    const int page_id = nq_pack_target(p, slot);
     return p.boundary_mask[slot] != 0 && p.hot_lengths[slot] == p.page_size && p.page_counts[slot] < p.max_pages &&
            page_id >= 0 && page_id < p.pool_capacity;
 }
@@ -130,7 +136,7 @@ __device__ __forceinline__ void nq_expand_block(const uint32_t* codes, int8_t* l
 __global__ void __launch_bounds__(256) nq_kv_expand_packed_kernel(const PackParams p) {
     const int slot = blockIdx.x;
     if (!nq_pack_selected(p, slot)) return;
-    const int page_id = p.target_page_ids[slot];
+    const int page_id = nq_pack_target(p, slot);
     const int blocks = p.page_size * p.heads * (p.dim >> 3);
     const bool is_value = blockIdx.y != 0;
     const uint32_t* codes = reinterpret_cast<const uint32_t*>(is_value ? p.value_codes : p.key_codes) +
@@ -156,7 +162,7 @@ __global__ void __launch_bounds__(NQ_ENC_THREADS, 5) nq_kv_pack_pages_kernel(con
     extern __shared__ __align__(16) float smem[];
     const int slot = blockIdx.x;
     if (!nq_pack_selected(p, slot)) return;  // CTA-uniform
-    const int page_id = p.target_page_ids[slot];
+    const int page_id = nq_pack_target(p, slot);
     const int is_value = blockIdx.y / p.ctas_per_stream;
     const int chunk = blockIdx.y - is_value * p.ctas_per_stream;
     const int rows = p.page_size * p.heads, rpc = nq_encode_rows_per_cta(p.dim), bpr = p.dim >> 3;
@@ -178,7 +184,7 @@ __global__ void __launch_bounds__(256) nq_kv_publish_kernel(const PackParams p) 
     if (slot >= p.max_sequences) return;
     if (!nq_pack_selected(p, slot)) return;
     const int count = p.page_counts[slot];
-    p.page_indices[(int64_t)slot * p.max_pages + count] = p.target_page_ids[slot];
+    p.page_indices[(int64_t)slot * p.max_pages + count] = nq_pack_target(p, slot);
     p.page_counts[slot] = count + 1;
     p.last_page_lens[slot] = p.page_size;
     p.hot_lengths_rw[slot] = 0;
@@ -346,7 +352,7 @@ static int kv_pack_publish_impl(const void* hot_keys, const void* hot_values, in
                                 int32_t* last_page_lens, int max_sequences, int max_pages, int pool_capacity,
                                 int page_size, int heads, int dim, int8_t* key_lattice, int8_t* value_lattice,
                                 nq_stream_t stream) {
-    NQ_REQUIRE(hot_keys && hot_values && hot_lengths && boundary_mask && target_page_ids && key_codes && key_betas &&
+    NQ_REQUIRE(hot_keys && hot_values && hot_lengths && boundary_mask && key_codes && key_betas &&
                    key_norms && value_codes && value_betas && value_norms && key_beta_table && value_beta_table &&
                    page_indices && page_counts && last_page_lens,
                NQ_ERR_ARG, "nq_kv_pack_publish: null pointer");

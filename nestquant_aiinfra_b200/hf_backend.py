@@ -405,9 +405,9 @@ class BatchedNQKVLlamaCache(Cache):
         mask = self._all_slots if mask is None else mask
         if self.page_allocation == "device":
             cache.device_alloc_targets(mask)   # pops a page for every slot that is about to pack
-        else:
-            torch.add(self._page_base, cache.page_counts, out=cache.graph_target_page_ids)
-        launch_pack_full_hot_pages_graph_safe(cache, boundary_mask=mask)
+        # static ids (slot * max_pages + page_counts) are formed inside the pack kernels: no id tensor to refresh
+        launch_pack_full_hot_pages_graph_safe(cache, boundary_mask=mask,
+                                              static_page_ids=self.page_allocation != "device")
 
     def update(self, key_states: torch.Tensor, value_states: torch.Tensor, layer_idx: int, cache_kwargs=None):
         self._validate_layer(layer_idx)

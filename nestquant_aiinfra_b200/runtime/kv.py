@@ -412,8 +412,11 @@ append_hot_k1_graph_safe = _launch_append_hot_k1_graph_safe
 
 
 def launch_pack_full_hot_pages_graph_safe(cache: NQKVHotColdCache, *, boundary_mask: torch.Tensor,
-                                          batched_encode: bool = True) -> None:
-    """Encode and publish the full hot pages of the boundary-selected slots (nqkv_graph_pack.py:76-135)."""
+                                          batched_encode: bool = True, static_page_ids: bool = False) -> None:
+    """Encode and publish the full hot pages of the boundary-selected slots (nqkv_graph_pack.py:76-135).
+
+    ``static_page_ids=True``: the pool is a fixed partition of ``max_pages_per_sequence`` pages per slot and slot
+    ``s`` packs into page ``s * max_pages + page_counts[s]``; ``cache.graph_target_page_ids`` is not read."""
     pool = cache.pool
     if boundary_mask.dtype != torch.bool or tuple(boundary_mask.shape) != (cache.max_sequences,):
         raise ValueError("boundary_mask must be bool with cache capacity shape")
@@ -421,7 +424,8 @@ def launch_pack_full_hot_pages_graph_safe(cache: NQKVHotColdCache, *, boundary_m
         raise ValueError("boundary_mask must be on the cache device")
     args = [
         _ptr(cache.hot_keys), _ptr(cache.hot_values), _DTYPE_TAG[pool.output_dtype], _ptr(cache.hot_lengths),
-        _ptr(boundary_mask), _ptr(cache.graph_target_page_ids), _ptr(pool.key_codes), _ptr(pool.key_betas),
+        _ptr(boundary_mask), _ptr(None if static_page_ids else cache.graph_target_page_ids), _ptr(pool.key_codes),
+        _ptr(pool.key_betas),
         _ptr(pool.key_norms), _ptr(pool.value_codes), _ptr(pool.value_betas), _ptr(pool.value_norms),
         _ptr(pool.beta_table), _ptr(pool.value_beta_table), _ptr(cache.page_indices), _ptr(cache.page_counts),
         _ptr(cache.last_page_len), _INT(cache.max_sequences), _INT(cache.max_pages_per_sequence),
