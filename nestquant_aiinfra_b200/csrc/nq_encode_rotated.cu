@@ -39,10 +39,10 @@ nq_encode_rotated_kernel(const T* __restrict__ x, const T* __restrict__ x2, int6
     const int64_t row0 = (int64_t)blockIdx.x * rpc;
     const int nrows = (int)min((int64_t)rpc, rows - row0);
     const int total = nrows * k;
-    // 16-bit dtypes: packed butterflies on the rows in their own dtype, held in the upper half of `rotated`
-    // until they are handed to the encoder as float32 (nq_fwht_packed_to_floats)
+    // 16-bit dtypes: packed butterflies on the rows in their own dtype, held at the end of `rotated` until they
+    // are handed to the encoder as float32 (nq_fwht_packed_to_floats)
     const bool packed = sizeof(T) == 2 && hadamard_block >= 16;
-    uint32_t* words = reinterpret_cast<uint32_t*>(rotated + (total >> 1));
+    uint32_t* words = nq_fwht_words_in_place(rotated, total);
     if (MODE == kPlain) {
         if constexpr (sizeof(T) == 2) {
             if (packed) nq_fwht_rows_packed<T>(x + row0 * k, words, total, hadamard_block);

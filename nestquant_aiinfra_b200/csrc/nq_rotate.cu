@@ -84,7 +84,8 @@ int launch_hadamard(const void* x, void* out, int64_t rows, int64_t n, cudaStrea
                     int64_t in_stride = 0) {
     int rpc = (int)(n >= 2048 ? 1 : 2048 / n);
     // rows are held as float32, or (16-bit dtypes, packed path) in their own dtype
-    const size_t smem = (size_t)rpc * n * ((sizeof(T) == 2 && n >= 16) ? sizeof(T) : sizeof(float));
+    const size_t smem = (sizeof(T) == 2 && n >= 16) ? (size_t)nq_fwht_padded_words(rpc * (int)n) * sizeof(uint32_t)
+                                                    : (size_t)rpc * n * sizeof(float);
     auto kernel = nq_hadamard_kernel<T, SILU_MUL>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -116,8 +116,10 @@ __device__ __forceinline__ void nq_fwht_rows_to_smem(const T* __restrict__ x, fl
 // A thread always works on TWO radix-8 groups at once, value j of both groups in one register, so
 // that all three stages of a pass combine different registers: in pass 0 the two groups are
 // neighbours (16 consecutive elements), in the later passes neighbouring columns, whose values are
-// already adjacent in memory (one 32-bit word).  Word addresses are XOR-swizzled (bits 2..4 with
-// bits 5..7) so that the pass with eight-element spacing is free of bank conflicts as well.
+// already adjacent in memory (one 32-bit word).  Every 32 words are followed by 4 words of padding
+// (word w lives at w + (w >> 5) * 4): the pass with eight-element spacing is then free of bank
+// conflicts as well, and since the spacing of every pass is 4 words or a multiple of 32 words the
+// addresses of a thread's values stay an arithmetic sequence (one add per access).
 template <typename T> struct NqPacked;
 template <> struct NqPacked<__nv_bfloat16> {
     using pair = __nv_bfloat162;
@@ -155,11 +157,13 @@ __device__ __forceinline__ void nq_butterflies_packed(uint32_t v[8]) {
     }
 }
 
-__device__ __forceinline__ int nq_fwht_swizzle(int word) { return word ^ (((word >> 5) & 7) << 2); }
+__device__ __forceinline__ int nq_fwht_pad(int word) { return word + ((word >> 5) << 2); }
+// words a padded buffer of `total` elements takes
+__host__ __device__ __forceinline__ int nq_fwht_padded_words(int total) { return (total >> 1) + (total >> 4) + 4; }
 
 // All butterfly stages of total / n rows of n elements (n a power of two >= 16, total a multiple of 16)
-// read from x; the result stays in `words` (total / 2 packed words at swizzled addresses, element
-// 2i in the low half of word i), NOT yet divided by sqrt(n).  Ends with a barrier.
+// read from x; the result stays in `words` (nq_fwht_padded_words(total) words, element 2i in the
+// low half of word i at its padded address), NOT yet divided by sqrt(n).  Ends with a barrier.
 // load(g) supplies the 8 consecutive elements of group g as four packed words.
 template <typename T, class Load>
 __device__ __forceinline__ void nq_fwht_groups_packed(Load&& load, uint32_t* words, int total, int n) {
@@ -185,37 +189,41 @@ __device__ __forceinline__ void nq_fwht_groups_packed(Load&& load, uint32_t* wor
         oa.y = __byte_perm(v[2], v[3], 0x5410); ob.y = __byte_perm(v[2], v[3], 0x7632);
         oa.z = __byte_perm(v[4], v[5], 0x5410); ob.z = __byte_perm(v[4], v[5], 0x7632);
         oa.w = __byte_perm(v[6], v[7], 0x5410); ob.w = __byte_perm(v[6], v[7], 0x7632);
-        *reinterpret_cast<uint4*>(words + nq_fwht_swizzle(8 * pg)) = oa;
-        *reinterpret_cast<uint4*>(words + nq_fwht_swizzle(8 * pg + 4)) = ob;
+        uint4* dst = reinterpret_cast<uint4*>(words + nq_fwht_pad(8 * pg));  // 8 words of one 32-word segment
+        dst[0] = oa;
+        dst[1] = ob;
     }
     __syncthreads();
     int done = 3;
     while (done < log_n) {
         const int stages = min(3, log_n - done);
-        const int wp = 1 << (done - 1);        // words between the values a thread combines (w / 2)
+        const int wp = 1 << (done - 1);        // words between the values a thread combines (w / 2): 4, 32, 256, ...
         const int spanw = wp << stages;        // words covered by one family of column pairs
         const int work = (total >> 1) >> stages;
+        // padded distance of wp words: a thread's 4-word steps stay inside one 32-word segment (its first word has
+        // bits 2..4 clear), larger steps are whole segments
+        const int step = wp >= 32 ? wp + (wp >> 3) : wp;
         for (int t = threadIdx.x; t < work; t += nthreads) {
-            const int base = (t / wp) * spanw + (t % wp);
+            uint32_t* mine = words + nq_fwht_pad((t / wp) * spanw + (t % wp));
             uint32_t v[8];
             if (stages == 3) {
 #pragma unroll
-                for (int j = 0; j < 8; ++j) v[j] = words[nq_fwht_swizzle(base + j * wp)];
+                for (int j = 0; j < 8; ++j) v[j] = mine[j * step];
                 nq_butterflies_packed<T, 3>(v);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) words[nq_fwht_swizzle(base + j * wp)] = v[j];
+                for (int j = 0; j < 8; ++j) mine[j * step] = v[j];
             } else if (stages == 2) {
 #pragma unroll
-                for (int j = 0; j < 4; ++j) v[j] = words[nq_fwht_swizzle(base + j * wp)];
+                for (int j = 0; j < 4; ++j) v[j] = mine[j * step];
                 nq_butterflies_packed<T, 2>(v);
 #pragma unroll
-                for (int j = 0; j < 4; ++j) words[nq_fwht_swizzle(base + j * wp)] = v[j];
+                for (int j = 0; j < 4; ++j) mine[j * step] = v[j];
             } else {
-                v[0] = words[nq_fwht_swizzle(base)];
-                v[1] = words[nq_fwht_swizzle(base + wp)];
+                v[0] = mine[0];
+                v[1] = mine[step];
                 nq_butterflies_packed<T, 1>(v);
-                words[nq_fwht_swizzle(base)] = v[0];
-                words[nq_fwht_swizzle(base + wp)] = v[1];
+                mine[0] = v[0];
+                mine[step] = v[1];
             }
         }
         __syncthreads();
@@ -261,7 +269,7 @@ __device__ __forceinline__ void nq_silu_mul8(float gate[8], const float up[8]) {
 // The 8 consecutive elements of group g (elements 8g .. 8g+7) of a packed row buffer, as float32.
 template <typename T>
 __device__ __forceinline__ void nq_fwht_packed_group(const uint32_t* words, int g, float v[8]) {
-    const uint4 w = *reinterpret_cast<const uint4*>(words + nq_fwht_swizzle(4 * g));
+    const uint4 w = *reinterpret_cast<const uint4*>(words + nq_fwht_pad(4 * g));
     NqPacked<T>::to_floats(w.x, v[0], v[1]);
     NqPacked<T>::to_floats(w.y, v[2], v[3]);
     NqPacked<T>::to_floats(w.z, v[4], v[5]);
@@ -269,15 +277,21 @@ __device__ __forceinline__ void nq_fwht_packed_group(const uint32_t* words, int 
 }
 
 // In-place hand-over of a packed transform to a consumer that reads float32: `floats` is a region of `total`
-// floats whose UPPER half holds the packed words of nq_fwht_groups_packed (words = floats + total / 2 as
-// 32-bit words).  Every value is divided by `root` (IEEE), rounded to T and written as float32 at its element
-// index.  Chunks of 8 groups per thread go front to back; inside a chunk all words are read before the first
-// float is written (one barrier), and the floats of a chunk never reach words of a later chunk: chunk c ends
-// at byte 4 (c+1) C of the region, the words not yet read start at byte 2 total + 2 (c+1) C >= that.
+// floats whose END holds the padded packed words of nq_fwht_groups_packed (nq_fwht_words_in_place).  Every
+// value is divided by `root` (IEEE), rounded to T and written as float32 at its element index.  Chunks of 8
+// groups per thread (C elements) go front to back; inside a chunk all words are read before the first float is
+// written (one barrier), and the floats of a chunk never reach words of a later chunk: chunk c ends at byte
+// 4 (c+1) C of the region, the words not yet read start at byte ~1.75 total + 2.25 (c+1) C, which is larger
+// while elements remain ((c+1) C <= total - C, against at most 28 bytes of rounding of the start).
 // Called by all `nthreads` threads of the CTA; ends with a barrier.
+__device__ __forceinline__ uint32_t* nq_fwht_words_in_place(float* floats, int total) {
+    const int start = (total - nq_fwht_padded_words(total)) & ~3;  // 16-byte aligned, never negative for total >= 16
+    return reinterpret_cast<uint32_t*>(floats + (start > 0 ? start : 0));
+}
+
 template <typename T>
 __device__ __forceinline__ void nq_fwht_packed_to_floats(float* floats, int total, float root, float inv_root) {
-    const uint32_t* words = reinterpret_cast<const uint32_t*>(floats + (total >> 1));
+    const uint32_t* words = nq_fwht_words_in_place(floats, total);
     const int groups = total >> 3;
     const int nthreads = blockDim.x;
     for (int g0 = 0; g0 < groups; g0 += nthreads * 8) {
@@ -285,7 +299,7 @@ __device__ __forceinline__ void nq_fwht_packed_to_floats(float* floats, int tota
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             const int g = g0 + i * nthreads + threadIdx.x;
-            w[i] = g < groups ? *reinterpret_cast<const uint4*>(words + nq_fwht_swizzle(4 * g)) : make_uint4(0, 0, 0, 0);
+            w[i] = g < groups ? *reinterpret_cast<const uint4*>(words + nq_fwht_pad(4 * g)) : make_uint4(0, 0, 0, 0);
         }
         __syncthreads();
 #pragma unroll
