@@ -300,7 +300,7 @@ class BatchedNQKVLlamaRunner:
         torch.cuda.synchronize(self.device)
         self._restore(state)
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
+        with torch.cuda.graph(graph, stream=self._capture_stream()):
             self._logits_step()
         torch.cuda.synchronize(self.device)
         self._restore(state)
@@ -409,11 +409,18 @@ class BatchedNQKVLlamaRunner:
         torch.cuda.synchronize(self.device)
         self._restore(state)
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
+        with torch.cuda.graph(graph, stream=self._capture_stream()):
             self._step()
         torch.cuda.synchronize(self.device)
         self._restore(state)
         self.graph = graph
+
+    def _capture_stream(self) -> torch.cuda.Stream:
+        """The step is captured on a stream of the highest priority, so that its kernels keep their priority as
+        graph nodes over the weight decodes that run beside them on the lowest one."""
+        if getattr(self, "_step_stream", None) is None:
+            self._step_stream = torch.cuda.Stream(self.device, priority=-5)
+        return self._step_stream
 
     def decode(self, token: torch.Tensor | None = None, *, positions: torch.Tensor | None = None,
                active_mask: torch.Tensor | None = None, valid_lengths: torch.Tensor | None = None) -> torch.Tensor:

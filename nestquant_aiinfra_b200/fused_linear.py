@@ -241,6 +241,7 @@ class FusedNQRTLinear(nn.Module):
         self._group: "SharedProjectionGroup | None" = None
         self._group_index = 0
         self._ahead: "_AheadUnit | None" = None  # set by WeightDecodeAhead
+        self._ahead_trigger = None  # (scheduler, layer) on a layer's first projection, see WeightDecodeAhead.EARLY_START
         self.input_transform_cache = input_transform_cache
         self.output_dtype = output_dtype
         self.compute_backend = compute_backend
@@ -354,6 +355,10 @@ class FusedNQRTLinear(nn.Module):
 
     def forward(self, inputs: torch.Tensor) -> torch.Tensor:
         self._check_inputs(inputs)
+        if self._ahead_trigger is not None and inputs.ndim >= 2 and inputs.shape[-2] == 1:
+            # first projection of a decoder layer in a decode step: the weights the layer needs after its attention
+            # start decoding on the second stream now
+            self._ahead_trigger[0].launch(self._ahead_trigger[1], inputs.numel() // self.in_features)
         original_dtype = inputs.dtype
         # The rotation of the input runs inside the encoder launch when the sizes allow it
         # (bit-identical to hadamard() followed by the encoder); otherwise as its own launch.
@@ -451,7 +456,8 @@ class WeightDecodeAhead:
 
     The paged attention of a decode step leaves SMs idle towards its end (sequences of different lengths);
     the weight decodes of ``o_proj``, gate / up and ``down_proj`` of the same layer do not depend on it.
-    ``launch(layer)`` -- called right before the layer's attention is queued -- forks a second stream
+    ``launch(layer)`` -- called at the layer's first projection of a decode step (``EARLY_START``), or right
+    before the layer's attention is queued -- forks a second stream of the lowest priority
     from the current one, queues those decodes there into scratch matrices shared by all layers, and
     the projections then wait for "their" decode and run the tensor-core GEMM on the scratch (the
     resident entry of the library).  Same kernels on the same operands as the plain sequence, so the
@@ -461,18 +467,31 @@ class WeightDecodeAhead:
     """
 
     MIN_ROWS = 8
+    # Fork at the layer's FIRST projection (a decode step's q_proj call) instead of right before its attention: the
+    # decodes then also fill the SMs that the short launches leading up to the attention leave idle.  This only pays
+    # because the second stream has the lowest priority and the runner captures its step on a stream of the highest
+    # one: with equal priorities the full-grid decode kernels take the SMs from exactly those launches.
+    EARLY_START = True
     _BEFORE_ATTENTION = ("q_proj", "k_proj", "v_proj")
 
     def __init__(self, layers, device: torch.device | str) -> None:
         self.device = torch.device(device)
-        self.stream = torch.cuda.Stream(self.device)
+        self.stream = torch.cuda.Stream(self.device, priority=0)  # lowest: the decodes only fill what the step leaves idle
         self.layers: list[list[_AheadUnit]] = []
         sizes: list[int] = []
-        for layer in layers:
+        self.triggers: list[tuple[FusedNQRTLinear, int]] = []
+        for layer_index, layer in enumerate(layers):
             units: list[_AheadUnit] = []
             seen: set[int] = set()
+            first = True
             for name, module in layer.named_modules():
-                if not isinstance(module, FusedNQRTLinear) or any(part in self._BEFORE_ATTENTION for part in name.split(".")):
+                if not isinstance(module, FusedNQRTLinear):
+                    continue
+                if any(part in self._BEFORE_ATTENTION for part in name.split(".")):
+                    if first and self.EARLY_START:
+                        module._ahead_trigger = (self, layer_index)
+                        self.triggers.append((module, layer_index))
+                    first = False
                     continue
                 group = module._group
                 if group is not None:
@@ -504,6 +523,8 @@ class WeightDecodeAhead:
     def launch(self, layer_index: int, rows: int) -> None:
         if rows < self.MIN_ROWS or not 0 <= layer_index < len(self.layers) or not self.layers[layer_index]:
             return
+        if any(unit.armed for unit in self.layers[layer_index]):
+            return  # already queued for this step
         main = torch.cuda.current_stream(self.device)
         fork = torch.cuda.Event()
         fork.record(main)
@@ -518,11 +539,15 @@ class WeightDecodeAhead:
             for unit in units:
                 unit.owner._ahead = None
                 unit.armed = False
+        for module, _ in self.triggers:
+            module._ahead_trigger = None
 
     def attach(self) -> None:
         for units in self.layers:
             for unit in units:
                 unit.owner._ahead = unit
+        for module, layer_index in self.triggers:
+            module._ahead_trigger = (self, layer_index)
 
 
 def keep_decoded_weights_(model: nn.Module, device: torch.device | str | None = None) -> int:
