@@ -1416,7 +1416,7 @@ def main() -> None:
                         help="tensor-parallel sum after o_proj / down_proj: this repository's peer-memory kernel "
                              "(falls back to NCCL when symmetric memory is unavailable or a wait gives up) or NCCL; "
                              "the other one is timed too and reported under all_reduce.other_collective")
-    parser.add_argument("--tp-decode-ahead", choices=("on", "off"), default="off",
+    parser.add_argument("--tp-decode-ahead", choices=("on", "off"), default="on",
                         help="tensor-parallel decode: decode the shard's o / gate-up / down weights of a layer on a "
                              "second stream during the layer's attention (as the single-GPU runner does by default)")
     parser.add_argument("--tp-resident", action="store_true",
