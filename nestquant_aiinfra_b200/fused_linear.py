@@ -520,11 +520,12 @@ class WeightDecodeAhead:
     def scratch_bytes(self) -> int:
         return sum(t.numel() * 2 for t in self.scratch)
 
-    def launch(self, layer_index: int, rows: int) -> None:
+    def launch(self, layer_index: int, rows: int, *, at_attention: bool = False) -> None:
         if rows < self.MIN_ROWS or not 0 <= layer_index < len(self.layers) or not self.layers[layer_index]:
             return
-        if any(unit.armed for unit in self.layers[layer_index]):
-            return  # already queued for this step
+        if at_attention and self.triggers and any(unit.armed for unit in self.layers[layer_index]):
+            return  # queued at the layer's first projection already
+        # (the first caller of a layer always queues: units a failed step left armed are decoded afresh)
         main = torch.cuda.current_stream(self.device)
         fork = torch.cuda.Event()
         fork.record(main)

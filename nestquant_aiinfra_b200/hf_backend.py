@@ -530,7 +530,7 @@ class BatchedNQKVLlamaCache(Cache):
                  else hadamard(query_states.float()).to(self.dtype))[:, :, 0].contiguous()
         if self.decode_ahead is not None:
             # the weights the layer needs after its attention are decoded on a second stream meanwhile
-            self.decode_ahead.launch(layer_idx, query.shape[0])
+            self.decode_ahead.launch(layer_idx, query.shape[0], at_attention=True)
         workspace = self._decode_workspace
         if query.shape[0] != workspace.batch_size:
             workspace = BatchedNQKVAttentionWorkspace.create(self.layer_caches[layer_idx], batch_size=query.shape[0],
